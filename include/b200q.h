@@ -1,0 +1,152 @@
+/* b200q - C ABI of the sm_100a packed-GGUF quantized-inference kernels.
+ *
+ * Every entry point
+ *   - takes plain device pointers and sizes (no framework types),
+ *   - takes the CUDA stream as a `void*` (a `cudaStream_t`; NULL = legacy default stream),
+ *   - only enqueues work: no allocation, no synchronisation, no host read-back, so calls
+ *     can be captured into a CUDA graph (exceptions are stated on the function),
+ *   - validates its arguments on the host BEFORE any launch and returns
+ *       0 = ok, 1 = invalid argument, 2 = CUDA launch/runtime error, 3 = unsupported shape;
+ *     `b200q_last_error()` gives the message of the calling thread's last failure.
+ *
+ * The packed byte layouts are the GGUF block layouts of the reference
+ * (mini_llm/ops/quantized_weight.py:24-37,208-250); format ids follow the reference's CPU
+ * library and Triton decoder (mini_llm/ops/native_packed_cpu.py:25-26,
+ * mini_llm/ops/quantized_linear.py:34).
+ */
+#ifndef B200Q_H
+#define B200Q_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* packed formats */
+#define B200Q_Q8_0 0
+#define B200Q_Q4_K 2
+#define B200Q_Q5_K 4
+#define B200Q_Q6_K 5
+
+/* activation / output element types */
+#define B200Q_F32 0
+#define B200Q_F16 1
+#define B200Q_BF16 2
+
+/* return codes */
+#define B200Q_OK 0
+#define B200Q_EINVAL 1
+#define B200Q_ECUDA 2
+#define B200Q_EUNSUPPORTED 3
+
+/* Library / build identification; also proves the shared object loaded. */
+int b200q_abi_version(void);
+const char *b200q_last_error(void);
+
+/* Device status word written by kernels whose bounded waits gave up (0 = healthy).
+ * Reads the word with a blocking copy: not capturable. */
+int b200q_device_status(int *status_out);
+
+/* out[n,k] (fp32) = dequantised W. Replaces PackedGGUFWeight.dequantize_reference
+ * (mini_llm/ops/quantized_weight.py:166-250) as a device kernel; bit-exact with it. */
+int b200q_dequantize(const void *w, int fmt, int64_t n, int k, float *out, void *stream);
+
+/* y[m,n] = x[m,k] @ W[n,k]^T, FP32 accumulation; W is read once for up to 8 tokens.
+ * Replaces quantized_linear's device branch and its Triton kernel
+ * (mini_llm/ops/quantized_linear.py:174-192,272-335) and has the argument order of the
+ * reference's CPU ABI mylocal_packed_gemv (mini_llm/ops/native_packed_cpu.cpp:206-216). */
+int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype, int m, void *y,
+               int y_dtype, void *stream);
+
+/* h[m,f] = silu(x @ G^T) * (x @ U^T); gate and up may use different formats.
+ * Replaces quantized_swiglu and _packed_gate_up_swiglu_kernel
+ * (mini_llm/ops/quantized_linear.py:194-221,338-400). */
+int b200q_swiglu(const void *gate, int gate_fmt, const void *up, int up_fmt, int f, int k,
+                 const void *x, int x_dtype, int m, void *h, int h_dtype, void *stream);
+
+/* y = x * rsqrt(mean(x^2)+eps) * gamma; x fp32/bf16/fp16 rows of length d, gamma fp32 or the
+ * output type. Replaces RMSNormInference.forward (mini_llm/ops/rmsnorm_inference.py:80-119,
+ * 304-318). */
+int b200q_rmsnorm(const void *x, int x_dtype, const void *gamma, int gamma_dtype, int rows, int d,
+                  float eps, void *y, int y_dtype, void *stream);
+
+/* res_out(fp32) = residual(fp32) + alpha*branch; y = rmsnorm(res_out)*gamma.
+ * Replaces forward_residual_add / residual_add_rmsnorm_f32_bf16
+ * (mini_llm/ops/rmsnorm_inference.py:228-252,525-539). res_out may alias residual. */
+int b200q_residual_rmsnorm(const float *residual, const void *branch, int branch_dtype, float alpha,
+                           const void *gamma, int gamma_dtype, int rows, int d, float eps,
+                           float *res_out, void *y, int y_dtype, void *stream);
+
+/* logits[t,e] (fp32) = x[t,d] @ Wr[d,e] + bias[e] (bias may be NULL); FP32 accumulation in
+ * ascending d. Replaces the router logits product of RouterInference.forward
+ * (mini_llm/ops/router_inference.py:38-46) and _vector_matmul
+ * (mini_llm/ops/inference_matmul.py:17-41). */
+int b200q_router_logits(const void *x, int x_dtype, int t, int d, const float *wr, const float *bias,
+                        int e, float *logits, void *stream);
+
+/* scale[t] (fp32) = sigmoid(x[t,:] . gate[:]) - the admission weight of the shared expert
+ * (mini_llm/external/qwen3next_moe.py:145-146). */
+int b200q_shared_gate(const void *x, int x_dtype, int t, int d, const float *gate, float *scale,
+                      void *stream);
+
+/* Per row: softmax over all n logits, top-k by descending logit (ties -> lower id, NaN last),
+ * weights = p[ids]; if renormalize != 0, divided by max(sum, floor_value).
+ * Replaces expert_topk_forward + renormalisation (mini_llm/ops/router.py:21-43,
+ * mini_llm/ops/router_inference.py:47-60) and the fused decode kernel normalized_topk
+ * (mini_llm/ops/router_decode.py:16-96) for any number of rows. n <= 4096, k <= 32. */
+int b200q_router_topk(const float *logits, int rows, int n, int k, int renormalize,
+                      float floor_value, float *weights, int64_t *ids, void *stream);
+
+/* Device routing plan: stable counting sort of the rows*k assignments by expert id.
+ * Outputs (all device, caller-allocated):
+ *   counts[e]            assignments per expert
+ *   offsets[e+1]         exclusive prefix sum
+ *   order[rows*k]        flat assignment index (row*k+slot) at each sorted position
+ *   inv[rows*k]          sorted position of each flat assignment (inverse of order)
+ *   seg_expert/seg_begin/seg_count[max_segments] + num_segments[1]
+ *                        compacted list of active experts, ascending id, each split into
+ *                        runs of at most seg_cap assignments
+ *   status[1]            0; 1 if an id was outside [0,e) (it is then counted as expert 0);
+ *                        2 if max_segments was too small (extra segments are dropped)
+ * Replaces RoutingPlan.from_router_outputs (mini_llm/ops/routing_plan.py:52-118) and
+ * plan_routes (mini_llm/ops/device_expert_plan.py:17-36) without the host round trip. */
+int b200q_moe_plan(const void *ids, int ids_is_i64, int rows, int k, int e, int seg_cap,
+                   int32_t *counts, int32_t *offsets, int32_t *order, int32_t *inv,
+                   int32_t *seg_expert, int32_t *seg_begin, int32_t *seg_count,
+                   int32_t *num_segments, int max_segments, int32_t *status, void *stream);
+
+/* Grouped gate/up + SwiGLU over the plan's segments:
+ *   hbuf[pos, f] (fp32) = silu(x[token(pos)] . G_e) * (x[token(pos)] . U_e)
+ * for every sorted position pos of every segment; token(pos) = order[pos] / k.
+ * Expert e's matrices start at gate_base + e*gate_stride (bytes) etc.
+ * Replaces _grouped_gate_up (mini_llm/ops/grouped_quantized_experts.py:31-43) and the
+ * per-expert loop of ExpertsInference.forward (mini_llm/ops/experts_inference.py:293-310). */
+int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, const void *up_base,
+                      int64_t up_stride, int up_fmt, int f, int d, const void *x, int x_dtype, int k,
+                      const int32_t *order, const int32_t *seg_expert, const int32_t *seg_begin,
+                      const int32_t *seg_count, const int32_t *num_segments, int max_segments,
+                      float *hbuf, void *stream);
+
+/* Grouped down projection with the route weight applied and stored per assignment:
+ *   terms[pos, d] (fp32) = (hbuf[pos] . D_e) * route[order[pos]]
+ * Replaces _grouped_down_weighted (mini_llm/ops/grouped_quantized_experts.py:45-68). */
+int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, int d, int f,
+                   const float *hbuf, const float *route, const int32_t *order,
+                   const int32_t *seg_expert, const int32_t *seg_begin, const int32_t *seg_count,
+                   const int32_t *num_segments, int max_segments, float *terms, void *stream);
+
+/* out[row, d] = sum over the row's k assignments of terms[pos], added one by one in
+ * ascending expert id starting from zero (plain FP32 adds, no FMA, no tree), plus an optional
+ * extra[row,d]*extra_scale[row] term added last (the shared expert). `inv` maps the flat
+ * assignment index to its sorted position (inverse of `order`).
+ * Replaces _ordered_reduce (mini_llm/ops/grouped_quantized_experts.py:70-79) and the ordered
+ * scatter-add of ExpertsInference.forward (mini_llm/ops/experts_inference.py:293-310). */
+int b200q_moe_combine(const float *terms, const int32_t *inv, int rows, int k, int d,
+                      const float *extra, const float *extra_scale, void *out, int out_dtype,
+                      void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H */

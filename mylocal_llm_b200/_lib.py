@@ -1,0 +1,97 @@
+"""ctypes binding of ``libb200q.so`` (the C ABI declared in ``include/b200q.h``).
+
+The library is the only compute back end of this package: there is no Triton path, no
+PyTorch-eager path and no CPU fallback. If the shared object is missing the loader tries one
+in-tree nvcc build and otherwise raises; nothing silently degrades.
+"""
+
+import ctypes
+import threading
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libb200q.so"
+
+FORMAT_ID = {"Q8_0": 0, "Q4_K": 2, "Q5_K": 4, "Q6_K": 5}
+DTYPE_ID = {"float32": 0, "float16": 1, "bfloat16": 2}
+
+_c_int, _c_i64, _c_f32, _ptr = ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p
+
+# name -> argument types (all return int unless noted); mirrors include/b200q.h
+SIGNATURES = {
+    "b200q_abi_version": [],
+    "b200q_device_status": [_ptr],
+    "b200q_dequantize": [_ptr, _c_int, _c_i64, _c_int, _ptr, _ptr],
+    "b200q_gemv": [_ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr, _c_int, _ptr],
+    "b200q_swiglu": [_ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr, _c_int, _ptr],
+    "b200q_rmsnorm": [_ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _c_f32, _ptr, _c_int, _ptr],
+    "b200q_residual_rmsnorm": [_ptr, _ptr, _c_int, _c_f32, _ptr, _c_int, _c_int, _c_int, _c_f32, _ptr, _ptr,
+                               _c_int, _ptr],
+    "b200q_router_logits": [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _ptr, _ptr],
+    "b200q_shared_gate": [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr],
+    "b200q_router_topk": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_f32, _ptr, _ptr, _ptr],
+    "b200q_moe_plan": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+                       _ptr, _c_int, _ptr, _ptr],
+    "b200q_moe_gate_up": [_ptr, _c_i64, _c_int, _ptr, _c_i64, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int,
+                          _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr],
+    "b200q_moe_down": [_ptr, _c_i64, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
+                       _ptr, _ptr],
+    "b200q_moe_combine": [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr],
+}
+
+_LOCK = threading.Lock()
+_LIB = None
+
+
+class B200QError(RuntimeError):
+    """A b200q entry point returned a non-zero code."""
+
+
+def load():
+    """Load (building once if absent) and return the ctypes library handle."""
+    global _LIB
+    with _LOCK:
+        if _LIB is not None:
+            return _LIB
+        if not LIB_PATH.exists():
+            from . import build as _build
+            _build.build()
+        lib = ctypes.CDLL(str(LIB_PATH))
+        for name, argtypes in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = _c_int
+        lib.b200q_last_error.argtypes = []
+        lib.b200q_last_error.restype = ctypes.c_char_p
+        _LIB = lib
+        return lib
+
+
+def last_error():
+    return (load().b200q_last_error() or b"").decode("utf-8", "replace")
+
+
+def call(name, *args):
+    """Call an entry point; map its return code to the reference's exception types."""
+    rc = getattr(load(), name)(*args)
+    if rc == 0:
+        return
+    message = f"{name}: {last_error()}"
+    if rc == 1:
+        raise ValueError(message)
+    if rc == 3:
+        raise NotImplementedError(message)
+    raise B200QError(message)
+
+
+def current_stream():
+    """Raw handle of the framework's current CUDA stream (the launch stream of every call)."""
+    import torch
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def device_status():
+    """Blocking read of the device status word (0 = no kernel gave up on a wait)."""
+    value = ctypes.c_int(0)
+    call("b200q_device_status", ctypes.byref(value))
+    return value.value

@@ -1,0 +1,143 @@
+// Shared device/host helpers for the b200q kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200q.h"
+
+namespace b200q {
+
+// ---------------------------------------------------------------------------------------------
+// Formats (block layouts: mini_llm/ops/quantized_weight.py:24-37 of the reference)
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ constexpr int fmt_elems(int fmt) { return fmt == B200Q_Q8_0 ? 32 : 256; }
+__host__ __device__ constexpr int fmt_bytes(int fmt) {
+    return fmt == B200Q_Q8_0 ? 34 : fmt == B200Q_Q4_K ? 144 : fmt == B200Q_Q5_K ? 176
+         : fmt == B200Q_Q6_K ? 210 : 0;
+}
+inline bool fmt_valid(int fmt) {
+    return fmt == B200Q_Q8_0 || fmt == B200Q_Q4_K || fmt == B200Q_Q5_K || fmt == B200Q_Q6_K;
+}
+inline bool dtype_valid(int dt) { return dt == B200Q_F32 || dt == B200Q_F16 || dt == B200Q_BF16; }
+inline size_t dtype_size(int dt) { return dt == B200Q_F32 ? 4 : 2; }
+
+// Host-side error reporting (thread local; message of the last failing call).
+void set_error(const char *fmt, ...);
+int fail(int rc, const char *fmt, ...);
+int check_launch(const char *what);
+
+// Device status word: kernels that give up on a bounded wait store a code here.
+int *device_status_word();
+constexpr int STATUS_WAIT_FULL = 101;   // consumer gave up waiting for a staged tile
+constexpr int STATUS_WAIT_EMPTY = 102;  // producer gave up waiting for a free stage
+
+constexpr int NUM_SMS_FALLBACK = 148;
+int sm_count();
+
+// ---------------------------------------------------------------------------------------------
+// Small device utilities
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ float half_bits_to_float(uint32_t bits16) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16)));
+}
+
+__device__ __forceinline__ float load_as_float(const void *p, int dtype, size_t i) {
+    if (dtype == B200Q_F32) return static_cast<const float *>(p)[i];
+    if (dtype == B200Q_F16) return __half2float(static_cast<const __half *>(p)[i]);
+    return __bfloat162float(static_cast<const __nv_bfloat16 *>(p)[i]);
+}
+
+__device__ __forceinline__ void store_from_float(void *p, int dtype, size_t i, float v) {
+    if (dtype == B200Q_F32) static_cast<float *>(p)[i] = v;
+    else if (dtype == B200Q_F16) static_cast<__half *>(p)[i] = __float2half_rn(v);
+    else static_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// silu(g)*u with an overflow-safe logistic, as the reference's CPU kernel
+// (mini_llm/ops/native_packed_cpu.cpp:236-238).
+__device__ __forceinline__ float swiglu_f32(float g, float u) {
+    float s = g >= 0.0f ? 1.0f / (1.0f + __expf(-g)) : __expf(g) / (1.0f + __expf(g));
+    return (g * s) * u;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// ---------------------------------------------------------------------------------------------
+// mbarrier + bulk-copy (TMA, untiled) wrappers. No cluster multicast anywhere.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Wait with a wall-clock limit. Returns false (and records `code`) instead of spinning forever.
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+            atomicExch(status, code);
+            return false;
+        }
+    }
+}
+
+// 1-D bulk copy global -> this CTA's shared memory; dst, src 16-byte aligned, bytes % 16 == 0.
+__device__ __forceinline__ void bulk_copy_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes,
+                                              uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+}  // namespace b200q

@@ -1,0 +1,205 @@
+"""Quantized GGUF linear / SwiGLU / expert-FFN operators on device-resident packed bytes.
+
+Host-side mirror of the reference's ``mini_llm/ops/quantized_linear.py``:
+
+* ``DevicePackedGGUFWeight`` (:45-74), ``packed_to_device`` (:77-86),
+  ``supports_packed_gpu_type`` / ``SUPPORTED_GPU_PACKED_FORMATS`` (:34-41)
+* ``quantized_linear(x, weight, *, block_k=512, cpu_packed_backend="reference")`` (:272-335)
+* ``quantized_swiglu(x, gate, up, *, block_k=512)`` (:338-400)
+* ``PackedExpertFFNInference(gate, up, down, *, fuse_gate_up=True).forward(x)`` (:403-424)
+
+Contract kept: ``y[..., N] = x[..., K] @ W[N, K].T`` with FP32 accumulation, output dtype =
+activation dtype, activations contiguous 2-D or 3-D, packed bytes never expanded. Device
+arrays are torch CUDA tensors (the reference uses CuPy); the launch stream is torch's current
+stream. ``block_k`` is validated for error parity and otherwise unused (the kernels choose
+their own tiling). A host ``PackedGGUFWeight`` is rejected: there is no CPU execution path.
+"""
+
+from dataclasses import dataclass
+import ctypes
+import math
+
+import numpy as np
+
+from . import _lib
+from .quantized_weight import BLOCK_FORMATS, PackedGGUFWeight
+
+SUPPORTED_GPU_PACKED_FORMATS = frozenset(_lib.FORMAT_ID)
+_BLOCK_K = (256, 512, 1024)
+
+
+def supports_packed_gpu_type(quant_type):
+    """Kernel format support, independent of whether a GPU is present."""
+    return quant_type in SUPPORTED_GPU_PACKED_FORMATS
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _is_cuda_tensor(x):
+    torch = _torch()
+    return isinstance(x, torch.Tensor) and x.is_cuda
+
+
+def _dtype_id(t):
+    name = str(t.dtype).replace("torch.", "")
+    if name not in _lib.DTYPE_ID:
+        raise TypeError("GPU input must be FP16, BF16, or FP32")
+    return _lib.DTYPE_ID[name]
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+@dataclass(frozen=True)
+class DevicePackedGGUFWeight:
+    """GPU-resident packed matrix ``[N, K]``; same layout contract as ``PackedGGUFWeight``."""
+
+    data: object
+    shape: tuple
+    quant_type: str
+
+    def __post_init__(self):
+        if self.quant_type not in BLOCK_FORMATS:
+            raise ValueError(f"Unsupported GGUF type {self.quant_type}")
+        if not supports_packed_gpu_type(self.quant_type):
+            raise NotImplementedError(f"No packed GPU kernel for {self.quant_type}")
+        torch = _torch()
+        if not isinstance(self.data, torch.Tensor) or self.data.dtype != torch.uint8 or not self.data.is_cuda:
+            raise TypeError("Device packed bytes must be a torch CUDA uint8 tensor")
+        if not self.data.is_contiguous():
+            raise ValueError("Device packed bytes must be contiguous")
+        shape = tuple(int(i) for i in self.shape)
+        if len(shape) != 2 or min(shape) <= 0:
+            raise ValueError("Device packed linear weights must be [N, K]")
+        qk, qb = BLOCK_FORMATS[self.quant_type]
+        if shape[-1] % qk or int(self.data.numel()) != math.prod(shape) // qk * qb:
+            raise ValueError("Invalid packed byte length or K block alignment")
+        object.__setattr__(self, "shape", shape)
+
+    @property
+    def nbytes(self):
+        return int(self.data.numel())
+
+
+def packed_bytes_to_device(raw):
+    """Copy a host uint8 array to the current CUDA device (one transfer, no decoding)."""
+    torch = _torch()
+    if not torch.cuda.is_available():
+        raise RuntimeError("Packed GPU weights require a CUDA device")
+    return torch.from_numpy(np.ascontiguousarray(raw, dtype=np.uint8)).cuda()
+
+
+def packed_to_device(weight):
+    """Transfer the packed bytes of one matrix/expert to HBM once."""
+    if not isinstance(weight, PackedGGUFWeight) or len(weight.shape) != 2:
+        raise TypeError("Expected a two-dimensional PackedGGUFWeight")
+    if not supports_packed_gpu_type(weight.quant_type):
+        raise NotImplementedError(f"No packed GPU kernel for {weight.quant_type}")
+    return DevicePackedGGUFWeight(packed_bytes_to_device(weight.data), weight.shape, weight.quant_type)
+
+
+def dequantize_device(data, rows, k, quant_type):
+    """FP32 ``[rows, k]`` CUDA tensor decoded from packed device bytes (verification helper)."""
+    torch = _torch()
+    out = torch.empty((rows, k), dtype=torch.float32, device=data.device)
+    _lib.call("b200q_dequantize", _ptr(data), _lib.FORMAT_ID[quant_type], rows, k, _ptr(out),
+              _lib.current_stream())
+    return out
+
+
+def _check_activation(x, what="Packed linear input"):
+    if isinstance(x, np.ndarray):
+        return
+    if not _is_cuda_tensor(x):
+        raise TypeError(f"{what} must be a NumPy array or a torch CUDA tensor")
+
+
+def quantized_linear(x, weight, *, block_k=512, cpu_packed_backend="reference"):
+    """``x @ weight.T`` for packed GGUF ``[out_features, in_features]`` on the GPU."""
+    _check_activation(x)
+    if x.ndim not in (2, 3):
+        raise ValueError("Expected x as [M, K] or [B, T, K]")
+    if x.shape[-1] != weight.shape[-1]:
+        raise ValueError("Input K does not match packed weight K")
+    if len(weight.shape) != 2:
+        raise ValueError("Packed linear weights must be [N, K]")
+    if isinstance(weight, PackedGGUFWeight):
+        raise RuntimeError("Host-packed weights have no execution path here (no CPU fallback); "
+                           "upload them once with packed_to_device()")
+    if not isinstance(weight, DevicePackedGGUFWeight):
+        raise TypeError("Expected PackedGGUFWeight or DevicePackedGGUFWeight")
+    if not _is_cuda_tensor(x):
+        raise TypeError("Device-packed weight requires a torch CUDA activation tensor (NumPy input given)")
+    if not x.is_contiguous():
+        raise ValueError("GPU input must be a contiguous tensor")
+    dt = _dtype_id(x)
+    if block_k not in _BLOCK_K:
+        raise ValueError("block_k must be 256, 512 or 1024")
+    if x.device != weight.data.device:
+        raise ValueError("activation and packed weight must be on the same CUDA device")
+    torch = _torch()
+    n, k = weight.shape
+    m = int(x.numel()) // k
+    out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    if m:
+        _lib.call("b200q_gemv", _ptr(weight.data), _lib.FORMAT_ID[weight.quant_type], n, k, _ptr(x), dt, m,
+                  _ptr(out), dt, _lib.current_stream())
+    return out.reshape(tuple(x.shape[:-1]) + (n,))
+
+
+def quantized_swiglu(x, gate, up, *, block_k=512):
+    """``SiLU(x @ gate.T) * (x @ up.T)`` in one launch; gate/up formats may differ."""
+    if not isinstance(gate, (PackedGGUFWeight, DevicePackedGGUFWeight)) or not isinstance(
+            up, (PackedGGUFWeight, DevicePackedGGUFWeight)):
+        raise TypeError("gate and up must be packed GGUF weights")
+    if type(gate) is not type(up):
+        raise TypeError("gate and up must both be host-packed or both device-packed")
+    if len(gate.shape) != 2 or up.shape != gate.shape:
+        raise ValueError("gate/up must share two-dimensional [F,K] shape")
+    _check_activation(x, "Quantized SwiGLU input")
+    if x.ndim not in (2, 3):
+        raise ValueError("Expected x as [M,K] or [B,T,K]")
+    f, k = gate.shape
+    if x.shape[-1] != k:
+        raise ValueError("Input K does not match gate/up K")
+    if isinstance(gate, PackedGGUFWeight):
+        raise RuntimeError("Host-packed gate/up have no execution path here (no CPU fallback); "
+                           "upload them once with packed_to_device()")
+    if not _is_cuda_tensor(x) or not x.is_contiguous():
+        raise ValueError("GPU activations must be a contiguous torch CUDA tensor")
+    dt = _dtype_id(x)
+    if block_k not in _BLOCK_K:
+        raise ValueError("block_k must be 256, 512 or 1024")
+    torch = _torch()
+    m = int(x.numel()) // k
+    out = torch.empty((m, f), dtype=x.dtype, device=x.device)
+    if m:
+        _lib.call("b200q_swiglu", _ptr(gate.data), _lib.FORMAT_ID[gate.quant_type], _ptr(up.data),
+                  _lib.FORMAT_ID[up.quant_type], f, k, _ptr(x), dt, m, _ptr(out), dt, _lib.current_stream())
+    return out.reshape(tuple(x.shape[:-1]) + (f,))
+
+
+class PackedExpertFFNInference:
+    """Three packed projections of one SwiGLU expert (gate/up ``[F, D]``, down ``[D, F]``)."""
+
+    def __init__(self, gate, up, down, *, fuse_gate_up=True):
+        self.gate, self.up, self.down = gate, up, down
+        self.fuse_gate_up = bool(fuse_gate_up)
+        if gate.shape != up.shape:
+            raise ValueError("Gate and up projections must have identical dimensions")
+        if down.shape != (gate.shape[1], gate.shape[0]):
+            raise ValueError("Down projection dimensions must be transposed")
+
+    def forward(self, x):
+        if self.fuse_gate_up:
+            h = quantized_swiglu(x, self.gate, self.up)
+        else:
+            torch = _torch()
+            g = quantized_linear(x, self.gate).float()
+            u = quantized_linear(x, self.up).float()
+            h = (torch.nn.functional.silu(g) * u).to(x.dtype)
+        return quantized_linear(h.contiguous(), self.down)
