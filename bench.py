@@ -1,0 +1,344 @@
+#!/usr/bin/env python
+"""Benchmark of the packed-GGUF hot path on B200 (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A *step* is one pass of the hot path over one batch of synthetic input. The default workload
+is the K-quant decode GEMV of the baseline's second configuration (W [8192 x 2048], Q4_K,
+bf16 activations, M = 1): one step runs the GEMV once over each of ``copies`` distinct weight
+copies whose total size exceeds twice the L2 capacity, so every launch streams its weights
+from HBM. ``value`` is algorithmic GB/s (packed bytes + activations + outputs per launch) with
+everything resident in HBM; ``e2e`` is the same quantity through the operator API with the
+activations coming from pinned host memory and the outputs copied back every step.
+
+With N > 1 (launched by torchrun, one rank per GPU) the dense GEMV does not shard: every rank
+runs an independent replica (weak scaling, no collective on the data path) and the job value is
+the sum. ``--impl reference`` times the reference's own CPU kernels (oracle/_ref, else the
+plain-C port) on the host cores instead.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+L2_BYTES = 126 * 1024 * 1024
+BLOCKS = {"Q8_0": (32, 34), "Q4_K": (256, 144), "Q5_K": (256, 176), "Q6_K": (256, 210)}
+
+WORKLOADS = {
+    # name: (format, n, k, m, activation dtype)
+    "gemv_q4k_8192x2048_m1": ("Q4_K", 8192, 2048, 1, "bfloat16"),
+    "gemv_q4k_2048x8192_m1": ("Q4_K", 2048, 8192, 1, "bfloat16"),
+    "gemv_q5k_8192x2048_m1": ("Q5_K", 8192, 2048, 1, "bfloat16"),
+    "gemv_q6k_8192x2048_m1": ("Q6_K", 8192, 2048, 1, "bfloat16"),
+    "gemv_q4k_8192x2048_m8": ("Q4_K", 8192, 2048, 8, "bfloat16"),
+    "gemv_q8_0_4096x4096_m1": ("Q8_0", 4096, 4096, 1, "float32"),
+    "gemv_q8_0_4096x4096_m8": ("Q8_0", 4096, 4096, 8, "float32"),
+    "gemv_q4k_65536x8192_m1": ("Q4_K", 65536, 8192, 1, "bfloat16"),
+}
+DEFAULT_WORKLOAD = "gemv_q4k_8192x2048_m1"
+
+
+def packed_bytes(fmt, n, k):
+    qk, qb = BLOCKS[fmt]
+    return n * k // qk * qb
+
+
+def algorithmic_bytes(fmt, n, k, m, act_bytes):
+    return packed_bytes(fmt, n, k) + m * k * act_bytes + m * n * act_bytes
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            data = json.loads(path.read_text())
+            return float(data["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        clocks, max_clock, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                max_clock = float(parts[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+# ------------------------------------------------------------------------------ CPU reference arm
+def cpu_threads():
+    return max(1, len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
+
+
+def cpu_gemv_throughput(fmt, n, k, m, act_bytes, seconds):
+    """Time the reference's CPU GEMV (row-sliced over all host threads) for about `seconds`."""
+    from oracle import build_oracle as bo
+    from mylocal_llm_b200.quantize import random_packed
+    handle = bo.load_ref()
+    kind = "reference"
+    if handle is None:
+        handle = bo.load_port()
+        kind = "port"
+    _, gemv, _ = handle
+    rows = min(n, 2048)                                   # bounded sample of the weight rows
+    w = random_packed(fmt, (rows, k), seed=0, d=0.01, dmin=0.005)
+    x = np.random.default_rng(1).normal(0, 1, (m, k)).astype(np.float32)
+    threads = cpu_threads()
+    rb = w.nbytes // rows
+    bounds = np.linspace(0, rows, threads + 1).astype(int)
+    outs = [np.empty((m, max(1, b - a)), np.float32) for a, b in zip(bounds[:-1], bounds[1:])]
+    fmt_id = bo.FORMAT_ID[fmt]
+
+    def work(i):
+        a, b = int(bounds[i]), int(bounds[i + 1])
+        if b > a:
+            gemv(w.data.ctypes.data + a * rb, fmt_id, b - a, k, x.ctypes.data, m, outs[i].ctypes.data)
+
+    from concurrent.futures import ThreadPoolExecutor
+    pool = ThreadPoolExecutor(threads)
+    list(pool.map(work, range(threads)))                  # warm-up
+    passes, t0 = 0, time.perf_counter()
+    while True:
+        list(pool.map(work, range(threads)))
+        passes += 1
+        elapsed = time.perf_counter() - t0
+        if elapsed >= seconds:
+            break
+    pool.shutdown()
+    per_pass = algorithmic_bytes(fmt, rows, k, m, act_bytes)
+    gbs = per_pass * passes / elapsed / 1e9
+    sample = f"{passes} passes over {rows} of {n} rows ({fmt}, K={k}, M={m}) in {elapsed:.1f} s"
+    return gbs, kind, threads, sample, elapsed / passes
+
+
+def run_reference_arm(args, name):
+    fmt, n, k, m, act = WORKLOADS[name]
+    act_bytes = 4 if act == "float32" else 2
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per_step = max(1.0, 20.0 / max(1, args.steps + args.warmup))
+    results = [cpu_gemv_throughput(fmt, n, k, m, act_bytes, per_step) for _ in range(args.warmup + args.steps)]
+    timed = results[args.warmup:]
+    gbs = statistics.mean(r[0] for r in timed)
+    kind, threads, sample = timed[0][1], timed[0][2], timed[0][3]
+    line = {
+        "impl": "reference", "metric": "quant-GEMV HBM GB/s (algorithmic bytes per launch / time)",
+        "value": round(gbs, 3), "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(1e3 * statistics.mean(r[4] for r in timed), 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "format": fmt, "n": n, "k": k, "m": m, "activation": act,
+                   "l2": "CPU run; each step is a bounded sample of the workload"},
+        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------- GPU arm
+def run_gpu_arm(args, name):
+    import torch
+    import torch.distributed as dist
+    from mylocal_llm_b200 import packed_to_device, quantized_linear
+    from mylocal_llm_b200.quantize import random_packed
+
+    fmt, n, k, m, act = WORKLOADS[name]
+    act_dtype = getattr(torch, act)
+    act_bytes = 4 if act == "float32" else 2
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the kernels)")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    wbytes = packed_bytes(fmt, n, k)
+    copies = max(2, -(-2 * L2_BYTES // wbytes))
+    copies = min(copies, 64)
+    base = random_packed(fmt, (n, k), seed=1234 + rank, d=0.01, dmin=0.005)
+    weights = []
+    for c in range(copies):
+        weights.append(packed_to_device(base))   # a distinct HBM allocation per copy
+    rng = np.random.default_rng(7 + rank)
+    host_x = torch.from_numpy(rng.normal(0, 1, (copies, m, k)).astype(np.float32)).to(act_dtype).pin_memory()
+    dev_x = host_x.cuda()
+    host_y = torch.empty((copies, m, n), dtype=act_dtype).pin_memory()
+
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        outs = [quantized_linear(dev_x[c], weights[c]) for c in range(copies)]   # warm-up, lazy init
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            outs = [quantized_linear(dev_x[c], weights[c]) for c in range(copies)]
+        out_stack = outs
+
+        def barrier():
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        # ---- device-resident throughput
+        for _ in range(max(3, args.warmup)):
+            graph.replay()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        stop.record(stream)
+        barrier()
+        dev_ms = start.elapsed_time(stop)
+
+        # ---- end to end: pinned host activations in, outputs back, every step
+        def e2e_step():
+            dev_x.copy_(host_x, non_blocking=True)
+            graph.replay()
+            for c in range(copies):
+                host_y[c].copy_(out_stack[c], non_blocking=True)
+
+        for _ in range(max(3, args.warmup)):
+            e2e_step()
+        barrier()
+        start2, stop2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start2.record(stream)
+        for _ in range(args.steps):
+            e2e_step()
+        stop2.record(stream)
+        barrier()
+        e2e_ms = start2.elapsed_time(stop2)
+        clocks = sampler.stop() if rank == 0 else None
+
+    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = (float(v) for v in times.cpu())
+
+    from mylocal_llm_b200 import _lib
+    status = _lib.device_status()
+    if status:
+        raise SystemExit(f"device status word = {status}: a kernel gave up on a bounded wait")
+
+    if rank == 0:
+        per_launch = algorithmic_bytes(fmt, n, k, m, act_bytes)
+        launches = copies * args.steps
+        job_bytes = per_launch * launches * world
+        value = job_bytes / (dev_ms * 1e-3) / 1e9
+        e2e_value = job_bytes / (e2e_ms * 1e-3) / 1e9
+        peak, peak_kind = measured_peaks()
+        per_gpu = per_launch * launches / (dev_ms * 1e-3) / 1e9
+        want_cpu = world == 1 and not args.skip_cpu_baseline
+        cpu_gbs, cpu_kind, cpu_cores, cpu_sample, _ = (cpu_gemv_throughput(fmt, n, k, m, act_bytes, 12.0)
+                                                       if want_cpu else (None, None, None, None, None))
+        line = {
+            "metric": "quant-GEMV HBM GB/s (algorithmic bytes per launch / time)",
+            "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(dev_ms / args.steps, 5), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": name, "format": fmt, "n": n, "k": k, "m": m, "activation": act,
+                       "copies_per_step": copies, "parallelism": "replicas only" if world > 1 else "single GPU",
+                       "l2": f"{copies} distinct weight copies per step = {copies * wbytes / 1e6:.0f} MB > 2x L2",
+                       "timing": "CUDA graph of one step, CUDA events on the launch stream"},
+            "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
+                         "frac": round(per_gpu / peak, 4), "peak_source": f"of {peak_kind}",
+                         "frac_of_nominal_8TBs": round(per_gpu / 8000.0, 4), "traffic": None,
+                         "kernel": "stream_gemv_kernel", "us_per_launch": round(dev_ms * 1e3 / launches, 3),
+                         "algorithmic_bytes_per_launch": per_launch},
+            "e2e": {"value": round(e2e_value, 2), "unit": "GB/s",
+                    "h2d_bytes_per_step": int(host_x.numel() * host_x.element_size()),
+                    "d2h_bytes_per_step": int(host_y.numel() * host_y.element_size())},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        if cpu_gbs is not None:
+            line["cpu_baseline"] = {"value": round(cpu_gbs, 3), "unit": "GB/s", "cores": cpu_cores,
+                                    "kind": cpu_kind, "sample": cpu_sample}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--skip-cpu-baseline", action="store_true",
+                    help="omit the host-core baseline leg (exploratory runs only)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args, args.workload)
+    else:
+        run_gpu_arm(args, args.workload)
+
+
+if __name__ == "__main__":
+    main()

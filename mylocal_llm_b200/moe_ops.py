@@ -1,0 +1,143 @@
+"""Thin torch-tensor wrappers over the MoE entry points of the C ABI.
+
+Each function allocates its outputs with torch, passes raw pointers to ``libb200q.so`` and
+returns torch tensors; all work is enqueued on torch's current stream and nothing here
+synchronises or reads device memory back.
+"""
+
+import ctypes
+from dataclasses import dataclass
+
+from . import _lib
+
+SEGMENT_CAP = 8  # tokens of one expert handled per pass of the grouped kernels
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _dtype_id(t):
+    name = str(t.dtype).replace("torch.", "")
+    if name not in _lib.DTYPE_ID:
+        raise TypeError("activations must be FP16, BF16 or FP32")
+    return _lib.DTYPE_ID[name]
+
+
+def router_logits(x2d, w_router, bias=None):
+    """FP32 ``x[T,D] @ W[D,E] (+ bias)``; W and bias are FP32 device tensors."""
+    torch = _torch()
+    t, d = x2d.shape
+    e = w_router.shape[1]
+    if w_router.dtype != torch.float32 or not w_router.is_contiguous() or w_router.shape[0] != d:
+        raise ValueError("router weight must be a contiguous FP32 [D, E] tensor")
+    out = torch.empty((t, e), dtype=torch.float32, device=x2d.device)
+    _lib.call("b200q_router_logits", _ptr(x2d), _dtype_id(x2d), t, d, _ptr(w_router), _ptr(bias), e, _ptr(out),
+              _lib.current_stream())
+    return out
+
+
+def router_topk(logits2d, k, *, renormalize, floor=1e-30):
+    """(FP32 weights [T,k], int64 ids [T,k]) from FP32 logits [T,E]."""
+    torch = _torch()
+    if logits2d.dtype != torch.float32 or not logits2d.is_contiguous():
+        raise ValueError("logits must be a contiguous FP32 tensor")
+    t, e = logits2d.shape
+    weights = torch.empty((t, k), dtype=torch.float32, device=logits2d.device)
+    ids = torch.empty((t, k), dtype=torch.int64, device=logits2d.device)
+    _lib.call("b200q_router_topk", _ptr(logits2d), t, e, int(k), 1 if renormalize else 0, float(floor),
+              _ptr(weights), _ptr(ids), _lib.current_stream())
+    return weights, ids
+
+
+def shared_gate(x2d, gate_vec):
+    """sigmoid(x[T,D] . g[D]) as FP32 [T]."""
+    torch = _torch()
+    t, d = x2d.shape
+    out = torch.empty((t,), dtype=torch.float32, device=x2d.device)
+    _lib.call("b200q_shared_gate", _ptr(x2d), _dtype_id(x2d), t, d, _ptr(gate_vec), _ptr(out),
+              _lib.current_stream())
+    return out
+
+
+@dataclass
+class DeviceRoutingPlan:
+    """Device-resident routing plan (all int32 CUDA tensors); see ``b200q_moe_plan``."""
+
+    rows: int
+    k: int
+    n_experts: int
+    counts: object
+    offsets: object
+    order: object
+    inv: object
+    seg_expert: object
+    seg_begin: object
+    seg_count: object
+    num_segments: object
+    max_segments: int
+    status: object
+
+
+def max_segments_for(rows, k, n_experts, seg_cap=SEGMENT_CAP):
+    total = rows * k
+    return min(n_experts, total) + total // seg_cap
+
+
+def moe_plan(ids, n_experts, *, workspace=None):
+    """Build the device routing plan for integer ids ``[T,k]`` (int32 or int64)."""
+    torch = _torch()
+    if ids.dtype not in (torch.int32, torch.int64) or not ids.is_contiguous():
+        raise ValueError("expert ids must be a contiguous int32/int64 tensor")
+    rows, k = ids.shape
+    total = rows * k
+    max_seg = max_segments_for(rows, k, n_experts)
+    i32 = dict(dtype=torch.int32, device=ids.device)
+    plan = DeviceRoutingPlan(
+        rows, k, n_experts,
+        torch.empty(n_experts, **i32), torch.empty(n_experts + 1, **i32), torch.empty(total, **i32),
+        torch.empty(total, **i32), torch.empty(max_seg, **i32), torch.empty(max_seg, **i32),
+        torch.empty(max_seg, **i32), torch.empty(1, **i32), max_seg, torch.empty(1, **i32))
+    _lib.call("b200q_moe_plan", _ptr(ids), 1 if ids.dtype == torch.int64 else 0, rows, k, n_experts, SEGMENT_CAP,
+              _ptr(plan.counts), _ptr(plan.offsets), _ptr(plan.order), _ptr(plan.inv), _ptr(plan.seg_expert),
+              _ptr(plan.seg_begin), _ptr(plan.seg_count), _ptr(plan.num_segments), max_seg, _ptr(plan.status),
+              _lib.current_stream())
+    return plan
+
+
+def moe_gate_up(x2d, plan, gate_bank, up_bank, gate_fmt, up_fmt, f, d, gate_stride, up_stride):
+    """FP32 hidden activations ``[T*k, F]`` in sorted-assignment order."""
+    torch = _torch()
+    hbuf = torch.empty((plan.rows * plan.k, f), dtype=torch.float32, device=x2d.device)
+    _lib.call("b200q_moe_gate_up", _ptr(gate_bank), int(gate_stride), _lib.FORMAT_ID[gate_fmt], _ptr(up_bank),
+              int(up_stride), _lib.FORMAT_ID[up_fmt], f, d, _ptr(x2d), _dtype_id(x2d), plan.k, _ptr(plan.order),
+              _ptr(plan.seg_expert), _ptr(plan.seg_begin), _ptr(plan.seg_count), _ptr(plan.num_segments),
+              plan.max_segments, _ptr(hbuf), _lib.current_stream())
+    return hbuf
+
+
+def moe_down(hbuf, route_weights, plan, down_bank, down_fmt, d, f, down_stride):
+    """Route-weighted FP32 terms ``[T*k, D]`` in sorted-assignment order."""
+    torch = _torch()
+    if route_weights.dtype != torch.float32 or not route_weights.is_contiguous():
+        raise ValueError("routing weights must be a contiguous FP32 tensor")
+    terms = torch.empty((plan.rows * plan.k, d), dtype=torch.float32, device=hbuf.device)
+    _lib.call("b200q_moe_down", _ptr(down_bank), int(down_stride), _lib.FORMAT_ID[down_fmt], d, f, _ptr(hbuf),
+              _ptr(route_weights), _ptr(plan.order), _ptr(plan.seg_expert), _ptr(plan.seg_begin),
+              _ptr(plan.seg_count), _ptr(plan.num_segments), plan.max_segments, _ptr(terms), _lib.current_stream())
+    return terms
+
+
+def moe_combine(terms, plan, d, *, extra=None, extra_scale=None, out_dtype=None):
+    """Ordered per-token sum of the k terms (+ optional shared-expert term) -> ``[T, D]``."""
+    torch = _torch()
+    out_dtype = out_dtype or torch.float32
+    out = torch.empty((plan.rows, d), dtype=out_dtype, device=terms.device)
+    _lib.call("b200q_moe_combine", _ptr(terms), _ptr(plan.inv), plan.rows, plan.k, d, _ptr(extra), _ptr(extra_scale),
+              _ptr(out), _lib.DTYPE_ID[str(out_dtype).replace("torch.", "")], _lib.current_stream())
+    return out

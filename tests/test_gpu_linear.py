@@ -1,0 +1,217 @@
+"""GPU parity of the packed linear / SwiGLU / expert-FFN operators against the CPU oracle.
+
+Bars: dequantised weights bit-exact; FP32 outputs within the reference's own tolerances
+(GEMV rtol 2e-5 / atol 2e-3 vs FP64, tests/test_0106b_quantized_linear.py:119-121; Q6_K
+rtol 2e-5 / atol 2e-5, tests/test_0106l_q6k_packed.py:82-83; fused SwiGLU rtol 3e-4 /
+atol 2e-4 and fp16 rtol 2e-2 / atol 6e-3, tests/test_0106c:99-100; expert FFN rtol 2e-4 /
+atol 2e-5, tests/test_0106l:95). bf16 is not covered by the reference; it gets fp16's band.
+"""
+
+import numpy as np
+import pytest
+
+from oracle import packed_oracle as po
+from mylocal_llm_b200 import (
+    PackedExpertFFNInference, PackedGGUFWeight, packed_to_device, quantized_linear, quantized_swiglu)
+from mylocal_llm_b200.quantize import quantize, random_packed
+from mylocal_llm_b200.quantized_linear import DevicePackedGGUFWeight, dequantize_device
+
+pytestmark = pytest.mark.gpu
+FORMATS = ("Q8_0", "Q4_K", "Q5_K", "Q6_K")
+
+
+def to_cuda(torch, a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def rounded(torch, a, dtype):
+    """Host copy of `a` after rounding to the device storage dtype (oracle input)."""
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dtype).to(torch.float64).numpy()
+
+
+# ------------------------------------------------------------------------------- dequantize
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("kind", ["random", "quant"])
+def test_dequantize_bit_exact_with_reference_golden(cuda, golden, fmt, kind):
+    data = golden[f"deq_{fmt}_{kind}_bytes"]
+    shape = tuple(int(v) for v in golden[f"deq_{fmt}_{kind}_shape"])
+    got = PackedGGUFWeight(data, shape, fmt).dequantize_reference()
+    np.testing.assert_array_equal(got, golden[f"deq_{fmt}_{kind}_out"])
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_dequantize_bit_exact_random_bytes_large(cuda, fmt):
+    w = random_packed(fmt, (64, 2048), seed=11)
+    got = dequantize_device(to_cuda(cuda, w.data), 64, 2048, fmt).cpu().numpy()
+    np.testing.assert_array_equal(got, po.dequantize(w.data, w.shape, fmt))
+
+
+# ------------------------------------------------------------------------------------ linear
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_linear_matches_reference_golden(cuda, golden, fmt):
+    shape = tuple(int(v) for v in golden[f"lin_{fmt}_shape"])
+    w = packed_to_device(PackedGGUFWeight(golden[f"lin_{fmt}_bytes"], shape, fmt))
+    y = quantized_linear(to_cuda(cuda, golden[f"lin_{fmt}_x"]), w).cpu().numpy()
+    np.testing.assert_allclose(y, golden[f"lin_{fmt}_y_numpy"], rtol=2e-5, atol=2e-3)
+    np.testing.assert_allclose(y, golden[f"lin_{fmt}_y_native"], rtol=2e-5, atol=2e-3)
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("n,k,m", [(7, 256, 1), (13, 512, 2), (19, 768, 3), (33, 2048, 6), (40, 4096, 1),
+                                   (24, 8192, 2), (5, 10240, 1), (300, 1024, 8), (64, 2048, 11)])
+def test_linear_fp32_tails_and_slices(cuda, fmt, n, k, m):
+    w = random_packed(fmt, (n, k), seed=n * 7 + k)
+    x = np.random.default_rng(m + k).normal(0, 1, (m, k)).astype(np.float32)
+    y = quantized_linear(to_cuda(cuda, x), packed_to_device(w)).cpu().numpy()
+    ref = po.linear_fp64(x, w.data, w.shape, fmt)
+    atol = 2e-5 if fmt == "Q6_K" else 2e-3
+    np.testing.assert_allclose(y, ref, rtol=2e-5, atol=atol)
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_linear_identity_activations_read_back_every_coefficient(cuda, fmt):
+    k = 512
+    w = random_packed(fmt, (9, k), seed=3)
+    dense = po.dequantize(w.data, w.shape, fmt)
+    dw = packed_to_device(w)
+    eye = np.eye(k, dtype=np.float32)
+    y = quantized_linear(to_cuda(cuda, eye), dw).cpu().numpy()          # [k, 9]
+    np.testing.assert_array_equal(y, dense.T)
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_linear_low_precision_activations(cuda, fmt, dtype):
+    tdt = getattr(cuda, dtype)
+    w = quantize(np.random.default_rng(1).normal(0, 0.02, (48, 2048)).astype(np.float32), fmt)
+    x = np.random.default_rng(2).normal(0, 1, (2, 3, 2048)).astype(np.float32)
+    xd = to_cuda(cuda, x, tdt)
+    y = quantized_linear(xd, packed_to_device(w))
+    assert y.shape == (2, 3, 48) and y.dtype == tdt
+    ref = po.linear_fp64(rounded(cuda, x, tdt), w.data, w.shape, fmt).reshape(2, 3, 48)
+    np.testing.assert_allclose(y.float().cpu().numpy(), ref, rtol=2e-2, atol=6e-3)
+
+
+def test_linear_config0_shape_q8_0(cuda):
+    # BASELINE config 0: W [4096,4096] N(0,0.02) seed 0 -> Q8_0; x fp32 [1|8, 4096]
+    rng = np.random.default_rng(0)
+    w = quantize(rng.normal(0, 0.02, (4096, 4096)).astype(np.float32), "Q8_0")
+    dw = packed_to_device(w)
+    dense = po.dequantize(w.data, w.shape, "Q8_0").astype(np.float64)
+    for m in (1, 8):
+        x = rng.normal(0, 1, (m, 4096)).astype(np.float32)
+        y = quantized_linear(to_cuda(cuda, x), dw).cpu().numpy()
+        np.testing.assert_allclose(y, x.astype(np.float64) @ dense.T, rtol=2e-5, atol=2e-3)
+
+
+@pytest.mark.parametrize("fmt", ["Q4_K", "Q5_K", "Q6_K"])
+@pytest.mark.parametrize("shape", [(8192, 2048), (2048, 8192)])
+def test_linear_config1_shapes_bf16(cuda, fmt, shape):
+    # BASELINE config 1 at decode batch sizes; random-byte weights keep the host side fast
+    w = random_packed(fmt, shape, seed=shape[0], d=0.01, dmin=0.005)
+    dw = packed_to_device(w)
+    dense = po.dequantize(w.data, w.shape, fmt).astype(np.float64)
+    for m in (1, 8):
+        x = np.random.default_rng(m).normal(0, 1, (m, shape[1])).astype(np.float32)
+        xd = to_cuda(cuda, x, cuda.bfloat16)
+        y = quantized_linear(xd, dw).float().cpu().numpy()
+        ref = rounded(cuda, x, cuda.bfloat16) @ dense.T
+        np.testing.assert_allclose(y, ref, rtol=2e-2, atol=2e-2 * np.abs(ref).max())
+
+
+def test_linear_is_deterministic_and_leaves_inputs_unchanged(cuda):
+    w = random_packed("Q4_K", (257, 4096), seed=8)
+    dw = packed_to_device(w)
+    x = to_cuda(cuda, np.random.default_rng(9).normal(0, 1, (3, 4096)).astype(np.float32))
+    x0, w0 = x.clone(), dw.data.clone()
+    a = quantized_linear(x, dw)
+    b = quantized_linear(x, dw)
+    assert cuda.equal(a, b)
+    assert cuda.equal(x, x0) and cuda.equal(dw.data, w0)
+
+
+def test_linear_on_side_stream_and_unaligned_weight_pointer(cuda):
+    w = random_packed("Q6_K", (37, 1024), seed=12)
+    x = np.random.default_rng(13).normal(0, 1, (2, 1024)).astype(np.float32)
+    ref = po.linear_fp64(x, w.data, w.shape, "Q6_K")
+    # weight bytes placed 6 bytes into an allocation: not 16-byte aligned
+    holder = cuda.zeros(w.nbytes + 64, dtype=cuda.uint8, device="cuda")
+    holder[6:6 + w.nbytes] = cuda.from_numpy(w.data.copy()).cuda()
+    dw = DevicePackedGGUFWeight(holder[6:6 + w.nbytes], w.shape, "Q6_K")
+    assert dw.data.data_ptr() % 16 != 0
+    stream = cuda.cuda.Stream()
+    xd = to_cuda(cuda, x)
+    cuda.cuda.synchronize()
+    with cuda.cuda.stream(stream):
+        y = quantized_linear(xd, dw)
+    stream.synchronize()
+    np.testing.assert_allclose(y.cpu().numpy(), ref, rtol=2e-5, atol=2e-5)
+
+
+def test_linear_large_output_dimension(cuda):
+    # more rows than a 16-bit grid dimension (tests/test_0106p_large_packed_output.py:11-26)
+    w = random_packed("Q8_0", (70001, 64), seed=21)
+    x = np.random.default_rng(22).normal(0, 1, (1, 64)).astype(np.float32)
+    y = quantized_linear(to_cuda(cuda, x), packed_to_device(w)).cpu().numpy()
+    np.testing.assert_allclose(y, po.linear_fp64(x, w.data, w.shape, "Q8_0"), rtol=2e-5, atol=2e-3)
+
+
+def test_linear_cuda_graph_replay_with_changing_inputs(cuda):
+    w = random_packed("Q5_K", (96, 2048), seed=31)
+    dw = packed_to_device(w)
+    static_x = cuda.zeros((1, 2048), dtype=cuda.float32, device="cuda")
+    quantized_linear(static_x, dw)                      # warm-up outside capture
+    cuda.cuda.synchronize()
+    graph = cuda.cuda.CUDAGraph()
+    with cuda.cuda.graph(graph):
+        static_y = quantized_linear(static_x, dw)
+    for seed in (1, 2):
+        x = np.random.default_rng(seed).normal(0, 1, (1, 2048)).astype(np.float32)
+        static_x.copy_(cuda.from_numpy(x))
+        graph.replay()
+        cuda.cuda.synchronize()
+        np.testing.assert_allclose(static_y.cpu().numpy(), po.linear_fp64(x, w.data, w.shape, "Q5_K"),
+                                   rtol=2e-5, atol=2e-3)
+
+
+# ------------------------------------------------------------------------------------ SwiGLU
+def test_swiglu_and_expert_ffn_match_reference_golden(cuda, golden):
+    d, f = (int(v) for v in golden["ffn_dims"])
+    gate = packed_to_device(PackedGGUFWeight(golden["ffn_gate_bytes"], (f, d), "Q4_K"))
+    up = packed_to_device(PackedGGUFWeight(golden["ffn_up_bytes"], (f, d), "Q5_K"))
+    down = packed_to_device(PackedGGUFWeight(golden["ffn_down_bytes"], (d, f), "Q6_K"))
+    x = to_cuda(cuda, golden["ffn_x"])
+    h = quantized_swiglu(x, gate, up).cpu().numpy()
+    np.testing.assert_allclose(h, golden["ffn_swiglu"], rtol=3e-4, atol=2e-4)
+    for fuse in (True, False):
+        y = PackedExpertFFNInference(gate, up, down, fuse_gate_up=fuse).forward(x).cpu().numpy()
+        np.testing.assert_allclose(y, golden["ffn_out"], rtol=2e-4, atol=2e-5)
+
+
+@pytest.mark.parametrize("gf,uf", [("Q4_K", "Q4_K"), ("Q5_K", "Q5_K"), ("Q6_K", "Q6_K"), ("Q8_0", "Q8_0"),
+                                   ("Q4_K", "Q6_K"), ("Q8_0", "Q4_K"), ("Q6_K", "Q5_K")])
+@pytest.mark.parametrize("m", [1, 5])
+def test_swiglu_mixed_formats(cuda, gf, uf, m):
+    f, k = 70, 2304
+    rng = np.random.default_rng(41)
+    gate = quantize(rng.normal(0, 0.03, (f, k)).astype(np.float32), gf)
+    up = quantize(rng.normal(0, 0.03, (f, k)).astype(np.float32), uf)
+    x = rng.normal(0, 1, (m, k)).astype(np.float32)
+    h = quantized_swiglu(to_cuda(cuda, x), packed_to_device(gate), packed_to_device(up)).cpu().numpy()
+    ref = po.swiglu_fp64(x, (gate.data, gate.shape, gf), (up.data, up.shape, uf))
+    np.testing.assert_allclose(h, ref, rtol=3e-4, atol=2e-4)
+
+
+def test_expert_ffn_config3_shape(cuda):
+    # one expert of BASELINE config 3: gate/up Q4_K [512,2048], down Q6_K [2048,512]
+    rng = np.random.default_rng(51)
+    gate = quantize(rng.normal(0, 0.02, (512, 2048)).astype(np.float32), "Q4_K")
+    up = quantize(rng.normal(0, 0.02, (512, 2048)).astype(np.float32), "Q4_K")
+    down = quantize(rng.normal(0, 0.02, (2048, 512)).astype(np.float32), "Q6_K")
+    x = rng.normal(0, 1, (4, 2048)).astype(np.float32)
+    ffn = PackedExpertFFNInference(*(packed_to_device(w) for w in (gate, up, down)))
+    y = ffn.forward(to_cuda(cuda, x)).cpu().numpy()
+    ref = po.expert_ffn_fp64(x, (gate.data, gate.shape, "Q4_K"), (up.data, up.shape, "Q4_K"),
+                             (down.data, down.shape, "Q6_K"))
+    np.testing.assert_allclose(y, ref, rtol=2e-4, atol=2e-5)

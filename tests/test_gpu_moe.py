@@ -1,0 +1,149 @@
+"""GPU parity of the router / routing-plan / grouped-expert kernels against the oracle.
+
+Tolerances are the reference's: router weights 2e-7 with exact ids
+(tests/test_0106v_router_decode.py:37-38), grouped experts rtol 4e-4 / atol 8e-6
+(tests/test_0106t_grouped_quantized_experts.py:172), MoE layer rtol 3e-5 / atol 2e-6 against
+FP64 where stated (tests/test_0106o_qwen3next_decoder.py:192).
+"""
+
+import numpy as np
+import pytest
+
+from oracle import packed_oracle as po
+from mylocal_llm_b200 import moe_ops
+from mylocal_llm_b200.quantize import quantize
+
+pytestmark = pytest.mark.gpu
+
+
+def to_cuda(torch, a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+# ------------------------------------------------------------------------------------ router
+def test_router_topk_matches_reference_golden(cuda, golden):
+    logits, k = golden["router_logits"], int(golden["router_k"])
+    w, ids = moe_ops.router_topk(to_cuda(cuda, logits), k, renormalize=False)
+    np.testing.assert_array_equal(ids.cpu().numpy(), golden["router_ids"])
+    np.testing.assert_allclose(w.cpu().numpy(), golden["router_w_raw"], rtol=0, atol=2e-7)
+
+
+def test_router_projection_and_renormalisation_match_reference_golden(cuda, golden):
+    k = int(golden["router_k"])
+    logits = moe_ops.router_logits(to_cuda(cuda, golden["router_fw_x"]), to_cuda(cuda, golden["router_fw_W"]))
+    ref_logits = golden["router_fw_x"].astype(np.float64) @ golden["router_fw_W"].astype(np.float64)
+    np.testing.assert_allclose(logits.cpu().numpy(), ref_logits, rtol=1e-5, atol=1e-5)
+    w, ids = moe_ops.router_topk(logits, k, renormalize=True, floor=2.0 ** -14)
+    np.testing.assert_array_equal(ids.cpu().numpy(), golden["router_fw_ids"])
+    np.testing.assert_allclose(w.cpu().numpy(), golden["router_fw_w"], rtol=0, atol=2e-7)
+
+
+def test_router_ties_infinities_and_nans(cuda):
+    rows = np.array([[1, 1, 1, 1], [0, np.inf, -np.inf, 5], [np.nan, 2, 2, 1], [3, np.nan, np.nan, 3]], np.float32)
+    w, ids = moe_ops.router_topk(to_cuda(cuda, rows), 3, renormalize=True, floor=2.0 ** -14)
+    np.testing.assert_array_equal(ids.cpu().numpy(), [[0, 1, 2], [1, 3, 0], [1, 2, 3], [0, 3, 1]])
+    w_ref, ids_ref = po.router_topk_rows_fp32(rows, 3, 2.0 ** -14)
+    got = w.cpu().numpy()
+    np.testing.assert_array_equal(np.isnan(got), np.isnan(w_ref))
+    np.testing.assert_allclose(np.nan_to_num(got), np.nan_to_num(w_ref), rtol=0, atol=2e-7)
+
+
+@pytest.mark.parametrize("rows,n,k", [(1, 512, 10), (16, 512, 10), (256, 512, 10), (3, 4096, 32), (5, 7, 7)])
+def test_router_topk_shapes_against_oracle(cuda, rows, n, k):
+    logits = np.random.default_rng(rows + n).normal(0, 1.5, (rows, n)).astype(np.float32)
+    w, ids = moe_ops.router_topk(to_cuda(cuda, logits), k, renormalize=True, floor=2.0 ** -14)
+    w_ref, ids_ref = po.router_topk(logits, k, 2.0 ** -14)
+    np.testing.assert_array_equal(ids.cpu().numpy(), ids_ref)
+    np.testing.assert_allclose(w.cpu().numpy(), w_ref, rtol=0, atol=2e-7)
+
+
+# -------------------------------------------------------------------------------------- plan
+@pytest.mark.parametrize("rows,k,e,dtype", [(1, 10, 512, "int64"), (11, 3, 9, "int64"), (256, 10, 512, "int32"),
+                                            (700, 4, 33, "int64"), (5, 2, 4096, "int32")])
+def test_routing_plan_is_the_stable_sort_by_expert(cuda, rows, k, e, dtype):
+    rng = np.random.default_rng(rows * k + e)
+    ids = np.stack([rng.choice(e, size=k, replace=k > e) for _ in range(rows)]).astype(dtype)
+    plan = moe_ops.moe_plan(to_cuda(cuda, ids), e)
+    order, counts, offsets = po.routing_plan(ids, e)
+    np.testing.assert_array_equal(plan.counts.cpu().numpy(), counts)
+    np.testing.assert_array_equal(plan.offsets.cpu().numpy(), offsets)
+    np.testing.assert_array_equal(plan.order.cpu().numpy(), order)
+    inv = np.empty_like(order)
+    inv[order] = np.arange(order.size)
+    np.testing.assert_array_equal(plan.inv.cpu().numpy(), inv)
+    assert int(plan.status.item()) == 0
+    nseg = int(plan.num_segments.item())
+    seg_e = plan.seg_expert.cpu().numpy()[:nseg]
+    seg_b = plan.seg_begin.cpu().numpy()[:nseg]
+    seg_c = plan.seg_count.cpu().numpy()[:nseg]
+    expect = [(ex, offsets[ex] + r, min(moe_ops.SEGMENT_CAP, counts[ex] - r))
+              for ex in range(e) for r in range(0, counts[ex], moe_ops.SEGMENT_CAP)]
+    assert [(int(a), int(b), int(c)) for a, b, c in zip(seg_e, seg_b, seg_c)] == expect
+
+
+def test_routing_plan_flags_out_of_range_ids(cuda):
+    ids = np.array([[0, 9], [2, 1]], np.int64)
+    plan = moe_ops.moe_plan(to_cuda(cuda, ids), 4)
+    assert int(plan.status.item()) == 1
+
+
+def test_routing_plan_golden_counts(cuda, golden):
+    plan = moe_ops.moe_plan(to_cuda(cuda, golden["plan_ids"]), 9)
+    np.testing.assert_array_equal(plan.counts.cpu().numpy(), golden["plan_sizes"])
+    np.testing.assert_array_equal(plan.offsets.cpu().numpy(), golden["plan_offsets"])
+    sorted_experts = golden["plan_ids"].reshape(-1)[plan.order.cpu().numpy()]
+    np.testing.assert_array_equal(sorted_experts, golden["plan_expert_sorted"])
+
+
+# ----------------------------------------------------------------------------------- combine
+def test_combine_adds_in_ascending_expert_order_without_fma_or_tree(cuda):
+    # terms [1e8, 1, -1e8, 3] summed left to right give 3; any tree or reordering gives 4 or 0
+    k, d = 4, 8
+    ids = np.array([[3, 0, 2, 1]], np.int64)          # slot -> expert
+    per_expert = {0: 1e8, 1: 1.0, 2: -1e8, 3: 3.0}
+    plan = moe_ops.moe_plan(to_cuda(cuda, ids), 4)
+    terms = np.zeros((k, d), np.float32)
+    for pos, flat in enumerate(plan.order.cpu().numpy()):
+        terms[pos] = per_expert[int(ids[0, flat])]
+    out = moe_ops.moe_combine(to_cuda(cuda, terms), plan, d).cpu().numpy()
+    np.testing.assert_array_equal(out, np.full((1, d), 3.0, np.float32))
+
+
+# -------------------------------------------------------------------------- grouped experts
+def run_routed(torch, hidden, weights, ids, gate_bank, up_bank, down_bank, d, f, e, fmts, x_dtype=None):
+    x = to_cuda(torch, hidden, x_dtype)
+    plan = moe_ops.moe_plan(to_cuda(torch, ids), e)
+    gs, us, ds = (bank.shape[1] for bank in (gate_bank, up_bank, down_bank))
+    gb, ub, db = (to_cuda(torch, bank.reshape(-1)) for bank in (gate_bank, up_bank, down_bank))
+    hbuf = moe_ops.moe_gate_up(x, plan, gb, ub, fmts[0], fmts[1], f, d, gs, us)
+    terms = moe_ops.moe_down(hbuf, to_cuda(torch, weights.astype(np.float32)), plan, db, fmts[2], d, f, ds)
+    return moe_ops.moe_combine(terms, plan, d)
+
+
+@pytest.mark.parametrize("tag", ["moe", "moe1"])
+def test_grouped_experts_match_reference_golden(cuda, golden, tag):
+    d, f, e, k = (int(v) for v in golden["moe_dims"])
+    out = run_routed(cuda, golden[f"{tag}_hidden"], golden[f"{tag}_weights"], golden[f"{tag}_ids"],
+                     golden["moe_gate_bytes"], golden["moe_up_bytes"], golden["moe_down_bytes"], d, f, e,
+                     ("Q4_K", "Q4_K", "Q6_K"))
+    np.testing.assert_allclose(out.cpu().numpy(), golden[f"{tag}_routed"], rtol=4e-4, atol=8e-6)
+
+
+@pytest.mark.parametrize("tokens", [1, 16, 40])
+def test_grouped_experts_against_fp64_oracle_with_crowded_experts(cuda, tokens):
+    # few experts and many tokens: segments longer than the per-pass cap, repeated experts per pass
+    d, f, e, k = 512, 256, 5, 2
+    rng = np.random.default_rng(tokens)
+    packs = [[quantize(rng.normal(0, 0.05, s).astype(np.float32), q) for _ in range(e)]
+             for s, q in (((f, d), "Q4_K"), ((f, d), "Q5_K"), ((d, f), "Q6_K"))]
+    banks = [np.stack([p.data for p in group]) for group in packs]
+    hidden = rng.normal(0, 1, (tokens, d)).astype(np.float32)
+    logits = rng.normal(0, 1, (tokens, e))
+    w, ids = po.router_topk(logits, k, 2.0 ** -14)
+    out = run_routed(cuda, hidden, w.astype(np.float32), ids, *banks, d, f, e, ("Q4_K", "Q5_K", "Q6_K"))
+    experts = [tuple((packs[j][i].data, packs[j][i].shape, q) for j, q in enumerate(("Q4_K", "Q5_K", "Q6_K")))
+               for i in range(e)]
+    ref = po.experts_forward_fp32sum(hidden, w.astype(np.float32), ids,
+                                     lambda ex, rows: po.expert_ffn_fp64(rows, *experts[ex]), e)
+    np.testing.assert_allclose(out.cpu().numpy(), ref, rtol=4e-4, atol=8e-6)
