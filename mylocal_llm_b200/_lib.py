@@ -6,11 +6,13 @@ in-tree nvcc build and otherwise raises; nothing silently degrades.
 """
 
 import ctypes
+import os
 import threading
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
-LIB_PATH = _PKG / "libb200q.so"
+# B200Q_LIBRARY points the loader at another build of the same ABI (A/B measurements).
+LIB_PATH = Path(os.environ.get("B200Q_LIBRARY") or _PKG / "libb200q.so")
 
 FORMAT_ID = {"Q8_0": 0, "Q4_K": 2, "Q5_K": 4, "Q6_K": 5}
 DTYPE_ID = {"float32": 0, "float16": 1, "bfloat16": 2}

@@ -1,0 +1,34 @@
+// Request descriptor shared by the C ABI dispatcher and the tensor-core GEMV launcher.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200q {
+
+struct MmaRequest {
+    int mode;  // 0 linear, 1 SwiGLU, 2 grouped gate/up, 3 grouped down
+    const uint8_t *wa;
+    const uint8_t *wb;
+    int fmt_a, fmt_b;
+    long long stride_a, stride_b;
+    int n, k, m;
+    const void *x;
+    int x_dtype;
+    void *y;
+    int y_dtype;
+    int topk;
+    const int32_t *order;
+    const int32_t *seg_expert;
+    const int32_t *seg_begin;
+    const int32_t *seg_count;
+    const int32_t *num_segments;
+    int max_segments;
+    const float *route;
+    int *status;
+};
+
+// Launches the tensor-core kernel when the request fits it (alignment, K multiple of 256, shared
+// memory); otherwise leaves *launched false and the caller runs the FP32-lane kernel.
+int mma_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched);
+
+}  // namespace b200q

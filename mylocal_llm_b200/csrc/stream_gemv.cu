@@ -1,6 +1,9 @@
 // Host launchers + C ABI for the streaming GEMV family (linear, SwiGLU, grouped experts).
 #include <cstdio>
+#include <cstdlib>
+#include <cstring>
 
+#include "mma_host.h"
 #include "stream_gemv.cuh"
 
 namespace b200q {
@@ -91,6 +94,13 @@ static int tokens_per_launch(int m, int k) {
 
 static bool k_ok(int fmt, int k) { return k > 0 && k % fmt_elems(fmt) == 0; }
 
+// B200Q_KERNEL=lanes forces the FP32-lane kernels (used by the parity tests to cover both
+// families); anything else lets every call pick the tensor-core kernel when it applies.
+static bool mma_allowed() {
+    const char *v = std::getenv("B200Q_KERNEL");
+    return !(v && std::strcmp(v, "lanes") == 0);
+}
+
 }  // namespace b200q
 
 using namespace b200q;
@@ -114,6 +124,26 @@ int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype,
     a.x_dtype = x_dtype;
     a.y_dtype = y_dtype;
     a.status = status;
+    if (mma_allowed()) {
+        // up to 8 tokens per pass on the tensor cores
+        bool all = true;
+        for (int t0 = 0; t0 < m && all; t0 += 8) {
+            MmaRequest q{};
+            q.mode = 0; q.wa = a.wa; q.fmt_a = q.fmt_b = fmt; q.n = n; q.k = k; q.m = (m - t0 < 8) ? m - t0 : 8;
+            q.x = static_cast<const uint8_t *>(x) + static_cast<size_t>(t0) * k * dtype_size(x_dtype);
+            q.x_dtype = x_dtype;
+            q.y = static_cast<uint8_t *>(y) + static_cast<size_t>(t0) * n * dtype_size(y_dtype);
+            q.y_dtype = y_dtype; q.status = status;
+            bool launched = false;
+            int rc = mma_try_launch(q, static_cast<cudaStream_t>(stream), &launched);
+            if (rc) return rc;
+            if (!launched) {
+                if (t0) return fail(B200Q_ECUDA, "gemv: kernel selection changed between token groups");
+                all = false;
+            }
+        }
+        if (all) return B200Q_OK;
+    }
     const int mt = tokens_per_launch(m, k);
     if (mt < 1) return fail(B200Q_EUNSUPPORTED, "gemv: K=%d too large", k);
     int rc = plan_tiles(a, false, mt);
@@ -151,6 +181,26 @@ int b200q_swiglu(const void *gate, int gate_fmt, const void *up, int up_fmt, int
     a.x_dtype = x_dtype;
     a.y_dtype = h_dtype;
     a.status = status;
+    if (mma_allowed()) {
+        bool all = true;
+        for (int t0 = 0; t0 < m && all; t0 += 8) {
+            MmaRequest q{};
+            q.mode = 1; q.wa = a.wa; q.wb = a.wb; q.fmt_a = gate_fmt; q.fmt_b = up_fmt; q.n = f; q.k = k;
+            q.m = (m - t0 < 8) ? m - t0 : 8;
+            q.x = static_cast<const uint8_t *>(x) + static_cast<size_t>(t0) * k * dtype_size(x_dtype);
+            q.x_dtype = x_dtype;
+            q.y = static_cast<uint8_t *>(h) + static_cast<size_t>(t0) * f * dtype_size(h_dtype);
+            q.y_dtype = h_dtype; q.status = status;
+            bool launched = false;
+            int rc = mma_try_launch(q, static_cast<cudaStream_t>(stream), &launched);
+            if (rc) return rc;
+            if (!launched) {
+                if (t0) return fail(B200Q_ECUDA, "swiglu: kernel selection changed between token groups");
+                all = false;
+            }
+        }
+        if (all) return B200Q_OK;
+    }
     const int mt = tokens_per_launch(m, k);
     if (mt < 1) return fail(B200Q_EUNSUPPORTED, "swiglu: K=%d too large", k);
     int rc = plan_tiles(a, true, mt);
@@ -204,6 +254,16 @@ int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, 
     a.num_segments = num_segments;
     a.max_segments = max_segments;
     a.status = status;
+    if (mma_allowed()) {
+        MmaRequest q{};
+        q.mode = 2; q.wa = a.wa; q.wb = a.wb; q.fmt_a = gate_fmt; q.fmt_b = up_fmt; q.stride_a = gate_stride;
+        q.stride_b = up_stride; q.n = f; q.k = d; q.m = MAX_TOKENS; q.x = x; q.x_dtype = x_dtype; q.y = hbuf;
+        q.y_dtype = B200Q_F32; q.topk = k; q.order = order; q.seg_expert = seg_expert; q.seg_begin = seg_begin;
+        q.seg_count = seg_count; q.num_segments = num_segments; q.max_segments = max_segments; q.status = status;
+        bool launched = false;
+        int rc = mma_try_launch(q, static_cast<cudaStream_t>(stream), &launched);
+        if (rc || launched) return rc;
+    }
     if (static_cast<long long>(MAX_TOKENS) * d * 4 > XBUF_LIMIT)
         return fail(B200Q_EUNSUPPORTED, "moe_gate_up: d=%d too large for %d tokens per segment", d, MAX_TOKENS);
     int rc = plan_tiles(a, true, MAX_TOKENS);
@@ -242,6 +302,16 @@ int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, int
     a.max_segments = max_segments;
     a.route = route;
     a.status = status;
+    if (mma_allowed()) {
+        MmaRequest q{};
+        q.mode = 3; q.wa = a.wa; q.fmt_a = q.fmt_b = down_fmt; q.stride_a = down_stride; q.n = d; q.k = f;
+        q.m = MAX_TOKENS; q.x = hbuf; q.x_dtype = B200Q_F32; q.y = terms; q.y_dtype = B200Q_F32; q.topk = 1;
+        q.order = order; q.seg_expert = seg_expert; q.seg_begin = seg_begin; q.seg_count = seg_count;
+        q.num_segments = num_segments; q.max_segments = max_segments; q.route = route; q.status = status;
+        bool launched = false;
+        int rc = mma_try_launch(q, static_cast<cudaStream_t>(stream), &launched);
+        if (rc || launched) return rc;
+    }
     if (static_cast<long long>(MAX_TOKENS) * f * 4 > XBUF_LIMIT)
         return fail(B200Q_EUNSUPPORTED, "moe_down: f=%d too large for %d tokens per segment", f, MAX_TOKENS);
     int rc = plan_tiles(a, false, MAX_TOKENS);

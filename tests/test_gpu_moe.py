@@ -16,6 +16,13 @@ from mylocal_llm_b200.quantize import quantize
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["tensor", "lanes"])
+def kernel_family(request, monkeypatch):
+    """Run every case on both kernel families: tensor-core fragments (default) and FP32 lanes."""
+    monkeypatch.setenv("B200Q_KERNEL", "lanes" if request.param == "lanes" else "auto")
+    return request.param
+
+
 def to_cuda(torch, a, dtype=None):
     t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
     return t if dtype is None else t.to(dtype)
