@@ -1,0 +1,72 @@
+// Instantiations and launcher of the direct-load tensor-core GEMV (Q4_K / Q5_K).
+#include "mma_direct.cuh"
+#include "mma_host.h"
+
+namespace b200q {
+
+using DirectFn = void (*)(const DirectArgs);
+
+template <bool Q5, int NT>
+static DirectFn pick_mode(int mode) {
+    switch (mode) {
+        case 0: return mma_direct_kernel<Q5, 0, NT>;
+        case 1: return mma_direct_kernel<Q5, 1, NT>;
+        case 2: return mma_direct_kernel<Q5, 2, NT>;
+        case 3: return mma_direct_kernel<Q5, 3, NT>;
+    }
+    return nullptr;
+}
+
+int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) {
+    *launched = false;
+    const bool dual = (q.mode == 1 || q.mode == 2);
+    const bool grouped = q.mode >= 2;
+    if (q.fmt_a != B200Q_Q4_K && q.fmt_a != B200Q_Q5_K) return B200Q_OK;
+    if (dual && q.fmt_a != q.fmt_b) return B200Q_OK;
+    if (q.k % 256 != 0 || q.m > 8) return B200Q_OK;
+    if (reinterpret_cast<uintptr_t>(q.wa) & 15) return B200Q_OK;
+    if (dual && (reinterpret_cast<uintptr_t>(q.wb) & 15)) return B200Q_OK;
+    if (grouped && ((q.stride_a & 15) || (dual && (q.stride_b & 15)))) return B200Q_OK;
+
+    DirectArgs a{};
+    a.wa = q.wa; a.wb = q.wb; a.stride_a = q.stride_a; a.stride_b = q.stride_b;
+    a.rb = q.k / 256 * fmt_bytes(q.fmt_a);
+    a.n = q.n; a.k = q.k; a.m = q.m;
+    a.nterms = (q.x_dtype == B200Q_F32) ? 2 : 1;
+    const int nsb = q.k / 256;
+    int kp = 1;
+    while (kp * 2 <= MD_WARPS && kp * 2 <= nsb) kp *= 2;
+    a.kp = kp;
+    a.rg = MD_WARPS / kp;
+    a.off_bfrag = MD_CTRL_BYTES + MD_PART_BYTES;
+    const long long bfrag_bytes = static_cast<long long>(a.nterms) * nsb * 16 * 256;
+    const long long xs_bytes = static_cast<long long>(nsb) * 2 * 128;
+    const long long smem = a.off_bfrag + bfrag_bytes + xs_bytes;
+    if (smem > MM_SMEM_LIMIT) return B200Q_OK;
+    a.off_xsfrag = static_cast<int>(a.off_bfrag + bfrag_bytes);
+    a.x = q.x; a.x_dtype = q.x_dtype; a.y = q.y; a.y_dtype = q.y_dtype;
+    a.topk = q.topk; a.order = q.order; a.seg_expert = q.seg_expert; a.seg_begin = q.seg_begin;
+    a.seg_count = q.seg_count; a.num_segments = q.num_segments; a.max_segments = q.max_segments;
+    a.route = q.route;
+
+    const bool q5 = q.fmt_a == B200Q_Q5_K;
+    DirectFn fn = q5 ? (a.nterms == 2 ? pick_mode<true, 2>(q.mode) : pick_mode<true, 1>(q.mode))
+                     : (a.nterms == 2 ? pick_mode<false, 2>(q.mode) : pick_mode<false, 1>(q.mode));
+    if (!fn) return B200Q_OK;
+    cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void *>(fn),
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM_LIMIT);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail(B200Q_ECUDA, "direct gemv: shared memory opt-in failed: %s", cudaGetErrorString(err));
+    }
+    int grid = sm_count();
+    if (!grouped) {
+        const int blocks = (q.n + 16 * a.rg - 1) / (16 * a.rg);
+        if (blocks < grid) grid = blocks;
+    }
+    fn<<<grid, MD_THREADS, static_cast<size_t>(smem), stream>>>(a);
+    *launched = true;
+    return check_launch("direct gemv");
+}
+
+}  // namespace b200q

@@ -1,0 +1,425 @@
+// Direct-load tensor-core GEMV for Q4_K / Q5_K (sm_100a), up to 8 tokens per pass.
+//
+// Q4_K / Q5_K super-blocks are 16-byte multiples, so every lane can fetch exactly the packed
+// bytes it needs with 128-bit global loads (four lanes cover 64 contiguous bytes of a row, eight
+// rows per instruction) - no shared-memory staging of weights, no producer warp, no barrier on
+// the weight path. 16 warps per SM, each with the next super-block already in flight, keep about
+// 48 KB of loads outstanding per SM.
+//
+// Arithmetic per super-block (256 weights of one row):
+//   * 4- or 5-bit codes -> FP16 pairs by byte permute; one packed FMA turns (1024+q) into sc*q
+//     exactly (sc*q <= 63*31 < 2048 is an integer FP16 holds exactly), so the 6-bit sub-block
+//     scales ride inside the A fragments and one accumulator serves the whole super-block;
+//   * 16 mma.m16n8k16 steps accumulate sum(sc*q*x) in FP32 for 16 rows x 8 tokens;
+//   * the minima go through one more mma: A = the eight 6-bit mins, B = per-sub-block activation
+//     sums (FP16 high + remainder), giving sum(mn * sum_x);
+//   * y += d * acc - dmin * acc_min in FP32.
+// Every product is exact; roundings are the FP32 accumulations, as in the FP32-lane kernels.
+//
+// Activations are prepared once per CTA (or per expert segment) exactly as in mma_gemv.cuh:
+// power-of-two scaling per token, FP16 high (+ remainder for FP32 inputs), stored as B fragments.
+#pragma once
+
+#include "mma_gemv.cuh"
+
+namespace b200q {
+
+constexpr int MD_WARPS = 16;
+constexpr int MD_THREADS = MD_WARPS * 32;
+constexpr int MD_CTRL_BYTES = 1024;
+constexpr int MD_PART_FLOATS = MD_WARPS * 256;          // [warp][16 rows][8 tokens][2 streams]
+constexpr int MD_PART_BYTES = 2 * MD_PART_FLOATS * 4;   // double buffered
+constexpr float MD_XS_SCALE = 0.015625f;                // activation sums are stored divided by 64
+
+struct DirectArgs {
+    const uint8_t *wa;
+    const uint8_t *wb;
+    long long stride_a, stride_b;
+    int rb;              // packed bytes per weight row (both streams share the format)
+    int n, k, m;
+    int kp, rg;          // warps along K and row groups per CTA pass (kp * rg == 16)
+    int nterms;
+    int off_bfrag, off_xsfrag;
+    const void *x;
+    int x_dtype;
+    void *y;
+    int y_dtype;
+    int topk;
+    const int32_t *order;
+    const int32_t *seg_expert;
+    const int32_t *seg_begin;
+    const int32_t *seg_count;
+    const int32_t *num_segments;
+    int max_segments;
+    const float *route;
+};
+
+__device__ __forceinline__ uint4 ldg128(const uint8_t *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// Packed bytes of one row's super-block as seen by one lane.
+template <bool Q5>
+struct SuperBlockRegs {
+    uint4 hd;   // d, dmin, 12 scale/min bytes
+    uint4 qa;   // quants bytes [16*tig, +16)        -> sub-blocks 2*(tig>>1), +1
+    uint4 qb;   // quants bytes [64 + 16*tig, +16)   -> sub-blocks 4 + 2*(tig>>1), +1
+    uint4 qh;   // Q5_K: high-bit bytes of elements [16*(tig&1), +16)
+};
+
+template <bool Q5>
+__device__ __forceinline__ void load_superblock(SuperBlockRegs<Q5> &r, const uint8_t *blk, int tig) {
+    r.hd = ldg128(blk);
+    if (Q5) {
+        r.qh = ldg128(blk + 16 + 16 * (tig & 1));
+        r.qa = ldg128(blk + 48 + 16 * tig);
+        r.qb = ldg128(blk + 112 + 16 * tig);
+    } else {
+        r.qh = make_uint4(0u, 0u, 0u, 0u);
+        r.qa = ldg128(blk + 16 + 16 * tig);
+        r.qb = ldg128(blk + 80 + 16 * tig);
+    }
+}
+
+// Scales of one row for this lane: the four sub-blocks its quant bytes belong to, as FP16 pairs
+// (sc, sc) and (-1024*sc, -1024*sc); plus the A operand of the min product and d, dmin.
+struct RowScales {
+    uint32_t sc[4];     // [span A low, span A high, span B low, span B high]
+    uint32_t nsc[4];
+    uint32_t mins;      // (mn[2*tig], mn[2*tig+1]) as exact FP16 pair
+    float d, dmin;
+};
+
+__device__ __forceinline__ RowScales decode_scales(const uint4 &hd, int tig) {
+    RowScales s;
+    s.d = half_bits_to_float(hd.x & 0xffffu);
+    s.dmin = half_bits_to_float(hd.x >> 16);
+    const uint32_t sc_lo = hd.y & 0x3f3f3f3fu;                                       // sub-blocks 0..3
+    const uint32_t sc_hi = (hd.w & 0x0f0f0f0fu) | ((hd.y >> 2) & 0x30303030u);        // sub-blocks 4..7
+    const uint32_t mn_lo = hd.z & 0x3f3f3f3fu;
+    const uint32_t mn_hi = ((hd.w >> 4) & 0x0f0f0f0fu) | ((hd.z >> 2) & 0x30303030u);
+    const int sh = (tig >> 1) * 16;   // sub-block pair 2*(tig>>1) inside each word
+    const uint32_t a2 = sc_lo >> sh, b2 = sc_hi >> sh;   // low two bytes: the lane's two sub-blocks
+    const uint32_t bias = 0x64006400u, k1024 = 0xe400e400u;   // 1024, -1024 as FP16 pairs
+    s.sc[0] = hsub2_u32(__byte_perm(a2, 0x64646464u, 0x4040), bias);
+    s.sc[1] = hsub2_u32(__byte_perm(a2, 0x64646464u, 0x4141), bias);
+    s.sc[2] = hsub2_u32(__byte_perm(b2, 0x64646464u, 0x4040), bias);
+    s.sc[3] = hsub2_u32(__byte_perm(b2, 0x64646464u, 0x4141), bias);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s.nsc[i] = hmul2_u32(s.sc[i], k1024);
+    const uint32_t mw = ((tig & 2) ? mn_hi : mn_lo) >> ((tig & 1) * 16);
+    s.mins = hsub2_u32(__byte_perm(mw, 0x64646464u, 0x4140), bias);
+    return s;
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Activation fragments for the direct kernel. Fragment (sb, fi) with fi = (X*2 + nib)*4 + j holds,
+// for lane (g = lane>>2, tig = lane&3), token g at positions
+//   256*sb + 32*(4*X + 2*(tig>>1) + nib) + 16*(tig&1) + 4*j + {0,2 -> b0 ; 1,3 -> b1}
+// which are exactly the positions of the codes that lane extracts from word j of its quant bytes.
+// xsfrag (sb, term) holds (sum_x[sub 2*tig], sum_x[sub 2*tig+1]) / 64 for token g.
+// ---------------------------------------------------------------------------------------------
+template <int NTERMS, typename RowFn>
+__device__ __forceinline__ void prepare_direct(RowFn row_of, int m_tokens, int k, const void *x, int x_dtype,
+                                               uint2 *bfrag, uint32_t *xsfrag, float *tok_scale, int tid) {
+    const int warp = tid >> 5, lane = tid & 31;
+    const int nsb = k >> 8;
+    const int nfrag = nsb * 16;
+    if (warp < 8) {
+        float amax = 0.f;
+        if (warp < m_tokens) {
+            const size_t base = static_cast<size_t>(row_of(warp)) * k;
+            for (int i = lane; i < k; i += 32) amax = fmaxf(amax, fabsf(load_as_float(x, x_dtype, base + i)));
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (lane == 0) {
+            float s = 1.0f;
+            if (amax > 0.f && amax < __int_as_float(0x7f800000)) {
+                int e;
+                frexpf(amax, &e);
+                s = ldexpf(1.0f, min(14 - e, 100));
+            }
+            tok_scale[warp] = s;
+            tok_scale[8 + warp] = 1.0f / s;
+        }
+    }
+    named_barrier_sync(1, MD_THREADS);
+    const int g = lane >> 2, tig = lane & 3;
+    const bool live = g < m_tokens;
+    const float s = tok_scale[g];
+    const size_t base = live ? static_cast<size_t>(row_of(g)) * k : 0;
+    for (int sb = warp; sb < nsb; sb += MD_WARPS) {
+#pragma unroll
+        for (int X = 0; X < 2; ++X) {
+#pragma unroll
+            for (int nib = 0; nib < 2; ++nib) {
+                const int sub = 4 * X + 2 * (tig >> 1) + nib;
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int k0 = 256 * sb + 32 * sub + 16 * (tig & 1) + 4 * j;
+                    float v[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (live) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) v[i] = load_as_float(x, x_dtype, base + k0 + i) * s;
+                    }
+                    __half hi[4], lo[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        hi[i] = __float2half_rn(v[i]);
+                        lo[i] = __float2half_rn(v[i] - __half2float(hi[i]));
+                        sum += __half2float(hi[i]);
+                        if (NTERMS == 2) sum += __half2float(lo[i]);
+                    }
+                    const int f = sb * 16 + (X * 2 + nib) * 4 + j;
+                    uint2 out;
+                    out.x = static_cast<uint32_t>(__half_as_ushort(hi[0])) | (static_cast<uint32_t>(__half_as_ushort(hi[2])) << 16);
+                    out.y = static_cast<uint32_t>(__half_as_ushort(hi[1])) | (static_cast<uint32_t>(__half_as_ushort(hi[3])) << 16);
+                    bfrag[f * 32 + lane] = out;
+                    if (NTERMS == 2) {
+                        out.x = static_cast<uint32_t>(__half_as_ushort(lo[0])) | (static_cast<uint32_t>(__half_as_ushort(lo[2])) << 16);
+                        out.y = static_cast<uint32_t>(__half_as_ushort(lo[1])) | (static_cast<uint32_t>(__half_as_ushort(lo[3])) << 16);
+                        bfrag[(nfrag + f) * 32 + lane] = out;
+                    }
+                }
+                // the other half of the sub-block's 32 positions sits in the neighbouring lane
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                // after both nibble planes: lanes with (tig&1)==0 own (sub even, sub odd) of pair (X, tig>>1)
+                const float scaled = sum * MD_XS_SCALE;
+                const __half h = __float2half_rn(scaled);
+                const __half l = __float2half_rn(scaled - __half2float(h));
+                // target lane of the min product: tig_t = (tig>>1) + 2*X, slots (2*tig_t, 2*tig_t+1) = (sub even, odd)
+                if ((tig & 1) == 0) {
+                    const int lane_t = 4 * g + (tig >> 1) + 2 * X;
+                    unsigned short *ph = reinterpret_cast<unsigned short *>(xsfrag + (sb * 2 + 0) * 32 + lane_t);
+                    unsigned short *pl = reinterpret_cast<unsigned short *>(xsfrag + (sb * 2 + 1) * 32 + lane_t);
+                    ph[nib] = __half_as_ushort(h);
+                    pl[nib] = __half_as_ushort(l);
+                }
+            }
+        }
+    }
+    named_barrier_sync(1, MD_THREADS);
+}
+
+// 16 mma steps of one super-block for rows (g, g+8): acc += sum(sc*q*x); accm += sum(mn * sum_x/64).
+template <bool Q5, int NTERMS>
+__device__ __forceinline__ void superblock_mma(const SuperBlockRegs<Q5> &ra, const SuperBlockRegs<Q5> &rb,
+                                               const uint2 *bfrag, int nfrag, const uint32_t *xsfrag, int sb, int lane,
+                                               float (&tot)[4]) {
+    const int tig = lane & 3;
+    const RowScales sa = decode_scales(ra.hd, tig), sbk = decode_scales(rb.hd, tig);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint32_t qa_a[4] = {ra.qa.x, ra.qa.y, ra.qa.z, ra.qa.w}, qb_a[4] = {ra.qb.x, ra.qb.y, ra.qb.z, ra.qb.w};
+    const uint32_t qa_b[4] = {rb.qa.x, rb.qa.y, rb.qa.z, rb.qa.w}, qb_b[4] = {rb.qb.x, rb.qb.y, rb.qb.z, rb.qb.w};
+    const uint32_t qh_a[4] = {ra.qh.x, ra.qh.y, ra.qh.z, ra.qh.w}, qh_b[4] = {rb.qh.x, rb.qh.y, rb.qh.z, rb.qh.w};
+    const int pair = tig >> 1;
+#pragma unroll
+    for (int X = 0; X < 2; ++X) {
+#pragma unroll
+        for (int nib = 0; nib < 2; ++nib) {
+            const int si = X * 2 + nib;
+            // Q5_K: bit (sub-block index) of the high-bit byte, moved to bit 4 of the code
+            const int sub = 4 * X + 2 * pair + nib;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t wa = X ? qb_a[j] : qa_a[j], wb = X ? qb_b[j] : qa_b[j];
+                uint32_t va = nib ? (wa >> 4) & 0x0f0f0f0fu : wa & 0x0f0f0f0fu;
+                uint32_t vb = nib ? (wb >> 4) & 0x0f0f0f0fu : wb & 0x0f0f0f0fu;
+                if (Q5) {
+                    va |= ((qh_a[j] >> sub) << 4) & 0x10101010u;
+                    vb |= ((qh_b[j] >> sub) << 4) & 0x10101010u;
+                }
+                const uint32_t a0 = hfma2_u32(__byte_perm(va, 0x64646464u, 0x4240), sa.sc[si], sa.nsc[si]);
+                const uint32_t a2 = hfma2_u32(__byte_perm(va, 0x64646464u, 0x4341), sa.sc[si], sa.nsc[si]);
+                const uint32_t a1 = hfma2_u32(__byte_perm(vb, 0x64646464u, 0x4240), sbk.sc[si], sbk.nsc[si]);
+                const uint32_t a3 = hfma2_u32(__byte_perm(vb, 0x64646464u, 0x4341), sbk.sc[si], sbk.nsc[si]);
+                const BFrag b = load_bfrag<NTERMS>(bfrag, nfrag, sb * 16 + si * 4 + j, lane);
+                mma_terms<NTERMS>(acc, a0, a1, a2, a3, b);
+            }
+        }
+    }
+    float accm[4] = {0.f, 0.f, 0.f, 0.f};
+    mma_f16(accm, sa.mins, sbk.mins, 0u, 0u, xsfrag[(sb * 2 + 0) * 32 + lane], 0u);
+    mma_f16(accm, sa.mins, sbk.mins, 0u, 0u, xsfrag[(sb * 2 + 1) * 32 + lane], 0u);
+    const float ma = sa.dmin * 64.0f, mb = sbk.dmin * 64.0f;
+    tot[0] = fmaf(sa.d, acc[0], fmaf(-ma, accm[0], tot[0]));
+    tot[1] = fmaf(sa.d, acc[1], fmaf(-ma, accm[1], tot[1]));
+    tot[2] = fmaf(sbk.d, acc[2], fmaf(-mb, accm[2], tot[2]));
+    tot[3] = fmaf(sbk.d, acc[3], fmaf(-mb, accm[3], tot[3]));
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Kernel. MODE as in stream_gemv.cuh: 0 linear, 1 SwiGLU, 2 grouped gate/up, 3 grouped down.
+// Work item of a warp = (row block, super-block of its K part, stream); the packed bytes of the
+// next item are requested before the current one is computed.
+// ---------------------------------------------------------------------------------------------
+template <bool Q5, int MODE, int NTERMS>
+__global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectArgs a) {
+    constexpr bool DUAL = (MODE == 1 || MODE == 2);
+    constexpr bool GROUPED = (MODE >= 2);
+    constexpr int QB = Q5 ? 176 : 144;
+
+    extern __shared__ __align__(128) uint8_t smem[];
+    float *tok_scale = reinterpret_cast<float *>(smem);           // [8] scale, [8] inverse
+    float *route_w = reinterpret_cast<float *>(smem + 128);       // [8]
+    int *seg_tokens = reinterpret_cast<int *>(smem + 192);        // [8]
+    float *partial = reinterpret_cast<float *>(smem + MD_CTRL_BYTES);
+    uint2 *bfrag = reinterpret_cast<uint2 *>(smem + a.off_bfrag);
+    uint32_t *xsfrag = reinterpret_cast<uint32_t *>(smem + a.off_xsfrag);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, tig = lane & 3;
+    const int rgi = warp / a.kp, kpi = warp - rgi * a.kp;
+    const int nsb = a.k >> 8;
+    const int nfrag = nsb * 16;
+
+    const int rows_per_block = 16 * a.rg;
+    const int blocks_per_unit = (a.n + rows_per_block - 1) / rows_per_block;
+    long long units = 1;
+    if (GROUPED) {
+        int nseg = *a.num_segments;
+        if (nseg > a.max_segments) nseg = a.max_segments;
+        units = nseg;
+    }
+    const long long total_blocks = units * blocks_per_unit;
+    const long long blk_begin = total_blocks * blockIdx.x / gridDim.x;
+    const long long blk_end = total_blocks * (blockIdx.x + 1) / gridDim.x;
+    if (blk_begin >= blk_end) return;
+
+    // items of this warp inside one row block: its super-blocks x streams
+    const int sb_count = kpi < nsb ? (nsb - kpi + a.kp - 1) / a.kp : 0;
+    const int items_per_block = sb_count * (DUAL ? 2 : 1);
+
+    auto item_pointers = [&](long long blk, int item, const uint8_t *&pa, const uint8_t *&pb) {
+        const int unit = static_cast<int>(blk / blocks_per_unit);
+        const int row0 = static_cast<int>(blk - static_cast<long long>(unit) * blocks_per_unit) * rows_per_block;
+        const int stream = DUAL ? (item & 1) : 0;
+        const int sb = kpi + (DUAL ? (item >> 1) : item) * a.kp;
+        const int expert = GROUPED ? a.seg_expert[unit] : 0;
+        const uint8_t *base = stream ? a.wb + static_cast<long long>(expert) * a.stride_b
+                                     : a.wa + static_cast<long long>(expert) * a.stride_a;
+        const int ra = min(row0 + 16 * rgi + g, a.n - 1), rb = min(row0 + 16 * rgi + g + 8, a.n - 1);
+        pa = base + static_cast<size_t>(ra) * a.rb + static_cast<size_t>(sb) * QB;
+        pb = base + static_cast<size_t>(rb) * a.rb + static_cast<size_t>(sb) * QB;
+    };
+
+    SuperBlockRegs<Q5> cur_a, cur_b, nxt_a, nxt_b;
+    if (items_per_block > 0) {
+        const uint8_t *pa, *pb;
+        item_pointers(blk_begin, 0, pa, pb);
+        load_superblock<Q5>(nxt_a, pa, tig);
+        load_superblock<Q5>(nxt_b, pb, tig);
+    }
+
+    int m_tokens = a.m;
+    int seg_begin = 0, cur_unit = -1, last_single = -1;
+    if (!GROUPED)
+        prepare_direct<NTERMS>([](int t) { return t; }, a.m, a.k, a.x, a.x_dtype, bfrag, xsfrag, tok_scale, tid);
+
+    int pbuf = 0;
+    for (long long blk = blk_begin; blk < blk_end; ++blk) {
+        const int unit = static_cast<int>(blk / blocks_per_unit);
+        const int row0 = static_cast<int>(blk - static_cast<long long>(unit) * blocks_per_unit) * rows_per_block;
+        if (GROUPED && unit != cur_unit) {
+            cur_unit = unit;
+            seg_begin = a.seg_begin[unit];
+            m_tokens = min(a.seg_count[unit], 8);
+            int single = -1;
+            if (MODE == 2 && m_tokens == 1) single = a.order[seg_begin] / a.topk;
+            const bool reuse = (single >= 0 && single == last_single);
+            last_single = single;
+            if (!reuse) {
+                named_barrier_sync(1, MD_THREADS);
+                if (tid < m_tokens) {
+                    const int flat = a.order[seg_begin + tid];
+                    seg_tokens[tid] = (MODE == 2) ? flat / a.topk : seg_begin + tid;
+                    if (MODE == 3) route_w[tid] = a.route[flat];
+                }
+                named_barrier_sync(1, MD_THREADS);
+                prepare_direct<NTERMS>([&](int t) { return seg_tokens[t]; }, m_tokens, a.k, a.x, a.x_dtype, bfrag,
+                                       xsfrag, tok_scale, tid);
+            }
+        }
+
+        float tot_a[4] = {0.f, 0.f, 0.f, 0.f}, tot_b[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int item = 0; item < items_per_block; ++item) {
+            cur_a = nxt_a;
+            cur_b = nxt_b;
+            // request the next item (same block, or the first item of the next block)
+            {
+                long long nblk = blk;
+                int nitem = item + 1;
+                if (nitem == items_per_block) { nitem = 0; ++nblk; }
+                if (nblk < blk_end) {
+                    const uint8_t *pa, *pb;
+                    item_pointers(nblk, nitem, pa, pb);
+                    load_superblock<Q5>(nxt_a, pa, tig);
+                    load_superblock<Q5>(nxt_b, pb, tig);
+                }
+            }
+            const int stream = DUAL ? (item & 1) : 0;
+            const int sb = kpi + (DUAL ? (item >> 1) : item) * a.kp;
+            if (stream == 0) superblock_mma<Q5, NTERMS>(cur_a, cur_b, bfrag, nfrag, xsfrag, sb, lane, tot_a);
+            else superblock_mma<Q5, NTERMS>(cur_a, cur_b, bfrag, nfrag, xsfrag, sb, lane, tot_b);
+        }
+
+        // combine the kp partial sums of each row group in fixed order
+        float *pb = partial + pbuf * MD_PART_FLOATS + warp * 256;
+        pb[(g * 8 + 2 * tig) * 2 + 0] = tot_a[0];
+        pb[(g * 8 + 2 * tig + 1) * 2 + 0] = tot_a[1];
+        pb[((g + 8) * 8 + 2 * tig) * 2 + 0] = tot_a[2];
+        pb[((g + 8) * 8 + 2 * tig + 1) * 2 + 0] = tot_a[3];
+        if (DUAL) {
+            pb[(g * 8 + 2 * tig) * 2 + 1] = tot_b[0];
+            pb[(g * 8 + 2 * tig + 1) * 2 + 1] = tot_b[1];
+            pb[((g + 8) * 8 + 2 * tig) * 2 + 1] = tot_b[2];
+            pb[((g + 8) * 8 + 2 * tig + 1) * 2 + 1] = tot_b[3];
+        }
+        const int group_threads = a.kp * 32;
+        if (a.kp == 1) __syncwarp();
+        else named_barrier_sync(2 + rgi, group_threads);   // rg <= 8 here: barrier ids 2..9
+        for (int o = kpi * 32 + lane; o < 128; o += group_threads) {
+            const int r = o >> 3, t = o & 7;
+            const int orow = row0 + 16 * rgi + r;
+            if (orow >= a.n || t >= m_tokens) continue;
+            const float *src = partial + pbuf * MD_PART_FLOATS + (rgi * a.kp) * 256 + (r * 8 + t) * 2;
+            float pa = 0.f, pbv = 0.f;
+            for (int kq = 0; kq < a.kp; ++kq) {
+                pa += src[kq * 256];
+                if (DUAL) pbv += src[kq * 256 + 1];
+            }
+            const float inv = tok_scale[8 + t];
+            pa *= inv;
+            pbv *= inv;
+            if (MODE == 0) store_from_float(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, pa);
+            else if (MODE == 1)
+                store_from_float(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, swiglu_f32(pa, pbv));
+            else if (MODE == 2)
+                static_cast<float *>(a.y)[static_cast<size_t>(seg_begin + t) * a.n + orow] = swiglu_f32(pa, pbv);
+            else
+                static_cast<float *>(a.y)[static_cast<size_t>(seg_begin + t) * a.n + orow] = pa * route_w[t];
+        }
+        pbuf ^= 1;
+    }
+}
+
+}  // namespace b200q

@@ -413,7 +413,7 @@ __device__ __forceinline__ void prepare_activations(RowFn row_of, int m_tokens, 
         }
 #pragma unroll
         for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        if (lane == 0) {
+        if (lane == 0 && warp < 8) {
             float s = 1.0f;
             if (amax > 0.f && amax < __int_as_float(0x7f800000)) {
                 int e;
@@ -648,7 +648,11 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_gemv_kernel(const MmaArgs a
                 return;
             }
             const int k0 = kt * kc + kpi * 256;
+#ifdef B200Q_MM_NO_COMPUTE   // measurement aid: stream the tiles, skip the arithmetic
+            if (false) {
+#else
             if (rows_live && k0 < a.k) {
+#endif
                 const uint8_t *stage = stage_base + static_cast<size_t>(s) * a.stage_bytes;
                 const int f0 = k0 >> 4;
                 {

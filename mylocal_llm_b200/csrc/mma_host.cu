@@ -1,4 +1,7 @@
 // Host-side planning and launch of the tensor-core GEMV (mma_gemv.cuh).
+#include <cstdlib>
+#include <cstring>
+
 #include "mma_gemv.cuh"
 #include "mma_host.h"
 
@@ -47,8 +50,17 @@ static bool plan(MmaArgs &a, int fmt_a, int fmt_b, bool dual, int cw) {
     return true;
 }
 
+static bool direct_allowed() {
+    const char *v = std::getenv("B200Q_KERNEL");
+    return !(v && std::strcmp(v, "staged") == 0);
+}
+
 int mma_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) {
     *launched = false;
+    if (direct_allowed()) {
+        int rc = direct_try_launch(q, stream, launched);
+        if (rc || *launched) return rc;
+    }
     const bool dual = (q.mode == 1 || q.mode == 2);
     const bool grouped = q.mode >= 2;
     if (q.k % 256 != 0 || q.k > 65536) return B200Q_OK;

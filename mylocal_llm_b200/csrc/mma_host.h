@@ -31,4 +31,7 @@ struct MmaRequest {
 // memory); otherwise leaves *launched false and the caller runs the FP32-lane kernel.
 int mma_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched);
 
+// Same contract for the direct-load kernel (Q4_K / Q5_K only); tried first.
+int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched);
+
 }  // namespace b200q

@@ -19,10 +19,12 @@ from mylocal_llm_b200.quantized_linear import DevicePackedGGUFWeight, dequantize
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=["tensor", "lanes"])
+@pytest.fixture(autouse=True, params=["tensor", "staged", "lanes"])
 def kernel_family(request, monkeypatch):
-    """Run every case on both kernel families: tensor-core fragments (default) and FP32 lanes."""
-    monkeypatch.setenv("B200Q_KERNEL", "lanes" if request.param == "lanes" else "auto")
+    """Run every case on all kernel families: "tensor" is the default selection (direct-load
+    tensor-core kernel where it applies), "staged" the bulk-copy staged tensor-core kernel,
+    "lanes" the FP32-lane kernel."""
+    monkeypatch.setenv("B200Q_KERNEL", {"tensor": "auto", "staged": "staged", "lanes": "lanes"}[request.param])
     return request.param
 FORMATS = ("Q8_0", "Q4_K", "Q5_K", "Q6_K")
 
@@ -84,8 +86,8 @@ def test_linear_identity_activations_read_back_every_coefficient(cuda, fmt, kern
     dw = packed_to_device(w)
     eye = np.eye(k, dtype=np.float32)
     y = quantized_linear(to_cuda(cuda, eye), dw).cpu().numpy()          # [k, 9]
-    if fmt == "Q4_K" and kernel_family == "tensor":
-        # the tensor-core Q4_K path folds its code offset into the min term: one extra rounding
+    if fmt == "Q4_K" and kernel_family == "staged":
+        # the staged tensor-core Q4_K path folds its code offset into the min term: one extra rounding
         np.testing.assert_allclose(y, dense.T, rtol=2e-7, atol=1e-7)
     else:
         np.testing.assert_array_equal(y, dense.T)

@@ -16,10 +16,12 @@ from mylocal_llm_b200.quantize import quantize
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=["tensor", "lanes"])
+@pytest.fixture(autouse=True, params=["tensor", "staged", "lanes"])
 def kernel_family(request, monkeypatch):
-    """Run every case on both kernel families: tensor-core fragments (default) and FP32 lanes."""
-    monkeypatch.setenv("B200Q_KERNEL", "lanes" if request.param == "lanes" else "auto")
+    """Run every case on all kernel families: "tensor" is the default selection (direct-load
+    tensor-core kernel where it applies), "staged" the bulk-copy staged tensor-core kernel,
+    "lanes" the FP32-lane kernel."""
+    monkeypatch.setenv("B200Q_KERNEL", {"tensor": "auto", "staged": "staged", "lanes": "lanes"}[request.param])
     return request.param
 
 
