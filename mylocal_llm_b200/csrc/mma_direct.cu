@@ -34,8 +34,12 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) 
     a.n = q.n; a.k = q.k; a.m = q.m;
     a.nterms = (q.x_dtype == B200Q_F32) ? 2 : 1;
     const int nsb = q.k / 256;
+    // Warps along K: as few as still give every warp of every SM a few tasks (fewer partial sums
+    // to combine, longer runs per warp), never more than there are super-blocks in a row.
+    const long long row_groups = (static_cast<long long>(q.n) + 15) / 16 * (grouped ? q.max_segments : 1);
+    const long long wanted = 3LL * sm_count() * MD_WARPS;
     int kp = 1;
-    while (kp * 2 <= MD_WARPS && kp * 2 <= nsb) kp *= 2;
+    while (kp * 2 <= MD_WARPS && kp * 2 <= nsb && row_groups * kp < wanted) kp *= 2;
     a.kp = kp;
     a.rg = MD_WARPS / kp;
     a.off_bfrag = MD_CTRL_BYTES + MD_PART_BYTES;

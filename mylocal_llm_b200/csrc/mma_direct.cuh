@@ -135,85 +135,130 @@ __device__ __forceinline__ RowScales decode_scales(const uint4 &hd, int tig) {
 // which are exactly the positions of the codes that lane extracts from word j of its quant bytes.
 // xsfrag (sb, term) holds (sum_x[sub 2*tig], sum_x[sub 2*tig+1]) / 64 for token g.
 // ---------------------------------------------------------------------------------------------
+// Four consecutive activations starting at element index e (a multiple of 4) as floats.
+// `vec_ok` tells whether the tensor allows aligned vector loads.
+__device__ __forceinline__ void load4(const void *x, int x_dtype, size_t e, bool vec_ok, float (&v)[4]) {
+    if (x_dtype == B200Q_F32) {
+        if (vec_ok) {
+            const float4 t = *reinterpret_cast<const float4 *>(static_cast<const float *>(x) + e);
+            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] = static_cast<const float *>(x)[e + i];
+        }
+    } else {
+        uint2 raw;
+        if (vec_ok) raw = *reinterpret_cast<const uint2 *>(static_cast<const uint16_t *>(x) + e);
+        else {
+            const uint16_t *p = static_cast<const uint16_t *>(x) + e;
+            raw.x = p[0] | (static_cast<uint32_t>(p[1]) << 16);
+            raw.y = p[2] | (static_cast<uint32_t>(p[3]) << 16);
+        }
+        if (x_dtype == B200Q_F16) {
+            v[0] = __half2float(__ushort_as_half(static_cast<unsigned short>(raw.x & 0xffffu)));
+            v[1] = __half2float(__ushort_as_half(static_cast<unsigned short>(raw.x >> 16)));
+            v[2] = __half2float(__ushort_as_half(static_cast<unsigned short>(raw.y & 0xffffu)));
+            v[3] = __half2float(__ushort_as_half(static_cast<unsigned short>(raw.y >> 16)));
+        } else {  // bf16: the upper 16 bits of an FP32
+            v[0] = __uint_as_float(raw.x << 16);
+            v[1] = __uint_as_float(raw.x & 0xffff0000u);
+            v[2] = __uint_as_float(raw.y << 16);
+            v[3] = __uint_as_float(raw.y & 0xffff0000u);
+        }
+    }
+}
+
 template <int NTERMS, typename RowFn>
 __device__ __forceinline__ void prepare_direct(RowFn row_of, int m_tokens, int k, const void *x, int x_dtype,
                                                uint2 *bfrag, uint32_t *xsfrag, float *tok_scale, int tid) {
     const int warp = tid >> 5, lane = tid & 31;
     const int nsb = k >> 8;
     const int nfrag = nsb * 16;
-    if (warp < 8) {
-        float amax = 0.f;
-        if (warp < m_tokens) {
-            const size_t base = static_cast<size_t>(row_of(warp)) * k;
-            for (int i = lane; i < k; i += 32) amax = fmaxf(amax, fabsf(load_as_float(x, x_dtype, base + i)));
-        }
+    const size_t esize = x_dtype == B200Q_F32 ? 4 : 2;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(x) % (4 * esize)) == 0;   // rows are multiples of 256 elements
+    unsigned int *amax_bits = reinterpret_cast<unsigned int *>(tok_scale + 16);   // [8], non-negative floats as ints
+    if (tid < 8) amax_bits[tid] = 0u;
+    named_barrier_sync(1, MD_THREADS);
+    // 1. per-token maximum magnitude, all threads: a warp's 32 chunks of 4 belong to one token
+    {
+        const int chunks_per_token = k >> 2;
+        const int total = m_tokens * chunks_per_token;
+        for (int c0 = warp * 32; c0 < total; c0 += MD_THREADS) {
+            const int c = c0 + lane;
+            const int t = c0 / chunks_per_token;
+            float v[4];
+            load4(x, x_dtype, static_cast<size_t>(row_of(t)) * k + static_cast<size_t>(c - t * chunks_per_token) * 4, vec_ok, v);
+            float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
-        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        if (lane == 0) {
-            float s = 1.0f;
-            if (amax > 0.f && amax < __int_as_float(0x7f800000)) {
-                int e;
-                frexpf(amax, &e);
-                s = ldexpf(1.0f, min(14 - e, 100));
-            }
-            tok_scale[warp] = s;
-            tok_scale[8 + warp] = 1.0f / s;
+            for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            // NaN/Inf inputs: keep the scale at 1 (the bit pattern compares above every finite value)
+            if (lane == 0) atomicMax(&amax_bits[t], __float_as_uint(amax));
         }
     }
     named_barrier_sync(1, MD_THREADS);
+    if (tid < 8) {
+        const float amax = __uint_as_float(amax_bits[tid]);
+        float s = 1.0f;
+        if (amax > 0.f && amax < __int_as_float(0x7f800000)) {
+            int e;
+            frexpf(amax, &e);
+            s = ldexpf(1.0f, min(14 - e, 100));   // scaled maximum in [2^13, 2^14)
+        }
+        tok_scale[tid] = s;
+        tok_scale[8 + tid] = 1.0f / s;
+    }
+    named_barrier_sync(1, MD_THREADS);
+    // 2. fragments: a warp builds the four fragments of one (super-block, span, nibble plane) at a time
     const int g = lane >> 2, tig = lane & 3;
     const bool live = g < m_tokens;
     const float s = tok_scale[g];
     const size_t base = live ? static_cast<size_t>(row_of(g)) * k : 0;
-    for (int sb = warp; sb < nsb; sb += MD_WARPS) {
+    for (int grp = warp; grp < nsb * 4; grp += MD_WARPS) {
+        const int sb = grp >> 2, X = (grp >> 1) & 1, nib = grp & 1;
+        const int sub = 4 * X + 2 * (tig >> 1) + nib;
+        float sum = 0.f;
 #pragma unroll
-        for (int X = 0; X < 2; ++X) {
+        for (int j = 0; j < 4; ++j) {
+            const int k0 = 256 * sb + 32 * sub + 16 * (tig & 1) + 4 * j;
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (live) {
+                load4(x, x_dtype, base + k0, vec_ok, v);
 #pragma unroll
-            for (int nib = 0; nib < 2; ++nib) {
-                const int sub = 4 * X + 2 * (tig >> 1) + nib;
-                float sum = 0.f;
+                for (int i = 0; i < 4; ++i) v[i] *= s;
+            }
+            __half hi[4], lo[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int k0 = 256 * sb + 32 * sub + 16 * (tig & 1) + 4 * j;
-                    float v[4] = {0.f, 0.f, 0.f, 0.f};
-                    if (live) {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) v[i] = load_as_float(x, x_dtype, base + k0 + i) * s;
-                    }
-                    __half hi[4], lo[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        hi[i] = __float2half_rn(v[i]);
-                        lo[i] = __float2half_rn(v[i] - __half2float(hi[i]));
-                        sum += __half2float(hi[i]);
-                        if (NTERMS == 2) sum += __half2float(lo[i]);
-                    }
-                    const int f = sb * 16 + (X * 2 + nib) * 4 + j;
-                    uint2 out;
-                    out.x = static_cast<uint32_t>(__half_as_ushort(hi[0])) | (static_cast<uint32_t>(__half_as_ushort(hi[2])) << 16);
-                    out.y = static_cast<uint32_t>(__half_as_ushort(hi[1])) | (static_cast<uint32_t>(__half_as_ushort(hi[3])) << 16);
-                    bfrag[f * 32 + lane] = out;
-                    if (NTERMS == 2) {
-                        out.x = static_cast<uint32_t>(__half_as_ushort(lo[0])) | (static_cast<uint32_t>(__half_as_ushort(lo[2])) << 16);
-                        out.y = static_cast<uint32_t>(__half_as_ushort(lo[1])) | (static_cast<uint32_t>(__half_as_ushort(lo[3])) << 16);
-                        bfrag[(nfrag + f) * 32 + lane] = out;
-                    }
-                }
-                // the other half of the sub-block's 32 positions sits in the neighbouring lane
-                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                // after both nibble planes: lanes with (tig&1)==0 own (sub even, sub odd) of pair (X, tig>>1)
-                const float scaled = sum * MD_XS_SCALE;
-                const __half h = __float2half_rn(scaled);
-                const __half l = __float2half_rn(scaled - __half2float(h));
-                // target lane of the min product: tig_t = (tig>>1) + 2*X, slots (2*tig_t, 2*tig_t+1) = (sub even, odd)
-                if ((tig & 1) == 0) {
-                    const int lane_t = 4 * g + (tig >> 1) + 2 * X;
-                    unsigned short *ph = reinterpret_cast<unsigned short *>(xsfrag + (sb * 2 + 0) * 32 + lane_t);
-                    unsigned short *pl = reinterpret_cast<unsigned short *>(xsfrag + (sb * 2 + 1) * 32 + lane_t);
-                    ph[nib] = __half_as_ushort(h);
-                    pl[nib] = __half_as_ushort(l);
+            for (int i = 0; i < 4; ++i) {
+                hi[i] = __float2half_rn(v[i]);
+                sum += __half2float(hi[i]);
+                if (NTERMS == 2) {
+                    lo[i] = __float2half_rn(v[i] - __half2float(hi[i]));
+                    sum += __half2float(lo[i]);
                 }
             }
+            const int f = sb * 16 + (X * 2 + nib) * 4 + j;
+            uint2 out;
+            out.x = static_cast<uint32_t>(__half_as_ushort(hi[0])) | (static_cast<uint32_t>(__half_as_ushort(hi[2])) << 16);
+            out.y = static_cast<uint32_t>(__half_as_ushort(hi[1])) | (static_cast<uint32_t>(__half_as_ushort(hi[3])) << 16);
+            bfrag[f * 32 + lane] = out;
+            if (NTERMS == 2) {
+                out.x = static_cast<uint32_t>(__half_as_ushort(lo[0])) | (static_cast<uint32_t>(__half_as_ushort(lo[2])) << 16);
+                out.y = static_cast<uint32_t>(__half_as_ushort(lo[1])) | (static_cast<uint32_t>(__half_as_ushort(lo[3])) << 16);
+                bfrag[(nfrag + f) * 32 + lane] = out;
+            }
+        }
+        // the other 16 positions of the sub-block sit in the neighbouring lane
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        const float scaled = sum * MD_XS_SCALE;
+        const __half h = __float2half_rn(scaled);
+        const __half l = __float2half_rn(scaled - __half2float(h));
+        // operand of the min product: lane tig_t = (tig>>1) + 2*X holds sub-blocks (2*tig_t, 2*tig_t+1)
+        if ((tig & 1) == 0) {
+            const int lane_t = 4 * g + (tig >> 1) + 2 * X;
+            unsigned short *ph = reinterpret_cast<unsigned short *>(xsfrag + (sb * 2 + 0) * 32 + lane_t);
+            unsigned short *pl = reinterpret_cast<unsigned short *>(xsfrag + (sb * 2 + 1) * 32 + lane_t);
+            ph[nib] = __half_as_ushort(h);
+            pl[nib] = __half_as_ushort(l);
         }
     }
     named_barrier_sync(1, MD_THREADS);
@@ -226,7 +271,7 @@ __device__ __forceinline__ void superblock_mma(const SuperBlockRegs<Q5> &ra, con
                                                float (&tot)[4]) {
     const int tig = lane & 3;
     const RowScales sa = decode_scales(ra.hd, tig), sbk = decode_scales(rb.hd, tig);
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
     const uint32_t qa_a[4] = {ra.qa.x, ra.qa.y, ra.qa.z, ra.qa.w}, qb_a[4] = {ra.qb.x, ra.qb.y, ra.qb.z, ra.qb.w};
     const uint32_t qa_b[4] = {rb.qa.x, rb.qa.y, rb.qa.z, rb.qa.w}, qb_b[4] = {rb.qb.x, rb.qb.y, rb.qb.z, rb.qb.w};
     const uint32_t qh_a[4] = {ra.qh.x, ra.qh.y, ra.qh.z, ra.qh.w}, qh_b[4] = {rb.qh.x, rb.qh.y, rb.qh.z, rb.qh.w};
@@ -252,10 +297,13 @@ __device__ __forceinline__ void superblock_mma(const SuperBlockRegs<Q5> &ra, con
                 const uint32_t a1 = hfma2_u32(__byte_perm(vb, 0x64646464u, 0x4240), sbk.sc[si], sbk.nsc[si]);
                 const uint32_t a3 = hfma2_u32(__byte_perm(vb, 0x64646464u, 0x4341), sbk.sc[si], sbk.nsc[si]);
                 const BFrag b = load_bfrag<NTERMS>(bfrag, nfrag, sb * 16 + si * 4 + j, lane);
-                mma_terms<NTERMS>(acc, a0, a1, a2, a3, b);
+                if (X) mma_terms<NTERMS>(acc2, a0, a1, a2, a3, b);
+                else mma_terms<NTERMS>(acc, a0, a1, a2, a3, b);
             }
         }
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] += acc2[i];
     float accm[4] = {0.f, 0.f, 0.f, 0.f};
     mma_f16(accm, sa.mins, sbk.mins, 0u, 0u, xsfrag[(sb * 2 + 0) * 32 + lane], 0u);
     mma_f16(accm, sa.mins, sbk.mins, 0u, 0u, xsfrag[(sb * 2 + 1) * 32 + lane], 0u);
@@ -309,26 +357,42 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
     const int sb_count = kpi < nsb ? (nsb - kpi + a.kp - 1) / a.kp : 0;
     const int items_per_block = sb_count * (DUAL ? 2 : 1);
 
-    auto item_pointers = [&](long long blk, int item, const uint8_t *&pa, const uint8_t *&pb) {
-        const int unit = static_cast<int>(blk / blocks_per_unit);
-        const int row0 = static_cast<int>(blk - static_cast<long long>(unit) * blocks_per_unit) * rows_per_block;
-        const int stream = DUAL ? (item & 1) : 0;
-        const int sb = kpi + (DUAL ? (item >> 1) : item) * a.kp;
+    // Row pointers of a row block for this lane (rows g and g+8 of its row group, both streams);
+    // rows past the end are clamped to the last row (loaded, never stored).
+    struct BlockPtrs {
+        const uint8_t *a_lo, *a_hi, *b_lo, *b_hi;
+    };
+    auto block_ptrs = [&](int unit, int row0) {
+        BlockPtrs p;
         const int expert = GROUPED ? a.seg_expert[unit] : 0;
-        const uint8_t *base = stream ? a.wb + static_cast<long long>(expert) * a.stride_b
-                                     : a.wa + static_cast<long long>(expert) * a.stride_a;
-        const int ra = min(row0 + 16 * rgi + g, a.n - 1), rb = min(row0 + 16 * rgi + g + 8, a.n - 1);
-        pa = base + static_cast<size_t>(ra) * a.rb + static_cast<size_t>(sb) * QB;
-        pb = base + static_cast<size_t>(rb) * a.rb + static_cast<size_t>(sb) * QB;
+        const size_t off_lo = static_cast<size_t>(min(row0 + 16 * rgi + g, a.n - 1)) * a.rb + static_cast<size_t>(kpi) * QB;
+        const size_t off_hi = static_cast<size_t>(min(row0 + 16 * rgi + g + 8, a.n - 1)) * a.rb + static_cast<size_t>(kpi) * QB;
+        const uint8_t *base_a = a.wa + static_cast<long long>(expert) * a.stride_a;
+        p.a_lo = base_a + off_lo;
+        p.a_hi = base_a + off_hi;
+        p.b_lo = p.b_hi = nullptr;
+        if (DUAL) {
+            const uint8_t *base_b = a.wb + static_cast<long long>(expert) * a.stride_b;
+            p.b_lo = base_b + off_lo;
+            p.b_hi = base_b + off_hi;
+        }
+        return p;
+    };
+    // item -> byte offset from the block pointers, and stream
+    const int sb_step_bytes = a.kp * QB;
+    auto issue_item = [&](const BlockPtrs &p, int item, SuperBlockRegs<Q5> &ra, SuperBlockRegs<Q5> &rb) {
+        const int stream = DUAL ? (item & 1) : 0;
+        const size_t off = static_cast<size_t>(DUAL ? (item >> 1) : item) * sb_step_bytes;
+        load_superblock<Q5>(ra, (stream ? p.b_lo : p.a_lo) + off, tig);
+        load_superblock<Q5>(rb, (stream ? p.b_hi : p.a_hi) + off, tig);
     };
 
+    int unit_i = static_cast<int>(blk_begin / blocks_per_unit);
+    int bi = static_cast<int>(blk_begin - static_cast<long long>(unit_i) * blocks_per_unit);
+    BlockPtrs cur_p = block_ptrs(unit_i, bi * rows_per_block), nxt_p = cur_p;
+
     SuperBlockRegs<Q5> cur_a, cur_b, nxt_a, nxt_b;
-    if (items_per_block > 0) {
-        const uint8_t *pa, *pb;
-        item_pointers(blk_begin, 0, pa, pb);
-        load_superblock<Q5>(nxt_a, pa, tig);
-        load_superblock<Q5>(nxt_b, pb, tig);
-    }
+    if (items_per_block > 0) issue_item(cur_p, 0, nxt_a, nxt_b);
 
     int m_tokens = a.m;
     int seg_begin = 0, cur_unit = -1, last_single = -1;
@@ -337,8 +401,12 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
 
     int pbuf = 0;
     for (long long blk = blk_begin; blk < blk_end; ++blk) {
-        const int unit = static_cast<int>(blk / blocks_per_unit);
-        const int row0 = static_cast<int>(blk - static_cast<long long>(unit) * blocks_per_unit) * rows_per_block;
+        const int unit = unit_i;
+        const int row0 = bi * rows_per_block;
+        // advance the (unit, block-in-unit) counters and look up the next block's pointers
+        if (++bi == blocks_per_unit) { bi = 0; ++unit_i; }
+        const bool has_next = blk + 1 < blk_end;
+        if (has_next) nxt_p = block_ptrs(unit_i, bi * rows_per_block);
         if (GROUPED && unit != cur_unit) {
             cur_unit = unit;
             seg_begin = a.seg_begin[unit];
@@ -365,17 +433,8 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
             cur_a = nxt_a;
             cur_b = nxt_b;
             // request the next item (same block, or the first item of the next block)
-            {
-                long long nblk = blk;
-                int nitem = item + 1;
-                if (nitem == items_per_block) { nitem = 0; ++nblk; }
-                if (nblk < blk_end) {
-                    const uint8_t *pa, *pb;
-                    item_pointers(nblk, nitem, pa, pb);
-                    load_superblock<Q5>(nxt_a, pa, tig);
-                    load_superblock<Q5>(nxt_b, pb, tig);
-                }
-            }
+            if (item + 1 < items_per_block) issue_item(cur_p, item + 1, nxt_a, nxt_b);
+            else if (has_next) issue_item(nxt_p, 0, nxt_a, nxt_b);
             const int stream = DUAL ? (item & 1) : 0;
             const int sb = kpi + (DUAL ? (item >> 1) : item) * a.kp;
             if (stream == 0) superblock_mma<Q5, NTERMS>(cur_a, cur_b, bfrag, nfrag, xsfrag, sb, lane, tot_a);
@@ -419,6 +478,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
                 static_cast<float *>(a.y)[static_cast<size_t>(seg_begin + t) * a.n + orow] = pa * route_w[t];
         }
         pbuf ^= 1;
+        cur_p = nxt_p;
     }
 }
 
