@@ -46,6 +46,13 @@ WORKLOADS = {
     "gemv_q8_0_4096x4096_m8": ("Q8_0", 4096, 4096, 8, "float32"),
     "gemv_q4k_65536x8192_m1": ("Q4_K", 65536, 8192, 1, "bfloat16"),
 }
+# name: (layers, tokens per step, chained)  - the packed MoE layer of the baseline's fourth configuration
+# (hidden 2048, 512 experts of width 512, top-10, shared expert, Q4_K gate/up + Q6_K down); "stack" = the
+# 48-layer decode step of the fifth configuration (RMSNorm + residual per layer, identity token mixing).
+MOE_WORKLOADS = {
+    "moe_layer_t1": (8, 1, False), "moe_layer_t16": (8, 16, False), "moe_layer_t64": (4, 64, False),
+    "moe_layer_t256": (2, 256, False), "moe_stack_b1": (48, 1, True), "moe_stack_b64": (48, 64, True),
+}
 DEFAULT_WORKLOAD = "gemv_q4k_8192x2048_m1"
 
 
@@ -324,20 +331,230 @@ def run_gpu_arm(args, name):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------ MoE workloads
+MOE_SHAPE = dict(d_model=2048, d_ff=512, n_experts=512, top_k=10, shared_d_ff=512)
+EXPERT_BYTES = 2 * packed_bytes("Q4_K", 512, 2048) + packed_bytes("Q6_K", 2048, 512)
+
+
+def cpu_moe_throughput(layers, seconds):
+    """Reference CPU expert FFN (one token, Q4_K/Q4_K/Q6_K, D=2048, F=512) over all host threads;
+    returns decode tokens/s of a `layers`-deep stack: each token needs (top_k + 1) expert FFNs per layer."""
+    from oracle import build_oracle as bo
+    from mylocal_llm_b200.quantize import random_packed
+    handle = bo.load_ref()
+    kind = "reference"
+    if handle is None:
+        handle, kind = bo.load_port(), "port"
+    d, f = MOE_SHAPE["d_model"], MOE_SHAPE["d_ff"]
+    trip = [random_packed(q, sh, seed=i, d=1 / 2048, dmin=1 / 4096)
+            for i, (q, sh) in enumerate((("Q4_K", (f, d)), ("Q4_K", (f, d)), ("Q6_K", (d, f))))]
+    x = np.random.default_rng(0).normal(0, 1, (1, d)).astype(np.float32)
+    threads = cpu_threads()
+    from concurrent.futures import ThreadPoolExecutor
+    pool = ThreadPoolExecutor(threads)
+    work = lambda _: bo.cpu_expert(handle, (trip[0].data, "Q4_K"), (trip[1].data, "Q4_K"), (trip[2].data, "Q6_K"), d, f, x)
+    list(pool.map(work, range(threads)))
+    calls, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < seconds:
+        list(pool.map(work, range(threads * 4)))
+        calls += threads * 4
+    elapsed = time.perf_counter() - t0
+    pool.shutdown()
+    per_token = layers * (MOE_SHAPE["top_k"] + 1)
+    sample = f"{calls} single-token expert FFNs (Q4_K/Q4_K/Q6_K, D={d}, F={f}) in {elapsed:.1f} s"
+    return calls / elapsed / per_token, kind, threads, sample
+
+
+def run_moe_reference_arm(args, name):
+    layers, tokens, chained = MOE_WORKLOADS[name]
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    eff_layers = layers if chained else 1
+    per_step = max(1.0, 20.0 / max(1, args.steps + args.warmup))
+    runs = [cpu_moe_throughput(eff_layers, per_step) for _ in range(args.warmup + args.steps)][args.warmup:]
+    tps = statistics.mean(r[0] for r in runs)
+    line = {
+        "impl": "reference", "metric": "MoE decode tokens/s", "value": round(tps, 4), "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * tokens / tps, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "layers": eff_layers, "tokens_per_step": tokens, **MOE_SHAPE,
+                   "formats": "Q4_K gate/up, Q6_K down", "l2": "CPU run; each step is a bounded sample of expert FFNs"},
+        "cpu_baseline": {"value": round(tps, 4), "unit": "tokens/s", "cores": runs[0][2], "kind": runs[0][1],
+                         "sample": runs[0][3]},
+        "e2e": {"value": round(tps, 4), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def run_moe_gpu_arm(args, name):
+    import torch
+    import torch.distributed as dist
+    from mylocal_llm_b200 import _lib, moe_ops
+    from mylocal_llm_b200.moe_stack import PackedMoEStack
+
+    layers, tokens, chained = MOE_WORKLOADS[name]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the kernels)")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    stack = PackedMoEStack.synthetic(layers, seed=rank, **MOE_SHAPE)
+    d = MOE_SHAPE["d_model"]
+    rng = np.random.default_rng(11 + rank)
+    host_x = torch.from_numpy(rng.normal(0, 1, (1, tokens, d)).astype(np.float32)).pin_memory()
+    dev_x = host_x.cuda()
+    host_y = torch.empty((1, tokens, d), dtype=torch.float32).pin_memory()
+
+    def step_fn():
+        if chained:
+            return stack.forward(dev_x)[0]
+        outs = None
+        hidden = dev_x.to(torch.bfloat16)
+        for layer in stack.layers:                       # independent layers: distinct weights defeat L2
+            outs = layer.forward(hidden)
+        return outs.float()
+
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        # launches per step, counted once through the library's call log
+        calls = []
+        real_call = _lib.call
+        _lib.call = lambda fn, *a: (calls.append(fn), real_call(fn, *a))[1]
+        out = step_fn()
+        stream.synchronize()
+        _lib.call = real_call
+        launches_per_step = len(calls)
+        step_fn()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            out = step_fn()
+
+        def barrier():
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        for _ in range(max(3, args.warmup)):
+            graph.replay()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        barrier()
+        dev_ms = e0.elapsed_time(e1)
+
+        def e2e_step():
+            dev_x.copy_(host_x, non_blocking=True)
+            graph.replay()
+            host_y.copy_(out, non_blocking=True)
+
+        for _ in range(max(3, args.warmup)):
+            e2e_step()
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record(stream)
+        for _ in range(args.steps):
+            e2e_step()
+        f1.record(stream)
+        barrier()
+        e2e_ms = f0.elapsed_time(f1)
+        clocks = sampler.stop() if rank == 0 else None
+
+        # dominant kernel (grouped gate/up): its own duration and bytes, eager launches with events
+        records = []
+        real_gate_up = moe_ops.moe_gate_up
+
+        def timed_gate_up(x2d, plan, *a, **kw):
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record(stream)
+            res = real_gate_up(x2d, plan, *a, **kw)
+            a1.record(stream)
+            records.append((a0, a1, plan.counts))
+            return res
+
+        moe_ops.moe_gate_up = timed_gate_up
+        for _ in range(2):
+            records.clear()
+            step_fn()
+            stream.synchronize()
+        moe_ops.moe_gate_up = real_gate_up
+        gate_up_ms = [a0.elapsed_time(a1) for a0, a1, _ in records]
+        distinct = [int((c > 0).sum().item()) for _, _, c in records]
+
+    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = (float(v) for v in times.cpu())
+    if _lib.device_status():
+        raise SystemExit("device status word is set: a kernel gave up on a bounded wait")
+
+    if rank == 0:
+        tokens_per_step = tokens * (1 if chained else layers)
+        value = tokens_per_step * world * args.steps / (dev_ms * 1e-3)
+        e2e_value = tokens_per_step * world * args.steps / (e2e_ms * 1e-3)
+        peak, peak_kind = measured_peaks()
+        gu_bytes = statistics.mean(distinct) * 2 * packed_bytes("Q4_K", 512, 2048) + tokens * d * 2 \
+            + tokens * MOE_SHAPE["top_k"] * 512 * 4
+        gu_us = statistics.mean(gate_up_ms) * 1e3
+        achieved = gu_bytes / (gu_us * 1e-6) / 1e9
+        layer_bytes = statistics.mean(distinct) * EXPERT_BYTES + EXPERT_BYTES + 4 * 2048 * 512 + 2 * tokens * d * 2
+        line = {
+            "metric": "MoE decode tokens/s", "value": round(value, 2), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 5),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": name, "layers": layers, "tokens_per_step": tokens, "chained": chained, **MOE_SHAPE,
+                       "formats": "Q4_K gate/up, Q6_K down", "activation": "bfloat16, FP32 residual",
+                       "packed_bytes_resident": stack.packed_bytes,
+                       "parallelism": "replicas only" if world > 1 else "single GPU",
+                       "l2": f"{layers} distinct layers per step, {layer_bytes * layers / 1e6:.0f} MB touched per step",
+                       "timing": "CUDA graph of one step, CUDA events on the launch stream",
+                       "distinct_experts_per_layer": round(statistics.mean(distinct), 1),
+                       "algorithmic_bytes_per_layer": int(layer_bytes),
+                       "layer_GBs": round(layer_bytes * layers * args.steps / (dev_ms * 1e-3) / 1e9, 1)},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "peak_source": f"of {peak_kind}",
+                         "frac_of_nominal_8TBs": round(achieved / 8000.0, 4), "traffic": None,
+                         "kernel": "grouped gate/up + SwiGLU (mma_direct_kernel, mode 2)",
+                         "us_per_launch": round(gu_us, 3), "algorithmic_bytes_per_launch": int(gu_bytes)},
+            "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s",
+                    "h2d_bytes_per_step": int(host_x.numel() * 4), "d2h_bytes_per_step": int(host_y.numel() * 4)},
+            "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+        }
+        if world == 1 and not args.skip_cpu_baseline:
+            tps, kind, cores, sample = cpu_moe_throughput(layers if chained else 1, 12.0)
+            line["cpu_baseline"] = {"value": round(tps, 4), "unit": "tokens/s", "cores": cores, "kind": kind,
+                                    "sample": sample}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(MOE_WORKLOADS))
     ap.add_argument("--skip-cpu-baseline", action="store_true",
                     help="omit the host-core baseline leg (exploratory runs only)")
     args = ap.parse_args()
+    moe = args.workload in MOE_WORKLOADS
     if args.impl == "reference":
-        run_reference_arm(args, args.workload)
+        (run_moe_reference_arm if moe else run_reference_arm)(args, args.workload)
     else:
-        run_gpu_arm(args, args.workload)
+        (run_moe_gpu_arm if moe else run_gpu_arm)(args, args.workload)
 
 
 if __name__ == "__main__":

@@ -119,11 +119,15 @@ int b200q_moe_plan(const void *ids, int ids_is_i64, int rows, int k, int e, int 
 /* Grouped gate/up + SwiGLU over the plan's segments:
  *   hbuf[pos, f] (fp32) = silu(x[token(pos)] . G_e) * (x[token(pos)] . U_e)
  * for every sorted position pos of every segment; token(pos) = order[pos] / k.
- * Expert e's matrices start at gate_base + e*gate_stride (bytes) etc.
+ * Expert e's matrices start at gate_base + e*gate_stride (bytes) inside a contiguous bank, or, when
+ * gate_table / up_table (device arrays of one address per expert, the reference's pointer table of
+ * mini_llm/ops/grouped_quantized_experts.py:186-196) are given, at table[e]; tables_aligned16 != 0
+ * promises that every table entry is 16-byte aligned (enables the tensor-core kernels).
  * Replaces _grouped_gate_up (mini_llm/ops/grouped_quantized_experts.py:31-43) and the
  * per-expert loop of ExpertsInference.forward (mini_llm/ops/experts_inference.py:293-310). */
 int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, const void *up_base,
-                      int64_t up_stride, int up_fmt, int f, int d, const void *x, int x_dtype, int k,
+                      int64_t up_stride, int up_fmt, const uint64_t *gate_table, const uint64_t *up_table,
+                      int tables_aligned16, int f, int d, const void *x, int x_dtype, int k,
                       const int32_t *order, const int32_t *seg_expert, const int32_t *seg_begin,
                       const int32_t *seg_count, const int32_t *num_segments, int max_segments,
                       float *hbuf, void *stream);
@@ -131,8 +135,8 @@ int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, 
 /* Grouped down projection with the route weight applied and stored per assignment:
  *   terms[pos, d] (fp32) = (hbuf[pos] . D_e) * route[order[pos]]
  * Replaces _grouped_down_weighted (mini_llm/ops/grouped_quantized_experts.py:45-68). */
-int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, int d, int f,
-                   const float *hbuf, const float *route, const int32_t *order,
+int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, const uint64_t *down_table,
+                   int tables_aligned16, int d, int f, const float *hbuf, const float *route, const int32_t *order,
                    const int32_t *seg_expert, const int32_t *seg_begin, const int32_t *seg_count,
                    const int32_t *num_segments, int max_segments, float *terms, void *stream);
 

@@ -16,7 +16,17 @@ from .quantized_linear import (
     supports_packed_gpu_type,
 )
 
+from .router_inference import RouterInference, expert_topk_forward, try_normalized_topk
+from .experts_inference import (ExpertsInference, PackedExpertBank, ResidentExpertExecutor,
+                                routed_experts_forward, synthetic_bank)
+from .grouped_quantized_experts import (grouped_quantized_experts_forward,
+                                        supports_grouped_quantized_experts)
+from .moe_layer import PackedMoELayer, RMSNormInference
+
 __all__ = [
+    "RouterInference", "expert_topk_forward", "try_normalized_topk", "ExpertsInference", "PackedExpertBank",
+    "ResidentExpertExecutor", "routed_experts_forward", "synthetic_bank", "grouped_quantized_experts_forward",
+    "supports_grouped_quantized_experts", "PackedMoELayer", "RMSNormInference",
     "BLOCK_FORMATS", "PackedGGUFWeight", "SUPPORTED_GPU_PACKED_FORMATS", "DevicePackedGGUFWeight",
     "PackedExpertFFNInference", "packed_to_device", "quantized_linear", "quantized_swiglu",
     "supports_packed_gpu_type",

@@ -34,10 +34,10 @@ SIGNATURES = {
     "b200q_router_topk": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_f32, _ptr, _ptr, _ptr],
     "b200q_moe_plan": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
                        _ptr, _c_int, _ptr, _ptr],
-    "b200q_moe_gate_up": [_ptr, _c_i64, _c_int, _ptr, _c_i64, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int,
-                          _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr],
-    "b200q_moe_down": [_ptr, _c_i64, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
-                       _ptr, _ptr],
+    "b200q_moe_gate_up": [_ptr, _c_i64, _c_int, _ptr, _c_i64, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr,
+                          _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr],
+    "b200q_moe_down": [_ptr, _c_i64, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+                       _c_int, _ptr, _ptr],
     "b200q_moe_combine": [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr],
 }
 

@@ -73,6 +73,14 @@ __device__ __forceinline__ float swiglu_f32(float g, float u) {
     return (g * s) * u;
 }
 
+// Start of expert `e`'s packed matrix: entry of a device pointer table when one is given,
+// otherwise base + e * stride inside a contiguous bank.
+__device__ __forceinline__ const uint8_t *expert_matrix(const uint8_t *base, long long stride,
+                                                        const unsigned long long *table, int e) {
+    if (table) return reinterpret_cast<const uint8_t *>(static_cast<uintptr_t>(table[e]));
+    return base + static_cast<long long>(e) * stride;
+}
+
 __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

@@ -26,10 +26,12 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) 
     if (q.k % 256 != 0 || q.m > 8) return B200Q_OK;
     if (reinterpret_cast<uintptr_t>(q.wa) & 15) return B200Q_OK;
     if (dual && (reinterpret_cast<uintptr_t>(q.wb) & 15)) return B200Q_OK;
-    if (grouped && ((q.stride_a & 15) || (dual && (q.stride_b & 15)))) return B200Q_OK;
+    if (grouped && !q.table_a && ((q.stride_a & 15) || (dual && (q.stride_b & 15)))) return B200Q_OK;
+    if (grouped && q.table_a && !q.tables_aligned16) return B200Q_OK;
 
     DirectArgs a{};
     a.wa = q.wa; a.wb = q.wb; a.stride_a = q.stride_a; a.stride_b = q.stride_b;
+    a.table_a = q.table_a; a.table_b = q.table_b;
     a.rb = q.k / 256 * fmt_bytes(q.fmt_a);
     a.n = q.n; a.k = q.k; a.m = q.m;
     a.nterms = (q.x_dtype == B200Q_F32) ? 2 : 1;

@@ -35,6 +35,7 @@ struct DirectArgs {
     const uint8_t *wa;
     const uint8_t *wb;
     long long stride_a, stride_b;
+    const unsigned long long *table_a, *table_b;   // optional per-expert pointer tables
     int rb;              // packed bytes per weight row (both streams share the format)
     int n, k, m;
     int kp, rg;          // warps along K and row groups per CTA pass (kp * rg == 16)
@@ -367,12 +368,12 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
         const int expert = GROUPED ? a.seg_expert[unit] : 0;
         const size_t off_lo = static_cast<size_t>(min(row0 + 16 * rgi + g, a.n - 1)) * a.rb + static_cast<size_t>(kpi) * QB;
         const size_t off_hi = static_cast<size_t>(min(row0 + 16 * rgi + g + 8, a.n - 1)) * a.rb + static_cast<size_t>(kpi) * QB;
-        const uint8_t *base_a = a.wa + static_cast<long long>(expert) * a.stride_a;
+        const uint8_t *base_a = expert_matrix(a.wa, a.stride_a, a.table_a, expert);
         p.a_lo = base_a + off_lo;
         p.a_hi = base_a + off_hi;
         p.b_lo = p.b_hi = nullptr;
         if (DUAL) {
-            const uint8_t *base_b = a.wb + static_cast<long long>(expert) * a.stride_b;
+            const uint8_t *base_b = expert_matrix(a.wb, a.stride_b, a.table_b, expert);
             p.b_lo = base_b + off_lo;
             p.b_hi = base_b + off_hi;
         }

@@ -42,10 +42,13 @@ struct MmaArgs {
     const uint8_t *wa;
     const uint8_t *wb;
     long long stride_a, stride_b;
+    const unsigned long long *table_a, *table_b;   // optional per-expert pointer tables
     int rb_a, rb_b;      // packed bytes per full weight row
     int n, k, m;
     int kp, rg;          // warps along K, row groups per tile (kp * rg == cw)
     int cw;              // consumer warps that compute (8, or 4 when shared memory is tight)
+    int contig;          // 1: a tile spans whole rows and is fetched with one copy per stream
+                         //    (pitch == row bytes); 0: one copy per row segment into padded slots
     int seg_a, seg_b;    // packed bytes of one row segment of a full tile (kp * 256 positions)
     int pitch_a, pitch_b;  // shared-memory bytes per row slot (== 16 mod 128)
     int region_a;        // bytes of stream A inside a stage
@@ -526,8 +529,8 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_gemv_kernel(const MmaArgs a
             const int row0 = static_cast<int>(blk - static_cast<long long>(unit) * blocks_per_unit) * rows_per_block;
             const int rows = min(rows_per_block, a.n - row0);
             const int expert = GROUPED ? a.seg_expert[unit] : 0;
-            const uint8_t *base_a = a.wa + static_cast<long long>(expert) * a.stride_a;
-            const uint8_t *base_b = DUAL ? a.wb + static_cast<long long>(expert) * a.stride_b : nullptr;
+            const uint8_t *base_a = expert_matrix(a.wa, a.stride_a, a.table_a, expert);
+            const uint8_t *base_b = DUAL ? expert_matrix(a.wb, a.stride_b, a.table_b, expert) : nullptr;
             for (int kt = 0; kt < ktiles; ++kt, ++it) {
                 if (*abort_flag) return;
                 const int s = it % S;
@@ -537,14 +540,19 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_gemv_kernel(const MmaArgs a
                 }
                 uint8_t *stage = stage_base + static_cast<size_t>(s) * a.stage_bytes;
                 const int kvalid = min(kc, a.k - kt * kc);
-                const uint32_t len_a = static_cast<uint32_t>(kvalid / QK_A * QB_A);
-                const uint32_t len_b = DUAL ? static_cast<uint32_t>(kvalid / QK_B * QB_B) : 0u;
+                // contiguous mode: the whole tile is one "row" of rows * row_bytes
+                const int copies = a.contig ? 1 : rows;
+                const uint32_t len_a = a.contig ? static_cast<uint32_t>(rows) * a.rb_a
+                                                : static_cast<uint32_t>(kvalid / QK_A * QB_A);
+                const uint32_t len_b = !DUAL ? 0u
+                                       : a.contig ? static_cast<uint32_t>(rows) * a.rb_b
+                                                  : static_cast<uint32_t>(kvalid / QK_B * QB_B);
                 // pass 1: total bytes of all aligned windows; the few bytes a window may not cover
                 // at the very end of a matrix are copied by hand before the barrier is armed
                 const uintptr_t lim_a = reinterpret_cast<uintptr_t>(base_a) + static_cast<size_t>(a.n) * a.rb_a;
                 const uintptr_t lim_b = DUAL ? reinterpret_cast<uintptr_t>(base_b) + static_cast<size_t>(a.n) * a.rb_b : 0;
                 uint32_t tx = 0;
-                for (int r = lane; r < rows; r += 32) {
+                for (int r = lane; r < copies; r += 32) {
                     const uintptr_t ga = reinterpret_cast<uintptr_t>(base_a + static_cast<size_t>(row0 + r) * a.rb_a +
                                                                      static_cast<size_t>(kt) * a.seg_a);
                     const CopyWindow wa = copy_window(ga, len_a, lim_a);
@@ -571,8 +579,8 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_gemv_kernel(const MmaArgs a
                     else mbar_arrive(&full_bar[s]);
                 }
                 __syncwarp();
-                // pass 2: one bulk copy per row segment
-                for (int r = lane; r < rows; r += 32) {
+                // pass 2: one bulk copy per row segment (or per tile)
+                for (int r = lane; r < copies; r += 32) {
                     const uintptr_t ga = reinterpret_cast<uintptr_t>(base_a + static_cast<size_t>(row0 + r) * a.rb_a +
                                                                      static_cast<size_t>(kt) * a.seg_a);
                     const CopyWindow wa = copy_window(ga, len_a, lim_a);
@@ -614,8 +622,8 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_gemv_kernel(const MmaArgs a
         const uint8_t *base_a = a.wa, *base_b = a.wb;
         if (GROUPED) {
             const int expert = a.seg_expert[unit];
-            base_a += static_cast<long long>(expert) * a.stride_a;
-            if (DUAL) base_b += static_cast<long long>(expert) * a.stride_b;
+            base_a = expert_matrix(a.wa, a.stride_a, a.table_a, expert);
+            if (DUAL) base_b = expert_matrix(a.wb, a.stride_b, a.table_b, expert);
             if (unit != cur_unit) {
                 cur_unit = unit;
                 seg_begin = a.seg_begin[unit];
@@ -660,8 +668,9 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_gemv_kernel(const MmaArgs a
                     const size_t seg_off = static_cast<size_t>(kt) * a.seg_a;
                     const int task_off = kpi * (256 / QK_A * QB_A);
                     auto slot = [&](int r) -> const uint8_t * {
+                        const int head_row = a.contig ? row0 : my_row + r;
                         const int head = static_cast<int>(
-                            reinterpret_cast<uintptr_t>(base_a + static_cast<size_t>(my_row + r) * a.rb_a + seg_off) & 15);
+                            reinterpret_cast<uintptr_t>(base_a + static_cast<size_t>(head_row) * a.rb_a + seg_off) & 15);
                         return stage + static_cast<size_t>(16 * rgi + r) * a.pitch_a + head + task_off;
                     };
                     FA::header(slot(lane & 15), lane, stab);
@@ -672,8 +681,9 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_gemv_kernel(const MmaArgs a
                     const size_t seg_off = static_cast<size_t>(kt) * a.seg_b;
                     const int task_off = kpi * (256 / QK_B * QB_B);
                     auto slot = [&](int r) -> const uint8_t * {
+                        const int head_row = a.contig ? row0 : my_row + r;
                         const int head = static_cast<int>(
-                            reinterpret_cast<uintptr_t>(base_b + static_cast<size_t>(my_row + r) * a.rb_b + seg_off) & 15);
+                            reinterpret_cast<uintptr_t>(base_b + static_cast<size_t>(head_row) * a.rb_b + seg_off) & 15);
                         return stage + a.region_a + static_cast<size_t>(16 * rgi + r) * a.pitch_b + head + task_off;
                     };
                     FB::header(slot(lane & 15), lane, stab + 256);

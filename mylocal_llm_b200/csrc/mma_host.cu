@@ -21,6 +21,17 @@ static int slot_pitch(int seg_bytes) {
     return p;
 }
 
+// Worst number of lanes of one 32-bit shared-memory load that fall on the same bank when eight
+// rows `row_bytes` apart are read at the same column (four consecutive words per row).
+static int bank_conflict_degree(int row_bytes) {
+    int hits[32] = {0};
+    for (int g = 0; g < 8; ++g)
+        for (int t = 0; t < 4; ++t) ++hits[((static_cast<long long>(g) * row_bytes) / 4 + t) & 31];
+    int worst = 0;
+    for (int b = 0; b < 32; ++b) worst = hits[b] > worst ? hits[b] : worst;
+    return worst;
+}
+
 static bool plan(MmaArgs &a, int fmt_a, int fmt_b, bool dual, int cw) {
     int kp = 1;
     while (kp * 2 <= cw && kp * 2 * 256 <= a.k) kp *= 2;
@@ -28,14 +39,25 @@ static bool plan(MmaArgs &a, int fmt_a, int fmt_b, bool dual, int cw) {
     a.kp = kp;
     a.rg = cw / kp;
     a.seg_a = kp * 256 / fmt_elems(fmt_a) * fmt_bytes(fmt_a);
-    a.pitch_a = slot_pitch(a.seg_a);
-    a.region_a = 16 * a.rg * a.pitch_a;
-    a.seg_b = a.pitch_b = 0;
+    a.seg_b = dual ? kp * 256 / fmt_elems(fmt_b) * fmt_bytes(fmt_b) : 0;
+    // One copy per tile when the tile spans whole rows and the natural row stride spreads the
+    // rows over the banks; otherwise one copy per row into padded slots.
+    a.contig = (kp * 256 >= a.k && bank_conflict_degree(a.rb_a) <= 2 &&
+                (!dual || bank_conflict_degree(a.rb_b) <= 2)) ? 1 : 0;
     int region_b = 0;
-    if (dual) {
-        a.seg_b = kp * 256 / fmt_elems(fmt_b) * fmt_bytes(fmt_b);
-        a.pitch_b = slot_pitch(a.seg_b);
-        region_b = 16 * a.rg * a.pitch_b;
+    if (a.contig) {
+        a.pitch_a = a.rb_a;
+        a.region_a = (16 * a.rg * a.rb_a + 32 + 15) / 16 * 16;
+        a.pitch_b = dual ? a.rb_b : 0;
+        if (dual) region_b = (16 * a.rg * a.rb_b + 32 + 15) / 16 * 16;
+    } else {
+        a.pitch_a = slot_pitch(a.seg_a);
+        a.region_a = 16 * a.rg * a.pitch_a;
+        a.pitch_b = 0;
+        if (dual) {
+            a.pitch_b = slot_pitch(a.seg_b);
+            region_b = 16 * a.rg * a.pitch_b;
+        }
     }
     a.stage_bytes = a.region_a + region_b;
     a.off_bfrag = MM_CTRL_BYTES + MM_STAB_BYTES + MM_PART_BYTES;
@@ -67,12 +89,14 @@ int mma_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) {
     if (dual && q.fmt_a != q.fmt_b) return B200Q_OK;
     if (reinterpret_cast<uintptr_t>(q.wa) & 15) return B200Q_OK;
     if (dual && (reinterpret_cast<uintptr_t>(q.wb) & 15)) return B200Q_OK;
-    if (grouped && ((q.stride_a & 15) || (dual && (q.stride_b & 15)))) return B200Q_OK;
+    if (grouped && !q.table_a && ((q.stride_a & 15) || (dual && (q.stride_b & 15)))) return B200Q_OK;
+    if (grouped && q.table_a && !q.tables_aligned16) return B200Q_OK;
     if (q.m > 8) return B200Q_OK;
 
     MmaArgs a{};
     a.wa = q.wa; a.wb = q.wb;
     a.stride_a = q.stride_a; a.stride_b = q.stride_b;
+    a.table_a = q.table_a; a.table_b = q.table_b;
     a.rb_a = q.k / fmt_elems(q.fmt_a) * fmt_bytes(q.fmt_a);
     a.rb_b = dual ? q.k / fmt_elems(q.fmt_b) * fmt_bytes(q.fmt_b) : 0;
     a.n = q.n; a.k = q.k; a.m = q.m;

@@ -11,6 +11,8 @@ struct MmaRequest {
     const uint8_t *wb;
     int fmt_a, fmt_b;
     long long stride_a, stride_b;
+    const unsigned long long *table_a, *table_b;   // optional per-expert pointer tables
+    int tables_aligned16;                          // caller vouches: every table entry is 16-byte aligned
     int n, k, m;
     const void *x;
     int x_dtype;

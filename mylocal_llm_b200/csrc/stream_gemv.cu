@@ -220,11 +220,12 @@ int b200q_swiglu(const void *gate, int gate_fmt, const void *up, int up_fmt, int
 }
 
 int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, const void *up_base,
-                      int64_t up_stride, int up_fmt, int f, int d, const void *x, int x_dtype, int k,
+                      int64_t up_stride, int up_fmt, const uint64_t *gate_table, const uint64_t *up_table,
+                      int tables_aligned16, int f, int d, const void *x, int x_dtype, int k,
                       const int32_t *order, const int32_t *seg_expert, const int32_t *seg_begin,
                       const int32_t *seg_count, const int32_t *num_segments, int max_segments, float *hbuf,
                       void *stream) {
-    if (!gate_base || !up_base || !x || !order || !seg_expert || !seg_begin || !seg_count || !num_segments || !hbuf)
+    if ((!gate_table != !up_table) || (!gate_table && (!gate_base || !up_base)) || !x || !order || !seg_expert || !seg_begin || !seg_count || !num_segments || !hbuf)
         return fail(B200Q_EINVAL, "moe_gate_up: NULL pointer");
     if (!fmt_valid(gate_fmt) || !fmt_valid(up_fmt) || !dtype_valid(x_dtype))
         return fail(B200Q_EINVAL, "moe_gate_up: bad format/dtype");
@@ -237,6 +238,8 @@ int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, 
     a.wb = static_cast<const uint8_t *>(up_base);
     a.stride_a = gate_stride;
     a.stride_b = up_stride;
+    a.table_a = reinterpret_cast<const unsigned long long *>(gate_table);
+    a.table_b = reinterpret_cast<const unsigned long long *>(up_table);
     a.rb_a = d / fmt_elems(gate_fmt) * fmt_bytes(gate_fmt);
     a.rb_b = d / fmt_elems(up_fmt) * fmt_bytes(up_fmt);
     a.n = f;
@@ -257,7 +260,8 @@ int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, 
     if (mma_allowed()) {
         MmaRequest q{};
         q.mode = 2; q.wa = a.wa; q.wb = a.wb; q.fmt_a = gate_fmt; q.fmt_b = up_fmt; q.stride_a = gate_stride;
-        q.stride_b = up_stride; q.n = f; q.k = d; q.m = MAX_TOKENS; q.x = x; q.x_dtype = x_dtype; q.y = hbuf;
+        q.stride_b = up_stride; q.table_a = a.table_a; q.table_b = a.table_b; q.tables_aligned16 = tables_aligned16;
+        q.n = f; q.k = d; q.m = MAX_TOKENS; q.x = x; q.x_dtype = x_dtype; q.y = hbuf;
         q.y_dtype = B200Q_F32; q.topk = k; q.order = order; q.seg_expert = seg_expert; q.seg_begin = seg_begin;
         q.seg_count = seg_count; q.num_segments = num_segments; q.max_segments = max_segments; q.status = status;
         bool launched = false;
@@ -272,11 +276,12 @@ int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, 
                   "moe_gate_up");
 }
 
-int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, int d, int f, const float *hbuf,
+int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, const uint64_t *down_table,
+                   int tables_aligned16, int d, int f, const float *hbuf,
                    const float *route, const int32_t *order, const int32_t *seg_expert, const int32_t *seg_begin,
                    const int32_t *seg_count, const int32_t *num_segments, int max_segments, float *terms,
                    void *stream) {
-    if (!down_base || !hbuf || !route || !order || !seg_expert || !seg_begin || !seg_count || !num_segments || !terms)
+    if ((!down_base && !down_table) || !hbuf || !route || !order || !seg_expert || !seg_begin || !seg_count || !num_segments || !terms)
         return fail(B200Q_EINVAL, "moe_down: NULL pointer");
     if (!fmt_valid(down_fmt)) return fail(B200Q_EINVAL, "moe_down: bad format");
     if (d <= 0 || max_segments <= 0 || !k_ok(down_fmt, f)) return fail(B200Q_EINVAL, "moe_down: bad shape d=%d f=%d", d, f);
@@ -285,6 +290,7 @@ int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, int
     StreamArgs a{};
     a.wa = static_cast<const uint8_t *>(down_base);
     a.stride_a = down_stride;
+    a.table_a = reinterpret_cast<const unsigned long long *>(down_table);
     a.rb_a = f / fmt_elems(down_fmt) * fmt_bytes(down_fmt);
     a.n = d;
     a.k = f;
@@ -304,7 +310,8 @@ int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, int
     a.status = status;
     if (mma_allowed()) {
         MmaRequest q{};
-        q.mode = 3; q.wa = a.wa; q.fmt_a = q.fmt_b = down_fmt; q.stride_a = down_stride; q.n = d; q.k = f;
+        q.mode = 3; q.wa = a.wa; q.fmt_a = q.fmt_b = down_fmt; q.stride_a = down_stride; q.table_a = a.table_a;
+        q.tables_aligned16 = tables_aligned16; q.n = d; q.k = f;
         q.m = MAX_TOKENS; q.x = hbuf; q.x_dtype = B200Q_F32; q.y = terms; q.y_dtype = B200Q_F32; q.topk = 1;
         q.order = order; q.seg_expert = seg_expert; q.seg_begin = seg_begin; q.seg_count = seg_count;
         q.num_segments = num_segments; q.max_segments = max_segments; q.route = route; q.status = status;

@@ -42,6 +42,7 @@ struct StreamArgs {
     const uint8_t *wa;
     const uint8_t *wb;
     long long stride_a, stride_b;
+    const unsigned long long *table_a, *table_b;   // optional per-expert pointer tables
     int rb_a, rb_b;        // packed bytes per row
     int n;                 // rows per matrix
     int k;                 // reduction length
@@ -192,7 +193,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const St
                 }
             }
             const int expert = GROUPED ? a.seg_expert[t.unit] : 0;
-            const uint8_t *base_a = a.wa + static_cast<long long>(expert) * a.stride_a;
+            const uint8_t *base_a = expert_matrix(a.wa, a.stride_a, a.table_a, expert);
             uint8_t *region = stage_base + static_cast<size_t>(s) * stage_bytes;
             uint32_t tx = 0;
             // Reads of this stage by the consumers (generic proxy) are ordered before the
@@ -201,7 +202,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const St
             issue_rows(region, base_a + static_cast<size_t>(t.row0) * a.rb_a, base_a, base_a + matrix_bytes_a,
                        static_cast<uint32_t>(t.rows) * a.rb_a, &full_bar[s], lane, tx);
             if (DUAL) {
-                const uint8_t *base_b = a.wb + static_cast<long long>(expert) * a.stride_b;
+                const uint8_t *base_b = expert_matrix(a.wb, a.stride_b, a.table_b, expert);
                 issue_rows(region + a.region_a, base_b + static_cast<size_t>(t.row0) * a.rb_b, base_b,
                            base_b + matrix_bytes_b, static_cast<uint32_t>(t.rows) * a.rb_b, &full_bar[s], lane, tx);
             }
@@ -242,8 +243,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const St
         const uint8_t *base_a = a.wa, *base_b = a.wb;
         if (GROUPED) {
             const int expert = a.seg_expert[t.unit];
-            base_a += static_cast<long long>(expert) * a.stride_a;
-            if (DUAL) base_b += static_cast<long long>(expert) * a.stride_b;
+            base_a = expert_matrix(a.wa, a.stride_a, a.table_a, expert);
+            if (DUAL) base_b = expert_matrix(a.wb, a.stride_b, a.table_b, expert);
             if (t.unit != cur_unit) {
                 // New segment: gather its tokens' activations into shared memory.
                 cur_unit = t.unit;

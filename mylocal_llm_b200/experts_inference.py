@@ -1,0 +1,203 @@
+"""Routed expert execution on device-resident packed banks.
+
+Host-side mirror of the reference's sparse dispatcher ``ExpertsInference.forward``
+(``mini_llm/ops/experts_inference.py:160-312``) and of the part of
+``HeterogeneousExpertExecutor`` that the dispatcher calls
+(``mini_llm/ops/expert_residency.py:1166-1208``: ``forward``, ``try_forward_grouped``,
+``dispatch_scope``). Differences that follow from the target: a B200 holds every expert of the
+model in HBM, so there is no cache, no eviction and no CPU path; and the dispatch plan is built on
+the device (``b200q_moe_plan``), so no expert count or id ever travels to the host - the same code
+path serves one token and many, and can be captured in a CUDA graph.
+
+Semantics kept: each token adds ``route_weight * FFN_e(x)`` over its k experts in ascending
+expert id, every term rounded to FP32 before the next plain FP32 add.
+"""
+
+import contextlib
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import moe_ops
+from .quantized_linear import DevicePackedGGUFWeight, PackedExpertFFNInference, packed_bytes_to_device
+from .quantized_weight import BLOCK_FORMATS, PackedGGUFWeight, packed_nbytes
+
+
+def _torch():
+    import torch
+    return torch
+
+
+@dataclass
+class PackedExpertBank:
+    """All experts of one MoE layer as three contiguous packed banks in HBM.
+
+    ``gate`` / ``up`` hold ``[E, F, D]`` and ``down`` ``[E, D, F]`` packed rows (uint8 CUDA
+    tensors); expert ``e`` starts ``e * stride`` bytes into its bank.
+    """
+
+    gate: object
+    up: object
+    down: object
+    gate_type: str
+    up_type: str
+    down_type: str
+    n_experts: int
+    d_model: int
+    d_ff: int
+
+    def __post_init__(self):
+        for name, fmt, shape in (("gate", self.gate_type, (self.d_ff, self.d_model)),
+                                 ("up", self.up_type, (self.d_ff, self.d_model)),
+                                 ("down", self.down_type, (self.d_model, self.d_ff))):
+            if fmt not in BLOCK_FORMATS:
+                raise ValueError(f"Unsupported packed GGUF type: {fmt}")
+            data = getattr(self, name)
+            expect = self.n_experts * packed_nbytes(shape, fmt)
+            if int(data.numel()) != expect:
+                raise ValueError(f"{name} bank: expected {expect} bytes, got {int(data.numel())}")
+
+    @property
+    def gate_stride(self):
+        return packed_nbytes((self.d_ff, self.d_model), self.gate_type)
+
+    @property
+    def up_stride(self):
+        return packed_nbytes((self.d_ff, self.d_model), self.up_type)
+
+    @property
+    def down_stride(self):
+        return packed_nbytes((self.d_model, self.d_ff), self.down_type)
+
+    @property
+    def nbytes(self):
+        return int(self.gate.numel() + self.up.numel() + self.down.numel())
+
+    @classmethod
+    def from_packed(cls, gate, up, down):
+        """Upload three host ``PackedGGUFWeight`` tensors shaped [E,F,D], [E,F,D], [E,D,F]."""
+        for w in (gate, up, down):
+            if not isinstance(w, PackedGGUFWeight) or len(w.shape) != 3:
+                raise TypeError("expected three-dimensional PackedGGUFWeight banks")
+        e, f, d = gate.shape
+        if up.shape != (e, f, d) or down.shape != (e, d, f):
+            raise ValueError("expert bank shapes must be gate/up [E,F,D], down [E,D,F]")
+        return cls(packed_bytes_to_device(gate.data), packed_bytes_to_device(up.data),
+                   packed_bytes_to_device(down.data), gate.quant_type, up.quant_type, down.quant_type, e, d, f)
+
+    def expert(self, index):
+        """Zero-copy ``PackedExpertFFNInference`` handle of one expert."""
+        if not 0 <= int(index) < self.n_experts:
+            raise IndexError(index)
+        i = int(index)
+        view = lambda bank, stride, shape, fmt: DevicePackedGGUFWeight(bank[i * stride:(i + 1) * stride], shape, fmt)
+        return PackedExpertFFNInference(
+            view(self.gate, self.gate_stride, (self.d_ff, self.d_model), self.gate_type),
+            view(self.up, self.up_stride, (self.d_ff, self.d_model), self.up_type),
+            view(self.down, self.down_stride, (self.d_model, self.d_ff), self.down_type))
+
+
+def routed_experts_forward(x2d, weights2d, ids2d, bank, *, extra=None, extra_scale=None, out_dtype=None):
+    """plan -> grouped gate/up -> grouped down (route-weighted) -> ordered combine.
+
+    x2d [T,D]; weights2d FP32 [T,k]; ids2d int32/int64 [T,k]; returns [T,D].
+    """
+    torch = _torch()
+    plan = moe_ops.moe_plan(ids2d, bank.n_experts)
+    hbuf = moe_ops.moe_gate_up(x2d, plan, bank.gate, bank.up, bank.gate_type, bank.up_type, bank.d_ff,
+                               bank.d_model, bank.gate_stride, bank.up_stride)
+    route = weights2d if weights2d.dtype == torch.float32 else weights2d.float()
+    terms = moe_ops.moe_down(hbuf, route.contiguous().reshape(-1), plan, bank.down, bank.down_type, bank.d_model,
+                             bank.d_ff, bank.down_stride)
+    return moe_ops.moe_combine(terms, plan, bank.d_model, extra=extra, extra_scale=extra_scale,
+                               out_dtype=out_dtype or x2d.dtype)
+
+
+class ResidentExpertExecutor:
+    """Executor with every expert resident in HBM (the reference's executor API, minus caching).
+
+    ``banks`` maps layer id -> ``PackedExpertBank``.
+    """
+
+    overlaps_cpu_gpu = False
+    routing_profiler = None
+
+    def __init__(self, banks, *, model_id="model", compute_dtype="float32"):
+        if not banks:
+            raise ValueError("at least one expert bank is required")
+        self.banks = dict(banks)
+        first = next(iter(self.banks.values()))
+        self.model_id = model_id
+        self.d_model, self.d_ff = first.d_model, first.d_ff
+        self.compute_dtype = compute_dtype
+
+    def bank(self, layer_id):
+        return self.banks[int(layer_id)]
+
+    def forward(self, layer_id, expert_id, x):
+        """One expert's FFN on a batch of rows ``[M, D]``."""
+        return self.bank(layer_id).expert(expert_id).forward(x)
+
+    def dispatch_scope(self, layer_id, expert_ids):
+        return contextlib.nullcontext()
+
+    def forward_routed(self, layer_id, x2d, weights2d, ids2d, **kwargs):
+        return routed_experts_forward(x2d, weights2d, ids2d, self.bank(layer_id), **kwargs)
+
+    def statistics(self):
+        return {"resident_layers": len(self.banks), "resident_bytes": sum(b.nbytes for b in self.banks.values())}
+
+
+class ExpertsInference:
+    """Mixture of expert FFNs for inference; evaluates only the selected experts."""
+
+    def __init__(self, d_model, d_ff, n_experts, dtype="float32", *, expert_executor=None, layer_id=0):
+        if expert_executor is None:
+            raise RuntimeError("ExpertsInference needs an expert_executor holding packed banks "
+                               "(dense per-expert weights are not part of this package)")
+        self.d_model, self.d_ff, self.n_experts = d_model, d_ff, n_experts
+        self.expert_executor = expert_executor
+        self.layer_id = int(layer_id)
+
+    def forward(self, x, weights, expert_indices, *, on_cpu_submitted=None):
+        """x [B,T,D]; weights [B,T,k]; expert_indices [B,T,k] -> [B,T,D] in x's dtype."""
+        batch, seq, d_model = x.shape
+        k = weights.shape[-1]
+        n = batch * seq
+        x2d = x.reshape(n, d_model)
+        if not x2d.is_contiguous():
+            x2d = x2d.contiguous()
+        ids = expert_indices.reshape(n, k)
+        if not ids.is_contiguous():
+            ids = ids.contiguous()
+        out = self.expert_executor.forward_routed(self.layer_id, x2d, weights.reshape(n, k), ids)
+        if on_cpu_submitted is not None:
+            on_cpu_submitted()
+        return out.reshape(batch, seq, d_model)
+
+
+def synthetic_bank(n_experts, d_model, d_ff, types=("Q4_K", "Q4_K", "Q6_K"), seed=0, device="cuda"):
+    """Random-byte expert bank generated on the device (benchmark / smoke input).
+
+    The quant codes and sub-block scales are uniform random bytes; the FP16 super-block scales are
+    set to small finite values so that outputs stay O(1). Layout and sizes are exactly those of a
+    real bank; the bytes are reproducible for a given seed.
+    """
+    torch = _torch()
+    gen = torch.Generator(device=device)
+    banks = []
+    for i, (fmt, shape) in enumerate(zip(types, ((d_ff, d_model), (d_ff, d_model), (d_model, d_ff)))):
+        gen.manual_seed(seed * 3 + i)
+        qk, qb = BLOCK_FORMATS[fmt]
+        nblocks = n_experts * shape[0] * shape[1] // qk
+        raw = torch.randint(0, 256, (nblocks, qb), dtype=torch.uint8, device=device, generator=gen)
+        half = lambda v: torch.tensor(np.frombuffer(np.float16(v).tobytes(), np.uint8).copy(), device=device)
+        if fmt == "Q6_K":
+            raw[:, 208:210] = half(1.0 / 4096)
+        elif fmt in ("Q4_K", "Q5_K"):
+            raw[:, 0:2] = half(1.0 / 2048)
+            raw[:, 2:4] = half(1.0 / 4096)
+        else:
+            raw[:, 0:2] = half(1.0 / 2048)
+        banks.append(raw.reshape(-1))
+    return PackedExpertBank(banks[0], banks[1], banks[2], types[0], types[1], types[2], n_experts, d_model, d_ff)

@@ -1,0 +1,150 @@
+"""Packed sparse-MoE layer: renormalised routed SwiGLU experts plus a (sigmoid-gated) shared expert.
+
+Mirrors the forward of the reference's ``Qwen3NextMoEInference``
+(``mini_llm/external/qwen3next_moe.py:129-147``):
+
+    weights, ids = router(hidden)                      # softmax over all E, top-k, renormalised
+    routed       = experts(hidden, weights, ids)       # ascending-expert ordered FP32 sum
+    shared       = down_sh( silu(hidden@gate_sh.T) * (hidden@up_sh.T) )
+    out          = routed + shared * sigmoid(hidden @ shared_gate)
+
+``shared_gate`` is optional: without it the shared expert is always on (weight 1), which is the
+variant the benchmark configuration describes. The reference requires FP32 hidden states; this
+layer also accepts BF16/FP16 (accumulation stays FP32, the output is rounded once).
+
+``RMSNormInference`` mirrors ``mini_llm/ops/rmsnorm_inference.py:304-318,451-495,525-539``.
+"""
+
+import ctypes
+
+from . import _lib, moe_ops
+from .experts_inference import ExpertsInference, PackedExpertBank, ResidentExpertExecutor
+from .quantized_linear import DevicePackedGGUFWeight, quantized_linear, quantized_swiglu
+from .router_inference import RouterInference
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _dtype_id(t):
+    return _lib.DTYPE_ID[str(t.dtype).replace("torch.", "")]
+
+
+class RMSNormInference:
+    """``y = x / sqrt(mean(x^2) + eps) * gamma`` with FP32 math; optional fused residual add."""
+
+    def __init__(self, d_model, eps=1e-6, dtype="float32"):
+        self.d_model = int(d_model)
+        self.eps = float(eps)
+        self.dtype = dtype
+        self.gamma = None
+
+    def set_weights(self, gamma):
+        self.gamma = gamma
+
+    def _check(self, x):
+        if self.gamma is None:
+            raise RuntimeError("RMSNorm weights are not set")
+        if x.shape[-1] != self.d_model or tuple(self.gamma.shape) != (self.d_model,):
+            raise ValueError("RMSNorm expects [..., d_model] input and a [d_model] weight")
+        if not x.is_contiguous() or not self.gamma.is_contiguous():
+            raise ValueError("RMSNorm operands must be contiguous")
+
+    def forward(self, x):
+        """Output has x's shape and dtype."""
+        torch = _torch()
+        self._check(x)
+        y = torch.empty_like(x)
+        rows = x.numel() // self.d_model
+        if rows:
+            _lib.call("b200q_rmsnorm", _ptr(x), _dtype_id(x), _ptr(self.gamma), _dtype_id(self.gamma), rows,
+                      self.d_model, self.eps, _ptr(y), _dtype_id(y), _lib.current_stream())
+        return y
+
+    def forward_residual(self, x):
+        """Normalise an FP32 residual stream directly into the weight's dtype."""
+        torch = _torch()
+        self._check(x)
+        y = torch.empty(x.shape, dtype=self.gamma.dtype, device=x.device)
+        rows = x.numel() // self.d_model
+        if rows:
+            _lib.call("b200q_rmsnorm", _ptr(x), _dtype_id(x), _ptr(self.gamma), _dtype_id(self.gamma), rows,
+                      self.d_model, self.eps, _ptr(y), _dtype_id(y), _lib.current_stream())
+        return y
+
+    def forward_residual_add(self, residual, branch, alpha=1.0):
+        """``res = residual + alpha*branch`` (FP32), ``y = rmsnorm(res)`` in the weight's dtype."""
+        torch = _torch()
+        self._check(residual)
+        if residual.dtype != torch.float32:
+            raise TypeError("the residual stream must be FP32")
+        if branch.shape != residual.shape or not branch.is_contiguous():
+            raise ValueError("branch must be contiguous and shaped like the residual")
+        res_out = torch.empty_like(residual)
+        y = torch.empty(residual.shape, dtype=self.gamma.dtype, device=residual.device)
+        rows = residual.numel() // self.d_model
+        if rows:
+            _lib.call("b200q_residual_rmsnorm", _ptr(residual), _ptr(branch), _dtype_id(branch), float(alpha),
+                      _ptr(self.gamma), _dtype_id(self.gamma), rows, self.d_model, self.eps, _ptr(res_out), _ptr(y),
+                      _dtype_id(y), _lib.current_stream())
+        return res_out, y
+
+
+class PackedMoELayer:
+    """Router + routed expert bank + shared expert, all packed and resident in HBM."""
+
+    def __init__(self, bank, router_weight, top_k, *, shared=None, shared_gate=None, layer_id=0,
+                 normalization_floor=2.0 ** -14, executor=None):
+        """bank: PackedExpertBank; router_weight: FP32 [D, E] CUDA tensor; shared: optional
+        (gate, up, down) DevicePackedGGUFWeight triple; shared_gate: optional FP32 [D] vector."""
+        if not isinstance(bank, PackedExpertBank):
+            raise TypeError("bank must be a PackedExpertBank")
+        self.bank = bank
+        self.layer_id = int(layer_id)
+        self.router = RouterInference(bank.d_model, bank.n_experts, top_k, renormalize_selected=True,
+                                      normalization_floor=normalization_floor)
+        self.router.W_router = router_weight
+        self.router.b_router = None
+        self.executor = executor or ResidentExpertExecutor({self.layer_id: bank})
+        self.experts = ExpertsInference(bank.d_model, bank.d_ff, bank.n_experts, expert_executor=self.executor,
+                                        layer_id=self.layer_id)
+        if shared is not None:
+            if len(shared) != 3 or not all(isinstance(w, DevicePackedGGUFWeight) for w in shared):
+                raise TypeError("shared expert must be three DevicePackedGGUFWeight projections")
+            if shared[0].shape != shared[1].shape or shared[2].shape != (shared[0].shape[1], shared[0].shape[0]):
+                raise ValueError("shared expert shapes must be gate/up [F, D], down [D, F]")
+        self.shared = shared
+        self.shared_gate = shared_gate
+
+    def forward(self, hidden):
+        """hidden [B, T, D] -> [B, T, D] in hidden's dtype."""
+        torch = _torch()
+        if not isinstance(hidden, torch.Tensor) or not hidden.is_cuda:
+            raise TypeError("MoE layer requires a CUDA tensor")
+        if hidden.ndim != 3 or hidden.shape[0] < 1 or hidden.shape[-1] != self.bank.d_model:
+            raise ValueError("hidden must have shape [positive batch,time,d_model]")
+        if not hidden.shape[1]:
+            return torch.empty_like(hidden)
+        batch, seq, d = hidden.shape
+        x2d = hidden.reshape(batch * seq, d)
+        if not x2d.is_contiguous():
+            x2d = x2d.contiguous()
+        logits = self.router.logits(x2d)
+        weights, ids = moe_ops.router_topk(logits, self.router.k, renormalize=True,
+                                           floor=self.router.normalization_floor)
+        extra = extra_scale = None
+        if self.shared is not None:
+            gate, up, down = self.shared
+            shared_hidden = quantized_swiglu(x2d, gate, up, out_dtype=torch.float32)
+            extra = quantized_linear(shared_hidden, down)
+            if self.shared_gate is not None:
+                extra_scale = moe_ops.shared_gate(x2d, self.shared_gate)
+        out = self.executor.forward_routed(self.layer_id, x2d, weights, ids, extra=extra, extra_scale=extra_scale,
+                                           out_dtype=hidden.dtype)
+        return out.reshape(batch, seq, d)

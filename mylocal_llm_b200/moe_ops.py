@@ -110,24 +110,31 @@ def moe_plan(ids, n_experts, *, workspace=None):
     return plan
 
 
-def moe_gate_up(x2d, plan, gate_bank, up_bank, gate_fmt, up_fmt, f, d, gate_stride, up_stride):
-    """FP32 hidden activations ``[T*k, F]`` in sorted-assignment order."""
+def moe_gate_up(x2d, plan, gate_bank, up_bank, gate_fmt, up_fmt, f, d, gate_stride, up_stride, *,
+                gate_table=None, up_table=None, tables_aligned16=False):
+    """FP32 hidden activations ``[T*k, F]`` in sorted-assignment order.
+
+    Experts live either in contiguous banks (``*_bank`` + byte stride) or behind device pointer
+    tables (int64 tensors with one address per expert)."""
     torch = _torch()
     hbuf = torch.empty((plan.rows * plan.k, f), dtype=torch.float32, device=x2d.device)
     _lib.call("b200q_moe_gate_up", _ptr(gate_bank), int(gate_stride), _lib.FORMAT_ID[gate_fmt], _ptr(up_bank),
-              int(up_stride), _lib.FORMAT_ID[up_fmt], f, d, _ptr(x2d), _dtype_id(x2d), plan.k, _ptr(plan.order),
+              int(up_stride), _lib.FORMAT_ID[up_fmt], _ptr(gate_table), _ptr(up_table), 1 if tables_aligned16 else 0,
+              f, d, _ptr(x2d), _dtype_id(x2d), plan.k, _ptr(plan.order),
               _ptr(plan.seg_expert), _ptr(plan.seg_begin), _ptr(plan.seg_count), _ptr(plan.num_segments),
               plan.max_segments, _ptr(hbuf), _lib.current_stream())
     return hbuf
 
 
-def moe_down(hbuf, route_weights, plan, down_bank, down_fmt, d, f, down_stride):
+def moe_down(hbuf, route_weights, plan, down_bank, down_fmt, d, f, down_stride, *, down_table=None,
+             tables_aligned16=False):
     """Route-weighted FP32 terms ``[T*k, D]`` in sorted-assignment order."""
     torch = _torch()
     if route_weights.dtype != torch.float32 or not route_weights.is_contiguous():
         raise ValueError("routing weights must be a contiguous FP32 tensor")
     terms = torch.empty((plan.rows * plan.k, d), dtype=torch.float32, device=hbuf.device)
-    _lib.call("b200q_moe_down", _ptr(down_bank), int(down_stride), _lib.FORMAT_ID[down_fmt], d, f, _ptr(hbuf),
+    _lib.call("b200q_moe_down", _ptr(down_bank), int(down_stride), _lib.FORMAT_ID[down_fmt], _ptr(down_table),
+              1 if tables_aligned16 else 0, d, f, _ptr(hbuf),
               _ptr(route_weights), _ptr(plan.order), _ptr(plan.seg_expert), _ptr(plan.seg_begin),
               _ptr(plan.seg_count), _ptr(plan.num_segments), plan.max_segments, _ptr(terms), _lib.current_stream())
     return terms

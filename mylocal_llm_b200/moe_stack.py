@@ -1,0 +1,73 @@
+"""A stack of packed MoE layers with RMSNorm and an FP32 residual stream (decode-step harness).
+
+Each layer is ``x -> x + MoE(RMSNorm(x))``: the residual stream is FP32, the normalised branch input
+and the MoE output are BF16 (or FP32), and the residual add of layer i is fused into the RMSNorm
+of layer i+1 (``residual_add_rmsnorm``), as the reference's low-precision engine chains them
+(``mini_llm/blocks/transformer_block_inference.py:344-364``,
+``mini_llm/ops/rmsnorm_inference.py:525-539``). Token mixing is the identity, which isolates the
+quantized path exactly as the 48-layer benchmark configuration prescribes.
+"""
+
+from .experts_inference import synthetic_bank
+from .moe_layer import PackedMoELayer, RMSNormInference
+from .quantize import random_packed
+from .quantized_linear import packed_to_device
+
+
+def _torch():
+    import torch
+    return torch
+
+
+class PackedMoEStack:
+    def __init__(self, layers, norms, final_norm):
+        if len(layers) != len(norms) or not layers:
+            raise ValueError("one RMSNorm per MoE layer is required")
+        self.layers, self.norms, self.final_norm = list(layers), list(norms), final_norm
+
+    @property
+    def packed_bytes(self):
+        total = 0
+        for layer in self.layers:
+            total += layer.bank.nbytes
+            if layer.shared is not None:
+                total += sum(w.nbytes for w in layer.shared)
+        return total
+
+    def forward(self, residual):
+        """residual FP32 [B, T, D] -> (new residual FP32, final normalised activations)."""
+        res = residual
+        hidden = self.norms[0].forward_residual(res)
+        for i, layer in enumerate(self.layers):
+            branch = layer.forward(hidden)
+            norm = self.norms[i + 1] if i + 1 < len(self.layers) else self.final_norm
+            res, hidden = norm.forward_residual_add(res, branch)
+        return res, hidden
+
+    @classmethod
+    def synthetic(cls, n_layers, *, d_model=2048, d_ff=512, n_experts=512, top_k=10, shared_d_ff=512,
+                  types=("Q4_K", "Q4_K", "Q6_K"), act_dtype=None, seed=0, eps=1e-5, device="cuda"):
+        """Random-init stack with the benchmark shape; weights are generated on the device."""
+        torch = _torch()
+        act_dtype = act_dtype or torch.bfloat16
+        gen = torch.Generator(device=device)
+        layers, norms = [], []
+        for i in range(n_layers):
+            bank = synthetic_bank(n_experts, d_model, d_ff, types, seed=seed * 1000 + i, device=device)
+            gen.manual_seed(seed * 1000 + i)
+            w_router = torch.empty((d_model, n_experts), dtype=torch.float32, device=device)
+            w_router.normal_(0.0, 0.02, generator=gen)
+            shared = None
+            if shared_d_ff:
+                shared = tuple(packed_to_device(random_packed(fmt, shape, seed=seed * 7919 + 3 * i + j,
+                                                              d=1.0 / 2048, dmin=1.0 / 4096))
+                               for j, (fmt, shape) in enumerate(zip(types, ((shared_d_ff, d_model),
+                                                                             (shared_d_ff, d_model),
+                                                                             (d_model, shared_d_ff)))))
+            layers.append(PackedMoELayer(bank, w_router, top_k, shared=shared, layer_id=i))
+            norm = RMSNormInference(d_model, eps=eps)
+            norm.set_weights(torch.ones(d_model, dtype=act_dtype, device=device))
+            norms.append(norm)
+        final = RMSNormInference(d_model, eps=eps)
+        final.set_weights(torch.ones(d_model, dtype=act_dtype, device=device))
+        return cls(layers, norms, final)

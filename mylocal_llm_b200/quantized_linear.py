@@ -118,8 +118,11 @@ def _check_activation(x, what="Packed linear input"):
         raise TypeError(f"{what} must be a NumPy array or a torch CUDA tensor")
 
 
-def quantized_linear(x, weight, *, block_k=512, cpu_packed_backend="reference"):
-    """``x @ weight.T`` for packed GGUF ``[out_features, in_features]`` on the GPU."""
+def quantized_linear(x, weight, *, block_k=512, cpu_packed_backend="reference", out_dtype=None):
+    """``x @ weight.T`` for packed GGUF ``[out_features, in_features]`` on the GPU.
+
+    ``out_dtype`` (an addition to the reference signature) selects the output element type;
+    by default the output has the activation dtype, as in the reference."""
     _check_activation(x)
     if x.ndim not in (2, 3):
         raise ValueError("Expected x as [M, K] or [B, T, K]")
@@ -144,14 +147,14 @@ def quantized_linear(x, weight, *, block_k=512, cpu_packed_backend="reference"):
     torch = _torch()
     n, k = weight.shape
     m = int(x.numel()) // k
-    out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    out = torch.empty((m, n), dtype=out_dtype or x.dtype, device=x.device)
     if m:
         _lib.call("b200q_gemv", _ptr(weight.data), _lib.FORMAT_ID[weight.quant_type], n, k, _ptr(x), dt, m,
-                  _ptr(out), dt, _lib.current_stream())
+                  _ptr(out), _dtype_id(out), _lib.current_stream())
     return out.reshape(tuple(x.shape[:-1]) + (n,))
 
 
-def quantized_swiglu(x, gate, up, *, block_k=512):
+def quantized_swiglu(x, gate, up, *, block_k=512, out_dtype=None):
     """``SiLU(x @ gate.T) * (x @ up.T)`` in one launch; gate/up formats may differ."""
     if not isinstance(gate, (PackedGGUFWeight, DevicePackedGGUFWeight)) or not isinstance(
             up, (PackedGGUFWeight, DevicePackedGGUFWeight)):
@@ -176,10 +179,11 @@ def quantized_swiglu(x, gate, up, *, block_k=512):
         raise ValueError("block_k must be 256, 512 or 1024")
     torch = _torch()
     m = int(x.numel()) // k
-    out = torch.empty((m, f), dtype=x.dtype, device=x.device)
+    out = torch.empty((m, f), dtype=out_dtype or x.dtype, device=x.device)
     if m:
         _lib.call("b200q_swiglu", _ptr(gate.data), _lib.FORMAT_ID[gate.quant_type], _ptr(up.data),
-                  _lib.FORMAT_ID[up.quant_type], f, k, _ptr(x), dt, m, _ptr(out), dt, _lib.current_stream())
+                  _lib.FORMAT_ID[up.quant_type], f, k, _ptr(x), dt, m, _ptr(out), _dtype_id(out),
+                  _lib.current_stream())
     return out.reshape(tuple(x.shape[:-1]) + (f,))
 
 
