@@ -85,6 +85,11 @@ int b200q_residual_rmsnorm(const float *residual, const void *branch, int branch
 int b200q_router_logits(const void *x, int x_dtype, int t, int d, const float *wr, const float *bias,
                         int e, float *logits, void *stream);
 
+/* Same product with the weight stored [e, d] (the orientation GGUF files use for
+ * ffn_gate_inp.weight): one warp per expert row, all SMs busy even for a single token. */
+int b200q_router_logits_t(const void *x, int x_dtype, int t, int d, const float *wt, const float *bias,
+                          int e, float *logits, void *stream);
+
 /* scale[t] (fp32) = sigmoid(x[t,:] . gate[:]) - the admission weight of the shared expert
  * (mini_llm/external/qwen3next_moe.py:145-146). */
 int b200q_shared_gate(const void *x, int x_dtype, int t, int d, const float *gate, float *scale,
@@ -97,6 +102,14 @@ int b200q_shared_gate(const void *x, int x_dtype, int t, int d, const float *gat
  * (mini_llm/ops/router_decode.py:16-96) for any number of rows. n <= 4096, k <= 32. */
 int b200q_router_topk(const float *logits, int rows, int n, int k, int renormalize,
                       float floor_value, float *weights, int64_t *ids, void *stream);
+
+/* b200q_router_topk that also appends one fixed assignment per row: outputs have k+1 entries, the
+ * last being (extra_id, extra_weight[row] or 1 when extra_weight is NULL). Used to run an always-on
+ * shared expert (mini_llm/external/qwen3next_moe.py:138-147) through the grouped expert kernels as
+ * the highest expert id, so that it is added last. extra_id < 0 appends nothing. */
+int b200q_router_topk_ex(const float *logits, int rows, int n, int k, int renormalize,
+                         float floor_value, int extra_id, const float *extra_weight, float *weights,
+                         int64_t *ids, void *stream);
 
 /* Device routing plan: stable counting sort of the rows*k assignments by expert id.
  * Outputs (all device, caller-allocated):

@@ -387,6 +387,11 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float *terms, co
     }
 }
 
+int launch_combine_cols(const float *terms, const int32_t *inv, int rows, int k, int d, const float *extra,
+                        const float *extra_scale, void *out, int out_dtype, cudaStream_t stream);
+int launch_topk_warp(const float *logits, int rows, int n, int k, int renorm, float floor_value, int extra_id,
+                     const float *extra_weight, float *weights, int64_t *ids, cudaStream_t stream);
+
 }  // namespace b200q
 
 using namespace b200q;
@@ -454,15 +459,24 @@ int b200q_shared_gate(const void *x, int x_dtype, int t, int d, const float *gat
     return check_launch("shared_gate");
 }
 
-int b200q_router_topk(const float *logits, int rows, int n, int k, int renormalize, float floor_value,
-                      float *weights, int64_t *ids, void *stream) {
+int b200q_router_topk_ex(const float *logits, int rows, int n, int k, int renormalize, float floor_value,
+                         int extra_id, const float *extra_weight, float *weights, int64_t *ids, void *stream) {
     if (!logits || !weights || !ids) return fail(B200Q_EINVAL, "router_topk: NULL pointer");
     if (rows <= 0 || n < 1 || n > 4096 || k < 1 || k > 32 || k > n)
         return fail(B200Q_EINVAL, "router_topk: need 1<=n<=4096, 1<=k<=min(32,n)");
     if (renormalize && !(floor_value > 0.0f)) return fail(B200Q_EINVAL, "router_topk: floor must be positive");
+    if (n <= 1024)
+        return launch_topk_warp(logits, rows, n, k, renormalize, floor_value, extra_id, extra_weight, weights, ids,
+                                static_cast<cudaStream_t>(stream));
+    if (extra_id >= 0) return fail(B200Q_EUNSUPPORTED, "router_topk: an appended expert needs n <= 1024");
     router_topk_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, n, k, renormalize, floor_value,
                                                                             weights, ids);
     return check_launch("router_topk");
+}
+
+int b200q_router_topk(const float *logits, int rows, int n, int k, int renormalize, float floor_value,
+                      float *weights, int64_t *ids, void *stream) {
+    return b200q_router_topk_ex(logits, rows, n, k, renormalize, floor_value, -1, nullptr, weights, ids, stream);
 }
 
 int b200q_moe_plan(const void *ids, int ids_is_i64, int rows, int k, int e, int seg_cap, int32_t *counts,
@@ -486,9 +500,8 @@ int b200q_moe_combine(const float *terms, const int32_t *inv, int rows, int k, i
     if (!terms || !inv || !out) return fail(B200Q_EINVAL, "moe_combine: NULL pointer");
     if (rows <= 0 || k < 1 || k > 64 || d <= 0 || !dtype_valid(out_dtype))
         return fail(B200Q_EINVAL, "moe_combine: bad argument (k <= 64)");
-    moe_combine_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(terms, inv, k, d, extra, extra_scale, out,
-                                                                            out_dtype);
-    return check_launch("moe_combine");
+    return launch_combine_cols(terms, inv, rows, k, d, extra, extra_scale, out, out_dtype,
+                               static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -1,0 +1,210 @@
+// Decode-oriented router kernels: logits from an [E, D] weight (one warp per expert row), and
+// softmax + top-k with one warp per token row. Semantics as in aux_kernels.cu / the reference
+// (mini_llm/ops/router_decode.py:16-96): descending logit, ties -> lower id, NaN last,
+// p = exp(v - max) / sum, optional division by max(selected mass, floor).
+#include "common.cuh"
+
+namespace b200q {
+
+constexpr int RT_TOK = 16;      // tokens per CTA pass of the logits kernel
+constexpr int RT_CHUNK = 2048;  // D positions held in registers at a time
+
+// logits[t, e] = x[t, :] . wt[e, :] + bias[e];  wt is [E, D] row-major FP32.
+// CTA = 8 warps; warp w handles expert rows (blockIdx.x*8 + w) * rpw .. +rpw-1; tokens of tile
+// blockIdx.y are staged in shared memory as FP32.
+__global__ void __launch_bounds__(256) router_logits_t_kernel(const void *x, int x_dtype, int t, int d, const float *wt,
+                                                              const float *bias, int e, int rpw, float *logits) {
+    extern __shared__ float xs[];   // [RT_TOK][d]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int t0 = blockIdx.y * RT_TOK;
+    const int nt = min(RT_TOK, t - t0);
+    for (int i = tid; i < nt * d; i += 256) xs[i] = load_as_float(x, x_dtype, static_cast<size_t>(t0) * d + i);
+    __syncthreads();
+    for (int r = 0; r < rpw; ++r) {
+        const int row = (blockIdx.x * 8 + warp) * rpw + r;
+        if (row >= e) break;
+        float acc[RT_TOK];
+#pragma unroll
+        for (int i = 0; i < RT_TOK; ++i) acc[i] = 0.f;
+        for (int c0 = 0; c0 < d; c0 += RT_CHUNK) {
+            float4 w[RT_CHUNK / 128];
+#pragma unroll
+            for (int i = 0; i < RT_CHUNK / 128; ++i) {
+                const int col = c0 + i * 128 + lane * 4;
+                w[i] = col < d ? *reinterpret_cast<const float4 *>(wt + static_cast<size_t>(row) * d + col)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int tt = 0; tt < RT_TOK; ++tt) {
+                if (tt < nt) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int i = 0; i < RT_CHUNK / 128; ++i) {
+                        const int col = c0 + i * 128 + lane * 4;
+                        if (col < d) {
+                            const float4 xv = *reinterpret_cast<const float4 *>(xs + tt * d + col);
+                            s = fmaf(w[i].x, xv.x, s);
+                            s = fmaf(w[i].y, xv.y, s);
+                            s = fmaf(w[i].z, xv.z, s);
+                            s = fmaf(w[i].w, xv.w, s);
+                        }
+                    }
+                    acc[tt] += s;
+                }
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < RT_TOK; ++tt) {
+            if (tt < nt) {
+                const float s = warp_sum(acc[tt]);
+                if (lane == 0) logits[static_cast<size_t>(t0 + tt) * e + row] = s + (bias ? bias[row] : 0.f);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ bool better_route(float a, int ia, float b, int ib, int n) {
+    if (ia == n) return false;
+    if (ib == n) return true;
+    if (isnan(a)) return isnan(b) && ia < ib;
+    if (isnan(b)) return true;
+    return a > b || (a == b && ia < ib);
+}
+
+// One warp per row, n <= 1024 (32 values per lane in registers). Output rows have
+// k_out = k + (extra_id >= 0) entries; the appended entry is (extra_id, extra_weight[row] or 1).
+__global__ void __launch_bounds__(128) router_topk_warp_kernel(const float *logits, int rows, int n, int k, int renorm,
+                                                               float floor_value, int extra_id,
+                                                               const float *extra_weight, float *weights,
+                                                               int64_t *ids) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const float neg_inf = __int_as_float(0xff800000), qnan = __int_as_float(0x7fc00000);
+    const float *src = logits + static_cast<size_t>(row) * n;
+    float v[32];
+    unsigned used = 0u;
+    float mx = neg_inf;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const int idx = i * 32 + lane;
+        v[i] = idx < n ? src[idx] : neg_inf;
+        if (idx < n) mx = (isnan(v[i]) || isnan(mx)) ? qnan : fmaxf(mx, v[i]);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, mx, o);
+        mx = (isnan(mx) || isnan(other)) ? qnan : fmaxf(mx, other);
+    }
+    float den = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+        if (i * 32 + lane < n) den += expf(v[i] - mx);
+    den = warp_sum(den);
+    const int k_out = k + (extra_id >= 0 ? 1 : 0);
+    float mass = 0.f;
+    float mine = 0.f;            // lane s keeps the probability of slot s
+    for (int slot = 0; slot < k; ++slot) {
+        float best = neg_inf;
+        int bi = n;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int idx = i * 32 + lane;
+            if (idx < n && !((used >> i) & 1u) && better_route(v[i], idx, best, bi, n)) { best = v[i]; bi = idx; }
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better_route(ov, oi, best, bi, n)) { best = ov; bi = oi; }
+        }
+        if ((bi & 31) == lane && bi < n) used |= 1u << (bi >> 5);
+        const float p = __fdiv_rn(expf(best - mx), den);
+        mass = __fadd_rn(mass, p);             // sequential in slot order, identical on every lane
+        if (lane == slot) mine = p;
+        if (lane == 0) ids[static_cast<size_t>(row) * k_out + slot] = bi;
+    }
+    float norm = 1.0f;
+    if (renorm) norm = isnan(mass) ? mass : fmaxf(mass, floor_value);
+    if (lane < k) weights[static_cast<size_t>(row) * k_out + lane] = renorm ? __fdiv_rn(mine, norm) : mine;
+    if (extra_id >= 0 && lane == 0) {
+        ids[static_cast<size_t>(row) * k_out + k] = extra_id;
+        weights[static_cast<size_t>(row) * k_out + k] = extra_weight ? extra_weight[row] : 1.0f;
+    }
+}
+
+// Ordered combine, one thread per output column: the k terms are loaded first (independent
+// loads), then added one by one in ascending position order with plain FP32 adds.
+template <int KMAX>
+__global__ void __launch_bounds__(256) moe_combine_cols_kernel(const float *terms, const int32_t *inv, int k, int d,
+                                                               const float *extra, const float *extra_scale,
+                                                               void *out, int out_dtype) {
+    __shared__ int pos_sorted[KMAX];
+    __shared__ int pos_raw[KMAX];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    if (tid < k) pos_raw[tid] = inv[static_cast<size_t>(row) * k + tid];
+    __syncthreads();
+    if (tid < k) {
+        const int p = pos_raw[tid];
+        int r = 0;
+        for (int j = 0; j < k; ++j) r += pos_raw[j] < p;
+        pos_sorted[r] = p;
+    }
+    __syncthreads();
+    const int c = blockIdx.y * 256 + tid;
+    if (c >= d) return;
+    float v[KMAX];
+#pragma unroll
+    for (int r = 0; r < KMAX; ++r)
+        if (r < k) v[r] = terms[static_cast<size_t>(pos_sorted[r]) * d + c];
+    float acc = 0.f;
+#pragma unroll
+    for (int r = 0; r < KMAX; ++r)
+        if (r < k) acc = __fadd_rn(acc, v[r]);
+    if (extra) acc = __fadd_rn(acc, __fmul_rn(extra[static_cast<size_t>(row) * d + c], extra_scale ? extra_scale[row] : 1.0f));
+    store_from_float(out, out_dtype, static_cast<size_t>(row) * d + c, acc);
+}
+
+int launch_combine_cols(const float *terms, const int32_t *inv, int rows, int k, int d, const float *extra,
+                        const float *extra_scale, void *out, int out_dtype, cudaStream_t stream) {
+    dim3 grid(rows, (d + 255) / 256);
+    if (k <= 16)
+        moe_combine_cols_kernel<16><<<grid, 256, 0, stream>>>(terms, inv, k, d, extra, extra_scale, out, out_dtype);
+    else
+        moe_combine_cols_kernel<64><<<grid, 256, 0, stream>>>(terms, inv, k, d, extra, extra_scale, out, out_dtype);
+    return check_launch("moe_combine");
+}
+
+int launch_topk_warp(const float *logits, int rows, int n, int k, int renorm, float floor_value, int extra_id,
+                     const float *extra_weight, float *weights, int64_t *ids, cudaStream_t stream) {
+    router_topk_warp_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(logits, rows, n, k, renorm, floor_value, extra_id,
+                                                                extra_weight, weights, ids);
+    return check_launch("router_topk");
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" int b200q_router_logits_t(const void *x, int x_dtype, int t, int d, const float *wt, const float *bias,
+                                     int e, float *logits, void *stream) {
+    if (!x || !wt || !logits) return fail(B200Q_EINVAL, "router_logits_t: NULL pointer");
+    if (!dtype_valid(x_dtype)) return fail(B200Q_EINVAL, "router_logits_t: bad dtype");
+    if (t <= 0 || d <= 0 || e <= 0 || d % 4) return fail(B200Q_EINVAL, "router_logits_t: bad shape (d %% 4 == 0)");
+    if (reinterpret_cast<uintptr_t>(wt) & 15) return fail(B200Q_EINVAL, "router_logits_t: weight must be 16-byte aligned");
+    const size_t smem = static_cast<size_t>(RT_TOK) * d * sizeof(float);
+    if (smem > 200 * 1024) return fail(B200Q_EUNSUPPORTED, "router_logits_t: d=%d too large", d);
+    cudaError_t err = cudaFuncSetAttribute(router_logits_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           200 * 1024);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail(B200Q_ECUDA, "router_logits_t: %s", cudaGetErrorString(err));
+    }
+    const int tiles = (t + RT_TOK - 1) / RT_TOK;
+    int rpw = 4;   // fewer rows per warp when the grid would leave SMs idle
+    while (rpw > 1 && static_cast<long long>((e + 8 * rpw - 1) / (8 * rpw)) * tiles < sm_count()) rpw >>= 1;
+    dim3 grid((e + 8 * rpw - 1) / (8 * rpw), tiles);
+    router_logits_t_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(x, x_dtype, t, d, wt, bias, e, rpw,
+                                                                                   logits);
+    return check_launch("router_logits_t");
+}

@@ -85,6 +85,22 @@ class PackedExpertBank:
         return cls(packed_bytes_to_device(gate.data), packed_bytes_to_device(up.data),
                    packed_bytes_to_device(down.data), gate.quant_type, up.quant_type, down.quant_type, e, d, f)
 
+    def pointer_tables(self, extra=None):
+        """Device pointer tables (three int64 tensors with one address per expert) and whether every
+        address is 16-byte aligned. ``extra`` = optional (gate, up, down) DevicePackedGGUFWeight triple
+        appended as expert ``n_experts`` (an always-on shared expert of the same shape and formats)."""
+        torch = _torch()
+        cols = []
+        for bank, stride, w in ((self.gate, self.gate_stride, 0), (self.up, self.up_stride, 1),
+                                (self.down, self.down_stride, 2)):
+            ptrs = [bank.data_ptr() + e * stride for e in range(self.n_experts)]
+            if extra is not None:
+                ptrs.append(extra[w].data.data_ptr())
+            cols.append(ptrs)
+        aligned = all(p % 16 == 0 for col in cols for p in col)
+        tables = tuple(torch.tensor(col, dtype=torch.int64, device=self.gate.device) for col in cols)
+        return tables, aligned
+
     def expert(self, index):
         """Zero-copy ``PackedExpertFFNInference`` handle of one expert."""
         if not 0 <= int(index) < self.n_experts:
@@ -97,16 +113,26 @@ class PackedExpertBank:
             view(self.down, self.down_stride, (self.d_model, self.d_ff), self.down_type))
 
 
-def routed_experts_forward(x2d, weights2d, ids2d, bank, *, extra=None, extra_scale=None, out_dtype=None):
+def routed_experts_forward(x2d, weights2d, ids2d, bank, *, extra=None, extra_scale=None, out_dtype=None,
+                           tables=None, tables_aligned16=False, n_experts=None):
     """plan -> grouped gate/up -> grouped down (route-weighted) -> ordered combine.
 
-    x2d [T,D]; weights2d FP32 [T,k]; ids2d int32/int64 [T,k]; returns [T,D].
+    x2d [T,D]; weights2d FP32 [T,k]; ids2d int32/int64 [T,k]; returns [T,D]. With ``tables`` (from
+    ``PackedExpertBank.pointer_tables``) experts are addressed through pointer tables and
+    ``n_experts`` may exceed the bank (appended shared expert).
     """
     torch = _torch()
-    plan = moe_ops.moe_plan(ids2d, bank.n_experts)
+    plan = moe_ops.moe_plan(ids2d, n_experts or bank.n_experts)
+    route = weights2d if weights2d.dtype == torch.float32 else weights2d.float()
+    if tables is not None:
+        hbuf = moe_ops.moe_gate_up(x2d, plan, None, None, bank.gate_type, bank.up_type, bank.d_ff, bank.d_model, 0, 0,
+                                   gate_table=tables[0], up_table=tables[1], tables_aligned16=tables_aligned16)
+        terms = moe_ops.moe_down(hbuf, route.contiguous().reshape(-1), plan, None, bank.down_type, bank.d_model,
+                                 bank.d_ff, 0, down_table=tables[2], tables_aligned16=tables_aligned16)
+        return moe_ops.moe_combine(terms, plan, bank.d_model, extra=extra, extra_scale=extra_scale,
+                                   out_dtype=out_dtype or x2d.dtype)
     hbuf = moe_ops.moe_gate_up(x2d, plan, bank.gate, bank.up, bank.gate_type, bank.up_type, bank.d_ff,
                                bank.d_model, bank.gate_stride, bank.up_stride)
-    route = weights2d if weights2d.dtype == torch.float32 else weights2d.float()
     terms = moe_ops.moe_down(hbuf, route.contiguous().reshape(-1), plan, bank.down, bank.down_type, bank.d_model,
                              bank.d_ff, bank.down_stride)
     return moe_ops.moe_combine(terms, plan, bank.d_model, extra=extra, extra_scale=extra_scale,

@@ -121,6 +121,14 @@ class PackedMoELayer:
                 raise ValueError("shared expert shapes must be gate/up [F, D], down [D, F]")
         self.shared = shared
         self.shared_gate = shared_gate
+        # A shared expert with the routed experts' shape and formats runs through the grouped kernels
+        # as expert id E (the highest id, hence added last), addressed through pointer tables.
+        self._tables = None
+        if shared is not None and all(
+                w.shape == ref_shape and w.quant_type == ref_type for w, ref_shape, ref_type in zip(
+                    shared, ((bank.d_ff, bank.d_model), (bank.d_ff, bank.d_model), (bank.d_model, bank.d_ff)),
+                    (bank.gate_type, bank.up_type, bank.down_type))) and bank.n_experts < 1024:
+            self._tables = bank.pointer_tables(extra=shared)
 
     def forward(self, hidden):
         """hidden [B, T, D] -> [B, T, D] in hidden's dtype."""
@@ -136,6 +144,16 @@ class PackedMoELayer:
         if not x2d.is_contiguous():
             x2d = x2d.contiguous()
         logits = self.router.logits(x2d)
+        if self._tables is not None:
+            scale = moe_ops.shared_gate(x2d, self.shared_gate) if self.shared_gate is not None else None
+            weights, ids = moe_ops.router_topk(logits, self.router.k, renormalize=True,
+                                               floor=self.router.normalization_floor,
+                                               extra_id=self.bank.n_experts, extra_weight=scale)
+            tables, aligned = self._tables
+            out = self.executor.forward_routed(self.layer_id, x2d, weights, ids, out_dtype=hidden.dtype,
+                                               tables=tables, tables_aligned16=aligned,
+                                               n_experts=self.bank.n_experts + 1)
+            return out.reshape(batch, seq, d)
         weights, ids = moe_ops.router_topk(logits, self.router.k, renormalize=True,
                                            floor=self.router.normalization_floor)
         extra = extra_scale = None

@@ -42,16 +42,33 @@ def router_logits(x2d, w_router, bias=None):
     return out
 
 
-def router_topk(logits2d, k, *, renormalize, floor=1e-30):
-    """(FP32 weights [T,k], int64 ids [T,k]) from FP32 logits [T,E]."""
+def router_logits_t(x2d, w_router_t, bias=None):
+    """FP32 ``x[T,D] @ Wt[E,D].T (+ bias)`` for a router weight stored expert-major."""
+    torch = _torch()
+    t, d = x2d.shape
+    e = w_router_t.shape[0]
+    if w_router_t.dtype != torch.float32 or not w_router_t.is_contiguous() or w_router_t.shape[1] != d:
+        raise ValueError("router weight must be a contiguous FP32 [E, D] tensor")
+    out = torch.empty((t, e), dtype=torch.float32, device=x2d.device)
+    _lib.call("b200q_router_logits_t", _ptr(x2d), _dtype_id(x2d), t, d, _ptr(w_router_t), _ptr(bias), e, _ptr(out),
+              _lib.current_stream())
+    return out
+
+
+def router_topk(logits2d, k, *, renormalize, floor=1e-30, extra_id=-1, extra_weight=None):
+    """(FP32 weights [T,k'], int64 ids [T,k']) from FP32 logits [T,E].
+
+    With ``extra_id >= 0`` one more assignment (that id, weight ``extra_weight[t]`` or 1) is appended
+    to every row, so k' = k + 1."""
     torch = _torch()
     if logits2d.dtype != torch.float32 or not logits2d.is_contiguous():
         raise ValueError("logits must be a contiguous FP32 tensor")
     t, e = logits2d.shape
-    weights = torch.empty((t, k), dtype=torch.float32, device=logits2d.device)
-    ids = torch.empty((t, k), dtype=torch.int64, device=logits2d.device)
-    _lib.call("b200q_router_topk", _ptr(logits2d), t, e, int(k), 1 if renormalize else 0, float(floor),
-              _ptr(weights), _ptr(ids), _lib.current_stream())
+    k_out = int(k) + (1 if extra_id >= 0 else 0)
+    weights = torch.empty((t, k_out), dtype=torch.float32, device=logits2d.device)
+    ids = torch.empty((t, k_out), dtype=torch.int64, device=logits2d.device)
+    _lib.call("b200q_router_topk_ex", _ptr(logits2d), t, e, int(k), 1 if renormalize else 0, float(floor),
+              int(extra_id), _ptr(extra_weight), _ptr(weights), _ptr(ids), _lib.current_stream())
     return weights, ids
 
 

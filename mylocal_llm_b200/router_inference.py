@@ -71,15 +71,34 @@ class RouterInference:
             raise ValueError("normalization_floor must be finite and positive")
         self.renormalize_selected = renormalize_selected
         self.normalization_floor = float(normalization_floor)
-        self.W_router = None
+        self._w = None
+        self._w_expert_major = None
         self.b_router = None
+
+    @property
+    def W_router(self):
+        """FP32 ``[d_model, n_experts]`` weight (the reference's orientation)."""
+        return self._w
+
+    @W_router.setter
+    def W_router(self, value):
+        # Keep an expert-major [E, D] copy: the decode kernel gives every expert row its own warp.
+        self._w = value
+        self._w_expert_major = None if value is None else value.t().contiguous()
+
+    def set_expert_major_weight(self, weight_t):
+        """Use an ``[n_experts, d_model]`` weight directly (the orientation stored in GGUF files)."""
+        self._w = None
+        self._w_expert_major = weight_t
 
     def set_weights(self, router):
         self.W_router = router.W_router_param.data
         self.b_router = router.b_router_param.data
 
     def logits(self, x2d):
-        return moe_ops.router_logits(x2d, self.W_router, self.b_router)
+        if self._w_expert_major is not None and x2d.shape[1] % 4 == 0:
+            return moe_ops.router_logits_t(x2d, self._w_expert_major, self.b_router)
+        return moe_ops.router_logits(x2d, self._w, self.b_router)
 
     def forward(self, x):
         torch = _torch()

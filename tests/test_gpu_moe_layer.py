@@ -193,3 +193,52 @@ def test_rmsnorm_matches_reference_golden(cuda, golden):
     assert y16.dtype == cuda.bfloat16
     np.testing.assert_allclose(res16.cpu().numpy(), ref_res, rtol=1e-6, atol=1e-6)
     np.testing.assert_allclose(y16.float().cpu().numpy(), ref_y, rtol=1e-2, atol=1e-2)
+
+
+def test_expert_major_router_logits_and_appended_expert(cuda):
+    from mylocal_llm_b200 import moe_ops
+    rng = np.random.default_rng(77)
+    for t, d, e in ((1, 2048, 512), (5, 256, 24), (37, 1024, 100)):
+        x = rng.normal(0, 1, (t, d)).astype(np.float32)
+        w = rng.normal(0, 0.05, (d, e)).astype(np.float32)
+        bias = rng.normal(0, 0.1, e).astype(np.float32)
+        ref = x.astype(np.float64) @ w.astype(np.float64) + bias
+        a = moe_ops.router_logits(to_cuda(cuda, x), to_cuda(cuda, w), to_cuda(cuda, bias))
+        b = moe_ops.router_logits_t(to_cuda(cuda, x), to_cuda(cuda, np.ascontiguousarray(w.T)), to_cuda(cuda, bias))
+        np.testing.assert_allclose(a.cpu().numpy(), ref, rtol=2e-5, atol=2e-5)
+        np.testing.assert_allclose(b.cpu().numpy(), ref, rtol=2e-5, atol=2e-5)
+        xb = to_cuda(cuda, x, cuda.bfloat16)
+        c = moe_ops.router_logits_t(xb, to_cuda(cuda, np.ascontiguousarray(w.T)), None)
+        np.testing.assert_allclose(c.cpu().numpy(), xb.double().cpu().numpy() @ w.astype(np.float64), rtol=2e-5, atol=2e-5)
+    logits = rng.normal(0, 1, (6, 40)).astype(np.float32)
+    scale = rng.random(6).astype(np.float32)
+    w1, i1 = moe_ops.router_topk(to_cuda(cuda, logits), 4, renormalize=True, floor=2.0 ** -14)
+    w2, i2 = moe_ops.router_topk(to_cuda(cuda, logits), 4, renormalize=True, floor=2.0 ** -14, extra_id=40,
+                                 extra_weight=to_cuda(cuda, scale))
+    assert tuple(w2.shape) == (6, 5)
+    assert cuda.equal(w2[:, :4], w1) and cuda.equal(i2[:, :4], i1)
+    np.testing.assert_array_equal(i2[:, 4].cpu().numpy(), np.full(6, 40))
+    np.testing.assert_array_equal(w2[:, 4].cpu().numpy(), scale)
+    w3, _ = moe_ops.router_topk(to_cuda(cuda, logits), 4, renormalize=True, floor=2.0 ** -14, extra_id=40)
+    np.testing.assert_array_equal(w3[:, 4].cpu().numpy(), np.ones(6, np.float32))
+
+
+def test_moe_layer_with_shared_expert_of_a_different_width(cuda):
+    # a shared expert that cannot join the routed bank (other width / formats) takes the separate path
+    d, f, fs, e, k, tokens = 512, 256, 512, 6, 2, 9
+    rng = np.random.default_rng(123)
+    mk = lambda shape, q: quantize(rng.normal(0, 0.06, shape).astype(np.float32), q)
+    gate, up, down = mk((e, f, d), "Q4_K"), mk((e, f, d), "Q5_K"), mk((e, d, f), "Q6_K")
+    sg, su, sd = mk((fs, d), "Q8_0"), mk((fs, d), "Q8_0"), mk((d, fs), "Q8_0")
+    w_router = rng.normal(0, 0.1, (d, e)).astype(np.float32)
+    gate_vec = rng.normal(0, 0.1, d).astype(np.float32)
+    hidden = rng.normal(0, 1, (1, tokens, d)).astype(np.float32)
+    layer = PackedMoELayer(PackedExpertBank.from_packed(gate, up, down), to_cuda(cuda, w_router), k,
+                           shared=tuple(packed_to_device(w) for w in (sg, su, sd)), shared_gate=to_cuda(cuda, gate_vec))
+    assert layer._tables is None
+    out = layer.forward(to_cuda(cuda, hidden))[0].cpu().numpy()
+    experts = [tuple((w.select_outer(i).data, w.select_outer(i).shape, w.quant_type) for w in (gate, up, down))
+               for i in range(e)]
+    ref = po.moe_layer_fp64(hidden[0], w_router, k, 2.0 ** -14, experts,
+                            tuple((w.data, w.shape, w.quant_type) for w in (sg, su, sd)), gate_vec)
+    np.testing.assert_allclose(out, ref, rtol=4e-4, atol=8e-6)
