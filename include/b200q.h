@@ -163,6 +163,22 @@ int b200q_moe_combine(const float *terms, const int32_t *inv, int rows, int k, i
                       const float *extra, const float *extra_scale, void *out, int out_dtype,
                       void *stream);
 
+/* One SwiGLU expert, y[m,d_model] = down( silu(x gate^T) * (x up^T) ), for callers that cannot
+ * allocate device memory. (No counterpart in the reference: its expert FFN allocates the hidden
+ * activations with CuPy.) The FP32 hidden activations [m, d_ff] between the two kernels live in a
+ * fixed array inside the library (512 KiB on every GPU that loads it), so the call performs no
+ * cudaMalloc/cudaFree and needs no framework allocator: meant for hosts without a device allocator
+ * of their own and for loops where allocation is forbidden or would stall the device.
+ *   - limit: m * d_ff <= 131072 (e.g. 8 tokens x 16384); larger requests return 3 with a message;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current): make that first call before starting any stream capture;
+ *   - every call on a device shares the one array: calls that can overlap on the GPU (different
+ *     streams, or graphs replayed concurrently) race on it - serialise them. Nothing needs to be
+ *     cleared between calls; each call overwrites all it reads. */
+int b200q_expert_ffn_static(const void *gate, int gate_fmt, const void *up, int up_fmt, const void *down,
+                            int down_fmt, int d_model, int d_ff, const void *x, int x_dtype, int m,
+                            void *y, int y_dtype, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
