@@ -402,7 +402,17 @@ def run_moe_gpu_arm(args, name):
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    stack = PackedMoEStack.synthetic(layers, seed=rank, **MOE_SHAPE)
+    comm = None
+    if world > 1:
+        # expert-parallel: experts sharded over the ranks, `tokens` rows per rank (weak scaling in tokens)
+        from mylocal_llm_b200.expert_parallel import CollectiveComm, ExpertParallelMoEStack, PeerComm
+        if args.exchange == "peer":
+            comm = PeerComm(None, max_rows=tokens, d_model=MOE_SHAPE["d_model"], k_out=MOE_SHAPE["top_k"] + 1)
+        else:
+            comm = CollectiveComm()
+        stack = ExpertParallelMoEStack.synthetic(layers, comm, seed=0, **MOE_SHAPE)
+    else:
+        stack = PackedMoEStack.synthetic(layers, seed=0, **MOE_SHAPE)
     d = MOE_SHAPE["d_model"]
     rng = np.random.default_rng(11 + rank)
     host_x = torch.from_numpy(rng.normal(0, 1, (1, tokens, d)).astype(np.float32)).pin_memory()
@@ -490,7 +500,10 @@ def run_moe_gpu_arm(args, name):
             stream.synchronize()
         moe_ops.moe_gate_up = real_gate_up
         gate_up_ms = [a0.elapsed_time(a1) for a0, a1, _ in records]
-        distinct = [int((c > 0).sum().item()) for _, _, c in records]
+        # expert-parallel plans end with one entry counting the assignments other ranks execute
+        executed = [c[:-1] if world > 1 else c for _, _, c in records]
+        distinct = [int((c > 0).sum().item()) for c in executed]
+        assignments = [int(c.sum().item()) for c in executed]
 
     times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -504,8 +517,8 @@ def run_moe_gpu_arm(args, name):
         value = tokens_per_step * world * args.steps / (dev_ms * 1e-3)
         e2e_value = tokens_per_step * world * args.steps / (e2e_ms * 1e-3)
         peak, peak_kind = measured_peaks()
-        gu_bytes = statistics.mean(distinct) * 2 * packed_bytes("Q4_K", 512, 2048) + tokens * d * 2 \
-            + tokens * MOE_SHAPE["top_k"] * 512 * 4
+        gu_bytes = statistics.mean(distinct) * 2 * packed_bytes("Q4_K", 512, 2048) + world * tokens * d * 2 \
+            + statistics.mean(assignments) * 512 * 4
         gu_us = statistics.mean(gate_up_ms) * 1e3
         achieved = gu_bytes / (gu_us * 1e-6) / 1e9
         layer_bytes = statistics.mean(distinct) * EXPERT_BYTES + EXPERT_BYTES + 4 * 2048 * 512 + 2 * tokens * d * 2
@@ -516,7 +529,9 @@ def run_moe_gpu_arm(args, name):
             "config": {"workload": name, "layers": layers, "tokens_per_step": tokens, "chained": chained, **MOE_SHAPE,
                        "formats": "Q4_K gate/up, Q6_K down", "activation": "bfloat16, FP32 residual",
                        "packed_bytes_resident": stack.packed_bytes,
-                       "parallelism": "replicas only" if world > 1 else "single GPU",
+                       "parallelism": (f"expert-parallel ep{world}: {MOE_SHAPE['n_experts'] // world} experts per rank, "
+                                       f"{tokens} tokens per rank, exchange={args.exchange}") if world > 1
+                       else "single GPU",
                        "l2": f"{layers} distinct layers per step, {layer_bytes * layers / 1e6:.0f} MB touched per step",
                        "timing": "CUDA graph of one step, CUDA events on the launch stream",
                        "distinct_experts_per_layer": round(statistics.mean(distinct), 1),
@@ -536,6 +551,8 @@ def run_moe_gpu_arm(args, name):
             line["cpu_baseline"] = {"value": round(tps, 4), "unit": "tokens/s", "cores": cores, "kind": kind,
                                     "sample": sample}
         print(json.dumps(line))
+    if comm is not None:
+        comm.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -547,6 +564,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(MOE_WORKLOADS))
+    ap.add_argument("--exchange", default="peer", choices=["peer", "collective"],
+                    help="expert-parallel exchange at N > 1: peer-memory stores + device barrier, or NCCL")
     ap.add_argument("--skip-cpu-baseline", action="store_true",
                     help="omit the host-core baseline leg (exploratory runs only)")
     args = ap.parse_args()

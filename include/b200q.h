@@ -129,6 +129,15 @@ int b200q_moe_plan(const void *ids, int ids_is_i64, int rows, int k, int e, int 
                    int32_t *seg_expert, int32_t *seg_begin, int32_t *seg_count,
                    int32_t *num_segments, int max_segments, int32_t *status, void *stream);
 
+/* b200q_moe_plan with one expert id whose assignments are counted and sorted but get no segment, so
+ * the grouped kernels never touch them (skip_expert < 0: none). Expert-parallel ranks map the
+ * assignments that belong to other ranks to that id. (No counterpart in the reference, which has no
+ * multi-GPU path.) */
+int b200q_moe_plan_ex(const void *ids, int ids_is_i64, int rows, int k, int e, int skip_expert, int seg_cap,
+                      int32_t *counts, int32_t *offsets, int32_t *order, int32_t *inv,
+                      int32_t *seg_expert, int32_t *seg_begin, int32_t *seg_count,
+                      int32_t *num_segments, int max_segments, int32_t *status, void *stream);
+
 /* Grouped gate/up + SwiGLU over the plan's segments:
  *   hbuf[pos, f] (fp32) = silu(x[token(pos)] . G_e) * (x[token(pos)] . U_e)
  * for every sorted position pos of every segment; token(pos) = order[pos] / k.
@@ -147,9 +156,11 @@ int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, 
 
 /* Grouped down projection with the route weight applied and stored per assignment:
  *   terms[pos, d] (fp32) = (hbuf[pos] . D_e) * route[order[pos]]
+ * With flat_rows != 0 the row index is order[pos] (the flat assignment index row*k+slot) instead of
+ * pos - the layout an expert-parallel exchange needs, because it does not depend on the rank.
  * Replaces _grouped_down_weighted (mini_llm/ops/grouped_quantized_experts.py:45-68). */
 int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, const uint64_t *down_table,
-                   int tables_aligned16, int d, int f, const float *hbuf, const float *route, const int32_t *order,
+                   int tables_aligned16, int flat_rows, int d, int f, const float *hbuf, const float *route, const int32_t *order,
                    const int32_t *seg_expert, const int32_t *seg_begin, const int32_t *seg_count,
                    const int32_t *num_segments, int max_segments, float *terms, void *stream);
 
@@ -162,6 +173,53 @@ int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, con
 int b200q_moe_combine(const float *terms, const int32_t *inv, int rows, int k, int d,
                       const float *extra, const float *extra_scale, void *out, int out_dtype,
                       void *stream);
+
+/* Ordered combine for terms stored at the flat assignment index: out[row] = sum of terms[row*k+slot]
+ * in ascending (expert id, slot) order, plain FP32 adds from zero (same semantics as
+ * b200q_moe_combine; used by the home rank of an expert-parallel layer). */
+int b200q_moe_combine_ids(const float *terms, const void *ids, int ids_is_i64, int rows, int k, int d,
+                          const float *extra, const float *extra_scale, void *out, int out_dtype, void *stream);
+
+/* ---- Expert-parallel execution over the GPUs of one node (no counterpart in the reference, which is
+ * single-process; semantics = the single-GPU layer, bit for bit). ------------------------------- */
+
+/* Routing plan of one rank: ids hold GLOBAL expert ids for the tokens of ALL ranks ([rows,k]).
+ * Global ids first_expert..first_expert+n_local-1 become local experts 0..n_local-1; shared_id
+ * (< 0: none) becomes local expert n_local for rows home_lo..home_hi-1 (the rows this rank is home
+ * of); everything else is sorted last and gets no segment. counts/offsets have n_local+2 (+1)
+ * entries. Ids outside [0, e_global) set *status = 1. */
+int b200q_moe_plan_ep(const void *ids, int ids_is_i64, int rows, int k, int e_global, int first_expert, int n_local,
+                      int shared_id, int home_lo, int home_hi, int seg_cap, int32_t *counts, int32_t *offsets,
+                      int32_t *order, int32_t *inv, int32_t *seg_expert, int32_t *seg_begin, int32_t *seg_count,
+                      int32_t *num_segments, int max_segments, int32_t *status, void *stream);
+
+/* b200q_moe_down with the projection and the exchange in one kernel: the term row of flat assignment
+ * i (= row*k + slot over all ranks' rows) is stored at row i - r*rows_per_rank of the buffer whose
+ * address is term_tables[r], r = i / rows_per_rank - the home rank's arena, written through peer
+ * memory. Each row has exactly one writer, so no reduction and no clearing is needed; a
+ * b200q_peer_barrier must separate it from the home rank's combine. */
+int b200q_moe_down_peer(const void *down_base, int64_t down_stride, int down_fmt, const uint64_t *down_table,
+                        int tables_aligned16, int d, int f, const float *hbuf, const float *route,
+                        const int32_t *order, const int32_t *seg_expert, const int32_t *seg_begin,
+                        const int32_t *seg_count, const int32_t *num_segments, int max_segments,
+                        const uint64_t *term_tables, int rows_per_rank, void *stream);
+
+/* Peer arena: cudaMalloc'd, cleared, exported as a 64-byte CUDA IPC handle; peers map it with
+ * b200q_peer_open (which also enables peer access). Setup-time calls, not for the decode loop. */
+int b200q_peer_alloc(size_t bytes, void **ptr, unsigned char *handle64);
+int b200q_peer_open(const unsigned char *handle64, void **ptr);
+int b200q_peer_close(void *ptr);
+int b200q_peer_free(void *ptr);
+
+/* Barrier over the ranks' streams. pads: device array of `world` addresses, entry r = rank r's
+ * signal pad (>= 128 zero-initialised bytes inside its arena). Returns when every rank has reached
+ * its matching call, or after timeout_ms with 201 in the device status word (b200q_device_status).
+ * One rank per GPU only: ranks sharing a GPU would wait on one another's unscheduled kernels. */
+int b200q_peer_barrier(const uint64_t *pads, int rank, int world, int timeout_ms, void *stream);
+
+/* All-gather by stores: copies `bytes` from src to dst_bases[p] + dst_offset_bytes for every p < world. */
+int b200q_peer_push_rows(const void *src, size_t bytes, const uint64_t *dst_bases, size_t dst_offset_bytes,
+                         int world, void *stream);
 
 /* One SwiGLU expert, y[m,d_model] = down( silu(x gate^T) * (x up^T) ), for callers that cannot
  * allocate device memory. (No counterpart in the reference: its expert FFN allocates the hidden

@@ -40,7 +40,20 @@ SIGNATURES = {
                        _ptr, _c_int, _ptr, _ptr],
     "b200q_moe_gate_up": [_ptr, _c_i64, _c_int, _ptr, _c_i64, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr,
                           _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr],
-    "b200q_moe_down": [_ptr, _c_i64, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+    "b200q_moe_plan_ex": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+                          _ptr, _ptr, _c_int, _ptr, _ptr],
+    "b200q_moe_combine_ids": [_ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr],
+    "b200q_moe_plan_ep": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                          _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr],
+    "b200q_moe_down_peer": [_ptr, _c_i64, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+                            _ptr, _c_int, _ptr, _c_int, _ptr],
+    "b200q_peer_alloc": [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), _ptr],
+    "b200q_peer_open": [_ptr, ctypes.POINTER(ctypes.c_void_p)],
+    "b200q_peer_close": [_ptr],
+    "b200q_peer_free": [_ptr],
+    "b200q_peer_barrier": [_ptr, _c_int, _c_int, _c_int, _ptr],
+    "b200q_peer_push_rows": [_ptr, ctypes.c_size_t, _ptr, ctypes.c_size_t, _c_int, _ptr],
+    "b200q_moe_down": [_ptr, _c_i64, _c_int, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
                        _c_int, _ptr, _ptr],
     "b200q_moe_combine": [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr],
 }

@@ -242,7 +242,15 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float *logits, i
 constexpr int PLAN_THREADS = 1024;
 constexpr int PLAN_MAX_EXPERTS = 4096;
 
+// Optional id translation for an expert-parallel rank: global ids first..first+n_local-1 become
+// 0..n_local-1; the shared-expert id becomes n_local for the rows this rank is home of; every other
+// assignment becomes n_local+1, which the caller passes as skip_expert.
+struct PlanIdMap {
+    int enabled, k, first, n_local, shared_id, home_lo, home_hi, e_global;
+};
+
 __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const void *ids, int ids_is_i64, int total, int e,
+                                                                int skip_expert, const PlanIdMap map,
                                                                 int seg_cap, int32_t *counts, int32_t *offsets,
                                                                 int32_t *order, int32_t *inv, int32_t *seg_expert,
                                                                 int32_t *seg_begin, int32_t *seg_count,
@@ -262,7 +270,13 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const void *ids,
     auto load_id = [&](int i) -> int {
         long long v = ids_is_i64 ? static_cast<const long long *>(ids)[i]
                                  : static_cast<long long>(static_cast<const int *>(ids)[i]);
-        if (v < 0 || v >= e) { bad = 1; v = 0; }
+        if (map.enabled) {
+            if (v < 0 || v >= map.e_global) { bad = 1; v = map.first; }
+            const int row = i / map.k;
+            if (v >= map.first && v < map.first + map.n_local) v -= map.first;
+            else if (v == map.shared_id && row >= map.home_lo && row < map.home_hi) v = map.n_local;
+            else v = map.n_local + 1;
+        } else if (v < 0 || v >= e) { bad = 1; v = 0; }
         return static_cast<int>(v);
     };
 
@@ -331,7 +345,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const void *ids,
     __syncthreads();
     for (int base = 0; base < e; base += PLAN_THREADS) {
         const int i = base + tid;
-        const int c = i < e ? (off[i + 1] - off[i]) : 0;
+        const int c = (i < e && i != skip_expert) ? (off[i + 1] - off[i]) : 0;   // skipped expert: no segments
         const int nsegs = (c + seg_cap - 1) / seg_cap;
         scan_tmp[tid] = nsegs;
         __syncthreads();
@@ -479,7 +493,8 @@ int b200q_router_topk(const float *logits, int rows, int n, int k, int renormali
     return b200q_router_topk_ex(logits, rows, n, k, renormalize, floor_value, -1, nullptr, weights, ids, stream);
 }
 
-int b200q_moe_plan(const void *ids, int ids_is_i64, int rows, int k, int e, int seg_cap, int32_t *counts,
+int b200q_moe_plan_ex(const void *ids, int ids_is_i64, int rows, int k, int e, int skip_expert, int seg_cap,
+                      int32_t *counts,
                    int32_t *offsets, int32_t *order, int32_t *inv, int32_t *seg_expert, int32_t *seg_begin,
                    int32_t *seg_count, int32_t *num_segments, int max_segments, int32_t *status, void *stream) {
     if (!ids || !counts || !offsets || !order || !inv || !seg_expert || !seg_begin || !seg_count || !num_segments ||
@@ -490,9 +505,36 @@ int b200q_moe_plan(const void *ids, int ids_is_i64, int rows, int k, int e, int 
     const long long total = static_cast<long long>(rows) * k;
     if (total > (1 << 24)) return fail(B200Q_EUNSUPPORTED, "moe_plan: too many assignments");
     moe_plan_kernel<<<1, PLAN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-        ids, ids_is_i64, static_cast<int>(total), e, seg_cap, counts, offsets, order, inv, seg_expert, seg_begin,
+        ids, ids_is_i64, static_cast<int>(total), e, skip_expert, PlanIdMap{}, seg_cap, counts, offsets, order, inv, seg_expert, seg_begin,
         seg_count, num_segments, max_segments, status);
     return check_launch("moe_plan");
+}
+
+int b200q_moe_plan_ep(const void *ids, int ids_is_i64, int rows, int k, int e_global, int first_expert, int n_local,
+                      int shared_id, int home_lo, int home_hi, int seg_cap, int32_t *counts, int32_t *offsets,
+                      int32_t *order, int32_t *inv, int32_t *seg_expert, int32_t *seg_begin, int32_t *seg_count,
+                      int32_t *num_segments, int max_segments, int32_t *status, void *stream) {
+    if (!ids || !counts || !offsets || !order || !inv || !seg_expert || !seg_begin || !seg_count || !num_segments ||
+        !status)
+        return fail(B200Q_EINVAL, "moe_plan_ep: NULL pointer");
+    if (rows <= 0 || k <= 0 || n_local <= 0 || n_local + 2 > PLAN_MAX_EXPERTS || first_expert < 0 ||
+        e_global < first_expert + n_local || seg_cap < 1 || seg_cap > 8 || max_segments < 1 || home_lo < 0 ||
+        home_hi < home_lo || home_hi > rows)
+        return fail(B200Q_EINVAL, "moe_plan_ep: bad argument");
+    const long long total = static_cast<long long>(rows) * k;
+    if (total > (1 << 24)) return fail(B200Q_EUNSUPPORTED, "moe_plan_ep: too many assignments");
+    PlanIdMap map{1, k, first_expert, n_local, shared_id, home_lo, home_hi, e_global};
+    moe_plan_kernel<<<1, PLAN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+        ids, ids_is_i64, static_cast<int>(total), n_local + 2, n_local + 1, map, seg_cap, counts, offsets, order, inv,
+        seg_expert, seg_begin, seg_count, num_segments, max_segments, status);
+    return check_launch("moe_plan_ep");
+}
+
+int b200q_moe_plan(const void *ids, int ids_is_i64, int rows, int k, int e, int seg_cap, int32_t *counts,
+                   int32_t *offsets, int32_t *order, int32_t *inv, int32_t *seg_expert, int32_t *seg_begin,
+                   int32_t *seg_count, int32_t *num_segments, int max_segments, int32_t *status, void *stream) {
+    return b200q_moe_plan_ex(ids, ids_is_i64, rows, k, e, -1, seg_cap, counts, offsets, order, inv, seg_expert,
+                             seg_begin, seg_count, num_segments, max_segments, status, stream);
 }
 
 int b200q_moe_combine(const float *terms, const int32_t *inv, int rows, int k, int d, const float *extra,

@@ -75,6 +75,15 @@ __device__ __forceinline__ float swiglu_f32(float g, float u) {
 
 // Start of expert `e`'s packed matrix: entry of a device pointer table when one is given,
 // otherwise base + e * stride inside a contiguous bank.
+// Where a route-weighted term row goes. Without a table: row `row` of the local buffer. With a table
+// (one base address per rank, possibly peer memory): rank row / rows_per_rank owns the row.
+__device__ __forceinline__ float *term_row_pointer(float *local, const uint64_t *table, int rows_per_rank, int n,
+                                                   int row) {
+    if (!table) return local + static_cast<size_t>(row) * n;
+    const int home = row / rows_per_rank;
+    return reinterpret_cast<float *>(table[home]) + static_cast<size_t>(row - home * rows_per_rank) * n;
+}
+
 __device__ __forceinline__ const uint8_t *expert_matrix(const uint8_t *base, long long stride,
                                                         const unsigned long long *table, int e) {
     if (table) return reinterpret_cast<const uint8_t *>(static_cast<uintptr_t>(table[e]));

@@ -53,7 +53,7 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) 
     a.x = q.x; a.x_dtype = q.x_dtype; a.y = q.y; a.y_dtype = q.y_dtype;
     a.topk = q.topk; a.order = q.order; a.seg_expert = q.seg_expert; a.seg_begin = q.seg_begin;
     a.seg_count = q.seg_count; a.num_segments = q.num_segments; a.max_segments = q.max_segments;
-    a.route = q.route;
+    a.route = q.route; a.flat_rows = q.flat_rows; a.y_table = q.y_table; a.rows_per_rank = q.rows_per_rank;
 
     const bool q5 = q.fmt_a == B200Q_Q5_K;
     DirectFn fn = q5 ? (a.nterms == 2 ? pick_mode<true, 2>(q.mode) : pick_mode<true, 1>(q.mode))

@@ -53,6 +53,9 @@ struct DirectArgs {
     const int32_t *num_segments;
     int max_segments;
     const float *route;
+    int flat_rows;       // mode 3: term rows stored at the flat assignment index
+    const uint64_t *y_table;   // mode 3, optional: per-rank base addresses of the term buffers (peer memory)
+    int rows_per_rank;   // flat rows owned by each rank when y_table is set
 };
 
 __device__ __forceinline__ uint4 ldg128(const uint8_t *p) {
@@ -331,6 +334,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
     float *tok_scale = reinterpret_cast<float *>(smem);           // [8] scale, [8] inverse
     float *route_w = reinterpret_cast<float *>(smem + 128);       // [8]
     int *seg_tokens = reinterpret_cast<int *>(smem + 192);        // [8]
+    float **out_ptr = reinterpret_cast<float **>(smem + 256);     // [8] mode 3 output row pointers
     float *partial = reinterpret_cast<float *>(smem + MD_CTRL_BYTES);
     uint2 *bfrag = reinterpret_cast<uint2 *>(smem + a.off_bfrag);
     uint32_t *xsfrag = reinterpret_cast<uint32_t *>(smem + a.off_xsfrag);
@@ -421,7 +425,10 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
                 if (tid < m_tokens) {
                     const int flat = a.order[seg_begin + tid];
                     seg_tokens[tid] = (MODE == 2) ? flat / a.topk : seg_begin + tid;
-                    if (MODE == 3) route_w[tid] = a.route[flat];
+                    if (MODE == 3) {
+                        route_w[tid] = a.route[flat];
+                        out_ptr[tid] = term_row_pointer(static_cast<float *>(a.y), a.y_table, a.rows_per_rank, a.n, a.flat_rows ? flat : seg_begin + tid);
+                    }
                 }
                 named_barrier_sync(1, MD_THREADS);
                 prepare_direct<NTERMS>([&](int t) { return seg_tokens[t]; }, m_tokens, a.k, a.x, a.x_dtype, bfrag,
@@ -476,7 +483,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
             else if (MODE == 2)
                 static_cast<float *>(a.y)[static_cast<size_t>(seg_begin + t) * a.n + orow] = swiglu_f32(pa, pbv);
             else
-                static_cast<float *>(a.y)[static_cast<size_t>(seg_begin + t) * a.n + orow] = pa * route_w[t];
+                out_ptr[t][orow] = pa * route_w[t];
         }
         pbuf ^= 1;
         cur_p = nxt_p;

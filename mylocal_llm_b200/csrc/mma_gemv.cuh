@@ -68,6 +68,9 @@ struct MmaArgs {
     const int32_t *num_segments;
     int max_segments;
     const float *route;
+    int flat_rows;       // mode 3: term rows stored at the flat assignment index
+    const uint64_t *y_table;   // mode 3, optional: per-rank base addresses of the term buffers (peer memory)
+    int rows_per_rank;   // flat rows owned by each rank when y_table is set
     int *status;
 };
 
@@ -486,6 +489,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_gemv_kernel(const MmaArgs a
     float *tok_scale = reinterpret_cast<float *>(smem + 512);   // [8] scale, [8] inverse
     float *route_w = reinterpret_cast<float *>(smem + 640);     // [8]
     int *seg_tokens = reinterpret_cast<int *>(smem + 704);      // [8]
+    float **out_ptr = reinterpret_cast<float **>(smem + 768);   // [8] mode 3 output row pointers
     float *stab_all = reinterpret_cast<float *>(smem + MM_CTRL_BYTES);
     float *partial = reinterpret_cast<float *>(smem + MM_CTRL_BYTES + MM_STAB_BYTES);
     uint2 *bfrag = reinterpret_cast<uint2 *>(smem + a.off_bfrag);
@@ -637,7 +641,10 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_gemv_kernel(const MmaArgs a
                     if (ctid < m_tokens) {
                         const int flat = a.order[seg_begin + ctid];
                         seg_tokens[ctid] = (MODE == 2) ? flat / a.topk : seg_begin + ctid;
-                        if (MODE == 3) route_w[ctid] = a.route[flat];
+                        if (MODE == 3) {
+                            route_w[ctid] = a.route[flat];
+                            out_ptr[ctid] = term_row_pointer(static_cast<float *>(a.y), a.y_table, a.rows_per_rank, a.n, a.flat_rows ? flat : seg_begin + ctid);
+                        }
                     }
                     named_barrier_sync(1, MM_CTHREADS);
                     prepare_activations<NTERMS>([&](int t) { return seg_tokens[t]; }, m_tokens, a.k, a.x, a.x_dtype,
@@ -732,7 +739,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_gemv_kernel(const MmaArgs a
             else if (MODE == 2)
                 static_cast<float *>(a.y)[static_cast<size_t>(seg_begin + t) * a.n + orow] = swiglu_f32(pa, pbv);
             else
-                static_cast<float *>(a.y)[static_cast<size_t>(seg_begin + t) * a.n + orow] = pa * route_w[t];
+                out_ptr[t][orow] = pa * route_w[t];
         }
         pbuf ^= 1;
     }

@@ -104,7 +104,7 @@ int mma_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) {
     a.x = q.x; a.x_dtype = q.x_dtype; a.y = q.y; a.y_dtype = q.y_dtype;
     a.topk = q.topk; a.order = q.order; a.seg_expert = q.seg_expert; a.seg_begin = q.seg_begin;
     a.seg_count = q.seg_count; a.num_segments = q.num_segments; a.max_segments = q.max_segments;
-    a.route = q.route; a.status = q.status;
+    a.route = q.route; a.flat_rows = q.flat_rows; a.y_table = q.y_table; a.rows_per_rank = q.rows_per_rank; a.status = q.status;
     if (!plan(a, q.fmt_a, q.fmt_b, dual, MM_WARPS) && !plan(a, q.fmt_a, q.fmt_b, dual, MM_WARPS / 2)) return B200Q_OK;
 
     MmaKernelFn fn = dual ? mma_pick_dual(q.mode, q.fmt_a, a.nterms) : mma_pick_single(q.mode, q.fmt_a, a.nterms);

@@ -26,6 +26,9 @@ struct MmaRequest {
     const int32_t *num_segments;
     int max_segments;
     const float *route;
+    int flat_rows;
+    const uint64_t *y_table;
+    int rows_per_rank;
     int *status;
 };
 

@@ -165,6 +165,40 @@ __global__ void __launch_bounds__(256) moe_combine_cols_kernel(const float *term
     store_from_float(out, out_dtype, static_cast<size_t>(row) * d + c, acc);
 }
 
+// Same ordered sum for terms stored at the flat assignment index (row*k + slot): the slots of a row
+// are ordered by (expert id, slot) - the order the stable sort by expert id gives them.
+template <int KMAX>
+__global__ void __launch_bounds__(256) moe_combine_ids_kernel(const float *terms, const void *ids, int ids_is_i64,
+                                                              int k, int d, const float *extra,
+                                                              const float *extra_scale, void *out, int out_dtype) {
+    __shared__ int slot_sorted[KMAX];
+    __shared__ long long id_raw[KMAX];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    if (tid < k)
+        id_raw[tid] = ids_is_i64 ? static_cast<const long long *>(ids)[static_cast<size_t>(row) * k + tid]
+                                 : static_cast<long long>(static_cast<const int *>(ids)[static_cast<size_t>(row) * k + tid]);
+    __syncthreads();
+    if (tid < k) {
+        const long long mine = id_raw[tid];
+        int r = 0;
+        for (int j = 0; j < k; ++j) r += (id_raw[j] < mine) || (id_raw[j] == mine && j < tid);
+        slot_sorted[r] = tid;
+    }
+    __syncthreads();
+    const int c = blockIdx.y * 256 + tid;
+    if (c >= d) return;
+    float v[KMAX];
+#pragma unroll
+    for (int r = 0; r < KMAX; ++r)
+        if (r < k) v[r] = terms[(static_cast<size_t>(row) * k + slot_sorted[r]) * d + c];
+    float acc = 0.f;
+#pragma unroll
+    for (int r = 0; r < KMAX; ++r)
+        if (r < k) acc = __fadd_rn(acc, v[r]);
+    if (extra) acc = __fadd_rn(acc, __fmul_rn(extra[static_cast<size_t>(row) * d + c], extra_scale ? extra_scale[row] : 1.0f));
+    store_from_float(out, out_dtype, static_cast<size_t>(row) * d + c, acc);
+}
+
 int launch_combine_cols(const float *terms, const int32_t *inv, int rows, int k, int d, const float *extra,
                         const float *extra_scale, void *out, int out_dtype, cudaStream_t stream) {
     dim3 grid(rows, (d + 255) / 256);
@@ -185,6 +219,22 @@ int launch_topk_warp(const float *logits, int rows, int n, int k, int renorm, fl
 }  // namespace b200q
 
 using namespace b200q;
+
+extern "C" int b200q_moe_combine_ids(const float *terms, const void *ids, int ids_is_i64, int rows, int k, int d,
+                                     const float *extra, const float *extra_scale, void *out, int out_dtype,
+                                     void *stream) {
+    if (!terms || !ids || !out) return fail(B200Q_EINVAL, "moe_combine_ids: NULL pointer");
+    if (rows <= 0 || k < 1 || k > 64 || d <= 0 || !dtype_valid(out_dtype))
+        return fail(B200Q_EINVAL, "moe_combine_ids: bad argument (k <= 64)");
+    dim3 grid(rows, (d + 255) / 256);
+    if (k <= 16)
+        moe_combine_ids_kernel<16><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(terms, ids, ids_is_i64, k, d, extra,
+                                                                                      extra_scale, out, out_dtype);
+    else
+        moe_combine_ids_kernel<64><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(terms, ids, ids_is_i64, k, d, extra,
+                                                                                      extra_scale, out, out_dtype);
+    return check_launch("moe_combine_ids");
+}
 
 extern "C" int b200q_router_logits_t(const void *x, int x_dtype, int t, int d, const float *wt, const float *bias,
                                      int e, float *logits, void *stream) {

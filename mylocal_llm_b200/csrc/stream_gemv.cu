@@ -276,13 +276,15 @@ int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, 
                   "moe_gate_up");
 }
 
-int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, const uint64_t *down_table,
-                   int tables_aligned16, int d, int f, const float *hbuf,
-                   const float *route, const int32_t *order, const int32_t *seg_expert, const int32_t *seg_begin,
-                   const int32_t *seg_count, const int32_t *num_segments, int max_segments, float *terms,
-                   void *stream) {
-    if ((!down_base && !down_table) || !hbuf || !route || !order || !seg_expert || !seg_begin || !seg_count || !num_segments || !terms)
+static int moe_down_impl(const void *down_base, int64_t down_stride, int down_fmt, const uint64_t *down_table,
+                         int tables_aligned16, int flat_rows, int d, int f, const float *hbuf, const float *route,
+                         const int32_t *order, const int32_t *seg_expert, const int32_t *seg_begin,
+                         const int32_t *seg_count, const int32_t *num_segments, int max_segments, float *terms,
+                         const uint64_t *y_table, int rows_per_rank, void *stream) {
+    if ((!down_base && !down_table) || !hbuf || !route || !order || !seg_expert || !seg_begin || !seg_count ||
+        !num_segments || (!terms && !y_table))
         return fail(B200Q_EINVAL, "moe_down: NULL pointer");
+    if (y_table && rows_per_rank < 1) return fail(B200Q_EINVAL, "moe_down: rows_per_rank must be positive");
     if (!fmt_valid(down_fmt)) return fail(B200Q_EINVAL, "moe_down: bad format");
     if (d <= 0 || max_segments <= 0 || !k_ok(down_fmt, f)) return fail(B200Q_EINVAL, "moe_down: bad shape d=%d f=%d", d, f);
     int *status = device_status_word();
@@ -307,6 +309,9 @@ int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, con
     a.num_segments = num_segments;
     a.max_segments = max_segments;
     a.route = route;
+    a.flat_rows = (flat_rows || y_table) ? 1 : 0;
+    a.y_table = y_table;
+    a.rows_per_rank = rows_per_rank;
     a.status = status;
     if (mma_allowed()) {
         MmaRequest q{};
@@ -314,7 +319,9 @@ int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, con
         q.tables_aligned16 = tables_aligned16; q.n = d; q.k = f;
         q.m = MAX_TOKENS; q.x = hbuf; q.x_dtype = B200Q_F32; q.y = terms; q.y_dtype = B200Q_F32; q.topk = 1;
         q.order = order; q.seg_expert = seg_expert; q.seg_begin = seg_begin; q.seg_count = seg_count;
-        q.num_segments = num_segments; q.max_segments = max_segments; q.route = route; q.status = status;
+        q.num_segments = num_segments; q.max_segments = max_segments; q.route = route; q.flat_rows = a.flat_rows;
+        q.y_table = y_table; q.rows_per_rank = rows_per_rank;
+        q.status = status;
         bool launched = false;
         int rc = mma_try_launch(q, static_cast<cudaStream_t>(stream), &launched);
         if (rc || launched) return rc;
@@ -324,6 +331,27 @@ int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, con
     int rc = plan_tiles(a, false, MAX_TOKENS);
     if (rc) return rc;
     return launch(pick_single<3>(down_fmt), a, false, sm_count(), static_cast<cudaStream_t>(stream), "moe_down");
+}
+
+int b200q_moe_down(const void *down_base, int64_t down_stride, int down_fmt, const uint64_t *down_table,
+                   int tables_aligned16, int flat_rows, int d, int f, const float *hbuf,
+                   const float *route, const int32_t *order, const int32_t *seg_expert, const int32_t *seg_begin,
+                   const int32_t *seg_count, const int32_t *num_segments, int max_segments, float *terms,
+                   void *stream) {
+    return moe_down_impl(down_base, down_stride, down_fmt, down_table, tables_aligned16, flat_rows, d, f, hbuf, route,
+                         order, seg_expert, seg_begin, seg_count, num_segments, max_segments, terms, nullptr, 0,
+                         stream);
+}
+
+int b200q_moe_down_peer(const void *down_base, int64_t down_stride, int down_fmt, const uint64_t *down_table,
+                        int tables_aligned16, int d, int f, const float *hbuf, const float *route,
+                        const int32_t *order, const int32_t *seg_expert, const int32_t *seg_begin,
+                        const int32_t *seg_count, const int32_t *num_segments, int max_segments,
+                        const uint64_t *term_tables, int rows_per_rank, void *stream) {
+    if (!term_tables) return fail(B200Q_EINVAL, "moe_down_peer: NULL term table");
+    return moe_down_impl(down_base, down_stride, down_fmt, down_table, tables_aligned16, 1, d, f, hbuf, route, order,
+                         seg_expert, seg_begin, seg_count, num_segments, max_segments, nullptr, term_tables,
+                         rows_per_rank, stream);
 }
 
 }  // extern "C"

@@ -66,6 +66,9 @@ struct StreamArgs {
     const int32_t *num_segments;
     int max_segments;
     const float *route;    // mode 3: flat [rows*topk] route weights
+    int flat_rows;         // mode 3: store term rows at the flat assignment index instead of the sorted position
+    const uint64_t *y_table;   // mode 3, optional: per-rank base addresses of the term buffers (peer memory)
+    int rows_per_rank;     // flat rows owned by each rank when y_table is set
     int *status;
 };
 
@@ -144,6 +147,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const St
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 256);
     float *route_w = reinterpret_cast<float *>(smem + 512);            // [MAX_TOKENS]
     int *seg_tokens = reinterpret_cast<int *>(smem + 512 + 64);        // [MAX_TOKENS]
+    float **out_ptr = reinterpret_cast<float **>(smem + 512 + 128);    // [MAX_TOKENS] mode 3 output row pointers
     float *partial = reinterpret_cast<float *>(smem + SMEM_CTRL_BYTES);
     float *xbuf = reinterpret_cast<float *>(smem + SMEM_CTRL_BYTES + SMEM_PART_BYTES);
     uint8_t *stage_base = smem + SMEM_CTRL_BYTES + SMEM_PART_BYTES + a.xbuf_bytes;
@@ -260,7 +264,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const St
                     if (ctid < m_tokens) {
                         const int flat = a.order[seg_begin + ctid];
                         seg_tokens[ctid] = (MODE == 2) ? flat / a.topk : seg_begin + ctid;
-                        if (MODE == 3) route_w[ctid] = a.route[flat];
+                        if (MODE == 3) {
+                            route_w[ctid] = a.route[flat];
+                            out_ptr[ctid] = term_row_pointer(static_cast<float *>(a.y), a.y_table, a.rows_per_rank, a.n, a.flat_rows ? flat : seg_begin + ctid);
+                        }
                     }
                     named_barrier_sync(1, CTHREADS);
                     const int total = m_tokens * K;
@@ -322,7 +329,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const St
                             static_cast<float *>(a.y)[static_cast<size_t>(seg_begin + m) * a.n + orow] =
                                 swiglu_f32(pa, pb);
                         else
-                            static_cast<float *>(a.y)[static_cast<size_t>(seg_begin + m) * a.n + orow] =
+                            out_ptr[m][orow] =
                                 pa * route_w[m];
                     }
                 } else if (lane == 0) {
@@ -352,7 +359,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const St
                 else if (MODE == 2)
                     static_cast<float *>(a.y)[static_cast<size_t>(seg_begin + m) * a.n + orow] = swiglu_f32(pa, pb);
                 else
-                    static_cast<float *>(a.y)[static_cast<size_t>(seg_begin + m) * a.n + orow] = pa * route_w[m];
+                    out_ptr[m][orow] = pa * route_w[m];
             }
             pbuf ^= 1;
         }

@@ -106,8 +106,10 @@ def max_segments_for(rows, k, n_experts, seg_cap=SEGMENT_CAP):
     return min(n_experts, total) + total // seg_cap
 
 
-def moe_plan(ids, n_experts, *, workspace=None):
-    """Build the device routing plan for integer ids ``[T,k]`` (int32 or int64)."""
+def moe_plan(ids, n_experts, *, skip_expert=-1):
+    """Build the device routing plan for integer ids ``[T,k]`` (int32 or int64).
+
+    Assignments to ``skip_expert`` are sorted and counted but never executed."""
     torch = _torch()
     if ids.dtype not in (torch.int32, torch.int64) or not ids.is_contiguous():
         raise ValueError("expert ids must be a contiguous int32/int64 tensor")
@@ -120,7 +122,8 @@ def moe_plan(ids, n_experts, *, workspace=None):
         torch.empty(n_experts, **i32), torch.empty(n_experts + 1, **i32), torch.empty(total, **i32),
         torch.empty(total, **i32), torch.empty(max_seg, **i32), torch.empty(max_seg, **i32),
         torch.empty(max_seg, **i32), torch.empty(1, **i32), max_seg, torch.empty(1, **i32))
-    _lib.call("b200q_moe_plan", _ptr(ids), 1 if ids.dtype == torch.int64 else 0, rows, k, n_experts, SEGMENT_CAP,
+    _lib.call("b200q_moe_plan_ex", _ptr(ids), 1 if ids.dtype == torch.int64 else 0, rows, k, n_experts,
+              int(skip_expert), SEGMENT_CAP,
               _ptr(plan.counts), _ptr(plan.offsets), _ptr(plan.order), _ptr(plan.inv), _ptr(plan.seg_expert),
               _ptr(plan.seg_begin), _ptr(plan.seg_count), _ptr(plan.num_segments), max_seg, _ptr(plan.status),
               _lib.current_stream())
@@ -144,14 +147,16 @@ def moe_gate_up(x2d, plan, gate_bank, up_bank, gate_fmt, up_fmt, f, d, gate_stri
 
 
 def moe_down(hbuf, route_weights, plan, down_bank, down_fmt, d, f, down_stride, *, down_table=None,
-             tables_aligned16=False):
-    """Route-weighted FP32 terms ``[T*k, D]`` in sorted-assignment order."""
+             tables_aligned16=False, flat_rows=False, out=None):
+    """Route-weighted FP32 terms ``[T*k, D]`` in sorted-assignment order, or (``flat_rows``) at the
+    flat assignment index ``row*k+slot``; ``out`` lets the caller supply (and pre-zero) the buffer."""
     torch = _torch()
     if route_weights.dtype != torch.float32 or not route_weights.is_contiguous():
         raise ValueError("routing weights must be a contiguous FP32 tensor")
-    terms = torch.empty((plan.rows * plan.k, d), dtype=torch.float32, device=hbuf.device)
+    terms = out if out is not None else torch.empty((plan.rows * plan.k, d), dtype=torch.float32,
+                                                     device=hbuf.device)
     _lib.call("b200q_moe_down", _ptr(down_bank), int(down_stride), _lib.FORMAT_ID[down_fmt], _ptr(down_table),
-              1 if tables_aligned16 else 0, d, f, _ptr(hbuf),
+              1 if tables_aligned16 else 0, 1 if flat_rows else 0, d, f, _ptr(hbuf),
               _ptr(route_weights), _ptr(plan.order), _ptr(plan.seg_expert), _ptr(plan.seg_begin),
               _ptr(plan.seg_count), _ptr(plan.num_segments), plan.max_segments, _ptr(terms), _lib.current_stream())
     return terms
@@ -165,3 +170,57 @@ def moe_combine(terms, plan, d, *, extra=None, extra_scale=None, out_dtype=None)
     _lib.call("b200q_moe_combine", _ptr(terms), _ptr(plan.inv), plan.rows, plan.k, d, _ptr(extra), _ptr(extra_scale),
               _ptr(out), _lib.DTYPE_ID[str(out_dtype).replace("torch.", "")], _lib.current_stream())
     return out
+
+
+def moe_combine_ids(terms_flat, ids2d, d, *, extra=None, extra_scale=None, out_dtype=None):
+    """Ordered per-token sum of terms stored at the flat assignment index; ``ids2d`` [T,k] gives the
+    order (ascending expert id, then slot). ``extra`` [T,d] (times ``extra_scale`` [T]) is added last."""
+    torch = _torch()
+    out_dtype = out_dtype or torch.float32
+    rows, k = ids2d.shape
+    if not ids2d.is_contiguous():
+        raise ValueError("expert ids must be contiguous")
+    out = torch.empty((rows, d), dtype=out_dtype, device=terms_flat.device)
+    _lib.call("b200q_moe_combine_ids", _ptr(terms_flat), _ptr(ids2d), 1 if ids2d.dtype == torch.int64 else 0, rows, k,
+              d, _ptr(extra), _ptr(extra_scale), _ptr(out), _lib.DTYPE_ID[str(out_dtype).replace("torch.", "")],
+              _lib.current_stream())
+    return out
+
+
+def moe_plan_ep(ids, *, e_global, first_expert, n_local, shared_id, home_lo, home_hi):
+    """Routing plan of one expert-parallel rank over the gathered ids ``[T_all, k]`` (global ids).
+
+    Local expert ids: 0..n_local-1 routed, n_local = shared expert (home rows only), n_local+1 =
+    assignments other ranks execute (sorted last, never run)."""
+    torch = _torch()
+    if ids.dtype not in (torch.int32, torch.int64) or not ids.is_contiguous():
+        raise ValueError("expert ids must be a contiguous int32/int64 tensor")
+    rows, k = ids.shape
+    n_plan = n_local + 2
+    total = rows * k
+    max_seg = max_segments_for(rows, k, n_plan)
+    i32 = dict(dtype=torch.int32, device=ids.device)
+    plan = DeviceRoutingPlan(
+        rows, k, n_plan,
+        torch.empty(n_plan, **i32), torch.empty(n_plan + 1, **i32), torch.empty(total, **i32),
+        torch.empty(total, **i32), torch.empty(max_seg, **i32), torch.empty(max_seg, **i32),
+        torch.empty(max_seg, **i32), torch.empty(1, **i32), max_seg, torch.empty(1, **i32))
+    _lib.call("b200q_moe_plan_ep", _ptr(ids), 1 if ids.dtype == torch.int64 else 0, rows, k, int(e_global),
+              int(first_expert), int(n_local), int(shared_id), int(home_lo), int(home_hi), SEGMENT_CAP,
+              _ptr(plan.counts), _ptr(plan.offsets), _ptr(plan.order), _ptr(plan.inv), _ptr(plan.seg_expert),
+              _ptr(plan.seg_begin), _ptr(plan.seg_count), _ptr(plan.num_segments), max_seg, _ptr(plan.status),
+              _lib.current_stream())
+    return plan
+
+
+def moe_down_peer(hbuf, route_weights, plan, down_fmt, d, f, *, down_table, tables_aligned16, term_tables,
+                  rows_per_rank):
+    """Grouped down projection whose route-weighted term rows go straight to their home rank's buffer
+    (``term_tables``: int64 device tensor with one base address per rank)."""
+    torch = _torch()
+    if route_weights.dtype != torch.float32 or not route_weights.is_contiguous():
+        raise ValueError("routing weights must be a contiguous FP32 tensor")
+    _lib.call("b200q_moe_down_peer", None, 0, _lib.FORMAT_ID[down_fmt], _ptr(down_table),
+              1 if tables_aligned16 else 0, d, f, _ptr(hbuf), _ptr(route_weights), _ptr(plan.order),
+              _ptr(plan.seg_expert), _ptr(plan.seg_begin), _ptr(plan.seg_count), _ptr(plan.num_segments),
+              plan.max_segments, _ptr(term_tables), int(rows_per_rank), _lib.current_stream())

@@ -1,0 +1,220 @@
+"""Expert-parallel MoE on the GPU: whatever the number of ranks, the result must be the single-GPU
+layer's, bit for bit.
+
+One GPU is enough for most of it: the ranks' device steps run one after the other on the same GPU
+(no kernel waits on another rank there), and the exchange is done by hand. The real two-process runs
+(NCCL collectives, and peer-memory stores with the device barrier) need two GPUs and are skipped
+otherwise.
+"""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from mylocal_llm_b200 import PackedMoELayer, packed_to_device
+from mylocal_llm_b200 import _lib
+from mylocal_llm_b200.expert_parallel import (CollectiveComm, DeviceExpertEngine, ExpertParallelMoELayer, LocalComm,
+                                              PeerComm, expert_partition, shard_bank)
+from mylocal_llm_b200.experts_inference import synthetic_bank
+from mylocal_llm_b200.quantize import random_packed
+
+pytestmark = pytest.mark.gpu
+
+D, F, E, K = 512, 256, 16, 4
+TYPES = ("Q4_K", "Q4_K", "Q6_K")
+
+
+@pytest.fixture(autouse=True, params=["tensor", "lanes"])
+def kernel_family(request, monkeypatch):
+    monkeypatch.setenv("B200Q_KERNEL", {"tensor": "auto", "lanes": "lanes"}[request.param])
+    return request.param
+
+
+def build_model(torch, *, shared_ff=F, with_gate=False, seed=0):
+    bank = synthetic_bank(E, D, F, TYPES, seed=seed)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(100 + seed)
+    w_router = torch.empty((D, E), dtype=torch.float32, device="cuda").normal_(0.0, 0.3, generator=gen)
+    shared = None
+    if shared_ff:
+        shapes = ((shared_ff, D), (shared_ff, D), (D, shared_ff))
+        shared = tuple(packed_to_device(random_packed(fmt, shape, seed=50 + seed + j, d=1.0 / 2048, dmin=1.0 / 4096))
+                       for j, (fmt, shape) in enumerate(zip(TYPES, shapes)))
+    gate = None
+    if with_gate:
+        gate = torch.empty(D, dtype=torch.float32, device="cuda").normal_(0.0, 0.1, generator=gen)
+    return bank, w_router, shared, gate
+
+
+def make_rows(torch, rows, dtype, seed=1):
+    x = np.random.default_rng(seed).normal(0, 1, (rows, D)).astype(np.float32)
+    return torch.from_numpy(x).cuda().to(dtype)
+
+
+def engines_for(world, bank, w_router, shared, gate):
+    out = []
+    for rank in range(world):
+        first, local = shard_bank(bank, rank, world)
+        out.append(DeviceExpertEngine(local, w_router, K, first_expert=first, n_experts_global=E, shared=shared,
+                                      shared_gate=gate))
+    return out
+
+
+@pytest.mark.parametrize("world,rows", [(1, 5), (2, 1), (2, 16), (4, 3)])
+@pytest.mark.parametrize("variant", ["folded", "folded_gate", "separate_shared", "no_shared"])
+def test_emulated_ranks_with_summed_terms_equal_the_single_gpu_layer(cuda, world, rows, variant):
+    torch = cuda
+    bank, w_router, shared, gate = build_model(
+        torch, shared_ff={"separate_shared": 512, "no_shared": 0}.get(variant, F), with_gate=variant == "folded_gate")
+    if variant == "separate_shared":
+        gate = torch.full((D,), 0.01, dtype=torch.float32, device="cuda")
+    x_all = make_rows(torch, world * rows, torch.bfloat16)
+    want = PackedMoELayer(bank, w_router, K, shared=shared, shared_gate=gate).forward(x_all[None])[0]
+    engines = engines_for(world, bank, w_router, shared, gate)
+    weights, ids = engines[0].route(x_all)
+    total = None
+    for rank, engine in enumerate(engines):
+        w_r, ids_r = engine.route(x_all)
+        assert torch.equal(ids_r, ids) and torch.equal(w_r, weights)
+        terms = engine.local_terms(x_all, weights, ids, rank * rows, (rank + 1) * rows)
+        if total is not None:                       # every row has exactly one producer
+            assert not bool(((total != 0) & (terms != 0)).any())
+        total = terms if total is None else total + terms
+    k_out = engines[0].k_out
+    got = []
+    for rank, engine in enumerate(engines):
+        lo, hi = rank * rows, (rank + 1) * rows
+        got.append(engine.combine(total[lo * k_out:hi * k_out], ids[lo:hi].contiguous(), x_all[lo:hi],
+                                  torch.bfloat16))
+    assert torch.equal(torch.cat(got), want)
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("world,rows", [(2, 4), (4, 1)])
+def test_emulated_ranks_storing_into_home_buffers_equal_the_single_gpu_layer(cuda, world, rows):
+    torch = cuda
+    bank, w_router, shared, gate = build_model(torch, with_gate=True, seed=3)
+    x_all = make_rows(torch, world * rows, torch.float32, seed=4)
+    want = PackedMoELayer(bank, w_router, K, shared=shared, shared_gate=gate).forward(x_all[None])[0]
+    engines = engines_for(world, bank, w_router, shared, gate)
+    k_out = engines[0].k_out
+    homes = [torch.full((rows * k_out, D), float("nan"), dtype=torch.float32, device="cuda") for _ in range(world)]
+    table = torch.tensor([h.data_ptr() for h in homes], dtype=torch.int64, device="cuda")
+    weights, ids = engines[0].route(x_all)
+    for rank, engine in enumerate(engines):
+        engine.local_terms(x_all, weights, ids, rank * rows, (rank + 1) * rows, peer=(table, rows * k_out))
+    got = []
+    for rank, engine in enumerate(engines):
+        assert not bool(torch.isnan(homes[rank]).any())        # every term row was written by someone
+        lo, hi = rank * rows, (rank + 1) * rows
+        got.append(engine.combine(homes[rank], ids[lo:hi].contiguous(), x_all[lo:hi], torch.float32))
+    assert torch.equal(torch.cat(got), want)
+    assert _lib.device_status() == 0
+
+
+def test_plan_ep_reports_ids_outside_the_global_range(cuda):
+    from mylocal_llm_b200 import moe_ops
+    ids = cuda.tensor([[0, 3], [17, 1]], dtype=cuda.int64, device="cuda")
+    plan = moe_ops.moe_plan_ep(ids, e_global=17, first_expert=0, n_local=8, shared_id=16, home_lo=0, home_hi=2)
+    assert int(plan.status.item()) == 1
+    plan = moe_ops.moe_plan_ep(ids.clamp(max=16), e_global=17, first_expert=0, n_local=8, shared_id=16, home_lo=0,
+                               home_hi=1)
+    assert int(plan.status.item()) == 0
+    # rows: [0, 3] local; [16 -> not home (row 1) -> skipped, 1 local]
+    assert plan.counts.cpu().tolist() == [1, 1, 0, 1, 0, 0, 0, 0, 0, 1]
+    with pytest.raises(ValueError):
+        moe_ops.moe_plan_ep(ids, e_global=4, first_expert=0, n_local=8, shared_id=-1, home_lo=0, home_hi=2)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_peer_comm_in_a_world_of_one(cuda):
+    """Arena allocation, push, barrier and peer-table stores with a single rank (nothing to wait for)."""
+    import torch.distributed as dist
+    torch = cuda
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{_free_port()}", rank=0, world_size=1)
+    try:
+        bank, w_router, shared, gate = build_model(torch, seed=6)
+        comm = PeerComm(None, max_rows=8, d_model=D, k_out=K + 1)
+        layer = ExpertParallelMoELayer(DeviceExpertEngine(bank, w_router, K, first_expert=0, n_experts_global=E,
+                                                          shared=shared), comm, D)
+        for rows in (8, 2):
+            x = make_rows(torch, rows, torch.bfloat16, seed=rows)
+            want = PackedMoELayer(bank, w_router, K, shared=shared).forward(x[None])
+            assert torch.equal(layer.forward(x[None]), want)
+        with pytest.raises(ValueError):
+            layer.forward(make_rows(torch, 9, torch.bfloat16)[None])
+        assert _lib.device_status() == 0
+        comm.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_local_comm_layer_equals_packed_layer(cuda):
+    torch = cuda
+    bank, w_router, shared, gate = build_model(torch, with_gate=True, seed=8)
+    layer = ExpertParallelMoELayer(DeviceExpertEngine(bank, w_router, K, first_expert=0, n_experts_global=E,
+                                                      shared=shared, shared_gate=gate), LocalComm(), D)
+    x = make_rows(torch, 7, torch.float32)[None]
+    assert torch.equal(layer.forward(x), PackedMoELayer(bank, w_router, K, shared=shared, shared_gate=gate).forward(x))
+
+
+# ---------------------------------------------------------------------------- two real processes
+def _rank_main(rank, world, port, family, queue):
+    import torch
+    import torch.distributed as dist
+    os.environ["B200Q_KERNEL"] = family
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    ok, note = True, ""
+    try:
+        bank, w_router, shared, gate = build_model(torch, with_gate=True, seed=11)
+        first, local = shard_bank(bank, rank, world)
+        engine = DeviceExpertEngine(local, w_router, K, first_expert=first, n_experts_global=E, shared=shared,
+                                    shared_gate=gate)
+        reference = PackedMoELayer(bank, w_router, K, shared=shared, shared_gate=gate)
+        comms = [("collective", CollectiveComm()), ("peer", PeerComm(None, max_rows=16, d_model=D, k_out=K + 1))]
+        for name, comm in comms:
+            layer = ExpertParallelMoELayer(engine, comm, D)
+            for rows, dtype in ((16, torch.bfloat16), (1, torch.float32), (5, torch.bfloat16)):
+                x_all = make_rows(torch, world * rows, dtype, seed=rows)
+                want = reference.forward(x_all[None])[0][rank * rows:(rank + 1) * rows]
+                for _ in range(3):                                    # repeated calls reuse the arenas
+                    got = layer.forward(x_all[rank * rows:(rank + 1) * rows][None].contiguous())[0]
+                    if not torch.equal(got, want):
+                        ok, note = False, f"{name} rows={rows} differs"
+            torch.cuda.synchronize()
+            comm.close()
+        if _lib.device_status() != 0:
+            ok, note = False, f"device status {_lib.device_status()}"
+    except Exception as exc:                                          # reported to the parent
+        ok, note = False, repr(exc)
+    finally:
+        queue.put((rank, ok, note))
+        dist.destroy_process_group()
+
+
+def test_two_gpus_collective_and_peer_exchange(cuda, kernel_family):
+    if cuda.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = _free_port()
+    family = {"tensor": "auto", "lanes": "lanes"}[kernel_family]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, family, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [queue.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+    assert all(ok for _, ok, _ in results), results
