@@ -53,7 +53,9 @@ MOE_WORKLOADS = {
     "moe_layer_t1": (8, 1, False), "moe_layer_t16": (8, 16, False), "moe_layer_t64": (4, 64, False),
     "moe_layer_t256": (2, 256, False), "moe_stack_b1": (48, 1, True), "moe_stack_b64": (48, 64, True),
 }
-DEFAULT_WORKLOAD = "gemv_q4k_8192x2048_m1"
+DEFAULT_WORKLOAD = "moe_stack_b64"
+# dense decode GEMVs timed briefly next to every MoE run (rank 0): second configuration + one large matrix
+SIDE_GEMVS = ("gemv_q4k_8192x2048_m1", "gemv_q8_0_4096x4096_m1", "gemv_q4k_65536x8192_m1")
 
 
 def packed_bytes(fmt, n, k):
@@ -331,6 +333,57 @@ def run_gpu_arm(args, name):
         dist.destroy_process_group()
 
 
+def gemv_side_numbers(names, replays=20):
+    """Short device-resident timing of dense decode GEMVs (same method as run_gpu_arm), reported next to
+    the MoE number so one line carries both halves of the metric."""
+    import torch
+    from mylocal_llm_b200 import packed_to_device, quantized_linear
+    from mylocal_llm_b200.quantize import random_packed
+    peak, _ = measured_peaks()
+    out = {}
+    stream = torch.cuda.Stream()
+    for name in names:
+        fmt, n, k, m, act = WORKLOADS[name]
+        act_dtype = getattr(torch, act)
+        wbytes = packed_bytes(fmt, n, k)
+        copies = min(max(2, -(-2 * L2_BYTES // wbytes)), 64)
+        base = random_packed(fmt, (n, k), seed=99, d=0.01, dmin=0.005)
+        weights = [packed_to_device(base) for _ in range(copies)]
+        x = torch.randn((copies, m, k), device="cuda").to(act_dtype)
+        with torch.cuda.stream(stream):
+            for c in range(copies):
+                quantized_linear(x[c], weights[c])
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for c in range(copies):
+                    quantized_linear(x[c], weights[c])
+            for _ in range(3):
+                graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(replays):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (replays * copies)
+        graph.reset()
+        per_launch = algorithmic_bytes(fmt, n, k, m, 4 if act == "float32" else 2)
+        gbs = per_launch / (us * 1e-6) / 1e9
+        out[name] = {"GB/s": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4), "us_per_launch": round(us, 3)}
+        del weights, graph
+    torch.cuda.empty_cache()
+    return out
+
+
+def exit_watchdog(seconds=90):
+    """Teardown of a process group whose collectives were captured in a CUDA graph can block; the
+    result line is already printed by then, so a stuck teardown ends the process instead of the run."""
+    timer = threading.Timer(seconds, lambda: os._exit(0))
+    timer.daemon = True
+    timer.start()
+
+
 # ------------------------------------------------------------------------------ MoE workloads
 MOE_SHAPE = dict(d_model=2048, d_ff=512, n_experts=512, top_k=10, shared_d_ff=512)
 EXPERT_BYTES = 2 * packed_bytes("Q4_K", 512, 2048) + packed_bytes("Q6_K", 2048, 512)
@@ -402,6 +455,7 @@ def run_moe_gpu_arm(args, name):
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    side = gemv_side_numbers(SIDE_GEMVS) if rank == 0 and not args.skip_side else None
     comm = None
     if world > 1:
         # expert-parallel: experts sharded over the ranks, `tokens` rows per rank (weak scaling in tokens)
@@ -546,11 +600,17 @@ def run_moe_gpu_arm(args, name):
                     "h2d_bytes_per_step": int(host_x.numel() * 4), "d2h_bytes_per_step": int(host_y.numel() * 4)},
             "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
         }
+        if side is not None:
+            line["dense_gemv"] = side
         if world == 1 and not args.skip_cpu_baseline:
             tps, kind, cores, sample = cpu_moe_throughput(layers if chained else 1, 12.0)
             line["cpu_baseline"] = {"value": round(tps, 4), "unit": "tokens/s", "cores": cores, "kind": kind,
                                     "sample": sample}
         print(json.dumps(line))
+    sys.stdout.flush()
+    exit_watchdog()
+    graph.reset()
+    torch.cuda.synchronize()
     if comm is not None:
         comm.close()
     if world > 1:
@@ -566,6 +626,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(MOE_WORKLOADS))
     ap.add_argument("--exchange", default="peer", choices=["peer", "collective"],
                     help="expert-parallel exchange at N > 1: peer-memory stores + device barrier, or NCCL")
+    ap.add_argument("--skip-side", action="store_true", help="omit the dense-GEMV side measurements")
     ap.add_argument("--skip-cpu-baseline", action="store_true",
                     help="omit the host-core baseline leg (exploratory runs only)")
     args = ap.parse_args()

@@ -28,6 +28,9 @@ extern "C" {
 #define B200Q_Q4_K 2
 #define B200Q_Q5_K 4
 #define B200Q_Q6_K 5
+/* Q6_K re-ordered on the device into 16-row x 1-super-block tiles (b200q_q6k_retile): same size, same
+ * values, 16-byte aligned pieces. Accepted by b200q_gemv and b200q_moe_down(_peer) only. */
+#define B200Q_Q6_K_TILED 21
 
 /* activation / output element types */
 #define B200Q_F32 0
@@ -179,6 +182,14 @@ int b200q_moe_combine(const float *terms, const int32_t *inv, int rows, int k, i
  * b200q_moe_combine; used by the home rank of an expert-parallel layer). */
 int b200q_moe_combine_ids(const float *terms, const void *ids, int ids_is_i64, int rows, int k, int d,
                           const float *extra, const float *extra_scale, void *out, int out_dtype, void *stream);
+
+/* Lossless re-ordering of a native Q6_K matrix [rows, k] (rows % 16 == 0, k % 256 == 0; a bank of
+ * experts is one matrix of E*rows_per_expert rows) into the tile layout and back. Out of place; the
+ * tiled buffer must be 16-byte aligned. GGUF stores 210-byte Q6_K blocks, which no 128-bit load can
+ * address; the tile layout is what the tensor-core kernel streams at full width. (No counterpart in
+ * the reference, which reads native blocks byte by byte: mini_llm/ops/quantized_linear.py:139-158.) */
+int b200q_q6k_retile(const void *native, void *tiled, int64_t rows, int k, void *stream);
+int b200q_q6k_untile(const void *tiled, void *native, int64_t rows, int k, void *stream);
 
 /* ---- Expert-parallel execution over the GPUs of one node (no counterpart in the reference, which is
  * single-process; semantics = the single-GPU layer, bit for bit). ------------------------------- */

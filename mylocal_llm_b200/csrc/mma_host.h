@@ -39,4 +39,8 @@ int mma_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched);
 // Same contract for the direct-load kernel (Q4_K / Q5_K only); tried first.
 int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched);
 
+// Weights in the Q6_K tile layout (mode 0 or 3, at most 8 tokens): there is no other kernel for
+// this layout, so a request that does not fit returns an error instead of declining.
+int q6k_tiled_launch(const MmaRequest &q, cudaStream_t stream);
+
 }  // namespace b200q

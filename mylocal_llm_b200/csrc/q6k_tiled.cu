@@ -1,0 +1,150 @@
+// Q6_K tile layout: re-ordering kernels, the GEMV launcher and the C ABI entry points.
+#include "q6k_tiled.cuh"
+#include "mma_host.h"
+
+namespace b200q {
+
+// One thread per (tile, lane): writes the lane's 24 code words; lanes 0-15 also copy one row's
+// scales (biased by 128) and d.
+__global__ void __launch_bounds__(256) q6k_retile_kernel(const uint8_t *src, uint8_t *dst, long long tiles, int nsb) {
+    const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    const long long tile = idx >> 5;
+    if (tile >= tiles) return;
+    const int lane = static_cast<int>(idx & 31), g = lane >> 2, tig = lane & 3;
+    const long long group = tile / nsb;
+    const int sb = static_cast<int>(tile - group * nsb);
+    const size_t row_bytes = static_cast<size_t>(nsb) * 210;
+    uint8_t *out = dst + static_cast<size_t>(tile) * Q6T_TILE_BYTES;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const uint8_t *blk = src + (static_cast<size_t>(group) * 16 + g + 8 * half) * row_bytes + static_cast<size_t>(sb) * 210;
+        uint32_t words[12];
+        for (int c = 0; c < 4; ++c) {
+            uint32_t w[3];
+            q6k_pack_chunk(blk, c, tig, w);
+            words[3 * c] = w[0]; words[3 * c + 1] = w[1]; words[3 * c + 2] = w[2];
+        }
+        for (int p = 0; p < 3; ++p)
+            *reinterpret_cast<uint4 *>(out + (3 * half + p) * 512 + lane * 16) =
+                make_uint4(words[4 * p], words[4 * p + 1], words[4 * p + 2], words[4 * p + 3]);
+    }
+    if (lane < 16) {
+        const uint8_t *blk = src + (static_cast<size_t>(group) * 16 + lane) * row_bytes + static_cast<size_t>(sb) * 210;
+        for (int i = 0; i < 16; ++i) out[Q6T_SCALES_OFF + 16 * lane + i] = blk[192 + i] ^ 0x80u;
+        out[Q6T_D_OFF + 2 * lane] = blk[208];
+        out[Q6T_D_OFF + 2 * lane + 1] = blk[209];
+    }
+}
+
+// Inverse: one thread per (tile, row): rebuilds the row's native 210-byte block.
+__global__ void __launch_bounds__(256) q6k_untile_kernel(const uint8_t *src, uint8_t *dst, long long tiles, int nsb) {
+    const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    const long long tile = idx >> 4;
+    if (tile >= tiles) return;
+    const int row = static_cast<int>(idx & 15), g = row & 7, half = row >> 3;
+    const long long group = tile / nsb;
+    const int sb = static_cast<int>(tile - group * nsb);
+    const uint8_t *in = src + static_cast<size_t>(tile) * Q6T_TILE_BYTES;
+    uint8_t *blk = dst + (static_cast<size_t>(group) * 16 + row) * (static_cast<size_t>(nsb) * 210) + static_cast<size_t>(sb) * 210;
+    for (int i = 0; i < 192; ++i) blk[i] = 0;
+    for (int tig = 0; tig < 4; ++tig) {
+        const int lane = 4 * g + tig;
+        uint32_t words[12];
+        for (int p = 0; p < 3; ++p) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(in + (3 * half + p) * 512 + lane * 16);
+            words[4 * p] = v.x; words[4 * p + 1] = v.y; words[4 * p + 2] = v.z; words[4 * p + 3] = v.w;
+        }
+        for (int c = 0; c < 4; ++c) {
+            const uint32_t w[3] = {words[3 * c], words[3 * c + 1], words[3 * c + 2]};
+            for (int j = 0; j < 4; ++j)
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t code = q6k_tiled_code(w, j, i);
+                    const int h = c >> 1, l = 16 * (c & 1) + 4 * tig + i;
+                    const int qi = 64 * h + 32 * (j & 1) + l;
+                    blk[qi] |= static_cast<uint8_t>((j >> 1) ? (code & 15u) << 4 : (code & 15u));
+                    blk[128 + 32 * h + l] |= static_cast<uint8_t>((code >> 4) << (2 * j));
+                }
+        }
+    }
+    for (int i = 0; i < 16; ++i) blk[192 + i] = in[Q6T_SCALES_OFF + 16 * row + i] ^ 0x80u;
+    blk[208] = in[Q6T_D_OFF + 2 * row];
+    blk[209] = in[Q6T_D_OFF + 2 * row + 1];
+}
+
+using Q6Fn = void (*)(const Q6TiledArgs);
+
+// Runs the tiled kernel for a mode 0 or mode 3 request whose weights are in the tile layout.
+int q6k_tiled_launch(const MmaRequest &q, cudaStream_t stream) {
+    const bool grouped = q.mode == 3;
+    if (q.mode != 0 && q.mode != 3) return fail(B200Q_EUNSUPPORTED, "tiled Q6_K: only linear and grouped down");
+    if (q.k % 256 != 0 || q.n % 16 != 0 || q.m < 1 || q.m > 8)
+        return fail(B200Q_EUNSUPPORTED, "tiled Q6_K: needs K %% 256 == 0, N %% 16 == 0, 1..8 tokens per pass");
+    if ((reinterpret_cast<uintptr_t>(q.wa) & 15) || (grouped && !q.table_a && (q.stride_a & 15)) ||
+        (grouped && q.table_a && !q.tables_aligned16))
+        return fail(B200Q_EINVAL, "tiled Q6_K: weights must be 16-byte aligned");
+    Q6TiledArgs a{};
+    a.w = q.wa; a.stride = q.stride_a; a.table = q.table_a;
+    a.n = q.n; a.k = q.k; a.m = q.m;
+    a.nterms = (q.x_dtype == B200Q_F32) ? 2 : 1;
+    const int nsb = q.k / 256;
+    const long long row_groups = static_cast<long long>(q.n / 16) * (grouped ? q.max_segments : 1);
+    const long long wanted = 3LL * sm_count() * Q6T_WARPS;
+    int kp = 1;
+    while (kp * 2 <= Q6T_WARPS && kp * 2 <= nsb && row_groups * kp < wanted) kp *= 2;
+    a.kp = kp;
+    a.rg = Q6T_WARPS / kp;
+    a.off_bfrag = Q6T_CTRL_BYTES + Q6T_PART_BYTES;
+    const long long smem = a.off_bfrag + static_cast<long long>(a.nterms) * (q.k / 16) * 256;
+    if (smem > MM_SMEM_LIMIT) return fail(B200Q_EUNSUPPORTED, "tiled Q6_K: K=%d too large", q.k);
+    a.x = q.x; a.x_dtype = q.x_dtype; a.y = q.y; a.y_dtype = q.y_dtype;
+    a.order = q.order; a.seg_expert = q.seg_expert; a.seg_begin = q.seg_begin; a.seg_count = q.seg_count;
+    a.num_segments = q.num_segments; a.max_segments = q.max_segments; a.route = q.route;
+    a.flat_rows = q.flat_rows; a.y_table = q.y_table; a.rows_per_rank = q.rows_per_rank;
+    Q6Fn fn = grouped ? (a.nterms == 2 ? q6k_tiled_kernel<3, 2> : q6k_tiled_kernel<3, 1>)
+                      : (a.nterms == 2 ? q6k_tiled_kernel<0, 2> : q6k_tiled_kernel<0, 1>);
+    cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void *>(fn),
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM_LIMIT);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail(B200Q_ECUDA, "tiled Q6_K: shared memory opt-in failed: %s", cudaGetErrorString(err));
+    }
+    int grid = sm_count();
+    if (!grouped) {
+        const int blocks = (q.n / 16 + a.rg - 1) / a.rg;
+        if (blocks < grid) grid = blocks;
+    }
+    fn<<<grid, Q6T_THREADS, static_cast<size_t>(smem), stream>>>(a);
+    return check_launch("tiled Q6_K gemv");
+}
+
+static int retile_common(const void *src, void *dst, long long rows, int k, bool forward, void *stream) {
+    if (!src || !dst) return fail(B200Q_EINVAL, "q6k_retile: NULL pointer");
+    if (rows <= 0 || rows % 16 != 0 || k <= 0 || k % 256 != 0)
+        return fail(B200Q_EINVAL, "q6k_retile: rows must be a multiple of 16 and K a multiple of 256");
+    if (src == dst) return fail(B200Q_EINVAL, "q6k_retile: in-place conversion is not supported");
+    if (reinterpret_cast<uintptr_t>(forward ? dst : src) & 15)
+        return fail(B200Q_EINVAL, "q6k_retile: the tiled buffer must be 16-byte aligned");
+    const int nsb = k / 256;
+    const long long tiles = rows / 16 * nsb;
+    const long long threads = tiles * (forward ? 32 : 16);
+    const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
+    if (forward)
+        q6k_retile_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst), tiles, nsb);
+    else
+        q6k_untile_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst), tiles, nsb);
+    return check_launch("q6k_retile");
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" int b200q_q6k_retile(const void *native, void *tiled, int64_t rows, int k, void *stream) {
+    return retile_common(native, tiled, rows, k, true, stream);
+}
+
+extern "C" int b200q_q6k_untile(const void *tiled, void *native, int64_t rows, int k, void *stream) {
+    return retile_common(tiled, native, rows, k, false, stream);
+}

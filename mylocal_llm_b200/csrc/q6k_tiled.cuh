@@ -1,0 +1,375 @@
+// Q6_K in a device-side tile layout, and the tensor-core GEMV that reads it (sm_100a).
+//
+// A GGUF Q6_K super-block is 210 bytes (ql[128] | qh[64] | int8 scales[16] | fp16 d), so rows and
+// blocks start on 2-byte boundaries only: no 128-bit load, no aligned bulk copy, and every 32-bit
+// fetch of a code word straddles two words half of the time. The kernels that read the native
+// layout therefore stage rows through shared memory and pay two loads plus a byte permute per
+// word. Weights are written once and read on every decode step, so the bytes are re-ordered once,
+// at upload, into tiles that a warp can consume straight from global memory:
+//
+//   tile = 16 rows x 1 super-block = 3360 bytes (the size of the 16 native blocks, 16-byte aligned)
+//     [   0, 3072)  six planes of 512 bytes; plane p holds one uint4 per lane (lane*16):
+//                   planes 0-2 = the 12 code words of row g = lane>>2, planes 3-5 = row g+8
+//     [3072, 3328)  16 rows x 16 scale bytes, stored as scale+128 (unsigned)
+//     [3328, 3360)  16 x fp16 d
+//   tiles are ordered (row group, super-block), so a row group's K range is contiguous.
+//
+// Code words: lane tig = lane&3 owns, in each 16-value scale group s of the block, the values
+// 4*tig .. 4*tig+3. For chunk c = 0..3 (scale groups c, c+2, c+4, c+6 of one half: s = 8*(c>>1) +
+// 2*j + (c&1), j = 0..3) three words W0..W2 hold its 16 six-bit codes as FP16-pair fields:
+//   Wj (j<3): bits [0,6) value0, [16,22) value2 of group j  -> pair P0
+//             bits [6,12) value1, [22,28) value3 of group j -> pair P1
+//   group j = 3: low nibbles of (value0, value2) in W0[12,16) / W0[28,32), of (value1, value3) in
+//             W1[12,16) / W1[28,32); high two bits in W2[12,14) / W2[28,30) and W2[14,16) / W2[30,32)
+// so one AND-OR (after at most one shift) turns a field into the FP16 pair (1024+code, 1024+code),
+// and one packed add of -1056 gives the exact signed codes (code - 32) as an mma A operand. The
+// pairing (values 0,2 | 1,3) matches the activation fragments of prepare_fragments().
+//
+// The re-ordering is lossless: b200q_q6k_untile restores the GGUF bytes bit for bit.
+#pragma once
+
+#include "mma_direct.cuh"
+
+namespace b200q {
+
+constexpr int Q6T_TILE_BYTES = 3360;
+constexpr int Q6T_SCALES_OFF = 3072;
+constexpr int Q6T_D_OFF = 3328;
+constexpr int Q6T_WARPS = 16;
+constexpr int Q6T_THREADS = Q6T_WARPS * 32;
+constexpr int Q6T_CTRL_BYTES = 1024;
+constexpr int Q6T_PART_FLOATS = Q6T_WARPS * 128;           // [warp][16 rows][8 tokens]
+constexpr int Q6T_PART_BYTES = 2 * Q6T_PART_FLOATS * 4;    // double buffered
+
+struct Q6TiledArgs {
+    const uint8_t *w;
+    long long stride;
+    const unsigned long long *table;
+    int n, k, m;
+    int kp, rg;
+    int nterms;
+    int off_bfrag;
+    const void *x;
+    int x_dtype;
+    void *y;
+    int y_dtype;
+    const int32_t *order;
+    const int32_t *seg_expert;
+    const int32_t *seg_begin;
+    const int32_t *seg_count;
+    const int32_t *num_segments;
+    int max_segments;
+    const float *route;
+    int flat_rows;
+    const uint64_t *y_table;
+    int rows_per_rank;
+};
+
+// Code of value `i` (0..3) of lane `tig` in scale group s of a native block.
+__host__ __device__ inline uint32_t q6k_native_code(const uint8_t *blk, int s, int tig, int i) {
+    const int h = s >> 3, j = (s >> 1) & 3, l = 16 * (s & 1) + 4 * tig + i;
+    const uint32_t qlb = blk[64 * h + 32 * (j & 1) + l];
+    const uint32_t nib = (j >> 1) ? (qlb >> 4) : (qlb & 15u);
+    const uint32_t hi = (blk[128 + 32 * h + l] >> (2 * j)) & 3u;
+    return nib | (hi << 4);
+}
+
+// The three words of chunk c for lane tig of one native block.
+__host__ __device__ inline void q6k_pack_chunk(const uint8_t *blk, int c, int tig, uint32_t (&w)[3]) {
+    uint32_t code[4][4];
+    for (int j = 0; j < 4; ++j)
+        for (int i = 0; i < 4; ++i) code[j][i] = q6k_native_code(blk, 8 * (c >> 1) + 2 * j + (c & 1), tig, i);
+    for (int j = 0; j < 3; ++j)
+        w[j] = code[j][0] | (code[j][2] << 16) | (code[j][1] << 6) | (code[j][3] << 22);
+    w[0] |= ((code[3][0] & 15u) << 12) | ((code[3][2] & 15u) << 28);
+    w[1] |= ((code[3][1] & 15u) << 12) | ((code[3][3] & 15u) << 28);
+    w[2] |= ((code[3][0] >> 4) << 12) | ((code[3][2] >> 4) << 28) | ((code[3][1] >> 4) << 14) | ((code[3][3] >> 4) << 30);
+}
+
+// Inverse of q6k_pack_chunk: code of (group j of the chunk, value i).
+__host__ __device__ inline uint32_t q6k_tiled_code(const uint32_t (&w)[3], int j, int i) {
+    const int half = (i >> 1) * 16;            // values 0,1 in the low half-word, 2,3 in the high one
+    const int odd = i & 1;
+    if (j < 3) return (w[j] >> (half + 6 * odd)) & 63u;
+    const uint32_t nib = (w[odd] >> (half + 12)) & 15u;
+    const uint32_t hi = (w[2] >> (half + 12 + 2 * odd)) & 3u;
+    return nib | (hi << 4);
+}
+
+struct Q6TileRegs {
+    uint4 c[6];      // planes 0-2: row g, planes 3-5: row g+8
+    uint4 sa, sb;    // biased scales of row g / row g+8
+    uint32_t dd;     // fp16 d of row g (low half) and row g+8 (high half)
+};
+
+__device__ __forceinline__ uint32_t ldg_u16(const uint8_t *p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void load_q6_tile(Q6TileRegs &r, const uint8_t *tile, int lane) {
+    const int g = lane >> 2;
+#pragma unroll
+    for (int p = 0; p < 6; ++p) r.c[p] = ldg128(tile + p * 512 + lane * 16);
+    r.sa = ldg128(tile + Q6T_SCALES_OFF + 16 * g);
+    r.sb = ldg128(tile + Q6T_SCALES_OFF + 16 * (g + 8));
+    r.dd = ldg_u16(tile + Q6T_D_OFF + 2 * g) | (ldg_u16(tile + Q6T_D_OFF + 2 * (g + 8)) << 16);
+}
+
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t c) { return (a & mask) | c; }
+
+__device__ __forceinline__ uint32_t hadd2_u32(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("add.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// Scale byte b of `word` (stored +128) as an exact float.
+__device__ __forceinline__ float biased_byte_to_float(uint32_t word, int b) {
+    const uint32_t bits = __byte_perm(word, 0x4b000000u, 0x7650 + b);     // 8388608 + byte
+    return __uint_as_float(bits) - 8388736.0f;
+}
+
+// One tile: 16 scale groups = 16 mma steps; tot += d * sum_s scale_s * (codes_s . x_s).
+template <int NTERMS>
+__device__ __forceinline__ void q6_tile_mma(const Q6TileRegs &r, const uint2 *bfrag, int nfrag, int sb, int lane,
+                                            float (&tot)[4]) {
+    const uint32_t magic = 0x64006400u, neg = 0xe420e420u;       // 1024 | code ; -(1024 + 32)
+    const uint32_t wa[12] = {r.c[0].x, r.c[0].y, r.c[0].z, r.c[0].w, r.c[1].x, r.c[1].y,
+                             r.c[1].z, r.c[1].w, r.c[2].x, r.c[2].y, r.c[2].z, r.c[2].w};
+    const uint32_t wb[12] = {r.c[3].x, r.c[3].y, r.c[3].z, r.c[3].w, r.c[4].x, r.c[4].y,
+                             r.c[4].z, r.c[4].w, r.c[5].x, r.c[5].y, r.c[5].z, r.c[5].w};
+    const uint32_t sa[4] = {r.sa.x, r.sa.y, r.sa.z, r.sa.w}, sb4[4] = {r.sb.x, r.sb.y, r.sb.z, r.sb.w};
+    float blk[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t a0w = wa[3 * c], a1w = wa[3 * c + 1], a2w = wa[3 * c + 2];
+        const uint32_t b0w = wb[3 * c], b1w = wb[3 * c + 1], b2w = wb[3 * c + 2];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t p0a, p1a, p0b, p1b;
+            if (j < 3) {
+                const uint32_t va = j == 0 ? a0w : (j == 1 ? a1w : a2w);
+                const uint32_t vb = j == 0 ? b0w : (j == 1 ? b1w : b2w);
+                p0a = and_or(va, 0x003f003fu, magic);
+                p1a = and_or(va >> 6, 0x003f003fu, magic);
+                p0b = and_or(vb, 0x003f003fu, magic);
+                p1b = and_or(vb >> 6, 0x003f003fu, magic);
+            } else {
+                p0a = and_or(a2w >> 8, 0x00300030u, and_or(a0w >> 12, 0x000f000fu, magic));
+                p1a = and_or(a2w >> 10, 0x00300030u, and_or(a1w >> 12, 0x000f000fu, magic));
+                p0b = and_or(b2w >> 8, 0x00300030u, and_or(b0w >> 12, 0x000f000fu, magic));
+                p1b = and_or(b2w >> 10, 0x00300030u, and_or(b1w >> 12, 0x000f000fu, magic));
+            }
+            const int s = 8 * (c >> 1) + 2 * j + (c & 1);
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            const BFrag b = load_bfrag<NTERMS>(bfrag, nfrag, sb * 16 + s, lane);
+            mma_terms<NTERMS>(acc, hadd2_u32(p0a, neg), hadd2_u32(p0b, neg), hadd2_u32(p1a, neg), hadd2_u32(p1b, neg),
+                              b);
+            const float fa = biased_byte_to_float(sa[s >> 2], s & 3), fb = biased_byte_to_float(sb4[s >> 2], s & 3);
+            blk[0] = fmaf(fa, acc[0], blk[0]);
+            blk[1] = fmaf(fa, acc[1], blk[1]);
+            blk[2] = fmaf(fb, acc[2], blk[2]);
+            blk[3] = fmaf(fb, acc[3], blk[3]);
+        }
+    }
+    const float da = half_bits_to_float(r.dd & 0xffffu), db = half_bits_to_float(r.dd >> 16);
+    tot[0] = fmaf(da, blk[0], tot[0]);
+    tot[1] = fmaf(da, blk[1], tot[1]);
+    tot[2] = fmaf(db, blk[2], tot[2]);
+    tot[3] = fmaf(db, blk[3], tot[3]);
+}
+
+// Activation fragments in natural order: fragment f (16 positions 16f..16f+15), lane (g, tig):
+// token g, positions 16f + 4tig + {0,2} -> b0, {1,3} -> b1; FP16 high part (+ remainder plane for
+// FP32 inputs) after a per-token power-of-two scaling. All Q6T_THREADS threads take part.
+template <int NTERMS, typename RowFn>
+__device__ __forceinline__ void prepare_fragments(RowFn row_of, int m_tokens, int k, const void *x, int x_dtype,
+                                                  uint2 *bfrag, float *tok_scale, int tid) {
+    const int warp = tid >> 5, lane = tid & 31;
+    const int nfrag = k >> 4;
+    const size_t esize = x_dtype == B200Q_F32 ? 4 : 2;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(x) % (4 * esize)) == 0;
+    unsigned int *amax_bits = reinterpret_cast<unsigned int *>(tok_scale + 16);
+    if (tid < 8) amax_bits[tid] = 0u;
+    named_barrier_sync(1, Q6T_THREADS);
+    {
+        const int chunks_per_token = k >> 2;              // k is a multiple of 256: whole warps per token
+        const int total = m_tokens * chunks_per_token;
+        for (int c0 = warp * 32; c0 < total; c0 += Q6T_THREADS) {
+            const int c = c0 + lane;
+            const int t = c0 / chunks_per_token;
+            float v[4];
+            load4(x, x_dtype, static_cast<size_t>(row_of(t)) * k + static_cast<size_t>(c - t * chunks_per_token) * 4,
+                  vec_ok, v);
+            float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+            for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            if (lane == 0) atomicMax(&amax_bits[t], __float_as_uint(amax));
+        }
+    }
+    named_barrier_sync(1, Q6T_THREADS);
+    if (tid < 8) {
+        const float amax = __uint_as_float(amax_bits[tid]);
+        float s = 1.0f;
+        if (amax > 0.f && amax < __int_as_float(0x7f800000)) {
+            int e;
+            frexpf(amax, &e);
+            s = ldexpf(1.0f, min(14 - e, 100));
+        }
+        tok_scale[tid] = s;
+        tok_scale[8 + tid] = 1.0f / s;
+    }
+    named_barrier_sync(1, Q6T_THREADS);
+    const int g = lane >> 2, tig = lane & 3;
+    const bool live = g < m_tokens;
+    const float s = tok_scale[g];
+    const size_t base = live ? static_cast<size_t>(row_of(g)) * k : 0;
+    for (int f = warp; f < nfrag; f += Q6T_WARPS) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (live) {
+            load4(x, x_dtype, base + 16 * f + 4 * tig, vec_ok, v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] *= s;
+        }
+        unsigned short hi[4], lo[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half h = __float2half_rn(v[i]);
+            hi[i] = __half_as_ushort(h);
+            lo[i] = __half_as_ushort(__float2half_rn(v[i] - __half2float(h)));
+        }
+        bfrag[f * 32 + lane] = make_uint2(hi[0] | (static_cast<uint32_t>(hi[2]) << 16),
+                                          hi[1] | (static_cast<uint32_t>(hi[3]) << 16));
+        if (NTERMS == 2)
+            bfrag[(nfrag + f) * 32 + lane] = make_uint2(lo[0] | (static_cast<uint32_t>(lo[2]) << 16),
+                                                        lo[1] | (static_cast<uint32_t>(lo[3]) << 16));
+    }
+    named_barrier_sync(1, Q6T_THREADS);
+}
+
+// MODE 0: y[m, n] = x W^T.  MODE 3: grouped down projection over the plan's segments, rows scaled
+// by the route weight. Warp (rgi, kpi) owns row group rgi of the CTA's row block and the
+// super-blocks kpi, kpi+kp, ...; the next tile is requested before the current one is computed.
+template <int MODE, int NTERMS>
+__global__ void __launch_bounds__(Q6T_THREADS, 1) q6k_tiled_kernel(const Q6TiledArgs a) {
+    constexpr bool GROUPED = (MODE == 3);
+    extern __shared__ __align__(128) uint8_t smem[];
+    float *tok_scale = reinterpret_cast<float *>(smem);           // [8] scale, [8] inverse, [8] amax bits
+    float *route_w = reinterpret_cast<float *>(smem + 128);       // [8]
+    int *seg_tokens = reinterpret_cast<int *>(smem + 192);        // [8]
+    float **out_ptr = reinterpret_cast<float **>(smem + 256);     // [8]
+    float *partial = reinterpret_cast<float *>(smem + Q6T_CTRL_BYTES);
+    uint2 *bfrag = reinterpret_cast<uint2 *>(smem + a.off_bfrag);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, tig = lane & 3;
+    const int rgi = warp / a.kp, kpi = warp - rgi * a.kp;
+    const int nsb = a.k >> 8;
+    const int nfrag = a.k >> 4;
+    const int groups_total = a.n >> 4;                     // n is a multiple of 16
+
+    const int blocks_per_unit = (groups_total + a.rg - 1) / a.rg;
+    long long units = 1;
+    if (GROUPED) {
+        int nseg = *a.num_segments;
+        if (nseg > a.max_segments) nseg = a.max_segments;
+        units = nseg;
+    }
+    const long long total_blocks = units * blocks_per_unit;
+    const long long blk_begin = total_blocks * blockIdx.x / gridDim.x;
+    const long long blk_end = total_blocks * (blockIdx.x + 1) / gridDim.x;
+    if (blk_begin >= blk_end) return;
+
+    const int items_per_block = kpi < nsb ? (nsb - kpi + a.kp - 1) / a.kp : 0;
+    auto block_base = [&](int unit, int bi) -> const uint8_t * {
+        const int expert = GROUPED ? a.seg_expert[unit] : 0;
+        const int group = min(bi * a.rg + rgi, groups_total - 1);      // clamped groups are loaded, never stored
+        return expert_matrix(a.w, a.stride, a.table, expert) +
+               (static_cast<size_t>(group) * nsb + kpi) * Q6T_TILE_BYTES;
+    };
+    const size_t item_step = static_cast<size_t>(a.kp) * Q6T_TILE_BYTES;
+
+    int unit_i = static_cast<int>(blk_begin / blocks_per_unit);
+    int bi = static_cast<int>(blk_begin - static_cast<long long>(unit_i) * blocks_per_unit);
+    const uint8_t *cur_p = block_base(unit_i, bi), *nxt_p = cur_p;
+    Q6TileRegs cur, nxt;
+    if (items_per_block > 0) load_q6_tile(nxt, cur_p, lane);
+
+    int m_tokens = a.m;
+    int seg_begin = 0, cur_unit = -1;
+    if (!GROUPED) prepare_fragments<NTERMS>([](int t) { return t; }, a.m, a.k, a.x, a.x_dtype, bfrag, tok_scale, tid);
+
+    int pbuf = 0;
+    for (long long blk = blk_begin; blk < blk_end; ++blk) {
+        const int unit = unit_i;
+        const int group0 = bi * a.rg;
+        if (++bi == blocks_per_unit) { bi = 0; ++unit_i; }
+        const bool has_next = blk + 1 < blk_end;
+        if (has_next) nxt_p = block_base(unit_i, bi);
+        if (GROUPED && unit != cur_unit) {
+            cur_unit = unit;
+            seg_begin = a.seg_begin[unit];
+            m_tokens = min(a.seg_count[unit], 8);
+            named_barrier_sync(1, Q6T_THREADS);
+            if (tid < m_tokens) {
+                const int flat = a.order[seg_begin + tid];
+                seg_tokens[tid] = seg_begin + tid;
+                route_w[tid] = a.route[flat];
+                out_ptr[tid] = term_row_pointer(static_cast<float *>(a.y), a.y_table, a.rows_per_rank, a.n,
+                                                a.flat_rows ? flat : seg_begin + tid);
+            }
+            named_barrier_sync(1, Q6T_THREADS);
+            prepare_fragments<NTERMS>([&](int t) { return seg_tokens[t]; }, m_tokens, a.k, a.x, a.x_dtype, bfrag,
+                                      tok_scale, tid);
+        }
+
+        float tot[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int item = 0; item < items_per_block; ++item) {
+            cur = nxt;
+            if (item + 1 < items_per_block) load_q6_tile(nxt, cur_p + (item + 1) * item_step, lane);
+            else if (has_next) load_q6_tile(nxt, nxt_p, lane);
+            q6_tile_mma<NTERMS>(cur, bfrag, nfrag, kpi + item * a.kp, lane, tot);
+        }
+
+        const int group = group0 + rgi;
+        if (a.kp == 1) {
+            // the warp owns its rows' whole K range: store straight from the accumulators
+            if (group < groups_total) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int orow = group * 16 + g + 8 * (i >> 1), t = 2 * tig + (i & 1);
+                    if (t < m_tokens) {
+                        const float v = tot[i] * tok_scale[8 + t];
+                        if (MODE == 0) store_from_float(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, v);
+                        else out_ptr[t][orow] = v * route_w[t];
+                    }
+                }
+            }
+        } else {
+            float *pb = partial + pbuf * Q6T_PART_FLOATS + warp * 128;
+            pb[g * 8 + 2 * tig] = tot[0];
+            pb[g * 8 + 2 * tig + 1] = tot[1];
+            pb[(g + 8) * 8 + 2 * tig] = tot[2];
+            pb[(g + 8) * 8 + 2 * tig + 1] = tot[3];
+            const int group_threads = a.kp * 32;
+            named_barrier_sync(2 + rgi, group_threads);            // kp >= 2: at most 8 row groups, ids 2..9
+            for (int o = kpi * 32 + lane; o < 128; o += group_threads) {
+                const int r = o >> 3, t = o & 7;
+                if (group >= groups_total || t >= m_tokens) continue;
+                const float *src = partial + pbuf * Q6T_PART_FLOATS + (rgi * a.kp) * 128 + r * 8 + t;
+                float v = 0.f;
+                for (int kq = 0; kq < a.kp; ++kq) v += src[kq * 128];
+                v *= tok_scale[8 + t];
+                const int orow = group * 16 + r;
+                if (MODE == 0) store_from_float(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, v);
+                else out_ptr[t][orow] = v * route_w[t];
+            }
+            pbuf ^= 1;
+        }
+        cur_p = nxt_p;
+    }
+}
+
+}  // namespace b200q

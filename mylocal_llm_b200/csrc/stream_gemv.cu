@@ -110,6 +110,22 @@ extern "C" {
 int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype, int m, void *y, int y_dtype,
                void *stream) {
     if (!w || !x || !y) return fail(B200Q_EINVAL, "gemv: NULL pointer");
+    if (fmt == B200Q_Q6_K_TILED) {
+        if (!dtype_valid(x_dtype) || !dtype_valid(y_dtype)) return fail(B200Q_EINVAL, "gemv: bad dtype");
+        if (n <= 0 || m <= 0 || k <= 0) return fail(B200Q_EINVAL, "gemv: bad shape n=%d k=%d m=%d", n, k, m);
+        for (int t0 = 0; t0 < m; t0 += 8) {
+            MmaRequest q{};
+            q.mode = 0; q.wa = static_cast<const uint8_t *>(w); q.fmt_a = q.fmt_b = fmt; q.n = n; q.k = k;
+            q.m = (m - t0 < 8) ? m - t0 : 8;
+            q.x = static_cast<const uint8_t *>(x) + static_cast<size_t>(t0) * k * dtype_size(x_dtype);
+            q.x_dtype = x_dtype;
+            q.y = static_cast<uint8_t *>(y) + static_cast<size_t>(t0) * n * dtype_size(y_dtype);
+            q.y_dtype = y_dtype;
+            int rc = q6k_tiled_launch(q, static_cast<cudaStream_t>(stream));
+            if (rc) return rc;
+        }
+        return B200Q_OK;
+    }
     if (!fmt_valid(fmt)) return fail(B200Q_EINVAL, "gemv: unknown format %d", fmt);
     if (!dtype_valid(x_dtype) || !dtype_valid(y_dtype)) return fail(B200Q_EINVAL, "gemv: bad dtype");
     if (n <= 0 || m <= 0 || !k_ok(fmt, k)) return fail(B200Q_EINVAL, "gemv: bad shape n=%d k=%d m=%d", n, k, m);
@@ -285,6 +301,18 @@ static int moe_down_impl(const void *down_base, int64_t down_stride, int down_fm
         !num_segments || (!terms && !y_table))
         return fail(B200Q_EINVAL, "moe_down: NULL pointer");
     if (y_table && rows_per_rank < 1) return fail(B200Q_EINVAL, "moe_down: rows_per_rank must be positive");
+    if (down_fmt == B200Q_Q6_K_TILED) {
+        if (d <= 0 || f <= 0 || max_segments <= 0) return fail(B200Q_EINVAL, "moe_down: bad shape d=%d f=%d", d, f);
+        MmaRequest q{};
+        q.mode = 3; q.wa = static_cast<const uint8_t *>(down_base); q.fmt_a = q.fmt_b = down_fmt;
+        q.stride_a = down_stride; q.table_a = reinterpret_cast<const unsigned long long *>(down_table);
+        q.tables_aligned16 = tables_aligned16; q.n = d; q.k = f; q.m = MAX_TOKENS; q.x = hbuf; q.x_dtype = B200Q_F32;
+        q.y = terms; q.y_dtype = B200Q_F32; q.topk = 1; q.order = order; q.seg_expert = seg_expert;
+        q.seg_begin = seg_begin; q.seg_count = seg_count; q.num_segments = num_segments; q.max_segments = max_segments;
+        q.route = route; q.flat_rows = (flat_rows || y_table) ? 1 : 0; q.y_table = y_table;
+        q.rows_per_rank = rows_per_rank;
+        return q6k_tiled_launch(q, static_cast<cudaStream_t>(stream));
+    }
     if (!fmt_valid(down_fmt)) return fail(B200Q_EINVAL, "moe_down: bad format");
     if (d <= 0 || max_segments <= 0 || !k_ok(down_fmt, f)) return fail(B200Q_EINVAL, "moe_down: bad shape d=%d f=%d", d, f);
     int *status = device_status_word();

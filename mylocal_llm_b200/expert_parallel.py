@@ -219,7 +219,12 @@ class DeviceExpertEngine:
 
     def __init__(self, bank, router_weight, top_k, *, first_expert, n_experts_global, shared=None, shared_gate=None,
                  normalization_floor=2.0 ** -14):
+        from .quantized_linear import retile_enabled, retile_weight
         from .router_inference import RouterInference
+        if retile_enabled():
+            bank = bank.retiled()
+            if shared is not None:
+                shared = (shared[0], shared[1], retile_weight(shared[2]))
         self.bank = bank
         self.first_expert, self.n_global = int(first_expert), int(n_experts_global)
         self.router = RouterInference(bank.d_model, self.n_global, top_k, renormalize_selected=True,

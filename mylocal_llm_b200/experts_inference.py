@@ -20,7 +20,7 @@ import numpy as np
 
 from . import moe_ops
 from .quantized_linear import DevicePackedGGUFWeight, PackedExpertFFNInference, packed_bytes_to_device
-from .quantized_weight import BLOCK_FORMATS, PackedGGUFWeight, packed_nbytes
+from .quantized_weight import BLOCK_FORMATS, DEVICE_LAYOUTS, PackedGGUFWeight, packed_nbytes
 
 
 def _torch():
@@ -50,7 +50,7 @@ class PackedExpertBank:
         for name, fmt, shape in (("gate", self.gate_type, (self.d_ff, self.d_model)),
                                  ("up", self.up_type, (self.d_ff, self.d_model)),
                                  ("down", self.down_type, (self.d_model, self.d_ff))):
-            if fmt not in BLOCK_FORMATS:
+            if fmt not in BLOCK_FORMATS and not (name == "down" and fmt in DEVICE_LAYOUTS):
                 raise ValueError(f"Unsupported packed GGUF type: {fmt}")
             data = getattr(self, name)
             expect = self.n_experts * packed_nbytes(shape, fmt)
@@ -84,6 +84,16 @@ class PackedExpertBank:
             raise ValueError("expert bank shapes must be gate/up [E,F,D], down [E,D,F]")
         return cls(packed_bytes_to_device(gate.data), packed_bytes_to_device(up.data),
                    packed_bytes_to_device(down.data), gate.quant_type, up.quant_type, down.quant_type, e, d, f)
+
+    def retiled(self):
+        """Bank whose Q6_K down projections are in the tile layout (a new down tensor; gate and up
+        are shared). Other down types, and d_model not a multiple of 16, return the bank itself."""
+        from .quantized_linear import TILED_MAX_K, retile_q6k
+        if self.down_type != "Q6_K" or self.d_model % 16 or self.d_ff > TILED_MAX_K:
+            return self
+        down = retile_q6k(self.down, self.n_experts * self.d_model, self.d_ff)
+        return PackedExpertBank(self.gate, self.up, down, self.gate_type, self.up_type, "Q6_K_TILED",
+                                self.n_experts, self.d_model, self.d_ff)
 
     def pointer_tables(self, extra=None):
         """Device pointer tables (three int64 tensors with one address per expert) and whether every

@@ -19,7 +19,8 @@ import ctypes
 
 from . import _lib, moe_ops
 from .experts_inference import ExpertsInference, PackedExpertBank, ResidentExpertExecutor
-from .quantized_linear import DevicePackedGGUFWeight, quantized_linear, quantized_swiglu
+from .quantized_linear import (DevicePackedGGUFWeight, quantized_linear, quantized_swiglu, retile_enabled,
+                               retile_weight)
 from .router_inference import RouterInference
 
 
@@ -105,6 +106,11 @@ class PackedMoELayer:
         (gate, up, down) DevicePackedGGUFWeight triple; shared_gate: optional FP32 [D] vector."""
         if not isinstance(bank, PackedExpertBank):
             raise TypeError("bank must be a PackedExpertBank")
+        if retile_enabled() and executor is None:
+            # Q6_K down projections are re-ordered once into the tile layout the fast kernel reads
+            bank = bank.retiled()
+            if shared is not None and len(shared) == 3 and isinstance(shared[2], DevicePackedGGUFWeight):
+                shared = (shared[0], shared[1], retile_weight(shared[2]))
         self.bank = bank
         self.layer_id = int(layer_id)
         self.router = RouterInference(bank.d_model, bank.n_experts, top_k, renormalize_selected=True,

@@ -22,9 +22,9 @@ import math
 import numpy as np
 
 from . import _lib
-from .quantized_weight import BLOCK_FORMATS, PackedGGUFWeight
+from .quantized_weight import BLOCK_FORMATS, DEVICE_LAYOUTS, PackedGGUFWeight, block_format
 
-SUPPORTED_GPU_PACKED_FORMATS = frozenset(_lib.FORMAT_ID)
+SUPPORTED_GPU_PACKED_FORMATS = frozenset(name for name in _lib.FORMAT_ID if name in BLOCK_FORMATS)
 _BLOCK_K = (256, 512, 1024)
 
 
@@ -63,9 +63,9 @@ class DevicePackedGGUFWeight:
     quant_type: str
 
     def __post_init__(self):
-        if self.quant_type not in BLOCK_FORMATS:
+        if self.quant_type not in BLOCK_FORMATS and self.quant_type not in DEVICE_LAYOUTS:
             raise ValueError(f"Unsupported GGUF type {self.quant_type}")
-        if not supports_packed_gpu_type(self.quant_type):
+        if self.quant_type not in _lib.FORMAT_ID:
             raise NotImplementedError(f"No packed GPU kernel for {self.quant_type}")
         torch = _torch()
         if not isinstance(self.data, torch.Tensor) or self.data.dtype != torch.uint8 or not self.data.is_cuda:
@@ -75,7 +75,7 @@ class DevicePackedGGUFWeight:
         shape = tuple(int(i) for i in self.shape)
         if len(shape) != 2 or min(shape) <= 0:
             raise ValueError("Device packed linear weights must be [N, K]")
-        qk, qb = BLOCK_FORMATS[self.quant_type]
+        qk, qb = block_format(self.quant_type)
         if shape[-1] % qk or int(self.data.numel()) != math.prod(shape) // qk * qb:
             raise ValueError("Invalid packed byte length or K block alignment")
         object.__setattr__(self, "shape", shape)
@@ -102,9 +102,49 @@ def packed_to_device(weight):
     return DevicePackedGGUFWeight(packed_bytes_to_device(weight.data), weight.shape, weight.quant_type)
 
 
+# The tiled kernel keeps the activation fragments of the whole K range in shared memory (two FP16
+# planes for FP32 activations): 4096 is the largest K that fits for every activation type.
+TILED_MAX_K = 4096
+
+
+def retile_enabled():
+    """Whether uploads of Q6_K down projections are re-ordered into the tile layout (default on;
+    ``B200Q_RETILE=0`` keeps the native GGUF bytes and the kernels that read them)."""
+    import os
+    return os.environ.get("B200Q_RETILE", "1") != "0"
+
+
+def retile_q6k(data, rows, k):
+    """Native Q6_K bytes of a ``[rows, k]`` matrix (or a bank of experts, ``rows`` = all rows) ->
+    new tensor in the 16-row tile layout (same size; lossless, see ``untile_q6k``)."""
+    torch = _torch()
+    out = torch.empty_like(data)
+    _lib.call("b200q_q6k_retile", _ptr(data), _ptr(out), int(rows), int(k), _lib.current_stream())
+    return out
+
+
+def untile_q6k(data, rows, k):
+    """Inverse of ``retile_q6k``: restores the GGUF bytes bit for bit."""
+    torch = _torch()
+    out = torch.empty_like(data)
+    _lib.call("b200q_q6k_untile", _ptr(data), _ptr(out), int(rows), int(k), _lib.current_stream())
+    return out
+
+
+def retile_weight(weight):
+    """``DevicePackedGGUFWeight`` in the tile layout when its type has one and the shape allows it
+    (Q6_K, rows a multiple of 16, K <= TILED_MAX_K); otherwise the weight itself."""
+    if weight.quant_type != "Q6_K" or weight.shape[0] % 16 or weight.shape[1] > TILED_MAX_K:
+        return weight
+    return DevicePackedGGUFWeight(retile_q6k(weight.data, weight.shape[0], weight.shape[1]), weight.shape,
+                                  "Q6_K_TILED")
+
+
 def dequantize_device(data, rows, k, quant_type):
     """FP32 ``[rows, k]`` CUDA tensor decoded from packed device bytes (verification helper)."""
     torch = _torch()
+    if quant_type in DEVICE_LAYOUTS:
+        data, quant_type = untile_q6k(data, rows, k), DEVICE_LAYOUTS[quant_type]
     out = torch.empty((rows, k), dtype=torch.float32, device=data.device)
     _lib.call("b200q_dequantize", _ptr(data), _lib.FORMAT_ID[quant_type], rows, k, _ptr(out),
               _lib.current_stream())

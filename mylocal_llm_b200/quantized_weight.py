@@ -22,8 +22,18 @@ BLOCK_FORMATS = {
 }
 
 
+# Device-only layouts: a lossless re-ordering of a GGUF type's bytes (same size) that only the GPU
+# kernels read; host-side PackedGGUFWeight never carries them.
+DEVICE_LAYOUTS = {"Q6_K_TILED": "Q6_K"}
+
+
+def block_format(quant_type):
+    """(values per block, bytes per block) of a GGUF type or of a device layout of it."""
+    return BLOCK_FORMATS[DEVICE_LAYOUTS.get(quant_type, quant_type)]
+
+
 def packed_nbytes(shape, quant_type):
-    qk, qb = BLOCK_FORMATS[quant_type]
+    qk, qb = block_format(quant_type)
     return math.prod(int(d) for d in shape) // qk * qb
 
 

@@ -29,6 +29,7 @@ TYPES = ("Q4_K", "Q4_K", "Q6_K")
 @pytest.fixture(autouse=True, params=["tensor", "lanes"])
 def kernel_family(request, monkeypatch):
     monkeypatch.setenv("B200Q_KERNEL", {"tensor": "auto", "lanes": "lanes"}[request.param])
+    monkeypatch.setenv("B200Q_RETILE", "1" if request.param == "tensor" else "0")
     return request.param
 
 
@@ -170,6 +171,7 @@ def _rank_main(rank, world, port, family, queue):
     import torch
     import torch.distributed as dist
     os.environ["B200Q_KERNEL"] = family
+    os.environ["B200Q_RETILE"] = "1" if family == "auto" else "0"
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,

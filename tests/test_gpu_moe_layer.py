@@ -13,9 +13,12 @@ from mylocal_llm_b200.quantize import quantize
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=["tensor", "lanes"])
+@pytest.fixture(autouse=True, params=["tensor", "staged", "lanes"])
 def kernel_family(request, monkeypatch):
-    monkeypatch.setenv("B200Q_KERNEL", {"tensor": "auto", "lanes": "lanes"}[request.param])
+    """"tensor": default kernel selection with Q6_K down projections in the tile layout; "staged" and
+    "lanes": native GGUF bytes through the staged tensor-core and the FP32-lane kernels."""
+    monkeypatch.setenv("B200Q_KERNEL", {"tensor": "auto", "staged": "staged", "lanes": "lanes"}[request.param])
+    monkeypatch.setenv("B200Q_RETILE", "1" if request.param == "tensor" else "0")
     return request.param
 
 
