@@ -1,5 +1,5 @@
 // Decode-oriented router kernels: logits from an [E, D] weight (one warp per expert row), and
-// softmax + top-k with one warp per token row. Semantics as in aux_kernels.cu / the reference
+// softmax + top-k with one four-warp CTA per token row. Semantics as in aux_kernels.cu / the reference
 // (mini_llm/ops/router_decode.py:16-96): descending logit, ties -> lower id, NaN last,
 // p = exp(v - max) / sum, optional division by max(selected mass, floor).
 #include "common.cuh"
@@ -60,76 +60,6 @@ __global__ void __launch_bounds__(256) router_logits_t_kernel(const void *x, int
                 if (lane == 0) logits[static_cast<size_t>(t0 + tt) * e + row] = s + (bias ? bias[row] : 0.f);
             }
         }
-    }
-}
-
-__device__ __forceinline__ bool better_route(float a, int ia, float b, int ib, int n) {
-    if (ia == n) return false;
-    if (ib == n) return true;
-    if (isnan(a)) return isnan(b) && ia < ib;
-    if (isnan(b)) return true;
-    return a > b || (a == b && ia < ib);
-}
-
-// One warp per row, n <= 1024 (32 values per lane in registers). Output rows have
-// k_out = k + (extra_id >= 0) entries; the appended entry is (extra_id, extra_weight[row] or 1).
-__global__ void __launch_bounds__(128) router_topk_warp_kernel(const float *logits, int rows, int n, int k, int renorm,
-                                                               float floor_value, int extra_id,
-                                                               const float *extra_weight, float *weights,
-                                                               int64_t *ids) {
-    const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (row >= rows) return;
-    const float neg_inf = __int_as_float(0xff800000), qnan = __int_as_float(0x7fc00000);
-    const float *src = logits + static_cast<size_t>(row) * n;
-    float v[32];
-    unsigned used = 0u;
-    float mx = neg_inf;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        const int idx = i * 32 + lane;
-        v[i] = idx < n ? src[idx] : neg_inf;
-        if (idx < n) mx = (isnan(v[i]) || isnan(mx)) ? qnan : fmaxf(mx, v[i]);
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) {
-        const float other = __shfl_xor_sync(0xffffffffu, mx, o);
-        mx = (isnan(mx) || isnan(other)) ? qnan : fmaxf(mx, other);
-    }
-    float den = 0.f;
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-        if (i * 32 + lane < n) den += expf(v[i] - mx);
-    den = warp_sum(den);
-    const int k_out = k + (extra_id >= 0 ? 1 : 0);
-    float mass = 0.f;
-    float mine = 0.f;            // lane s keeps the probability of slot s
-    for (int slot = 0; slot < k; ++slot) {
-        float best = neg_inf;
-        int bi = n;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const int idx = i * 32 + lane;
-            if (idx < n && !((used >> i) & 1u) && better_route(v[i], idx, best, bi, n)) { best = v[i]; bi = idx; }
-        }
-#pragma unroll
-        for (int o = 16; o; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (better_route(ov, oi, best, bi, n)) { best = ov; bi = oi; }
-        }
-        if ((bi & 31) == lane && bi < n) used |= 1u << (bi >> 5);
-        const float p = __fdiv_rn(expf(best - mx), den);
-        mass = __fadd_rn(mass, p);             // sequential in slot order, identical on every lane
-        if (lane == slot) mine = p;
-        if (lane == 0) ids[static_cast<size_t>(row) * k_out + slot] = bi;
-    }
-    float norm = 1.0f;
-    if (renorm) norm = isnan(mass) ? mass : fmaxf(mass, floor_value);
-    if (lane < k) weights[static_cast<size_t>(row) * k_out + lane] = renorm ? __fdiv_rn(mine, norm) : mine;
-    if (extra_id >= 0 && lane == 0) {
-        ids[static_cast<size_t>(row) * k_out + k] = extra_id;
-        weights[static_cast<size_t>(row) * k_out + k] = extra_weight ? extra_weight[row] : 1.0f;
     }
 }
 
@@ -209,10 +139,110 @@ int launch_combine_cols(const float *terms, const int32_t *inv, int rows, int k,
     return check_launch("moe_combine");
 }
 
+// One CTA of four warps per row, n <= 1024 (eight values per thread, value idx = i*128 + tid).
+// Every value becomes a 64-bit key that orders like the selection rule: high word = the float's
+// bits made monotonic (NaN -> 0, below -inf; -0 counted as +0), low word = ~index, so the largest
+// key is the largest logit and, among equals, the lowest index. A round is then two warp-wide
+// integer maximum reductions plus one exchange between the four warps.
+__device__ __forceinline__ uint32_t orderable_bits(float v) {
+    if (isnan(v)) return 0u;
+    const uint32_t b = __float_as_uint(v + 0.0f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float from_orderable_bits(uint32_t h) {
+    if (h == 0u) return __int_as_float(0x7fc00000);
+    return __uint_as_float((h & 0x80000000u) ? (h & 0x7fffffffu) : ~h);
+}
+
+__global__ void __launch_bounds__(128) router_topk_block_kernel(const float *logits, int n, int k, int renorm,
+                                                                float floor_value, int extra_id,
+                                                                const float *extra_weight, float *weights,
+                                                                int64_t *ids) {
+    __shared__ unsigned long long warp_best[2][4];
+    __shared__ float red[4];
+    __shared__ float sel_p[32];
+    __shared__ int sel_i[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row = blockIdx.x;
+    const float neg_inf = __int_as_float(0xff800000), qnan = __int_as_float(0x7fc00000);
+    const float *src = logits + static_cast<size_t>(row) * n;
+    float v[8];
+    uint32_t hi[8];
+    float mx = neg_inf;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int idx = i * 128 + tid;
+        v[i] = idx < n ? src[idx] : neg_inf;
+        hi[i] = idx < n ? orderable_bits(v[i]) : 0u;
+        if (idx < n) mx = (isnan(v[i]) || isnan(mx)) ? qnan : fmaxf(mx, v[i]);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, mx, o);
+        mx = (isnan(mx) || isnan(other)) ? qnan : fmaxf(mx, other);
+    }
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = red[0];
+#pragma unroll
+    for (int w = 1; w < 4; ++w) mx = (isnan(mx) || isnan(red[w])) ? qnan : fmaxf(mx, red[w]);
+    __syncthreads();
+    float den = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (i * 128 + tid < n) den += expf(v[i] - mx);
+    den = warp_sum(den);
+    if (lane == 0) red[warp] = den;
+    __syncthreads();
+    den = ((red[0] + red[1]) + red[2]) + red[3];
+
+    for (int slot = 0; slot < k; ++slot) {
+        // best key of this thread among its values that are inside the row and not yet taken
+        uint32_t bh = 0u, bl = 0u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t lo = ~static_cast<uint32_t>(i * 128 + tid);
+            const bool take = (i * 128 + tid < n) && (hi[i] > bh || (hi[i] == bh && lo > bl)) && hi[i] != 0xffffffffu;
+            if (take) { bh = hi[i]; bl = lo; }
+        }
+        const uint32_t wh = __reduce_max_sync(0xffffffffu, bh);
+        const uint32_t wl = __reduce_max_sync(0xffffffffu, bh == wh ? bl : 0u);
+        if (lane == 0) warp_best[slot & 1][warp] = (static_cast<unsigned long long>(wh) << 32) | wl;
+        __syncthreads();
+        unsigned long long best = warp_best[slot & 1][0];
+#pragma unroll
+        for (int w = 1; w < 4; ++w) best = max(best, warp_best[slot & 1][w]);
+        const int bi = static_cast<int>(~static_cast<uint32_t>(best));
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (i * 128 + tid == bi) hi[i] = 0xffffffffu;          // marks "taken" (never a real key)
+        if (tid == 0) {
+            sel_p[slot] = __fdiv_rn(expf(from_orderable_bits(static_cast<uint32_t>(best >> 32)) - mx), den);
+            sel_i[slot] = bi;
+        }
+    }
+    __syncthreads();
+    const int k_out = k + (extra_id >= 0 ? 1 : 0);
+    float norm = 1.0f;
+    if (renorm) {
+        float mass = 0.f;
+        for (int s = 0; s < k; ++s) mass = __fadd_rn(mass, sel_p[s]);      // slot order, same on every thread
+        norm = isnan(mass) ? mass : fmaxf(mass, floor_value);
+    }
+    if (tid < k) {
+        weights[static_cast<size_t>(row) * k_out + tid] = renorm ? __fdiv_rn(sel_p[tid], norm) : sel_p[tid];
+        ids[static_cast<size_t>(row) * k_out + tid] = sel_i[tid];
+    }
+    if (extra_id >= 0 && tid == 0) {
+        ids[static_cast<size_t>(row) * k_out + k] = extra_id;
+        weights[static_cast<size_t>(row) * k_out + k] = extra_weight ? extra_weight[row] : 1.0f;
+    }
+}
+
 int launch_topk_warp(const float *logits, int rows, int n, int k, int renorm, float floor_value, int extra_id,
                      const float *extra_weight, float *weights, int64_t *ids, cudaStream_t stream) {
-    router_topk_warp_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(logits, rows, n, k, renorm, floor_value, extra_id,
-                                                                extra_weight, weights, ids);
+    router_topk_block_kernel<<<rows, 128, 0, stream>>>(logits, n, k, renorm, floor_value, extra_id, extra_weight,
+                                                       weights, ids);
     return check_launch("router_topk");
 }
 
