@@ -172,10 +172,16 @@ __device__ __forceinline__ void load4(const void *x, int x_dtype, size_t e, bool
     }
 }
 
-template <int NTERMS, typename RowFn>
+// Every thread owns whole chunks of four consecutive activations (chunk c of token t covers
+// positions 4c..4c+3, which is exactly one fragment entry): one pass loads them and finds the
+// per-token maximum, the second converts from registers (chunks beyond KEEP per thread are
+// loaded again). Entries of tokens >= m_tokens are left as they are: a column of B only feeds the
+// same column of the product, and those columns are never stored.
+
+template <int NTERMS, int KEEP, typename RowFn>
 __device__ __forceinline__ void prepare_direct(RowFn row_of, int m_tokens, int k, const void *x, int x_dtype,
                                                uint2 *bfrag, uint32_t *xsfrag, float *tok_scale, int tid) {
-    const int warp = tid >> 5, lane = tid & 31;
+    const int lane = tid & 31;
     const int nsb = k >> 8;
     const int nfrag = nsb * 16;
     const size_t esize = x_dtype == B200Q_F32 ? 4 : 2;
@@ -183,21 +189,27 @@ __device__ __forceinline__ void prepare_direct(RowFn row_of, int m_tokens, int k
     unsigned int *amax_bits = reinterpret_cast<unsigned int *>(tok_scale + 16);   // [8], non-negative floats as ints
     if (tid < 8) amax_bits[tid] = 0u;
     named_barrier_sync(1, MD_THREADS);
-    // 1. per-token maximum magnitude, all threads: a warp's 32 chunks of 4 belong to one token
-    {
-        const int chunks_per_token = k >> 2;
-        const int total = m_tokens * chunks_per_token;
-        for (int c0 = warp * 32; c0 < total; c0 += MD_THREADS) {
-            const int c = c0 + lane;
-            const int t = c0 / chunks_per_token;
-            float v[4];
-            load4(x, x_dtype, static_cast<size_t>(row_of(t)) * k + static_cast<size_t>(c - t * chunks_per_token) * 4, vec_ok, v);
-            float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    const int chunks_per_token = k >> 2;            // a multiple of 64: a warp's 32 chunks share one token
+    const int total = m_tokens * chunks_per_token;
+    float kept[KEEP][4];
+    const int first = tid & ~31;
+    // 1. load, per-token maximum magnitude
+    auto load_chunk = [&](int c0, float (&v)[4]) {
+        const int t = c0 / chunks_per_token;
+        load4(x, x_dtype, static_cast<size_t>(row_of(t)) * k + static_cast<size_t>(c0 + lane - t * chunks_per_token) * 4,
+              vec_ok, v);
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
-            for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            // NaN/Inf inputs: keep the scale at 1 (the bit pattern compares above every finite value)
-            if (lane == 0) atomicMax(&amax_bits[t], __float_as_uint(amax));
-        }
+        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        // NaN/Inf inputs: keep the scale at 1 (the bit pattern compares above every finite value)
+        if (lane == 0) atomicMax(&amax_bits[t], __float_as_uint(amax));
+    };
+#pragma unroll
+    for (int sl = 0; sl < KEEP; ++sl)
+        if (first + sl * MD_THREADS < total) load_chunk(first + sl * MD_THREADS, kept[sl]);
+    for (int c0 = first + KEEP * MD_THREADS; c0 < total; c0 += MD_THREADS) {
+        float v[4];
+        load_chunk(c0, v);
     }
     named_barrier_sync(1, MD_THREADS);
     if (tid < 8) {
@@ -212,58 +224,60 @@ __device__ __forceinline__ void prepare_direct(RowFn row_of, int m_tokens, int k
         tok_scale[8 + tid] = 1.0f / s;
     }
     named_barrier_sync(1, MD_THREADS);
-    // 2. fragments: a warp builds the four fragments of one (super-block, span, nibble plane) at a time
-    const int g = lane >> 2, tig = lane & 3;
-    const bool live = g < m_tokens;
-    const float s = tok_scale[g];
-    const size_t base = live ? static_cast<size_t>(row_of(g)) * k : 0;
-    for (int grp = warp; grp < nsb * 4; grp += MD_WARPS) {
-        const int sb = grp >> 2, X = (grp >> 1) & 1, nib = grp & 1;
-        const int sub = 4 * X + 2 * (tig >> 1) + nib;
+    // 2. scale, split, store: the chunk at position p of token t is fragment entry (f, lane 4t+tig) with
+    //    sb = p>>8, sub = (p>>5)&7, X = sub>>2, nib = sub&1, tig = 2*((sub>>1)&1) + ((p>>4)&1), j = (p>>2)&3
+    auto store_chunk = [&](int c0, const float (&v)[4]) {
+        const int t = c0 / chunks_per_token;
+        const int p = (c0 + lane - t * chunks_per_token) * 4;
+        const float s = tok_scale[t];
+        __half hi[4], lo[4];
         float sum = 0.f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int k0 = 256 * sb + 32 * sub + 16 * (tig & 1) + 4 * j;
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (live) {
-                load4(x, x_dtype, base + k0, vec_ok, v);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) v[i] *= s;
-            }
-            __half hi[4], lo[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                hi[i] = __float2half_rn(v[i]);
-                sum += __half2float(hi[i]);
-                if (NTERMS == 2) {
-                    lo[i] = __float2half_rn(v[i] - __half2float(hi[i]));
-                    sum += __half2float(lo[i]);
-                }
-            }
-            const int f = sb * 16 + (X * 2 + nib) * 4 + j;
-            uint2 out;
-            out.x = static_cast<uint32_t>(__half_as_ushort(hi[0])) | (static_cast<uint32_t>(__half_as_ushort(hi[2])) << 16);
-            out.y = static_cast<uint32_t>(__half_as_ushort(hi[1])) | (static_cast<uint32_t>(__half_as_ushort(hi[3])) << 16);
-            bfrag[f * 32 + lane] = out;
+        for (int i = 0; i < 4; ++i) {
+            const float sv = v[i] * s;
+            hi[i] = __float2half_rn(sv);
+            sum += __half2float(hi[i]);
             if (NTERMS == 2) {
-                out.x = static_cast<uint32_t>(__half_as_ushort(lo[0])) | (static_cast<uint32_t>(__half_as_ushort(lo[2])) << 16);
-                out.y = static_cast<uint32_t>(__half_as_ushort(lo[1])) | (static_cast<uint32_t>(__half_as_ushort(lo[3])) << 16);
-                bfrag[(nfrag + f) * 32 + lane] = out;
+                lo[i] = __float2half_rn(sv - __half2float(hi[i]));
+                sum += __half2float(lo[i]);
             }
         }
-        // the other 16 positions of the sub-block sit in the neighbouring lane
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        const float scaled = sum * MD_XS_SCALE;
-        const __half h = __float2half_rn(scaled);
-        const __half l = __float2half_rn(scaled - __half2float(h));
-        // operand of the min product: lane tig_t = (tig>>1) + 2*X holds sub-blocks (2*tig_t, 2*tig_t+1)
-        if ((tig & 1) == 0) {
-            const int lane_t = 4 * g + (tig >> 1) + 2 * X;
-            unsigned short *ph = reinterpret_cast<unsigned short *>(xsfrag + (sb * 2 + 0) * 32 + lane_t);
-            unsigned short *pl = reinterpret_cast<unsigned short *>(xsfrag + (sb * 2 + 1) * 32 + lane_t);
-            ph[nib] = __half_as_ushort(h);
-            pl[nib] = __half_as_ushort(l);
+        const int sb = p >> 8, sub = (p >> 5) & 7;
+        const int X = sub >> 2, nib = sub & 1, tig = 2 * ((sub >> 1) & 1) + ((p >> 4) & 1), j = (p >> 2) & 3;
+        const int f = sb * 16 + (X * 2 + nib) * 4 + j;
+        const int dst = 4 * t + tig;
+        uint2 out;
+        out.x = static_cast<uint32_t>(__half_as_ushort(hi[0])) | (static_cast<uint32_t>(__half_as_ushort(hi[2])) << 16);
+        out.y = static_cast<uint32_t>(__half_as_ushort(hi[1])) | (static_cast<uint32_t>(__half_as_ushort(hi[3])) << 16);
+        bfrag[f * 32 + dst] = out;
+        if (NTERMS == 2) {
+            out.x = static_cast<uint32_t>(__half_as_ushort(lo[0])) | (static_cast<uint32_t>(__half_as_ushort(lo[2])) << 16);
+            out.y = static_cast<uint32_t>(__half_as_ushort(lo[1])) | (static_cast<uint32_t>(__half_as_ushort(lo[3])) << 16);
+            bfrag[(nfrag + f) * 32 + dst] = out;
         }
+        // sub-block sum: its eight chunks sit in eight consecutive lanes
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        if ((lane & 7) == 0) {
+            const float scaled = sum * MD_XS_SCALE;
+            const __half h = __float2half_rn(scaled);
+            const __half l = __float2half_rn(scaled - __half2float(h));
+            // operand of the min product: lane 4*t + (sub>>1) holds sub-blocks (sub & ~1, sub | 1)
+            const int lane_t = 4 * t + (sub >> 1);
+            reinterpret_cast<unsigned short *>(xsfrag + (sb * 2 + 0) * 32 + lane_t)[nib] = __half_as_ushort(h);
+            reinterpret_cast<unsigned short *>(xsfrag + (sb * 2 + 1) * 32 + lane_t)[nib] = __half_as_ushort(l);
+        }
+    };
+#pragma unroll
+    for (int sl = 0; sl < KEEP; ++sl)
+        if (first + sl * MD_THREADS < total) store_chunk(first + sl * MD_THREADS, kept[sl]);
+    for (int c0 = first + KEEP * MD_THREADS; c0 < total; c0 += MD_THREADS) {
+        const int t = c0 / chunks_per_token;
+        float v[4];
+        load4(x, x_dtype, static_cast<size_t>(row_of(t)) * k + static_cast<size_t>(c0 + lane - t * chunks_per_token) * 4,
+              vec_ok, v);
+        store_chunk(c0, v);
     }
     named_barrier_sync(1, MD_THREADS);
 }
@@ -402,7 +416,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
     int m_tokens = a.m;
     int seg_begin = 0, cur_unit = -1, last_single = -1;
     if (!GROUPED)
-        prepare_direct<NTERMS>([](int t) { return t; }, a.m, a.k, a.x, a.x_dtype, bfrag, xsfrag, tok_scale, tid);
+        prepare_direct<NTERMS, 4>([](int t) { return t; }, a.m, a.k, a.x, a.x_dtype, bfrag, xsfrag, tok_scale, tid);
 
     int pbuf = 0;
     for (long long blk = blk_begin; blk < blk_end; ++blk) {
@@ -431,7 +445,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
                     }
                 }
                 named_barrier_sync(1, MD_THREADS);
-                prepare_direct<NTERMS>([&](int t) { return seg_tokens[t]; }, m_tokens, a.k, a.x, a.x_dtype, bfrag,
+                prepare_direct<NTERMS, 2>([&](int t) { return seg_tokens[t]; }, m_tokens, a.k, a.x, a.x_dtype, bfrag,
                                        xsfrag, tok_scale, tid);
             }
         }

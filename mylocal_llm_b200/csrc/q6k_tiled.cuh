@@ -184,30 +184,39 @@ __device__ __forceinline__ void q6_tile_mma(const Q6TileRegs &r, const uint2 *bf
 // Activation fragments in natural order: fragment f (16 positions 16f..16f+15), lane (g, tig):
 // token g, positions 16f + 4tig + {0,2} -> b0, {1,3} -> b1; FP16 high part (+ remainder plane for
 // FP32 inputs) after a per-token power-of-two scaling. All Q6T_THREADS threads take part.
-template <int NTERMS, typename RowFn>
+template <int NTERMS, int KEEP, typename RowFn>
 __device__ __forceinline__ void prepare_fragments(RowFn row_of, int m_tokens, int k, const void *x, int x_dtype,
                                                   uint2 *bfrag, float *tok_scale, int tid) {
-    const int warp = tid >> 5, lane = tid & 31;
+    const int lane = tid & 31;
     const int nfrag = k >> 4;
     const size_t esize = x_dtype == B200Q_F32 ? 4 : 2;
     const bool vec_ok = (reinterpret_cast<uintptr_t>(x) % (4 * esize)) == 0;
     unsigned int *amax_bits = reinterpret_cast<unsigned int *>(tok_scale + 16);
     if (tid < 8) amax_bits[tid] = 0u;
     named_barrier_sync(1, Q6T_THREADS);
-    {
-        const int chunks_per_token = k >> 2;              // k is a multiple of 256: whole warps per token
-        const int total = m_tokens * chunks_per_token;
-        for (int c0 = warp * 32; c0 < total; c0 += Q6T_THREADS) {
-            const int c = c0 + lane;
-            const int t = c0 / chunks_per_token;
-            float v[4];
-            load4(x, x_dtype, static_cast<size_t>(row_of(t)) * k + static_cast<size_t>(c - t * chunks_per_token) * 4,
-                  vec_ok, v);
-            float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    // Every thread owns whole chunks of four consecutive activations (= one fragment entry): the first
+    // pass loads them and finds the per-token maximum, the second converts from registers (chunks
+    // beyond KEEP per thread are loaded again). Entries of tokens >= m_tokens stay as they are: a
+    // column of B only feeds the same column of the product, and those columns are never stored.
+    const int chunks_per_token = k >> 2;              // a multiple of 64: a warp's 32 chunks share one token
+    const int total = m_tokens * chunks_per_token;
+    const int first = tid & ~31;
+    float kept[KEEP][4];
+    auto load_chunk = [&](int c0, float (&v)[4]) {
+        const int t = c0 / chunks_per_token;
+        load4(x, x_dtype, static_cast<size_t>(row_of(t)) * k + static_cast<size_t>(c0 + lane - t * chunks_per_token) * 4,
+              vec_ok, v);
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
-            for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            if (lane == 0) atomicMax(&amax_bits[t], __float_as_uint(amax));
-        }
+        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (lane == 0) atomicMax(&amax_bits[t], __float_as_uint(amax));
+    };
+#pragma unroll
+    for (int sl = 0; sl < KEEP; ++sl)
+        if (first + sl * Q6T_THREADS < total) load_chunk(first + sl * Q6T_THREADS, kept[sl]);
+    for (int c0 = first + KEEP * Q6T_THREADS; c0 < total; c0 += Q6T_THREADS) {
+        float v[4];
+        load_chunk(c0, v);
     }
     named_barrier_sync(1, Q6T_THREADS);
     if (tid < 8) {
@@ -222,29 +231,34 @@ __device__ __forceinline__ void prepare_fragments(RowFn row_of, int m_tokens, in
         tok_scale[8 + tid] = 1.0f / s;
     }
     named_barrier_sync(1, Q6T_THREADS);
-    const int g = lane >> 2, tig = lane & 3;
-    const bool live = g < m_tokens;
-    const float s = tok_scale[g];
-    const size_t base = live ? static_cast<size_t>(row_of(g)) * k : 0;
-    for (int f = warp; f < nfrag; f += Q6T_WARPS) {
-        float v[4] = {0.f, 0.f, 0.f, 0.f};
-        if (live) {
-            load4(x, x_dtype, base + 16 * f + 4 * tig, vec_ok, v);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) v[i] *= s;
-        }
+    auto store_chunk = [&](int c0, const float (&v)[4]) {
+        const int t = c0 / chunks_per_token;
+        const int p = (c0 + lane - t * chunks_per_token) * 4;      // position of the chunk in the row
+        const float s = tok_scale[t];
         unsigned short hi[4], lo[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const __half h = __float2half_rn(v[i]);
+            const float sv = v[i] * s;
+            const __half h = __float2half_rn(sv);
             hi[i] = __half_as_ushort(h);
-            lo[i] = __half_as_ushort(__float2half_rn(v[i] - __half2float(h)));
+            lo[i] = __half_as_ushort(__float2half_rn(sv - __half2float(h)));
         }
-        bfrag[f * 32 + lane] = make_uint2(hi[0] | (static_cast<uint32_t>(hi[2]) << 16),
-                                          hi[1] | (static_cast<uint32_t>(hi[3]) << 16));
+        const int f = p >> 4, dst = 4 * t + ((p >> 2) & 3);
+        bfrag[f * 32 + dst] = make_uint2(hi[0] | (static_cast<uint32_t>(hi[2]) << 16),
+                                         hi[1] | (static_cast<uint32_t>(hi[3]) << 16));
         if (NTERMS == 2)
-            bfrag[(nfrag + f) * 32 + lane] = make_uint2(lo[0] | (static_cast<uint32_t>(lo[2]) << 16),
-                                                        lo[1] | (static_cast<uint32_t>(lo[3]) << 16));
+            bfrag[(nfrag + f) * 32 + dst] = make_uint2(lo[0] | (static_cast<uint32_t>(lo[2]) << 16),
+                                                       lo[1] | (static_cast<uint32_t>(lo[3]) << 16));
+    };
+#pragma unroll
+    for (int sl = 0; sl < KEEP; ++sl)
+        if (first + sl * Q6T_THREADS < total) store_chunk(first + sl * Q6T_THREADS, kept[sl]);
+    for (int c0 = first + KEEP * Q6T_THREADS; c0 < total; c0 += Q6T_THREADS) {
+        const int t = c0 / chunks_per_token;
+        float v[4];
+        load4(x, x_dtype, static_cast<size_t>(row_of(t)) * k + static_cast<size_t>(c0 + lane - t * chunks_per_token) * 4,
+              vec_ok, v);
+        store_chunk(c0, v);
     }
     named_barrier_sync(1, Q6T_THREADS);
 }
@@ -299,7 +313,7 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) q6k_tiled_kernel(const Q6Tiled
 
     int m_tokens = a.m;
     int seg_begin = 0, cur_unit = -1;
-    if (!GROUPED) prepare_fragments<NTERMS>([](int t) { return t; }, a.m, a.k, a.x, a.x_dtype, bfrag, tok_scale, tid);
+    if (!GROUPED) prepare_fragments<NTERMS, 4>([](int t) { return t; }, a.m, a.k, a.x, a.x_dtype, bfrag, tok_scale, tid);
 
     int pbuf = 0;
     for (long long blk = blk_begin; blk < blk_end; ++blk) {
@@ -321,7 +335,7 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) q6k_tiled_kernel(const Q6Tiled
                                                 a.flat_rows ? flat : seg_begin + tid);
             }
             named_barrier_sync(1, Q6T_THREADS);
-            prepare_fragments<NTERMS>([&](int t) { return seg_tokens[t]; }, m_tokens, a.k, a.x, a.x_dtype, bfrag,
+            prepare_fragments<NTERMS, 2>([&](int t) { return seg_tokens[t]; }, m_tokens, a.k, a.x, a.x_dtype, bfrag,
                                       tok_scale, tid);
         }
 
