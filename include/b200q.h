@@ -31,6 +31,10 @@ extern "C" {
 /* Q6_K re-ordered on the device into 16-row x 1-super-block tiles (b200q_q6k_retile): same size, same
  * values, 16-byte aligned pieces. Accepted by b200q_gemv and b200q_moe_down(_peer) only. */
 #define B200Q_Q6_K_TILED 21
+/* Q4_K re-ordered the same way (b200q_q4k_retile): a permutation of 16-byte pieces inside each
+ * 16-row x 1-super-block tile. Accepted by b200q_gemv, b200q_swiglu, b200q_moe_gate_up and
+ * b200q_moe_down(_peer); gate and up must share the layout. */
+#define B200Q_Q4_K_TILED 22
 
 /* activation / output element types */
 #define B200Q_F32 0
@@ -188,6 +192,8 @@ int b200q_moe_combine_ids(const float *terms, const void *ids, int ids_is_i64, i
  * tiled buffer must be 16-byte aligned. GGUF stores 210-byte Q6_K blocks, which no 128-bit load can
  * address; the tile layout is what the tensor-core kernel streams at full width. (No counterpart in
  * the reference, which reads native blocks byte by byte: mini_llm/ops/quantized_linear.py:139-158.) */
+int b200q_q4k_retile(const void *native, void *tiled, int64_t rows, int k, void *stream);
+int b200q_q4k_untile(const void *tiled, void *native, int64_t rows, int k, void *stream);
 int b200q_q6k_retile(const void *native, void *tiled, int64_t rows, int k, void *stream);
 int b200q_q6k_untile(const void *tiled, void *native, int64_t rows, int k, void *stream);
 

@@ -24,6 +24,7 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) 
     if (q.fmt_a != B200Q_Q4_K && q.fmt_a != B200Q_Q5_K) return B200Q_OK;
     if (dual && q.fmt_a != q.fmt_b) return B200Q_OK;
     if (q.k % 256 != 0 || q.m > 8) return B200Q_OK;
+    if (q.tiled && (q.fmt_a != B200Q_Q4_K || q.n % 16 != 0)) return B200Q_OK;
     if (reinterpret_cast<uintptr_t>(q.wa) & 15) return B200Q_OK;
     if (dual && (reinterpret_cast<uintptr_t>(q.wb) & 15)) return B200Q_OK;
     if (grouped && !q.table_a && ((q.stride_a & 15) || (dual && (q.stride_b & 15)))) return B200Q_OK;
@@ -33,6 +34,7 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) 
     a.wa = q.wa; a.wb = q.wb; a.stride_a = q.stride_a; a.stride_b = q.stride_b;
     a.table_a = q.table_a; a.table_b = q.table_b;
     a.rb = q.k / 256 * fmt_bytes(q.fmt_a);
+    a.tiled = q.tiled;
     a.n = q.n; a.k = q.k; a.m = q.m;
     a.nterms = (q.x_dtype == B200Q_F32) ? 2 : 1;
     const int nsb = q.k / 256;

@@ -37,6 +37,7 @@ struct DirectArgs {
     long long stride_a, stride_b;
     const unsigned long long *table_a, *table_b;   // optional per-expert pointer tables
     int rb;              // packed bytes per weight row (both streams share the format)
+    int tiled;           // Q4_K only: weights in the 16-row tile layout (see load_superblock_tiled)
     int n, k, m;
     int kp, rg;          // warps along K and row groups per CTA pass (kp * rg == 16)
     int nterms;
@@ -98,6 +99,26 @@ __device__ __forceinline__ void load_superblock(SuperBlockRegs<Q5> &r, const uin
         r.qa = ldg128(blk + 16 + 16 * tig);
         r.qb = ldg128(blk + 80 + 16 * tig);
     }
+}
+
+// Q4_K tile layout (device-side re-ordering of the GGUF bytes, same size): a tile holds the 16
+// super-blocks of 16 consecutive rows at one K position (2304 bytes):
+//   [0, 256)     the 16 rows' first 16 bytes (d, dmin, scales/mins), row r at 16*r
+//   [256, 2304)  four planes of 512 bytes with one 16-byte piece per lane (lane*16): planes 0/1 =
+//                bytes [16+16tig, +16) and [80+16tig, +16) of row g's block, planes 2/3 the same of
+//                row g+8 - exactly the pieces load_superblock() fetches, so the arithmetic is shared.
+// Tiles are ordered (row group, super-block): a warp instruction reads 512 contiguous bytes.
+constexpr int Q4T_TILE_BYTES = 2304;
+__device__ __forceinline__ void load_superblock_tiled(SuperBlockRegs<false> &ra, SuperBlockRegs<false> &rb,
+                                                      const uint8_t *tile, int lane) {
+    const int g = lane >> 2;
+    ra.hd = ldg128(tile + 16 * g);
+    rb.hd = ldg128(tile + 16 * (g + 8));
+    ra.qa = ldg128(tile + 256 + lane * 16);
+    ra.qb = ldg128(tile + 768 + lane * 16);
+    rb.qa = ldg128(tile + 1280 + lane * 16);
+    rb.qb = ldg128(tile + 1792 + lane * 16);
+    ra.qh = rb.qh = make_uint4(0u, 0u, 0u, 0u);
 }
 
 // Scales of one row for this lane: the four sub-blocks its quant bytes belong to, as FP16 pairs
@@ -384,8 +405,14 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
     auto block_ptrs = [&](int unit, int row0) {
         BlockPtrs p;
         const int expert = GROUPED ? a.seg_expert[unit] : 0;
-        const size_t off_lo = static_cast<size_t>(min(row0 + 16 * rgi + g, a.n - 1)) * a.rb + static_cast<size_t>(kpi) * QB;
-        const size_t off_hi = static_cast<size_t>(min(row0 + 16 * rgi + g + 8, a.n - 1)) * a.rb + static_cast<size_t>(kpi) * QB;
+        size_t off_lo, off_hi;
+        if (!Q5 && a.tiled) {   // tile of (row group, super-block kpi); n is a multiple of 16 here
+            const int group = min((row0 >> 4) + rgi, (a.n >> 4) - 1);
+            off_lo = off_hi = (static_cast<size_t>(group) * nsb + kpi) * Q4T_TILE_BYTES;
+        } else {
+            off_lo = static_cast<size_t>(min(row0 + 16 * rgi + g, a.n - 1)) * a.rb + static_cast<size_t>(kpi) * QB;
+            off_hi = static_cast<size_t>(min(row0 + 16 * rgi + g + 8, a.n - 1)) * a.rb + static_cast<size_t>(kpi) * QB;
+        }
         const uint8_t *base_a = expert_matrix(a.wa, a.stride_a, a.table_a, expert);
         p.a_lo = base_a + off_lo;
         p.a_hi = base_a + off_hi;
@@ -398,10 +425,16 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
         return p;
     };
     // item -> byte offset from the block pointers, and stream
-    const int sb_step_bytes = a.kp * QB;
+    const int sb_step_bytes = a.kp * ((!Q5 && a.tiled) ? Q4T_TILE_BYTES : QB);
     auto issue_item = [&](const BlockPtrs &p, int item, SuperBlockRegs<Q5> &ra, SuperBlockRegs<Q5> &rb) {
         const int stream = DUAL ? (item & 1) : 0;
         const size_t off = static_cast<size_t>(DUAL ? (item >> 1) : item) * sb_step_bytes;
+        if constexpr (!Q5) {
+            if (a.tiled) {
+                load_superblock_tiled(ra, rb, (stream ? p.b_lo : p.a_lo) + off, lane);
+                return;
+            }
+        }
         load_superblock<Q5>(ra, (stream ? p.b_lo : p.a_lo) + off, tig);
         load_superblock<Q5>(rb, (stream ? p.b_hi : p.a_hi) + off, tig);
     };

@@ -79,10 +79,11 @@ static bool direct_allowed() {
 
 int mma_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) {
     *launched = false;
-    if (direct_allowed()) {
+    if (direct_allowed() || q.tiled) {
         int rc = direct_try_launch(q, stream, launched);
         if (rc || *launched) return rc;
     }
+    if (q.tiled) return B200Q_OK;       // only the direct kernel reads the tile layout
     const bool dual = (q.mode == 1 || q.mode == 2);
     const bool grouped = q.mode >= 2;
     if (q.k % 256 != 0 || q.k > 65536) return B200Q_OK;

@@ -126,6 +126,8 @@ int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype,
         }
         return B200Q_OK;
     }
+    const bool tiled = fmt == B200Q_Q4_K_TILED;
+    if (tiled) fmt = B200Q_Q4_K;
     if (!fmt_valid(fmt)) return fail(B200Q_EINVAL, "gemv: unknown format %d", fmt);
     if (!dtype_valid(x_dtype) || !dtype_valid(y_dtype)) return fail(B200Q_EINVAL, "gemv: bad dtype");
     if (n <= 0 || m <= 0 || !k_ok(fmt, k)) return fail(B200Q_EINVAL, "gemv: bad shape n=%d k=%d m=%d", n, k, m);
@@ -140,7 +142,7 @@ int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype,
     a.x_dtype = x_dtype;
     a.y_dtype = y_dtype;
     a.status = status;
-    if (mma_allowed()) {
+    if (mma_allowed() || tiled) {
         // up to 8 tokens per pass on the tensor cores
         bool all = true;
         for (int t0 = 0; t0 < m && all; t0 += 8) {
@@ -149,7 +151,7 @@ int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype,
             q.x = static_cast<const uint8_t *>(x) + static_cast<size_t>(t0) * k * dtype_size(x_dtype);
             q.x_dtype = x_dtype;
             q.y = static_cast<uint8_t *>(y) + static_cast<size_t>(t0) * n * dtype_size(y_dtype);
-            q.y_dtype = y_dtype; q.status = status;
+            q.y_dtype = y_dtype; q.status = status; q.tiled = tiled;
             bool launched = false;
             int rc = mma_try_launch(q, static_cast<cudaStream_t>(stream), &launched);
             if (rc) return rc;
@@ -160,6 +162,7 @@ int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype,
         }
         if (all) return B200Q_OK;
     }
+    if (tiled) return fail(B200Q_EUNSUPPORTED, "gemv: no kernel reads this shape in the Q4_K tile layout");
     const int mt = tokens_per_launch(m, k);
     if (mt < 1) return fail(B200Q_EUNSUPPORTED, "gemv: K=%d too large", k);
     int rc = plan_tiles(a, false, mt);
@@ -181,6 +184,9 @@ int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype,
 int b200q_swiglu(const void *gate, int gate_fmt, const void *up, int up_fmt, int f, int k, const void *x,
                  int x_dtype, int m, void *h, int h_dtype, void *stream) {
     if (!gate || !up || !x || !h) return fail(B200Q_EINVAL, "swiglu: NULL pointer");
+    const bool tiled = gate_fmt == B200Q_Q4_K_TILED;
+    if (tiled != (up_fmt == B200Q_Q4_K_TILED)) return fail(B200Q_EINVAL, "swiglu: gate and up must share the layout");
+    if (tiled) gate_fmt = up_fmt = B200Q_Q4_K;
     if (!fmt_valid(gate_fmt) || !fmt_valid(up_fmt)) return fail(B200Q_EINVAL, "swiglu: unknown format");
     if (!dtype_valid(x_dtype) || !dtype_valid(h_dtype)) return fail(B200Q_EINVAL, "swiglu: bad dtype");
     if (f <= 0 || m <= 0 || !k_ok(gate_fmt, k) || !k_ok(up_fmt, k))
@@ -197,10 +203,11 @@ int b200q_swiglu(const void *gate, int gate_fmt, const void *up, int up_fmt, int
     a.x_dtype = x_dtype;
     a.y_dtype = h_dtype;
     a.status = status;
-    if (mma_allowed()) {
+    if (mma_allowed() || tiled) {
         bool all = true;
         for (int t0 = 0; t0 < m && all; t0 += 8) {
             MmaRequest q{};
+            q.tiled = tiled;
             q.mode = 1; q.wa = a.wa; q.wb = a.wb; q.fmt_a = gate_fmt; q.fmt_b = up_fmt; q.n = f; q.k = k;
             q.m = (m - t0 < 8) ? m - t0 : 8;
             q.x = static_cast<const uint8_t *>(x) + static_cast<size_t>(t0) * k * dtype_size(x_dtype);
@@ -217,6 +224,7 @@ int b200q_swiglu(const void *gate, int gate_fmt, const void *up, int up_fmt, int
         }
         if (all) return B200Q_OK;
     }
+    if (tiled) return fail(B200Q_EUNSUPPORTED, "swiglu: no kernel reads this shape in the Q4_K tile layout");
     const int mt = tokens_per_launch(m, k);
     if (mt < 1) return fail(B200Q_EUNSUPPORTED, "swiglu: K=%d too large", k);
     int rc = plan_tiles(a, true, mt);
@@ -243,6 +251,10 @@ int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, 
                       void *stream) {
     if ((!gate_table != !up_table) || (!gate_table && (!gate_base || !up_base)) || !x || !order || !seg_expert || !seg_begin || !seg_count || !num_segments || !hbuf)
         return fail(B200Q_EINVAL, "moe_gate_up: NULL pointer");
+    const bool tiled = gate_fmt == B200Q_Q4_K_TILED;
+    if (tiled != (up_fmt == B200Q_Q4_K_TILED))
+        return fail(B200Q_EINVAL, "moe_gate_up: gate and up must share the layout");
+    if (tiled) gate_fmt = up_fmt = B200Q_Q4_K;
     if (!fmt_valid(gate_fmt) || !fmt_valid(up_fmt) || !dtype_valid(x_dtype))
         return fail(B200Q_EINVAL, "moe_gate_up: bad format/dtype");
     if (f <= 0 || k <= 0 || max_segments <= 0 || !k_ok(gate_fmt, d) || !k_ok(up_fmt, d))
@@ -273,8 +285,9 @@ int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, 
     a.num_segments = num_segments;
     a.max_segments = max_segments;
     a.status = status;
-    if (mma_allowed()) {
+    if (mma_allowed() || tiled) {
         MmaRequest q{};
+        q.tiled = tiled;
         q.mode = 2; q.wa = a.wa; q.wb = a.wb; q.fmt_a = gate_fmt; q.fmt_b = up_fmt; q.stride_a = gate_stride;
         q.stride_b = up_stride; q.table_a = a.table_a; q.table_b = a.table_b; q.tables_aligned16 = tables_aligned16;
         q.n = f; q.k = d; q.m = MAX_TOKENS; q.x = x; q.x_dtype = x_dtype; q.y = hbuf;
@@ -284,6 +297,7 @@ int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, 
         int rc = mma_try_launch(q, static_cast<cudaStream_t>(stream), &launched);
         if (rc || launched) return rc;
     }
+    if (tiled) return fail(B200Q_EUNSUPPORTED, "moe_gate_up: no kernel reads this shape in the Q4_K tile layout");
     if (static_cast<long long>(MAX_TOKENS) * d * 4 > XBUF_LIMIT)
         return fail(B200Q_EUNSUPPORTED, "moe_gate_up: d=%d too large for %d tokens per segment", d, MAX_TOKENS);
     int rc = plan_tiles(a, true, MAX_TOKENS);
@@ -313,6 +327,8 @@ static int moe_down_impl(const void *down_base, int64_t down_stride, int down_fm
         q.rows_per_rank = rows_per_rank;
         return q6k_tiled_launch(q, static_cast<cudaStream_t>(stream));
     }
+    const bool tiled = down_fmt == B200Q_Q4_K_TILED;
+    if (tiled) down_fmt = B200Q_Q4_K;
     if (!fmt_valid(down_fmt)) return fail(B200Q_EINVAL, "moe_down: bad format");
     if (d <= 0 || max_segments <= 0 || !k_ok(down_fmt, f)) return fail(B200Q_EINVAL, "moe_down: bad shape d=%d f=%d", d, f);
     int *status = device_status_word();
@@ -341,8 +357,9 @@ static int moe_down_impl(const void *down_base, int64_t down_stride, int down_fm
     a.y_table = y_table;
     a.rows_per_rank = rows_per_rank;
     a.status = status;
-    if (mma_allowed()) {
+    if (mma_allowed() || tiled) {
         MmaRequest q{};
+        q.tiled = tiled;
         q.mode = 3; q.wa = a.wa; q.fmt_a = q.fmt_b = down_fmt; q.stride_a = down_stride; q.table_a = a.table_a;
         q.tables_aligned16 = tables_aligned16; q.n = d; q.k = f;
         q.m = MAX_TOKENS; q.x = hbuf; q.x_dtype = B200Q_F32; q.y = terms; q.y_dtype = B200Q_F32; q.topk = 1;
@@ -354,6 +371,7 @@ static int moe_down_impl(const void *down_base, int64_t down_stride, int down_fm
         int rc = mma_try_launch(q, static_cast<cudaStream_t>(stream), &launched);
         if (rc || launched) return rc;
     }
+    if (tiled) return fail(B200Q_EUNSUPPORTED, "moe_down: no kernel reads this shape in the Q4_K tile layout");
     if (static_cast<long long>(MAX_TOKENS) * f * 4 > XBUF_LIMIT)
         return fail(B200Q_EUNSUPPORTED, "moe_down: f=%d too large for %d tokens per segment", f, MAX_TOKENS);
     int rc = plan_tiles(a, false, MAX_TOKENS);

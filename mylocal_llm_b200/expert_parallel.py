@@ -224,7 +224,10 @@ class DeviceExpertEngine:
         if retile_enabled():
             bank = bank.retiled()
             if shared is not None:
-                shared = (shared[0], shared[1], retile_weight(shared[2]))
+                gate_t, up_t = retile_weight(shared[0]), retile_weight(shared[1])
+                if gate_t.quant_type != up_t.quant_type:          # gate and up share one layout
+                    gate_t, up_t = shared[0], shared[1]
+                shared = (gate_t, up_t, retile_weight(shared[2]))
         self.bank = bank
         self.first_expert, self.n_global = int(first_expert), int(n_experts_global)
         self.router = RouterInference(bank.d_model, self.n_global, top_k, renormalize_selected=True,

@@ -50,7 +50,7 @@ class PackedExpertBank:
         for name, fmt, shape in (("gate", self.gate_type, (self.d_ff, self.d_model)),
                                  ("up", self.up_type, (self.d_ff, self.d_model)),
                                  ("down", self.down_type, (self.d_model, self.d_ff))):
-            if fmt not in BLOCK_FORMATS and not (name == "down" and fmt in DEVICE_LAYOUTS):
+            if fmt not in BLOCK_FORMATS and fmt not in DEVICE_LAYOUTS:
                 raise ValueError(f"Unsupported packed GGUF type: {fmt}")
             data = getattr(self, name)
             expect = self.n_experts * packed_nbytes(shape, fmt)
@@ -86,14 +86,23 @@ class PackedExpertBank:
                    packed_bytes_to_device(down.data), gate.quant_type, up.quant_type, down.quant_type, e, d, f)
 
     def retiled(self):
-        """Bank whose Q6_K down projections are in the tile layout (a new down tensor; gate and up
-        are shared). Other down types, and d_model not a multiple of 16, return the bank itself."""
-        from .quantized_linear import TILED_MAX_K, retile_q6k
-        if self.down_type != "Q6_K" or self.d_model % 16 or self.d_ff > TILED_MAX_K:
+        """Bank with its Q4_K / Q6_K projections in the tile layout (new tensors for the converted
+        banks, the others are shared). Gate and up are converted together or not at all; shapes the
+        layout does not cover keep the GGUF bytes."""
+        from .quantized_linear import can_retile, retile_bytes, _RETILE
+        gate, up, down = self.gate, self.up, self.down
+        gate_type, up_type, down_type = self.gate_type, self.up_type, self.down_type
+        if gate_type == up_type and can_retile(gate_type, self.d_ff, self.d_model) and gate_type == "Q4_K":
+            gate = retile_bytes(gate, self.n_experts * self.d_ff, self.d_model, gate_type)
+            up = retile_bytes(up, self.n_experts * self.d_ff, self.d_model, up_type)
+            gate_type = up_type = _RETILE[gate_type][1]
+        if can_retile(down_type, self.d_model, self.d_ff):
+            down = retile_bytes(down, self.n_experts * self.d_model, self.d_ff, down_type)
+            down_type = _RETILE[down_type][1]
+        if (gate_type, down_type) == (self.gate_type, self.down_type):
             return self
-        down = retile_q6k(self.down, self.n_experts * self.d_model, self.d_ff)
-        return PackedExpertBank(self.gate, self.up, down, self.gate_type, self.up_type, "Q6_K_TILED",
-                                self.n_experts, self.d_model, self.d_ff)
+        return PackedExpertBank(gate, up, down, gate_type, up_type, down_type, self.n_experts, self.d_model,
+                                self.d_ff)
 
     def pointer_tables(self, extra=None):
         """Device pointer tables (three int64 tensors with one address per expert) and whether every

@@ -114,37 +114,56 @@ def retile_enabled():
     return os.environ.get("B200Q_RETILE", "1") != "0"
 
 
-def retile_q6k(data, rows, k):
-    """Native Q6_K bytes of a ``[rows, k]`` matrix (or a bank of experts, ``rows`` = all rows) ->
-    new tensor in the 16-row tile layout (same size; lossless, see ``untile_q6k``)."""
+_RETILE = {"Q6_K": ("b200q_q6k_retile", "Q6_K_TILED"), "Q4_K": ("b200q_q4k_retile", "Q4_K_TILED")}
+_UNTILE = {"Q6_K_TILED": "b200q_q6k_untile", "Q4_K_TILED": "b200q_q4k_untile"}
+
+
+def retile_bytes(data, rows, k, quant_type):
+    """Native ``quant_type`` bytes of a ``[rows, k]`` matrix (or a bank of experts, ``rows`` = all
+    rows) -> new tensor in the 16-row tile layout (same size; lossless, see ``untile_bytes``)."""
     torch = _torch()
     out = torch.empty_like(data)
-    _lib.call("b200q_q6k_retile", _ptr(data), _ptr(out), int(rows), int(k), _lib.current_stream())
+    _lib.call(_RETILE[quant_type][0], _ptr(data), _ptr(out), int(rows), int(k), _lib.current_stream())
     return out
+
+
+def untile_bytes(data, rows, k, tiled_type):
+    """Inverse of ``retile_bytes``: restores the GGUF bytes bit for bit."""
+    torch = _torch()
+    out = torch.empty_like(data)
+    _lib.call(_UNTILE[tiled_type], _ptr(data), _ptr(out), int(rows), int(k), _lib.current_stream())
+    return out
+
+
+def retile_q6k(data, rows, k):
+    return retile_bytes(data, rows, k, "Q6_K")
 
 
 def untile_q6k(data, rows, k):
-    """Inverse of ``retile_q6k``: restores the GGUF bytes bit for bit."""
-    torch = _torch()
-    out = torch.empty_like(data)
-    _lib.call("b200q_q6k_untile", _ptr(data), _ptr(out), int(rows), int(k), _lib.current_stream())
-    return out
+    return untile_bytes(data, rows, k, "Q6_K_TILED")
 
 
-def retile_weight(weight):
-    """``DevicePackedGGUFWeight`` in the tile layout when its type has one and the shape allows it
-    (Q6_K, rows a multiple of 16, K <= TILED_MAX_K); otherwise the weight itself."""
-    if weight.quant_type != "Q6_K" or weight.shape[0] % 16 or weight.shape[1] > TILED_MAX_K:
+def can_retile(quant_type, rows, k, force=False):
+    return quant_type in _RETILE and rows % 16 == 0 and (k <= TILED_MAX_K or force)
+
+
+def retile_weight(weight, force=False):
+    """``DevicePackedGGUFWeight`` in the tile layout when its type has one (Q4_K, Q6_K) and the shape
+    allows it (rows a multiple of 16, K <= TILED_MAX_K); otherwise the weight itself. ``force`` lifts
+    the K limit for callers that only ever pass 16-bit activations (Q4_K up to K = 8192)."""
+    if not can_retile(weight.quant_type, weight.shape[0], weight.shape[1], force):
         return weight
-    return DevicePackedGGUFWeight(retile_q6k(weight.data, weight.shape[0], weight.shape[1]), weight.shape,
-                                  "Q6_K_TILED")
+    if weight.quant_type == "Q6_K" and weight.shape[1] > TILED_MAX_K:
+        return weight
+    return DevicePackedGGUFWeight(retile_bytes(weight.data, weight.shape[0], weight.shape[1], weight.quant_type),
+                                  weight.shape, _RETILE[weight.quant_type][1])
 
 
 def dequantize_device(data, rows, k, quant_type):
     """FP32 ``[rows, k]`` CUDA tensor decoded from packed device bytes (verification helper)."""
     torch = _torch()
     if quant_type in DEVICE_LAYOUTS:
-        data, quant_type = untile_q6k(data, rows, k), DEVICE_LAYOUTS[quant_type]
+        data, quant_type = untile_bytes(data, rows, k, quant_type), DEVICE_LAYOUTS[quant_type]
     out = torch.empty((rows, k), dtype=torch.float32, device=data.device)
     _lib.call("b200q_dequantize", _ptr(data), _lib.FORMAT_ID[quant_type], rows, k, _ptr(out),
               _lib.current_stream())
