@@ -229,7 +229,7 @@ def run_gpu_arm(args, name):
     base = random_packed(fmt, (n, k), seed=1234 + rank, d=0.01, dmin=0.005)
     weights = []
     for c in range(copies):
-        weights.append(packed_to_device(base))   # a distinct HBM allocation per copy
+        weights.append(upload(base, act))   # a distinct HBM allocation per copy
     rng = np.random.default_rng(7 + rank)
     host_x = torch.from_numpy(rng.normal(0, 1, (copies, m, k)).astype(np.float32)).to(act_dtype).pin_memory()
     dev_x = host_x.cuda()
@@ -333,6 +333,16 @@ def run_gpu_arm(args, name):
         dist.destroy_process_group()
 
 
+def upload(packed, act):
+    """Host packed weight -> HBM, re-ordered into the device tile layout where one exists (the default
+    of the MoE layers as well; B200Q_RETILE=0 keeps the GGUF bytes). K > 4096 is tiled only for 16-bit
+    activations, the case the tiled kernel's shared-memory budget covers."""
+    from mylocal_llm_b200 import packed_to_device
+    from mylocal_llm_b200.quantized_linear import retile_enabled, retile_weight
+    dev = packed_to_device(packed)
+    return retile_weight(dev, force=act != "float32") if retile_enabled() else dev
+
+
 def gemv_side_numbers(names, replays=20):
     """Short device-resident timing of dense decode GEMVs (same method as run_gpu_arm), reported next to
     the MoE number so one line carries both halves of the metric."""
@@ -348,7 +358,7 @@ def gemv_side_numbers(names, replays=20):
         wbytes = packed_bytes(fmt, n, k)
         copies = min(max(2, -(-2 * L2_BYTES // wbytes)), 64)
         base = random_packed(fmt, (n, k), seed=99, d=0.01, dmin=0.005)
-        weights = [packed_to_device(base) for _ in range(copies)]
+        weights = [upload(base, act) for _ in range(copies)]
         x = torch.randn((copies, m, k), device="cuda").to(act_dtype)
         with torch.cuda.stream(stream):
             for c in range(copies):
@@ -370,7 +380,8 @@ def gemv_side_numbers(names, replays=20):
         graph.reset()
         per_launch = algorithmic_bytes(fmt, n, k, m, 4 if act == "float32" else 2)
         gbs = per_launch / (us * 1e-6) / 1e9
-        out[name] = {"GB/s": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4), "us_per_launch": round(us, 3)}
+        out[name] = {"GB/s": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4), "us_per_launch": round(us, 3),
+                     "layout": weights[0].quant_type}
         del weights, graph
     torch.cuda.empty_cache()
     return out

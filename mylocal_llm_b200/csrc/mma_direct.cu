@@ -44,6 +44,14 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) 
     const long long wanted = 3LL * sm_count() * MD_WARPS;
     int kp = 1;
     while (kp * 2 <= MD_WARPS && kp * 2 <= nsb && row_groups * kp < wanted) kp *= 2;
+    // ... and enough row blocks that the CTAs finish together: at least six per SM (a grouped launch
+    // counts half of the segment bound, the usual number of active segments).
+    auto blocks_for = [&](int parts) {
+        const int rows = 16 * (MD_WARPS / parts);
+        const long long per_unit = (q.n + rows - 1) / rows;
+        return per_unit * (grouped ? (q.max_segments > 1 ? q.max_segments / 2 : 1) : 1);
+    };
+    while (kp * 2 <= MD_WARPS && kp * 2 <= nsb && blocks_for(kp) < 6LL * sm_count()) kp *= 2;
     a.kp = kp;
     a.rg = MD_WARPS / kp;
     a.off_bfrag = MD_CTRL_BYTES + MD_PART_BYTES;

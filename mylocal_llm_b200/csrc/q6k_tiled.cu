@@ -115,6 +115,13 @@ int q6k_tiled_launch(const MmaRequest &q, cudaStream_t stream) {
     const long long wanted = 3LL * sm_count() * Q6T_WARPS;
     int kp = 1;
     while (kp * 2 <= Q6T_WARPS && kp * 2 <= nsb && row_groups * kp < wanted) kp *= 2;
+    // enough row blocks that the CTAs finish together (six per SM; half the segment bound when grouped)
+    auto blocks_for = [&](int parts) {
+        const int groups = Q6T_WARPS / parts;
+        const long long per_unit = (q.n / 16 + groups - 1) / groups;
+        return per_unit * (grouped ? (q.max_segments > 1 ? q.max_segments / 2 : 1) : 1);
+    };
+    while (kp * 2 <= Q6T_WARPS && kp * 2 <= nsb && blocks_for(kp) < 6LL * sm_count()) kp *= 2;
     a.kp = kp;
     a.rg = Q6T_WARPS / kp;
     a.off_bfrag = Q6T_CTRL_BYTES + Q6T_PART_BYTES;
