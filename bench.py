@@ -3,18 +3,25 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-A *step* is one pass of the hot path over one batch of synthetic input. The default workload
-is the K-quant decode GEMV of the baseline's second configuration (W [8192 x 2048], Q4_K,
-bf16 activations, M = 1): one step runs the GEMV once over each of ``copies`` distinct weight
-copies whose total size exceeds twice the L2 capacity, so every launch streams its weights
-from HBM. ``value`` is algorithmic GB/s (packed bytes + activations + outputs per launch) with
-everything resident in HBM; ``e2e`` is the same quantity through the operator API with the
-activations coming from pinned host memory and the outputs copied back every step.
+A *step* is one pass of the hot path over one batch of synthetic input. The default workload,
+``moe_stack_b64``, is the decode step of the baseline's fifth configuration: 48 packed sparse-MoE
+layers (hidden 2048, 512 experts of width 512, top-10 renormalised routing, always-on shared expert,
+Q4_K gate/up + Q6_K down, about 50 GB packed and resident in HBM) with per-layer RMSNorm and an FP32
+residual stream, 64 tokens per GPU and step; token mixing is the identity. ``value`` is decode
+tokens/s with the step captured in a CUDA graph and everything resident in HBM; ``e2e`` is the same
+step with its activations copied in from pinned host memory and the result copied back every step.
+The 48 distinct layers touch about 22-33 GB per step, far more than L2, so every launch streams its
+weights from HBM. ``roofline`` describes the dominant kernel (grouped gate/up + SwiGLU): algorithmic
+bytes of one launch over its own CUDA-event duration. ``dense_gemv`` adds a short measurement of the
+dense decode GEMVs of the second configuration (the other half of the metric); the ``gemv_*``
+workloads run those as the main measurement instead.
 
-With N > 1 (launched by torchrun, one rank per GPU) the dense GEMV does not shard: every rank
-runs an independent replica (weak scaling, no collective on the data path) and the job value is
-the sum. ``--impl reference`` times the reference's own CPU kernels (oracle/_ref, else the
-plain-C port) on the host cores instead.
+With N > 1 (launched by torchrun, one rank per GPU) the MoE workloads run expert-parallel: the experts
+of every layer are sharded over the ranks, each rank brings its own 64 (or ``tokens``) rows per step
+(weak scaling in tokens), rows and expert terms are exchanged through peer memory (``--exchange
+collective`` uses NCCL instead), and ``value`` is the tokens of all ranks over the slowest rank's time.
+The dense GEMV workloads do not shard: N independent replicas, no collective. ``--impl reference``
+times the reference's own CPU kernels (oracle/_ref, else the plain-C port) on the host cores instead.
 """
 
 import argparse
