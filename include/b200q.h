@@ -237,6 +237,11 @@ int b200q_peer_barrier(const uint64_t *pads, int rank, int world, int timeout_ms
 /* All-gather by stores: copies `bytes` from src to dst_bases[p] + dst_offset_bytes for every p < world. */
 int b200q_peer_push_rows(const void *src, size_t bytes, const uint64_t *dst_bases, size_t dst_offset_bytes,
                          int world, void *stream);
+/* The same for up to three buffers in one launch (rows, routing weights, expert ids): buffer z goes
+ * to dst_bases[p] + dst_offset_z for every p < world; a size of 0 skips a buffer. */
+int b200q_peer_push3(const void *src0, size_t bytes0, size_t dst_offset0, const void *src1, size_t bytes1,
+                     size_t dst_offset1, const void *src2, size_t bytes2, size_t dst_offset2,
+                     const uint64_t *dst_bases, int world, void *stream);
 
 /* One SwiGLU expert, y[m,d_model] = down( silu(x gate^T) * (x up^T) ), for callers that cannot
  * allocate device memory. (No counterpart in the reference: its expert FFN allocates the hidden

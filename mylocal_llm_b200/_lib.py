@@ -56,6 +56,8 @@ SIGNATURES = {
     "b200q_peer_close": [_ptr],
     "b200q_peer_free": [_ptr],
     "b200q_peer_barrier": [_ptr, _c_int, _c_int, _c_int, _ptr],
+    "b200q_peer_push3": [_ptr, ctypes.c_size_t, ctypes.c_size_t, _ptr, ctypes.c_size_t, ctypes.c_size_t, _ptr,
+                         ctypes.c_size_t, ctypes.c_size_t, _ptr, _c_int, _ptr],
     "b200q_peer_push_rows": [_ptr, ctypes.c_size_t, _ptr, ctypes.c_size_t, _c_int, _ptr],
     "b200q_moe_down": [_ptr, _c_i64, _c_int, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
                        _c_int, _ptr, _ptr],

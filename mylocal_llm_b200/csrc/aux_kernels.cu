@@ -249,22 +249,57 @@ struct PlanIdMap {
     int enabled, k, first, n_local, shared_id, home_lo, home_hi, e_global;
 };
 
-__global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const void *ids, int ids_is_i64, int total, int e,
-                                                                int skip_expert, const PlanIdMap map,
-                                                                int seg_cap, int32_t *counts, int32_t *offsets,
-                                                                int32_t *order, int32_t *inv, int32_t *seg_expert,
-                                                                int32_t *seg_begin, int32_t *seg_count,
-                                                                int32_t *num_segments, int max_segments,
-                                                                int32_t *status) {
+// Exclusive scan of one value per thread over the CTA (PLAN_THREADS threads); *total gets the sum.
+__device__ __forceinline__ int plan_block_scan(int v, int *warp_tot, int *total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += n;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = warp_tot[lane];
+        int winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += n;
+        }
+        warp_tot[lane] = winc - w;              // exclusive prefix of the warp totals
+        if (lane == 31) *total = winc;
+    }
+    __syncthreads();
+    const int out = warp_tot[warp] + inc - v;
+    __syncthreads();                            // warp_tot may be reused right away
+    return out;
+}
+
+// words > 0: `bits` (dynamic shared memory) holds one bit per (expert, row); an assignment's rank
+// inside its expert is then a population count over the rows before it - no serial pass. This needs
+// every row to name an expert at most once (top-k output does); a row that repeats an expert sets
+// `dup` and the kernel falls back to the ordered pass. Assignments of skip_expert are never run
+// and only need distinct positions.
+__global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const void *ids, int ids_is_i64, int total, int k,
+                                                                int e, int skip_expert, const PlanIdMap map,
+                                                                int words, int seg_cap, int32_t *counts,
+                                                                int32_t *offsets, int32_t *order, int32_t *inv,
+                                                                int32_t *seg_expert, int32_t *seg_begin,
+                                                                int32_t *seg_count, int32_t *num_segments,
+                                                                int max_segments, int32_t *status) {
+    extern __shared__ unsigned int bits[];    // [e][words]
     __shared__ int cnt[PLAN_MAX_EXPERTS];     // counts, then running cursor
     __shared__ int off[PLAN_MAX_EXPERTS + 1];
-    __shared__ int scan_tmp[PLAN_THREADS];
-    __shared__ int carry;
-    __shared__ int bad;
+    __shared__ int warp_tot[32];
+    __shared__ int carry, scan_total, skip_cursor;
+    __shared__ int bad, dup;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     for (int i = tid; i < e; i += PLAN_THREADS) cnt[i] = 0;
-    if (tid == 0) { bad = 0; carry = 0; }
+    for (int i = tid; i < e * words; i += PLAN_THREADS) bits[i] = 0u;
+    if (tid == 0) { bad = 0; dup = 0; carry = 0; skip_cursor = 0; }
     __syncthreads();
 
     auto load_id = [&](int i) -> int {
@@ -280,24 +315,25 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const void *ids,
         return static_cast<int>(v);
     };
 
-    for (int i = tid; i < total; i += PLAN_THREADS) atomicAdd(&cnt[load_id(i)], 1);
+    for (int i = tid; i < total; i += PLAN_THREADS) {
+        const int ex = load_id(i);
+        atomicAdd(&cnt[ex], 1);
+        if (words && ex != skip_expert) {
+            const int row = i / k;
+            const unsigned int bit = 1u << (row & 31);
+            if (atomicOr(&bits[ex * words + (row >> 5)], bit) & bit) dup = 1;
+        }
+    }
     __syncthreads();
 
     // exclusive scan of counts over experts, 1024 at a time
     for (int base = 0; base < e; base += PLAN_THREADS) {
         const int i = base + tid;
         const int c = i < e ? cnt[i] : 0;
-        scan_tmp[tid] = c;
+        const int ex_prefix = plan_block_scan(c, warp_tot, &scan_total);
+        if (i < e) off[i] = carry + ex_prefix;
         __syncthreads();
-        for (int o = 1; o < PLAN_THREADS; o <<= 1) {
-            const int v = tid >= o ? scan_tmp[tid - o] : 0;
-            __syncthreads();
-            scan_tmp[tid] += v;
-            __syncthreads();
-        }
-        if (i < e) off[i] = carry + scan_tmp[tid] - c;
-        __syncthreads();
-        if (tid == PLAN_THREADS - 1) carry += scan_tmp[tid];
+        if (tid == 0) carry += scan_total;
         __syncthreads();
     }
     if (tid == 0) off[e] = carry;
@@ -308,34 +344,52 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const void *ids,
     }
     if (tid == 0) offsets[e] = off[e];
     __syncthreads();
-    for (int i = tid; i < e; i += PLAN_THREADS) cnt[i] = off[i];  // running cursor
-    __syncthreads();
 
-    // stable placement: chunks of 1024 assignments in order, warps of a chunk in order
-    for (int base = 0; base < total; base += PLAN_THREADS) {
-        const int i = base + tid;
-        const bool valid = i < total;
-        const int ex = valid ? load_id(i) : -1;
-        const unsigned same = __match_any_sync(0xffffffffu, ex);
-        const int rank = __popc(same & ((1u << lane) - 1u));
-        const int leader = __ffs(same) - 1;
-        const int nwarps = (min(total - base, PLAN_THREADS) + 31) >> 5;
-        int pos = 0;
-        for (int w = 0; w < nwarps; ++w) {
-            if (warp == w && valid) {
-                int start = 0;
-                if (lane == leader) {
-                    start = cnt[ex];
-                    cnt[ex] = start + __popc(same);
-                }
-                start = __shfl_sync(same, start, leader);
-                pos = start + rank;
+    if (words && !dup) {
+        for (int i = tid; i < total; i += PLAN_THREADS) {
+            const int ex = load_id(i);
+            int pos;
+            if (ex == skip_expert) {
+                pos = off[ex] + atomicAdd(&skip_cursor, 1);
+            } else {
+                const int row = i / k;
+                const unsigned int *w = bits + ex * words;
+                int rank = __popc(w[row >> 5] & ((1u << (row & 31)) - 1u));
+                for (int q = 0; q < (row >> 5); ++q) rank += __popc(w[q]);
+                pos = off[ex] + rank;
             }
-            __syncthreads();
-        }
-        if (valid) {
             order[pos] = i;
             inv[i] = pos;
+        }
+    } else {
+        for (int i = tid; i < e; i += PLAN_THREADS) cnt[i] = off[i];  // running cursor
+        __syncthreads();
+        // stable placement: chunks of 1024 assignments in order, warps of a chunk in order
+        for (int base = 0; base < total; base += PLAN_THREADS) {
+            const int i = base + tid;
+            const bool valid = i < total;
+            const int ex = valid ? load_id(i) : -1;
+            const unsigned same = __match_any_sync(0xffffffffu, ex);
+            const int rank = __popc(same & ((1u << lane) - 1u));
+            const int leader = __ffs(same) - 1;
+            const int nwarps = (min(total - base, PLAN_THREADS) + 31) >> 5;
+            int pos = 0;
+            for (int w = 0; w < nwarps; ++w) {
+                if (warp == w && valid) {
+                    int start = 0;
+                    if (lane == leader) {
+                        start = cnt[ex];
+                        cnt[ex] = start + __popc(same);
+                    }
+                    start = __shfl_sync(same, start, leader);
+                    pos = start + rank;
+                }
+                __syncthreads();
+            }
+            if (valid) {
+                order[pos] = i;
+                inv[i] = pos;
+            }
         }
     }
     __syncthreads();
@@ -347,15 +401,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const void *ids,
         const int i = base + tid;
         const int c = (i < e && i != skip_expert) ? (off[i + 1] - off[i]) : 0;   // skipped expert: no segments
         const int nsegs = (c + seg_cap - 1) / seg_cap;
-        scan_tmp[tid] = nsegs;
-        __syncthreads();
-        for (int o = 1; o < PLAN_THREADS; o <<= 1) {
-            const int v = tid >= o ? scan_tmp[tid - o] : 0;
-            __syncthreads();
-            scan_tmp[tid] += v;
-            __syncthreads();
-        }
-        int s0 = carry + scan_tmp[tid] - nsegs;
+        const int s0 = carry + plan_block_scan(nsegs, warp_tot, &scan_total);
         for (int r = 0; r < nsegs; ++r) {
             if (s0 + r < max_segments) {
                 seg_expert[s0 + r] = i;
@@ -364,7 +410,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const void *ids,
             }
         }
         __syncthreads();
-        if (tid == PLAN_THREADS - 1) carry += scan_tmp[tid];
+        if (tid == 0) carry += scan_total;
         __syncthreads();
     }
     if (tid == 0) {
@@ -493,6 +539,30 @@ int b200q_router_topk(const float *logits, int rows, int n, int k, int renormali
     return b200q_router_topk_ex(logits, rows, n, k, renormalize, floor_value, -1, nullptr, weights, ids, stream);
 }
 
+// Chooses the rank-by-bitmask path when its table fits in shared memory.
+static int launch_plan(const void *ids, int ids_is_i64, int rows, int k, int e, int skip_expert, const PlanIdMap &map,
+                       int seg_cap, int32_t *counts, int32_t *offsets, int32_t *order, int32_t *inv,
+                       int32_t *seg_expert, int32_t *seg_begin, int32_t *seg_count, int32_t *num_segments,
+                       int max_segments, int32_t *status, void *stream, const char *what) {
+    constexpr size_t PLAN_BITS_LIMIT = 160 * 1024;
+    int words = (rows + 31) / 32;
+    size_t bits_bytes = static_cast<size_t>(e) * words * sizeof(unsigned int);
+    if (bits_bytes > PLAN_BITS_LIMIT) { words = 0; bits_bytes = 0; }
+    if (bits_bytes > 8 * 1024) {      // beyond what fits next to the static arrays without opting in
+        cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void *>(moe_plan_kernel),
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(PLAN_BITS_LIMIT));
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            return fail(B200Q_ECUDA, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(err));
+        }
+    }
+    moe_plan_kernel<<<1, PLAN_THREADS, bits_bytes, static_cast<cudaStream_t>(stream)>>>(
+        ids, ids_is_i64, rows * k, k, e, skip_expert, map, words, seg_cap, counts, offsets, order, inv, seg_expert,
+        seg_begin, seg_count, num_segments, max_segments, status);
+    return check_launch(what);
+}
+
 int b200q_moe_plan_ex(const void *ids, int ids_is_i64, int rows, int k, int e, int skip_expert, int seg_cap,
                       int32_t *counts,
                    int32_t *offsets, int32_t *order, int32_t *inv, int32_t *seg_expert, int32_t *seg_begin,
@@ -504,10 +574,8 @@ int b200q_moe_plan_ex(const void *ids, int ids_is_i64, int rows, int k, int e, i
         return fail(B200Q_EINVAL, "moe_plan: bad argument (experts <= %d, 1 <= seg_cap <= 8)", PLAN_MAX_EXPERTS);
     const long long total = static_cast<long long>(rows) * k;
     if (total > (1 << 24)) return fail(B200Q_EUNSUPPORTED, "moe_plan: too many assignments");
-    moe_plan_kernel<<<1, PLAN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-        ids, ids_is_i64, static_cast<int>(total), e, skip_expert, PlanIdMap{}, seg_cap, counts, offsets, order, inv, seg_expert, seg_begin,
-        seg_count, num_segments, max_segments, status);
-    return check_launch("moe_plan");
+    return launch_plan(ids, ids_is_i64, rows, k, e, skip_expert, PlanIdMap{}, seg_cap, counts, offsets, order, inv,
+                       seg_expert, seg_begin, seg_count, num_segments, max_segments, status, stream, "moe_plan");
 }
 
 int b200q_moe_plan_ep(const void *ids, int ids_is_i64, int rows, int k, int e_global, int first_expert, int n_local,
@@ -524,10 +592,8 @@ int b200q_moe_plan_ep(const void *ids, int ids_is_i64, int rows, int k, int e_gl
     const long long total = static_cast<long long>(rows) * k;
     if (total > (1 << 24)) return fail(B200Q_EUNSUPPORTED, "moe_plan_ep: too many assignments");
     PlanIdMap map{1, k, first_expert, n_local, shared_id, home_lo, home_hi, e_global};
-    moe_plan_kernel<<<1, PLAN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-        ids, ids_is_i64, static_cast<int>(total), n_local + 2, n_local + 1, map, seg_cap, counts, offsets, order, inv,
-        seg_expert, seg_begin, seg_count, num_segments, max_segments, status);
-    return check_launch("moe_plan_ep");
+    return launch_plan(ids, ids_is_i64, rows, k, n_local + 2, n_local + 1, map, seg_cap, counts, offsets, order, inv,
+                       seg_expert, seg_begin, seg_count, num_segments, max_segments, status, stream, "moe_plan_ep");
 }
 
 int b200q_moe_plan(const void *ids, int ids_is_i64, int rows, int k, int e, int seg_cap, int32_t *counts,

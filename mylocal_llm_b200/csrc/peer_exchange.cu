@@ -69,6 +69,29 @@ __global__ void __launch_bounds__(256) peer_push_kernel(const uint4 *src, long l
         dst[i] = src[i];
 }
 
+// Up to three buffers in one launch: grid (blocks, world, 3); segment z of rank p goes to
+// dst_bases[p] + offset[z].
+struct PushSegments {
+    const uint8_t *src[3];
+    long long bytes[3];
+    long long dst_offset[3];
+    int wide[3];          // 1: everything is 16-byte aligned (uint4 copies), 0: 4-byte copies
+};
+__global__ void __launch_bounds__(256) peer_push3_kernel(const PushSegments seg, const uint64_t *dst_bases) {
+    const int z = blockIdx.z;
+    const uint8_t *src = seg.src[z];
+    uint8_t *dst = reinterpret_cast<uint8_t *>(dst_bases[blockIdx.y]) + seg.dst_offset[z];
+    const long long first = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    const long long step = static_cast<long long>(gridDim.x) * 256;
+    if (seg.wide[z]) {
+        for (long long i = first; i < seg.bytes[z] / 16; i += step)
+            reinterpret_cast<uint4 *>(dst)[i] = reinterpret_cast<const uint4 *>(src)[i];
+    } else {
+        for (long long i = first; i < seg.bytes[z] / 4; i += step)
+            reinterpret_cast<uint32_t *>(dst)[i] = reinterpret_cast<const uint32_t *>(src)[i];
+    }
+}
+
 }  // namespace b200q
 
 using namespace b200q;
@@ -151,6 +174,32 @@ int b200q_peer_push_rows(const void *src, size_t bytes, const uint64_t *dst_base
     peer_push_kernel<<<dim3(blocks, world), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4 *>(src), n16, dst_bases, static_cast<long long>(dst_offset_bytes / 16));
     return check_launch("peer_push_rows");
+}
+
+int b200q_peer_push3(const void *src0, size_t bytes0, size_t dst_offset0, const void *src1, size_t bytes1,
+                     size_t dst_offset1, const void *src2, size_t bytes2, size_t dst_offset2,
+                     const uint64_t *dst_bases, int world, void *stream) {
+    if (!dst_bases) return fail(B200Q_EINVAL, "peer_push3: NULL pointer");
+    if (world < 1 || world > PEER_MAX_RANKS) return fail(B200Q_EINVAL, "peer_push3: bad world size");
+    const void *srcs[3] = {src0, src1, src2};
+    const size_t bytes[3] = {bytes0, bytes1, bytes2}, offs[3] = {dst_offset0, dst_offset1, dst_offset2};
+    PushSegments seg{};
+    long long most = 0;
+    for (int z = 0; z < 3; ++z) {
+        if (bytes[z] && !srcs[z]) return fail(B200Q_EINVAL, "peer_push3: NULL source");
+        if (bytes[z] % 4 || offs[z] % 4 || reinterpret_cast<uintptr_t>(srcs[z]) % 4)
+            return fail(B200Q_EINVAL, "peer_push3: sizes and addresses must be multiples of 4 bytes");
+        seg.src[z] = static_cast<const uint8_t *>(srcs[z]);
+        seg.bytes[z] = static_cast<long long>(bytes[z]);
+        seg.dst_offset[z] = static_cast<long long>(offs[z]);
+        seg.wide[z] = !(bytes[z] % 16 || offs[z] % 16 || reinterpret_cast<uintptr_t>(srcs[z]) % 16);
+        const long long units = static_cast<long long>(bytes[z]) / (seg.wide[z] ? 16 : 4);
+        if (units > most) most = units;
+    }
+    if (most == 0) return B200Q_OK;
+    const int blocks = static_cast<int>(std::min<long long>((most + 255) / 256, 64));
+    peer_push3_kernel<<<dim3(blocks, world, 3), 256, 0, static_cast<cudaStream_t>(stream)>>>(seg, dst_bases);
+    return check_launch("peer_push3");
 }
 
 }  // extern "C"

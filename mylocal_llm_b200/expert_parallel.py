@@ -6,8 +6,9 @@ bit for bit, the single-GPU layer's (``moe_layer.PackedMoELayer``), whatever the
 * rank ``r`` of ``G`` owns the contiguous expert range ``expert_partition(E, G)[r]`` of every layer;
   router weights, shared expert and norms are replicated; tokens are data-parallel (every rank
   brings the same number of rows per call);
-* per layer: all-gather the rows of all ranks -> every rank routes all rows (replicated, cheap) ->
-  each rank runs the assignments that hit its experts (plus the shared expert for its own rows) ->
+* per layer: every rank routes its own rows -> rows, routing weights and expert ids of all ranks are
+  gathered on every rank -> each rank runs the assignments that hit its experts (plus the shared
+  expert for its own rows) ->
   the route-weighted FP32 term of assignment ``row*k+slot`` travels to the row's home rank -> the
   home rank adds its rows' terms in ascending expert id (the reference's order,
   ``mini_llm/ops/grouped_quantized_experts.py:70-79``).
@@ -56,6 +57,10 @@ class LocalComm:
 
     def all_gather_rows(self, x2d):
         return x2d
+
+    def gather_routed(self, x2d, weights, ids):
+        """Rows, routing weights and expert ids of all ranks, rank-major."""
+        return self.all_gather_rows(x2d), self.all_gather_rows(weights), self.all_gather_rows(ids)
 
     def exchange_terms(self, terms_all, rows_per_rank):
         return terms_all
@@ -115,7 +120,8 @@ class _RawDeviceMemory:
 class PeerComm(LocalComm):
     """Exchange through mapped peer memory (CUDA IPC arenas) with a bounded device-side barrier.
 
-    Arena of each rank: ``[signal pad 256 B | gathered rows | term rows this rank is home of]``,
+    Arena of each rank: ``[signal pad 256 B | gathered rows | gathered routing weights | gathered
+    expert ids | term rows this rank is home of]``,
     sized for ``max_rows`` rows per rank of width ``d_model`` and ``k_out`` terms per row.
     ``group`` is only used at construction, to exchange the 64-byte IPC handles.
     """
@@ -135,7 +141,9 @@ class PeerComm(LocalComm):
         self.device = torch.device("cuda", torch.cuda.current_device())
         align = lambda v: (v + 255) // 256 * 256
         self.rows_offset = self.PAD_BYTES
-        self.terms_offset = align(self.rows_offset + self.world * self.max_rows * self.d_model * 4)
+        self.weights_offset = align(self.rows_offset + self.world * self.max_rows * self.d_model * 4)
+        self.ids_offset = align(self.weights_offset + self.world * self.max_rows * self.k_out * 4)
+        self.terms_offset = align(self.ids_offset + self.world * self.max_rows * self.k_out * 8)
         self.nbytes = align(self.terms_offset + self.max_rows * self.k_out * self.d_model * 4)
         base = ctypes.c_void_p()
         handle = (ctypes.c_ubyte * 64)()
@@ -186,6 +194,28 @@ class PeerComm(LocalComm):
                   ctypes.c_void_p(self.rows_table.data_ptr()), self.rank * nbytes, self.world, _lib.current_stream())
         self.barrier()
         return self._view(self.rows_offset, (self.world * rows, d), x2d.dtype)
+
+    def gather_routed(self, x2d, weights, ids):
+        """One store kernel for the three buffers, one barrier; returns views of the local arena."""
+        torch = _torch()
+        rows, d = x2d.shape
+        self._check(rows, d)
+        k_out = weights.shape[1]
+        if k_out > self.k_out or tuple(ids.shape) != (rows, k_out):
+            raise ValueError(f"PeerComm was sized for {self.k_out} routes per row")
+        if weights.dtype != torch.float32 or ids.dtype != torch.int64:
+            raise TypeError("routing weights must be FP32 and expert ids int64")
+        x2d, weights, ids = x2d.contiguous(), weights.contiguous(), ids.contiguous()
+        xb, wb, ib = rows * d * x2d.element_size(), rows * k_out * 4, rows * k_out * 8
+        _lib.call("b200q_peer_push3", ctypes.c_void_p(x2d.data_ptr()), xb, self.rows_offset + self.rank * xb,
+                  ctypes.c_void_p(weights.data_ptr()), wb, self.weights_offset + self.rank * wb,
+                  ctypes.c_void_p(ids.data_ptr()), ib, self.ids_offset + self.rank * ib,
+                  ctypes.c_void_p(self.pad_table.data_ptr()), self.world, _lib.current_stream())
+        self.barrier()
+        n = self.world * rows
+        return (self._view(self.rows_offset, (n, d), x2d.dtype),
+                self._view(self.weights_offset, (n, k_out), torch.float32),
+                self._view(self.ids_offset, (n, k_out), torch.int64))
 
     def term_buffers(self, rows, k_out, d):
         """(device table of the ranks' term buffers, this rank's own buffer [rows*k_out, d])."""
@@ -311,8 +341,7 @@ class ExpertParallelMoELayer:
         if not x2d.is_contiguous():
             x2d = x2d.contiguous()
         comm, engine = self.comm, self.engine
-        x_all = comm.all_gather_rows(x2d)
-        weights, ids = engine.route(x_all)
+        x_all, weights, ids = comm.gather_routed(x2d, *engine.route(x2d))
         home_lo, home_hi = comm.rank * rows, (comm.rank + 1) * rows
         rows_per_rank = rows * engine.k_out
         if comm.peer:
