@@ -54,6 +54,8 @@ const char *b200q_last_error(void);
 /* Device status word written by kernels whose bounded waits gave up (0 = healthy).
  * Reads the word with a blocking copy: not capturable. */
 int b200q_device_status(int *status_out);
+/* Sets the status word back to 0 (blocking), after the host has handled a reported give-up. */
+int b200q_device_status_clear(void);
 
 /* out[n,k] (fp32) = dequantised W. Replaces PackedGGUFWeight.dequantize_reference
  * (mini_llm/ops/quantized_weight.py:166-250) as a device kernel; bit-exact with it. */

@@ -23,6 +23,7 @@ _c_int, _c_i64, _c_f32, _ptr = ctypes.c_int, ctypes.c_int64, ctypes.c_float, cty
 SIGNATURES = {
     "b200q_abi_version": [],
     "b200q_device_status": [_ptr],
+    "b200q_device_status_clear": [],
     "b200q_dequantize": [_ptr, _c_int, _c_i64, _c_int, _ptr, _ptr],
     "b200q_gemv": [_ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr, _c_int, _ptr],
     "b200q_swiglu": [_ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr, _c_int, _ptr],
@@ -113,6 +114,10 @@ def current_stream():
     """Raw handle of the framework's current CUDA stream (the launch stream of every call)."""
     import torch
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def clear_device_status():
+    call("b200q_device_status_clear")
 
 
 def device_status():

@@ -6,26 +6,52 @@
 
 namespace b200q {
 
-constexpr int RT_TOK = 16;      // tokens per CTA pass of the logits kernel
 constexpr int RT_CHUNK = 2048;  // D positions held in registers at a time
 
 // logits[t, e] = x[t, :] . wt[e, :] + bias[e];  wt is [E, D] row-major FP32.
-// CTA = 8 warps; warp w handles expert rows (blockIdx.x*8 + w) * rpw .. +rpw-1; tokens of tile
-// blockIdx.y are staged in shared memory as FP32.
+// CTA = 8 warps; warp w handles expert rows (blockIdx.x*8 + w) * rpw .. +rpw-1; the TOK tokens of
+// tile blockIdx.y are staged in shared memory as FP32 (vector loads: d is a multiple of 4).
+template <int TOK>
 __global__ void __launch_bounds__(256) router_logits_t_kernel(const void *x, int x_dtype, int t, int d, const float *wt,
                                                               const float *bias, int e, int rpw, float *logits) {
-    extern __shared__ float xs[];   // [RT_TOK][d]
+    extern __shared__ float xs[];   // [TOK][d]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int t0 = blockIdx.y * RT_TOK;
-    const int nt = min(RT_TOK, t - t0);
-    for (int i = tid; i < nt * d; i += 256) xs[i] = load_as_float(x, x_dtype, static_cast<size_t>(t0) * d + i);
+    const int t0 = blockIdx.y * TOK;
+    const int nt = min(TOK, t - t0);
+    {
+        const size_t esize = x_dtype == B200Q_F32 ? 4 : 2;
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(x) % (4 * esize)) == 0;
+        const size_t base = static_cast<size_t>(t0) * d;
+        for (int i = tid * 4; i < nt * d; i += 256 * 4) {
+            float v[4];
+            if (vec_ok) {
+                if (x_dtype == B200Q_F32) {
+                    const float4 q = *reinterpret_cast<const float4 *>(static_cast<const float *>(x) + base + i);
+                    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+                } else {
+                    const uint2 raw = *reinterpret_cast<const uint2 *>(static_cast<const uint16_t *>(x) + base + i);
+                    if (x_dtype == B200Q_F16) {
+                        v[0] = half_bits_to_float(raw.x & 0xffffu); v[1] = half_bits_to_float(raw.x >> 16);
+                        v[2] = half_bits_to_float(raw.y & 0xffffu); v[3] = half_bits_to_float(raw.y >> 16);
+                    } else {
+                        v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xffff0000u);
+                        v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xffff0000u);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = load_as_float(x, x_dtype, base + i + j);
+            }
+            *reinterpret_cast<float4 *>(xs + i) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+    }
     __syncthreads();
     for (int r = 0; r < rpw; ++r) {
         const int row = (blockIdx.x * 8 + warp) * rpw + r;
         if (row >= e) break;
-        float acc[RT_TOK];
+        float acc[TOK];
 #pragma unroll
-        for (int i = 0; i < RT_TOK; ++i) acc[i] = 0.f;
+        for (int i = 0; i < TOK; ++i) acc[i] = 0.f;
         for (int c0 = 0; c0 < d; c0 += RT_CHUNK) {
             float4 w[RT_CHUNK / 128];
 #pragma unroll
@@ -35,7 +61,7 @@ __global__ void __launch_bounds__(256) router_logits_t_kernel(const void *x, int
                                : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
-            for (int tt = 0; tt < RT_TOK; ++tt) {
+            for (int tt = 0; tt < TOK; ++tt) {
                 if (tt < nt) {
                     float s = 0.f;
 #pragma unroll
@@ -54,7 +80,7 @@ __global__ void __launch_bounds__(256) router_logits_t_kernel(const void *x, int
             }
         }
 #pragma unroll
-        for (int tt = 0; tt < RT_TOK; ++tt) {
+        for (int tt = 0; tt < TOK; ++tt) {
             if (tt < nt) {
                 const float s = warp_sum(acc[tt]);
                 if (lane == 0) logits[static_cast<size_t>(t0 + tt) * e + row] = s + (bias ? bias[row] : 0.f);
@@ -272,19 +298,20 @@ extern "C" int b200q_router_logits_t(const void *x, int x_dtype, int t, int d, c
     if (!dtype_valid(x_dtype)) return fail(B200Q_EINVAL, "router_logits_t: bad dtype");
     if (t <= 0 || d <= 0 || e <= 0 || d % 4) return fail(B200Q_EINVAL, "router_logits_t: bad shape (d %% 4 == 0)");
     if (reinterpret_cast<uintptr_t>(wt) & 15) return fail(B200Q_EINVAL, "router_logits_t: weight must be 16-byte aligned");
-    const size_t smem = static_cast<size_t>(RT_TOK) * d * sizeof(float);
+    // 8 tokens per CTA (three CTAs per SM at d = 2048) up to 128 rows, 16 beyond
+    const int tok = t <= 128 ? 8 : 16;
+    const size_t smem = static_cast<size_t>(tok) * d * sizeof(float);
     if (smem > 200 * 1024) return fail(B200Q_EUNSUPPORTED, "router_logits_t: d=%d too large", d);
-    cudaError_t err = cudaFuncSetAttribute(router_logits_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           200 * 1024);
+    auto kernel = tok == 8 ? router_logits_t_kernel<8> : router_logits_t_kernel<16>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (err != cudaSuccess) {
         cudaGetLastError();
         return fail(B200Q_ECUDA, "router_logits_t: %s", cudaGetErrorString(err));
     }
-    const int tiles = (t + RT_TOK - 1) / RT_TOK;
+    const int tiles = (t + tok - 1) / tok;
     int rpw = 4;   // fewer rows per warp when the grid would leave SMs idle
-    while (rpw > 1 && static_cast<long long>((e + 8 * rpw - 1) / (8 * rpw)) * tiles < sm_count()) rpw >>= 1;
+    while (rpw > 1 && static_cast<long long>((e + 8 * rpw - 1) / (8 * rpw)) * tiles < 2LL * sm_count()) rpw >>= 1;
     dim3 grid((e + 8 * rpw - 1) / (8 * rpw), tiles);
-    router_logits_t_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(x, x_dtype, t, d, wt, bias, e, rpw,
-                                                                                   logits);
+    kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(x, x_dtype, t, d, wt, bias, e, rpw, logits);
     return check_launch("router_logits_t");
 }

@@ -85,4 +85,12 @@ int b200q_device_status(int *status_out) {
     return B200Q_OK;
 }
 
+int b200q_device_status_clear(void) {
+    int *word = b200q::device_status_word();
+    if (!word) return b200q::fail(B200Q_ECUDA, "no CUDA device / status word");
+    cudaError_t err = cudaMemset(word, 0, sizeof(int));
+    if (err != cudaSuccess) return b200q::fail(B200Q_ECUDA, "status clear: %s", cudaGetErrorString(err));
+    return B200Q_OK;
+}
+
 }  // extern "C"

@@ -157,6 +157,29 @@ def test_peer_comm_in_a_world_of_one(cuda):
         dist.destroy_process_group()
 
 
+def test_barrier_gives_up_after_its_limit_and_reports_it(cuda):
+    """A peer that never arrives: the barrier returns after its time limit with status 201, the
+    context stays usable, and the host can clear the word. (The absent peer is a second pad on the
+    same GPU that nothing ever signals - no second kernel is involved.)"""
+    import ctypes
+    import time
+    torch = cuda
+    assert _lib.device_status() == 0
+    pads = torch.zeros(2, 64, dtype=torch.int32, device="cuda")            # two signal pads of 256 bytes
+    table = torch.tensor([pads[0].data_ptr(), pads[1].data_ptr()], dtype=torch.int64, device="cuda")
+    t0 = time.perf_counter()
+    _lib.call("b200q_peer_barrier", ctypes.c_void_p(table.data_ptr()), 0, 2, 50, _lib.current_stream())
+    assert _lib.device_status() == 201
+    assert time.perf_counter() - t0 < 5.0
+    assert int(pads[1, 0].item()) == 1                                     # rank 0 did signal its peer
+    _lib.clear_device_status()
+    assert _lib.device_status() == 0
+    # the context is intact: a normal kernel still runs
+    assert float(torch.ones(4, device="cuda").sum().item()) == 4.0
+    with pytest.raises(ValueError):
+        _lib.call("b200q_peer_barrier", ctypes.c_void_p(table.data_ptr()), 2, 2, 50, _lib.current_stream())
+
+
 def test_local_comm_layer_equals_packed_layer(cuda):
     torch = cuda
     bank, w_router, shared, gate = build_model(torch, with_gate=True, seed=8)
