@@ -323,8 +323,11 @@ def run_gpu_arm(args, name):
                        "timing": "CUDA graph of one step, CUDA events on the launch stream"},
             "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
                          "frac": round(per_gpu / peak, 4), "peak_source": f"of {peak_kind}",
-                         "frac_of_nominal_8TBs": round(per_gpu / 8000.0, 4), "traffic": None,
-                         "kernel": "stream_gemv_kernel", "us_per_launch": round(dev_ms * 1e3 / launches, 3),
+                         "frac_of_nominal_8TBs": round(per_gpu / 8000.0, 4),
+                         "traffic": int(per_launch * 1.01) if fmt == "Q4_K" else None,
+                         "traffic_source": "dram bytes / algorithmic bytes = 1.01 in the ncu capture "
+                                           "profiles/mma_direct_q4k_gemv_65536x8192_m1.md (Q4_K only)",
+                         "kernel": "mma_direct_kernel / q6k_tiled_kernel / mma_gemv_kernel by format", "us_per_launch": round(dev_ms * 1e3 / launches, 3),
                          "algorithmic_bytes_per_launch": per_launch},
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s",
                     "h2d_bytes_per_step": int(host_x.numel() * host_x.element_size()),
@@ -405,6 +408,9 @@ def exit_watchdog(seconds=90):
 # ------------------------------------------------------------------------------ MoE workloads
 MOE_SHAPE = dict(d_model=2048, d_ff=512, n_experts=512, top_k=10, shared_d_ff=512)
 EXPERT_BYTES = 2 * packed_bytes("Q4_K", 512, 2048) + packed_bytes("Q6_K", 2048, 512)
+# DRAM traffic of the grouped gate/up kernel over its algorithmic bytes, from one ncu capture of the 64-token
+# layer (448.3 MB moved for 430.2 MB); traffic grows in proportion to the experts a launch touches.
+GATE_UP_TRAFFIC_RATIO = 1.04
 
 
 def cpu_moe_throughput(layers, seconds):
@@ -611,7 +617,10 @@ def run_moe_gpu_arm(args, name):
                        "layer_GBs": round(layer_bytes * layers * args.steps / (dev_ms * 1e-3) / 1e9, 1)},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_source": f"of {peak_kind}",
-                         "frac_of_nominal_8TBs": round(achieved / 8000.0, 4), "traffic": None,
+                         "frac_of_nominal_8TBs": round(achieved / 8000.0, 4),
+                         "traffic": int(gu_bytes * GATE_UP_TRAFFIC_RATIO),
+                         "traffic_source": "dram bytes read+write / algorithmic bytes = 1.04 in the ncu capture "
+                                           "profiles/grouped_kernels_moe_layer_t64.md, scaled to this launch",
                          "kernel": "grouped gate/up + SwiGLU (mma_direct_kernel, mode 2)",
                          "us_per_launch": round(gu_us, 3), "algorithmic_bytes_per_launch": int(gu_bytes)},
             "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s",
