@@ -1,6 +1,6 @@
 """Generate the committed golden vectors by running the REFERENCE implementation.
 
-Run in a container that has the reference tree (default ``/root/reference``):
+Run where the reference tree is available (its location: ``MYLOCAL_REFERENCE_ROOT``):
 
     python tests/golden/make_golden.py
 
