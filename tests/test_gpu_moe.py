@@ -68,8 +68,11 @@ def test_router_topk_shapes_against_oracle(cuda, rows, n, k):
 
 
 # -------------------------------------------------------------------------------------- plan
+# (7, 6, 4): more routes than experts, so rows repeat experts and the kernel takes its ordered pass;
+# (600, 3, 4096): the per-expert row bitmasks would not fit in shared memory, ordered pass as well
 @pytest.mark.parametrize("rows,k,e,dtype", [(1, 10, 512, "int64"), (11, 3, 9, "int64"), (256, 10, 512, "int32"),
-                                            (700, 4, 33, "int64"), (5, 2, 4096, "int32")])
+                                            (700, 4, 33, "int64"), (5, 2, 4096, "int32"), (7, 6, 4, "int64"),
+                                            (600, 3, 4096, "int32"), (2048, 11, 513, "int64")])
 def test_routing_plan_is_the_stable_sort_by_expert(cuda, rows, k, e, dtype):
     rng = np.random.default_rng(rows * k + e)
     ids = np.stack([rng.choice(e, size=k, replace=k > e) for _ in range(rows)]).astype(dtype)
@@ -89,6 +92,23 @@ def test_routing_plan_is_the_stable_sort_by_expert(cuda, rows, k, e, dtype):
     expect = [(ex, offsets[ex] + r, min(moe_ops.SEGMENT_CAP, counts[ex] - r))
               for ex in range(e) for r in range(0, counts[ex], moe_ops.SEGMENT_CAP)]
     assert [(int(a), int(b), int(c)) for a, b, c in zip(seg_e, seg_b, seg_c)] == expect
+
+
+def test_routing_plan_skips_one_expert(cuda):
+    rng = np.random.default_rng(3)
+    rows, k, e, skip = 40, 3, 12, 5
+    ids = np.stack([rng.choice(e, size=k, replace=False) for _ in range(rows)]).astype(np.int64)
+    plan = moe_ops.moe_plan(to_cuda(cuda, ids), e, skip_expert=skip)
+    order, counts, offsets = po.routing_plan(ids, e)
+    np.testing.assert_array_equal(plan.counts.cpu().numpy(), counts)
+    got_order = plan.order.cpu().numpy()
+    lo, hi = offsets[skip], offsets[skip + 1]
+    np.testing.assert_array_equal(got_order[:lo], order[:lo])                    # executed experts: stable order
+    np.testing.assert_array_equal(got_order[hi:], order[hi:])
+    assert sorted(got_order[lo:hi]) == sorted(order[lo:hi])                      # skipped: any order, all present
+    nseg = int(plan.num_segments.item())
+    assert skip not in plan.seg_expert.cpu().numpy()[:nseg].tolist()
+    assert nseg == sum(-(-int(c) // moe_ops.SEGMENT_CAP) for ex, c in enumerate(counts) if ex != skip)
 
 
 def test_routing_plan_flags_out_of_range_ids(cuda):
