@@ -22,6 +22,7 @@ from .experts_inference import (ExpertsInference, PackedExpertBank, ResidentExpe
 from .grouped_quantized_experts import (grouped_quantized_experts_forward,
                                         supports_grouped_quantized_experts)
 from .moe_layer import PackedMoELayer, RMSNormInference
+from .gguf_index import GGUFPackedIndex, project_gguf_linear, project_gguf_swiglu, resolve_gguf_weight
 
 __all__ = [
     "RouterInference", "expert_topk_forward", "try_normalized_topk", "ExpertsInference", "PackedExpertBank",
@@ -29,5 +30,6 @@ __all__ = [
     "supports_grouped_quantized_experts", "PackedMoELayer", "RMSNormInference",
     "BLOCK_FORMATS", "PackedGGUFWeight", "SUPPORTED_GPU_PACKED_FORMATS", "DevicePackedGGUFWeight",
     "PackedExpertFFNInference", "packed_to_device", "quantized_linear", "quantized_swiglu",
-    "supports_packed_gpu_type",
+    "supports_packed_gpu_type", "GGUFPackedIndex", "project_gguf_linear", "project_gguf_swiglu",
+    "resolve_gguf_weight",
 ]
