@@ -644,19 +644,177 @@ def run_moe_gpu_arm(args, name):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------ Llama decode workloads
+# Third configuration: SmolLM2-1.7B shape, random-init Q8_0 weights (embedding and untied LM head included),
+# 512-token prompt, then greedy decode; a step = one decode_one() of the whole batch.
+LLAMA_SHAPE = dict(vocab_size=49152, hidden_size=2048, intermediate_size=8192, num_hidden_layers=24,
+                   num_attention_heads=32, num_key_value_heads=32, head_dim=64, max_position_embeddings=2048,
+                   rope_theta=10000.0, rms_norm_eps=1e-5)
+LLAMA_WORKLOADS = {"llama_decode_b1": 1, "llama_decode_b16": 16}
+LLAMA_PROMPT, LLAMA_NEW = 512, 128
+
+
+def llama_bytes_per_step():
+    c = LLAMA_SHAPE
+    d, f, v = c["hidden_size"], c["intermediate_size"], c["vocab_size"]
+    per_layer = 4 * packed_bytes("Q8_0", d, d) + 2 * packed_bytes("Q8_0", f, d) + packed_bytes("Q8_0", d, f)
+    return c["num_hidden_layers"] * per_layer + packed_bytes("Q8_0", v, d)          # + LM head, read every step
+
+
+def run_llama_reference_arm(args, name):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    batch = LLAMA_WORKLOADS[name]
+    per_step = max(1.0, 20.0 / max(1, args.steps + args.warmup))
+    runs = [cpu_gemv_throughput("Q8_0", 8192, 2048, batch if batch <= 8 else 8, 4, per_step)
+            for _ in range(args.warmup + args.steps)][args.warmup:]
+    gbs = statistics.mean(r[0] for r in runs)
+    passes = -(-batch // 8)                      # the CPU kernel handles the batch in groups like the GPU path
+    tps = batch * gbs * 1e9 / (llama_bytes_per_step() * passes)
+    line = {
+        "impl": "reference", "metric": "decode tokens/s", "value": round(tps, 4), "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * batch / tps, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "batch": batch, **LLAMA_SHAPE, "format": "Q8_0",
+                   "l2": "CPU run: the reference's packed GEMV on a bounded row sample, scaled to the bytes of "
+                         "one decode step (attention and norms not included)"},
+        "cpu_baseline": {"value": round(tps, 4), "unit": "tokens/s", "cores": runs[0][2], "kind": runs[0][1],
+                         "sample": runs[0][3]},
+        "e2e": {"value": round(tps, 4), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def run_llama_gpu_arm(args, name):
+    import torch
+    import torch.distributed as dist
+    from mylocal_llm_b200 import _lib
+    from mylocal_llm_b200.llama_model import ExternalLlamaConfig, ExternalLlamaModel
+
+    batch = LLAMA_WORKLOADS[name]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the kernels)")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    model = ExternalLlamaModel.synthetic(ExternalLlamaConfig(**LLAMA_SHAPE), seed=rank)
+    state = model.create_generation_state(batch, LLAMA_PROMPT + LLAMA_NEW + 64)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(5 + rank)
+    prompt = torch.randint(0, LLAMA_SHAPE["vocab_size"], (batch, LLAMA_PROMPT), device="cuda", generator=gen)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        logits = model.prefill(prompt, state)
+        token = logits.argmax(dim=-1)
+        host_token = torch.empty(batch, dtype=torch.int64).pin_memory()
+        calls = []
+        real_call = _lib.call
+        _lib.call = lambda fn, *a: (calls.append(fn), real_call(fn, *a))[1]
+        token.copy_(model.decode_one(token, state).argmax(dim=-1))            # eager step: warm-up + launch count
+        _lib.call = real_call
+        launches_per_step = len(calls)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            token.copy_(model.decode_one(token, state).argmax(dim=-1))        # greedy: next token stays on the device
+
+        def barrier():
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        budget = state.horizon - LLAMA_PROMPT - 2
+        steps = min(args.steps, (budget - 2 * max(3, args.warmup)) // 2)
+        for _ in range(max(3, args.warmup)):
+            graph.replay()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            graph.replay()
+        e1.record(stream)
+        barrier()
+        dev_ms = e0.elapsed_time(e1)
+
+        def e2e_step():
+            graph.replay()
+            host_token.copy_(token, non_blocking=True)
+
+        for _ in range(max(3, args.warmup)):
+            e2e_step()
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record(stream)
+        for _ in range(steps):
+            e2e_step()
+            stream.synchronize()                  # the sampled token is needed on the host before the next step
+        f1.record(stream)
+        barrier()
+        e2e_ms = f0.elapsed_time(f1)
+        clocks = sampler.stop() if rank == 0 else None
+
+    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = (float(v) for v in times.cpu())
+    if _lib.device_status():
+        raise SystemExit("device status word is set: a kernel gave up on a bounded wait")
+    if rank == 0:
+        value = batch * world * steps / (dev_ms * 1e-3)
+        e2e_value = batch * world * steps / (e2e_ms * 1e-3)
+        peak, peak_kind = measured_peaks()
+        step_bytes = llama_bytes_per_step() * (-(-batch // 8))
+        achieved = step_bytes * steps / (dev_ms * 1e-3) / 1e9
+        line = {
+            "metric": "decode tokens/s", "value": round(value, 2), "unit": "tokens/s", "n_gpus": world,
+            "steps": steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / steps, 5),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": name, "batch": batch, "prompt_tokens": LLAMA_PROMPT, **LLAMA_SHAPE,
+                       "format": "Q8_0 (all linears, embedding, untied LM head)", "activation": "bfloat16, FP32 residual",
+                       "packed_bytes_resident": model.packed_bytes,
+                       "parallelism": "replicas only" if world > 1 else "single GPU",
+                       "l2": f"{llama_bytes_per_step() / 1e6:.0f} MB of packed weights read per step (> L2)",
+                       "timing": "CUDA graph of one greedy decode step, CUDA events on the launch stream"},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "peak_source": f"of {peak_kind}", "traffic": None,
+                         "kernel": "whole decode step: packed weight bytes per step / step time",
+                         "algorithmic_bytes_per_launch": int(step_bytes)},
+            "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": int(host_token.numel() * 8)},
+            "gpu_launches": launches_per_step * steps, "clocks": clocks,
+        }
+        print(json.dumps(line))
+    sys.stdout.flush()
+    exit_watchdog()
+    graph.reset()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(MOE_WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(MOE_WORKLOADS) + sorted(LLAMA_WORKLOADS))
     ap.add_argument("--exchange", default="peer", choices=["peer", "collective"],
                     help="expert-parallel exchange at N > 1: peer-memory stores + device barrier, or NCCL")
     ap.add_argument("--skip-side", action="store_true", help="omit the dense-GEMV side measurements")
     ap.add_argument("--skip-cpu-baseline", action="store_true",
                     help="omit the host-core baseline leg (exploratory runs only)")
     args = ap.parse_args()
+    if args.workload in LLAMA_WORKLOADS:
+        (run_llama_reference_arm if args.impl == "reference" else run_llama_gpu_arm)(args, args.workload)
+        return
     moe = args.workload in MOE_WORKLOADS
     if args.impl == "reference":
         (run_moe_reference_arm if moe else run_reference_arm)(args, args.workload)

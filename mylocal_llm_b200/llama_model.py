@@ -1,0 +1,282 @@
+"""Llama-family decoder whose every linear runs on the packed GGUF kernels.
+
+Mirrors the surface of the reference's ``ExternalLlamaModel``
+(``mini_llm/external/llama_model.py:16-178``: ``expected_shapes``, ``set_weights`` with canonical HF
+names, ``create_generation_state``, ``prefill``, ``decode_one``) and of its configuration
+(``mini_llm/external/config.py``). The reference expands GGUF weights to dense FP16/FP32 for this
+adapter; here they stay packed and resident in HBM, which is the point of the exercise:
+
+* q/k/v/o, gate/up (one fused SwiGLU launch), down and the LM head are ``quantized_linear`` /
+  ``quantized_swiglu`` on ``DevicePackedGGUFWeight`` (tile layouts where they exist);
+* RMSNorm is ``b200q_rmsnorm`` / the fused residual-add variant; the residual stream is FP32;
+* embedding rows are gathered as packed bytes and decoded by ``b200q_dequantize``;
+* rotate-half RoPE, the KV cache and softmax attention are plain torch ops (bookkeeping around the
+  packed kernels, not part of the packed path). The decode step has static shapes - the cache is
+  written at a device-side position and attention runs over the whole horizon under a mask - so
+  ``decode_one`` can be captured in a CUDA graph.
+"""
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from .moe_layer import RMSNormInference
+from .quantized_linear import (DevicePackedGGUFWeight, dequantize_device, packed_to_device, quantized_linear,
+                               quantized_swiglu, retile_enabled, retile_weight)
+from .quantized_weight import PackedGGUFWeight, block_format
+
+
+def _torch():
+    import torch
+    return torch
+
+
+@dataclass
+class ExternalLlamaConfig:
+    vocab_size: int
+    hidden_size: int
+    intermediate_size: int
+    num_hidden_layers: int
+    num_attention_heads: int
+    num_key_value_heads: int
+    head_dim: int
+    max_position_embeddings: int = 2048
+    rope_theta: float = 10000.0
+    rms_norm_eps: float = 1e-5
+    tie_word_embeddings: bool = False
+
+    def validate(self):
+        if min(self.vocab_size, self.hidden_size, self.intermediate_size, self.num_hidden_layers,
+               self.num_attention_heads, self.num_key_value_heads, self.head_dim, self.max_position_embeddings) <= 0:
+            raise ValueError("Llama configuration values must be positive")
+        if self.num_attention_heads % self.num_key_value_heads:
+            raise ValueError("num_attention_heads must be a multiple of num_key_value_heads")
+        if self.head_dim % 2:
+            raise ValueError("head_dim must be even for rotary embeddings")
+
+
+class GenerationState:
+    """KV cache ``[layers, B, kv_heads, horizon, head_dim]`` and the device-side position."""
+
+    def __init__(self, config, batch, horizon, dtype, device):
+        torch = _torch()
+        shape = (config.num_hidden_layers, batch, config.num_key_value_heads, horizon, config.head_dim)
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.position = torch.zeros(1, dtype=torch.int64, device=device)      # tokens already in the cache
+        self.length = 0                                                        # host copy, for checks only
+        self.batch, self.horizon = batch, horizon
+
+
+class ExternalLlamaModel:
+    def __init__(self, config, *, dtype="bfloat16", device="cuda"):
+        if not isinstance(config, ExternalLlamaConfig):
+            raise TypeError("config must be ExternalLlamaConfig")
+        config.validate()
+        torch = _torch()
+        if dtype not in ("float32", "float16", "bfloat16"):
+            raise ValueError("dtype must be float32, float16 or bfloat16")
+        self.config, self.dtype, self.device = config, getattr(torch, dtype), device
+        self._loaded = False
+
+    def expected_shapes(self):
+        cfg = self.config
+        d, f, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+        q, kv = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+        result = {"model.embed_tokens.weight": (v, d), "model.norm.weight": (d,)}
+        for i in range(cfg.num_hidden_layers):
+            stem = f"model.layers.{i}."
+            result.update({
+                stem + "input_layernorm.weight": (d,), stem + "post_attention_layernorm.weight": (d,),
+                stem + "self_attn.q_proj.weight": (q, d), stem + "self_attn.k_proj.weight": (kv, d),
+                stem + "self_attn.v_proj.weight": (kv, d), stem + "self_attn.o_proj.weight": (d, q),
+                stem + "mlp.gate_proj.weight": (f, d), stem + "mlp.up_proj.weight": (f, d),
+                stem + "mlp.down_proj.weight": (d, f),
+            })
+        if not cfg.tie_word_embeddings:
+            result["lm_head.weight"] = (v, d)
+        return result
+
+    # ------------------------------------------------------------------------------ weights
+    def _matrix(self, value, *, tile=True):
+        """Host ``PackedGGUFWeight`` / device packed weight -> device packed weight (tiled if possible)."""
+        if isinstance(value, PackedGGUFWeight):
+            value = packed_to_device(value)
+        if not isinstance(value, DevicePackedGGUFWeight):
+            raise TypeError("Llama projection weights must be packed GGUF matrices")
+        if tile and retile_enabled():
+            value = retile_weight(value, force=self.dtype != _torch().float32)
+        return value
+
+    def set_weights(self, weights, *, strict=True):
+        """Bind canonical HF-named tensors: matrices packed (host or device), norm vectors dense.
+        Incomplete or mis-shaped imports are rejected before anything is uploaded."""
+        torch = _torch()
+        expected = self.expected_shapes()
+        missing = sorted(set(expected) - set(weights))
+        optional = {"lm_head.weight"} if self.config.tie_word_embeddings else set()
+        extra = sorted(set(weights) - set(expected) - optional)
+        if missing or (strict and extra):
+            raise ValueError(f"Invalid Llama weight names: missing={missing[:5]}, extra={extra[:5]}")
+        for name, shape in expected.items():
+            if tuple(int(s) for s in weights[name].shape) != shape:
+                raise ValueError(f"{name}: expected shape {shape}, got {tuple(weights[name].shape)}")
+        cfg = self.config
+
+        def norm(name):
+            module = RMSNormInference(cfg.hidden_size, eps=cfg.rms_norm_eps)
+            gamma = torch.as_tensor(np.asarray(weights[name], dtype=np.float32)).to(self.device, self.dtype)
+            module.set_weights(gamma.contiguous())
+            return module
+
+        self.embed = self._matrix(weights["model.embed_tokens.weight"], tile=False)     # rows are gathered
+        self.lm_head = self.embed if cfg.tie_word_embeddings else self._matrix(weights["lm_head.weight"])
+        if cfg.tie_word_embeddings and retile_enabled():
+            self.lm_head = self._matrix(self.embed)
+        self.final_norm = norm("model.norm.weight")
+        self.layers = []
+        for i in range(cfg.num_hidden_layers):
+            p = f"model.layers.{i}."
+            self.layers.append({
+                "norm1": norm(p + "input_layernorm.weight"), "norm2": norm(p + "post_attention_layernorm.weight"),
+                "q": self._matrix(weights[p + "self_attn.q_proj.weight"]),
+                "k": self._matrix(weights[p + "self_attn.k_proj.weight"]),
+                "v": self._matrix(weights[p + "self_attn.v_proj.weight"]),
+                "o": self._matrix(weights[p + "self_attn.o_proj.weight"]),
+                "gate": self._matrix(weights[p + "mlp.gate_proj.weight"]),
+                "up": self._matrix(weights[p + "mlp.up_proj.weight"]),
+                "down": self._matrix(weights[p + "mlp.down_proj.weight"]),
+            })
+            if self.layers[-1]["gate"].quant_type != self.layers[-1]["up"].quant_type:
+                # one layout for the fused launch: keep both native
+                self.layers[-1]["gate"] = self._matrix(weights[p + "mlp.gate_proj.weight"], tile=False)
+                self.layers[-1]["up"] = self._matrix(weights[p + "mlp.up_proj.weight"], tile=False)
+        half = cfg.head_dim // 2
+        inv = 1.0 / (float(cfg.rope_theta) ** (2.0 * np.arange(half) / cfg.head_dim))
+        ang = np.arange(cfg.max_position_embeddings)[:, None] * inv[None, :]
+        self._cos = torch.as_tensor(np.cos(ang), dtype=torch.float32).to(self.device)
+        self._sin = torch.as_tensor(np.sin(ang), dtype=torch.float32).to(self.device)
+        self._loaded = True
+
+    @property
+    def packed_bytes(self):
+        total = self.embed.nbytes + (0 if self.config.tie_word_embeddings else self.lm_head.nbytes)
+        for layer in self.layers:
+            total += sum(layer[n].nbytes for n in ("q", "k", "v", "o", "gate", "up", "down"))
+        return total
+
+    # ------------------------------------------------------------------------------ running
+    def _require_weights(self):
+        if not self._loaded:
+            raise RuntimeError("External weights have not been loaded")
+
+    def create_generation_state(self, batch_size=1, max_length=None):
+        self._require_weights()
+        max_length = self.config.max_position_embeddings if max_length is None else int(max_length)
+        if not 1 <= max_length <= self.config.max_position_embeddings:
+            raise ValueError("Requested KV horizon exceeds configured positions")
+        return GenerationState(self.config, int(batch_size), max_length, self.dtype, self.device)
+
+    def _embed(self, token_ids):
+        torch = _torch()
+        v, d = self.embed.shape
+        qk, qb = block_format(self.embed.quant_type)
+        rows = self.embed.data.view(v, d // qk * qb).index_select(0, token_ids.reshape(-1)).contiguous()
+        return dequantize_device(rows.reshape(-1), rows.shape[0], d, self.embed.quant_type)      # FP32 [n, d]
+
+    def _rope(self, x, positions):
+        """x [B, T, H, Dh] (FP32), positions [T] int64 device tensor; rotate-half layout."""
+        torch = _torch()
+        half = x.shape[-1] // 2
+        cos = self._cos.index_select(0, positions)[None, :, None, :]
+        sin = self._sin.index_select(0, positions)[None, :, None, :]
+        x0, x1 = x[..., :half], x[..., half:]
+        return torch.cat([x0 * cos - x1 * sin, x0 * sin + x1 * cos], dim=-1)
+
+    def _forward(self, token_ids, state, positions, mask):
+        """token_ids [B, T]; positions [T] device int64; mask [T, horizon] additive FP32. Returns the
+        final normalised hidden states [B*T, d] in the model dtype."""
+        torch = _torch()
+        cfg = self.config
+        b, t = token_ids.shape
+        heads, kv_heads, dh = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        residual = self._embed(token_ids)                                         # FP32 [B*T, d]
+        hidden = self.layers[0]["norm1"].forward_residual(residual)
+        for i, layer in enumerate(self.layers):
+            q = quantized_linear(hidden, layer["q"], out_dtype=torch.float32).reshape(b, t, heads, dh)
+            k = quantized_linear(hidden, layer["k"], out_dtype=torch.float32).reshape(b, t, kv_heads, dh)
+            v = quantized_linear(hidden, layer["v"], out_dtype=torch.float32).reshape(b, t, kv_heads, dh)
+            q, k = self._rope(q, positions), self._rope(k, positions)
+            state.k[i].index_copy_(2, positions, k.permute(0, 2, 1, 3).to(self.dtype))
+            state.v[i].index_copy_(2, positions, v.permute(0, 2, 1, 3).to(self.dtype))
+            keys, values = state.k[i].float(), state.v[i].float()                 # [B, kv, horizon, dh]
+            if kv_heads != heads:
+                keys = keys.repeat_interleave(heads // kv_heads, dim=1)
+                values = values.repeat_interleave(heads // kv_heads, dim=1)
+            scores = torch.matmul(q.permute(0, 2, 1, 3), keys.transpose(-1, -2)) * (dh ** -0.5) + mask
+            ctx = torch.matmul(torch.softmax(scores, dim=-1), values)            # [B, heads, T, dh]
+            ctx = ctx.permute(0, 2, 1, 3).reshape(b * t, heads * dh).to(self.dtype).contiguous()
+            attn = quantized_linear(ctx, layer["o"])
+            residual, hidden = layer["norm2"].forward_residual_add(residual, attn)
+            act = quantized_swiglu(hidden, layer["gate"], layer["up"])
+            ffn = quantized_linear(act, layer["down"])
+            nxt = self.layers[i + 1]["norm1"] if i + 1 < len(self.layers) else self.final_norm
+            residual, hidden = nxt.forward_residual_add(residual, ffn)
+        return hidden
+
+    def prefill(self, token_ids, state):
+        """token_ids [B, T] int64 CUDA tensor; fills the cache from position 0; returns the logits of
+        the last position, FP32 [B, vocab]."""
+        self._require_weights()
+        torch = _torch()
+        b, t = token_ids.shape
+        if b != state.batch or t > state.horizon:
+            raise ValueError("prompt does not fit the generation state")
+        positions = torch.arange(t, device=self.device)
+        cols = torch.arange(state.horizon, device=self.device)
+        mask = torch.where(cols[None, :] <= positions[:, None], 0.0, float("-inf")).float()
+        hidden = self._forward(token_ids, state, positions, mask).reshape(b, t, -1)
+        state.position.fill_(t)
+        state.length = t
+        return quantized_linear(hidden[:, -1].contiguous(), self.lm_head, out_dtype=torch.float32)
+
+    def decode_one(self, token_ids, state):
+        """token_ids [B] int64 CUDA tensor: appends one position; returns FP32 logits [B, vocab].
+        All shapes are static and the position lives on the device (CUDA-graph capturable; the host
+        counter ``state.length`` is advisory and is not advanced inside a captured graph)."""
+        self._require_weights()
+        torch = _torch()
+        if state.length >= state.horizon:
+            raise ValueError("generation state is full")
+        positions = state.position.clone()
+        cols = torch.arange(state.horizon, device=self.device)
+        mask = torch.where(cols[None, :] <= positions[:, None], 0.0, float("-inf")).float()
+        hidden = self._forward(token_ids.reshape(-1, 1), state, positions, mask)
+        state.position.add_(1)
+        state.length += 1
+        return quantized_linear(hidden, self.lm_head, out_dtype=torch.float32)
+
+    @classmethod
+    def synthetic(cls, config, *, fmt="Q8_0", dtype="bfloat16", seed=0, device="cuda"):
+        """Random-init model with packed weights generated on the device (benchmark input): uniform
+        random codes with small finite block scales, layout and sizes of a real ``fmt`` model."""
+        torch = _torch()
+        if fmt != "Q8_0":
+            raise NotImplementedError("synthetic weights are generated for Q8_0")
+        model = cls(config, dtype=dtype, device=device)
+        gen = torch.Generator(device=device)
+
+        def matrix(shape, index):
+            gen.manual_seed(seed * 100003 + index)
+            blocks = shape[0] * shape[1] // 32
+            raw = torch.randint(0, 256, (blocks, 34), dtype=torch.uint8, device=device, generator=gen)
+            scale = np.frombuffer(np.float16(0.02 / 127 * 3).tobytes(), np.uint8)
+            raw[:, 0], raw[:, 1] = int(scale[0]), int(scale[1])
+            return DevicePackedGGUFWeight(raw.reshape(-1), shape, "Q8_0")
+
+        weights, index = {}, 0
+        for name, shape in model.expected_shapes().items():
+            index += 1
+            weights[name] = matrix(shape, index) if len(shape) == 2 else np.ones(shape, np.float32)
+        model.set_weights(weights)
+        return model
