@@ -97,7 +97,45 @@ __global__ void __launch_bounds__(256) q4k_retile_kernel(const uint8_t *src, uin
 
 using Q6Fn = void (*)(const Q6TiledArgs);
 
-// Runs the tiled kernel for a mode 0 or mode 3 request whose weights are in the tile layout.
+// Q8_0 <-> tile layout. One thread per (tile, lane): the 16 code words of its two rows (codes +128);
+// lanes 0-15 also move one row's eight block scales. FORWARD: native -> tiled.
+template <bool FORWARD>
+__global__ void __launch_bounds__(256) q8_retile_kernel(const uint8_t *src, uint8_t *dst, long long tiles, int nsb) {
+    const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    const long long tile = idx >> 5;
+    if (tile >= tiles) return;
+    const int lane = static_cast<int>(idx & 31), g = lane >> 2, tig = lane & 3;
+    const long long group = tile / nsb;
+    const int sb = static_cast<int>(tile - group * nsb);
+    const size_t row_bytes = static_cast<size_t>(nsb) * 272;
+    const uint8_t *in = FORWARD ? src : src + static_cast<size_t>(tile) * Q8T_TILE_BYTES;
+    uint8_t *out = FORWARD ? dst + static_cast<size_t>(tile) * Q8T_TILE_BYTES : dst;
+    for (int half = 0; half < 2; ++half) {
+        const size_t row_off = (static_cast<size_t>(group) * 16 + g + 8 * half) * row_bytes + static_cast<size_t>(sb) * 272;
+        for (int s = 0; s < 16; ++s) {
+            // step s = values 16s..16s+15 of the 256: block s>>1, byte 2 + 16*(s&1) + 4*tig + i inside it
+            const size_t native = row_off + static_cast<size_t>(s >> 1) * 34 + 2 + 16 * (s & 1) + 4 * tig;
+            const size_t tiled = static_cast<size_t>(4 * half + (s >> 2)) * 512 + lane * 16 + (s & 3) * 4;
+            for (int i = 0; i < 4; ++i) {
+                if (FORWARD) out[tiled + i] = in[native + i] ^ 0x80u;
+                else out[native + i] = in[tiled + i] ^ 0x80u;
+            }
+        }
+    }
+    if (lane < 16) {
+        const size_t row_off = (static_cast<size_t>(group) * 16 + lane) * row_bytes + static_cast<size_t>(sb) * 272;
+        for (int b = 0; b < 8; ++b)
+            for (int i = 0; i < 2; ++i) {
+                const size_t native = row_off + static_cast<size_t>(b) * 34 + i;
+                const size_t tiled = Q8T_SCALES_OFF + 16 * lane + 2 * b + i;
+                if (FORWARD) out[tiled] = in[native];
+                else out[native] = in[tiled];
+            }
+    }
+}
+
+// Runs the tiled kernel for a mode 0 or mode 3 request whose weights are in a tile layout
+// (q.fmt_a: B200Q_Q6_K_TILED or B200Q_Q8_0_TILED).
 int q6k_tiled_launch(const MmaRequest &q, cudaStream_t stream) {
     const bool grouped = q.mode == 3;
     if (q.mode != 0 && q.mode != 3) return fail(B200Q_EUNSUPPORTED, "tiled Q6_K: only linear and grouped down");
@@ -131,8 +169,13 @@ int q6k_tiled_launch(const MmaRequest &q, cudaStream_t stream) {
     a.order = q.order; a.seg_expert = q.seg_expert; a.seg_begin = q.seg_begin; a.seg_count = q.seg_count;
     a.num_segments = q.num_segments; a.max_segments = q.max_segments; a.route = q.route;
     a.flat_rows = q.flat_rows; a.y_table = q.y_table; a.rows_per_rank = q.rows_per_rank;
-    Q6Fn fn = grouped ? (a.nterms == 2 ? q6k_tiled_kernel<3, 2> : q6k_tiled_kernel<3, 1>)
-                      : (a.nterms == 2 ? q6k_tiled_kernel<0, 2> : q6k_tiled_kernel<0, 1>);
+    Q6Fn fn;
+    if (q.fmt_a == B200Q_Q8_0_TILED)
+        fn = grouped ? (a.nterms == 2 ? tiled_kernel<Q8Tile, 3, 2> : tiled_kernel<Q8Tile, 3, 1>)
+                     : (a.nterms == 2 ? tiled_kernel<Q8Tile, 0, 2> : tiled_kernel<Q8Tile, 0, 1>);
+    else
+        fn = grouped ? (a.nterms == 2 ? tiled_kernel<Q6Tile, 3, 2> : tiled_kernel<Q6Tile, 3, 1>)
+                     : (a.nterms == 2 ? tiled_kernel<Q6Tile, 0, 2> : tiled_kernel<Q6Tile, 0, 1>);
     cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void *>(fn),
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM_LIMIT);
     if (err != cudaSuccess) {
@@ -189,6 +232,31 @@ static int q4k_retile_common(const void *src, void *dst, long long rows, int k, 
         q4k_retile_kernel<false><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
             static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst), tiles, nsb);
     return check_launch("q4k_retile");
+}
+
+static int q8_retile_common(const void *src, void *dst, long long rows, int k, bool forward, void *stream) {
+    if (!src || !dst) return fail(B200Q_EINVAL, "q8_0_retile: NULL pointer");
+    if (rows <= 0 || rows % 16 != 0 || k <= 0 || k % 256 != 0)
+        return fail(B200Q_EINVAL, "q8_0_retile: rows must be a multiple of 16 and K a multiple of 256");
+    if (src == dst) return fail(B200Q_EINVAL, "q8_0_retile: in-place conversion is not supported");
+    const int nsb = k / 256;
+    const long long tiles = rows / 16 * nsb;
+    const unsigned blocks = static_cast<unsigned>((tiles * 32 + 255) / 256);
+    if (forward)
+        q8_retile_kernel<true><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst), tiles, nsb);
+    else
+        q8_retile_kernel<false><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst), tiles, nsb);
+    return check_launch("q8_0_retile");
+}
+
+extern "C" int b200q_q8_0_retile(const void *native, void *tiled, int64_t rows, int k, void *stream) {
+    return q8_retile_common(native, tiled, rows, k, true, stream);
+}
+
+extern "C" int b200q_q8_0_untile(const void *tiled, void *native, int64_t rows, int k, void *stream) {
+    return q8_retile_common(tiled, native, rows, k, false, stream);
 }
 
 extern "C" int b200q_q4k_retile(const void *native, void *tiled, int64_t rows, int k, void *stream) {

@@ -1,4 +1,4 @@
-// Q6_K in a device-side tile layout, and the tensor-core GEMV that reads it (sm_100a).
+// Q6_K and Q8_0 in device-side tile layouts, and the tensor-core GEMV that reads them (sm_100a).
 //
 // A GGUF Q6_K super-block is 210 bytes (ql[128] | qh[64] | int8 scales[16] | fp16 d), so rows and
 // blocks start on 2-byte boundaries only: no 128-bit load, no aligned bulk copy, and every 32-bit
@@ -181,6 +181,72 @@ __device__ __forceinline__ void q6_tile_mma(const Q6TileRegs &r, const uint2 *bf
     tot[3] = fmaf(db, blk[3], tot[3]);
 }
 
+// Tile policies of the kernel below: bytes per 16-row x 256-value tile, the registers of one tile,
+// how a lane loads them and how it multiplies them into its four accumulators.
+struct Q6Tile {
+    static constexpr int BYTES = Q6T_TILE_BYTES;
+    using Regs = Q6TileRegs;
+    static __device__ __forceinline__ void load(Regs &r, const uint8_t *tile, int lane) { load_q6_tile(r, tile, lane); }
+    template <int NTERMS>
+    static __device__ __forceinline__ void mma(const Regs &r, const uint2 *bfrag, int nfrag, int sb, int lane,
+                                               float (&tot)[4]) {
+        q6_tile_mma<NTERMS>(r, bfrag, nfrag, sb, lane, tot);
+    }
+};
+
+// Q8_0 tile (16 rows x 8 blocks of 32 values = 4352 bytes, the size of the 128 native 34-byte blocks):
+//   [   0, 4096)  eight planes of 512 bytes, one uint4 per lane: planes 0-3 = the 16 code words of
+//                 row g (word s = values 4*tig..4*tig+3 of the 16-value step s), planes 4-7 = row g+8;
+//                 codes are stored +128 (unsigned), so a byte permute gives the FP16 pair 1024+code+128
+//   [4096, 4352)  16 rows x 8 fp16 block scales
+constexpr int Q8T_TILE_BYTES = 4352;
+constexpr int Q8T_SCALES_OFF = 4096;
+struct Q8TileRegs {
+    uint4 c[8];
+    uint4 da, db;      // eight fp16 scales of row g / row g+8
+};
+struct Q8Tile {
+    static constexpr int BYTES = Q8T_TILE_BYTES;
+    using Regs = Q8TileRegs;
+    static __device__ __forceinline__ void load(Regs &r, const uint8_t *tile, int lane) {
+        const int g = lane >> 2;
+#pragma unroll
+        for (int p = 0; p < 8; ++p) r.c[p] = ldg128(tile + p * 512 + lane * 16);
+        r.da = ldg128(tile + Q8T_SCALES_OFF + 16 * g);
+        r.db = ldg128(tile + Q8T_SCALES_OFF + 16 * (g + 8));
+    }
+    template <int NTERMS>
+    static __device__ __forceinline__ void mma(const Regs &r, const uint2 *bfrag, int nfrag, int sb, int lane,
+                                               float (&tot)[4]) {
+        const uint32_t neg = 0xe480e480u;                       // -(1024 + 128)
+        const uint32_t wa[16] = {r.c[0].x, r.c[0].y, r.c[0].z, r.c[0].w, r.c[1].x, r.c[1].y, r.c[1].z, r.c[1].w,
+                                 r.c[2].x, r.c[2].y, r.c[2].z, r.c[2].w, r.c[3].x, r.c[3].y, r.c[3].z, r.c[3].w};
+        const uint32_t wb[16] = {r.c[4].x, r.c[4].y, r.c[4].z, r.c[4].w, r.c[5].x, r.c[5].y, r.c[5].z, r.c[5].w,
+                                 r.c[6].x, r.c[6].y, r.c[6].z, r.c[6].w, r.c[7].x, r.c[7].y, r.c[7].z, r.c[7].w};
+        const uint32_t da[4] = {r.da.x, r.da.y, r.da.z, r.da.w}, db[4] = {r.db.x, r.db.y, r.db.z, r.db.w};
+#pragma unroll
+        for (int blk = 0; blk < 8; ++blk) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int s = 2 * blk + h;
+                const uint32_t va = wa[s], vb = wb[s];
+                const BFrag b = load_bfrag<NTERMS>(bfrag, nfrag, sb * 16 + s, lane);
+                mma_terms<NTERMS>(acc, hadd2_u32(__byte_perm(va, 0x64646464u, 0x4240), neg),
+                                  hadd2_u32(__byte_perm(vb, 0x64646464u, 0x4240), neg),
+                                  hadd2_u32(__byte_perm(va, 0x64646464u, 0x4341), neg),
+                                  hadd2_u32(__byte_perm(vb, 0x64646464u, 0x4341), neg), b);
+            }
+            const float fa = half_bits_to_float((da[blk >> 1] >> (16 * (blk & 1))) & 0xffffu);
+            const float fb = half_bits_to_float((db[blk >> 1] >> (16 * (blk & 1))) & 0xffffu);
+            tot[0] = fmaf(fa, acc[0], tot[0]);
+            tot[1] = fmaf(fa, acc[1], tot[1]);
+            tot[2] = fmaf(fb, acc[2], tot[2]);
+            tot[3] = fmaf(fb, acc[3], tot[3]);
+        }
+    }
+};
+
 // Activation fragments in natural order: fragment f (16 positions 16f..16f+15), lane (g, tig):
 // token g, positions 16f + 4tig + {0,2} -> b0, {1,3} -> b1; FP16 high part (+ remainder plane for
 // FP32 inputs) after a per-token power-of-two scaling. All Q6T_THREADS threads take part.
@@ -266,8 +332,8 @@ __device__ __forceinline__ void prepare_fragments(RowFn row_of, int m_tokens, in
 // MODE 0: y[m, n] = x W^T.  MODE 3: grouped down projection over the plan's segments, rows scaled
 // by the route weight. Warp (rgi, kpi) owns row group rgi of the CTA's row block and the
 // super-blocks kpi, kpi+kp, ...; the next tile is requested before the current one is computed.
-template <int MODE, int NTERMS>
-__global__ void __launch_bounds__(Q6T_THREADS, 1) q6k_tiled_kernel(const Q6TiledArgs a) {
+template <typename TILE, int MODE, int NTERMS>
+__global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs a) {
     constexpr bool GROUPED = (MODE == 3);
     extern __shared__ __align__(128) uint8_t smem[];
     float *tok_scale = reinterpret_cast<float *>(smem);           // [8] scale, [8] inverse, [8] amax bits
@@ -301,15 +367,15 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) q6k_tiled_kernel(const Q6Tiled
         const int expert = GROUPED ? a.seg_expert[unit] : 0;
         const int group = min(bi * a.rg + rgi, groups_total - 1);      // clamped groups are loaded, never stored
         return expert_matrix(a.w, a.stride, a.table, expert) +
-               (static_cast<size_t>(group) * nsb + kpi) * Q6T_TILE_BYTES;
+               (static_cast<size_t>(group) * nsb + kpi) * TILE::BYTES;
     };
-    const size_t item_step = static_cast<size_t>(a.kp) * Q6T_TILE_BYTES;
+    const size_t item_step = static_cast<size_t>(a.kp) * TILE::BYTES;
 
     int unit_i = static_cast<int>(blk_begin / blocks_per_unit);
     int bi = static_cast<int>(blk_begin - static_cast<long long>(unit_i) * blocks_per_unit);
     const uint8_t *cur_p = block_base(unit_i, bi), *nxt_p = cur_p;
-    Q6TileRegs cur, nxt;
-    if (items_per_block > 0) load_q6_tile(nxt, cur_p, lane);
+    typename TILE::Regs cur, nxt;
+    if (items_per_block > 0) TILE::load(nxt, cur_p, lane);
 
     int m_tokens = a.m;
     int seg_begin = 0, cur_unit = -1;
@@ -342,9 +408,9 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) q6k_tiled_kernel(const Q6Tiled
         float tot[4] = {0.f, 0.f, 0.f, 0.f};
         for (int item = 0; item < items_per_block; ++item) {
             cur = nxt;
-            if (item + 1 < items_per_block) load_q6_tile(nxt, cur_p + (item + 1) * item_step, lane);
-            else if (has_next) load_q6_tile(nxt, nxt_p, lane);
-            q6_tile_mma<NTERMS>(cur, bfrag, nfrag, kpi + item * a.kp, lane, tot);
+            if (item + 1 < items_per_block) TILE::load(nxt, cur_p + (item + 1) * item_step, lane);
+            else if (has_next) TILE::load(nxt, nxt_p, lane);
+            TILE::template mma<NTERMS>(cur, bfrag, nfrag, kpi + item * a.kp, lane, tot);
         }
 
         const int group = group0 + rgi;

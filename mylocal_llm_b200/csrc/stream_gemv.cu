@@ -110,7 +110,7 @@ extern "C" {
 int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype, int m, void *y, int y_dtype,
                void *stream) {
     if (!w || !x || !y) return fail(B200Q_EINVAL, "gemv: NULL pointer");
-    if (fmt == B200Q_Q6_K_TILED) {
+    if (fmt == B200Q_Q6_K_TILED || fmt == B200Q_Q8_0_TILED) {
         if (!dtype_valid(x_dtype) || !dtype_valid(y_dtype)) return fail(B200Q_EINVAL, "gemv: bad dtype");
         if (n <= 0 || m <= 0 || k <= 0) return fail(B200Q_EINVAL, "gemv: bad shape n=%d k=%d m=%d", n, k, m);
         for (int t0 = 0; t0 < m; t0 += 8) {
@@ -315,7 +315,7 @@ static int moe_down_impl(const void *down_base, int64_t down_stride, int down_fm
         !num_segments || (!terms && !y_table))
         return fail(B200Q_EINVAL, "moe_down: NULL pointer");
     if (y_table && rows_per_rank < 1) return fail(B200Q_EINVAL, "moe_down: rows_per_rank must be positive");
-    if (down_fmt == B200Q_Q6_K_TILED) {
+    if (down_fmt == B200Q_Q6_K_TILED || down_fmt == B200Q_Q8_0_TILED) {
         if (d <= 0 || f <= 0 || max_segments <= 0) return fail(B200Q_EINVAL, "moe_down: bad shape d=%d f=%d", d, f);
         MmaRequest q{};
         q.mode = 3; q.wa = static_cast<const uint8_t *>(down_base); q.fmt_a = q.fmt_b = down_fmt;

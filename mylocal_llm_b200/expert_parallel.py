@@ -249,14 +249,12 @@ class DeviceExpertEngine:
 
     def __init__(self, bank, router_weight, top_k, *, first_expert, n_experts_global, shared=None, shared_gate=None,
                  normalization_floor=2.0 ** -14):
-        from .quantized_linear import retile_enabled, retile_weight
+        from .quantized_linear import retile_enabled, retile_gate_up, retile_weight
         from .router_inference import RouterInference
         if retile_enabled():
             bank = bank.retiled()
             if shared is not None:
-                gate_t, up_t = retile_weight(shared[0]), retile_weight(shared[1])
-                if gate_t.quant_type != up_t.quant_type:          # gate and up share one layout
-                    gate_t, up_t = shared[0], shared[1]
+                gate_t, up_t = retile_gate_up(shared[0], shared[1])
                 shared = (gate_t, up_t, retile_weight(shared[2]))
         self.bank = bank
         self.first_expert, self.n_global = int(first_expert), int(n_experts_global)

@@ -22,7 +22,7 @@ import numpy as np
 
 from .moe_layer import RMSNormInference
 from .quantized_linear import (DevicePackedGGUFWeight, dequantize_device, packed_to_device, quantized_linear,
-                               quantized_swiglu, retile_enabled, retile_weight)
+                               quantized_swiglu, retile_enabled, retile_gate_up, retile_weight)
 from .quantized_weight import PackedGGUFWeight, block_format
 
 
@@ -143,14 +143,18 @@ class ExternalLlamaModel:
                 "k": self._matrix(weights[p + "self_attn.k_proj.weight"]),
                 "v": self._matrix(weights[p + "self_attn.v_proj.weight"]),
                 "o": self._matrix(weights[p + "self_attn.o_proj.weight"]),
-                "gate": self._matrix(weights[p + "mlp.gate_proj.weight"]),
-                "up": self._matrix(weights[p + "mlp.up_proj.weight"]),
+                "gate": self._matrix(weights[p + "mlp.gate_proj.weight"], tile=False),
+                "up": self._matrix(weights[p + "mlp.up_proj.weight"], tile=False),
                 "down": self._matrix(weights[p + "mlp.down_proj.weight"]),
             })
-            if self.layers[-1]["gate"].quant_type != self.layers[-1]["up"].quant_type:
-                # one layout for the fused launch: keep both native
-                self.layers[-1]["gate"] = self._matrix(weights[p + "mlp.gate_proj.weight"], tile=False)
-                self.layers[-1]["up"] = self._matrix(weights[p + "mlp.up_proj.weight"], tile=False)
+            layer = self.layers[-1]
+            if retile_enabled():
+                force = self.dtype != torch.float32
+                if layer["gate"].quant_type == layer["up"].quant_type == "Q8_0":
+                    # no fused SwiGLU kernel reads Q8_0 tiles: two tiled GEMVs and an elementwise product
+                    layer["gate"], layer["up"] = retile_weight(layer["gate"], force), retile_weight(layer["up"], force)
+                else:
+                    layer["gate"], layer["up"] = retile_gate_up(layer["gate"], layer["up"], force)
         half = cfg.head_dim // 2
         inv = 1.0 / (float(cfg.rope_theta) ** (2.0 * np.arange(half) / cfg.head_dim))
         ang = np.arange(cfg.max_position_embeddings)[:, None] * inv[None, :]
@@ -218,7 +222,12 @@ class ExternalLlamaModel:
             ctx = ctx.permute(0, 2, 1, 3).reshape(b * t, heads * dh).to(self.dtype).contiguous()
             attn = quantized_linear(ctx, layer["o"])
             residual, hidden = layer["norm2"].forward_residual_add(residual, attn)
-            act = quantized_swiglu(hidden, layer["gate"], layer["up"])
+            if layer["gate"].quant_type == "Q8_0_TILED" and layer["up"].quant_type == "Q8_0_TILED":
+                g = quantized_linear(hidden, layer["gate"], out_dtype=torch.float32)
+                u = quantized_linear(hidden, layer["up"], out_dtype=torch.float32)
+                act = (torch.nn.functional.silu(g) * u).to(self.dtype)
+            else:
+                act = quantized_swiglu(hidden, layer["gate"], layer["up"])
             ffn = quantized_linear(act, layer["down"])
             nxt = self.layers[i + 1]["norm1"] if i + 1 < len(self.layers) else self.final_norm
             residual, hidden = nxt.forward_residual_add(residual, ffn)

@@ -110,9 +110,7 @@ class PackedMoELayer:
             # Q6_K down projections are re-ordered once into the tile layout the fast kernel reads
             bank = bank.retiled()
             if shared is not None and len(shared) == 3 and isinstance(shared[2], DevicePackedGGUFWeight):
-                gate_t, up_t = retile_weight(shared[0]), retile_weight(shared[1])
-                if gate_t.quant_type != up_t.quant_type:          # gate and up share one layout
-                    gate_t, up_t = shared[0], shared[1]
+                gate_t, up_t = retile_gate_up(shared[0], shared[1])
                 shared = (gate_t, up_t, retile_weight(shared[2]))
         self.bank = bank
         self.layer_id = int(layer_id)

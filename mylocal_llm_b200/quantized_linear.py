@@ -114,8 +114,9 @@ def retile_enabled():
     return os.environ.get("B200Q_RETILE", "1") != "0"
 
 
-_RETILE = {"Q6_K": ("b200q_q6k_retile", "Q6_K_TILED"), "Q4_K": ("b200q_q4k_retile", "Q4_K_TILED")}
-_UNTILE = {"Q6_K_TILED": "b200q_q6k_untile", "Q4_K_TILED": "b200q_q4k_untile"}
+_RETILE = {"Q6_K": ("b200q_q6k_retile", "Q6_K_TILED"), "Q4_K": ("b200q_q4k_retile", "Q4_K_TILED"),
+           "Q8_0": ("b200q_q8_0_retile", "Q8_0_TILED")}
+_UNTILE = {"Q6_K_TILED": "b200q_q6k_untile", "Q4_K_TILED": "b200q_q4k_untile", "Q8_0_TILED": "b200q_q8_0_untile"}
 
 
 def retile_bytes(data, rows, k, quant_type):
@@ -144,19 +145,30 @@ def untile_q6k(data, rows, k):
 
 
 def can_retile(quant_type, rows, k, force=False):
-    return quant_type in _RETILE and rows % 16 == 0 and (k <= TILED_MAX_K or force)
+    return quant_type in _RETILE and rows % 16 == 0 and k % 256 == 0 and (k <= TILED_MAX_K or force)
 
 
 def retile_weight(weight, force=False):
-    """``DevicePackedGGUFWeight`` in the tile layout when its type has one (Q4_K, Q6_K) and the shape
-    allows it (rows a multiple of 16, K <= TILED_MAX_K); otherwise the weight itself. ``force`` lifts
-    the K limit for callers that only ever pass 16-bit activations (Q4_K up to K = 8192)."""
+    """``DevicePackedGGUFWeight`` in the tile layout when its type has one (Q4_K, Q6_K, Q8_0) and the
+    shape allows it (rows a multiple of 16, K a multiple of 256 and <= TILED_MAX_K); otherwise the
+    weight itself. ``force`` lifts the K limit for callers that only ever pass 16-bit activations
+    (Q4_K and Q8_0 up to K = 8192)."""
     if not can_retile(weight.quant_type, weight.shape[0], weight.shape[1], force):
         return weight
     if weight.quant_type == "Q6_K" and weight.shape[1] > TILED_MAX_K:
         return weight
     return DevicePackedGGUFWeight(retile_bytes(weight.data, weight.shape[0], weight.shape[1], weight.quant_type),
                                   weight.shape, _RETILE[weight.quant_type][1])
+
+
+def retile_gate_up(gate, up, force=False):
+    """Gate / up pair for the fused SwiGLU launch: both in the tile layout when the fused kernel reads
+    it (Q4_K for both), otherwise both unchanged."""
+    if gate.quant_type == up.quant_type == "Q4_K":
+        gate_t, up_t = retile_weight(gate, force), retile_weight(up, force)
+        if gate_t.quant_type == up_t.quant_type:
+            return gate_t, up_t
+    return gate, up
 
 
 def dequantize_device(data, rows, k, quant_type):

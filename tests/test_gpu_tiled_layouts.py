@@ -187,3 +187,52 @@ def test_fully_tiled_bank_matches_the_native_bank(cuda, tokens):
     one = tiled.expert(3).forward(x)                              # per-expert handles see whole tiles
     np.testing.assert_allclose(one.float().cpu().numpy(), bank.expert(3).forward(x).float().cpu().numpy(),
                                rtol=2e-2, atol=2e-2)
+
+
+# ------------------------------------------------------------------------------------------ Q8_0
+@pytest.mark.parametrize("rows,k", [(16, 256), (48, 512), (4096, 4096)])
+def test_q8_0_retile_then_untile_restores_the_gguf_bytes(cuda, rows, k):
+    raw = np.random.default_rng(rows + k).integers(0, 256, rows * k // 32 * 34, dtype=np.uint8)
+    native = cuda.from_numpy(raw).cuda()
+    tiled = retile_bytes(native, rows, k, "Q8_0")
+    assert tiled.shape == native.shape and not cuda.equal(tiled, native)
+    assert cuda.equal(untile_bytes(tiled, rows, k, "Q8_0_TILED"), native)
+
+
+@pytest.mark.parametrize("n,k", [(4096, 4096), (2048, 8192), (8192, 2048), (16, 256), (48, 288)])
+@pytest.mark.parametrize("m", [1, 8, 11])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_q8_0_tiled_gemv_matches_the_oracle(cuda, n, k, m, dtype):
+    if n * k >= 4096 * 4096 and m == 11:
+        pytest.skip("large shapes: two batch sizes are enough")
+    rng = np.random.default_rng(n + k + m)
+    w = quantize(rng.normal(0, 0.02, (n, k)).astype(np.float32), "Q8_0")
+    dev = packed_to_device(w)
+    force = k > 4096 and dtype != "float32"
+    tiled = retile_weight(dev, force=force)
+    if k % 256 or (k > 4096 and not force):
+        assert tiled is dev                          # K not a multiple of 256, or too wide for FP32 inputs
+        return
+    assert tiled.quant_type == "Q8_0_TILED"
+    x = cuda.from_numpy(rng.normal(0, 1, (m, k)).astype(np.float32)).cuda().to(getattr(cuda, dtype))
+    got = quantized_linear(x, tiled).float().cpu().numpy()
+    ref = po.linear_fp64(x.float().cpu().numpy(), w.data, w.shape, "Q8_0")
+    if dtype == "float32":
+        np.testing.assert_allclose(got, ref, rtol=2e-5, atol=2e-3)
+    else:
+        np.testing.assert_allclose(got, ref, rtol=1.6e-2, atol=2e-2)
+    dq = dequantize_device(tiled.data, n, k, "Q8_0_TILED").cpu().numpy()
+    np.testing.assert_array_equal(dq, po.dequantize(w.data, w.shape, "Q8_0"))
+
+
+def test_q8_0_tiled_identity_columns_are_exact(cuda):
+    n, k = 32, 256
+    w = random_packed("Q8_0", (n, k), seed=9, d=0.01)
+    tiled = retile_weight(packed_to_device(w))
+    deq = po.dequantize(w.data, w.shape, "Q8_0")
+    for start in (0, 31, 248):
+        x = np.zeros((8, k), np.float32)
+        for t in range(8):
+            x[t, start + t] = 1.0
+        got = quantized_linear(cuda.from_numpy(x).cuda(), tiled).cpu().numpy()
+        np.testing.assert_array_equal(got, deq[:, start:start + 8].T)
