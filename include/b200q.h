@@ -204,6 +204,23 @@ int b200q_q8_0_retile(const void *native, void *tiled, int64_t rows, int k, void
 int b200q_q8_0_untile(const void *tiled, void *native, int64_t rows, int k, void *stream);
 int b200q_q6k_untile(const void *tiled, void *native, int64_t rows, int k, void *stream);
 
+/* ---- Decode-step bookkeeping of the Llama path (the reference's graph decoder has NVRTC kernels of
+ * the same role: qkv_rope_store_fp16_d64_dynamic / dense_attention_fp16_d64_dynamic,
+ * mini_llm/external/cuda_graph_decode.py:64-260). ------------------------------------------------ */
+
+/* Rotate-half RoPE of q (in place, FP32 [B,T,H,Dh]) and k, and store of rotated k and v (FP32
+ * [B,T,Hkv,Dh]) into the caches [B,Hkv,horizon,Dh] (cache_dtype) at positions[t] (device int64 [T]);
+ * cos/sin tables are FP32 [max_pos, Dh/2] with theta_i = pos / base^(2i/Dh). */
+int b200q_rope_kv_store(float *q, const float *k, const float *v, const int64_t *positions, const float *cos_table,
+                        const float *sin_table, int batch, int t, int heads, int kv_heads, int head_dim, int horizon,
+                        void *k_cache, void *v_cache, int cache_dtype, void *stream);
+
+/* Single-query attention: out[b, h*Dh..] = softmax(scale * q[b,h] . K[b,kv(h),0..pos]) V, with
+ * pos = position[0] read on the device (graph-capturable); q FP32 [B,H,Dh]; head_dim 64 or 128. */
+int b200q_decode_attention(const float *q, const void *k_cache, const void *v_cache, int cache_dtype,
+                           const int64_t *position, int batch, int heads, int kv_heads, int head_dim, int horizon,
+                           float scale, void *out, int out_dtype, void *stream);
+
 /* ---- Expert-parallel execution over the GPUs of one node (no counterpart in the reference, which is
  * single-process; semantics = the single-GPU layer, bit for bit). ------------------------------- */
 

@@ -1,0 +1,219 @@
+// Decode-step bookkeeping kernels of the Llama path: rotate-half RoPE fused with the KV-cache
+// store, and single-query attention over the cache. They replace a few dozen small framework
+// kernels per layer in the one-token step; the packed linears around them are the hot path.
+// Semantics follow the reference's inference attention (mini_llm/ops/attention_inference.py:255-277
+// for the rotation, 1/sqrt(d_head) scaled softmax over positions 0..pos, grouped KV heads).
+#include "common.cuh"
+
+namespace b200q {
+
+// q [B, T, H, Dh], k / v [B, T, Hkv, Dh] FP32; positions [T] (device); cos / sin [max_pos, Dh/2].
+// q is rotated in place; rotated k and plain v go to cache[b, hkv, positions[t], :].
+__global__ void __launch_bounds__(256) rope_kv_store_kernel(float *q, const float *k, const float *v,
+                                                            const long long *positions, const float *cos_t,
+                                                            const float *sin_t, int b, int t, int h, int hkv, int dh,
+                                                            int horizon, void *k_cache, void *v_cache,
+                                                            int cache_dtype) {
+    const int half = dh >> 1;
+    const long long total = static_cast<long long>(b) * t * (h + 2 * hkv) * half;
+    for (long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; idx < total;
+         idx += static_cast<long long>(gridDim.x) * 256) {
+        const int i = static_cast<int>(idx % half);
+        long long rest = idx / half;
+        const int head = static_cast<int>(rest % (h + 2 * hkv));
+        rest /= (h + 2 * hkv);
+        const int tt = static_cast<int>(rest % t);
+        const int bb = static_cast<int>(rest / t);
+        const long long pos = positions[tt];
+        if (head < h) {
+            float *p = q + ((static_cast<size_t>(bb) * t + tt) * h + head) * dh;
+            const float c = cos_t[pos * half + i], s = sin_t[pos * half + i];
+            const float x0 = p[i], x1 = p[half + i];
+            p[i] = x0 * c - x1 * s;
+            p[half + i] = x0 * s + x1 * c;
+        } else if (head < h + hkv) {
+            const int kh = head - h;
+            const float *p = k + ((static_cast<size_t>(bb) * t + tt) * hkv + kh) * dh;
+            const float c = cos_t[pos * half + i], s = sin_t[pos * half + i];
+            const float x0 = p[i], x1 = p[half + i];
+            const size_t dst = ((static_cast<size_t>(bb) * hkv + kh) * horizon + pos) * dh;
+            if (pos >= 0 && pos < horizon) {
+                store_from_float(k_cache, cache_dtype, dst + i, x0 * c - x1 * s);
+                store_from_float(k_cache, cache_dtype, dst + half + i, x0 * s + x1 * c);
+            }
+        } else {
+            const int vh = head - h - hkv;
+            const float *p = v + ((static_cast<size_t>(bb) * t + tt) * hkv + vh) * dh;
+            const size_t dst = ((static_cast<size_t>(bb) * hkv + vh) * horizon + pos) * dh;
+            if (pos >= 0 && pos < horizon) {
+                store_from_float(v_cache, cache_dtype, dst + i, p[i]);
+                store_from_float(v_cache, cache_dtype, dst + half + i, p[half + i]);
+            }
+        }
+    }
+}
+
+// EPL consecutive cache elements starting at element index `idx` (a multiple of EPL) as floats.
+template <int EPL>
+__device__ __forceinline__ void load_row_piece(const void *cache, int dtype, size_t idx, float (&out)[EPL]) {
+    if (dtype == B200Q_F32) {
+        if (EPL == 2) {
+            const float2 v = *reinterpret_cast<const float2 *>(static_cast<const float *>(cache) + idx);
+            out[0] = v.x; out[1] = v.y;
+        } else {
+            const float4 v = *reinterpret_cast<const float4 *>(static_cast<const float *>(cache) + idx);
+            out[0] = v.x; out[1] = v.y; out[2 % EPL] = v.z; out[3 % EPL] = v.w;
+        }
+    } else {
+        uint32_t raw[EPL / 2];
+        if (EPL == 2) raw[0] = *reinterpret_cast<const uint32_t *>(static_cast<const uint16_t *>(cache) + idx);
+        else {
+            const uint2 v = *reinterpret_cast<const uint2 *>(static_cast<const uint16_t *>(cache) + idx);
+            raw[0] = v.x; raw[(EPL / 2) - 1] = v.y;
+        }
+#pragma unroll
+        for (int e = 0; e < EPL / 2; ++e) {
+            if (dtype == B200Q_F16) {
+                out[2 * e] = half_bits_to_float(raw[e] & 0xffffu);
+                out[2 * e + 1] = half_bits_to_float(raw[e] >> 16);
+            } else {
+                out[2 * e] = __uint_as_float(raw[e] << 16);
+                out[2 * e + 1] = __uint_as_float(raw[e] & 0xffff0000u);
+            }
+        }
+    }
+}
+
+// One CTA of eight warps per (batch, head): warp w takes groups of ATT_U consecutive cache positions
+// (all their key and value loads are issued before any arithmetic, so the loop is not bound by one
+// load latency per position); each lane holds EPL = Dh/32 dimensions; scores by warp reduction,
+// running (max, sum, weighted values) per warp, merged across the warps at the end.
+constexpr int ATT_WARPS = 8;
+constexpr int ATT_U = 8;
+
+template <int EPL>
+__global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const float *q, const void *k_cache,
+                                                                          const void *v_cache, int cache_dtype,
+                                                                          const long long *position, int h, int hkv,
+                                                                          int horizon, float scale, void *out,
+                                                                          int out_dtype) {
+    constexpr int DH = EPL * 32;
+    __shared__ float sm_m[ATT_WARPS], sm_l[ATT_WARPS], sm_acc[ATT_WARPS][DH];
+    const int bh = blockIdx.x, bb = bh / h, head = bh - bb * h;
+    const int kvh = head / (h / hkv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    long long last = position[0];                       // newest valid cache position
+    if (last >= horizon) last = horizon - 1;
+    const float *qp = q + (static_cast<size_t>(bb) * h + head) * DH;
+    float qv[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) qv[e] = qp[lane * EPL + e] * scale;
+    const size_t base = (static_cast<size_t>(bb) * hkv + kvh) * horizon * DH + lane * EPL;
+    float m = __int_as_float(0xff800000), l = 0.f, acc[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
+    for (long long j0 = static_cast<long long>(warp) * ATT_U; j0 <= last; j0 += ATT_WARPS * ATT_U) {
+        float kk[ATT_U][EPL], vv[ATT_U][EPL], dot[ATT_U];
+#pragma unroll
+        for (int u = 0; u < ATT_U; ++u) {
+            const long long j = (j0 + u <= last) ? j0 + u : last;        // clamped rows are masked below
+            load_row_piece<EPL>(k_cache, cache_dtype, base + j * DH, kk[u]);
+            load_row_piece<EPL>(v_cache, cache_dtype, base + j * DH, vv[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < ATT_U; ++u) {
+            float d = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) d = fmaf(qv[e], kk[u][e], d);
+            dot[u] = d;
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+#pragma unroll
+            for (int u = 0; u < ATT_U; ++u) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], o);
+        }
+        float m_new = m;
+#pragma unroll
+        for (int u = 0; u < ATT_U; ++u)
+            if (j0 + u <= last) m_new = fmaxf(m_new, dot[u]);
+        const float corr = __expf(m - m_new);
+        l *= corr;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[e] *= corr;
+#pragma unroll
+        for (int u = 0; u < ATT_U; ++u) {
+            const float p = (j0 + u <= last) ? __expf(dot[u] - m_new) : 0.f;
+            l += p;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) acc[e] = fmaf(p, vv[u][e], acc[e]);
+        }
+        m = m_new;
+    }
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) sm_acc[warp][lane * EPL + e] = acc[e];
+    __syncthreads();
+    if (warp == 0) {
+        float mm = sm_m[0];
+#pragma unroll
+        for (int w = 1; w < ATT_WARPS; ++w) mm = fmaxf(mm, sm_m[w]);
+        float ll = 0.f, r[EPL];
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) r[e] = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) {
+            const float f = sm_l[w] > 0.f ? __expf(sm_m[w] - mm) : 0.f;
+            ll += sm_l[w] * f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) r[e] += sm_acc[w][lane * EPL + e] * f;
+        }
+        const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e)
+            store_from_float(out, out_dtype, (static_cast<size_t>(bb) * h + head) * DH + lane * EPL + e, r[e] * inv);
+    }
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int b200q_rope_kv_store(float *q, const float *k, const float *v, const int64_t *positions, const float *cos_table,
+                        const float *sin_table, int batch, int t, int heads, int kv_heads, int head_dim, int horizon,
+                        void *k_cache, void *v_cache, int cache_dtype, void *stream) {
+    if (!q || !k || !v || !positions || !cos_table || !sin_table || !k_cache || !v_cache)
+        return fail(B200Q_EINVAL, "rope_kv_store: NULL pointer");
+    if (batch <= 0 || t <= 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || head_dim % 2 || horizon <= 0 ||
+        !dtype_valid(cache_dtype))
+        return fail(B200Q_EINVAL, "rope_kv_store: bad argument");
+    const long long total = static_cast<long long>(batch) * t * (heads + 2 * kv_heads) * (head_dim / 2);
+    const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 4096));
+    rope_kv_store_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        q, k, v, reinterpret_cast<const long long *>(positions), cos_table, sin_table, batch, t, heads, kv_heads,
+        head_dim, horizon, k_cache, v_cache, cache_dtype);
+    return check_launch("rope_kv_store");
+}
+
+int b200q_decode_attention(const float *q, const void *k_cache, const void *v_cache, int cache_dtype,
+                           const int64_t *position, int batch, int heads, int kv_heads, int head_dim, int horizon,
+                           float scale, void *out, int out_dtype, void *stream) {
+    if (!q || !k_cache || !v_cache || !position || !out) return fail(B200Q_EINVAL, "decode_attention: NULL pointer");
+    if (batch <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || horizon <= 0 || !dtype_valid(cache_dtype) ||
+        !dtype_valid(out_dtype))
+        return fail(B200Q_EINVAL, "decode_attention: bad argument");
+    const long long *pos = reinterpret_cast<const long long *>(position);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (head_dim == 64)
+        decode_attention_kernel<2><<<batch * heads, ATT_WARPS * 32, 0, s>>>(q, k_cache, v_cache, cache_dtype, pos, heads, kv_heads,
+                                                                 horizon, scale, out, out_dtype);
+    else if (head_dim == 128)
+        decode_attention_kernel<4><<<batch * heads, ATT_WARPS * 32, 0, s>>>(q, k_cache, v_cache, cache_dtype, pos, heads, kv_heads,
+                                                                 horizon, scale, out, out_dtype);
+    else
+        return fail(B200Q_EUNSUPPORTED, "decode_attention: head_dim must be 64 or 128");
+    return check_launch("decode_attention");
+}
+
+}  // extern "C"

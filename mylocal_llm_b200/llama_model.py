@@ -16,10 +16,12 @@ adapter; here they stay packed and resident in HBM, which is the point of the ex
   ``decode_one`` can be captured in a CUDA graph.
 """
 
+import ctypes
 from dataclasses import dataclass
 
 import numpy as np
 
+from . import _lib
 from .moe_layer import RMSNormInference
 from .quantized_linear import (DevicePackedGGUFWeight, dequantize_device, packed_to_device, quantized_linear,
                                quantized_swiglu, retile_enabled, retile_gate_up, retile_weight)
@@ -77,6 +79,7 @@ class ExternalLlamaModel:
         if dtype not in ("float32", "float16", "bfloat16"):
             raise ValueError("dtype must be float32, float16 or bfloat16")
         self.config, self.dtype, self.device = config, getattr(torch, dtype), device
+        self.fused_decode = True       # one-token steps use the RoPE+store and attention kernels
         self._loaded = False
 
     def expected_shapes(self):
@@ -210,6 +213,20 @@ class ExternalLlamaModel:
             q = quantized_linear(hidden, layer["q"], out_dtype=torch.float32).reshape(b, t, heads, dh)
             k = quantized_linear(hidden, layer["k"], out_dtype=torch.float32).reshape(b, t, kv_heads, dh)
             v = quantized_linear(hidden, layer["v"], out_dtype=torch.float32).reshape(b, t, kv_heads, dh)
+            if t == 1 and dh in (64, 128) and self.fused_decode:
+                # one-token step: RoPE + cache store, then single-query attention, one kernel each
+                ptr = lambda x: ctypes.c_void_p(x.data_ptr())
+                cache_id = _lib.DTYPE_ID[str(self.dtype).replace("torch.", "")]
+                _lib.call("b200q_rope_kv_store", ptr(q), ptr(k), ptr(v), ptr(positions), ptr(self._cos), ptr(self._sin),
+                          b, 1, heads, kv_heads, dh, state.horizon, ptr(state.k[i]), ptr(state.v[i]), cache_id,
+                          _lib.current_stream())
+                ctx = torch.empty((b, heads * dh), dtype=self.dtype, device=q.device)
+                _lib.call("b200q_decode_attention", ptr(q), ptr(state.k[i]), ptr(state.v[i]), cache_id, ptr(positions), b,
+                          heads, kv_heads, dh, state.horizon, float(dh ** -0.5), ptr(ctx), cache_id, _lib.current_stream())
+                attn = quantized_linear(ctx, layer["o"])
+                residual, hidden = layer["norm2"].forward_residual_add(residual, attn)
+                hidden, residual = self._ffn(i, layer, hidden, residual)
+                continue
             q, k = self._rope(q, positions), self._rope(k, positions)
             state.k[i].index_copy_(2, positions, k.permute(0, 2, 1, 3).to(self.dtype))
             state.v[i].index_copy_(2, positions, v.permute(0, 2, 1, 3).to(self.dtype))
@@ -222,16 +239,23 @@ class ExternalLlamaModel:
             ctx = ctx.permute(0, 2, 1, 3).reshape(b * t, heads * dh).to(self.dtype).contiguous()
             attn = quantized_linear(ctx, layer["o"])
             residual, hidden = layer["norm2"].forward_residual_add(residual, attn)
-            if layer["gate"].quant_type == "Q8_0_TILED" and layer["up"].quant_type == "Q8_0_TILED":
-                g = quantized_linear(hidden, layer["gate"], out_dtype=torch.float32)
-                u = quantized_linear(hidden, layer["up"], out_dtype=torch.float32)
-                act = (torch.nn.functional.silu(g) * u).to(self.dtype)
-            else:
-                act = quantized_swiglu(hidden, layer["gate"], layer["up"])
-            ffn = quantized_linear(act, layer["down"])
-            nxt = self.layers[i + 1]["norm1"] if i + 1 < len(self.layers) else self.final_norm
-            residual, hidden = nxt.forward_residual_add(residual, ffn)
+            hidden, residual = self._ffn(i, layer, hidden, residual)
         return hidden
+
+    def _ffn(self, i, layer, hidden, residual):
+        """SwiGLU FFN on the normalised ``hidden``; returns the next layer's normalised input and the
+        updated FP32 residual stream."""
+        torch = _torch()
+        if layer["gate"].quant_type == "Q8_0_TILED" and layer["up"].quant_type == "Q8_0_TILED":
+            g = quantized_linear(hidden, layer["gate"], out_dtype=torch.float32)
+            u = quantized_linear(hidden, layer["up"], out_dtype=torch.float32)
+            act = (torch.nn.functional.silu(g) * u).to(self.dtype)
+        else:
+            act = quantized_swiglu(hidden, layer["gate"], layer["up"])
+        ffn = quantized_linear(act, layer["down"])
+        nxt = self.layers[i + 1]["norm1"] if i + 1 < len(self.layers) else self.final_norm
+        residual, hidden = nxt.forward_residual_add(residual, ffn)
+        return hidden, residual
 
     def prefill(self, token_ids, state):
         """token_ids [B, T] int64 CUDA tensor; fills the cache from position 0; returns the logits of

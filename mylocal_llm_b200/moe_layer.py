@@ -20,7 +20,7 @@ import ctypes
 from . import _lib, moe_ops
 from .experts_inference import ExpertsInference, PackedExpertBank, ResidentExpertExecutor
 from .quantized_linear import (DevicePackedGGUFWeight, quantized_linear, quantized_swiglu, retile_enabled,
-                               retile_weight)
+                               retile_gate_up, retile_weight)
 from .router_inference import RouterInference
 
 

@@ -49,6 +49,27 @@ def test_prefill_and_decode_logits_match_the_oracle(cuda, dtype, rtol, atol):
     assert state.length == 12 and int(state.position.item()) == 12
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_fused_decode_kernels_agree_with_the_framework_ops(cuda, dtype):
+    """RoPE + cache store and single-query attention as two kernels vs the same step in torch ops."""
+    torch = cuda
+    model = ExternalLlamaModel(ExternalLlamaConfig(**CFG), dtype=dtype)
+    packed, _ = make_weights(model, seed=7)
+    model.set_weights(packed)
+    tokens = torch.from_numpy(np.random.default_rng(8).integers(0, CFG["vocab_size"], (2, 9))).cuda()
+    outs = {}
+    for fused in (True, False):
+        model.fused_decode = fused
+        state = model.create_generation_state(2, 24)
+        model.prefill(tokens[:, :5].contiguous(), state)
+        outs[fused] = [model.decode_one(tokens[:, i].contiguous(), state).clone() for i in range(5, 9)]
+        outs[fused].append(state.k.float().clone())
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    for a, b in zip(outs[True], outs[False]):
+        scale = float(b.abs().max())
+        assert float((a - b).abs().max()) <= tol * max(scale, 1.0)
+
+
 def test_batched_prefill_rows_are_independent(cuda):
     torch = cuda
     model = ExternalLlamaModel(ExternalLlamaConfig(**CFG), dtype="float32")
