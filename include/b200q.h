@@ -210,16 +210,24 @@ int b200q_q6k_untile(const void *tiled, void *native, int64_t rows, int k, void 
 
 /* Rotate-half RoPE of q (in place, FP32 [B,T,H,Dh]) and k, and store of rotated k and v (FP32
  * [B,T,Hkv,Dh]) into the caches [B,Hkv,horizon,Dh] (cache_dtype) at positions[t] (device int64 [T]);
- * cos/sin tables are FP32 [max_pos, Dh/2] with theta_i = pos / base^(2i/Dh). */
-int b200q_rope_kv_store(float *q, const float *k, const float *v, const int64_t *positions, const float *cos_table,
+ * *_row_stride = elements between consecutive (b,t) rows (q, k, v may be column slices of one fused
+ * projection output); cos/sin tables are FP32 [max_pos, Dh/2] with theta_i = pos / base^(2i/Dh). */
+int b200q_rope_kv_store(float *q, const float *k, const float *v, int64_t q_row_stride, int64_t k_row_stride,
+                        int64_t v_row_stride, const int64_t *positions, const float *cos_table,
                         const float *sin_table, int batch, int t, int heads, int kv_heads, int head_dim, int horizon,
                         void *k_cache, void *v_cache, int cache_dtype, void *stream);
 
+/* act[m, f] = silu(gu[m, f]) * gu[m, F + f] for a stacked gate|up projection output gu [M, 2F] FP32
+ * (the epilogue of b200q_swiglu as a separate step, for weights whose tile layout has no fused
+ * SwiGLU kernel). */
+int b200q_silu_mul(const float *gate_up, int m, int f, void *out, int out_dtype, void *stream);
+
 /* Single-query attention: out[b, h*Dh..] = softmax(scale * q[b,h] . K[b,kv(h),0..pos]) V, with
- * pos = position[0] read on the device (graph-capturable); q FP32 [B,H,Dh]; head_dim 64 or 128. */
-int b200q_decode_attention(const float *q, const void *k_cache, const void *v_cache, int cache_dtype,
-                           const int64_t *position, int batch, int heads, int kv_heads, int head_dim, int horizon,
-                           float scale, void *out, int out_dtype, void *stream);
+ * pos = position[0] read on the device (graph-capturable); q FP32 [B,H,Dh] with q_row_stride elements
+ * between batch rows; head_dim 64 or 128. */
+int b200q_decode_attention(const float *q, int64_t q_row_stride, const void *k_cache, const void *v_cache,
+                           int cache_dtype, const int64_t *position, int batch, int heads, int kv_heads, int head_dim,
+                           int horizon, float scale, void *out, int out_dtype, void *stream);
 
 /* ---- Expert-parallel execution over the GPUs of one node (no counterpart in the reference, which is
  * single-process; semantics = the single-GPU layer, bit for bit). ------------------------------- */

@@ -7,9 +7,12 @@
 
 namespace b200q {
 
-// q [B, T, H, Dh], k / v [B, T, Hkv, Dh] FP32; positions [T] (device); cos / sin [max_pos, Dh/2].
-// q is rotated in place; rotated k and plain v go to cache[b, hkv, positions[t], :].
-__global__ void __launch_bounds__(256) rope_kv_store_kernel(float *q, const float *k, const float *v,
+// q [B, T, H, Dh], k / v [B, T, Hkv, Dh] FP32, each with its own element stride between (b, t)
+// rows (so they may be column slices of one fused projection output); positions [T] (device);
+// cos / sin [max_pos, Dh/2]. q is rotated in place; rotated k and plain v go to
+// cache[b, hkv, positions[t], :].
+__global__ void __launch_bounds__(256) rope_kv_store_kernel(float *q, const float *k, const float *v, long long q_row,
+                                                            long long k_row, long long v_row,
                                                             const long long *positions, const float *cos_t,
                                                             const float *sin_t, int b, int t, int h, int hkv, int dh,
                                                             int horizon, void *k_cache, void *v_cache,
@@ -26,14 +29,14 @@ __global__ void __launch_bounds__(256) rope_kv_store_kernel(float *q, const floa
         const int bb = static_cast<int>(rest / t);
         const long long pos = positions[tt];
         if (head < h) {
-            float *p = q + ((static_cast<size_t>(bb) * t + tt) * h + head) * dh;
+            float *p = q + (static_cast<size_t>(bb) * t + tt) * q_row + static_cast<size_t>(head) * dh;
             const float c = cos_t[pos * half + i], s = sin_t[pos * half + i];
             const float x0 = p[i], x1 = p[half + i];
             p[i] = x0 * c - x1 * s;
             p[half + i] = x0 * s + x1 * c;
         } else if (head < h + hkv) {
             const int kh = head - h;
-            const float *p = k + ((static_cast<size_t>(bb) * t + tt) * hkv + kh) * dh;
+            const float *p = k + (static_cast<size_t>(bb) * t + tt) * k_row + static_cast<size_t>(kh) * dh;
             const float c = cos_t[pos * half + i], s = sin_t[pos * half + i];
             const float x0 = p[i], x1 = p[half + i];
             const size_t dst = ((static_cast<size_t>(bb) * hkv + kh) * horizon + pos) * dh;
@@ -43,7 +46,7 @@ __global__ void __launch_bounds__(256) rope_kv_store_kernel(float *q, const floa
             }
         } else {
             const int vh = head - h - hkv;
-            const float *p = v + ((static_cast<size_t>(bb) * t + tt) * hkv + vh) * dh;
+            const float *p = v + (static_cast<size_t>(bb) * t + tt) * v_row + static_cast<size_t>(vh) * dh;
             const size_t dst = ((static_cast<size_t>(bb) * hkv + vh) * horizon + pos) * dh;
             if (pos >= 0 && pos < horizon) {
                 store_from_float(v_cache, cache_dtype, dst + i, p[i]);
@@ -94,9 +97,9 @@ constexpr int ATT_U = 8;
 template <int EPL>
 __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const float *q, const void *k_cache,
                                                                           const void *v_cache, int cache_dtype,
-                                                                          const long long *position, int h, int hkv,
-                                                                          int horizon, float scale, void *out,
-                                                                          int out_dtype) {
+                                                                          const long long *position, long long q_row,
+                                                                          int h, int hkv, int horizon, float scale,
+                                                                          void *out, int out_dtype) {
     constexpr int DH = EPL * 32;
     __shared__ float sm_m[ATT_WARPS], sm_l[ATT_WARPS], sm_acc[ATT_WARPS][DH];
     const int bh = blockIdx.x, bb = bh / h, head = bh - bb * h;
@@ -104,7 +107,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     long long last = position[0];                       // newest valid cache position
     if (last >= horizon) last = horizon - 1;
-    const float *qp = q + (static_cast<size_t>(bb) * h + head) * DH;
+    const float *qp = q + static_cast<size_t>(bb) * q_row + static_cast<size_t>(head) * DH;
     float qv[EPL];
 #pragma unroll
     for (int e = 0; e < EPL; ++e) qv[e] = qp[lane * EPL + e] * scale;
@@ -174,43 +177,67 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     }
 }
 
+// act[m, f] = silu(gu[m, f]) * gu[m, F + f] for a stacked gate|up projection output gu [M, 2F] (FP32).
+__global__ void __launch_bounds__(256) silu_mul_kernel(const float *gu, int m, int f, void *out, int out_dtype) {
+    const long long total = static_cast<long long>(m) * f;
+    for (long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; idx < total;
+         idx += static_cast<long long>(gridDim.x) * 256) {
+        const long long row = idx / f, col = idx - row * f;
+        const float g = gu[row * 2 * f + col], u = gu[row * 2 * f + f + col];
+        store_from_float(out, out_dtype, static_cast<size_t>(idx), swiglu_f32(g, u));
+    }
+}
+
 }  // namespace b200q
 
 using namespace b200q;
 
 extern "C" {
 
-int b200q_rope_kv_store(float *q, const float *k, const float *v, const int64_t *positions, const float *cos_table,
+int b200q_rope_kv_store(float *q, const float *k, const float *v, int64_t q_row_stride, int64_t k_row_stride,
+                        int64_t v_row_stride, const int64_t *positions, const float *cos_table,
                         const float *sin_table, int batch, int t, int heads, int kv_heads, int head_dim, int horizon,
                         void *k_cache, void *v_cache, int cache_dtype, void *stream) {
     if (!q || !k || !v || !positions || !cos_table || !sin_table || !k_cache || !v_cache)
         return fail(B200Q_EINVAL, "rope_kv_store: NULL pointer");
     if (batch <= 0 || t <= 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || head_dim % 2 || horizon <= 0 ||
-        !dtype_valid(cache_dtype))
+        !dtype_valid(cache_dtype) || q_row_stride < static_cast<int64_t>(heads) * head_dim ||
+        k_row_stride < static_cast<int64_t>(kv_heads) * head_dim ||
+        v_row_stride < static_cast<int64_t>(kv_heads) * head_dim)
         return fail(B200Q_EINVAL, "rope_kv_store: bad argument");
     const long long total = static_cast<long long>(batch) * t * (heads + 2 * kv_heads) * (head_dim / 2);
     const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 4096));
     rope_kv_store_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        q, k, v, reinterpret_cast<const long long *>(positions), cos_table, sin_table, batch, t, heads, kv_heads,
+        q, k, v, q_row_stride, k_row_stride, v_row_stride, reinterpret_cast<const long long *>(positions), cos_table,
+        sin_table, batch, t, heads, kv_heads,
         head_dim, horizon, k_cache, v_cache, cache_dtype);
     return check_launch("rope_kv_store");
 }
 
-int b200q_decode_attention(const float *q, const void *k_cache, const void *v_cache, int cache_dtype,
-                           const int64_t *position, int batch, int heads, int kv_heads, int head_dim, int horizon,
-                           float scale, void *out, int out_dtype, void *stream) {
+int b200q_silu_mul(const float *gate_up, int m, int f, void *out, int out_dtype, void *stream) {
+    if (!gate_up || !out) return fail(B200Q_EINVAL, "silu_mul: NULL pointer");
+    if (m <= 0 || f <= 0 || !dtype_valid(out_dtype)) return fail(B200Q_EINVAL, "silu_mul: bad argument");
+    const long long total = static_cast<long long>(m) * f;
+    const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 4096));
+    silu_mul_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(gate_up, m, f, out, out_dtype);
+    return check_launch("silu_mul");
+}
+
+int b200q_decode_attention(const float *q, int64_t q_row_stride, const void *k_cache, const void *v_cache,
+                           int cache_dtype, const int64_t *position, int batch, int heads, int kv_heads, int head_dim,
+                           int horizon, float scale, void *out, int out_dtype, void *stream) {
     if (!q || !k_cache || !v_cache || !position || !out) return fail(B200Q_EINVAL, "decode_attention: NULL pointer");
     if (batch <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || horizon <= 0 || !dtype_valid(cache_dtype) ||
-        !dtype_valid(out_dtype))
+        !dtype_valid(out_dtype) || q_row_stride < static_cast<int64_t>(heads) * head_dim)
         return fail(B200Q_EINVAL, "decode_attention: bad argument");
     const long long *pos = reinterpret_cast<const long long *>(position);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (head_dim == 64)
-        decode_attention_kernel<2><<<batch * heads, ATT_WARPS * 32, 0, s>>>(q, k_cache, v_cache, cache_dtype, pos, heads, kv_heads,
-                                                                 horizon, scale, out, out_dtype);
+        decode_attention_kernel<2><<<batch * heads, ATT_WARPS * 32, 0, s>>>(q, k_cache, v_cache, cache_dtype, pos, q_row_stride, heads,
+                                                                 kv_heads, horizon, scale, out, out_dtype);
     else if (head_dim == 128)
-        decode_attention_kernel<4><<<batch * heads, ATT_WARPS * 32, 0, s>>>(q, k_cache, v_cache, cache_dtype, pos, heads, kv_heads,
-                                                                 horizon, scale, out, out_dtype);
+        decode_attention_kernel<4><<<batch * heads, ATT_WARPS * 32, 0, s>>>(q, k_cache, v_cache, cache_dtype, pos, q_row_stride, heads,
+                                                                 kv_heads, horizon, scale, out, out_dtype);
     else
         return fail(B200Q_EUNSUPPORTED, "decode_attention: head_dim must be 64 or 128");
     return check_launch("decode_attention");

@@ -132,6 +132,16 @@ class ExternalLlamaModel:
             module.set_weights(gamma.contiguous())
             return module
 
+        def stacked(names):
+            """Rows of several same-format matrices with equal K as one device matrix (one launch for
+            all of them), or None when the formats differ."""
+            parts = [self._matrix(weights[n], tile=False) for n in names]
+            if len({w.quant_type for w in parts}) != 1 or len({w.shape[1] for w in parts}) != 1:
+                return None
+            data = torch.cat([w.data for w in parts])
+            rows = sum(w.shape[0] for w in parts)
+            return self._matrix(DevicePackedGGUFWeight(data, (rows, parts[0].shape[1]), parts[0].quant_type))
+
         self.embed = self._matrix(weights["model.embed_tokens.weight"], tile=False)     # rows are gathered
         self.lm_head = self.embed if cfg.tie_word_embeddings else self._matrix(weights["lm_head.weight"])
         if cfg.tie_word_embeddings and retile_enabled():
@@ -142,22 +152,27 @@ class ExternalLlamaModel:
             p = f"model.layers.{i}."
             self.layers.append({
                 "norm1": norm(p + "input_layernorm.weight"), "norm2": norm(p + "post_attention_layernorm.weight"),
-                "q": self._matrix(weights[p + "self_attn.q_proj.weight"]),
-                "k": self._matrix(weights[p + "self_attn.k_proj.weight"]),
-                "v": self._matrix(weights[p + "self_attn.v_proj.weight"]),
+                "qkv": stacked([p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight",
+                                p + "self_attn.v_proj.weight"]),
                 "o": self._matrix(weights[p + "self_attn.o_proj.weight"]),
                 "gate": self._matrix(weights[p + "mlp.gate_proj.weight"], tile=False),
                 "up": self._matrix(weights[p + "mlp.up_proj.weight"], tile=False),
                 "down": self._matrix(weights[p + "mlp.down_proj.weight"]),
             })
             layer = self.layers[-1]
-            if retile_enabled():
-                force = self.dtype != torch.float32
-                if layer["gate"].quant_type == layer["up"].quant_type == "Q8_0":
-                    # no fused SwiGLU kernel reads Q8_0 tiles: two tiled GEMVs and an elementwise product
-                    layer["gate"], layer["up"] = retile_weight(layer["gate"], force), retile_weight(layer["up"], force)
-                else:
-                    layer["gate"], layer["up"] = retile_gate_up(layer["gate"], layer["up"], force)
+            if layer["qkv"] is None:
+                for key, name in (("q", "q_proj"), ("k", "k_proj"), ("v", "v_proj")):
+                    layer[key] = self._matrix(weights[p + f"self_attn.{name}.weight"])
+            layer["gate_up"] = None
+            if layer["gate"].quant_type == layer["up"].quant_type == "Q8_0" and retile_enabled():
+                # no fused SwiGLU kernel reads Q8_0 tiles: one tiled GEMV for both, then the product
+                layer["gate_up"] = stacked([p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight"])
+                if layer["gate_up"] is not None and layer["gate_up"].quant_type != "Q8_0_TILED":
+                    layer["gate_up"] = None
+            if layer["gate_up"] is not None:
+                layer["gate"] = layer["up"] = None
+            elif retile_enabled():
+                layer["gate"], layer["up"] = retile_gate_up(layer["gate"], layer["up"], self.dtype != torch.float32)
         half = cfg.head_dim // 2
         inv = 1.0 / (float(cfg.rope_theta) ** (2.0 * np.arange(half) / cfg.head_dim))
         ang = np.arange(cfg.max_position_embeddings)[:, None] * inv[None, :]
@@ -169,7 +184,8 @@ class ExternalLlamaModel:
     def packed_bytes(self):
         total = self.embed.nbytes + (0 if self.config.tie_word_embeddings else self.lm_head.nbytes)
         for layer in self.layers:
-            total += sum(layer[n].nbytes for n in ("q", "k", "v", "o", "gate", "up", "down"))
+            total += sum(layer[n].nbytes for n in ("qkv", "q", "k", "v", "o", "gate_up", "gate", "up", "down")
+                         if layer.get(n) is not None)
         return total
 
     # ------------------------------------------------------------------------------ running
@@ -210,23 +226,30 @@ class ExternalLlamaModel:
         residual = self._embed(token_ids)                                         # FP32 [B*T, d]
         hidden = self.layers[0]["norm1"].forward_residual(residual)
         for i, layer in enumerate(self.layers):
-            q = quantized_linear(hidden, layer["q"], out_dtype=torch.float32).reshape(b, t, heads, dh)
-            k = quantized_linear(hidden, layer["k"], out_dtype=torch.float32).reshape(b, t, kv_heads, dh)
-            v = quantized_linear(hidden, layer["v"], out_dtype=torch.float32).reshape(b, t, kv_heads, dh)
+            qd, kd = heads * dh, kv_heads * dh
+            if layer["qkv"] is not None:                     # one launch for the three projections
+                qkv = quantized_linear(hidden, layer["qkv"], out_dtype=torch.float32)
+                q2, k2, v2 = qkv[:, :qd], qkv[:, qd:qd + kd], qkv[:, qd + kd:]
+            else:
+                q2 = quantized_linear(hidden, layer["q"], out_dtype=torch.float32)
+                k2 = quantized_linear(hidden, layer["k"], out_dtype=torch.float32)
+                v2 = quantized_linear(hidden, layer["v"], out_dtype=torch.float32)
             if t == 1 and dh in (64, 128) and self.fused_decode:
                 # one-token step: RoPE + cache store, then single-query attention, one kernel each
                 ptr = lambda x: ctypes.c_void_p(x.data_ptr())
                 cache_id = _lib.DTYPE_ID[str(self.dtype).replace("torch.", "")]
-                _lib.call("b200q_rope_kv_store", ptr(q), ptr(k), ptr(v), ptr(positions), ptr(self._cos), ptr(self._sin),
-                          b, 1, heads, kv_heads, dh, state.horizon, ptr(state.k[i]), ptr(state.v[i]), cache_id,
+                _lib.call("b200q_rope_kv_store", ptr(q2), ptr(k2), ptr(v2), q2.stride(0), k2.stride(0), v2.stride(0),
+                          ptr(positions), ptr(self._cos), ptr(self._sin), b, 1, heads, kv_heads, dh, state.horizon,
+                          ptr(state.k[i]), ptr(state.v[i]), cache_id, _lib.current_stream())
+                ctx = torch.empty((b, heads * dh), dtype=self.dtype, device=hidden.device)
+                _lib.call("b200q_decode_attention", ptr(q2), q2.stride(0), ptr(state.k[i]), ptr(state.v[i]), cache_id,
+                          ptr(positions), b, heads, kv_heads, dh, state.horizon, float(dh ** -0.5), ptr(ctx), cache_id,
                           _lib.current_stream())
-                ctx = torch.empty((b, heads * dh), dtype=self.dtype, device=q.device)
-                _lib.call("b200q_decode_attention", ptr(q), ptr(state.k[i]), ptr(state.v[i]), cache_id, ptr(positions), b,
-                          heads, kv_heads, dh, state.horizon, float(dh ** -0.5), ptr(ctx), cache_id, _lib.current_stream())
                 attn = quantized_linear(ctx, layer["o"])
                 residual, hidden = layer["norm2"].forward_residual_add(residual, attn)
                 hidden, residual = self._ffn(i, layer, hidden, residual)
                 continue
+            q, k, v = q2.reshape(b, t, heads, dh), k2.reshape(b, t, kv_heads, dh), v2.reshape(b, t, kv_heads, dh)
             q, k = self._rope(q, positions), self._rope(k, positions)
             state.k[i].index_copy_(2, positions, k.permute(0, 2, 1, 3).to(self.dtype))
             state.v[i].index_copy_(2, positions, v.permute(0, 2, 1, 3).to(self.dtype))
@@ -246,10 +269,12 @@ class ExternalLlamaModel:
         """SwiGLU FFN on the normalised ``hidden``; returns the next layer's normalised input and the
         updated FP32 residual stream."""
         torch = _torch()
-        if layer["gate"].quant_type == "Q8_0_TILED" and layer["up"].quant_type == "Q8_0_TILED":
-            g = quantized_linear(hidden, layer["gate"], out_dtype=torch.float32)
-            u = quantized_linear(hidden, layer["up"], out_dtype=torch.float32)
-            act = (torch.nn.functional.silu(g) * u).to(self.dtype)
+        if layer["gate_up"] is not None:
+            gu = quantized_linear(hidden, layer["gate_up"], out_dtype=torch.float32)
+            f = gu.shape[1] // 2
+            act = torch.empty((gu.shape[0], f), dtype=self.dtype, device=gu.device)
+            _lib.call("b200q_silu_mul", ctypes.c_void_p(gu.data_ptr()), gu.shape[0], f, ctypes.c_void_p(act.data_ptr()),
+                      _lib.DTYPE_ID[str(self.dtype).replace("torch.", "")], _lib.current_stream())
         else:
             act = quantized_swiglu(hidden, layer["gate"], layer["up"])
         ffn = quantized_linear(act, layer["down"])

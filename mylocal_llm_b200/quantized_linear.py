@@ -90,7 +90,14 @@ def packed_bytes_to_device(raw):
     torch = _torch()
     if not torch.cuda.is_available():
         raise RuntimeError("Packed GPU weights require a CUDA device")
-    return torch.from_numpy(np.ascontiguousarray(raw, dtype=np.uint8)).cuda()
+    host = np.ascontiguousarray(raw, dtype=np.uint8)
+    if not host.flags.writeable:
+        # read-only file mappings: the tensor is only the source of the copy and is never written
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)
+            return torch.from_numpy(host).cuda()
+    return torch.from_numpy(host).cuda()
 
 
 def packed_to_device(weight):

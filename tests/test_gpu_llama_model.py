@@ -15,14 +15,16 @@ FORMATS = {"self_attn.q_proj": "Q8_0", "self_attn.k_proj": "Q8_0", "self_attn.v_
            "self_attn.o_proj": "Q8_0", "mlp.gate_proj": "Q4_K", "mlp.up_proj": "Q4_K", "mlp.down_proj": "Q6_K"}
 
 
-def make_weights(model, seed=0):
+def make_weights(model, seed=0, uniform=False):
+    """Mixed formats by default; ``uniform`` = Q8_0 everywhere (the model then stacks q/k/v and
+    gate/up into single matrices)."""
     rng = np.random.default_rng(seed)
     packed, oracle = {}, {}
     for name, shape in model.expected_shapes().items():
         if len(shape) == 1:
             packed[name] = oracle[name] = (1.0 + 0.1 * rng.normal(size=shape)).astype(np.float32)
             continue
-        fmt = next((f for key, f in FORMATS.items() if key in name), "Q8_0")
+        fmt = "Q8_0" if uniform else next((f for key, f in FORMATS.items() if key in name), "Q8_0")
         scale = 0.5 if "embed" in name else 1.0 / np.sqrt(shape[1])
         w = quantize(rng.normal(0, scale, shape).astype(np.float32), fmt)
         packed[name] = w
@@ -30,12 +32,14 @@ def make_weights(model, seed=0):
     return packed, oracle
 
 
+@pytest.mark.parametrize("uniform", [False, True])
 @pytest.mark.parametrize("dtype,rtol,atol", [("float32", 2e-3, 2e-3), ("bfloat16", 6e-2, 6e-2)])
-def test_prefill_and_decode_logits_match_the_oracle(cuda, dtype, rtol, atol):
+def test_prefill_and_decode_logits_match_the_oracle(cuda, dtype, rtol, atol, uniform):
     torch = cuda
     model = ExternalLlamaModel(ExternalLlamaConfig(**CFG), dtype=dtype)
-    packed, oracle = make_weights(model)
+    packed, oracle = make_weights(model, uniform=uniform)
     model.set_weights(packed)
+    assert (model.layers[0]["qkv"] is not None) == uniform and (model.layers[0]["gate_up"] is not None) == uniform
     tokens = np.random.default_rng(1).integers(0, CFG["vocab_size"], 12)
     state = model.create_generation_state(1, 32)
     prompt = torch.from_numpy(tokens[:9][None]).cuda()
@@ -54,7 +58,7 @@ def test_fused_decode_kernels_agree_with_the_framework_ops(cuda, dtype):
     """RoPE + cache store and single-query attention as two kernels vs the same step in torch ops."""
     torch = cuda
     model = ExternalLlamaModel(ExternalLlamaConfig(**CFG), dtype=dtype)
-    packed, _ = make_weights(model, seed=7)
+    packed, _ = make_weights(model, seed=7, uniform=dtype == "bfloat16")
     model.set_weights(packed)
     tokens = torch.from_numpy(np.random.default_rng(8).integers(0, CFG["vocab_size"], (2, 9))).cuda()
     outs = {}
