@@ -96,12 +96,18 @@ class ClockSampler:
         self.proc = None
         self.lines = []
         self.thread = None
+        self.first_timed = 0
+
+    def mark_timed_region(self):
+        """Samples taken from now on belong to the timed region (the sampler is started before the warm-up
+        so that nvidia-smi is already running when a short timed region begins)."""
+        self.first_timed = len(self.lines)
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -124,7 +130,12 @@ class ClockSampler:
             self.thread.join(timeout=2)
         clocks, max_clock, reasons = [], None, set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.lines:
+        window = "timed region"
+        lines = self.lines[self.first_timed:]
+        if not lines:                       # region shorter than one sampling period: use the warm-up under the same load
+            lines, window = self.lines, "warm-up + timed region"
+        self.window = window
+        for line in lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -137,7 +148,7 @@ class ClockSampler:
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
-                "reasons": sorted(reasons), "samples": len(clocks)}
+                "reasons": sorted(reasons), "samples": len(clocks), "window": window}
 
 
 # ------------------------------------------------------------------------------ CPU reference arm
@@ -258,12 +269,13 @@ def run_gpu_arm(args, name):
             torch.cuda.synchronize()
 
         # ---- device-resident throughput
-        for _ in range(max(3, args.warmup)):
-            graph.replay()
-        barrier()
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
+        for _ in range(max(3, args.warmup)):
+            graph.replay()
+        barrier()
+        sampler.mark_timed_region()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record(stream)
         for _ in range(args.steps):
@@ -528,12 +540,13 @@ def run_moe_gpu_arm(args, name):
                 dist.barrier()
             torch.cuda.synchronize()
 
-        for _ in range(max(3, args.warmup)):
-            graph.replay()
-        barrier()
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
+        for _ in range(max(3, args.warmup)):
+            graph.replay()
+        barrier()
+        sampler.mark_timed_region()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(args.steps):
@@ -730,12 +743,13 @@ def run_llama_gpu_arm(args, name):
 
         budget = state.horizon - LLAMA_PROMPT - 2
         steps = min(args.steps, (budget - 2 * max(3, args.warmup)) // 2)
-        for _ in range(max(3, args.warmup)):
-            graph.replay()
-        barrier()
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
+        for _ in range(max(3, args.warmup)):
+            graph.replay()
+        barrier()
+        sampler.mark_timed_region()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(steps):
