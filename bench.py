@@ -52,6 +52,12 @@ WORKLOADS = {
     "gemv_q8_0_4096x4096_m1": ("Q8_0", 4096, 4096, 1, "float32"),
     "gemv_q8_0_4096x4096_m8": ("Q8_0", 4096, 4096, 8, "float32"),
     "gemv_q4k_65536x8192_m1": ("Q4_K", 65536, 8192, 1, "bfloat16"),
+    # shapes of the third configuration (Q8_0 Llama): LM head and the stacked gate|up projection
+    "gemv_q8_0_49152x2048_m1": ("Q8_0", 49152, 2048, 1, "bfloat16"),
+    "gemv_q8_0_16384x2048_m1": ("Q8_0", 16384, 2048, 1, "bfloat16"),
+    "gemv_q6k_65536x2048_m1": ("Q6_K", 65536, 2048, 1, "bfloat16"),
+    "gemv_q8_0_131072x4096_m1": ("Q8_0", 131072, 4096, 1, "bfloat16"),
+    "gemv_q8_0_131072x4096_m8": ("Q8_0", 131072, 4096, 8, "bfloat16"),
 }
 # name: (layers, tokens per step, chained)  - the packed MoE layer of the baseline's fourth configuration
 # (hidden 2048, 512 experts of width 512, top-10, shared expert, Q4_K gate/up + Q6_K down); "stack" = the
