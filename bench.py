@@ -58,6 +58,10 @@ WORKLOADS = {
     "gemv_q6k_65536x2048_m1": ("Q6_K", 65536, 2048, 1, "bfloat16"),
     "gemv_q8_0_131072x4096_m1": ("Q8_0", 131072, 4096, 1, "bfloat16"),
     "gemv_q8_0_131072x4096_m8": ("Q8_0", 131072, 4096, 8, "bfloat16"),
+    # 16 tokens: two 8-token tiles share one pass over the weights
+    "gemv_q8_0_131072x4096_m16": ("Q8_0", 131072, 4096, 16, "bfloat16"),
+    "gemv_q4k_65536x4096_m8": ("Q4_K", 65536, 4096, 8, "bfloat16"),
+    "gemv_q4k_65536x4096_m16": ("Q4_K", 65536, 4096, 16, "bfloat16"),
 }
 # name: (layers, tokens per step, chained)  - the packed MoE layer of the baseline's fourth configuration
 # (hidden 2048, 512 experts of width 512, top-10, shared expert, Q4_K gate/up + Q6_K down); "stack" = the

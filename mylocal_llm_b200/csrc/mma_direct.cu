@@ -6,15 +6,28 @@ namespace b200q {
 
 using DirectFn = void (*)(const DirectArgs);
 
-template <bool Q5, int NT>
-static DirectFn pick_mode(int mode) {
+template <bool Q5, int NTERMS>
+static DirectFn pick_mode(int mode, int token_tiles) {
     switch (mode) {
-        case 0: return mma_direct_kernel<Q5, 0, NT>;
-        case 1: return mma_direct_kernel<Q5, 1, NT>;
-        case 2: return mma_direct_kernel<Q5, 2, NT>;
-        case 3: return mma_direct_kernel<Q5, 3, NT>;
+        case 0: return token_tiles == 2 ? mma_direct_kernel<Q5, 0, NTERMS, 2> : mma_direct_kernel<Q5, 0, NTERMS, 1>;
+        case 1: return token_tiles == 2 ? mma_direct_kernel<Q5, 1, NTERMS, 2> : mma_direct_kernel<Q5, 1, NTERMS, 1>;
+        case 2: return mma_direct_kernel<Q5, 2, NTERMS, 1>;
+        case 3: return mma_direct_kernel<Q5, 3, NTERMS, 1>;
     }
     return nullptr;
+}
+
+static long long direct_smem_bytes(int k, int x_dtype, int token_tiles) {
+    const long long nterms = (x_dtype == B200Q_F32) ? 2 : 1;
+    const long long nsb = k / 256;
+    return MD_CTRL_BYTES + static_cast<long long>(token_tiles) * (MD_PART_BYTES + nterms * nsb * 16 * 256 + nsb * 2 * 128);
+}
+
+// Tokens one launch of the direct kernel can take: 16 in the dense modes (two 8-token tiles share
+// one pass over the weights) when both tiles' activation fragments fit in shared memory, else 8.
+int direct_tokens_per_pass(int fmt, int mode, int k, int x_dtype) {
+    if ((fmt != B200Q_Q4_K && fmt != B200Q_Q5_K) || mode > 1 || k <= 0 || k % 256 != 0) return 8;
+    return direct_smem_bytes(k, x_dtype, 2) <= MM_SMEM_LIMIT ? 16 : 8;
 }
 
 int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) {
@@ -23,7 +36,8 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) 
     const bool grouped = q.mode >= 2;
     if (q.fmt_a != B200Q_Q4_K && q.fmt_a != B200Q_Q5_K) return B200Q_OK;
     if (dual && q.fmt_a != q.fmt_b) return B200Q_OK;
-    if (q.k % 256 != 0 || q.m > 8) return B200Q_OK;
+    if (q.k % 256 != 0 || q.m > direct_tokens_per_pass(q.fmt_a, q.mode, q.k, q.x_dtype)) return B200Q_OK;
+    const int token_tiles = q.m > 8 ? 2 : 1;
     if (q.tiled && (q.fmt_a != B200Q_Q4_K || q.n % 16 != 0)) return B200Q_OK;
     if (reinterpret_cast<uintptr_t>(q.wa) & 15) return B200Q_OK;
     if (dual && (reinterpret_cast<uintptr_t>(q.wb) & 15)) return B200Q_OK;
@@ -54,10 +68,9 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) 
     while (kp * 2 <= MD_WARPS && kp * 2 <= nsb && blocks_for(kp) < 6LL * sm_count()) kp *= 2;
     a.kp = kp;
     a.rg = MD_WARPS / kp;
-    a.off_bfrag = MD_CTRL_BYTES + MD_PART_BYTES;
-    const long long bfrag_bytes = static_cast<long long>(a.nterms) * nsb * 16 * 256;
-    const long long xs_bytes = static_cast<long long>(nsb) * 2 * 128;
-    const long long smem = a.off_bfrag + bfrag_bytes + xs_bytes;
+    a.off_bfrag = MD_CTRL_BYTES + token_tiles * MD_PART_BYTES;
+    const long long bfrag_bytes = static_cast<long long>(token_tiles) * a.nterms * nsb * 16 * 256;
+    const long long smem = direct_smem_bytes(q.k, q.x_dtype, token_tiles);
     if (smem > MM_SMEM_LIMIT) return B200Q_OK;
     a.off_xsfrag = static_cast<int>(a.off_bfrag + bfrag_bytes);
     a.x = q.x; a.x_dtype = q.x_dtype; a.y = q.y; a.y_dtype = q.y_dtype;
@@ -66,8 +79,9 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) 
     a.route = q.route; a.flat_rows = q.flat_rows; a.y_table = q.y_table; a.rows_per_rank = q.rows_per_rank;
 
     const bool q5 = q.fmt_a == B200Q_Q5_K;
-    DirectFn fn = q5 ? (a.nterms == 2 ? pick_mode<true, 2>(q.mode) : pick_mode<true, 1>(q.mode))
-                     : (a.nterms == 2 ? pick_mode<false, 2>(q.mode) : pick_mode<false, 1>(q.mode));
+    DirectFn fn = q5 ? (a.nterms == 2 ? pick_mode<true, 2>(q.mode, token_tiles) : pick_mode<true, 1>(q.mode, token_tiles))
+                     : (a.nterms == 2 ? pick_mode<false, 2>(q.mode, token_tiles)
+                                      : pick_mode<false, 1>(q.mode, token_tiles));
     if (!fn) return B200Q_OK;
     cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void *>(fn),
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM_LIMIT);

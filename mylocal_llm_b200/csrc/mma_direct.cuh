@@ -1,4 +1,5 @@
-// Direct-load tensor-core GEMV for Q4_K / Q5_K (sm_100a), up to 8 tokens per pass.
+// Direct-load tensor-core GEMV for Q4_K / Q5_K (sm_100a), 8 tokens per token tile, one or two
+// token tiles per pass over the weights.
 //
 // Q4_K / Q5_K super-blocks are 16-byte multiples, so every lane can fetch exactly the packed
 // bytes it needs with 128-bit global loads (four lanes cover 64 contiguous bytes of a row, eight
@@ -304,13 +305,20 @@ __device__ __forceinline__ void prepare_direct(RowFn row_of, int m_tokens, int k
 }
 
 // 16 mma steps of one super-block for rows (g, g+8): acc += sum(sc*q*x); accm += sum(mn * sum_x/64).
-template <bool Q5, int NTERMS>
+// With NT token tiles (8 tokens each; their fragments `btile` / `xtile` entries apart) every decoded
+// A operand is multiplied into each tile, so the decode cost is paid once per 8*NT tokens; the
+// arithmetic of one token does not depend on NT.
+template <bool Q5, int NTERMS, int NT>
 __device__ __forceinline__ void superblock_mma(const SuperBlockRegs<Q5> &ra, const SuperBlockRegs<Q5> &rb,
-                                               const uint2 *bfrag, int nfrag, const uint32_t *xsfrag, int sb, int lane,
-                                               float (&tot)[4]) {
+                                               const uint2 *bfrag, int btile, int nfrag, const uint32_t *xsfrag,
+                                               int xtile, int sb, int lane, float (&tot)[NT][4]) {
     const int tig = lane & 3;
     const RowScales sa = decode_scales(ra.hd, tig), sbk = decode_scales(rb.hd, tig);
-    float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[NT][4], acc2[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nt][i] = acc2[nt][i] = 0.f;
     const uint32_t qa_a[4] = {ra.qa.x, ra.qa.y, ra.qa.z, ra.qa.w}, qb_a[4] = {ra.qb.x, ra.qb.y, ra.qb.z, ra.qb.w};
     const uint32_t qa_b[4] = {rb.qa.x, rb.qa.y, rb.qa.z, rb.qa.w}, qb_b[4] = {rb.qb.x, rb.qb.y, rb.qb.z, rb.qb.w};
     const uint32_t qh_a[4] = {ra.qh.x, ra.qh.y, ra.qh.z, ra.qh.w}, qh_b[4] = {rb.qh.x, rb.qh.y, rb.qh.z, rb.qh.w};
@@ -335,22 +343,28 @@ __device__ __forceinline__ void superblock_mma(const SuperBlockRegs<Q5> &ra, con
                 const uint32_t a2 = hfma2_u32(__byte_perm(va, 0x64646464u, 0x4341), sa.sc[si], sa.nsc[si]);
                 const uint32_t a1 = hfma2_u32(__byte_perm(vb, 0x64646464u, 0x4240), sbk.sc[si], sbk.nsc[si]);
                 const uint32_t a3 = hfma2_u32(__byte_perm(vb, 0x64646464u, 0x4341), sbk.sc[si], sbk.nsc[si]);
-                const BFrag b = load_bfrag<NTERMS>(bfrag, nfrag, sb * 16 + si * 4 + j, lane);
-                if (X) mma_terms<NTERMS>(acc2, a0, a1, a2, a3, b);
-                else mma_terms<NTERMS>(acc, a0, a1, a2, a3, b);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const BFrag b = load_bfrag<NTERMS>(bfrag + nt * btile, nfrag, sb * 16 + si * 4 + j, lane);
+                    if (X) mma_terms<NTERMS>(acc2[nt], a0, a1, a2, a3, b);
+                    else mma_terms<NTERMS>(acc[nt], a0, a1, a2, a3, b);
+                }
             }
         }
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i] += acc2[i];
-    float accm[4] = {0.f, 0.f, 0.f, 0.f};
-    mma_f16(accm, sa.mins, sbk.mins, 0u, 0u, xsfrag[(sb * 2 + 0) * 32 + lane], 0u);
-    mma_f16(accm, sa.mins, sbk.mins, 0u, 0u, xsfrag[(sb * 2 + 1) * 32 + lane], 0u);
     const float ma = sa.dmin * 64.0f, mb = sbk.dmin * 64.0f;
-    tot[0] = fmaf(sa.d, acc[0], fmaf(-ma, accm[0], tot[0]));
-    tot[1] = fmaf(sa.d, acc[1], fmaf(-ma, accm[1], tot[1]));
-    tot[2] = fmaf(sbk.d, acc[2], fmaf(-mb, accm[2], tot[2]));
-    tot[3] = fmaf(sbk.d, acc[3], fmaf(-mb, accm[3], tot[3]));
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nt][i] += acc2[nt][i];
+        float accm[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_f16(accm, sa.mins, sbk.mins, 0u, 0u, xsfrag[nt * xtile + (sb * 2 + 0) * 32 + lane], 0u);
+        mma_f16(accm, sa.mins, sbk.mins, 0u, 0u, xsfrag[nt * xtile + (sb * 2 + 1) * 32 + lane], 0u);
+        tot[nt][0] = fmaf(sa.d, acc[nt][0], fmaf(-ma, accm[0], tot[nt][0]));
+        tot[nt][1] = fmaf(sa.d, acc[nt][1], fmaf(-ma, accm[1], tot[nt][1]));
+        tot[nt][2] = fmaf(sbk.d, acc[nt][2], fmaf(-mb, accm[2], tot[nt][2]));
+        tot[nt][3] = fmaf(sbk.d, acc[nt][3], fmaf(-mb, accm[3], tot[nt][3]));
+    }
 }
 
 
@@ -359,11 +373,16 @@ __device__ __forceinline__ void superblock_mma(const SuperBlockRegs<Q5> &ra, con
 // Work item of a warp = (row block, super-block of its K part, stream); the packed bytes of the
 // next item are requested before the current one is computed.
 // ---------------------------------------------------------------------------------------------
-template <bool Q5, int MODE, int NTERMS>
+// NT (modes 0 and 1 only) is the number of 8-token tiles served by one pass over the weights: tile
+// nt holds tokens 8nt..8nt+7 with its own scales (MD_TOK_STRIDE floats further on), fragments and
+// activation sums.
+constexpr int MD_TOK_STRIDE = 128;     // floats between the token tiles' scale blocks (inside the control bytes)
+template <bool Q5, int MODE, int NTERMS, int NT = 1>
 __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectArgs a) {
     constexpr bool DUAL = (MODE == 1 || MODE == 2);
     constexpr bool GROUPED = (MODE >= 2);
     constexpr int QB = Q5 ? 176 : 144;
+    static_assert(NT == 1 || !GROUPED, "several token tiles only in the dense modes");
 
     extern __shared__ __align__(128) uint8_t smem[];
     float *tok_scale = reinterpret_cast<float *>(smem);           // [8] scale, [8] inverse
@@ -379,6 +398,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
     const int rgi = warp / a.kp, kpi = warp - rgi * a.kp;
     const int nsb = a.k >> 8;
     const int nfrag = nsb * 16;
+    const int btile = NTERMS * nfrag * 32, xtile = nsb * 64;     // fragment / sum entries of one token tile
 
     const int rows_per_block = 16 * a.rg;
     const int blocks_per_unit = (a.n + rows_per_block - 1) / rows_per_block;
@@ -448,8 +468,13 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
 
     int m_tokens = a.m;
     int seg_begin = 0, cur_unit = -1, last_single = -1;
-    if (!GROUPED)
-        prepare_direct<NTERMS, 4>([](int t) { return t; }, a.m, a.k, a.x, a.x_dtype, bfrag, xsfrag, tok_scale, tid);
+    if (!GROUPED) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+            prepare_direct<NTERMS, (NT == 1 ? 4 : 2)>([nt](int t) { return 8 * nt + t; }, max(min(a.m - 8 * nt, 8), 0),
+                                                      a.k, a.x, a.x_dtype, bfrag + nt * btile, xsfrag + nt * xtile,
+                                                      tok_scale + nt * MD_TOK_STRIDE, tid);
+    }
 
     int pbuf = 0;
     for (long long blk = blk_begin; blk < blk_end; ++blk) {
@@ -483,7 +508,11 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
             }
         }
 
-        float tot_a[4] = {0.f, 0.f, 0.f, 0.f}, tot_b[4] = {0.f, 0.f, 0.f, 0.f};
+        float tot_a[NT][4], tot_b[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tot_a[nt][i] = tot_b[nt][i] = 0.f;
         for (int item = 0; item < items_per_block; ++item) {
             // (copying the prefetched registers measured faster than alternating two register sets)
             cur_a = nxt_a;
@@ -493,36 +522,43 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
             else if (has_next) issue_item(nxt_p, 0, nxt_a, nxt_b);
             const int stream = DUAL ? (item & 1) : 0;
             const int sb = kpi + (DUAL ? (item >> 1) : item) * a.kp;
-            if (stream == 0) superblock_mma<Q5, NTERMS>(cur_a, cur_b, bfrag, nfrag, xsfrag, sb, lane, tot_a);
-            else superblock_mma<Q5, NTERMS>(cur_a, cur_b, bfrag, nfrag, xsfrag, sb, lane, tot_b);
+            if (stream == 0)
+                superblock_mma<Q5, NTERMS, NT>(cur_a, cur_b, bfrag, btile, nfrag, xsfrag, xtile, sb, lane, tot_a);
+            else
+                superblock_mma<Q5, NTERMS, NT>(cur_a, cur_b, bfrag, btile, nfrag, xsfrag, xtile, sb, lane, tot_b);
         }
 
-        // combine the kp partial sums of each row group in fixed order
-        float *pb = partial + pbuf * MD_PART_FLOATS + warp * 256;
-        pb[(g * 8 + 2 * tig) * 2 + 0] = tot_a[0];
-        pb[(g * 8 + 2 * tig + 1) * 2 + 0] = tot_a[1];
-        pb[((g + 8) * 8 + 2 * tig) * 2 + 0] = tot_a[2];
-        pb[((g + 8) * 8 + 2 * tig + 1) * 2 + 0] = tot_a[3];
-        if (DUAL) {
-            pb[(g * 8 + 2 * tig) * 2 + 1] = tot_b[0];
-            pb[(g * 8 + 2 * tig + 1) * 2 + 1] = tot_b[1];
-            pb[((g + 8) * 8 + 2 * tig) * 2 + 1] = tot_b[2];
-            pb[((g + 8) * 8 + 2 * tig + 1) * 2 + 1] = tot_b[3];
+        // combine the kp partial sums of each row group in fixed order:
+        // partial[warp][token tile][16 rows][8 tokens][2 streams]
+        float *pb = partial + pbuf * (NT * MD_PART_FLOATS) + warp * (NT * 256);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            float *pt = pb + nt * 256;
+            pt[(g * 8 + 2 * tig) * 2 + 0] = tot_a[nt][0];
+            pt[(g * 8 + 2 * tig + 1) * 2 + 0] = tot_a[nt][1];
+            pt[((g + 8) * 8 + 2 * tig) * 2 + 0] = tot_a[nt][2];
+            pt[((g + 8) * 8 + 2 * tig + 1) * 2 + 0] = tot_a[nt][3];
+            if (DUAL) {
+                pt[(g * 8 + 2 * tig) * 2 + 1] = tot_b[nt][0];
+                pt[(g * 8 + 2 * tig + 1) * 2 + 1] = tot_b[nt][1];
+                pt[((g + 8) * 8 + 2 * tig) * 2 + 1] = tot_b[nt][2];
+                pt[((g + 8) * 8 + 2 * tig + 1) * 2 + 1] = tot_b[nt][3];
+            }
         }
         const int group_threads = a.kp * 32;
         if (a.kp == 1) __syncwarp();
         else named_barrier_sync(2 + rgi, group_threads);   // rg <= 8 here: barrier ids 2..9
-        for (int o = kpi * 32 + lane; o < 128; o += group_threads) {
-            const int r = o >> 3, t = o & 7;
+        for (int o = kpi * 32 + lane; o < NT * 128; o += group_threads) {
+            const int nt = o >> 7, r = (o >> 3) & 15, tl = o & 7, t = 8 * nt + tl;
             const int orow = row0 + 16 * rgi + r;
             if (orow >= a.n || t >= m_tokens) continue;
-            const float *src = partial + pbuf * MD_PART_FLOATS + (rgi * a.kp) * 256 + (r * 8 + t) * 2;
+            const float *src = partial + pbuf * (NT * MD_PART_FLOATS) + (rgi * a.kp) * (NT * 256) + o * 2;
             float pa = 0.f, pbv = 0.f;
             for (int kq = 0; kq < a.kp; ++kq) {
-                pa += src[kq * 256];
-                if (DUAL) pbv += src[kq * 256 + 1];
+                pa += src[kq * (NT * 256)];
+                if (DUAL) pbv += src[kq * (NT * 256) + 1];
             }
-            const float inv = tok_scale[8 + t];
+            const float inv = tok_scale[nt * MD_TOK_STRIDE + 8 + tl];
             pa *= inv;
             pbv *= inv;
             if (MODE == 0) store_from_float(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, pa);

@@ -77,6 +77,10 @@ static bool direct_allowed() {
     return !(v && std::strcmp(v, "staged") == 0);
 }
 
+int mma_tokens_per_pass(int fmt, int mode, int k, int x_dtype, bool tiled) {
+    return (direct_allowed() || tiled) ? direct_tokens_per_pass(fmt, mode, k, x_dtype) : 8;
+}
+
 int mma_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) {
     *launched = false;
     if (direct_allowed() || q.tiled) {

@@ -36,12 +36,20 @@ struct MmaRequest {
 // Launches the tensor-core kernel when the request fits it (alignment, K multiple of 256, shared
 // memory); otherwise leaves *launched false and the caller runs the FP32-lane kernel.
 int mma_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched);
+// Tokens per mma_try_launch() request for this format / mode / K: 8, or 16 where the direct kernel
+// is in use and serves two token tiles per pass.
+int mma_tokens_per_pass(int fmt, int mode, int k, int x_dtype, bool tiled);
 
 // Same contract for the direct-load kernel (Q4_K / Q5_K only); tried first.
 int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched);
+// Tokens per launch the direct kernel takes for this format / mode / K (8, or 16 in the dense modes
+// when two token tiles fit in shared memory).
+int direct_tokens_per_pass(int fmt, int mode, int k, int x_dtype);
 
-// Weights in the Q6_K tile layout (mode 0 or 3, at most 8 tokens): there is no other kernel for
-// this layout, so a request that does not fit returns an error instead of declining.
+// Weights in the Q6_K / Q8_0 tile layouts (mode 0 or 3, at most tiled_tokens_per_pass() tokens):
+// there is no other kernel for these layouts, so a request that does not fit returns an error
+// instead of declining.
 int q6k_tiled_launch(const MmaRequest &q, cudaStream_t stream);
+int tiled_tokens_per_pass(int mode, int k, int x_dtype);
 
 }  // namespace b200q

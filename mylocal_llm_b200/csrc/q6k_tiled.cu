@@ -134,13 +134,24 @@ __global__ void __launch_bounds__(256) q8_retile_kernel(const uint8_t *src, uint
     }
 }
 
+// Tokens one launch of the tiled kernel can take: 16 (two 8-token tiles share one pass over the
+// weights) when both tiles' activation fragments fit in shared memory, else 8.
+int tiled_tokens_per_pass(int mode, int k, int x_dtype) {
+    if (mode != 0) return 8;
+    const long long nterms = (x_dtype == B200Q_F32) ? 2 : 1;
+    const long long smem2 = Q6T_CTRL_BYTES + 2LL * Q6T_PART_BYTES + 2LL * nterms * (k / 16) * 256;
+    return smem2 <= MM_SMEM_LIMIT ? 16 : 8;
+}
+
 // Runs the tiled kernel for a mode 0 or mode 3 request whose weights are in a tile layout
 // (q.fmt_a: B200Q_Q6_K_TILED or B200Q_Q8_0_TILED).
 int q6k_tiled_launch(const MmaRequest &q, cudaStream_t stream) {
     const bool grouped = q.mode == 3;
     if (q.mode != 0 && q.mode != 3) return fail(B200Q_EUNSUPPORTED, "tiled Q6_K: only linear and grouped down");
-    if (q.k % 256 != 0 || q.n % 16 != 0 || q.m < 1 || q.m > 8)
-        return fail(B200Q_EUNSUPPORTED, "tiled Q6_K: needs K %% 256 == 0, N %% 16 == 0, 1..8 tokens per pass");
+    const int nt = q.m > 8 ? 2 : 1;                    // 8-token tiles served by one pass over the weights
+    if (q.k % 256 != 0 || q.n % 16 != 0 || q.m < 1 || q.m > tiled_tokens_per_pass(q.mode, q.k, q.x_dtype))
+        return fail(B200Q_EUNSUPPORTED, "tiled Q6_K: needs K %% 256 == 0, N %% 16 == 0, 1..%d tokens per pass",
+                    tiled_tokens_per_pass(q.mode, q.k, q.x_dtype));
     if ((reinterpret_cast<uintptr_t>(q.wa) & 15) || (grouped && !q.table_a && (q.stride_a & 15)) ||
         (grouped && q.table_a && !q.tables_aligned16))
         return fail(B200Q_EINVAL, "tiled Q6_K: weights must be 16-byte aligned");
@@ -162,20 +173,23 @@ int q6k_tiled_launch(const MmaRequest &q, cudaStream_t stream) {
     while (kp * 2 <= Q6T_WARPS && kp * 2 <= nsb && blocks_for(kp) < 6LL * sm_count()) kp *= 2;
     a.kp = kp;
     a.rg = Q6T_WARPS / kp;
-    a.off_bfrag = Q6T_CTRL_BYTES + Q6T_PART_BYTES;
-    const long long smem = a.off_bfrag + static_cast<long long>(a.nterms) * (q.k / 16) * 256;
+    a.off_bfrag = Q6T_CTRL_BYTES + nt * Q6T_PART_BYTES;
+    const long long smem = a.off_bfrag + static_cast<long long>(nt) * a.nterms * (q.k / 16) * 256;
     if (smem > MM_SMEM_LIMIT) return fail(B200Q_EUNSUPPORTED, "tiled Q6_K: K=%d too large", q.k);
     a.x = q.x; a.x_dtype = q.x_dtype; a.y = q.y; a.y_dtype = q.y_dtype;
     a.order = q.order; a.seg_expert = q.seg_expert; a.seg_begin = q.seg_begin; a.seg_count = q.seg_count;
     a.num_segments = q.num_segments; a.max_segments = q.max_segments; a.route = q.route;
     a.flat_rows = q.flat_rows; a.y_table = q.y_table; a.rows_per_rank = q.rows_per_rank;
     Q6Fn fn;
-    if (q.fmt_a == B200Q_Q8_0_TILED)
-        fn = grouped ? (a.nterms == 2 ? tiled_kernel<Q8Tile, 3, 2> : tiled_kernel<Q8Tile, 3, 1>)
-                     : (a.nterms == 2 ? tiled_kernel<Q8Tile, 0, 2> : tiled_kernel<Q8Tile, 0, 1>);
-    else
-        fn = grouped ? (a.nterms == 2 ? tiled_kernel<Q6Tile, 3, 2> : tiled_kernel<Q6Tile, 3, 1>)
-                     : (a.nterms == 2 ? tiled_kernel<Q6Tile, 0, 2> : tiled_kernel<Q6Tile, 0, 1>);
+    if (q.fmt_a == B200Q_Q8_0_TILED) {
+        if (grouped) fn = a.nterms == 2 ? tiled_kernel<Q8Tile, 3, 2, 1> : tiled_kernel<Q8Tile, 3, 1, 1>;
+        else if (nt == 2) fn = a.nterms == 2 ? tiled_kernel<Q8Tile, 0, 2, 2> : tiled_kernel<Q8Tile, 0, 1, 2>;
+        else fn = a.nterms == 2 ? tiled_kernel<Q8Tile, 0, 2, 1> : tiled_kernel<Q8Tile, 0, 1, 1>;
+    } else {
+        if (grouped) fn = a.nterms == 2 ? tiled_kernel<Q6Tile, 3, 2, 1> : tiled_kernel<Q6Tile, 3, 1, 1>;
+        else if (nt == 2) fn = a.nterms == 2 ? tiled_kernel<Q6Tile, 0, 2, 2> : tiled_kernel<Q6Tile, 0, 1, 2>;
+        else fn = a.nterms == 2 ? tiled_kernel<Q6Tile, 0, 2, 1> : tiled_kernel<Q6Tile, 0, 1, 1>;
+    }
     cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void *>(fn),
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM_LIMIT);
     if (err != cudaSuccess) {

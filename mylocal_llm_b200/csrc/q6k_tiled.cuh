@@ -131,17 +131,23 @@ __device__ __forceinline__ float biased_byte_to_float(uint32_t word, int b) {
     return __uint_as_float(bits) - 8388736.0f;
 }
 
-// One tile: 16 scale groups = 16 mma steps; tot += d * sum_s scale_s * (codes_s . x_s).
-template <int NTERMS>
-__device__ __forceinline__ void q6_tile_mma(const Q6TileRegs &r, const uint2 *bfrag, int nfrag, int sb, int lane,
-                                            float (&tot)[4]) {
+// One tile: 16 scale groups = 16 mma steps; tot += d * sum_s scale_s * (codes_s . x_s). With NT
+// token tiles (8 tokens each, their fragments `tile_stride` entries apart) every decoded A operand
+// is multiplied into each of them, so the decode cost is paid once per 8*NT tokens.
+template <int NTERMS, int NT>
+__device__ __forceinline__ void q6_tile_mma(const Q6TileRegs &r, const uint2 *bfrag, int tile_stride, int nfrag, int sb,
+                                            int lane, float (&tot)[NT][4]) {
     const uint32_t magic = 0x64006400u, neg = 0xe420e420u;       // 1024 | code ; -(1024 + 32)
     const uint32_t wa[12] = {r.c[0].x, r.c[0].y, r.c[0].z, r.c[0].w, r.c[1].x, r.c[1].y,
                              r.c[1].z, r.c[1].w, r.c[2].x, r.c[2].y, r.c[2].z, r.c[2].w};
     const uint32_t wb[12] = {r.c[3].x, r.c[3].y, r.c[3].z, r.c[3].w, r.c[4].x, r.c[4].y,
                              r.c[4].z, r.c[4].w, r.c[5].x, r.c[5].y, r.c[5].z, r.c[5].w};
     const uint32_t sa[4] = {r.sa.x, r.sa.y, r.sa.z, r.sa.w}, sb4[4] = {r.sb.x, r.sb.y, r.sb.z, r.sb.w};
-    float blk[4] = {0.f, 0.f, 0.f, 0.f};
+    float blk[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) blk[nt][i] = 0.f;
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
         const uint32_t a0w = wa[3 * c], a1w = wa[3 * c + 1], a2w = wa[3 * c + 2];
@@ -163,22 +169,29 @@ __device__ __forceinline__ void q6_tile_mma(const Q6TileRegs &r, const uint2 *bf
                 p1b = and_or(b2w >> 10, 0x00300030u, and_or(b1w >> 12, 0x000f000fu, magic));
             }
             const int s = 8 * (c >> 1) + 2 * j + (c & 1);
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            const BFrag b = load_bfrag<NTERMS>(bfrag, nfrag, sb * 16 + s, lane);
-            mma_terms<NTERMS>(acc, hadd2_u32(p0a, neg), hadd2_u32(p0b, neg), hadd2_u32(p1a, neg), hadd2_u32(p1b, neg),
-                              b);
+            const uint32_t a0 = hadd2_u32(p0a, neg), a1 = hadd2_u32(p0b, neg), a2 = hadd2_u32(p1a, neg),
+                           a3 = hadd2_u32(p1b, neg);
             const float fa = biased_byte_to_float(sa[s >> 2], s & 3), fb = biased_byte_to_float(sb4[s >> 2], s & 3);
-            blk[0] = fmaf(fa, acc[0], blk[0]);
-            blk[1] = fmaf(fa, acc[1], blk[1]);
-            blk[2] = fmaf(fb, acc[2], blk[2]);
-            blk[3] = fmaf(fb, acc[3], blk[3]);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                const BFrag b = load_bfrag<NTERMS>(bfrag + nt * tile_stride, nfrag, sb * 16 + s, lane);
+                mma_terms<NTERMS>(acc, a0, a1, a2, a3, b);
+                blk[nt][0] = fmaf(fa, acc[0], blk[nt][0]);
+                blk[nt][1] = fmaf(fa, acc[1], blk[nt][1]);
+                blk[nt][2] = fmaf(fb, acc[2], blk[nt][2]);
+                blk[nt][3] = fmaf(fb, acc[3], blk[nt][3]);
+            }
         }
     }
     const float da = half_bits_to_float(r.dd & 0xffffu), db = half_bits_to_float(r.dd >> 16);
-    tot[0] = fmaf(da, blk[0], tot[0]);
-    tot[1] = fmaf(da, blk[1], tot[1]);
-    tot[2] = fmaf(db, blk[2], tot[2]);
-    tot[3] = fmaf(db, blk[3], tot[3]);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        tot[nt][0] = fmaf(da, blk[nt][0], tot[nt][0]);
+        tot[nt][1] = fmaf(da, blk[nt][1], tot[nt][1]);
+        tot[nt][2] = fmaf(db, blk[nt][2], tot[nt][2]);
+        tot[nt][3] = fmaf(db, blk[nt][3], tot[nt][3]);
+    }
 }
 
 // Tile policies of the kernel below: bytes per 16-row x 256-value tile, the registers of one tile,
@@ -187,10 +200,10 @@ struct Q6Tile {
     static constexpr int BYTES = Q6T_TILE_BYTES;
     using Regs = Q6TileRegs;
     static __device__ __forceinline__ void load(Regs &r, const uint8_t *tile, int lane) { load_q6_tile(r, tile, lane); }
-    template <int NTERMS>
-    static __device__ __forceinline__ void mma(const Regs &r, const uint2 *bfrag, int nfrag, int sb, int lane,
-                                               float (&tot)[4]) {
-        q6_tile_mma<NTERMS>(r, bfrag, nfrag, sb, lane, tot);
+    template <int NTERMS, int NT>
+    static __device__ __forceinline__ void mma(const Regs &r, const uint2 *bfrag, int tile_stride, int nfrag, int sb,
+                                               int lane, float (&tot)[NT][4]) {
+        q6_tile_mma<NTERMS, NT>(r, bfrag, tile_stride, nfrag, sb, lane, tot);
     }
 };
 
@@ -215,9 +228,9 @@ struct Q8Tile {
         r.da = ldg128(tile + Q8T_SCALES_OFF + 16 * g);
         r.db = ldg128(tile + Q8T_SCALES_OFF + 16 * (g + 8));
     }
-    template <int NTERMS>
-    static __device__ __forceinline__ void mma(const Regs &r, const uint2 *bfrag, int nfrag, int sb, int lane,
-                                               float (&tot)[4]) {
+    template <int NTERMS, int NT>
+    static __device__ __forceinline__ void mma(const Regs &r, const uint2 *bfrag, int tile_stride, int nfrag, int sb,
+                                               int lane, float (&tot)[NT][4]) {
         const uint32_t neg = 0xe480e480u;                       // -(1024 + 128)
         const uint32_t wa[16] = {r.c[0].x, r.c[0].y, r.c[0].z, r.c[0].w, r.c[1].x, r.c[1].y, r.c[1].z, r.c[1].w,
                                  r.c[2].x, r.c[2].y, r.c[2].z, r.c[2].w, r.c[3].x, r.c[3].y, r.c[3].z, r.c[3].w};
@@ -226,23 +239,34 @@ struct Q8Tile {
         const uint32_t da[4] = {r.da.x, r.da.y, r.da.z, r.da.w}, db[4] = {r.db.x, r.db.y, r.db.z, r.db.w};
 #pragma unroll
         for (int blk = 0; blk < 8; ++blk) {
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            float acc[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int s = 2 * blk + h;
                 const uint32_t va = wa[s], vb = wb[s];
-                const BFrag b = load_bfrag<NTERMS>(bfrag, nfrag, sb * 16 + s, lane);
-                mma_terms<NTERMS>(acc, hadd2_u32(__byte_perm(va, 0x64646464u, 0x4240), neg),
-                                  hadd2_u32(__byte_perm(vb, 0x64646464u, 0x4240), neg),
-                                  hadd2_u32(__byte_perm(va, 0x64646464u, 0x4341), neg),
-                                  hadd2_u32(__byte_perm(vb, 0x64646464u, 0x4341), neg), b);
+                const uint32_t a0 = hadd2_u32(__byte_perm(va, 0x64646464u, 0x4240), neg),
+                               a1 = hadd2_u32(__byte_perm(vb, 0x64646464u, 0x4240), neg),
+                               a2 = hadd2_u32(__byte_perm(va, 0x64646464u, 0x4341), neg),
+                               a3 = hadd2_u32(__byte_perm(vb, 0x64646464u, 0x4341), neg);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const BFrag b = load_bfrag<NTERMS>(bfrag + nt * tile_stride, nfrag, sb * 16 + s, lane);
+                    mma_terms<NTERMS>(acc[nt], a0, a1, a2, a3, b);
+                }
             }
             const float fa = half_bits_to_float((da[blk >> 1] >> (16 * (blk & 1))) & 0xffffu);
             const float fb = half_bits_to_float((db[blk >> 1] >> (16 * (blk & 1))) & 0xffffu);
-            tot[0] = fmaf(fa, acc[0], tot[0]);
-            tot[1] = fmaf(fa, acc[1], tot[1]);
-            tot[2] = fmaf(fb, acc[2], tot[2]);
-            tot[3] = fmaf(fb, acc[3], tot[3]);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                tot[nt][0] = fmaf(fa, acc[nt][0], tot[nt][0]);
+                tot[nt][1] = fmaf(fa, acc[nt][1], tot[nt][1]);
+                tot[nt][2] = fmaf(fb, acc[nt][2], tot[nt][2]);
+                tot[nt][3] = fmaf(fb, acc[nt][3], tot[nt][3]);
+            }
         }
     }
 };
@@ -332,11 +356,15 @@ __device__ __forceinline__ void prepare_fragments(RowFn row_of, int m_tokens, in
 // MODE 0: y[m, n] = x W^T.  MODE 3: grouped down projection over the plan's segments, rows scaled
 // by the route weight. Warp (rgi, kpi) owns row group rgi of the CTA's row block and the
 // super-blocks kpi, kpi+kp, ...; the next tile is requested before the current one is computed.
-template <typename TILE, int MODE, int NTERMS>
+// NT (mode 0 only) is the number of 8-token tiles served by one pass over the weights: tile nt
+// holds tokens 8nt..8nt+7, with its own scales (Q6T_TOK_STRIDE floats further on) and fragments.
+constexpr int Q6T_TOK_STRIDE = 128;     // floats between the token tiles' scale blocks (inside the control bytes)
+template <typename TILE, int MODE, int NTERMS, int NT>
 __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs a) {
     constexpr bool GROUPED = (MODE == 3);
+    static_assert(NT == 1 || MODE == 0, "several token tiles only in the linear mode");
     extern __shared__ __align__(128) uint8_t smem[];
-    float *tok_scale = reinterpret_cast<float *>(smem);           // [8] scale, [8] inverse, [8] amax bits
+    float *tok_scale = reinterpret_cast<float *>(smem);           // per token tile: [8] scale, [8] inverse, [8] amax bits
     float *route_w = reinterpret_cast<float *>(smem + 128);       // [8]
     int *seg_tokens = reinterpret_cast<int *>(smem + 192);        // [8]
     float **out_ptr = reinterpret_cast<float **>(smem + 256);     // [8]
@@ -348,6 +376,7 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs
     const int rgi = warp / a.kp, kpi = warp - rgi * a.kp;
     const int nsb = a.k >> 8;
     const int nfrag = a.k >> 4;
+    const int tile_stride = NTERMS * nfrag * 32;           // fragment entries of one token tile
     const int groups_total = a.n >> 4;                     // n is a multiple of 16
 
     const int blocks_per_unit = (groups_total + a.rg - 1) / a.rg;
@@ -379,7 +408,13 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs
 
     int m_tokens = a.m;
     int seg_begin = 0, cur_unit = -1;
-    if (!GROUPED) prepare_fragments<NTERMS, 4>([](int t) { return t; }, a.m, a.k, a.x, a.x_dtype, bfrag, tok_scale, tid);
+    if (!GROUPED) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+            prepare_fragments<NTERMS, (NT == 1 ? 4 : 2)>([nt](int t) { return 8 * nt + t; }, max(min(a.m - 8 * nt, 8), 0),
+                                                         a.k, a.x, a.x_dtype, bfrag + nt * tile_stride,
+                                                         tok_scale + nt * Q6T_TOK_STRIDE, tid);
+    }
 
     int pbuf = 0;
     for (long long blk = blk_begin; blk < blk_end; ++blk) {
@@ -405,12 +440,16 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs
                                       tok_scale, tid);
         }
 
-        float tot[4] = {0.f, 0.f, 0.f, 0.f};
+        float tot[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tot[nt][i] = 0.f;
         for (int item = 0; item < items_per_block; ++item) {
             cur = nxt;
             if (item + 1 < items_per_block) TILE::load(nxt, cur_p + (item + 1) * item_step, lane);
             else if (has_next) TILE::load(nxt, nxt_p, lane);
-            TILE::template mma<NTERMS>(cur, bfrag, nfrag, kpi + item * a.kp, lane, tot);
+            TILE::template mma<NTERMS, NT>(cur, bfrag, tile_stride, nfrag, kpi + item * a.kp, lane, tot);
         }
 
         const int group = group0 + rgi;
@@ -418,30 +457,36 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs
             // the warp owns its rows' whole K range: store straight from the accumulators
             if (group < groups_total) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int orow = group * 16 + g + 8 * (i >> 1), t = 2 * tig + (i & 1);
-                    if (t < m_tokens) {
-                        const float v = tot[i] * tok_scale[8 + t];
-                        if (MODE == 0) store_from_float(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, v);
-                        else out_ptr[t][orow] = v * route_w[t];
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int orow = group * 16 + g + 8 * (i >> 1), tl = 2 * tig + (i & 1), t = 8 * nt + tl;
+                        if (t < m_tokens) {
+                            const float v = tot[nt][i] * tok_scale[nt * Q6T_TOK_STRIDE + 8 + tl];
+                            if (MODE == 0) store_from_float(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, v);
+                            else out_ptr[t][orow] = v * route_w[t];
+                        }
                     }
-                }
             }
         } else {
-            float *pb = partial + pbuf * Q6T_PART_FLOATS + warp * 128;
-            pb[g * 8 + 2 * tig] = tot[0];
-            pb[g * 8 + 2 * tig + 1] = tot[1];
-            pb[(g + 8) * 8 + 2 * tig] = tot[2];
-            pb[(g + 8) * 8 + 2 * tig + 1] = tot[3];
+            // partial sums [warp][token tile][16 rows][8 tokens], combined over the kp warps in fixed order
+            float *pb = partial + pbuf * (NT * Q6T_PART_FLOATS) + warp * (NT * 128);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                pb[nt * 128 + g * 8 + 2 * tig] = tot[nt][0];
+                pb[nt * 128 + g * 8 + 2 * tig + 1] = tot[nt][1];
+                pb[nt * 128 + (g + 8) * 8 + 2 * tig] = tot[nt][2];
+                pb[nt * 128 + (g + 8) * 8 + 2 * tig + 1] = tot[nt][3];
+            }
             const int group_threads = a.kp * 32;
             named_barrier_sync(2 + rgi, group_threads);            // kp >= 2: at most 8 row groups, ids 2..9
-            for (int o = kpi * 32 + lane; o < 128; o += group_threads) {
-                const int r = o >> 3, t = o & 7;
+            for (int o = kpi * 32 + lane; o < NT * 128; o += group_threads) {
+                const int nt = o >> 7, r = (o >> 3) & 15, tl = o & 7, t = 8 * nt + tl;
                 if (group >= groups_total || t >= m_tokens) continue;
-                const float *src = partial + pbuf * Q6T_PART_FLOATS + (rgi * a.kp) * 128 + r * 8 + t;
+                const float *src = partial + pbuf * (NT * Q6T_PART_FLOATS) + (rgi * a.kp) * (NT * 128) + o;
                 float v = 0.f;
-                for (int kq = 0; kq < a.kp; ++kq) v += src[kq * 128];
-                v *= tok_scale[8 + t];
+                for (int kq = 0; kq < a.kp; ++kq) v += src[kq * (NT * 128)];
+                v *= tok_scale[nt * Q6T_TOK_STRIDE + 8 + tl];
                 const int orow = group * 16 + r;
                 if (MODE == 0) store_from_float(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, v);
                 else out_ptr[t][orow] = v * route_w[t];

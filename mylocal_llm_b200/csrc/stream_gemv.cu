@@ -113,10 +113,11 @@ int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype,
     if (fmt == B200Q_Q6_K_TILED || fmt == B200Q_Q8_0_TILED) {
         if (!dtype_valid(x_dtype) || !dtype_valid(y_dtype)) return fail(B200Q_EINVAL, "gemv: bad dtype");
         if (n <= 0 || m <= 0 || k <= 0) return fail(B200Q_EINVAL, "gemv: bad shape n=%d k=%d m=%d", n, k, m);
-        for (int t0 = 0; t0 < m; t0 += 8) {
+        const int per_pass = tiled_tokens_per_pass(0, k, x_dtype);
+        for (int t0 = 0; t0 < m; t0 += per_pass) {
             MmaRequest q{};
             q.mode = 0; q.wa = static_cast<const uint8_t *>(w); q.fmt_a = q.fmt_b = fmt; q.n = n; q.k = k;
-            q.m = (m - t0 < 8) ? m - t0 : 8;
+            q.m = (m - t0 < per_pass) ? m - t0 : per_pass;
             q.x = static_cast<const uint8_t *>(x) + static_cast<size_t>(t0) * k * dtype_size(x_dtype);
             q.x_dtype = x_dtype;
             q.y = static_cast<uint8_t *>(y) + static_cast<size_t>(t0) * n * dtype_size(y_dtype);
@@ -143,11 +144,13 @@ int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype,
     a.y_dtype = y_dtype;
     a.status = status;
     if (mma_allowed() || tiled) {
-        // up to 8 tokens per pass on the tensor cores
+        // 8 (or, for the direct kernel with two token tiles, 16) tokens per pass on the tensor cores
+        const int per_pass = mma_tokens_per_pass(fmt, 0, k, x_dtype, tiled);
         bool all = true;
-        for (int t0 = 0; t0 < m && all; t0 += 8) {
+        for (int t0 = 0; t0 < m && all; t0 += per_pass) {
             MmaRequest q{};
-            q.mode = 0; q.wa = a.wa; q.fmt_a = q.fmt_b = fmt; q.n = n; q.k = k; q.m = (m - t0 < 8) ? m - t0 : 8;
+            q.mode = 0; q.wa = a.wa; q.fmt_a = q.fmt_b = fmt; q.n = n; q.k = k;
+            q.m = (m - t0 < per_pass) ? m - t0 : per_pass;
             q.x = static_cast<const uint8_t *>(x) + static_cast<size_t>(t0) * k * dtype_size(x_dtype);
             q.x_dtype = x_dtype;
             q.y = static_cast<uint8_t *>(y) + static_cast<size_t>(t0) * n * dtype_size(y_dtype);
@@ -204,12 +207,13 @@ int b200q_swiglu(const void *gate, int gate_fmt, const void *up, int up_fmt, int
     a.y_dtype = h_dtype;
     a.status = status;
     if (mma_allowed() || tiled) {
+        const int per_pass = gate_fmt == up_fmt ? mma_tokens_per_pass(gate_fmt, 1, k, x_dtype, tiled) : 8;
         bool all = true;
-        for (int t0 = 0; t0 < m && all; t0 += 8) {
+        for (int t0 = 0; t0 < m && all; t0 += per_pass) {
             MmaRequest q{};
             q.tiled = tiled;
             q.mode = 1; q.wa = a.wa; q.wb = a.wb; q.fmt_a = gate_fmt; q.fmt_b = up_fmt; q.n = f; q.k = k;
-            q.m = (m - t0 < 8) ? m - t0 : 8;
+            q.m = (m - t0 < per_pass) ? m - t0 : per_pass;
             q.x = static_cast<const uint8_t *>(x) + static_cast<size_t>(t0) * k * dtype_size(x_dtype);
             q.x_dtype = x_dtype;
             q.y = static_cast<uint8_t *>(h) + static_cast<size_t>(t0) * f * dtype_size(h_dtype);

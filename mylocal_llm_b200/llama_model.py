@@ -10,10 +10,12 @@ adapter; here they stay packed and resident in HBM, which is the point of the ex
   ``quantized_swiglu`` on ``DevicePackedGGUFWeight`` (tile layouts where they exist);
 * RMSNorm is ``b200q_rmsnorm`` / the fused residual-add variant; the residual stream is FP32;
 * embedding rows are gathered as packed bytes and decoded by ``b200q_dequantize``;
-* rotate-half RoPE, the KV cache and softmax attention are plain torch ops (bookkeeping around the
-  packed kernels, not part of the packed path). The decode step has static shapes - the cache is
-  written at a device-side position and attention runs over the whole horizon under a mask - so
-  ``decode_one`` can be captured in a CUDA graph.
+* the one-token step runs rotate-half RoPE fused with the KV-cache store (``b200q_rope_kv_store``),
+  single-query attention over the cache (``b200q_decode_attention``), and ``b200q_silu_mul`` on
+  the output of the stacked gate|up projection; prefill (and ``fused_decode = False``) does the
+  RoPE / cache / attention bookkeeping with plain torch ops. The decode step has static shapes - the cache is written at a
+  device-side position and attention stops at that position - so ``decode_one`` can be captured in
+  a CUDA graph.
 """
 
 import ctypes
