@@ -107,11 +107,35 @@ class ClockSampler:
         self.lines = []
         self.thread = None
         self.first_timed = 0
+        self.t_mark = None
+        self.held = False
 
     def mark_timed_region(self):
         """Samples taken from now on belong to the timed region (the sampler is started before the warm-up
         so that nvidia-smi is already running when a short timed region begins)."""
         self.first_timed = len(self.lines)
+        self.t_mark = time.perf_counter()
+
+    def hold_load(self, step, step_ms, seconds=0.25, max_steps=100000):
+        """A timed region of a few milliseconds ends before nvidia-smi's next sample. Called right after it,
+        this keeps the same step running, untimed, until about `seconds` have passed since the region began,
+        so that the samples describe the clocks the timed steps ran at. Every rank calls it with the step
+        count agreed between the ranks (the step may hold an exchange between them); it does nothing when
+        the region was long enough by itself."""
+        import torch
+        import torch.distributed as dist
+        if self.t_mark is None:
+            return
+        remaining = seconds - (time.perf_counter() - self.t_mark)
+        count = min(max_steps, max(0, int(remaining / max(step_ms * 1e-3, 1e-6)) + 1)) if remaining > 0 else 0
+        if dist.is_available() and dist.is_initialized():
+            agreed = torch.tensor([count], dtype=torch.int64, device="cuda")
+            dist.all_reduce(agreed, op=dist.ReduceOp.MAX)
+            count = int(agreed.item())
+        for _ in range(count):
+            step()
+        torch.cuda.synchronize()
+        self.held = count > 0
 
     def start(self):
         try:
@@ -123,6 +147,9 @@ class ClockSampler:
             return
         self.thread = threading.Thread(target=self._pump, daemon=True)
         self.thread.start()
+        deadline = time.perf_counter() + 3.0          # nvidia-smi takes a moment to print its first line
+        while not self.lines and time.perf_counter() < deadline and self.proc.poll() is None:
+            time.sleep(0.01)
 
     def _pump(self):
         for line in self.proc.stdout:
@@ -140,7 +167,7 @@ class ClockSampler:
             self.thread.join(timeout=2)
         clocks, max_clock, reasons = [], None, set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        window = "timed region"
+        window = "timed region + the same step kept running until 250 ms had passed" if self.held else "timed region"
         lines = self.lines[self.first_timed:]
         if not lines:                       # region shorter than one sampling period: use the warm-up under the same load
             lines, window = self.lines, "warm-up + timed region"
@@ -293,6 +320,7 @@ def run_gpu_arm(args, name):
         stop.record(stream)
         barrier()
         dev_ms = start.elapsed_time(stop)
+        sampler.hold_load(graph.replay, dev_ms / args.steps)
 
         # ---- end to end: pinned host activations in, outputs back, every step
         def e2e_step():
@@ -564,6 +592,7 @@ def run_moe_gpu_arm(args, name):
         e1.record(stream)
         barrier()
         dev_ms = e0.elapsed_time(e1)
+        sampler.hold_load(graph.replay, dev_ms / max(1, args.steps))
 
         def e2e_step():
             dev_x.copy_(host_x, non_blocking=True)
@@ -675,6 +704,7 @@ LLAMA_SHAPE = dict(vocab_size=49152, hidden_size=2048, intermediate_size=8192, n
                    rope_theta=10000.0, rms_norm_eps=1e-5)
 LLAMA_WORKLOADS = {"llama_decode_b1": 1, "llama_decode_b16": 16}
 LLAMA_PROMPT, LLAMA_NEW = 512, 128
+LLAMA_HOLD = 160          # cache positions reserved for the untimed steps that keep the load up for the clock sampler
 
 
 def llama_bytes_per_step():
@@ -725,7 +755,7 @@ def run_llama_gpu_arm(args, name):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     model = ExternalLlamaModel.synthetic(ExternalLlamaConfig(**LLAMA_SHAPE), seed=rank)
-    state = model.create_generation_state(batch, LLAMA_PROMPT + LLAMA_NEW + 64)
+    state = model.create_generation_state(batch, LLAMA_PROMPT + LLAMA_NEW + 64 + LLAMA_HOLD)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(5 + rank)
     prompt = torch.randint(0, LLAMA_SHAPE["vocab_size"], (batch, LLAMA_PROMPT), device="cuda", generator=gen)
@@ -751,7 +781,7 @@ def run_llama_gpu_arm(args, name):
                 dist.barrier()
             torch.cuda.synchronize()
 
-        budget = state.horizon - LLAMA_PROMPT - 2
+        budget = state.horizon - LLAMA_HOLD - LLAMA_PROMPT - 2
         steps = min(args.steps, (budget - 2 * max(3, args.warmup)) // 2)
         sampler = ClockSampler(local_rank)
         if rank == 0:
@@ -767,6 +797,7 @@ def run_llama_gpu_arm(args, name):
         e1.record(stream)
         barrier()
         dev_ms = e0.elapsed_time(e1)
+        sampler.hold_load(graph.replay, dev_ms / max(1, steps), max_steps=LLAMA_HOLD)    # cache room is reserved for it
 
         def e2e_step():
             graph.replay()

@@ -17,6 +17,8 @@ __global__ void __launch_bounds__(256) rope_kv_store_kernel(float *q, const floa
                                                             const float *sin_t, int b, int t, int h, int hkv, int dh,
                                                             int horizon, void *k_cache, void *v_cache,
                                                             int cache_dtype) {
+    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
+    chain_wait();         // inputs come from preceding kernels
     const int half = dh >> 1;
     const long long total = static_cast<long long>(b) * t * (h + 2 * hkv) * half;
     for (long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; idx < total;
@@ -100,6 +102,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
                                                                           const long long *position, long long q_row,
                                                                           int h, int hkv, int horizon, float scale,
                                                                           void *out, int out_dtype) {
+    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
+    chain_wait();         // inputs come from preceding kernels
     constexpr int DH = EPL * 32;
     __shared__ float sm_m[ATT_WARPS], sm_l[ATT_WARPS], sm_acc[ATT_WARPS][DH];
     const int bh = blockIdx.x, bb = bh / h, head = bh - bb * h;
@@ -179,6 +183,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
 
 // act[m, f] = silu(gu[m, f]) * gu[m, F + f] for a stacked gate|up projection output gu [M, 2F] (FP32).
 __global__ void __launch_bounds__(256) silu_mul_kernel(const float *gu, int m, int f, void *out, int out_dtype) {
+    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
+    chain_wait();         // inputs come from preceding kernels
     const long long total = static_cast<long long>(m) * f;
     for (long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; idx < total;
          idx += static_cast<long long>(gridDim.x) * 256) {
@@ -207,10 +213,9 @@ int b200q_rope_kv_store(float *q, const float *k, const float *v, int64_t q_row_
         return fail(B200Q_EINVAL, "rope_kv_store: bad argument");
     const long long total = static_cast<long long>(batch) * t * (heads + 2 * kv_heads) * (head_dim / 2);
     const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 4096));
-    rope_kv_store_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        q, k, v, q_row_stride, k_row_stride, v_row_stride, reinterpret_cast<const long long *>(positions), cos_table,
-        sin_table, batch, t, heads, kv_heads,
-        head_dim, horizon, k_cache, v_cache, cache_dtype);
+    launch_chained(rope_kv_store_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), q, k, v,
+                   q_row_stride, k_row_stride, v_row_stride, reinterpret_cast<const long long *>(positions), cos_table,
+                   sin_table, batch, t, heads, kv_heads, head_dim, horizon, k_cache, v_cache, cache_dtype);
     return check_launch("rope_kv_store");
 }
 
@@ -219,7 +224,8 @@ int b200q_silu_mul(const float *gate_up, int m, int f, void *out, int out_dtype,
     if (m <= 0 || f <= 0 || !dtype_valid(out_dtype)) return fail(B200Q_EINVAL, "silu_mul: bad argument");
     const long long total = static_cast<long long>(m) * f;
     const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 4096));
-    silu_mul_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(gate_up, m, f, out, out_dtype);
+    launch_chained(silu_mul_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), gate_up, m, f, out,
+                   out_dtype);
     return check_launch("silu_mul");
 }
 
@@ -233,11 +239,11 @@ int b200q_decode_attention(const float *q, int64_t q_row_stride, const void *k_c
     const long long *pos = reinterpret_cast<const long long *>(position);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (head_dim == 64)
-        decode_attention_kernel<2><<<batch * heads, ATT_WARPS * 32, 0, s>>>(q, k_cache, v_cache, cache_dtype, pos, q_row_stride, heads,
-                                                                 kv_heads, horizon, scale, out, out_dtype);
+        launch_chained(decode_attention_kernel<2>, dim3(batch * heads), dim3(ATT_WARPS * 32), 0, s, q, k_cache, v_cache,
+                       cache_dtype, pos, q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
     else if (head_dim == 128)
-        decode_attention_kernel<4><<<batch * heads, ATT_WARPS * 32, 0, s>>>(q, k_cache, v_cache, cache_dtype, pos, q_row_stride, heads,
-                                                                 kv_heads, horizon, scale, out, out_dtype);
+        launch_chained(decode_attention_kernel<4>, dim3(batch * heads), dim3(ATT_WARPS * 32), 0, s, q, k_cache, v_cache,
+                       cache_dtype, pos, q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
     else
         return fail(B200Q_EUNSUPPORTED, "decode_attention: head_dim must be 64 or 128");
     return check_launch("decode_attention");

@@ -59,6 +59,8 @@ template <bool RESIDUAL>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const void *x, int x_dtype, const float *residual,
                                                       float alpha, const void *gamma, int gamma_dtype, int d,
                                                       float eps, float *res_out, void *y, int y_dtype) {
+    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
+    chain_wait();         // inputs come from preceding kernels
     __shared__ float warp_sums[8];
     __shared__ float inv_shared;
     const size_t base = static_cast<size_t>(blockIdx.x) * d;
@@ -289,6 +291,8 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const void *ids,
                                                                 int32_t *seg_expert, int32_t *seg_begin,
                                                                 int32_t *seg_count, int32_t *num_segments,
                                                                 int max_segments, int32_t *status) {
+    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
+    chain_wait();         // inputs come from preceding kernels
     extern __shared__ unsigned int bits[];    // [e][words]
     __shared__ int cnt[PLAN_MAX_EXPERTS];     // counts, then running cursor
     __shared__ int off[PLAN_MAX_EXPERTS + 1];
@@ -476,8 +480,8 @@ int b200q_rmsnorm(const void *x, int x_dtype, const void *gamma, int gamma_dtype
     if (!dtype_valid(x_dtype) || !dtype_valid(gamma_dtype) || !dtype_valid(y_dtype))
         return fail(B200Q_EINVAL, "rmsnorm: bad dtype");
     if (rows <= 0 || d <= 0) return fail(B200Q_EINVAL, "rmsnorm: bad shape");
-    rmsnorm_kernel<false><<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        x, x_dtype, nullptr, 0.f, gamma, gamma_dtype, d, eps, nullptr, y, y_dtype);
+    launch_chained(rmsnorm_kernel<false>, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), x, x_dtype,
+                   nullptr, 0.f, gamma, gamma_dtype, d, eps, nullptr, y, y_dtype);
     return check_launch("rmsnorm");
 }
 
@@ -488,8 +492,8 @@ int b200q_residual_rmsnorm(const float *residual, const void *branch, int branch
     if (!dtype_valid(branch_dtype) || !dtype_valid(gamma_dtype) || !dtype_valid(y_dtype))
         return fail(B200Q_EINVAL, "residual_rmsnorm: bad dtype");
     if (rows <= 0 || d <= 0) return fail(B200Q_EINVAL, "residual_rmsnorm: bad shape");
-    rmsnorm_kernel<true><<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        branch, branch_dtype, residual, alpha, gamma, gamma_dtype, d, eps, res_out, y, y_dtype);
+    launch_chained(rmsnorm_kernel<true>, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), branch,
+                   branch_dtype, residual, alpha, gamma, gamma_dtype, d, eps, res_out, y, y_dtype);
     return check_launch("residual_rmsnorm");
 }
 
@@ -557,9 +561,9 @@ static int launch_plan(const void *ids, int ids_is_i64, int rows, int k, int e, 
             return fail(B200Q_ECUDA, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(err));
         }
     }
-    moe_plan_kernel<<<1, PLAN_THREADS, bits_bytes, static_cast<cudaStream_t>(stream)>>>(
-        ids, ids_is_i64, rows * k, k, e, skip_expert, map, words, seg_cap, counts, offsets, order, inv, seg_expert,
-        seg_begin, seg_count, num_segments, max_segments, status);
+    launch_chained(moe_plan_kernel, dim3(1), dim3(PLAN_THREADS), bits_bytes, static_cast<cudaStream_t>(stream), ids,
+                   ids_is_i64, rows * k, k, e, skip_expert, map, words, seg_cap, counts, offsets, order, inv,
+                   seg_expert, seg_begin, seg_count, num_segments, max_segments, status);
     return check_launch(what);
 }
 

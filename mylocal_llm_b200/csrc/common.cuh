@@ -38,8 +38,53 @@ constexpr int NUM_SMS_FALLBACK = 148;
 int sm_count();
 
 // ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch. The decode step is a chain of short kernels on one stream; a
+// kernel launched through launch_chained() may become resident while its predecessor drains, and
+// blocks in chain_wait() until the predecessor grid has completed and its writes are visible.
+// Rules every such kernel follows:
+//   * chain_wait() is executed by every thread before the first access to memory that a preceding
+//     kernel writes (activations, plans, caches) and before its own first global write; only
+//     read-only weights may be requested earlier;
+//   * chain_trigger() lets the next kernel in the stream be scheduled; it carries no memory
+//     guarantee (the next kernel's own chain_wait() does).
+// Launched without the attribute (B200Q_CHAIN=0, or after a kernel that is launched normally)
+// both calls are no-ops and the stream order is the usual full serialisation.
+// ---------------------------------------------------------------------------------------------
+bool chain_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = chain_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Small device utilities
 // ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Asks L2 for the lines of [base, base + bytes) (at most `cap` bytes), all threads of the CTA
+// taking part. It returns nothing to the thread, so it may run before chain_wait(): a dense GEMV
+// that became resident early pulls its slice of the weights towards L2 while the preceding
+// kernel finishes.
+__device__ __forceinline__ void prefetch_l2_range(const uint8_t *base, size_t bytes, size_t cap, int tid, int threads) {
+    if (bytes > cap) bytes = cap;
+    for (size_t off = static_cast<size_t>(tid) * 128; off < bytes; off += static_cast<size_t>(threads) * 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
+}
+constexpr size_t CHAIN_PREFETCH_BYTES = 256 * 1024;     // per CTA
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

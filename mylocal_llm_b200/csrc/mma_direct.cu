@@ -94,7 +94,7 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) 
         const int blocks = (q.n + 16 * a.rg - 1) / (16 * a.rg);
         if (blocks < grid) grid = blocks;
     }
-    fn<<<grid, MD_THREADS, static_cast<size_t>(smem), stream>>>(a);
+    launch_chained(fn, dim3(grid), dim3(MD_THREADS), static_cast<size_t>(smem), stream, a);
     *launched = true;
     return check_launch("direct gemv");
 }

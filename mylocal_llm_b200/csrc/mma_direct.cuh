@@ -383,6 +383,8 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
     constexpr bool GROUPED = (MODE >= 2);
     constexpr int QB = Q5 ? 176 : 144;
     static_assert(NT == 1 || !GROUPED, "several token tiles only in the dense modes");
+    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
+    if (GROUPED) chain_wait();      // the segment list comes from the plan kernel
 
     extern __shared__ __align__(128) uint8_t smem[];
     float *tok_scale = reinterpret_cast<float *>(smem);           // [8] scale, [8] inverse
@@ -411,6 +413,23 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
     const long long total_blocks = units * blocks_per_unit;
     const long long blk_begin = total_blocks * blockIdx.x / gridDim.x;
     const long long blk_end = total_blocks * (blockIdx.x + 1) / gridDim.x;
+    if (!GROUPED) {
+        // the CTA's row blocks are one contiguous byte range of the matrix (rows, or 16-row tiles)
+        if (blk_begin < blk_end) {
+            size_t first, last;
+            if (!Q5 && a.tiled) {
+                first = static_cast<size_t>(blk_begin) * a.rg * nsb * Q4T_TILE_BYTES;
+                last = static_cast<size_t>(min(static_cast<long long>(a.n >> 4), blk_end * a.rg)) * nsb * Q4T_TILE_BYTES;
+            } else {
+                first = static_cast<size_t>(blk_begin) * rows_per_block * a.rb;
+                last = static_cast<size_t>(min(static_cast<long long>(a.n), blk_end * rows_per_block)) * a.rb;
+            }
+            const size_t cap = DUAL ? CHAIN_PREFETCH_BYTES / 2 : CHAIN_PREFETCH_BYTES;
+            prefetch_l2_range(a.wa + first, last - first, cap, tid, MD_THREADS);
+            if (DUAL) prefetch_l2_range(a.wb + first, last - first, cap, tid, MD_THREADS);
+        }
+        chain_wait();     // activations come from the preceding kernel
+    }
     if (blk_begin >= blk_end) return;
 
     // items of this warp inside one row block: its super-blocks x streams

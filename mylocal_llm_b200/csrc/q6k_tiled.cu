@@ -201,7 +201,7 @@ int q6k_tiled_launch(const MmaRequest &q, cudaStream_t stream) {
         const int blocks = (q.n / 16 + a.rg - 1) / a.rg;
         if (blocks < grid) grid = blocks;
     }
-    fn<<<grid, Q6T_THREADS, static_cast<size_t>(smem), stream>>>(a);
+    launch_chained(fn, dim3(grid), dim3(Q6T_THREADS), static_cast<size_t>(smem), stream, a);
     return check_launch("tiled Q6_K gemv");
 }
 

@@ -363,6 +363,8 @@ template <typename TILE, int MODE, int NTERMS, int NT>
 __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs a) {
     constexpr bool GROUPED = (MODE == 3);
     static_assert(NT == 1 || MODE == 0, "several token tiles only in the linear mode");
+    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
+    if (GROUPED) chain_wait();      // the segment list comes from the plan kernel
     extern __shared__ __align__(128) uint8_t smem[];
     float *tok_scale = reinterpret_cast<float *>(smem);           // per token tile: [8] scale, [8] inverse, [8] amax bits
     float *route_w = reinterpret_cast<float *>(smem + 128);       // [8]
@@ -389,6 +391,15 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs
     const long long total_blocks = units * blocks_per_unit;
     const long long blk_begin = total_blocks * blockIdx.x / gridDim.x;
     const long long blk_end = total_blocks * (blockIdx.x + 1) / gridDim.x;
+    if (!GROUPED) {
+        // the CTA's row blocks are one contiguous run of tiles
+        if (blk_begin < blk_end) {
+            const size_t first = static_cast<size_t>(blk_begin) * a.rg * nsb * TILE::BYTES;
+            const size_t last = static_cast<size_t>(min(static_cast<long long>(groups_total), blk_end * a.rg)) * nsb * TILE::BYTES;
+            prefetch_l2_range(a.w + first, last - first, CHAIN_PREFETCH_BYTES, tid, Q6T_THREADS);
+        }
+        chain_wait();     // activations come from the preceding kernel
+    }
     if (blk_begin >= blk_end) return;
 
     const int items_per_block = kpi < nsb ? (nsb - kpi + a.kp - 1) / a.kp : 0;

@@ -14,6 +14,8 @@ constexpr int RT_CHUNK = 2048;  // D positions held in registers at a time
 template <int TOK>
 __global__ void __launch_bounds__(256) router_logits_t_kernel(const void *x, int x_dtype, int t, int d, const float *wt,
                                                               const float *bias, int e, int rpw, float *logits) {
+    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
+    chain_wait();         // inputs come from preceding kernels
     extern __shared__ float xs[];   // [TOK][d]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int t0 = blockIdx.y * TOK;
@@ -95,6 +97,8 @@ template <int KMAX>
 __global__ void __launch_bounds__(256) moe_combine_cols_kernel(const float *terms, const int32_t *inv, int k, int d,
                                                                const float *extra, const float *extra_scale,
                                                                void *out, int out_dtype) {
+    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
+    chain_wait();         // inputs come from preceding kernels
     __shared__ int pos_sorted[KMAX];
     __shared__ int pos_raw[KMAX];
     const int row = blockIdx.x, tid = threadIdx.x;
@@ -127,6 +131,8 @@ template <int KMAX>
 __global__ void __launch_bounds__(256) moe_combine_ids_kernel(const float *terms, const void *ids, int ids_is_i64,
                                                               int k, int d, const float *extra,
                                                               const float *extra_scale, void *out, int out_dtype) {
+    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
+    chain_wait();         // inputs come from preceding kernels
     __shared__ int slot_sorted[KMAX];
     __shared__ long long id_raw[KMAX];
     const int row = blockIdx.x, tid = threadIdx.x;
@@ -159,9 +165,11 @@ int launch_combine_cols(const float *terms, const int32_t *inv, int rows, int k,
                         const float *extra_scale, void *out, int out_dtype, cudaStream_t stream) {
     dim3 grid(rows, (d + 255) / 256);
     if (k <= 16)
-        moe_combine_cols_kernel<16><<<grid, 256, 0, stream>>>(terms, inv, k, d, extra, extra_scale, out, out_dtype);
+        launch_chained(moe_combine_cols_kernel<16>, grid, dim3(256), 0, stream, terms, inv, k, d, extra, extra_scale, out,
+                       out_dtype);
     else
-        moe_combine_cols_kernel<64><<<grid, 256, 0, stream>>>(terms, inv, k, d, extra, extra_scale, out, out_dtype);
+        launch_chained(moe_combine_cols_kernel<64>, grid, dim3(256), 0, stream, terms, inv, k, d, extra, extra_scale, out,
+                       out_dtype);
     return check_launch("moe_combine");
 }
 
@@ -184,6 +192,8 @@ __global__ void __launch_bounds__(128) router_topk_block_kernel(const float *log
                                                                 float floor_value, int extra_id,
                                                                 const float *extra_weight, float *weights,
                                                                 int64_t *ids) {
+    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
+    chain_wait();         // inputs come from preceding kernels
     __shared__ unsigned long long warp_best[2][4];
     __shared__ float red[4];
     __shared__ float sel_p[32];
@@ -267,8 +277,8 @@ __global__ void __launch_bounds__(128) router_topk_block_kernel(const float *log
 
 int launch_topk_warp(const float *logits, int rows, int n, int k, int renorm, float floor_value, int extra_id,
                      const float *extra_weight, float *weights, int64_t *ids, cudaStream_t stream) {
-    router_topk_block_kernel<<<rows, 128, 0, stream>>>(logits, n, k, renorm, floor_value, extra_id, extra_weight,
-                                                       weights, ids);
+    launch_chained(router_topk_block_kernel, dim3(rows), dim3(128), 0, stream, logits, n, k, renorm, floor_value,
+                   extra_id, extra_weight, weights, ids);
     return check_launch("router_topk");
 }
 
@@ -284,11 +294,11 @@ extern "C" int b200q_moe_combine_ids(const float *terms, const void *ids, int id
         return fail(B200Q_EINVAL, "moe_combine_ids: bad argument (k <= 64)");
     dim3 grid(rows, (d + 255) / 256);
     if (k <= 16)
-        moe_combine_ids_kernel<16><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(terms, ids, ids_is_i64, k, d, extra,
-                                                                                      extra_scale, out, out_dtype);
+        launch_chained(moe_combine_ids_kernel<16>, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), terms, ids,
+                       ids_is_i64, k, d, extra, extra_scale, out, out_dtype);
     else
-        moe_combine_ids_kernel<64><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(terms, ids, ids_is_i64, k, d, extra,
-                                                                                      extra_scale, out, out_dtype);
+        launch_chained(moe_combine_ids_kernel<64>, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), terms, ids,
+                       ids_is_i64, k, d, extra, extra_scale, out, out_dtype);
     return check_launch("moe_combine_ids");
 }
 
@@ -312,6 +322,7 @@ extern "C" int b200q_router_logits_t(const void *x, int x_dtype, int t, int d, c
     int rpw = 4;   // fewer rows per warp when the grid would leave SMs idle
     while (rpw > 1 && static_cast<long long>((e + 8 * rpw - 1) / (8 * rpw)) * tiles < 2LL * sm_count()) rpw >>= 1;
     dim3 grid((e + 8 * rpw - 1) / (8 * rpw), tiles);
-    kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(x, x_dtype, t, d, wt, bias, e, rpw, logits);
+    launch_chained(kernel, grid, dim3(256), smem, static_cast<cudaStream_t>(stream), x, x_dtype, t, d, wt, bias, e, rpw,
+                   logits);
     return check_launch("router_logits_t");
 }

@@ -1,6 +1,8 @@
 // Host-side plumbing shared by all entry points: error text, device status word, SM count.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -31,6 +33,13 @@ int check_launch(const char *what) {
         return fail(B200Q_ECUDA, "%s: %s", what, cudaGetErrorString(err));
     }
     return B200Q_OK;
+}
+
+// Environment switch of the programmatic dependent launches (read at every launch so a test can
+// flip it): B200Q_CHAIN=0 launches every kernel with the usual full stream serialisation.
+bool chain_enabled() {
+    const char *v = std::getenv("B200Q_CHAIN");
+    return !(v && std::strcmp(v, "0") == 0);
 }
 
 // One status word per device, living in a __device__ variable so no allocation is needed.
