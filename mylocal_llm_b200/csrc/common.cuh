@@ -74,12 +74,14 @@ inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
 __device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void chain_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// Asks L2 for the lines of [base, base + bytes) (at most `cap` bytes), all threads of the CTA
-// taking part. It returns nothing to the thread, so it may run before chain_wait(): a dense GEMV
-// that became resident early pulls its slice of the weights towards L2 while the preceding
-// kernel finishes.
+// Asks L2 for the lines of [base, base + bytes), all threads of the CTA taking part; nothing is
+// requested when the range exceeds `cap` bytes. It returns nothing to the thread, so it may run
+// before chain_wait(): a small dense GEMV that became resident early pulls its slice of the
+// weights towards L2 while the preceding kernel finishes. (Large slices are left alone: a
+// prefetch running ahead of the register loads of a long stream measured 7-30 % slower than the
+// loads by themselves.)
 __device__ __forceinline__ void prefetch_l2_range(const uint8_t *base, size_t bytes, size_t cap, int tid, int threads) {
-    if (bytes > cap) bytes = cap;
+    if (bytes > cap) return;
     for (size_t off = static_cast<size_t>(tid) * 128; off < bytes; off += static_cast<size_t>(threads) * 128)
         asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
 }
