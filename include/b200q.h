@@ -186,6 +186,16 @@ int b200q_moe_combine(const float *terms, const int32_t *inv, int rows, int k, i
                       const float *extra, const float *extra_scale, void *out, int out_dtype,
                       void *stream);
 
+/* b200q_moe_combine fused with the residual add and RMSNorm that follow it in a decoder layer
+ * (b200q_residual_rmsnorm: mini_llm/ops/rmsnorm_inference.py:228-252 of the reference):
+ *   branch = the ordered sum, rounded to branch_dtype (the type b200q_moe_combine would store);
+ *   res_out = residual + alpha*branch (FP32);  y = rmsnorm(res_out)*gamma in y_dtype.
+ * Same bits as the two calls; k <= 16 (else B200Q_EUNSUPPORTED); res_out must not alias residual. */
+int b200q_moe_combine_norm(const float *terms, const int32_t *inv, int rows, int k, int d, const float *extra,
+                           const float *extra_scale, int branch_dtype, const float *residual, float alpha,
+                           const void *gamma, int gamma_dtype, float eps, float *res_out, void *y, int y_dtype,
+                           void *stream);
+
 /* Ordered combine for terms stored at the flat assignment index: out[row] = sum of terms[row*k+slot]
  * in ascending (expert id, slot) order, plain FP32 adds from zero (same semantics as
  * b200q_moe_combine; used by the home rank of an expert-parallel layer). */

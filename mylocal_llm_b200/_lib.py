@@ -70,6 +70,8 @@ SIGNATURES = {
     "b200q_moe_down": [_ptr, _c_i64, _c_int, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
                        _c_int, _ptr, _ptr],
     "b200q_moe_combine": [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr],
+    "b200q_moe_combine_norm": [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _ptr, _c_f32, _ptr, _c_int,
+                               _c_f32, _ptr, _ptr, _c_int, _ptr],
 }
 
 _LOCK = threading.Lock()

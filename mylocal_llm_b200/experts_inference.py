@@ -133,12 +133,14 @@ class PackedExpertBank:
 
 
 def routed_experts_forward(x2d, weights2d, ids2d, bank, *, extra=None, extra_scale=None, out_dtype=None,
-                           tables=None, tables_aligned16=False, n_experts=None):
+                           tables=None, tables_aligned16=False, n_experts=None, residual_norm=None):
     """plan -> grouped gate/up -> grouped down (route-weighted) -> ordered combine.
 
     x2d [T,D]; weights2d FP32 [T,k]; ids2d int32/int64 [T,k]; returns [T,D]. With ``tables`` (from
     ``PackedExpertBank.pointer_tables``) experts are addressed through pointer tables and
-    ``n_experts`` may exceed the bank (appended shared expert).
+    ``n_experts`` may exceed the bank (appended shared expert). With ``residual_norm = (norm,
+    residual)`` the combine also performs the residual add and RMSNorm that follow the layer and
+    the result is ``(new residual, normalised activations)`` (``moe_ops.moe_combine_norm``).
     """
     torch = _torch()
     plan = moe_ops.moe_plan(ids2d, n_experts or bank.n_experts)
@@ -148,14 +150,20 @@ def routed_experts_forward(x2d, weights2d, ids2d, bank, *, extra=None, extra_sca
                                    gate_table=tables[0], up_table=tables[1], tables_aligned16=tables_aligned16)
         terms = moe_ops.moe_down(hbuf, route.contiguous().reshape(-1), plan, None, bank.down_type, bank.d_model,
                                  bank.d_ff, 0, down_table=tables[2], tables_aligned16=tables_aligned16)
-        return moe_ops.moe_combine(terms, plan, bank.d_model, extra=extra, extra_scale=extra_scale,
-                                   out_dtype=out_dtype or x2d.dtype)
+        return _combine(terms, plan, bank.d_model, extra, extra_scale, out_dtype or x2d.dtype, residual_norm)
     hbuf = moe_ops.moe_gate_up(x2d, plan, bank.gate, bank.up, bank.gate_type, bank.up_type, bank.d_ff,
                                bank.d_model, bank.gate_stride, bank.up_stride)
     terms = moe_ops.moe_down(hbuf, route.contiguous().reshape(-1), plan, bank.down, bank.down_type, bank.d_model,
                              bank.d_ff, bank.down_stride)
-    return moe_ops.moe_combine(terms, plan, bank.d_model, extra=extra, extra_scale=extra_scale,
-                               out_dtype=out_dtype or x2d.dtype)
+    return _combine(terms, plan, bank.d_model, extra, extra_scale, out_dtype or x2d.dtype, residual_norm)
+
+
+def _combine(terms, plan, d, extra, extra_scale, out_dtype, residual_norm):
+    if residual_norm is None:
+        return moe_ops.moe_combine(terms, plan, d, extra=extra, extra_scale=extra_scale, out_dtype=out_dtype)
+    norm, residual = residual_norm
+    return moe_ops.moe_combine_norm(terms, plan, d, norm, residual, extra=extra, extra_scale=extra_scale,
+                                    branch_dtype=out_dtype)
 
 
 class ResidentExpertExecutor:

@@ -137,16 +137,41 @@ class PackedMoELayer:
                     (bank.gate_type, bank.up_type, bank.down_type))) and bank.n_experts < 1024:
             self._tables = bank.pointer_tables(extra=shared)
 
-    def forward(self, hidden):
-        """hidden [B, T, D] -> [B, T, D] in hidden's dtype."""
+    def can_fuse_residual_norm(self):
+        """Whether ``forward(hidden, residual_norm=...)`` is available: the resident executor's grouped
+        path with at most 16 terms per row (top-k plus the shared expert)."""
+        terms = self.router.k + (1 if self._tables is not None else 0)
+        return isinstance(self.executor, ResidentExpertExecutor) and terms <= moe_ops.COMBINE_NORM_MAX_K
+
+    def forward(self, hidden, residual_norm=None):
+        """hidden [B, T, D] -> [B, T, D] in hidden's dtype. With ``residual_norm = (norm, residual)``
+        (``RMSNormInference``, FP32 residual stream shaped like ``hidden``) the layer's last kernel also
+        adds the branch to the residual and normalises it, and the result is ``(new residual, normalised
+        activations)``: the same bits as ``norm.forward_residual_add(residual, self.forward(hidden))``."""
         torch = _torch()
         if not isinstance(hidden, torch.Tensor) or not hidden.is_cuda:
             raise TypeError("MoE layer requires a CUDA tensor")
         if hidden.ndim != 3 or hidden.shape[0] < 1 or hidden.shape[-1] != self.bank.d_model:
             raise ValueError("hidden must have shape [positive batch,time,d_model]")
+        if residual_norm is not None and not self.can_fuse_residual_norm():
+            raise NotImplementedError("this layer cannot fuse the residual add and norm into its combine")
         if not hidden.shape[1]:
+            if residual_norm is not None:
+                return residual_norm[0].forward_residual_add(residual_norm[1], torch.empty_like(hidden))
             return torch.empty_like(hidden)
         batch, seq, d = hidden.shape
+        fused = {}
+        if residual_norm is not None:
+            norm, residual = residual_norm
+            if residual.shape != hidden.shape or residual.dtype != torch.float32 or not residual.is_contiguous():
+                raise ValueError("the residual stream must be contiguous FP32 and shaped like hidden")
+            fused = {"residual_norm": (norm, residual.reshape(batch * seq, d))}
+
+        def shaped(out):
+            if residual_norm is None:
+                return out.reshape(batch, seq, d)
+            return out[0].reshape(batch, seq, d), out[1].reshape(batch, seq, d)
+
         x2d = hidden.reshape(batch * seq, d)
         if not x2d.is_contiguous():
             x2d = x2d.contiguous()
@@ -159,8 +184,8 @@ class PackedMoELayer:
             tables, aligned = self._tables
             out = self.executor.forward_routed(self.layer_id, x2d, weights, ids, out_dtype=hidden.dtype,
                                                tables=tables, tables_aligned16=aligned,
-                                               n_experts=self.bank.n_experts + 1)
-            return out.reshape(batch, seq, d)
+                                               n_experts=self.bank.n_experts + 1, **fused)
+            return shaped(out)
         weights, ids = moe_ops.router_topk(logits, self.router.k, renormalize=True,
                                            floor=self.router.normalization_floor)
         extra = extra_scale = None
@@ -171,5 +196,5 @@ class PackedMoELayer:
             if self.shared_gate is not None:
                 extra_scale = moe_ops.shared_gate(x2d, self.shared_gate)
         out = self.executor.forward_routed(self.layer_id, x2d, weights, ids, extra=extra, extra_scale=extra_scale,
-                                           out_dtype=hidden.dtype)
-        return out.reshape(batch, seq, d)
+                                           out_dtype=hidden.dtype, **fused)
+        return shaped(out)

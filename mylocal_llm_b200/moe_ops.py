@@ -172,6 +172,28 @@ def moe_combine(terms, plan, d, *, extra=None, extra_scale=None, out_dtype=None)
     return out
 
 
+COMBINE_NORM_MAX_K = 16
+
+
+def moe_combine_norm(terms, plan, d, norm, residual, *, extra=None, extra_scale=None, branch_dtype=None, alpha=1.0):
+    """``moe_combine`` fused with ``norm.forward_residual_add(residual, branch, alpha)``: returns
+    ``(new residual FP32 [T, D], normalised activations [T, D] in the norm weight's dtype)``, the same
+    bits as the two calls. ``branch_dtype`` is the type the combine alone would have produced."""
+    torch = _torch()
+    if residual.dtype != torch.float32 or not residual.is_contiguous() or residual.numel() != plan.rows * d:
+        raise ValueError("the residual stream must be a contiguous FP32 tensor of [rows, d]")
+    if plan.k > COMBINE_NORM_MAX_K:
+        raise NotImplementedError("fused combine + norm handles at most 16 terms per row")
+    branch_dtype = branch_dtype or torch.float32
+    res_out = torch.empty_like(residual)
+    y = torch.empty(residual.shape, dtype=norm.gamma.dtype, device=residual.device)
+    name = lambda dt: _lib.DTYPE_ID[str(dt).replace("torch.", "")]
+    _lib.call("b200q_moe_combine_norm", _ptr(terms), _ptr(plan.inv), plan.rows, plan.k, d, _ptr(extra),
+              _ptr(extra_scale), name(branch_dtype), _ptr(residual), float(alpha), _ptr(norm.gamma),
+              name(norm.gamma.dtype), float(norm.eps), _ptr(res_out), _ptr(y), name(y.dtype), _lib.current_stream())
+    return res_out, y
+
+
 def moe_combine_ids(terms_flat, ids2d, d, *, extra=None, extra_scale=None, out_dtype=None):
     """Ordered per-token sum of terms stored at the flat assignment index; ``ids2d`` [T,k] gives the
     order (ascending expert id, then slot). ``extra`` [T,d] (times ``extra_scale`` [T]) is added last."""

@@ -8,6 +8,8 @@ of layer i+1 (``residual_add_rmsnorm``), as the reference's low-precision engine
 quantized path exactly as the 48-layer benchmark configuration prescribes.
 """
 
+import os
+
 from .experts_inference import synthetic_bank
 from .moe_layer import PackedMoELayer, RMSNormInference
 from .quantize import random_packed
@@ -24,6 +26,10 @@ class PackedMoEStack:
         if len(layers) != len(norms) or not layers:
             raise ValueError("one RMSNorm per MoE layer is required")
         self.layers, self.norms, self.final_norm = list(layers), list(norms), final_norm
+        # B200Q_FUSE_NORM=1: combine + residual add + RMSNorm in one kernel where the layer allows. Off by
+        # default: one CTA per row has less parallelism than the two kernels it replaces and measured slower
+        # (1 token: 384 vs 425 tokens/s on the 48-layer stack; 64 tokens: 5019 vs 5069); the results are the same.
+        self.fuse_residual_norm = os.environ.get("B200Q_FUSE_NORM", "0") == "1"
 
     @property
     def packed_bytes(self):
@@ -39,9 +45,11 @@ class PackedMoEStack:
         res = residual
         hidden = self.norms[0].forward_residual(res)
         for i, layer in enumerate(self.layers):
-            branch = layer.forward(hidden)
             norm = self.norms[i + 1] if i + 1 < len(self.layers) else self.final_norm
-            res, hidden = norm.forward_residual_add(res, branch)
+            if self.fuse_residual_norm and layer.can_fuse_residual_norm():
+                res, hidden = layer.forward(hidden, residual_norm=(norm, res))
+            else:
+                res, hidden = norm.forward_residual_add(res, layer.forward(hidden))
         return res, hidden
 
     @classmethod
