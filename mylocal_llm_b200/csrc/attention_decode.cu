@@ -89,14 +89,15 @@ __device__ __forceinline__ void load_row_piece(const void *cache, int dtype, siz
     }
 }
 
-// One CTA of eight warps per (batch, head): warp w takes groups of ATT_U consecutive cache positions
+// One CTA of 32 warps per (batch, head): warp w takes groups of ATT_U consecutive cache positions
 // (all their key and value loads are issued before any arithmetic, so the loop is not bound by one
 // load latency per position); each lane holds EPL = Dh/32 dimensions; scores by warp reduction,
-// running (max, sum, weighted values) per warp, merged across the warps at the end.
-constexpr int ATT_WARPS = 8;
-constexpr int ATT_U = 8;
-
-template <int EPL>
+// running (max, sum, weighted values) per warp, merged across the warps at the end. A one-token
+// step has only batch x heads CTAs, so the positions of a head are spread over as many warps as a
+// CTA can hold: with 8 warps a 512-token context took nine dependent iterations (44 us per launch,
+// 40 % of a 1.7B Llama step), with 32 warps it takes three. When batch x heads already fills the
+// GPU several times over, 8 warps per CTA are the faster shape (less merging, no idle warps).
+template <int EPL, int ATT_U, int ATT_WARPS>
 __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const float *q, const void *k_cache,
                                                                           const void *v_cache, int cache_dtype,
                                                                           const long long *position, long long q_row,
@@ -238,12 +239,20 @@ int b200q_decode_attention(const float *q, int64_t q_row_stride, const void *k_c
         return fail(B200Q_EINVAL, "decode_attention: bad argument");
     const long long *pos = reinterpret_cast<const long long *>(position);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (head_dim == 64)
-        launch_chained(decode_attention_kernel<2>, dim3(batch * heads), dim3(ATT_WARPS * 32), 0, s, q, k_cache, v_cache,
-                       cache_dtype, pos, q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
+    const bool wide = static_cast<long long>(batch) * heads < 2LL * sm_count();      // few CTAs: 32 warps each
+    const dim3 grid(batch * heads);
+    if (head_dim == 64 && wide)
+        launch_chained(decode_attention_kernel<2, 8, 32>, grid, dim3(1024), 0, s, q, k_cache, v_cache, cache_dtype, pos,
+                       q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
+    else if (head_dim == 64)
+        launch_chained(decode_attention_kernel<2, 8, 8>, grid, dim3(256), 0, s, q, k_cache, v_cache, cache_dtype, pos,
+                       q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
+    else if (head_dim == 128 && wide)
+        launch_chained(decode_attention_kernel<4, 4, 32>, grid, dim3(1024), 0, s, q, k_cache, v_cache, cache_dtype, pos,
+                       q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
     else if (head_dim == 128)
-        launch_chained(decode_attention_kernel<4>, dim3(batch * heads), dim3(ATT_WARPS * 32), 0, s, q, k_cache, v_cache,
-                       cache_dtype, pos, q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
+        launch_chained(decode_attention_kernel<4, 8, 8>, grid, dim3(256), 0, s, q, k_cache, v_cache, cache_dtype, pos,
+                       q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
     else
         return fail(B200Q_EUNSUPPORTED, "decode_attention: head_dim must be 64 or 128");
     return check_launch("decode_attention");

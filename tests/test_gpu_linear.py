@@ -107,7 +107,7 @@ def test_linear_low_precision_activations(cuda, fmt, dtype):
 
 
 def test_linear_config0_shape_q8_0(cuda):
-    # BASELINE config 0: W [4096,4096] N(0,0.02) seed 0 -> Q8_0; x fp32 [1|8, 4096]
+    # first benchmark configuration: W [4096,4096] N(0,0.02) seed 0 -> Q8_0; x fp32 [1|8, 4096]
     rng = np.random.default_rng(0)
     w = quantize(rng.normal(0, 0.02, (4096, 4096)).astype(np.float32), "Q8_0")
     dw = packed_to_device(w)
@@ -121,7 +121,7 @@ def test_linear_config0_shape_q8_0(cuda):
 @pytest.mark.parametrize("fmt", ["Q4_K", "Q5_K", "Q6_K"])
 @pytest.mark.parametrize("shape", [(8192, 2048), (2048, 8192)])
 def test_linear_config1_shapes_bf16(cuda, fmt, shape):
-    # BASELINE config 1 at decode batch sizes; random-byte weights keep the host side fast
+    # second benchmark configuration at decode batch sizes; random-byte weights keep the host side fast
     w = random_packed(fmt, shape, seed=shape[0], d=0.01, dmin=0.005)
     dw = packed_to_device(w)
     dense = po.dequantize(w.data, w.shape, fmt).astype(np.float64)
@@ -217,7 +217,7 @@ def test_swiglu_mixed_formats(cuda, gf, uf, m):
 
 
 def test_expert_ffn_config3_shape(cuda):
-    # one expert of BASELINE config 3: gate/up Q4_K [512,2048], down Q6_K [2048,512]
+    # one expert of the fourth benchmark configuration: gate/up Q4_K [512,2048], down Q6_K [2048,512]
     rng = np.random.default_rng(51)
     gate = quantize(rng.normal(0, 0.02, (512, 2048)).astype(np.float32), "Q4_K")
     up = quantize(rng.normal(0, 0.02, (512, 2048)).astype(np.float32), "Q4_K")
