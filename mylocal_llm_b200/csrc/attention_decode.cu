@@ -3,6 +3,9 @@
 // kernels per layer in the one-token step; the packed linears around them are the hot path.
 // Semantics follow the reference's inference attention (mini_llm/ops/attention_inference.py:255-277
 // for the rotation, 1/sqrt(d_head) scaled softmax over positions 0..pos, grouped KV heads).
+#include <cooperative_groups.h>
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b200q {
@@ -97,7 +100,11 @@ __device__ __forceinline__ void load_row_piece(const void *cache, int dtype, siz
 // CTA can hold: with 8 warps a 512-token context took nine dependent iterations (44 us per launch,
 // 40 % of a 1.7B Llama step), with 32 warps it takes three. When batch x heads already fills the
 // GPU several times over, 8 warps per CTA are the faster shape (less merging, no idle warps).
-template <int EPL, int ATT_U, int ATT_WARPS>
+// SPLIT > 1: a thread-block cluster of SPLIT CTAs shares one (batch, head); CTA r of the cluster
+// takes every SPLIT-th group of positions, the partial (max, sum, weighted values) of the CTAs are
+// merged by CTA 0 through distributed shared memory between two cluster barriers (hardware
+// barriers; nothing spins). The kernel must then be launched with cluster dimension SPLIT.
+template <int EPL, int ATT_U, int ATT_WARPS, int SPLIT>
 __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const float *q, const void *k_cache,
                                                                           const void *v_cache, int cache_dtype,
                                                                           const long long *position, long long q_row,
@@ -107,7 +114,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     chain_wait();         // inputs come from preceding kernels
     constexpr int DH = EPL * 32;
     __shared__ float sm_m[ATT_WARPS], sm_l[ATT_WARPS], sm_acc[ATT_WARPS][DH];
-    const int bh = blockIdx.x, bb = bh / h, head = bh - bb * h;
+    __shared__ float fin_ml[2], fin_acc[DH];            // this CTA's merged partial (SPLIT > 1)
+    const int part = SPLIT > 1 ? static_cast<int>(blockIdx.x % SPLIT) : 0;      // rank inside the cluster
+    const int bh = blockIdx.x / SPLIT, bb = bh / h, head = bh - bb * h;
     const int kvh = head / (h / hkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     long long last = position[0];                       // newest valid cache position
@@ -120,7 +129,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     float m = __int_as_float(0xff800000), l = 0.f, acc[EPL];
 #pragma unroll
     for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
-    for (long long j0 = static_cast<long long>(warp) * ATT_U; j0 <= last; j0 += ATT_WARPS * ATT_U) {
+    for (long long j0 = static_cast<long long>(part * ATT_WARPS + warp) * ATT_U; j0 <= last;
+         j0 += SPLIT * ATT_WARPS * ATT_U) {
         float kk[ATT_U][EPL], vv[ATT_U][EPL], dot[ATT_U];
 #pragma unroll
         for (int u = 0; u < ATT_U; ++u) {
@@ -175,10 +185,47 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
 #pragma unroll
             for (int e = 0; e < EPL; ++e) r[e] += sm_acc[w][lane * EPL + e] * f;
         }
-        const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+        if (SPLIT == 1) {
+            const float inv = ll > 0.f ? 1.0f / ll : 0.f;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e)
-            store_from_float(out, out_dtype, (static_cast<size_t>(bb) * h + head) * DH + lane * EPL + e, r[e] * inv);
+            for (int e = 0; e < EPL; ++e)
+                store_from_float(out, out_dtype, (static_cast<size_t>(bb) * h + head) * DH + lane * EPL + e, r[e] * inv);
+        } else {
+            if (lane == 0) { fin_ml[0] = mm; fin_ml[1] = ll; }
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) fin_acc[lane * EPL + e] = r[e];
+        }
+    }
+    if constexpr (SPLIT > 1) {
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();                                   // every CTA's partial is in its shared memory
+        if (part == 0 && warp == 0) {
+            float pm[SPLIT], pl[SPLIT], mm = __int_as_float(0xff800000);
+#pragma unroll
+            for (int p = 0; p < SPLIT; ++p) {
+                const float *ml = cluster.map_shared_rank(fin_ml, p);
+                pm[p] = ml[0];
+                pl[p] = ml[1];
+                mm = fmaxf(mm, pm[p]);
+            }
+            float ll = 0.f, r[EPL];
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) r[e] = 0.f;
+#pragma unroll
+            for (int p = 0; p < SPLIT; ++p) {
+                const float f = pl[p] > 0.f ? __expf(pm[p] - mm) : 0.f;
+                const float *pa = cluster.map_shared_rank(fin_acc, p);
+                ll += pl[p] * f;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) r[e] += pa[lane * EPL + e] * f;
+            }
+            const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e)
+                store_from_float(out, out_dtype, (static_cast<size_t>(bb) * h + head) * DH + lane * EPL + e, r[e] * inv);
+        }
+        cluster.sync();                                   // partials stay alive until CTA 0 has read them
     }
 }
 
@@ -193,6 +240,14 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float *gu, int m, i
         const float g = gu[row * 2 * f + col], u = gu[row * 2 * f + f + col];
         store_from_float(out, out_dtype, static_cast<size_t>(idx), swiglu_f32(g, u));
     }
+}
+
+constexpr int ATT_SPLIT = 4;
+
+// B200Q_ATTENTION_SPLIT=0 keeps one CTA per (batch, head) (A/B measurements).
+static bool attention_split_enabled() {
+    const char *v = std::getenv("B200Q_ATTENTION_SPLIT");
+    return !(v && v[0] == '0' && v[1] == 0);
 }
 
 }  // namespace b200q
@@ -239,20 +294,30 @@ int b200q_decode_attention(const float *q, int64_t q_row_stride, const void *k_c
         return fail(B200Q_EINVAL, "decode_attention: bad argument");
     const long long *pos = reinterpret_cast<const long long *>(position);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const bool wide = static_cast<long long>(batch) * heads < 2LL * sm_count();      // few CTAs: 32 warps each
-    const dim3 grid(batch * heads);
-    if (head_dim == 64 && wide)
-        launch_chained(decode_attention_kernel<2, 8, 32>, grid, dim3(1024), 0, s, q, k_cache, v_cache, cache_dtype, pos,
-                       q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
+    // few (batch, head) pairs: 32 warps per CTA, and four CTAs (a cluster) per pair while those still fit the GPU
+    const long long pairs = static_cast<long long>(batch) * heads;
+    const bool wide = pairs < 2LL * sm_count();
+    const bool split = wide && pairs * ATT_SPLIT <= 2LL * sm_count() && attention_split_enabled();
+    if (head_dim == 64 && split)
+        launch_chained_cluster(decode_attention_kernel<2, 8, 32, ATT_SPLIT>, dim3(pairs * ATT_SPLIT), dim3(1024), 0, s,
+                               ATT_SPLIT, q, k_cache, v_cache, cache_dtype, pos, q_row_stride, heads, kv_heads, horizon,
+                               scale, out, out_dtype);
+    else if (head_dim == 64 && wide)
+        launch_chained(decode_attention_kernel<2, 8, 32, 1>, dim3(pairs), dim3(1024), 0, s, q, k_cache, v_cache, cache_dtype,
+                       pos, q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
     else if (head_dim == 64)
-        launch_chained(decode_attention_kernel<2, 8, 8>, grid, dim3(256), 0, s, q, k_cache, v_cache, cache_dtype, pos,
-                       q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
+        launch_chained(decode_attention_kernel<2, 8, 8, 1>, dim3(pairs), dim3(256), 0, s, q, k_cache, v_cache, cache_dtype,
+                       pos, q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
+    else if (head_dim == 128 && split)
+        launch_chained_cluster(decode_attention_kernel<4, 4, 32, ATT_SPLIT>, dim3(pairs * ATT_SPLIT), dim3(1024), 0, s,
+                               ATT_SPLIT, q, k_cache, v_cache, cache_dtype, pos, q_row_stride, heads, kv_heads, horizon,
+                               scale, out, out_dtype);
     else if (head_dim == 128 && wide)
-        launch_chained(decode_attention_kernel<4, 4, 32>, grid, dim3(1024), 0, s, q, k_cache, v_cache, cache_dtype, pos,
-                       q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
+        launch_chained(decode_attention_kernel<4, 4, 32, 1>, dim3(pairs), dim3(1024), 0, s, q, k_cache, v_cache, cache_dtype,
+                       pos, q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
     else if (head_dim == 128)
-        launch_chained(decode_attention_kernel<4, 8, 8>, grid, dim3(256), 0, s, q, k_cache, v_cache, cache_dtype, pos,
-                       q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
+        launch_chained(decode_attention_kernel<4, 8, 8, 1>, dim3(pairs), dim3(256), 0, s, q, k_cache, v_cache, cache_dtype,
+                       pos, q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
     else
         return fail(B200Q_EUNSUPPORTED, "decode_attention: head_dim must be 64 or 128");
     return check_launch("decode_attention");
