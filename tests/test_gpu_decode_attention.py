@@ -1,0 +1,79 @@
+"""Single-query attention over the KV cache (``b200q_decode_attention``) against an FP64 reference.
+
+The kernel picks its shape from the grid: a cluster of four 32-warp CTAs per (batch, head) for a
+handful of heads, one 32-warp CTA for a few hundred, one 8-warp CTA beyond that. Every shape has to
+give softmax(q.K^T / sqrt(d)) V over positions 0..pos (the reference's inference attention,
+mini_llm/ops/attention_inference.py:255-277), for positions inside the first group of a warp, across
+several iterations, and at the end of the horizon.
+"""
+
+import ctypes
+
+import numpy as np
+import pytest
+
+from mylocal_llm_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+
+
+def run_kernel(torch, q, k, v, pos, out_dtype):
+    batch, heads, dh = q.shape
+    kv_heads, horizon = k.shape[1], k.shape[2]
+    out = torch.empty((batch, heads * dh), dtype=out_dtype, device="cuda")
+    position = torch.tensor([pos], dtype=torch.int64, device="cuda")
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    ident = lambda dt: _lib.DTYPE_ID[str(dt).replace("torch.", "")]
+    q2 = q.reshape(batch, heads * dh).contiguous()
+    _lib.call("b200q_decode_attention", ptr(q2), q2.stride(0), ptr(k), ptr(v), ident(k.dtype), ptr(position), batch,
+              heads, kv_heads, dh, horizon, float(dh ** -0.5), ptr(out), ident(out_dtype), _lib.current_stream())
+    torch.cuda.synchronize()
+    return out.reshape(batch, heads, dh)
+
+
+def reference(torch, q, k, v, pos):
+    batch, heads, dh = q.shape
+    group = heads // k.shape[1]
+    kk = k[:, :, :pos + 1].double().repeat_interleave(group, dim=1)          # [B, H, P, dh]
+    vv = v[:, :, :pos + 1].double().repeat_interleave(group, dim=1)
+    scores = torch.einsum("bhd,bhpd->bhp", q.double(), kk) * dh ** -0.5
+    return torch.einsum("bhp,bhpd->bhd", torch.softmax(scores, dim=-1), vv)
+
+
+@pytest.mark.parametrize("batch,heads,kv_heads", [(1, 8, 2), (1, 32, 32), (5, 16, 4), (10, 32, 8)])
+@pytest.mark.parametrize("dh", [64, 128])
+@pytest.mark.parametrize("pos", [0, 5, 255, 256, 1023, 1024, 2299])
+@pytest.mark.parametrize("cache", ["bfloat16", "float32"])
+def test_decode_attention_matches_fp64(cuda, batch, heads, kv_heads, dh, pos, cache):
+    torch = cuda
+    if batch * heads * dh * pos > 10 * 32 * 64 * 1100 and cache == "float32":
+        pytest.skip("large case: one cache type is enough")
+    horizon = 2300
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(batch * 1000 + heads + dh + pos)
+    cdt = getattr(torch, cache)
+    q = torch.randn((batch, heads, dh), device="cuda", generator=gen)
+    k = torch.randn((batch, kv_heads, horizon, dh), device="cuda", generator=gen).to(cdt)
+    v = torch.randn((batch, kv_heads, horizon, dh), device="cuda", generator=gen).to(cdt)
+    k[:, :, pos + 1:] = float("nan")                    # positions after `pos` must never be read into the result
+    v[:, :, pos + 1:] = float("nan")
+    got = run_kernel(torch, q, k, v, pos, torch.float32).double()
+    ref = reference(torch, q, k, v, pos)
+    assert bool(torch.isfinite(got).all())
+    np.testing.assert_allclose(got.cpu().numpy(), ref.cpu().numpy(), rtol=2e-4, atol=2e-5)
+
+
+def test_split_and_single_cta_shapes_agree(cuda, monkeypatch):
+    torch = cuda
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(3)
+    q = torch.randn((1, 8, 64), device="cuda", generator=gen)
+    k = torch.randn((1, 8, 1500, 64), device="cuda", generator=gen).to(torch.bfloat16)
+    v = torch.randn((1, 8, 1500, 64), device="cuda", generator=gen).to(torch.bfloat16)
+    monkeypatch.setenv("B200Q_ATTENTION_SPLIT", "0")
+    single = run_kernel(torch, q, k, v, 1400, torch.float32)
+    monkeypatch.setenv("B200Q_ATTENTION_SPLIT", "1")
+    split = run_kernel(torch, q, k, v, 1400, torch.float32)
+    np.testing.assert_allclose(split.cpu().numpy(), single.cpu().numpy(), rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(split.double().cpu().numpy(), reference(torch, q, k, v, 1400).cpu().numpy(), rtol=2e-4,
+                               atol=2e-5)
