@@ -196,6 +196,17 @@ int b200q_moe_combine_norm(const float *terms, const int32_t *inv, int rows, int
                            const void *gamma, int gamma_dtype, float eps, float *res_out, void *y, int y_dtype,
                            void *stream);
 
+/* b200q_router_topk_ex and b200q_moe_plan for ONE token row in one launch (the one-token decode
+ * step): weights / ids as b200q_router_topk_ex (rows = 1), plan arrays as b200q_moe_plan for those
+ * ids over `e` experts with one row per segment (counts [e], offsets [e+1], order / inv [k'],
+ * seg_* [max_segments]). n <= 1024, k <= 31; an appended extra_id must be >= n (it is for the
+ * shared expert, id n). */
+int b200q_router_topk_plan_row(const float *logits, int n, int k, int renormalize, float floor_value, int extra_id,
+                               const float *extra_weight, float *weights, int64_t *ids, int e, int32_t *counts,
+                               int32_t *offsets, int32_t *order, int32_t *inv, int32_t *seg_expert, int32_t *seg_begin,
+                               int32_t *seg_count, int32_t *num_segments, int max_segments, int32_t *status,
+                               void *stream);
+
 /* Ordered combine for terms stored at the flat assignment index: out[row] = sum of terms[row*k+slot]
  * in ascending (expert id, slot) order, plain FP32 adds from zero (same semantics as
  * b200q_moe_combine; used by the home rank of an expert-parallel layer). */

@@ -36,6 +36,8 @@ SIGNATURES = {
     "b200q_router_logits_t": [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _ptr, _ptr],
     "b200q_router_topk_ex": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_f32, _c_int, _ptr, _ptr, _ptr, _ptr],
     "b200q_shared_gate": [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr],
+    "b200q_router_topk_plan_row": [_ptr, _c_int, _c_int, _c_int, _c_f32, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr,
+                                   _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr],
     "b200q_router_topk": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_f32, _ptr, _ptr, _ptr],
     "b200q_moe_plan": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
                        _ptr, _c_int, _ptr, _ptr],

@@ -558,7 +558,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float *terms, co
 int launch_combine_cols(const float *terms, const int32_t *inv, int rows, int k, int d, const float *extra,
                         const float *extra_scale, void *out, int out_dtype, cudaStream_t stream);
 int launch_topk_warp(const float *logits, int rows, int n, int k, int renorm, float floor_value, int extra_id,
-                     const float *extra_weight, float *weights, int64_t *ids, cudaStream_t stream);
+                     const float *extra_weight, float *weights, int64_t *ids, const RowPlanOut &plan,
+                     cudaStream_t stream);
 
 }  // namespace b200q
 
@@ -635,11 +636,30 @@ int b200q_router_topk_ex(const float *logits, int rows, int n, int k, int renorm
     if (renormalize && !(floor_value > 0.0f)) return fail(B200Q_EINVAL, "router_topk: floor must be positive");
     if (n <= 1024)
         return launch_topk_warp(logits, rows, n, k, renormalize, floor_value, extra_id, extra_weight, weights, ids,
-                                static_cast<cudaStream_t>(stream));
+                                RowPlanOut{}, static_cast<cudaStream_t>(stream));
     if (extra_id >= 0) return fail(B200Q_EUNSUPPORTED, "router_topk: an appended expert needs n <= 1024");
     router_topk_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, n, k, renormalize, floor_value,
                                                                             weights, ids);
     return check_launch("router_topk");
+}
+
+int b200q_router_topk_plan_row(const float *logits, int n, int k, int renormalize, float floor_value, int extra_id,
+                               const float *extra_weight, float *weights, int64_t *ids, int e, int32_t *counts,
+                               int32_t *offsets, int32_t *order, int32_t *inv, int32_t *seg_expert, int32_t *seg_begin,
+                               int32_t *seg_count, int32_t *num_segments, int max_segments, int32_t *status,
+                               void *stream) {
+    if (!logits || !weights || !ids || !counts || !offsets || !order || !inv || !seg_expert || !seg_begin ||
+        !seg_count || !num_segments || !status)
+        return fail(B200Q_EINVAL, "router_topk_plan_row: NULL pointer");
+    if (n < 1 || n > 1024 || k < 1 || k > 31 || k > n)
+        return fail(B200Q_EINVAL, "router_topk_plan_row: need 1<=n<=1024, 1<=k<=min(31,n)");
+    if (renormalize && !(floor_value > 0.0f)) return fail(B200Q_EINVAL, "router_topk_plan_row: floor must be positive");
+    const int top = extra_id >= 0 ? (extra_id >= n ? extra_id + 1 : n) : n;      // ids run up to max(n - 1, extra_id)
+    if (e < top || e > PLAN_MAX_EXPERTS || max_segments < 1 || (extra_id >= 0 && extra_id < n))
+        return fail(B200Q_EINVAL, "router_topk_plan_row: the plan must cover every id; an appended id lies above n");
+    RowPlanOut plan{counts, offsets, order, inv, seg_expert, seg_begin, seg_count, num_segments, status, e, max_segments};
+    return launch_topk_warp(logits, 1, n, k, renormalize, floor_value, extra_id, extra_weight, weights, ids, plan,
+                            static_cast<cudaStream_t>(stream));
 }
 
 int b200q_router_topk(const float *logits, int rows, int n, int k, int renormalize, float floor_value,

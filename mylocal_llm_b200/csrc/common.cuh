@@ -89,6 +89,15 @@ inline cudaError_t launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, d
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Routing-plan outputs the top-k kernel fills itself when it routes a single row (order == nullptr:
+// none). For one row the plan is a sort of k distinct ids, so the separate plan launch of a
+// one-token decode step is saved; the arrays are those of b200q_moe_plan.
+struct RowPlanOut {
+    int32_t *counts, *offsets, *order, *inv, *seg_expert, *seg_begin, *seg_count, *num_segments, *status;
+    int e;                 // experts of the plan (counts has e entries, offsets e + 1)
+    int max_segments;
+};
+
 // ---------------------------------------------------------------------------------------------
 // Small device utilities
 // ---------------------------------------------------------------------------------------------

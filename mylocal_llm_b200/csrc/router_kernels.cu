@@ -191,7 +191,7 @@ __device__ __forceinline__ float from_orderable_bits(uint32_t h) {
 __global__ void __launch_bounds__(128) router_topk_block_kernel(const float *logits, int n, int k, int renorm,
                                                                 float floor_value, int extra_id,
                                                                 const float *extra_weight, float *weights,
-                                                                int64_t *ids) {
+                                                                int64_t *ids, const RowPlanOut plan) {
     chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
     chain_wait();         // inputs come from preceding kernels
     __shared__ unsigned long long warp_best[2][4];
@@ -273,12 +273,43 @@ __global__ void __launch_bounds__(128) router_topk_block_kernel(const float *log
         ids[static_cast<size_t>(row) * k_out + k] = extra_id;
         weights[static_cast<size_t>(row) * k_out + k] = extra_weight ? extra_weight[row] : 1.0f;
     }
+    if (plan.order != nullptr) {
+        // Single row (grid of one CTA): the routing plan of its k_out distinct ids. Position of an
+        // assignment = number of smaller ids; one segment of one row per selected expert, ascending.
+        auto id_of = [&](int j) { return j < k ? sel_i[j] : extra_id; };
+        if (tid < k_out) {
+            const int mine = id_of(tid);
+            int pos = 0;
+            for (int j = 0; j < k_out; ++j) pos += id_of(j) < mine;
+            plan.order[pos] = tid;
+            plan.inv[tid] = pos;
+            if (pos < plan.max_segments) {
+                plan.seg_expert[pos] = mine;
+                plan.seg_begin[pos] = pos;
+                plan.seg_count[pos] = 1;
+            }
+        }
+        for (int ex = tid; ex <= plan.e; ex += 128) {
+            int below = 0, hit = 0;
+            for (int j = 0; j < k_out; ++j) {
+                below += id_of(j) < ex;
+                hit += id_of(j) == ex;
+            }
+            plan.offsets[ex] = below;
+            if (ex < plan.e) plan.counts[ex] = hit;
+        }
+        if (tid == 0) {
+            plan.num_segments[0] = min(k_out, plan.max_segments);
+            plan.status[0] = k_out > plan.max_segments ? 2 : 0;
+        }
+    }
 }
 
 int launch_topk_warp(const float *logits, int rows, int n, int k, int renorm, float floor_value, int extra_id,
-                     const float *extra_weight, float *weights, int64_t *ids, cudaStream_t stream) {
+                     const float *extra_weight, float *weights, int64_t *ids, const RowPlanOut &plan,
+                     cudaStream_t stream) {
     launch_chained(router_topk_block_kernel, dim3(rows), dim3(128), 0, stream, logits, n, k, renorm, floor_value,
-                   extra_id, extra_weight, weights, ids);
+                   extra_id, extra_weight, weights, ids, plan);
     return check_launch("router_topk");
 }
 

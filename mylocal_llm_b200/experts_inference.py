@@ -133,7 +133,7 @@ class PackedExpertBank:
 
 
 def routed_experts_forward(x2d, weights2d, ids2d, bank, *, extra=None, extra_scale=None, out_dtype=None,
-                           tables=None, tables_aligned16=False, n_experts=None, residual_norm=None):
+                           tables=None, tables_aligned16=False, n_experts=None, residual_norm=None, plan=None):
     """plan -> grouped gate/up -> grouped down (route-weighted) -> ordered combine.
 
     x2d [T,D]; weights2d FP32 [T,k]; ids2d int32/int64 [T,k]; returns [T,D]. With ``tables`` (from
@@ -143,7 +143,8 @@ def routed_experts_forward(x2d, weights2d, ids2d, bank, *, extra=None, extra_sca
     the result is ``(new residual, normalised activations)`` (``moe_ops.moe_combine_norm``).
     """
     torch = _torch()
-    plan = moe_ops.moe_plan(ids2d, n_experts or bank.n_experts)
+    if plan is None:                      # a caller that routed a single row may bring the plan along
+        plan = moe_ops.moe_plan(ids2d, n_experts or bank.n_experts)
     route = weights2d if weights2d.dtype == torch.float32 else weights2d.float()
     if tables is not None:
         hbuf = moe_ops.moe_gate_up(x2d, plan, None, None, bank.gate_type, bank.up_type, bank.d_ff, bank.d_model, 0, 0,

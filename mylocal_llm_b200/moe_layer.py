@@ -16,6 +16,7 @@ layer also accepts BF16/FP16 (accumulation stays FP32, the output is rounded onc
 """
 
 import ctypes
+import os
 
 from . import _lib, moe_ops
 from .experts_inference import ExpertsInference, PackedExpertBank, ResidentExpertExecutor
@@ -131,6 +132,8 @@ class PackedMoELayer:
         # A shared expert with the routed experts' shape and formats runs through the grouped kernels
         # as expert id E (the highest id, hence added last), addressed through pointer tables.
         self._tables = None
+        # B200Q_FUSE_PLAN=0: separate top-k and plan launches for a one-row step as well
+        self.fuse_row_plan = os.environ.get("B200Q_FUSE_PLAN", "1") != "0"
         if shared is not None and all(
                 w.shape == ref_shape and w.quant_type == ref_type for w, ref_shape, ref_type in zip(
                     shared, ((bank.d_ff, bank.d_model), (bank.d_ff, bank.d_model), (bank.d_model, bank.d_ff)),
@@ -178,9 +181,17 @@ class PackedMoELayer:
         logits = self.router.logits(x2d)
         if self._tables is not None:
             scale = moe_ops.shared_gate(x2d, self.shared_gate) if self.shared_gate is not None else None
-            weights, ids = moe_ops.router_topk(logits, self.router.k, renormalize=True,
-                                               floor=self.router.normalization_floor,
-                                               extra_id=self.bank.n_experts, extra_weight=scale)
+            if (x2d.shape[0] == 1 and self.fuse_row_plan and isinstance(self.executor, ResidentExpertExecutor)
+                    and self.bank.n_experts <= 1024 and self.router.k <= 31):
+                # one token: the top-k kernel writes the routing plan itself (one launch fewer)
+                weights, ids, plan = moe_ops.router_topk_plan_row(
+                    logits, self.router.k, self.bank.n_experts + 1, renormalize=True,
+                    floor=self.router.normalization_floor, extra_id=self.bank.n_experts, extra_weight=scale)
+                fused = dict(fused, plan=plan)
+            else:
+                weights, ids = moe_ops.router_topk(logits, self.router.k, renormalize=True,
+                                                   floor=self.router.normalization_floor,
+                                                   extra_id=self.bank.n_experts, extra_weight=scale)
             tables, aligned = self._tables
             out = self.executor.forward_routed(self.layer_id, x2d, weights, ids, out_dtype=hidden.dtype,
                                                tables=tables, tables_aligned16=aligned,

@@ -130,6 +130,30 @@ def moe_plan(ids, n_experts, *, skip_expert=-1):
     return plan
 
 
+def router_topk_plan_row(logits2d, k, n_experts, *, renormalize=True, floor=2.0 ** -14, extra_id=-1, extra_weight=None):
+    """``router_topk`` and ``moe_plan`` of a single token row in one launch: returns ``(weights [1,k'],
+    ids [1,k'], plan)`` with the same contents as the two calls (one-token decode step)."""
+    torch = _torch()
+    if logits2d.dtype != torch.float32 or not logits2d.is_contiguous() or logits2d.shape[0] != 1:
+        raise ValueError("logits must be a contiguous FP32 tensor of one row")
+    e = logits2d.shape[1]
+    k_out = int(k) + (1 if extra_id >= 0 else 0)
+    weights = torch.empty((1, k_out), dtype=torch.float32, device=logits2d.device)
+    ids = torch.empty((1, k_out), dtype=torch.int64, device=logits2d.device)
+    max_seg = max_segments_for(1, k_out, n_experts)
+    i32 = dict(dtype=torch.int32, device=logits2d.device)
+    plan = DeviceRoutingPlan(
+        1, k_out, n_experts,
+        torch.empty(n_experts, **i32), torch.empty(n_experts + 1, **i32), torch.empty(k_out, **i32),
+        torch.empty(k_out, **i32), torch.empty(max_seg, **i32), torch.empty(max_seg, **i32),
+        torch.empty(max_seg, **i32), torch.empty(1, **i32), max_seg, torch.empty(1, **i32))
+    _lib.call("b200q_router_topk_plan_row", _ptr(logits2d), e, int(k), 1 if renormalize else 0, float(floor),
+              int(extra_id), _ptr(extra_weight), _ptr(weights), _ptr(ids), int(n_experts), _ptr(plan.counts),
+              _ptr(plan.offsets), _ptr(plan.order), _ptr(plan.inv), _ptr(plan.seg_expert), _ptr(plan.seg_begin),
+              _ptr(plan.seg_count), _ptr(plan.num_segments), max_seg, _ptr(plan.status), _lib.current_stream())
+    return weights, ids, plan
+
+
 def moe_gate_up(x2d, plan, gate_bank, up_bank, gate_fmt, up_fmt, f, d, gate_stride, up_stride, *,
                 gate_table=None, up_table=None, tables_aligned16=False):
     """FP32 hidden activations ``[T*k, F]`` in sorted-assignment order.
