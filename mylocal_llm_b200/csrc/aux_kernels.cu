@@ -65,11 +65,34 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const void *x, int x_dtype
     __shared__ float inv_shared;
     const size_t base = static_cast<size_t>(blockIdx.x) * d;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // Rows of up to 256 * KEEP columns stay in registers between the two passes (with their gamma
+    // values, requested together with the row), so nothing is loaded after the reduction.
+    constexpr int KEEP = 16;
+    const bool in_regs = d <= 256 * KEEP;
+    float kept[KEEP], gam[KEEP];
     float ss = 0.f;
-    for (int c = tid; c < d; c += 256) {
-        float v = load_as_float(x, x_dtype, base + c);
-        if (RESIDUAL) v = residual[base + c] + alpha * v;
-        ss += v * v;
+    if (in_regs) {
+#pragma unroll
+        for (int i = 0; i < KEEP; ++i) {
+            const int c = tid + 256 * i;
+            kept[i] = 0.f;
+            gam[i] = 0.f;
+            if (c < d) {
+                float v = load_as_float(x, x_dtype, base + c);
+                if (RESIDUAL) v = residual[base + c] + alpha * v;
+                kept[i] = v;
+                gam[i] = load_as_float(gamma, gamma_dtype, c);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < KEEP; ++i)
+            if (tid + 256 * i < d) ss += kept[i] * kept[i];
+    } else {
+        for (int c = tid; c < d; c += 256) {
+            float v = load_as_float(x, x_dtype, base + c);
+            if (RESIDUAL) v = residual[base + c] + alpha * v;
+            ss += v * v;
+        }
     }
     ss = warp_sum(ss);
     if (lane == 0) warp_sums[warp] = ss;
@@ -81,6 +104,17 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const void *x, int x_dtype
     }
     __syncthreads();
     const float inv = inv_shared;
+    if (in_regs) {
+#pragma unroll
+        for (int i = 0; i < KEEP; ++i) {
+            const int c = tid + 256 * i;
+            if (c < d) {
+                if (RESIDUAL) res_out[base + c] = kept[i];
+                store_from_float(y, y_dtype, base + c, (kept[i] * inv) * gam[i]);
+            }
+        }
+        return;
+    }
     for (int c = tid; c < d; c += 256) {
         float v = load_as_float(x, x_dtype, base + c);
         if (RESIDUAL) {
