@@ -16,10 +16,12 @@ bytes of one launch over its own CUDA-event duration. ``dense_gemv`` adds a shor
 dense decode GEMVs of the second configuration (the other half of the metric); the ``gemv_*``
 workloads run those as the main measurement instead.
 
-With N > 1 (launched by torchrun, one rank per GPU) the MoE workloads run expert-parallel: the experts
-of every layer are sharded over the ranks, each rank brings its own 64 (or ``tokens``) rows per step
-(weak scaling in tokens), rows and expert terms are exchanged through peer memory (``--exchange
-collective`` uses NCCL instead), and ``value`` is the tokens of all ranks over the slowest rank's time.
+With N > 1 (launched by torchrun, one rank per GPU) the MoE workloads run expert-parallel with the
+baseline's batch: the experts of every layer AND the 64 (or ``tokens``) rows of a step are split over the
+ranks (strong scaling; a rank may hold no row at all), rows and expert terms are exchanged through peer
+memory (``--exchange collective`` uses NCCL instead), ``value`` is the step's tokens over the slowest
+rank's time, ``parity_checked`` says whether a 2-layer expert-parallel stack reproduced the single-GPU
+stack bit for bit on this run's GPUs, and ``ep_breakdown_us_per_layer_rank0`` splits a layer into phases.
 The dense GEMV workloads do not shard: N independent replicas, no collective. ``--impl reference``
 times the reference's own CPU kernels (oracle/_ref, else the plain-C port) on the host cores instead.
 """
@@ -458,38 +460,99 @@ def exit_watchdog(seconds=90):
 # ------------------------------------------------------------------------------ MoE workloads
 MOE_SHAPE = dict(d_model=2048, d_ff=512, n_experts=512, top_k=10, shared_d_ff=512)
 EXPERT_BYTES = 2 * packed_bytes("Q4_K", 512, 2048) + packed_bytes("Q6_K", 2048, 512)
-# DRAM traffic of the grouped gate/up kernel over its algorithmic bytes, from one ncu capture of the 64-token
-# layer (448.3 MB moved for 430.2 MB); traffic grows in proportion to the experts a launch touches.
+# DRAM traffic of the grouped gate/up kernel over its algorithmic bytes in one ncu capture of the 64-token
+# single-GPU layer (448.3 MB moved for 430.2 MB); other token counts and rank counts were not captured.
 GATE_UP_TRAFFIC_RATIO = 1.04
 
 
-def cpu_moe_throughput(layers, seconds):
-    """Reference CPU expert FFN (one token, Q4_K/Q4_K/Q6_K, D=2048, F=512) over all host threads;
-    returns decode tokens/s of a `layers`-deep stack: each token needs (top_k + 1) expert FFNs per layer."""
-    from oracle import build_oracle as bo
-    from mylocal_llm_b200.quantize import random_packed
-    handle = bo.load_ref()
-    kind = "reference"
-    if handle is None:
-        handle, kind = bo.load_port(), "port"
-    d, f = MOE_SHAPE["d_model"], MOE_SHAPE["d_ff"]
-    trip = [random_packed(q, sh, seed=i, d=1 / 2048, dmin=1 / 4096)
-            for i, (q, sh) in enumerate((("Q4_K", (f, d)), ("Q4_K", (f, d)), ("Q6_K", (d, f))))]
-    x = np.random.default_rng(0).normal(0, 1, (1, d)).astype(np.float32)
-    threads = cpu_threads()
-    from concurrent.futures import ThreadPoolExecutor
-    pool = ThreadPoolExecutor(threads)
-    work = lambda _: bo.cpu_expert(handle, (trip[0].data, "Q4_K"), (trip[1].data, "Q4_K"), (trip[2].data, "Q6_K"), d, f, x)
-    list(pool.map(work, range(threads)))
-    calls, t0 = 0, time.perf_counter()
-    while time.perf_counter() - t0 < seconds:
-        list(pool.map(work, range(threads * 4)))
-        calls += threads * 4
-    elapsed = time.perf_counter() - t0
-    pool.shutdown()
-    per_token = layers * (MOE_SHAPE["top_k"] + 1)
-    sample = f"{calls} single-token expert FFNs (Q4_K/Q4_K/Q6_K, D={d}, F={f}) in {elapsed:.1f} s"
-    return calls / elapsed / per_token, kind, threads, sample
+def split_rows(tokens, world, rank):
+    """Rows of a `tokens`-row batch that rank `rank` is home of, and the slot every rank reserves."""
+    base, rem = divmod(tokens, world)
+    return base + (1 if rank < rem else 0), base + (1 if rem else 0)
+
+
+def moe_config(name, world, exchange):
+    """Workload description shared by the GPU arm and the CPU reference arm (identical keys and values)."""
+    layers, tokens, chained = MOE_WORKLOADS[name]
+    touched = (min(512, 10 * tokens) + 1) * EXPERT_BYTES * layers / 1e9
+    return {"workload": name, "layers": layers, "tokens_per_step": tokens, "chained": chained, **MOE_SHAPE,
+            "formats": "Q4_K gate/up, Q6_K down", "activation": "bfloat16, FP32 residual",
+            "parallelism": f"expert-parallel ep{world}: {MOE_SHAPE['n_experts'] // world} experts per rank, the "
+                           f"{tokens} tokens of a step split over the ranks" if world > 1 else "single GPU",
+            "l2": f"inputs larger than L2: {layers} distinct layers per step, up to {touched:.1f} GB of packed "
+                  f"experts touched per step"}
+
+
+class CpuMoeSample:
+    """The reference's CPU path for one token through one MoE layer, on rotating weights.
+
+    Router logits (FP32 NumPy), softmax / top-k / renormalisation and the ascending-expert ordered FP32
+    sum are the oracle's restatement of the reference's RouterInference + ExpertsInference; the expert
+    FFNs are the reference's own C++ kernel (oracle/_ref, else the plain-C port), top_k + 1 calls per
+    token spread over the host threads. `n_rot` distinct experts (> 0.5 GB of packed bytes, more than the
+    host's last-level cache) are visited round-robin so the weights stream from DRAM as they would in a
+    512-expert layer."""
+
+    def __init__(self, n_rot=288):
+        from oracle import build_oracle as bo
+        from mylocal_llm_b200.quantize import random_packed
+        self.bo = bo
+        self.handle, self.kind = bo.load_ref(), "reference"
+        if self.handle is None:
+            self.handle, self.kind = bo.load_port(), "port"
+        self.d, self.f, self.k = MOE_SHAPE["d_model"], MOE_SHAPE["d_ff"], MOE_SHAPE["top_k"]
+        d, f = self.d, self.f
+        banks = [random_packed(q, (n_rot,) + sh, seed=i, d=1 / 2048, dmin=1 / 4096)
+                 for i, (q, sh) in enumerate((("Q4_K", (f, d)), ("Q4_K", (f, d)), ("Q6_K", (d, f))))]
+        self.banks = [b.data.reshape(n_rot, -1) for b in banks]
+        self.n_rot = n_rot
+        rng = np.random.default_rng(0)
+        self.router = rng.normal(0, 0.02, (d, MOE_SHAPE["n_experts"])).astype(np.float32)
+        self.x = rng.normal(0, 1, (64, d)).astype(np.float32)
+        self.threads = cpu_threads()
+        from concurrent.futures import ThreadPoolExecutor
+        self.pool = ThreadPoolExecutor(self.threads)
+        self.cursor = 0
+
+    def token_layer(self, t):
+        from oracle import packed_oracle as po
+        x = self.x[t % len(self.x)][None]
+        weights, ids = po.router_topk_rows_fp32(x @ self.router, self.k, 2.0 ** -14)
+        order = np.argsort(ids[0], kind="stable")
+        slots = [(self.cursor + j) % self.n_rot for j in range(self.k + 1)]       # k routed + the shared expert
+        self.cursor = (self.cursor + self.k + 1) % self.n_rot
+        run = lambda e: self.bo.cpu_expert(self.handle, (self.banks[0][e], "Q4_K"), (self.banks[1][e], "Q4_K"),
+                                           (self.banks[2][e], "Q6_K"), self.d, self.f, x)
+        outs = list(self.pool.map(run, slots))
+        y = np.zeros((1, self.d), np.float32)
+        for j in order:                                     # ascending expert id, plain FP32 adds
+            y = (y + (outs[j] * weights[0, j]).astype(np.float32)).astype(np.float32)
+        return (y + outs[self.k]).astype(np.float32)
+
+    def run(self, seconds):
+        n, t0 = 0, time.perf_counter()
+        while time.perf_counter() - t0 < seconds:
+            self.token_layer(n)
+            n += 1
+        return n, time.perf_counter() - t0
+
+    def close(self):
+        self.pool.shutdown()
+
+
+def cpu_moe_throughput(layers, seconds, sampler=None):
+    """Decode tokens/s of a `layers`-deep stack on the host cores, extrapolated from `seconds` of
+    token-layer passes (one pass = router + top_k + 1 expert FFNs + ordered sum for one token)."""
+    own = sampler is None
+    sampler = sampler or CpuMoeSample()
+    sampler.run(0.2)                                        # warm-up
+    n, elapsed = sampler.run(seconds)
+    if own:
+        sampler.close()
+    sample = (f"{n} token-layer passes (router, top-{sampler.k}, {sampler.k + 1} expert FFNs Q4_K/Q4_K/Q6_K "
+              f"D={sampler.d} F={sampler.f} rotating over {sampler.n_rot} distinct experts, ordered sum) in {elapsed:.1f} s; "
+              f"a token of the {layers}-layer stack needs {layers} passes")
+    return n / elapsed / layers, sampler.kind, sampler.threads, sample, n
 
 
 def run_moe_reference_arm(args, name):
@@ -498,20 +561,130 @@ def run_moe_reference_arm(args, name):
         return
     eff_layers = layers if chained else 1
     per_step = max(1.0, 20.0 / max(1, args.steps + args.warmup))
-    runs = [cpu_moe_throughput(eff_layers, per_step) for _ in range(args.warmup + args.steps)][args.warmup:]
+    sampler = CpuMoeSample()
+    runs = [cpu_moe_throughput(eff_layers, per_step, sampler) for _ in range(args.warmup + args.steps)][args.warmup:]
+    sampler.close()
     tps = statistics.mean(r[0] for r in runs)
+    passes = sum(r[4] for r in runs)
+    needed = eff_layers * tokens * args.steps
     line = {
         "impl": "reference", "metric": "MoE decode tokens/s", "value": round(tps, 4), "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * tokens / tps, 3),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "layers": eff_layers, "tokens_per_step": tokens, **MOE_SHAPE,
-                   "formats": "Q4_K gate/up, Q6_K down", "l2": "CPU run; each step is a bounded sample of expert FFNs"},
+        "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": moe_config(name, args.gpus, args.exchange),
+        "extrapolated": True,
+        "sampled": {"token_layer_passes_timed": passes, "token_layer_passes_in_the_full_steps": needed,
+                    "fraction": round(passes / needed, 6),
+                    "note": "ms_per_step is tokens_per_step / value, not a timed full step: each step times a "
+                            "bounded sample of token-layer passes"},
         "cpu_baseline": {"value": round(tps, 4), "unit": "tokens/s", "cores": runs[0][2], "kind": runs[0][1],
                          "sample": runs[0][3]},
         "e2e": {"value": round(tps, 4), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+def graph_time(torch, stream, fn, replays, warm=3):
+    """Capture fn() in a CUDA graph on `stream`; returns (ms per replay, graph, captured result)."""
+    fn()
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        out = fn()
+    for _ in range(warm):
+        graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(replays):
+        graph.replay()
+    e1.record(stream)
+    stream.synchronize()
+    return e0.elapsed_time(e1) / replays, graph, out
+
+
+def batch1_side_numbers(torch, stream, stack):
+    """Batch-1 decode, the first term of the metric, next to the main number: the 48-layer MoE stack at one
+    token (on the resident stack) and the Q8_0 Llama decoder of the third configuration after a 512-token
+    prompt. Whole-step HBM fraction = packed bytes a step must read / step time / measured copy peak."""
+    from mylocal_llm_b200.llama_model import ExternalLlamaConfig, ExternalLlamaModel
+    peak, _ = measured_peaks()
+    out = {}
+    x1 = torch.randn((1, 1, MOE_SHAPE["d_model"]), device="cuda")
+    ms, graph, _ = graph_time(torch, stream, lambda: stack.forward(x1)[0], replays=30)
+    graph.reset()
+    step_bytes = len(stack.layers) * ((MOE_SHAPE["top_k"] + 1) * EXPERT_BYTES + 4 * 2048 * 512)
+    out["moe_stack_b1"] = {"tokens/s": round(1e3 / ms, 1), "ms_per_step": round(ms, 4), "layers": len(stack.layers),
+                           "step_bytes": step_bytes, "frac_of_peak": round(step_bytes / (ms * 1e-3) / 1e9 / peak, 4)}
+    model = ExternalLlamaModel.synthetic(ExternalLlamaConfig(**LLAMA_SHAPE), seed=0)
+    state = model.create_generation_state(1, LLAMA_PROMPT + 256)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(5)
+    prompt = torch.randint(0, LLAMA_SHAPE["vocab_size"], (1, LLAMA_PROMPT), device="cuda", generator=gen)
+    token = model.prefill(prompt, state).argmax(dim=-1)
+    step = lambda: token.copy_(model.decode_one(token, state).argmax(dim=-1))
+    ms, graph, _ = graph_time(torch, stream, step, replays=64)
+    graph.reset()
+    out["llama_decode_b1"] = {"tokens/s": round(1e3 / ms, 1), "ms_per_step": round(ms, 4),
+                              "step_bytes": llama_bytes_per_step(),
+                              "frac_of_peak": round(llama_bytes_per_step() / (ms * 1e-3) / 1e9 / peak, 4),
+                              "context": f"{LLAMA_PROMPT}-token prompt, positions {LLAMA_PROMPT}..{LLAMA_PROMPT + 70}"}
+    del model, state
+    torch.cuda.empty_cache()
+    return out
+
+
+def ep_parity_check(torch, dist, comm, tokens, rank, world):
+    """Outside the timed region: a 2-layer expert-parallel stack built from the slices of full banks must
+    return, for this rank's rows, the bits of the single-GPU stack built from the same banks."""
+    from mylocal_llm_b200.expert_parallel import ExpertParallelMoEStack
+    from mylocal_llm_b200.moe_stack import PackedMoEStack
+    stack = PackedMoEStack.synthetic(2, seed=321, keep_native=True, **MOE_SHAPE)
+    twin = ExpertParallelMoEStack.sharded_from(stack, stack.native_banks, comm)
+    x = torch.from_numpy(np.random.default_rng(99).normal(0, 1, (1, tokens, MOE_SHAPE["d_model"])).astype(np.float32)).cuda()
+    want_res, want_hidden = stack.forward(x)
+    rows, slot = split_rows(tokens, world, rank)
+    lo = sum(split_rows(tokens, world, r)[0] for r in range(rank))
+    mine = x[:, lo:lo + rows].contiguous()
+    ok = True
+    for _ in range(2):
+        res, hidden = twin.forward(mine, slot_rows=slot)
+        ok = ok and torch.equal(res, want_res[:, lo:lo + rows]) and torch.equal(hidden, want_hidden[:, lo:lo + rows])
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    del stack, twin
+    torch.cuda.empty_cache()
+    return bool(flag.item())
+
+
+def ep_breakdown(torch, stream, step_fn, layers):
+    """Eager per-phase CUDA-event times of the expert-parallel layers on this rank, averaged over layers
+    (microseconds). "push" and "barrier" include the wait for the slowest rank."""
+    from mylocal_llm_b200 import expert_parallel as ep
+    marks = []
+
+    def hook(name):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(stream)
+        marks.append((name, ev))
+
+    totals = {}
+    for rep in range(3):
+        marks.clear()
+        ep.PHASE_HOOK = hook
+        hook("start")
+        step_fn()
+        ep.PHASE_HOOK = None
+        stream.synchronize()
+        if rep == 0:
+            continue                                        # first eager pass: warm-up
+        prev = marks[0][1]
+        for name, ev in marks[1:]:
+            # "route" closes the stretch since the previous layer's combine: residual add + RMSNorm, then routing
+            key = "norm+route" if name == "route" else name
+            totals[key] = totals.get(key, 0.0) + prev.elapsed_time(ev) * 1e3
+            prev = ev
+    return {k: round(v / (2 * layers), 2) for k, v in totals.items()}
 
 
 def run_moe_gpu_arm(args, name):
@@ -530,30 +703,32 @@ def run_moe_gpu_arm(args, name):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     side = gemv_side_numbers(SIDE_GEMVS) if rank == 0 and not args.skip_side else None
-    comm = None
+    comm, parity = None, None
+    rows, slot = split_rows(tokens, world, rank)
     if world > 1:
-        # expert-parallel: experts sharded over the ranks, `tokens` rows per rank (weak scaling in tokens)
+        # expert-parallel, strong scaling: the experts AND the `tokens` rows of a step are split over the ranks
         from mylocal_llm_b200.expert_parallel import CollectiveComm, ExpertParallelMoEStack, PeerComm
         if args.exchange == "peer":
-            comm = PeerComm(None, max_rows=tokens, d_model=MOE_SHAPE["d_model"], k_out=MOE_SHAPE["top_k"] + 1)
+            comm = PeerComm(None, max_rows=slot, d_model=MOE_SHAPE["d_model"], k_out=MOE_SHAPE["top_k"] + 1)
         else:
             comm = CollectiveComm()
+        parity = ep_parity_check(torch, dist, comm, tokens, rank, world)
         stack = ExpertParallelMoEStack.synthetic(layers, comm, seed=0, **MOE_SHAPE)
     else:
         stack = PackedMoEStack.synthetic(layers, seed=0, **MOE_SHAPE)
     d = MOE_SHAPE["d_model"]
     rng = np.random.default_rng(11 + rank)
-    host_x = torch.from_numpy(rng.normal(0, 1, (1, tokens, d)).astype(np.float32)).pin_memory()
+    host_x = torch.from_numpy(rng.normal(0, 1, (1, rows, d)).astype(np.float32)).pin_memory()
     dev_x = host_x.cuda()
-    host_y = torch.empty((1, tokens, d), dtype=torch.float32).pin_memory()
+    host_y = torch.empty((1, rows, d), dtype=torch.float32).pin_memory()
 
     def step_fn():
         if chained:
-            return stack.forward(dev_x)[0]
+            return stack.forward(dev_x, slot)[0] if world > 1 else stack.forward(dev_x)[0]
         outs = None
         hidden = dev_x.to(torch.bfloat16)
         for layer in stack.layers:                       # independent layers: distinct weights defeat L2
-            outs = layer.forward(hidden)
+            outs = layer.forward(hidden, slot) if world > 1 else layer.forward(hidden)
         return outs.float()
 
     stream = torch.cuda.Stream()
@@ -634,6 +809,10 @@ def run_moe_gpu_arm(args, name):
         executed = [c[:-1] if world > 1 else c for _, _, c in records]
         distinct = [int((c > 0).sum().item()) for c in executed]
         assignments = [int(c.sum().item()) for c in executed]
+        breakdown = ep_breakdown(torch, stream, step_fn, layers) if world > 1 else None
+        batch1 = None
+        if world == 1 and rank == 0 and chained and not args.skip_side:
+            batch1 = batch1_side_numbers(torch, stream, stack)
 
     times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -644,45 +823,53 @@ def run_moe_gpu_arm(args, name):
 
     if rank == 0:
         tokens_per_step = tokens * (1 if chained else layers)
-        value = tokens_per_step * world * args.steps / (dev_ms * 1e-3)
-        e2e_value = tokens_per_step * world * args.steps / (e2e_ms * 1e-3)
+        value = tokens_per_step * args.steps / (dev_ms * 1e-3)
+        e2e_value = tokens_per_step * args.steps / (e2e_ms * 1e-3)
         peak, peak_kind = measured_peaks()
-        gu_bytes = statistics.mean(distinct) * 2 * packed_bytes("Q4_K", 512, 2048) + world * tokens * d * 2 \
+        gu_bytes = statistics.mean(distinct) * 2 * packed_bytes("Q4_K", 512, 2048) + world * slot * d * 2 \
             + statistics.mean(assignments) * 512 * 4
         gu_us = statistics.mean(gate_up_ms) * 1e3
         achieved = gu_bytes / (gu_us * 1e-6) / 1e9
-        layer_bytes = statistics.mean(distinct) * EXPERT_BYTES + EXPERT_BYTES + 4 * 2048 * 512 + 2 * tokens * d * 2
+        # bytes this rank's layer must read: its distinct experts, shared expert, router weights, activations
+        layer_bytes = statistics.mean(distinct) * EXPERT_BYTES + (EXPERT_BYTES if world > 1 else 0) \
+            + 4 * 2048 * 512 + 2 * tokens * d * 2
+        single = world == 1 and tokens == 64
         line = {
             "metric": "MoE decode tokens/s", "value": round(value, 2), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 5),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": name, "layers": layers, "tokens_per_step": tokens, "chained": chained, **MOE_SHAPE,
-                       "formats": "Q4_K gate/up, Q6_K down", "activation": "bfloat16, FP32 residual",
-                       "packed_bytes_resident": stack.packed_bytes,
-                       "parallelism": (f"expert-parallel ep{world}: {MOE_SHAPE['n_experts'] // world} experts per rank, "
-                                       f"{tokens} tokens per rank, exchange={args.exchange}") if world > 1
-                       else "single GPU",
-                       "l2": f"{layers} distinct layers per step, {layer_bytes * layers / 1e6:.0f} MB touched per step",
-                       "timing": "CUDA graph of one step, CUDA events on the launch stream",
-                       "distinct_experts_per_layer": round(statistics.mean(distinct), 1),
-                       "algorithmic_bytes_per_layer": int(layer_bytes),
-                       "layer_GBs": round(layer_bytes * layers * args.steps / (dev_ms * 1e-3) / 1e9, 1)},
+            "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": moe_config(name, world, args.exchange),
+            "details": {"packed_bytes_resident_rank0": stack.packed_bytes, "exchange": args.exchange if world > 1 else None,
+                        "rows_rank0": rows, "slot_rows": slot,
+                        "timing": "CUDA graph of one step, CUDA events on the launch stream, max over ranks",
+                        "distinct_experts_per_layer_rank0": round(statistics.mean(distinct), 1),
+                        "assignments_per_layer_rank0": round(statistics.mean(assignments), 1),
+                        "algorithmic_bytes_per_layer_rank0": int(layer_bytes),
+                        "layer_GBs_rank0": round(layer_bytes * layers * args.steps / (dev_ms * 1e-3) / 1e9, 1)},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_source": f"of {peak_kind}",
                          "frac_of_nominal_8TBs": round(achieved / 8000.0, 4),
-                         "traffic": int(gu_bytes * GATE_UP_TRAFFIC_RATIO),
-                         "traffic_source": "dram bytes read+write / algorithmic bytes = 1.04 in the ncu capture "
-                                           "profiles/grouped_kernels_moe_layer_t64.md, scaled to this launch",
+                         "traffic": int(gu_bytes * GATE_UP_TRAFFIC_RATIO) if single else None,
+                         "traffic_source": ("dram bytes read+write / algorithmic bytes = 1.04 in an ncu capture of this "
+                                            "kernel on the 64-token single-GPU layer, scaled to this launch") if single
+                         else "not captured for this token / rank count",
                          "kernel": "grouped gate/up + SwiGLU (mma_direct_kernel, mode 2)",
                          "us_per_launch": round(gu_us, 3), "algorithmic_bytes_per_launch": int(gu_bytes)},
             "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s",
                     "h2d_bytes_per_step": int(host_x.numel() * 4), "d2h_bytes_per_step": int(host_y.numel() * 4)},
             "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
         }
+        if world > 1:
+            line["parity_checked"] = parity
+            line["parity_check"] = ("2-layer expert-parallel stack vs the single-GPU stack built from the same banks, "
+                                    "bit-identical on every rank's rows, outside the timed region")
+            line["ep_breakdown_us_per_layer_rank0"] = breakdown
         if side is not None:
             line["dense_gemv"] = side
+        if batch1 is not None:
+            line["batch1_decode"] = batch1
         if world == 1 and not args.skip_cpu_baseline:
-            tps, kind, cores, sample = cpu_moe_throughput(layers if chained else 1, 12.0)
+            tps, kind, cores, sample, _ = cpu_moe_throughput(layers if chained else 1, 12.0)
             line["cpu_baseline"] = {"value": round(tps, 4), "unit": "tokens/s", "cores": cores, "kind": kind,
                                     "sample": sample}
         print(json.dumps(line))

@@ -232,11 +232,14 @@ int b200q_q6k_untile(const void *tiled, void *native, int64_t rows, int k, void 
 /* Rotate-half RoPE of q (in place, FP32 [B,T,H,Dh]) and k, and store of rotated k and v (FP32
  * [B,T,Hkv,Dh]) into the caches [B,Hkv,horizon,Dh] (cache_dtype) at positions[t] (device int64 [T]);
  * *_row_stride = elements between consecutive (b,t) rows (q, k, v may be column slices of one fused
- * projection output); cos/sin tables are FP32 [max_pos, Dh/2] with theta_i = pos / base^(2i/Dh). */
+ * projection output); cos/sin tables are FP32 [table_rows, Dh/2] with theta_i = pos / base^(2i/Dh).
+ * The positions are read on the device (a captured step advances them between replays), so the
+ * kernel checks them itself: a position outside [0, min(horizon, table_rows)) reads no table entry,
+ * leaves q and the caches as they are and stores 301 in the device status word. */
 int b200q_rope_kv_store(float *q, const float *k, const float *v, int64_t q_row_stride, int64_t k_row_stride,
                         int64_t v_row_stride, const int64_t *positions, const float *cos_table,
-                        const float *sin_table, int batch, int t, int heads, int kv_heads, int head_dim, int horizon,
-                        void *k_cache, void *v_cache, int cache_dtype, void *stream);
+                        const float *sin_table, int table_rows, int batch, int t, int heads, int kv_heads,
+                        int head_dim, int horizon, void *k_cache, void *v_cache, int cache_dtype, void *stream);
 
 /* act[m, f] = silu(gu[m, f]) * gu[m, F + f] for a stacked gate|up projection output gu [M, 2F] FP32
  * (the epilogue of b200q_swiglu as a separate step, for weights whose tile layout has no fused
@@ -257,7 +260,8 @@ int b200q_decode_attention(const float *q, int64_t q_row_stride, const void *k_c
  * Global ids first_expert..first_expert+n_local-1 become local experts 0..n_local-1; shared_id
  * (< 0: none) becomes local expert n_local for rows home_lo..home_hi-1 (the rows this rank is home
  * of); everything else is sorted last and gets no segment. counts/offsets have n_local+2 (+1)
- * entries. Ids outside [0, e_global) set *status = 1. */
+ * entries. The id e_global itself marks a padding entry (rows a rank did not fill in its slot of
+ * the gathered ids): it is legal and never executed. Ids outside [0, e_global] set *status = 1. */
 int b200q_moe_plan_ep(const void *ids, int ids_is_i64, int rows, int k, int e_global, int first_expert, int n_local,
                       int shared_id, int home_lo, int home_hi, int seg_cap, int32_t *counts, int32_t *offsets,
                       int32_t *order, int32_t *inv, int32_t *seg_expert, int32_t *seg_begin, int32_t *seg_count,

@@ -47,17 +47,8 @@ def needs_build():
     return any(p.stat().st_mtime > stamp for p in _sources() + _headers())
 
 
-def build(force=False, verbose=False, defines=(), lib_path=None):
-    """Compile and link; returns the library path.
-
-    ``defines`` (e.g. ``["B200Q_CVT_MODE=1"]``) and ``lib_path`` build a variant library elsewhere,
-    for A/B measurements; the default call builds the in-tree ``libb200q.so``.
-    """
-    global LIB, OBJ_DIR
-    if lib_path is not None:
-        LIB = Path(lib_path)
-        OBJ_DIR = LIB.parent / "obj"
-        force = True
+def build(force=False, verbose=False):
+    """Compile and link the in-tree ``libb200q.so``; returns its path."""
     if not force and not needs_build():
         return LIB
     nvcc = _nvcc()
@@ -69,7 +60,7 @@ def build(force=False, verbose=False, defines=(), lib_path=None):
         if (not force and obj.exists() and obj.stat().st_mtime >= src.stat().st_mtime
                 and obj.stat().st_mtime >= header_stamp):
             return obj, ""
-        cmd = [nvcc, *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode:
             raise RuntimeError(f"nvcc failed for {src.name}:\n{proc.stderr[-4000:]}")
@@ -91,6 +82,4 @@ def build(force=False, verbose=False, defines=(), lib_path=None):
 
 
 if __name__ == "__main__":
-    _defines = [a[2:] for a in sys.argv[1:] if a.startswith("-D")]
-    _out = next((a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--out=")), None)
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, defines=_defines, lib_path=_out))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -12,14 +12,16 @@ namespace b200q {
 
 // q [B, T, H, Dh], k / v [B, T, Hkv, Dh] FP32, each with its own element stride between (b, t)
 // rows (so they may be column slices of one fused projection output); positions [T] (device);
-// cos / sin [max_pos, Dh/2]. q is rotated in place; rotated k and plain v go to
-// cache[b, hkv, positions[t], :].
+// cos / sin [table_rows, Dh/2]. q is rotated in place; rotated k and plain v go to
+// cache[b, hkv, positions[t], :]. A position outside [0, min(horizon, table_rows)) touches nothing
+// (no table read, q left as it is, no cache store) and records STATUS_POSITION_RANGE: a captured
+// step replayed past the end of the cache must not read past the end of the tables.
 __global__ void __launch_bounds__(256) rope_kv_store_kernel(float *q, const float *k, const float *v, long long q_row,
                                                             long long k_row, long long v_row,
                                                             const long long *positions, const float *cos_t,
-                                                            const float *sin_t, int b, int t, int h, int hkv, int dh,
-                                                            int horizon, void *k_cache, void *v_cache,
-                                                            int cache_dtype) {
+                                                            const float *sin_t, int table_rows, int b, int t, int h,
+                                                            int hkv, int dh, int horizon, void *k_cache,
+                                                            void *v_cache, int cache_dtype, int *status) {
     chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
     chain_wait();         // inputs come from preceding kernels
     const int half = dh >> 1;
@@ -33,6 +35,10 @@ __global__ void __launch_bounds__(256) rope_kv_store_kernel(float *q, const floa
         const int tt = static_cast<int>(rest % t);
         const int bb = static_cast<int>(rest / t);
         const long long pos = positions[tt];
+        if (pos < 0 || pos >= horizon || pos >= table_rows) {
+            if (i == 0 && head == 0) atomicExch(status, STATUS_POSITION_RANGE);
+            continue;
+        }
         if (head < h) {
             float *p = q + (static_cast<size_t>(bb) * t + tt) * q_row + static_cast<size_t>(head) * dh;
             const float c = cos_t[pos * half + i], s = sin_t[pos * half + i];
@@ -45,18 +51,14 @@ __global__ void __launch_bounds__(256) rope_kv_store_kernel(float *q, const floa
             const float c = cos_t[pos * half + i], s = sin_t[pos * half + i];
             const float x0 = p[i], x1 = p[half + i];
             const size_t dst = ((static_cast<size_t>(bb) * hkv + kh) * horizon + pos) * dh;
-            if (pos >= 0 && pos < horizon) {
-                store_from_float(k_cache, cache_dtype, dst + i, x0 * c - x1 * s);
-                store_from_float(k_cache, cache_dtype, dst + half + i, x0 * s + x1 * c);
-            }
+            store_from_float(k_cache, cache_dtype, dst + i, x0 * c - x1 * s);
+            store_from_float(k_cache, cache_dtype, dst + half + i, x0 * s + x1 * c);
         } else {
             const int vh = head - h - hkv;
             const float *p = v + (static_cast<size_t>(bb) * t + tt) * v_row + static_cast<size_t>(vh) * dh;
             const size_t dst = ((static_cast<size_t>(bb) * hkv + vh) * horizon + pos) * dh;
-            if (pos >= 0 && pos < horizon) {
-                store_from_float(v_cache, cache_dtype, dst + i, p[i]);
-                store_from_float(v_cache, cache_dtype, dst + half + i, p[half + i]);
-            }
+            store_from_float(v_cache, cache_dtype, dst + i, p[i]);
+            store_from_float(v_cache, cache_dtype, dst + half + i, p[half + i]);
         }
     }
 }
@@ -258,12 +260,12 @@ extern "C" {
 
 int b200q_rope_kv_store(float *q, const float *k, const float *v, int64_t q_row_stride, int64_t k_row_stride,
                         int64_t v_row_stride, const int64_t *positions, const float *cos_table,
-                        const float *sin_table, int batch, int t, int heads, int kv_heads, int head_dim, int horizon,
-                        void *k_cache, void *v_cache, int cache_dtype, void *stream) {
+                        const float *sin_table, int table_rows, int batch, int t, int heads, int kv_heads,
+                        int head_dim, int horizon, void *k_cache, void *v_cache, int cache_dtype, void *stream) {
     if (!q || !k || !v || !positions || !cos_table || !sin_table || !k_cache || !v_cache)
         return fail(B200Q_EINVAL, "rope_kv_store: NULL pointer");
     if (batch <= 0 || t <= 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || head_dim % 2 || horizon <= 0 ||
-        !dtype_valid(cache_dtype) || q_row_stride < static_cast<int64_t>(heads) * head_dim ||
+        table_rows <= 0 || !dtype_valid(cache_dtype) || q_row_stride < static_cast<int64_t>(heads) * head_dim ||
         k_row_stride < static_cast<int64_t>(kv_heads) * head_dim ||
         v_row_stride < static_cast<int64_t>(kv_heads) * head_dim)
         return fail(B200Q_EINVAL, "rope_kv_store: bad argument");
@@ -271,7 +273,8 @@ int b200q_rope_kv_store(float *q, const float *k, const float *v, int64_t q_row_
     const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 4096));
     launch_chained(rope_kv_store_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), q, k, v,
                    q_row_stride, k_row_stride, v_row_stride, reinterpret_cast<const long long *>(positions), cos_table,
-                   sin_table, batch, t, heads, kv_heads, head_dim, horizon, k_cache, v_cache, cache_dtype);
+                   sin_table, table_rows, batch, t, heads, kv_heads, head_dim, horizon, k_cache, v_cache, cache_dtype,
+                   device_status_word());
     return check_launch("rope_kv_store");
 }
 

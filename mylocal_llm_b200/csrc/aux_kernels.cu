@@ -448,9 +448,11 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const void *ids,
         long long v = ids_is_i64 ? static_cast<const long long *>(ids)[i]
                                  : static_cast<long long>(static_cast<const int *>(ids)[i]);
         if (map.enabled) {
-            if (v < 0 || v >= map.e_global) { bad = 1; v = map.first; }
+            // v == e_global: a padding entry (a rank that brought fewer rows than its slot) - nobody runs it
+            if (v < 0 || v > map.e_global) { bad = 1; v = map.first; }
             const int row = i / map.k;
-            if (v >= map.first && v < map.first + map.n_local) v -= map.first;
+            if (v == map.e_global) v = map.n_local + 1;
+            else if (v >= map.first && v < map.first + map.n_local) v -= map.first;
             else if (v == map.shared_id && row >= map.home_lo && row < map.home_hi) v = map.n_local;
             else v = map.n_local + 1;
         } else if (v < 0 || v >= e) { bad = 1; v = 0; }

@@ -33,6 +33,7 @@ int check_launch(const char *what);
 int *device_status_word();
 constexpr int STATUS_WAIT_FULL = 101;   // consumer gave up waiting for a staged tile
 constexpr int STATUS_WAIT_EMPTY = 102;  // producer gave up waiting for a free stage
+constexpr int STATUS_POSITION_RANGE = 301;  // a decode position lay outside the cache or the RoPE tables
 
 constexpr int NUM_SMS_FALLBACK = 148;
 int sm_count();

@@ -25,42 +25,20 @@ namespace b200q {
 constexpr int SLICE_K = 2048;
 constexpr int XREGS = 64;
 
-#ifndef B200Q_CVT_MODE
-#define B200Q_CVT_MODE 0
-#endif
-
 // Four unsigned bytes of `w` -> four floats (exact).
 __device__ __forceinline__ void cvt_u8x4(uint32_t w, float &f0, float &f1, float &f2, float &f3) {
-#if B200Q_CVT_MODE == 0
     f0 = static_cast<float>(w & 0xffu);
     f1 = static_cast<float>((w >> 8) & 0xffu);
     f2 = static_cast<float>((w >> 16) & 0xffu);
     f3 = static_cast<float>(w >> 24);
-#else
-    // byte -> low mantissa byte of 2^23, then subtract 2^23 (exact for 0..255)
-    const uint32_t magic = 0x4B000000u;
-    f0 = __uint_as_float(__byte_perm(w, magic, 0x7650)) - 8388608.0f;
-    f1 = __uint_as_float(__byte_perm(w, magic, 0x7651)) - 8388608.0f;
-    f2 = __uint_as_float(__byte_perm(w, magic, 0x7652)) - 8388608.0f;
-    f3 = __uint_as_float(__byte_perm(w, magic, 0x7653)) - 8388608.0f;
-#endif
 }
 
 // Four signed bytes of `w` -> four floats (exact).
 __device__ __forceinline__ void cvt_s8x4(uint32_t w, float &f0, float &f1, float &f2, float &f3) {
-#if B200Q_CVT_MODE == 0
     f0 = static_cast<float>(static_cast<int>(static_cast<int8_t>(w & 0xffu)));
     f1 = static_cast<float>(static_cast<int>(static_cast<int8_t>((w >> 8) & 0xffu)));
     f2 = static_cast<float>(static_cast<int>(static_cast<int8_t>((w >> 16) & 0xffu)));
     f3 = static_cast<float>(static_cast<int>(static_cast<int8_t>(w >> 24)));
-#else
-    const uint32_t magic = 0x4B000000u;
-    const uint32_t u = w ^ 0x80808080u;  // q + 128 in every byte
-    f0 = __uint_as_float(__byte_perm(u, magic, 0x7650)) - 8388736.0f;
-    f1 = __uint_as_float(__byte_perm(u, magic, 0x7651)) - 8388736.0f;
-    f2 = __uint_as_float(__byte_perm(u, magic, 0x7652)) - 8388736.0f;
-    f3 = __uint_as_float(__byte_perm(u, magic, 0x7653)) - 8388736.0f;
-#endif
 }
 
 // acc += (four codes of w as floats) . x[0..3], as two packed FMAs.

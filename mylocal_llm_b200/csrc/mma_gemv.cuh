@@ -663,11 +663,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_gemv_kernel(const MmaArgs a
                 return;
             }
             const int k0 = kt * kc + kpi * 256;
-#ifdef B200Q_MM_NO_COMPUTE   // measurement aid: stream the tiles, skip the arithmetic
-            if (false) {
-#else
             if (rows_live && k0 < a.k) {
-#endif
                 const uint8_t *stage = stage_base + static_cast<size_t>(s) * a.stage_bytes;
                 const int f0 = k0 >> 4;
                 {

@@ -23,8 +23,11 @@ static float *static_hidden_address() {
     static std::mutex mu;
     static float *ptrs[64] = {nullptr};
     int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    const cudaError_t dev_err = cudaGetDevice(&dev);
+    if (dev_err != cudaSuccess || dev < 0 || dev >= 64) {
         cudaGetLastError();
+        if (dev_err != cudaSuccess) set_error("expert_ffn_static: cudaGetDevice failed: %s", cudaGetErrorString(dev_err));
+        else set_error("expert_ffn_static: device ordinal %d is outside the 64 devices this entry point serves", dev);
         return nullptr;
     }
     std::lock_guard<std::mutex> lock(mu);
@@ -50,6 +53,22 @@ extern "C" int b200q_expert_ffn_static(const void *gate, int gate_fmt, const voi
                                        void *y, int y_dtype, void *stream) {
     if (!gate || !up || !down || !x || !y) return fail(B200Q_EINVAL, "expert_ffn_static: NULL pointer");
     if (m < 1 || d_ff < 1 || d_model < 1) return fail(B200Q_EINVAL, "expert_ffn_static: bad shape");
+    // everything the two inner calls would reject is checked here, so either both kernels launch or none
+    auto base_fmt = [](int fmt, bool swiglu_side) {
+        if (fmt == B200Q_Q4_K_TILED) return B200Q_Q4_K;
+        if (!swiglu_side && fmt == B200Q_Q6_K_TILED) return B200Q_Q6_K;
+        if (!swiglu_side && fmt == B200Q_Q8_0_TILED) return B200Q_Q8_0;
+        return fmt;
+    };
+    const int gf = base_fmt(gate_fmt, true), uf = base_fmt(up_fmt, true), df = base_fmt(down_fmt, false);
+    if (!fmt_valid(gf) || !fmt_valid(uf) || !fmt_valid(df)) return fail(B200Q_EINVAL, "expert_ffn_static: unknown format");
+    if ((gate_fmt == B200Q_Q4_K_TILED) != (up_fmt == B200Q_Q4_K_TILED))
+        return fail(B200Q_EINVAL, "expert_ffn_static: gate and up must share the layout");
+    if (!dtype_valid(x_dtype) || !dtype_valid(y_dtype)) return fail(B200Q_EINVAL, "expert_ffn_static: bad element type");
+    if (d_model % fmt_elems(gf) || d_model % fmt_elems(uf) || d_ff % fmt_elems(df))
+        return fail(B200Q_EINVAL, "expert_ffn_static: d_model / d_ff must be multiples of the formats' block size");
+    if ((gate_fmt != gf && (d_ff % 16 || d_model % 256)) || (down_fmt != df && (d_model % 16 || d_ff % 256)))
+        return fail(B200Q_EINVAL, "expert_ffn_static: a tile layout needs rows in multiples of 16 and K of 256");
     if (static_cast<long long>(m) * d_ff > B200Q_STATIC_FFN_MAX_FLOATS)
         return fail(B200Q_EUNSUPPORTED,
                     "expert_ffn_static: m*d_ff = %lld exceeds the built-in scratch of %d floats; use b200q_swiglu + "

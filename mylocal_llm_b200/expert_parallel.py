@@ -5,7 +5,7 @@ bit for bit, the single-GPU layer's (``moe_layer.PackedMoELayer``), whatever the
 
 * rank ``r`` of ``G`` owns the contiguous expert range ``expert_partition(E, G)[r]`` of every layer;
   router weights, shared expert and norms are replicated; tokens are data-parallel (every rank
-  brings the same number of rows per call);
+  reserves the same number of row slots per call and may fill fewer, down to none);
 * per layer: every rank routes its own rows -> rows, routing weights and expert ids of all ranks are
   gathered on every rank -> each rank runs the assignments that hit its experts (plus the shared
   expert for its own rows) ->
@@ -33,6 +33,17 @@ from . import _lib
 def _torch():
     import torch
     return torch
+
+
+# Optional callable(name): called between the phases of a layer ("route", "push", "plan", "gate_up", "down",
+# "barrier", "combine") after the phase's launches are issued. A benchmark sets it to record CUDA events;
+# it stays None in normal use.
+PHASE_HOOK = None
+
+
+def _phase(name):
+    if PHASE_HOOK is not None:
+        PHASE_HOOK(name)
 
 
 def expert_partition(n_experts, world):
@@ -270,6 +281,8 @@ class DeviceExpertEngine:
         self.folded = bool(same)
         self.tables, self.aligned = bank.pointer_tables(extra=shared if self.folded else None)
         self.k_out = int(top_k) + (1 if self.folded else 0)
+        # one past the last global id (the folded shared expert included): padding entry of the exchange
+        self.pad_id = self.n_global + (1 if self.folded else 0)
 
     def route(self, x_all):
         from . import moe_ops
@@ -289,17 +302,21 @@ class DeviceExpertEngine:
         plan = moe_ops.moe_plan_ep(ids, e_global=self.n_global + (1 if self.folded else 0),
                                    first_expert=self.first_expert, n_local=bank.n_experts,
                                    shared_id=self.n_global if self.folded else -1, home_lo=home_lo, home_hi=home_hi)
+        _phase("plan")
         hbuf = moe_ops.moe_gate_up(x_all, plan, None, None, bank.gate_type, bank.up_type, bank.d_ff, bank.d_model, 0, 0,
                                    gate_table=self.tables[0], up_table=self.tables[1], tables_aligned16=self.aligned)
+        _phase("gate_up")
         route = (weights if weights.dtype == torch.float32 else weights.float()).contiguous().reshape(-1)
         if peer is not None:
             moe_ops.moe_down_peer(hbuf, route, plan, bank.down_type, bank.d_model, bank.d_ff,
                                   down_table=self.tables[2], tables_aligned16=self.aligned, term_tables=peer[0],
                                   rows_per_rank=peer[1])
+            _phase("down")
             return None
         terms = torch.zeros((ids.shape[0] * ids.shape[1], bank.d_model), dtype=torch.float32, device=x_all.device)
         moe_ops.moe_down(hbuf, route, plan, None, bank.down_type, bank.d_model, bank.d_ff, 0,
                          down_table=self.tables[2], tables_aligned16=self.aligned, flat_rows=True, out=terms)
+        _phase("down")
         return terms
 
     def combine(self, terms_home, ids_home, x_home, out_dtype):
@@ -326,31 +343,74 @@ class ExpertParallelMoELayer:
 
     def __init__(self, engine, comm, d_model):
         self.engine, self.comm, self.d_model = engine, comm, int(d_model)
+        self._empty_slots = {}
 
-    def forward(self, hidden):
-        """hidden [B, T, D] (this rank's rows; same B*T on every rank) -> [B, T, D]."""
+    def forward(self, hidden, slot_rows=None):
+        """hidden [B, T, D] (this rank's rows) -> [B, T, D].
+
+        ``slot_rows`` = rows every rank reserves in the exchange, the same number on every rank and at
+        least this rank's ``B*T`` (default: ``B*T``, i.e. every rank brings the same number of rows).
+        A rank with fewer rows - none at all is allowed, as ``[1, 0, D]`` - fills the rest of its slot
+        with padding entries that no rank executes, so a batch that does not divide by the number of
+        ranks (one token on eight GPUs) costs only the experts its real rows select."""
         if hidden.ndim != 3 or hidden.shape[-1] != self.d_model:
             raise ValueError("hidden must have shape [batch,time,d_model]")
         batch, seq, d = hidden.shape
         rows = batch * seq
-        if rows == 0:
+        slot = rows if slot_rows is None else int(slot_rows)
+        if slot < rows:
+            raise ValueError("slot_rows must cover this rank's rows")
+        if slot == 0:
             return hidden.clone()
         x2d = hidden.reshape(rows, d)
         if not x2d.is_contiguous():
             x2d = x2d.contiguous()
         comm, engine = self.comm, self.engine
-        x_all, weights, ids = comm.gather_routed(x2d, *engine.route(x2d))
-        home_lo, home_hi = comm.rank * rows, (comm.rank + 1) * rows
-        rows_per_rank = rows * engine.k_out
+        weights = ids = None
+        if rows:
+            weights, ids = engine.route(x2d)
+        _phase("route")
+        x_slot, w_slot, ids_slot = self._fill_slot(x2d, weights, ids, rows, slot)
+        x_all, w_all, ids_all = comm.gather_routed(x_slot, w_slot, ids_slot)
+        _phase("push")
+        home_lo, home_hi = comm.rank * slot, comm.rank * slot + rows
+        rows_per_rank = slot * engine.k_out
         if comm.peer:
-            table, terms_home = comm.term_buffers(rows, engine.k_out, d)
-            engine.local_terms(x_all, weights, ids, home_lo, home_hi, peer=(table, rows_per_rank))
+            table, terms_home = comm.term_buffers(slot, engine.k_out, d)
+            engine.local_terms(x_all, w_all, ids_all, home_lo, home_hi, peer=(table, rows_per_rank))
             comm.barrier()
         else:
-            terms_all = engine.local_terms(x_all, weights, ids, home_lo, home_hi)
+            terms_all = engine.local_terms(x_all, w_all, ids_all, home_lo, home_hi)
             terms_home = comm.exchange_terms(terms_all, rows_per_rank)
-        out = engine.combine(terms_home, ids[home_lo:home_hi], x2d, hidden.dtype)
+        _phase("barrier")
+        if not rows:
+            return hidden.clone()
+        # the ids this rank routed itself, not the gathered copy: peers may already be writing the next
+        # call's entries into the arena while this combine runs
+        out = engine.combine(terms_home[:rows * engine.k_out], ids, x2d, hidden.dtype)
+        _phase("combine")
         return out.reshape(batch, seq, d)
+
+    def _fill_slot(self, x2d, weights, ids, rows, slot):
+        """This rank's slot of the exchange: its rows, then padding (zero rows, zero weights, the id
+        ``engine.pad_id`` that no rank executes)."""
+        if rows == slot:
+            return x2d, weights, ids
+        torch = _torch()
+        key = (slot, x2d.dtype, x2d.device)
+        if rows == 0 and key in self._empty_slots:
+            return self._empty_slots[key]
+        k_out, d = self.engine.k_out, self.d_model
+        x_slot = torch.zeros((slot, d), dtype=x2d.dtype, device=x2d.device)
+        w_slot = torch.zeros((slot, k_out), dtype=torch.float32, device=x2d.device)
+        ids_slot = torch.full((slot, k_out), self.engine.pad_id, dtype=torch.int64, device=x2d.device)
+        if rows:
+            x_slot[:rows] = x2d
+            w_slot[:rows] = weights
+            ids_slot[:rows] = ids
+        else:
+            self._empty_slots[key] = (x_slot, w_slot, ids_slot)
+        return x_slot, w_slot, ids_slot
 
 
 def shard_bank(bank, rank, world):
@@ -381,14 +441,31 @@ class ExpertParallelMoEStack:
                 total += sum(w.nbytes for w in layer.engine.shared)
         return total
 
-    def forward(self, residual):
+    def forward(self, residual, slot_rows=None):
+        """residual FP32 [B, T, D] (this rank's rows, possibly none) -> (new residual, normalised
+        activations); ``slot_rows`` as in ``ExpertParallelMoELayer.forward``."""
         res = residual
         hidden = self.norms[0].forward_residual(res)
         for i, layer in enumerate(self.layers):
-            branch = layer.forward(hidden)
+            branch = layer.forward(hidden, slot_rows)
             norm = self.norms[i + 1] if i + 1 < len(self.layers) else self.final_norm
             res, hidden = norm.forward_residual_add(res, branch)
         return res, hidden
+
+    @classmethod
+    def sharded_from(cls, stack, native_banks, comm):
+        """Expert-parallel twin of a single-GPU ``PackedMoEStack``: the same router weights, shared
+        experts and norms, and this rank's slice of every layer's full bank (``native_banks``: the
+        banks in GGUF layout the stack was built from). Its outputs equal the stack's bit for bit."""
+        layers = []
+        for layer, bank in zip(stack.layers, native_banks):
+            first, local = shard_bank(bank, comm.rank, comm.world)
+            engine = DeviceExpertEngine(local, layer.router.W_router, layer.router.k, first_expert=first,
+                                        n_experts_global=bank.n_experts, shared=layer.shared_native,
+                                        shared_gate=layer.shared_gate,
+                                        normalization_floor=layer.router.normalization_floor)
+            layers.append(ExpertParallelMoELayer(engine, comm, bank.d_model))
+        return cls(layers, stack.norms, stack.final_norm)
 
     @classmethod
     def synthetic(cls, n_layers, comm, *, d_model=2048, d_ff=512, n_experts=512, top_k=10, shared_d_ff=512,

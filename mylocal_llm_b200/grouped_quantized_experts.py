@@ -13,7 +13,7 @@ import numpy as np
 
 from . import moe_ops
 from .quantized_linear import DevicePackedGGUFWeight, PackedExpertFFNInference
-from .quantized_weight import BLOCK_FORMATS
+from .quantized_weight import block_format
 
 MAX_GROUPED_EXPERTS = 64
 
@@ -59,7 +59,7 @@ def _unsupported_reason(x, experts, routing_weights, block_k, routing_slots=None
             return "all experts must share per-projection shapes and quantization formats"
         signature = current
         for w in projections:
-            qk, qb = BLOCK_FORMATS[w.quant_type]
+            qk, qb = block_format(w.quant_type)       # GGUF bytes or a device tile layout of them
             if (w.data.dtype != torch.uint8 or not w.data.is_contiguous() or w.shape[1] % qk
                     or int(w.data.numel()) != w.shape[0] * w.shape[1] // qk * qb):
                 return "invalid packed projection storage or block alignment"

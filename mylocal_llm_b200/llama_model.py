@@ -241,7 +241,8 @@ class ExternalLlamaModel:
                 ptr = lambda x: ctypes.c_void_p(x.data_ptr())
                 cache_id = _lib.DTYPE_ID[str(self.dtype).replace("torch.", "")]
                 _lib.call("b200q_rope_kv_store", ptr(q2), ptr(k2), ptr(v2), q2.stride(0), k2.stride(0), v2.stride(0),
-                          ptr(positions), ptr(self._cos), ptr(self._sin), b, 1, heads, kv_heads, dh, state.horizon,
+                          ptr(positions), ptr(self._cos), ptr(self._sin), int(self._cos.shape[0]), b, 1, heads, kv_heads, dh,
+                          state.horizon,
                           ptr(state.k[i]), ptr(state.v[i]), cache_id, _lib.current_stream())
                 ctx = torch.empty((b, heads * dh), dtype=self.dtype, device=hidden.device)
                 _lib.call("b200q_decode_attention", ptr(q2), q2.stride(0), ptr(state.k[i]), ptr(state.v[i]), cache_id,

@@ -107,6 +107,7 @@ class PackedMoELayer:
         (gate, up, down) DevicePackedGGUFWeight triple; shared_gate: optional FP32 [D] vector."""
         if not isinstance(bank, PackedExpertBank):
             raise TypeError("bank must be a PackedExpertBank")
+        self.shared_native = shared          # as given, before any conversion to a tile layout
         if retile_enabled() and executor is None:
             # Q6_K down projections are re-ordered once into the tile layout the fast kernel reads
             bank = bank.retiled()

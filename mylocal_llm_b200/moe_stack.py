@@ -40,28 +40,37 @@ class PackedMoEStack:
                 total += sum(w.nbytes for w in layer.shared)
         return total
 
-    def forward(self, residual):
-        """residual FP32 [B, T, D] -> (new residual FP32, final normalised activations)."""
+    def forward(self, residual, trace=None):
+        """residual FP32 [B, T, D] -> (new residual FP32, final normalised activations). ``trace``: a list
+        that receives, per layer, ``(layer input, layer output)`` - the tensors a layer-by-layer check
+        against a reference needs; it forces the two-kernel combine + norm."""
         res = residual
         hidden = self.norms[0].forward_residual(res)
         for i, layer in enumerate(self.layers):
             norm = self.norms[i + 1] if i + 1 < len(self.layers) else self.final_norm
-            if self.fuse_residual_norm and layer.can_fuse_residual_norm():
+            if trace is None and self.fuse_residual_norm and layer.can_fuse_residual_norm():
                 res, hidden = layer.forward(hidden, residual_norm=(norm, res))
             else:
-                res, hidden = norm.forward_residual_add(res, layer.forward(hidden))
+                branch = layer.forward(hidden)
+                if trace is not None:
+                    trace.append((hidden, branch))
+                res, hidden = norm.forward_residual_add(res, branch)
         return res, hidden
 
     @classmethod
     def synthetic(cls, n_layers, *, d_model=2048, d_ff=512, n_experts=512, top_k=10, shared_d_ff=512,
-                  types=("Q4_K", "Q4_K", "Q6_K"), act_dtype=None, seed=0, eps=1e-5, device="cuda"):
-        """Random-init stack with the benchmark shape; weights are generated on the device."""
+                  types=("Q4_K", "Q4_K", "Q6_K"), act_dtype=None, seed=0, eps=1e-5, device="cuda", keep_native=False):
+        """Random-init stack with the benchmark shape; weights are generated on the device.
+        ``keep_native`` keeps the banks in GGUF layout as ``stack.native_banks`` (the layers convert
+        theirs to the tile layouts), e.g. to shard the same weights over several ranks."""
         torch = _torch()
         act_dtype = act_dtype or torch.bfloat16
         gen = torch.Generator(device=device)
-        layers, norms = [], []
+        layers, norms, native = [], [], []
         for i in range(n_layers):
             bank = synthetic_bank(n_experts, d_model, d_ff, types, seed=seed * 1000 + i, device=device)
+            if keep_native:
+                native.append(bank)
             gen.manual_seed(seed * 1000 + i)
             w_router = torch.empty((d_model, n_experts), dtype=torch.float32, device=device)
             w_router.normal_(0.0, 0.02, generator=gen)
@@ -78,4 +87,6 @@ class PackedMoEStack:
             norms.append(norm)
         final = RMSNormInference(d_model, eps=eps)
         final.set_weights(torch.ones(d_model, dtype=act_dtype, device=device))
-        return cls(layers, norms, final)
+        stack = cls(layers, norms, final)
+        stack.native_banks = native
+        return stack

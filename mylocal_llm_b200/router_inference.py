@@ -87,8 +87,9 @@ class RouterInference:
         self._w_expert_major = None if value is None else value.t().contiguous()
 
     def set_expert_major_weight(self, weight_t):
-        """Use an ``[n_experts, d_model]`` weight directly (the orientation stored in GGUF files)."""
-        self._w = None
+        """Use an ``[n_experts, d_model]`` weight directly (the orientation stored in GGUF files). The
+        expert-major kernel reads four columns per load; other widths keep a ``[d_model, n_experts]`` copy."""
+        self._w = None if weight_t.shape[1] % 4 == 0 else weight_t.t().contiguous()
         self._w_expert_major = weight_t
 
     def set_weights(self, router):

@@ -23,7 +23,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 PORT_SO = HERE / "_build" / "libpacked_oracle.so"
 REF_SO = HERE / "_ref" / "libref_packed_cpu.so"
-REFERENCE_ROOT = Path(os.environ.get("MYLOCAL_REFERENCE_ROOT", "/root/reference"))
+# the reference checkout: MYLOCAL_REFERENCE_ROOT, else a directory named "reference" beside this repository
+REFERENCE_ROOT = Path(os.environ.get("MYLOCAL_REFERENCE_ROOT") or HERE.parent.parent / "reference")
 REFERENCE_CPP = REFERENCE_ROOT / "mini_llm" / "ops" / "native_packed_cpu.cpp"
 
 FORMAT_ID = {"Q8_0": 0, "Q4_K": 2, "Q5_K": 4, "Q6_K": 5}
@@ -114,6 +115,22 @@ def load_ref():
                 expert.restype = ctypes.c_int
                 _LIBS["ref"] = (lib, gemv, expert)
         return _LIBS["ref"]
+
+
+def port_dequantize(data, shape, fmt):
+    """Bit-exact dequantisation by the plain-C port (pinned against the NumPy oracle and the reference's
+    golden vectors in tests/test_oracle_golden.py); about 20x faster than the NumPy loops, which is
+    what makes FP64 checks of whole 512-expert layers affordable."""
+    import numpy as np
+    lib, _, _ = load_port()
+    raw = np.ascontiguousarray(data, dtype=np.uint8).reshape(-1)
+    k = int(shape[-1])
+    n = int(np.prod(shape[:-1], dtype=np.int64))
+    out = np.empty((n, k), np.float32)
+    rc = lib.oracle_dequantize(raw.ctypes.data, FORMAT_ID[fmt], n, k, out.ctypes.data)
+    if rc:
+        raise RuntimeError(f"oracle_dequantize rc={rc}")
+    return out.reshape(shape)
 
 
 def cpu_gemv(handle, data, fmt, n, k, x):

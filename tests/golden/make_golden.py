@@ -27,7 +27,7 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REFERENCE = Path(os.environ.get("MYLOCAL_REFERENCE_ROOT", "/root/reference"))
+REFERENCE = Path(os.environ.get("MYLOCAL_REFERENCE_ROOT") or REPO.parent / "reference")
 
 os.environ["MINI_LLM_BACKEND"] = "numpy"
 os.environ.setdefault("MINI_LLM_NATIVE_BUILD_DIR", tempfile.mkdtemp(prefix="ref_native_"))

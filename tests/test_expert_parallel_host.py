@@ -52,6 +52,7 @@ class NumpyEngine:
         self.experts, self.router = experts, router
         self.first, self.count, self.n_global = first, count, n_global
         self.k_out = K + 1
+        self.pad_id = n_global + 1          # padding entries of a partly filled slot: nobody executes them
 
     def route(self, x_all):
         x = x_all.float().numpy()
@@ -113,20 +114,24 @@ def _free_port():
         return s.getsockname()[1]
 
 
-CASES = [(6, 3, "float32"), (7, 1, "float32"), (6, 4, "bfloat16")]     # experts, rows per rank, dtype
+# experts, rows of (rank 0, rank 1), dtype; consecutive cases change the row count on purpose, and the
+# unequal ones (a batch that does not divide by the ranks, a rank without rows) use padded slots
+CASES = [(6, (3, 3), "float32"), (7, (1, 1), "float32"), (6, (4, 4), "bfloat16"), (6, (2, 1), "float32"),
+         (7, (1, 0), "float32"), (6, (0, 3), "bfloat16"), (6, (3, 3), "float32")]
 
 
 def _rank_main(rank, world, port, queue):
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     try:
         comm = CollectiveComm()
-        for case, (n_experts, rows, dtype_name) in enumerate(CASES):
+        for case, (n_experts, counts, dtype_name) in enumerate(CASES):
             experts, router = _model(n_experts)
             first, count = expert_partition(n_experts, world)[rank]
             layer = ExpertParallelMoELayer(NumpyEngine(experts, router, first, count, n_experts), comm, D)
-            x_all = torch.from_numpy(_inputs(world, rows)).to(getattr(torch, dtype_name))
-            mine = x_all[rank * rows:(rank + 1) * rows]
-            out = layer.forward(mine[None].contiguous())[0]
+            x_all = torch.from_numpy(_inputs(1, sum(counts))).to(getattr(torch, dtype_name))
+            lo = sum(counts[:rank])
+            mine = x_all[lo:lo + counts[rank]].reshape(1, counts[rank], D)
+            out = layer.forward(mine.contiguous(), slot_rows=max(counts))[0]
             queue.put((case, rank, out.float().numpy()))
     finally:
         dist.destroy_process_group()
@@ -141,17 +146,21 @@ def test_two_gloo_ranks_reproduce_the_single_process_layer():
     for p in procs:
         p.start()
     results = {}
-    for _ in range(world * len(CASES)):
-        case, rank, out = queue.get(timeout=180)
-        results[case, rank] = out
-    for p in procs:
-        p.join(timeout=60)
-        assert p.exitcode == 0
-    for case, (n_experts, rows, dtype_name) in enumerate(CASES):
+    try:
+        for _ in range(world * len(CASES)):
+            case, rank, out = queue.get(timeout=180)
+            results[case, rank] = out
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.terminate()
+    assert all(p.exitcode == 0 for p in procs)
+    for case, (n_experts, counts, dtype_name) in enumerate(CASES):
         experts, router = _model(n_experts)
-        x_all = torch.from_numpy(_inputs(world, rows)).to(getattr(torch, dtype_name)).float().numpy()
+        x_all = torch.from_numpy(_inputs(1, sum(counts))).to(getattr(torch, dtype_name)).float().numpy()
         want = _single_process(experts, router, n_experts, x_all)
         if dtype_name == "bfloat16":
             want = torch.from_numpy(want).to(torch.bfloat16).float().numpy()
-        got = np.concatenate([results[case, r] for r in range(world)], axis=0)
-        assert np.array_equal(got, want), CASES[case]
+        got = np.concatenate([results[case, r].reshape(-1, D) for r in range(world)], axis=0)
+        assert got.shape == want.shape and np.array_equal(got, want), CASES[case]

@@ -77,3 +77,72 @@ def test_split_and_single_cta_shapes_agree(cuda, monkeypatch):
     np.testing.assert_allclose(split.cpu().numpy(), single.cpu().numpy(), rtol=1e-5, atol=1e-6)
     np.testing.assert_allclose(split.double().cpu().numpy(), reference(torch, q, k, v, 1400).cpu().numpy(), rtol=2e-4,
                                atol=2e-5)
+
+
+def run_rope(torch, q, k, v, positions, cos, sin, k_cache, v_cache):
+    batch, heads, dh = q.shape
+    kv_heads, horizon = k_cache.shape[1], k_cache.shape[2]
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    q2, k2, v2 = (a.reshape(batch, -1) for a in (q, k, v))
+    _lib.call("b200q_rope_kv_store", ptr(q2), ptr(k2), ptr(v2), q2.stride(0), k2.stride(0), v2.stride(0),
+              ptr(positions), ptr(cos), ptr(sin), int(cos.shape[0]), batch, 1, heads, kv_heads, dh, horizon,
+              ptr(k_cache), ptr(v_cache), _lib.DTYPE_ID[str(k_cache.dtype).replace("torch.", "")],
+              _lib.current_stream())
+    torch.cuda.synchronize()
+
+
+def rope_inputs(torch, table_rows, horizon, batch=2, heads=4, kv_heads=2, dh=64):
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(17)
+    q = torch.randn((batch, heads, dh), device="cuda", generator=gen)
+    k = torch.randn((batch, kv_heads, dh), device="cuda", generator=gen)
+    v = torch.randn((batch, kv_heads, dh), device="cuda", generator=gen)
+    inv = 10000.0 ** (-torch.arange(0, dh, 2, dtype=torch.float64) / dh)
+    ang = torch.arange(table_rows, dtype=torch.float64)[:, None] * inv[None, :]
+    cos, sin = ang.cos().float().cuda(), ang.sin().float().cuda()
+    k_cache = torch.full((batch, kv_heads, horizon, dh), 7.0, device="cuda")
+    v_cache = torch.full((batch, kv_heads, horizon, dh), 7.0, device="cuda")
+    return q, k, v, cos, sin, k_cache, v_cache
+
+
+def test_rope_store_rotates_and_writes_one_cache_row(cuda):
+    torch = cuda
+    q, k, v, cos, sin, k_cache, v_cache = rope_inputs(torch, table_rows=40, horizon=32)
+    pos = 9
+    rot = lambda x: torch.cat([x[..., :32] * cos[pos] - x[..., 32:] * sin[pos],
+                               x[..., :32] * sin[pos] + x[..., 32:] * cos[pos]], dim=-1)
+    q_ref, k_ref = rot(q.clone()), rot(k.clone())
+    run_rope(torch, q, k, v, torch.tensor([pos], dtype=torch.int64, device="cuda"), cos, sin, k_cache, v_cache)
+    np.testing.assert_allclose(q.cpu().numpy(), q_ref.cpu().numpy(), rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(k_cache[:, :, pos].cpu().numpy(), k_ref.cpu().numpy(), rtol=1e-6, atol=1e-6)
+    assert torch.equal(v_cache[:, :, pos], v)
+    untouched = torch.ones(32, dtype=torch.bool, device="cuda")
+    untouched[pos] = False
+    assert bool((k_cache[:, :, untouched] == 7.0).all()) and bool((v_cache[:, :, untouched] == 7.0).all())
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("pos,table_rows,horizon", [(32, 40, 32), (36, 36, 48), (-1, 40, 32)])
+def test_rope_store_skips_a_position_outside_cache_or_tables(cuda, pos, table_rows, horizon):
+    """A captured decode step advances its position on the device; replayed past the end it must not read
+    beyond the tables or write beyond the cache. Every address the kernel could form for the chosen
+    positions lies inside the buffers allocated here, so the test itself cannot fault."""
+    torch = cuda
+    q, k, v, cos, sin, k_cache, v_cache = rope_inputs(torch, table_rows=table_rows, horizon=horizon)
+    spare = torch.zeros((64, 32), device="cuda")                 # keeps table_rows an argument, not an allocation edge
+    cos_big, sin_big = torch.cat([cos, spare]), torch.cat([sin, spare])
+    q_before = q.clone()
+    _lib.clear_device_status()
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    q2, k2, v2 = (a.reshape(2, -1) for a in (q, k, v))
+    positions = torch.tensor([pos], dtype=torch.int64, device="cuda")
+    _lib.call("b200q_rope_kv_store", ptr(q2), ptr(k2), ptr(v2), q2.stride(0), k2.stride(0), v2.stride(0),
+              ptr(positions), ptr(cos_big), ptr(sin_big), table_rows, 2, 1, 4, 2, 64, horizon, ptr(k_cache),
+              ptr(v_cache), _lib.DTYPE_ID["float32"], _lib.current_stream())
+    torch.cuda.synchronize()
+    try:
+        assert _lib.device_status() == 301
+        assert torch.equal(q, q_before)
+        assert bool((k_cache == 7.0).all()) and bool((v_cache == 7.0).all())
+    finally:
+        _lib.clear_device_status()

@@ -117,7 +117,7 @@ def test_emulated_ranks_storing_into_home_buffers_equal_the_single_gpu_layer(cud
 
 def test_plan_ep_reports_ids_outside_the_global_range(cuda):
     from mylocal_llm_b200 import moe_ops
-    ids = cuda.tensor([[0, 3], [17, 1]], dtype=cuda.int64, device="cuda")
+    ids = cuda.tensor([[0, 3], [18, 1]], dtype=cuda.int64, device="cuda")
     plan = moe_ops.moe_plan_ep(ids, e_global=17, first_expert=0, n_local=8, shared_id=16, home_lo=0, home_hi=2)
     assert int(plan.status.item()) == 1
     plan = moe_ops.moe_plan_ep(ids.clamp(max=16), e_global=17, first_expert=0, n_local=8, shared_id=16, home_lo=0,
@@ -125,8 +125,54 @@ def test_plan_ep_reports_ids_outside_the_global_range(cuda):
     assert int(plan.status.item()) == 0
     # rows: [0, 3] local; [16 -> not home (row 1) -> skipped, 1 local]
     assert plan.counts.cpu().tolist() == [1, 1, 0, 1, 0, 0, 0, 0, 0, 1]
+    # the id e_global marks padding entries of a partly filled slot: legal, never executed, even on the home rank
+    padded = cuda.tensor([[2, 16], [17, 17]], dtype=cuda.int64, device="cuda")
+    plan = moe_ops.moe_plan_ep(padded, e_global=17, first_expert=0, n_local=8, shared_id=16, home_lo=0, home_hi=2)
+    assert int(plan.status.item()) == 0
+    assert plan.counts.cpu().tolist() == [0, 0, 1, 0, 0, 0, 0, 0, 1, 2]
+    assert int(plan.num_segments.item()) == 2
     with pytest.raises(ValueError):
         moe_ops.moe_plan_ep(ids, e_global=4, first_expert=0, n_local=8, shared_id=-1, home_lo=0, home_hi=2)
+
+
+@pytest.mark.parametrize("world,row_counts", [(2, (2, 1)), (4, (1, 0, 0, 0)), (4, (3, 3, 2, 2))])
+@pytest.mark.parametrize("variant", ["folded_gate", "no_shared"])
+def test_emulated_ranks_with_partly_filled_slots_equal_the_single_gpu_layer(cuda, world, row_counts, variant):
+    """A batch that does not divide by the number of ranks: every rank reserves the same slot, ranks with
+    fewer rows (or none) pad theirs with entries nobody executes."""
+    torch = cuda
+    bank, w_router, shared, gate = build_model(torch, shared_ff={"no_shared": 0}.get(variant, F),
+                                               with_gate=variant == "folded_gate", seed=5)
+    total_rows, slot = sum(row_counts), max(row_counts)
+    x_real = make_rows(torch, total_rows, torch.bfloat16, seed=9)
+    want = PackedMoELayer(bank, w_router, K, shared=shared, shared_gate=gate).forward(x_real[None])[0]
+    engines = engines_for(world, bank, w_router, shared, gate)
+    k_out = engines[0].k_out
+    starts = np.concatenate(([0], np.cumsum(row_counts)))
+    slots, routed = [], []
+    for rank, engine in enumerate(engines):
+        x_home = x_real[starts[rank]:starts[rank + 1]]
+        layer = ExpertParallelMoELayer(engine, LocalComm(), D)
+        w_r = ids_r = None
+        if row_counts[rank]:
+            w_r, ids_r = engine.route(x_home)
+        routed.append((x_home, ids_r))
+        slots.append(layer._fill_slot(x_home, w_r, ids_r, row_counts[rank], slot))
+    x_all, w_all, ids_all = (torch.cat([s[j] for s in slots]) for j in range(3))
+    total = None
+    for rank, engine in enumerate(engines):
+        terms = engine.local_terms(x_all, w_all, ids_all, rank * slot, rank * slot + row_counts[rank])
+        if total is not None:
+            assert not bool(((total != 0) & (terms != 0)).any())
+        total = terms if total is None else total + terms
+    got = []
+    for rank, engine in enumerate(engines):
+        x_home, ids_r = routed[rank]
+        if row_counts[rank]:
+            lo = rank * slot * k_out
+            got.append(engine.combine(total[lo:lo + row_counts[rank] * k_out], ids_r, x_home, torch.bfloat16))
+    assert torch.equal(torch.cat(got), want)
+    assert _lib.device_status() == 0
 
 
 def _free_port():
@@ -197,8 +243,9 @@ def _rank_main(rank, world, port, family, queue):
     os.environ["B200Q_RETILE"] = "1" if family == "auto" else "0"
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
+    import datetime
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
-                            device_id=torch.device("cuda", rank))
+                            device_id=torch.device("cuda", rank), timeout=datetime.timedelta(seconds=120))
     ok, note = True, ""
     try:
         bank, w_router, shared, gate = build_model(torch, with_gate=True, seed=11)
@@ -216,6 +263,17 @@ def _rank_main(rank, world, port, family, queue):
                     got = layer.forward(x_all[rank * rows:(rank + 1) * rows][None].contiguous())[0]
                     if not torch.equal(got, want):
                         ok, note = False, f"{name} rows={rows} differs"
+            # batches that do not divide by the number of ranks: (rows of rank 0, rows of rank 1), one slot size
+            for counts in ((2, 1), (1, 0), (5, 5), (0, 3)):
+                slot = max(counts)
+                x_real = make_rows(torch, sum(counts), torch.bfloat16, seed=40 + sum(counts))
+                lo = sum(counts[:rank])
+                mine = x_real[lo:lo + counts[rank]]
+                want = reference.forward(x_real[None])[0][lo:lo + counts[rank]]
+                for _ in range(2):
+                    got = layer.forward(mine.reshape(1, counts[rank], D).contiguous(), slot_rows=slot)[0]
+                    if tuple(got.shape) != (counts[rank], D) or not torch.equal(got, want):
+                        ok, note = False, f"{name} row counts {counts} differ"
             torch.cuda.synchronize()
             comm.close()
         if _lib.device_status() != 0:
@@ -239,7 +297,21 @@ def test_two_gpus_collective_and_peer_exchange(cuda, kernel_family):
     procs = [ctx.Process(target=_rank_main, args=(r, world, port, family, queue)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [queue.get(timeout=300) for _ in range(world)]
-    for p in procs:
-        p.join(timeout=120)
+    import queue as queue_module
+    results = []
+    try:
+        for _ in range(world):
+            results.append(queue.get(timeout=300))
+    except queue_module.Empty:
+        pass                                   # a rank died or blocked: reported below, children ended in `finally`
+    finally:
+        for p in procs:
+            p.join(timeout=60 if len(results) == world else 5)
+        for p in procs:
+            if p.is_alive():                   # never leave a child holding a GPU of a shared machine
+                p.terminate()
+                p.join(timeout=10)
+                if p.is_alive():
+                    p.kill()
+    assert len(results) == world, f"only {len(results)} of {world} ranks reported: {results}"
     assert all(ok for _, ok, _ in results), results
