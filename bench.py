@@ -648,7 +648,7 @@ def ep_parity_check(torch, dist, comm, tokens, rank, world):
     mine = x[:, lo:lo + rows].contiguous()
     ok = True
     for _ in range(2):
-        res, hidden = twin.forward(mine, slot_rows=slot)
+        res, hidden = twin.forward(mine, slot_rows=slot, total_rows=tokens)
         ok = ok and torch.equal(res, want_res[:, lo:lo + rows]) and torch.equal(hidden, want_hidden[:, lo:lo + rows])
     flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
@@ -724,11 +724,11 @@ def run_moe_gpu_arm(args, name):
 
     def step_fn():
         if chained:
-            return stack.forward(dev_x, slot)[0] if world > 1 else stack.forward(dev_x)[0]
+            return stack.forward(dev_x, slot, tokens)[0] if world > 1 else stack.forward(dev_x)[0]
         outs = None
         hidden = dev_x.to(torch.bfloat16)
         for layer in stack.layers:                       # independent layers: distinct weights defeat L2
-            outs = layer.forward(hidden, slot) if world > 1 else layer.forward(hidden)
+            outs = layer.forward(hidden, slot, tokens) if world > 1 else layer.forward(hidden)
         return outs.float()
 
     stream = torch.cuda.Stream()

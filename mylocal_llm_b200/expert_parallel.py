@@ -293,15 +293,20 @@ class DeviceExpertEngine:
         return moe_ops.router_topk(logits, self.router.k, renormalize=True, floor=self.router.normalization_floor,
                                    extra_id=self.n_global if self.folded else -1, extra_weight=scale)
 
-    def local_terms(self, x_all, weights, ids, home_lo, home_hi, *, peer=None):
+    def local_terms(self, x_all, weights, ids, home_lo, home_hi, *, peer=None, total_rows=None):
         """Run this rank's assignments. ``peer`` = (term table, rows_per_rank): rows go to their home
-        ranks' buffers and nothing is returned; otherwise returns the zero-filled flat term buffer."""
+        ranks' buffers and nothing is returned; otherwise returns the zero-filled flat term buffer.
+        ``total_rows`` = real rows of all ranks (default: every gathered row is real); the plan then
+        carries the segment bound of the single-GPU layer for that batch, which makes the grouped
+        kernels split K as they would there - the condition for bit-identical sums."""
         from . import moe_ops
         torch = _torch()
         bank = self.bank
-        plan = moe_ops.moe_plan_ep(ids, e_global=self.n_global + (1 if self.folded else 0),
-                                   first_expert=self.first_expert, n_local=bank.n_experts,
-                                   shared_id=self.n_global if self.folded else -1, home_lo=home_lo, home_hi=home_hi)
+        e_global = self.n_global + (1 if self.folded else 0)
+        bound = moe_ops.max_segments_for(int(total_rows or ids.shape[0]), ids.shape[1], e_global)
+        plan = moe_ops.moe_plan_ep(ids, e_global=e_global, first_expert=self.first_expert, n_local=bank.n_experts,
+                                   shared_id=self.n_global if self.folded else -1, home_lo=home_lo, home_hi=home_hi,
+                                   max_segments=bound)
         _phase("plan")
         hbuf = moe_ops.moe_gate_up(x_all, plan, None, None, bank.gate_type, bank.up_type, bank.d_ff, bank.d_model, 0, 0,
                                    gate_table=self.tables[0], up_table=self.tables[1], tables_aligned16=self.aligned)
@@ -345,14 +350,16 @@ class ExpertParallelMoELayer:
         self.engine, self.comm, self.d_model = engine, comm, int(d_model)
         self._empty_slots = {}
 
-    def forward(self, hidden, slot_rows=None):
+    def forward(self, hidden, slot_rows=None, total_rows=None):
         """hidden [B, T, D] (this rank's rows) -> [B, T, D].
 
         ``slot_rows`` = rows every rank reserves in the exchange, the same number on every rank and at
         least this rank's ``B*T`` (default: ``B*T``, i.e. every rank brings the same number of rows).
         A rank with fewer rows - none at all is allowed, as ``[1, 0, D]`` - fills the rest of its slot
         with padding entries that no rank executes, so a batch that does not divide by the number of
-        ranks (one token on eight GPUs) costs only the experts its real rows select."""
+        ranks (one token on eight GPUs) costs only the experts its real rows select. ``total_rows`` =
+        real rows of all ranks together (default ``world * slot_rows``); give it when slots are partly
+        filled and the result has to equal the single-GPU layer's bit for bit."""
         if hidden.ndim != 3 or hidden.shape[-1] != self.d_model:
             raise ValueError("hidden must have shape [batch,time,d_model]")
         batch, seq, d = hidden.shape
@@ -377,10 +384,11 @@ class ExpertParallelMoELayer:
         rows_per_rank = slot * engine.k_out
         if comm.peer:
             table, terms_home = comm.term_buffers(slot, engine.k_out, d)
-            engine.local_terms(x_all, w_all, ids_all, home_lo, home_hi, peer=(table, rows_per_rank))
+            engine.local_terms(x_all, w_all, ids_all, home_lo, home_hi, peer=(table, rows_per_rank),
+                               total_rows=total_rows)
             comm.barrier()
         else:
-            terms_all = engine.local_terms(x_all, w_all, ids_all, home_lo, home_hi)
+            terms_all = engine.local_terms(x_all, w_all, ids_all, home_lo, home_hi, total_rows=total_rows)
             terms_home = comm.exchange_terms(terms_all, rows_per_rank)
         _phase("barrier")
         if not rows:
@@ -441,13 +449,13 @@ class ExpertParallelMoEStack:
                 total += sum(w.nbytes for w in layer.engine.shared)
         return total
 
-    def forward(self, residual, slot_rows=None):
+    def forward(self, residual, slot_rows=None, total_rows=None):
         """residual FP32 [B, T, D] (this rank's rows, possibly none) -> (new residual, normalised
-        activations); ``slot_rows`` as in ``ExpertParallelMoELayer.forward``."""
+        activations); ``slot_rows`` and ``total_rows`` as in ``ExpertParallelMoELayer.forward``."""
         res = residual
         hidden = self.norms[0].forward_residual(res)
         for i, layer in enumerate(self.layers):
-            branch = layer.forward(hidden, slot_rows)
+            branch = layer.forward(hidden, slot_rows, total_rows)
             norm = self.norms[i + 1] if i + 1 < len(self.layers) else self.final_norm
             res, hidden = norm.forward_residual_add(res, branch)
         return res, hidden

@@ -233,18 +233,20 @@ def moe_combine_ids(terms_flat, ids2d, d, *, extra=None, extra_scale=None, out_d
     return out
 
 
-def moe_plan_ep(ids, *, e_global, first_expert, n_local, shared_id, home_lo, home_hi):
+def moe_plan_ep(ids, *, e_global, first_expert, n_local, shared_id, home_lo, home_hi, max_segments=None):
     """Routing plan of one expert-parallel rank over the gathered ids ``[T_all, k]`` (global ids).
 
     Local expert ids: 0..n_local-1 routed, n_local = shared expert (home rows only), n_local+1 =
-    assignments other ranks execute (sorted last, never run)."""
+    assignments other ranks execute (sorted last, never run). ``max_segments`` overrides the segment
+    bound (never below what this rank's plan can need): the grouped kernels derive their split of K
+    over warps from it, so a rank that passes the single-GPU layer's bound sums in the same order."""
     torch = _torch()
     if ids.dtype not in (torch.int32, torch.int64) or not ids.is_contiguous():
         raise ValueError("expert ids must be a contiguous int32/int64 tensor")
     rows, k = ids.shape
     n_plan = n_local + 2
     total = rows * k
-    max_seg = max_segments_for(rows, k, n_plan)
+    max_seg = max(max_segments_for(rows, k, n_plan), int(max_segments or 0))
     i32 = dict(dtype=torch.int32, device=ids.device)
     plan = DeviceRoutingPlan(
         rows, k, n_plan,

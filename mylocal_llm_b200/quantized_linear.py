@@ -227,9 +227,26 @@ def quantized_linear(x, weight, *, block_k=512, cpu_packed_backend="reference", 
     m = int(x.numel()) // k
     out = torch.empty((m, n), dtype=out_dtype or x.dtype, device=x.device)
     if m:
-        _lib.call("b200q_gemv", _ptr(weight.data), _lib.FORMAT_ID[weight.quant_type], n, k, _ptr(x), dt, m,
+        entry = "b200q_gemm" if _use_gemm(weight, x, m, n, k, dt) else "b200q_gemv"
+        _lib.call(entry, _ptr(weight.data), _lib.FORMAT_ID[weight.quant_type], n, k, _ptr(x), dt, m,
                   _ptr(out), _dtype_id(out), _lib.current_stream())
     return out.reshape(tuple(x.shape[:-1]) + (n,))
+
+
+GEMM_MIN_TOKENS = 17        # up to 16 tokens one GEMV pass reads the weights once; beyond, the tensor-core GEMM does
+
+
+def _use_gemm(weight, x, m, n, k, dt):
+    """More than 16 tokens of BF16 activations on a GGUF-layout weight go to the tcgen05 GEMM
+    (``b200q_gemm``: weights read once, BF16-weight precision); everything else stays on the GEMV
+    kernels (exact products, FP32 / FP16 activations, device tile layouts). ``B200Q_GEMM=0`` keeps
+    every call on the GEMV path."""
+    import os
+    if m < GEMM_MIN_TOKENS or weight.quant_type in DEVICE_LAYOUTS or os.environ.get("B200Q_GEMM", "1") == "0":
+        return False
+    if x.data_ptr() % 16 or weight.data.data_ptr() % 2:
+        return False
+    return bool(_lib.load().b200q_gemm_supported(_lib.FORMAT_ID[weight.quant_type], n, k, dt, m))
 
 
 def quantized_swiglu(x, gate, up, *, block_k=512, out_dtype=None):

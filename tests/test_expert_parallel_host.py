@@ -63,7 +63,7 @@ class NumpyEngine:
         ids = np.concatenate([ids.astype(np.int64), np.full((t, 1), self.n_global, np.int64)], axis=1)
         return torch.from_numpy(weights), torch.from_numpy(ids)
 
-    def local_terms(self, x_all, weights, ids, home_lo, home_hi, *, peer=None):
+    def local_terms(self, x_all, weights, ids, home_lo, home_hi, *, peer=None, total_rows=None):
         assert peer is None
         x, w, idn = x_all.float().numpy(), weights.numpy(), ids.numpy()
         terms = np.zeros((idn.size, D), np.float32)

@@ -161,7 +161,8 @@ def test_emulated_ranks_with_partly_filled_slots_equal_the_single_gpu_layer(cuda
     x_all, w_all, ids_all = (torch.cat([s[j] for s in slots]) for j in range(3))
     total = None
     for rank, engine in enumerate(engines):
-        terms = engine.local_terms(x_all, w_all, ids_all, rank * slot, rank * slot + row_counts[rank])
+        terms = engine.local_terms(x_all, w_all, ids_all, rank * slot, rank * slot + row_counts[rank],
+                                   total_rows=total_rows)
         if total is not None:
             assert not bool(((total != 0) & (terms != 0)).any())
         total = terms if total is None else total + terms
@@ -271,7 +272,8 @@ def _rank_main(rank, world, port, family, queue):
                 mine = x_real[lo:lo + counts[rank]]
                 want = reference.forward(x_real[None])[0][lo:lo + counts[rank]]
                 for _ in range(2):
-                    got = layer.forward(mine.reshape(1, counts[rank], D).contiguous(), slot_rows=slot)[0]
+                    got = layer.forward(mine.reshape(1, counts[rank], D).contiguous(), slot_rows=slot,
+                                        total_rows=sum(counts))[0]
                     if tuple(got.shape) != (counts[rank], D) or not torch.equal(got, want):
                         ok, note = False, f"{name} row counts {counts} differ"
             torch.cuda.synchronize()

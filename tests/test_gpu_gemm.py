@@ -1,0 +1,123 @@
+"""The tensor-core GEMM for many tokens (``b200q_gemm``: tcgen05.mma, accumulator in tensor memory,
+activations by TMA) against the FP64 oracle.
+
+Two bars per case. (1) Against the oracle product taken with the weights rounded to BF16 exactly as
+the kernel rounds them: what is left is FP32 accumulation, so the band is the packed linear's
+(rtol 2e-5 of tests/test_0106b_quantized_linear.py:119-121, absolute part scaled by the output RMS) -
+this bar finds every layout, swizzle, descriptor or tile-edge mistake. (2) Against the oracle product
+with the exact dequantised weights, element by element: rounding a weight to BF16 moves it by at most
+2^-9 relative (uniform, variance (2^-9)^2 / 3), so output (t, r) may differ by twelve standard deviations
+of the independent-error model, 12 * 2^-9 / sqrt(3) * sqrt(sum_i (w_ri x_ti)^2) - twelve rather than the
+usual six or seven because equal codes of one sub-block round by the same amount, so the errors of a row
+are positively correlated - plus the FP32 slack of bar (1); BF16 outputs add their own rounding (2^-8
+relative).
+"""
+
+import ctypes
+
+import numpy as np
+import pytest
+
+from oracle import build_oracle as bo
+from mylocal_llm_b200 import _lib, packed_to_device, quantized_linear
+from mylocal_llm_b200.quantize import quantize, random_packed
+
+pytestmark = pytest.mark.gpu
+
+FORMATS = ("Q8_0", "Q4_K", "Q5_K", "Q6_K")
+
+
+def bf16_round(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(torch.bfloat16).double().numpy()
+
+
+def run_gemm(torch, w, x_bf16, out_dtype):
+    n, k = w.shape
+    m = x_bf16.shape[0]
+    dev = packed_to_device(w)
+    y = torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda")
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    _lib.call("b200q_gemm", ptr(dev.data), _lib.FORMAT_ID[w.quant_type], n, k, ptr(x_bf16), _lib.DTYPE_ID["bfloat16"], m,
+              ptr(y), _lib.DTYPE_ID[str(out_dtype).replace("torch.", "")], _lib.current_stream())
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    return y
+
+
+def check(torch, w, m, seed, out_dtype=None):
+    out_dtype = out_dtype or torch.float32
+    n, k = w.shape
+    x = np.random.default_rng(seed).normal(0, 1, (m, k)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    y = run_gemm(torch, w, xd, out_dtype).double().cpu().numpy()
+    assert np.isfinite(y).all(), "some outputs were never written"
+    dense = bo.port_dequantize(w.data, w.shape, w.quant_type)
+    x64 = xd.double().cpu().numpy()
+    ref_rounded = x64 @ bf16_round(torch, dense).T
+    ref_exact = x64 @ dense.astype(np.float64).T
+    rms = float(np.sqrt((ref_exact ** 2).mean())) or 1.0
+    if out_dtype == torch.float32:
+        np.testing.assert_allclose(y, ref_rounded, rtol=2e-5, atol=2e-5 * rms)
+    sigma = 2.0 ** -9 / np.sqrt(3.0) * np.sqrt((x64 ** 2) @ (dense.astype(np.float64) ** 2).T)
+    slack = 12.0 * sigma + 2e-5 * rms + (2.0 ** -8 if out_dtype != torch.float32 else 2e-5) * np.abs(ref_exact)
+    worst = float((np.abs(y - ref_exact) / slack).max())
+    assert worst <= 1.0, f"BF16-weight bar exceeded: ratio {worst:.2f}"
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("n,k,m", [(64, 256, 17), (128, 256, 128), (64, 512, 33), (192, 1024, 129), (80, 256, 40),
+                                   (1024, 2048, 300)])
+def test_gemm_small_shapes_all_formats(cuda, fmt, n, k, m):
+    w = quantize(np.random.default_rng(n + k).normal(0, 0.02, (n, k)).astype(np.float32), fmt)
+    check(cuda, w, m, seed=m)
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_gemm_random_bytes_exercise_every_code_bit(cuda, fmt):
+    w = random_packed(fmt, (256, 1024), seed=5, d=0.01, dmin=0.005)
+    check(cuda, w, 70, seed=1)
+    check(cuda, w, 70, seed=1, out_dtype=cuda.bfloat16)
+
+
+@pytest.mark.parametrize("fmt", ["Q4_K", "Q5_K", "Q6_K"])
+@pytest.mark.parametrize("shape", [(8192, 2048), (2048, 8192)])
+@pytest.mark.parametrize("m", [32, 512])
+def test_gemm_second_configuration(cuda, fmt, shape, m):
+    w = random_packed(fmt, shape, seed=shape[0], d=0.01, dmin=0.005)
+    check(cuda, w, m, seed=m)
+
+
+def test_quantized_linear_routes_many_bf16_tokens_to_the_gemm(cuda, monkeypatch):
+    torch = cuda
+    w = quantize(np.random.default_rng(3).normal(0, 0.02, (512, 1024)).astype(np.float32), "Q4_K")
+    dev = packed_to_device(w)
+    calls = []
+    real = _lib.call
+    monkeypatch.setattr(_lib, "call", lambda name, *a: (calls.append(name), real(name, *a))[1])
+    x = torch.randn((2, 40, 1024), device="cuda").to(torch.bfloat16)
+    y = quantized_linear(x, dev)
+    assert calls == ["b200q_gemm"] and y.shape == (2, 40, 512) and y.dtype == torch.bfloat16
+    calls.clear()
+    quantized_linear(x[:, :8].contiguous(), dev)                       # 16 tokens: one GEMV pass
+    quantized_linear(x.float(), dev)                                   # FP32 activations keep the exact-product path
+    monkeypatch.setenv("B200Q_GEMM", "0")
+    y_gemv = quantized_linear(x, dev)
+    assert calls == ["b200q_gemv"] * 3
+    ref = y_gemv.float()
+    assert float((y.float() - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
+
+
+def test_gemm_rejects_what_it_does_not_cover(cuda):
+    torch = cuda
+    w = quantize(np.random.default_rng(3).normal(0, 0.02, (64, 256)).astype(np.float32), "Q4_K")
+    dev = packed_to_device(w)
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    x32 = torch.randn((32, 256), device="cuda")
+    y = torch.empty((32, 64), device="cuda")
+    with pytest.raises(NotImplementedError):
+        _lib.call("b200q_gemm", ptr(dev.data), 2, 64, 256, ptr(x32), 0, 32, ptr(y), 0, _lib.current_stream())
+    with pytest.raises(ValueError):
+        _lib.call("b200q_gemm", ptr(dev.data), 22, 64, 256, ptr(x32), 2, 32, ptr(y), 0, _lib.current_stream())
+    assert _lib.load().b200q_gemm_supported(2, 64, 256, 2, 32) == 1
+    assert _lib.load().b200q_gemm_supported(2, 64, 256, 0, 32) == 0
+    assert _lib.load().b200q_gemm_supported(0, 64, 96, 2, 32) == 0
