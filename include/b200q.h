@@ -76,7 +76,7 @@ int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype,
  * accumulator in tensor memory; the activations arrive by TMA. Serves the any-M contract of
  * quantized_linear (mini_llm/ops/quantized_linear.py:272-335, grid M*N at :322-334) for M > 16.
  * Requirements (else 3 = unsupported, use b200q_gemv): native GGUF layout (Q8_0, Q4_K, Q5_K, Q6_K),
- * BF16 activations, 16-byte aligned x, K a multiple of 64. Precision: weights are rounded to BF16
+ * BF16 activations, 16-byte aligned x, K a multiple of 256. Precision: weights are rounded to BF16
  * after the reference's FP32 dequantisation (relative 2^-9 per weight), accumulation is FP32.
  * b200q_gemm_supported answers the shape / type part of the requirements (1 = yes) without a launch. */
 int b200q_gemm(const void *w, int fmt, int n, int k, const void *x, int x_dtype, int m, void *y,

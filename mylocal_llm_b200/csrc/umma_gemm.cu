@@ -1,39 +1,49 @@
 // Batched / prefill GEMM on packed GGUF weights: y[m, n] = x[m, k] @ W[n, k]^T for m > 16 tokens.
 //
 // A GEMV pass re-reads the packed matrix once per 8 or 16 tokens; from a few dozen tokens on the
-// product is a real contraction and belongs on the 5th-generation tensor cores. One CTA owns a tile
-// of 128 (or 256) tokens x NT weight rows and walks K in slabs of 64:
-//   * the activation slab [128 tokens x 64 k] (BF16) arrives by TMA (cp.async.bulk.tensor.2d, 128-byte
-//     swizzle, rows beyond m zero-filled by the tensor map) and signals an mbarrier;
-//   * all threads decode the packed weights of the slab [NT rows x 64 k] - the reference's
-//     dequantisation (mini_llm/ops/quantized_weight.py:208-250), FP32 arithmetic, rounded once to
-//     BF16 - and store them in the same 128-byte-swizzled K-major layout;
-//   * one thread issues tcgen05.mma (kind::f16, M = 128, N = NT, K = 16, four per slab) with both
-//     operands described by shared-memory descriptors; the FP32 accumulator [128 x NT] lives in
-//     tensor memory; tcgen05.commit arrives on the stage's mbarrier when the tensor core has
-//     consumed the slab, which frees the stage for the decode two slabs later;
-//   * after the last slab the eight warps read the accumulator back with tcgen05.ld (each warp its
-//     32-lane quarter), convert and store y.
-// The tensor core works on slab i while the threads decode slab i+1 (four stages). Weights are
-// rounded to BF16, so results carry BF16-weight precision (relative 2^-9 per weight, like the BF16
-// activations this path requires); the GEMV kernels keep their exact-product arithmetic for m <= 16
-// and for FP32 activations.
+// product is a real contraction and belongs on the 5th-generation tensor cores. The roles are
+// swapped with respect to the textbook GEMM: the weight rows are the M dimension of the MMA. One CTA
+// owns 128 weight rows x NTOK tokens (NTOK = the batch rounded up to 16, at most 256; one or two
+// such token tiles per CTA) and walks K in slabs of 64:
+//   * the activation slab [NTOK tokens x 64 k] (BF16) arrives by TMA (cp.async.bulk.tensor.2d,
+//     128-byte swizzle, rows beyond m zero-filled by the tensor map);
+//   * sixteen decoder warps turn the packed weights of the slab [128 rows x 64 k] into BF16 - the
+//     reference's dequantisation (mini_llm/ops/quantized_weight.py:208-250) in FP32, rounded once -
+//     and store them in the same 128-byte-swizzled K-major layout; the packed bytes of a 256-wide
+//     group are requested a group ahead and wait in registers;
+//   * both arrive on the stage's `full` mbarrier (transaction bytes + one arrival per decoder warp);
+//     one lane of another warp waits for it and issues tcgen05.mma (kind::f16, M = 128, N = NTOK,
+//     K = 16, four per slab and token tile) with both operands described by shared-memory
+//     descriptors; the FP32 accumulator [128 x NTOK] lives in tensor memory; tcgen05.commit arrives
+//     on the stage's `free` mbarrier when the tensor core has consumed the slab, which lets the
+//     decoders and the TMA lane (one more warp) refill it;
+//   * after the last slab the decoder warps read the accumulator back with tcgen05.ld (each
+//     warp its 32-lane quarter = 32 weight rows), convert and store y (a warp stores 32 consecutive
+//     outputs of one token per instruction).
+// The MMA-issuing lane never waits for its own commits, so the tensor core always has queued work;
+// with NTOK = 256 an MMA runs about 128 cycles against ~55 cycles to issue it, i.e. the kernel is
+// tensor-bound; with a few dozen tokens it is bound by that issue latency (~400 cycles per slab).
+// Weights are rounded to BF16, so results carry BF16-weight precision (relative 2^-9 per weight,
+// like the BF16 activations this path requires); the GEMV kernels keep their exact-product
+// arithmetic for m <= 16 and for FP32 activations.
 //
-// Every mbarrier wait is bounded (2 s): on expiry the CTA records a status code, skips the rest of
-// its work, waits (bounded) for what it has in flight, frees its tensor memory and returns.
+// Every mbarrier wait is bounded (2 s): on expiry the waiting thread records a status code and
+// raises the CTA's abort flag; every role then leaves its loop, the copies in flight are waited for
+// (bounded), the tensor memory is freed and the CTA returns.
 #include <cuda.h>
 
+#include <algorithm>
 #include <mutex>
+#include <utility>
+#include <vector>
 
 #include "common.cuh"
 
 namespace b200q {
 
-constexpr int UG_THREADS = 256;
-constexpr int UG_BM = 128;          // tokens per accumulator (UMMA M)
+constexpr int UG_BM = 128;          // weight rows per CTA (UMMA M)
 constexpr int UG_BK = 64;           // K per slab: 64 BF16 = one 128-byte swizzle row
-constexpr int UG_STAGES = 4;
-constexpr int UG_A_BYTES = UG_BM * UG_BK * 2;
+constexpr int UG_W_BYTES = UG_BM * UG_BK * 2;      // one decoded weight slab
 constexpr int STATUS_UMMA_WAIT_TMA = 111;   // gave up waiting for an activation slab
 constexpr int STATUS_UMMA_WAIT_MMA = 112;   // gave up waiting for the tensor core to release a stage
 
@@ -43,6 +53,9 @@ struct UmmaGemmArgs {
     long long row_bytes;      // packed bytes per weight row (native layouts)
     void *y;
     int y_dtype;
+    int ntok;                 // tokens per accumulator (UMMA N): a multiple of 16, 16..256
+    int mt;                   // token tiles (accumulators) per CTA: 1 or 2
+    int stages;               // shared-memory stages (2..4)
     int *status;
 };
 
@@ -117,96 +130,137 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Decoding 32 consecutive weights of one packed row (positions 32*u .. 32*u+31) to FP32, with the
+// Decoding. A decoder thread owns one weight row of the tile and one 16-position quarter of every
+// 64-position slab. It fetches what it needs of a whole 256-position group (a K-quant super-block,
+// eight Q8_0 blocks) at once - four 16-byte code pieces, one per slab, plus the group's scales - and
+// keeps the next group in a second register set, so global-memory latency never sits on the path of
+// a slab. decode_slab<SL> turns the piece of slab SL of the group into 16 FP32 weights with the
 // reference's arithmetic: (d*sc)*q - (dmin*mn) for Q4_K / Q5_K, (d*sc)*q for Q6_K, d*q for Q8_0.
 // ---------------------------------------------------------------------------------------------
-// 32 bytes from an address with any alignment that is a multiple of 2.
-__device__ __forceinline__ void load32(const uint8_t *p, uint32_t (&w)[8]) {
+// 16 bytes from an address that is a multiple of 2.
+__device__ __forceinline__ uint4 load16(const uint8_t *p) {
     const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    uint4 v;
     if ((a & 15) == 0) {
-        const uint4 lo = *reinterpret_cast<const uint4 *>(p), hi = *reinterpret_cast<const uint4 *>(p + 16);
-        w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w; w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
+        v = *reinterpret_cast<const uint4 *>(p);
     } else if ((a & 3) == 0) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) w[i] = reinterpret_cast<const uint32_t *>(p)[i];
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(p);
+        v = make_uint4(w[0], w[1], w[2], w[3]);
     } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint16_t *h = reinterpret_cast<const uint16_t *>(p) + 2 * i;
-            w[i] = static_cast<uint32_t>(h[0]) | (static_cast<uint32_t>(h[1]) << 16);
-        }
+        const uint16_t *h = reinterpret_cast<const uint16_t *>(p);
+        v.x = h[0] | (static_cast<uint32_t>(h[1]) << 16);
+        v.y = h[2] | (static_cast<uint32_t>(h[3]) << 16);
+        v.z = h[4] | (static_cast<uint32_t>(h[5]) << 16);
+        v.w = h[6] | (static_cast<uint32_t>(h[7]) << 16);
     }
-}
-__device__ __forceinline__ float half_at(const uint8_t *p) {
-    return half_bits_to_float(*reinterpret_cast<const uint16_t *>(p));
+    return v;
 }
 
+__host__ __device__ constexpr int fmt_group_bytes(int fmt) {        // packed bytes of 256 positions of a row
+    return fmt == B200Q_Q8_0 ? 8 * 34 : fmt == B200Q_Q4_K ? 144 : fmt == B200Q_Q5_K ? 176 : 210;
+}
+
+struct RawGroup {
+    uint4 q[4];   // slab SL's 16 code bytes (Q4_K / Q5_K: nibble bytes; Q6_K: low-nibble bytes; Q8_0: codes)
+    uint4 h[2];   // Q5_K: h[0] = high-bit bytes; Q6_K: h[half] = bytes holding the upper two bits
+    uint4 hdr;    // Q4_K / Q5_K: d, dmin, 12 scale bytes; Q6_K: .x = 4 scale bytes (one per slab), .y = d;
+                  // Q8_0: .x, .y = the four slabs' block scales as FP16 pairs
+};
+
+// quart = the thread's quarter (0..3) of a slab; blk = the row's bytes of the group.
 template <int FMT>
-__device__ __forceinline__ void decode32(const uint8_t *row, int u, float (&out)[32]) {
-    uint32_t q[8];
-    if (FMT == B200Q_Q8_0) {
-        const uint8_t *b = row + static_cast<size_t>(u) * 34;
-        const float d = half_at(b);
-        // the 32 codes start 2 bytes into a 34-byte block
-        const uint16_t *h = reinterpret_cast<const uint16_t *>(b + 2);
+__device__ __forceinline__ void fetch_group(const uint8_t *blk, int quart, RawGroup &r) {
+    if constexpr (FMT == B200Q_Q8_0) {
+        // slab SL, quarter quart -> block 2*SL + (quart >> 1), half quart & 1 of its 32 codes
+        const uint8_t *b = blk + (quart >> 1) * 34;
+        uint32_t d[4];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const uint32_t v = h[i];
-            out[2 * i] = d * static_cast<float>(static_cast<int>(static_cast<int8_t>(v & 0xffu)));
-            out[2 * i + 1] = d * static_cast<float>(static_cast<int>(static_cast<int8_t>(v >> 8)));
+        for (int sl = 0; sl < 4; ++sl) {
+            d[sl] = *reinterpret_cast<const uint16_t *>(b + 68 * sl);
+            r.q[sl] = load16(b + 68 * sl + 2 + 16 * (quart & 1));
+        }
+        r.hdr.x = d[0] | (d[1] << 16);
+        r.hdr.y = d[2] | (d[3] << 16);
+        return;
+    }
+    if constexpr (FMT == B200Q_Q4_K || FMT == B200Q_Q5_K) {
+        // slab SL, quarter quart -> sub-block 2*SL + (quart >> 1), nibble bytes [32*SL + 16*(quart & 1), +16)
+        r.hdr = load16(blk);
+        const uint8_t *qs = blk + (FMT == B200Q_Q5_K ? 48 : 16) + 16 * (quart & 1);
+#pragma unroll
+        for (int sl = 0; sl < 4; ++sl) r.q[sl] = load16(qs + 32 * sl);
+        if (FMT == B200Q_Q5_K) r.h[0] = load16(blk + 16 + 16 * (quart & 1));
+        return;
+    } else {
+    // Q6_K: slab SL, quarter quart -> position 64*SL + 16*quart: half = SL >> 1, low-nibble bytes
+    // [64*half + 16*quart, +16) shifted by 4*(SL & 1), upper bits in bytes [128 + 32*half + 16*(quart & 1), +16)
+    // shifted by 2*(2*(SL & 1) + (quart >> 1)), scale 4*SL + quart
+#pragma unroll
+    for (int sl = 0; sl < 4; sl += 2) r.q[sl] = r.q[sl + 1] = load16(blk + 64 * (sl >> 1) + 16 * quart);
+    r.h[0] = load16(blk + 128 + 16 * (quart & 1));
+    r.h[1] = load16(blk + 160 + 16 * (quart & 1));
+    const uint8_t *sc = blk + 192 + quart;
+    r.hdr.x = sc[0] | (static_cast<uint32_t>(sc[4]) << 8) | (static_cast<uint32_t>(sc[8]) << 16) |
+              (static_cast<uint32_t>(sc[12]) << 24);
+    r.hdr.y = *reinterpret_cast<const uint16_t *>(blk + 208);
+    }
+}
+
+// Byte j of `codes` as a float, exactly: the byte becomes the low mantissa byte of 2^23.
+__device__ __forceinline__ float byte_to_float(uint32_t codes, int j, float bias) {
+    return __uint_as_float(__byte_perm(codes, 0x4B000000u, 0x7650u | static_cast<uint32_t>(j))) - bias;
+}
+
+template <int FMT, int SL>
+__device__ __forceinline__ void decode_slab(const RawGroup &r, int quart, float (&out)[16]) {
+    const uint32_t qw[4] = {r.q[SL].x, r.q[SL].y, r.q[SL].z, r.q[SL].w};
+    if constexpr (FMT == B200Q_Q8_0) {
+        const float d = half_bits_to_float(((SL < 2 ? r.hdr.x : r.hdr.y) >> (16 * (SL & 1))) & 0xffffu);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t u = qw[i] ^ 0x80808080u;              // code + 128 in every byte
+#pragma unroll
+            for (int j = 0; j < 4; ++j) out[4 * i + j] = d * byte_to_float(u, j, 8388736.0f);
         }
         return;
     }
-    const int sb = u >> 3, g = u & 7;
-    if (FMT == B200Q_Q4_K || FMT == B200Q_Q5_K) {
-        constexpr int QB = FMT == B200Q_Q5_K ? 176 : 144;
-        const uint8_t *b = row + static_cast<size_t>(sb) * QB;
-        const float d = half_at(b), dmin = half_at(b + 2);
-        const uint8_t *m = b + 4;
-        int sc, mn;
-        if (g < 4) {
-            sc = m[g] & 63;
-            mn = m[4 + g] & 63;
-        } else {
-            sc = (m[4 + g] & 15) | ((m[g - 4] >> 2) & 48);
-            mn = (m[4 + g] >> 4) | ((m[g] >> 2) & 48);
+    if constexpr (FMT == B200Q_Q4_K || FMT == B200Q_Q5_K) {
+        const int hi_sub = quart >> 1;                           // sub-block g = 2*SL + hi_sub
+        const float d = half_bits_to_float(r.hdr.x & 0xffffu), dmin = half_bits_to_float(r.hdr.x >> 16);
+        uint32_t sc, mn;
+        if (SL < 2) {                                            // g < 4: low six bits of bytes g and 4 + g
+            const int sh = 16 * SL + 8 * hi_sub;
+            sc = (r.hdr.y >> sh) & 63u;
+            mn = (r.hdr.z >> sh) & 63u;
+        } else {                                                 // g >= 4: nibbles of byte 4 + g, top bits of bytes g - 4, g
+            const int sh = 16 * (SL - 2) + 8 * hi_sub;
+            const uint32_t hi = (r.hdr.w >> sh) & 0xffu;
+            sc = (hi & 15u) | (((r.hdr.y >> sh) >> 2) & 48u);
+            mn = (hi >> 4) | (((r.hdr.z >> sh) >> 2) & 48u);
         }
-        const float scale = d * static_cast<float>(sc), minimum = dmin * static_cast<float>(mn);
-        load32(b + (FMT == B200Q_Q5_K ? 48 : 16) + 32 * (g >> 1), q);
-        uint32_t hb[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (FMT == B200Q_Q5_K) load32(b + 16, hb);
-        const int shift = 4 * (g & 1);
+        const float scale = d * static_cast<float>(sc), neg_min = -(dmin * static_cast<float>(mn));
+        const uint32_t hw[4] = {r.h[0].x, r.h[0].y, r.h[0].z, r.h[0].w};
+        const int shift = 4 * hi_sub, g = 2 * SL + hi_sub;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t nib = (q[i] >> shift) & 0x0f0f0f0fu;
-            const uint32_t top = FMT == B200Q_Q5_K ? ((hb[i] >> g) & 0x01010101u) << 4 : 0u;
-            const uint32_t code = nib | top;
+        for (int i = 0; i < 4; ++i) {
+            uint32_t code = (qw[i] >> shift) & 0x0f0f0f0fu;
+            if (FMT == B200Q_Q5_K) code |= ((hw[i] >> g) & 0x01010101u) << 4;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                out[4 * i + j] = __fmaf_rn(scale, static_cast<float>((code >> (8 * j)) & 0xffu), -minimum);
+            for (int j = 0; j < 4; ++j) out[4 * i + j] = __fmaf_rn(scale, byte_to_float(code, j, 8388608.0f), neg_min);
         }
         return;
     }
-    // Q6_K: position p = 32*g inside the super-block; half = p / 128, quarter = (p % 128) / 32
-    const uint8_t *b = row + static_cast<size_t>(sb) * 210;
-    const float d = half_at(b + 208);
-    const int half = g >> 2, quarter = g & 3;
-    uint32_t hi[8];
-    load32(b + 64 * half + 32 * (quarter & 1), q);
-    load32(b + 128 + 32 * half, hi);
-    const int8_t *scales = reinterpret_cast<const int8_t *>(b + 192 + 2 * g);
-    const float s0 = d * static_cast<float>(scales[0]), s1 = d * static_cast<float>(scales[1]);
-    const int lo_shift = 4 * (quarter >> 1), hi_shift = 2 * quarter;
+    // Q6_K
+    const float scale = half_bits_to_float(r.hdr.y) *
+                        static_cast<float>(static_cast<int>(static_cast<int8_t>((r.hdr.x >> (8 * SL)) & 0xffu)));
+    const uint4 hv = r.h[SL >> 1];
+    const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+    const int lo_shift = 4 * (SL & 1), hi_shift = 2 * (2 * (SL & 1) + (quart >> 1));
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t lo4 = (q[i] >> lo_shift) & 0x0f0f0f0fu;
-        const uint32_t hi2 = ((hi[i] >> hi_shift) & 0x03030303u) << 4;
-        const uint32_t code = lo4 | hi2;
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t code = ((qw[i] >> lo_shift) & 0x0f0f0f0fu) | (((hw[i] >> hi_shift) & 0x03030303u) << 4);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int v = static_cast<int>((code >> (8 * j)) & 0xffu) - 32;
-            out[4 * i + j] = (i < 4 ? s0 : s1) * static_cast<float>(v);
-        }
+        for (int j = 0; j < 4; ++j) out[4 * i + j] = scale * byte_to_float(code, j, 8388640.0f);   // code - 32
     }
 }
 
@@ -215,182 +269,268 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t *>(&v);
 }
 
+// One output y[t, col] from FP32 register bits.
+__device__ __forceinline__ void store_out(void *yv, int y_dtype, size_t idx, uint32_t bits) {
+    const float v = __uint_as_float(bits);
+    if (y_dtype == B200Q_F32) static_cast<float *>(yv)[idx] = v;
+    else if (y_dtype == B200Q_BF16) static_cast<__nv_bfloat16 *>(yv)[idx] = __float2bfloat16_rn(v);
+    else static_cast<__half *>(yv)[idx] = __float2half_rn(v);
+}
+
+// The weight ring as a decoder thread sees it.
+struct DecoderRing {
+    uint8_t *base;            // stage 0 of the ring (a stage's decoded weight slab comes first)
+    uint64_t *free_bar, *full_bar;
+    volatile int *abort_flag;
+    int *status;
+    int stage_bytes, stages;
+    int stage, wraps;         // stage of the next slab, and how many times the ring has wrapped
+};
+
+// Decode slab SL of the groups in `grp` into the ring's next stage and publish it; false = gave up.
+template <int FMT, int SL, int PIECES>
+__device__ __forceinline__ bool decode_store_slab(const RawGroup (&grp)[PIECES], const int (&prow)[PIECES],
+                                                  const int (&pquart)[PIECES], DecoderRing &ring, int lane) {
+    if (ring.wraps > 0 &&
+        !mbar_wait_bounded(&ring.free_bar[ring.stage], (ring.wraps - 1) & 1, ring.status, STATUS_UMMA_WAIT_MMA))
+        *ring.abort_flag = 1;
+    if (*ring.abort_flag) return false;
+    uint8_t *stage = ring.base + static_cast<size_t>(ring.stage) * ring.stage_bytes;
+#pragma unroll
+    for (int j = 0; j < PIECES; ++j) {
+        float wv[16];
+        decode_slab<FMT, SL>(grp[j], pquart[j], wv);
+        uint8_t *dst_row = stage + (prow[j] >> 3) * 1024 + (prow[j] & 7) * 128;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            uint4 v;
+            v.x = pack_bf16(wv[8 * c + 0], wv[8 * c + 1]);
+            v.y = pack_bf16(wv[8 * c + 2], wv[8 * c + 3]);
+            v.z = pack_bf16(wv[8 * c + 4], wv[8 * c + 5]);
+            v.w = pack_bf16(wv[8 * c + 6], wv[8 * c + 7]);
+            const int chunk = (pquart[j] * 2 + c) ^ (prow[j] & 7);         // 128-byte swizzle
+            *reinterpret_cast<uint4 *>(dst_row + chunk * 16) = v;
+        }
+    }
+    fence_proxy_async();          // the decoded pieces must be visible to the tensor core's reads
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ring.full_bar[ring.stage]);
+    if (++ring.stage == ring.stages) {
+        ring.stage = 0;
+        ++ring.wraps;
+    }
+    return true;
+}
+
+// The four slabs of group g from `grp`, then refill `grp` with group g + 2 and ask L2 for group g + 3.
+template <int FMT, int PIECES>
+__device__ __forceinline__ bool decode_group(RawGroup (&grp)[PIECES], const uint8_t *const (&row_ptr)[PIECES],
+                                             const int (&prow)[PIECES], const int (&pquart)[PIECES], int g, int ngroups,
+                                             DecoderRing &ring, int lane) {
+    constexpr int GB = fmt_group_bytes(FMT);
+    const bool ok = decode_store_slab<FMT, 0, PIECES>(grp, prow, pquart, ring, lane) &&
+                    decode_store_slab<FMT, 1, PIECES>(grp, prow, pquart, ring, lane) &&
+                    decode_store_slab<FMT, 2, PIECES>(grp, prow, pquart, ring, lane) &&
+                    decode_store_slab<FMT, 3, PIECES>(grp, prow, pquart, ring, lane);
+    if (!ok) return false;
+#pragma unroll
+    for (int j = 0; j < PIECES; ++j) {
+        fetch_group<FMT>(row_ptr[j] + static_cast<size_t>(min(g + 2, ngroups - 1)) * GB, pquart[j], grp[j]);
+        if (g + 3 < ngroups) asm volatile("prefetch.global.L2 [%0];" ::"l"(row_ptr[j] + static_cast<size_t>(g + 3) * GB));
+    }
+    return true;
+}
+
 // ---------------------------------------------------------------------------------------------
-// Kernel. FMT: native GGUF format; NT: weight rows per CTA (UMMA N, 64 or 128); MT: token tiles of
-// 128 per CTA (1 or 2; both use every decoded weight slab).
+// Kernel. FMT: native GGUF format. Eighteen warps: 0-15 decode (and run the epilogue), one lane of warp
+// 16 issues the MMAs, one lane of warp 17 the TMA loads. A stage holds one decoded weight slab (16 KB) followed by
+// `mt` activation slabs of ntok rows x 128 bytes.
 // ---------------------------------------------------------------------------------------------
-template <int FMT, int NT, int MT>
+constexpr int UG_MAX_STAGES = 4;
+constexpr int UG_DECODE_THREADS = 512;
+constexpr int UG_THREADS = UG_DECODE_THREADS + 64;
+constexpr int UG_PIECES = UG_BM * 4 / UG_DECODE_THREADS;      // 16-weight pieces per decoder thread and slab
+
+template <int FMT>
 __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_constant__ CUtensorMap xmap,
                                                                   const UmmaGemmArgs a) {
-    constexpr int B_BYTES = NT * UG_BK * 2;
-    constexpr int STAGE_BYTES = MT * UG_A_BYTES + B_BYTES;
-    constexpr uint32_t TMEM_COLS = MT * NT;                   // 64, 128 or 256: a power of two >= 32
-    constexpr uint32_t IDESC = umma_idesc_bf16(UG_BM, NT);
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t full_a[UG_STAGES], mma_done[UG_STAGES];
+    __shared__ __align__(8) uint64_t full_bar[UG_MAX_STAGES], free_bar[UG_MAX_STAGES], acc_done;
     __shared__ uint32_t tmem_base_slot;
-    __shared__ int abort_flag;
+    __shared__ volatile int abort_flag;
 
     chain_trigger();
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * NT;
-    const int m0 = blockIdx.y * (MT * UG_BM);
+    const int n0 = blockIdx.x * UG_BM;
+    const int ntok = a.ntok, mt_count = a.mt;
+    const int m0 = blockIdx.y * (mt_count * ntok);
     const int nslab = a.k / UG_BK;
+    const int S = a.stages;
+    const int x_bytes = ntok * UG_BK * 2;                       // one activation slab of one token tile
+    const int stage_bytes = UG_W_BYTES + mt_count * x_bytes;
+    const int acc_stride = (ntok + 31) & ~31;                   // TMEM columns between the accumulators
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < static_cast<uint32_t>(mt_count * acc_stride)) tmem_cols <<= 1;
 
     if (tid == 0) {
-#pragma unroll
-        for (int s = 0; s < UG_STAGES; ++s) {
-            mbar_init(&full_a[s], 1);
-            mbar_init(&mma_done[s], 1);
+        for (int s = 0; s < UG_MAX_STAGES; ++s) {
+            mbar_init(&full_bar[s], UG_DECODE_THREADS / 32 + 1);   // one arrival per decoder warp + the TMA lane's
+            mbar_init(&free_bar[s], 1);
         }
+        mbar_init(&acc_done, 1);
         abort_flag = 0;
         fence_barrier_init();
     }
     if (warp == 0) {
-        tmem_alloc(&tmem_base_slot, TMEM_COLS);
+        tmem_alloc(&tmem_base_slot, tmem_cols);
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_d = tmem_base_slot;
-    chain_wait();            // the activations come from the preceding kernel on the stream
 
-    // decode unit of this thread inside a slab: weight row `urow` of the tile, 32-value half `uhalf`
-    const int unit = tid;
-    const bool has_unit = unit < 2 * NT;
-    const int urow = unit % NT, uhalf = unit / NT;
-    const int wrow = min(n0 + urow, a.n - 1);                 // rows past the end decode the last row; never stored
-    const uint8_t *row_ptr = a.w + static_cast<size_t>(wrow) * a.row_bytes;
-
-    int issued = 0;          // slabs whose loads / MMAs have been issued (thread 0)
-    bool failed = false;
-    for (int i = 0; i < nslab; ++i) {
-        const int s = i % UG_STAGES;
-        uint8_t *stage = smem + static_cast<size_t>(s) * STAGE_BYTES;
-        if (i >= UG_STAGES &&
-            !mbar_wait_bounded(&mma_done[s], ((i / UG_STAGES) - 1) & 1, a.status, STATUS_UMMA_WAIT_MMA)) {
-            abort_flag = 1;
-        }
-        if (tid == 0 && !abort_flag) {
-            mbar_arrive_expect_tx(&full_a[s], MT * UG_A_BYTES);
+    if (warp < UG_DECODE_THREADS / 32) {
+        // ---------------------------------------------------------------- decoders
+        // piece j of this thread: weight row prow[j] of the tile, 16-value quarter pquart[j] of a slab's
+        // 64 positions; the lanes of a warp hold consecutive rows (conflict-free swizzled stores)
+        const uint8_t *row_ptr[UG_PIECES];
+        int prow[UG_PIECES], pquart[UG_PIECES];
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-                tma_load_2d(stage + mt * UG_A_BYTES, &xmap, i * UG_BK, m0 + mt * UG_BM, &full_a[s]);
+        for (int j = 0; j < UG_PIECES; ++j) {
+            const int id = tid + UG_DECODE_THREADS * j;
+            prow[j] = id % UG_BM;
+            pquart[j] = id / UG_BM;
+            const int wrow = min(n0 + prow[j], a.n - 1);      // rows past the end decode the last row; never stored
+            row_ptr[j] = a.w + static_cast<size_t>(wrow) * a.row_bytes;
+        }
+        // Two register sets hold the packed bytes of the current and the next 256-position group (the
+        // loop is unrolled by two so the sets are named statically and nothing is copied); one group
+        // further ahead the lines are only asked into L2. Weights are read-only: no dependency wait.
+        constexpr int GB = fmt_group_bytes(FMT);
+        const int ngroups = a.k / 256;
+        DecoderRing ring{smem, free_bar, full_bar, &abort_flag, a.status, stage_bytes, S, 0, 0};
+        RawGroup set0[UG_PIECES], set1[UG_PIECES];
+#pragma unroll
+        for (int j = 0; j < UG_PIECES; ++j) {
+            fetch_group<FMT>(row_ptr[j], pquart[j], set0[j]);
+            fetch_group<FMT>(row_ptr[j] + static_cast<size_t>(min(1, ngroups - 1)) * GB, pquart[j], set1[j]);
+        }
+        for (int g = 0; g < ngroups; g += 2) {
+            if (!decode_group<FMT, UG_PIECES>(set0, row_ptr, prow, pquart, g, ngroups, ring, lane)) break;
+            if (g + 1 < ngroups && !decode_group<FMT, UG_PIECES>(set1, row_ptr, prow, pquart, g + 1, ngroups, ring, lane))
+                break;
+        }
+    } else if (warp == UG_DECODE_THREADS / 32 + 1) {
+        // ---------------------------------------------------------------- TMA loads of the activation slabs
+        // (one lane works; the others park at the __syncwarp below - were they to run on to the spin-wait of
+        // the epilogue, their polling would take the issue slots of the working lane of their own warp)
+        if (lane == 0) {
+        chain_wait();                 // the activations come from the preceding kernel on the stream
+        // (stage index and barrier phase are kept as running counters: this lane's loop is a chain of
+        // dependent instructions, and a runtime division per slab would cost more than the copies' issue)
+        int issued = 0, s = 0, wraps = 0;
+        uint8_t *dst = smem + UG_W_BYTES;
+        for (int i = 0; i < nslab && !abort_flag; ++i) {
+            if (wraps > 0 && !mbar_wait_bounded(&free_bar[s], (wraps - 1) & 1, a.status, STATUS_UMMA_WAIT_MMA)) {
+                abort_flag = 1;
+                break;
+            }
+            mbar_arrive_expect_tx(&full_bar[s], mt_count * x_bytes);
+            for (int mt = 0; mt < mt_count; ++mt)
+                tma_load_2d(dst + mt * x_bytes, &xmap, i * UG_BK, m0 + mt * ntok, &full_bar[s]);
             issued = i + 1;
-        }
-        if (has_unit) {
-            float wv[32];
-            decode32<FMT>(row_ptr, i * 2 + uhalf, wv);
-            uint8_t *dst_row = stage + MT * UG_A_BYTES + (urow >> 3) * 1024 + (urow & 7) * 128;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint4 v;
-                v.x = pack_bf16(wv[8 * c + 0], wv[8 * c + 1]);
-                v.y = pack_bf16(wv[8 * c + 2], wv[8 * c + 3]);
-                v.z = pack_bf16(wv[8 * c + 4], wv[8 * c + 5]);
-                v.w = pack_bf16(wv[8 * c + 6], wv[8 * c + 7]);
-                const int chunk = (uhalf * 4 + c) ^ (urow & 7);            // 128-byte swizzle
-                *reinterpret_cast<uint4 *>(dst_row + chunk * 16) = v;
+            dst += stage_bytes;
+            if (++s == S) {
+                s = 0;
+                ++wraps;
+                dst = smem + UG_W_BYTES;
             }
         }
-        fence_proxy_async();          // the decoded slab must be visible to the tensor core's reads
-        __syncthreads();
         if (abort_flag) {
-            failed = true;
-            break;
-        }
-        if (tid == 0) {
-            if (!mbar_wait_bounded(&full_a[s], (i / UG_STAGES) & 1, a.status, STATUS_UMMA_WAIT_TMA)) {
-                abort_flag = 1;       // seen by everyone after the next barrier
-            } else {
-                tc_fence_after();
-                const uint64_t b_desc = smem_desc_sw128(stage + MT * UG_A_BYTES);
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    const uint64_t a_desc = smem_desc_sw128(stage + mt * UG_A_BYTES);
-#pragma unroll
-                    for (int kk = 0; kk < UG_BK / 16; ++kk)      // 16 BF16 = 32 bytes per step: +2 in the address field
-                        umma_bf16(tmem_d + mt * NT, a_desc + 2 * kk, b_desc + 2 * kk, IDESC, (i | kk) ? 1u : 0u);
-                }
-                umma_commit(&mma_done[s]);
+            // gave up somewhere: the copies already requested still write shared memory; they complete on
+            // their own within microseconds - give them that time before the CTA can exit
+            const uint64_t t0 = global_timer_ns();
+            while (issued > 0 && global_timer_ns() - t0 < 100000) {
             }
         }
+        }
+        __syncwarp();
+    } else if (warp == UG_DECODE_THREADS / 32) {
+        // ---------------------------------------------------------------- MMA issue (one lane, as above)
+        if (lane == 0) {
+        const uint32_t idesc = umma_idesc_bf16(UG_BM, ntok);
+        // descriptors advance by running additions (address field = bytes >> 4); see the note in the TMA lane
+        const uint64_t w_desc0 = smem_desc_sw128(smem);
+        const uint32_t stage_step = static_cast<uint32_t>(stage_bytes) >> 4, x_off = UG_W_BYTES >> 4,
+                       x_step = static_cast<uint32_t>(x_bytes) >> 4;
+        uint64_t w_desc = w_desc0;
+        uint32_t accumulate = 0;
+        int done_slabs = 0, s = 0, phase = 0;
+        for (int i = 0; i < nslab && !abort_flag; ++i) {
+            if (!mbar_wait_bounded(&full_bar[s], phase, a.status, STATUS_UMMA_WAIT_TMA)) {
+                abort_flag = 1;
+                break;
+            }
+            tc_fence_after();
+            for (int mt = 0; mt < mt_count; ++mt) {
+                const uint64_t x_desc = w_desc + x_off + mt * x_step;
+                const uint32_t d = tmem_d + mt * acc_stride;
+                umma_bf16(d, w_desc, x_desc, idesc, accumulate);              // 16 BF16 = 32 bytes per step:
+                umma_bf16(d, w_desc + 2, x_desc + 2, idesc, 1u);              // +2 in the address field
+                umma_bf16(d, w_desc + 4, x_desc + 4, idesc, 1u);
+                umma_bf16(d, w_desc + 6, x_desc + 6, idesc, 1u);
+            }
+            accumulate = 1u;
+            umma_commit(&free_bar[s]);
+            done_slabs = i + 1;
+            w_desc += stage_step;
+            if (++s == S) {
+                s = 0;
+                phase ^= 1;
+                w_desc = w_desc0;
+            }
+        }
+        if (done_slabs == nslab) umma_commit(&acc_done);
+        }
+        __syncwarp();
     }
 
-    if (!failed) {
-        // the last commit covers every MMA of the tile
-        const int last = nslab - 1;
-        if (!mbar_wait_bounded(&mma_done[last % UG_STAGES], (last / UG_STAGES) & 1, a.status, STATUS_UMMA_WAIT_MMA))
-            abort_flag = 1;
-        __syncthreads();
-        failed = abort_flag != 0;
+    // ---------------------------------------------------------------- epilogue (warps 0-7)
+    bool ok = !abort_flag;
+    if (ok && !mbar_wait_bounded(&acc_done, 0, a.status, STATUS_UMMA_WAIT_MMA)) {
+        abort_flag = 1;
+        ok = false;
     }
-    if (!failed) {
+    if (ok && warp < UG_DECODE_THREADS / 32) {
         tc_fence_after();
-        // warp w reads TMEM lanes 32*(w%4)..+31 (token rows) and the columns of its half of the tile
-        const int quarter = warp & 3, col_half = warp >> 2;
-        constexpr int COLS_PER_WARP = NT / 2;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            const int t = m0 + mt * UG_BM + 32 * quarter + lane;
-#pragma unroll
-            for (int c0 = 0; c0 < COLS_PER_WARP; c0 += 32) {
-                const int col = col_half * COLS_PER_WARP + c0;
+        chain_wait();        // y may still be read by what precedes this kernel on the stream
+        // warp w reads TMEM lanes 32*(w%4)..+31 = 32 weight rows; the 32-token chunks of every accumulator
+        // are dealt round-robin to the four groups of four warps
+        const int quarter = warp & 3;
+        const int row = n0 + 32 * quarter + lane;
+        const int nchunks = (ntok + 31) >> 5;
+        for (int mt = 0; mt < mt_count; ++mt) {
+            const int tile_t0 = m0 + mt * ntok;
+            if (tile_t0 >= a.m) break;                           // whole token tile beyond m (uniform in the CTA)
+            for (int c = warp >> 2; c < nchunks; c += UG_DECODE_THREADS / 128) {
                 uint32_t r[32];
-                tmem_ld32(tmem_d + (static_cast<uint32_t>(32 * quarter) << 16) + mt * NT + col, r);
+                tmem_ld32(tmem_d + (static_cast<uint32_t>(32 * quarter) << 16) + mt * acc_stride + 32 * c, r);
                 tmem_ld_wait();
-                if (t < a.m) {
-                    const int nbase = n0 + col;
-                    const size_t off = static_cast<size_t>(t) * a.n + nbase;
-                    const bool full = nbase + 32 <= a.n;
-                    if (a.y_dtype == B200Q_F32) {
-                        float *y = static_cast<float *>(a.y) + off;
-                        if (full && (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
+                if (row < a.n) {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                reinterpret_cast<uint4 *>(y)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (nbase + j < a.n) y[j] = __uint_as_float(r[j]);
-                        }
-                    } else {
-                        uint16_t *y = static_cast<uint16_t *>(a.y) + off;
-                        uint32_t packed[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const float lo = __uint_as_float(r[2 * j]), hi = __uint_as_float(r[2 * j + 1]);
-                            if (a.y_dtype == B200Q_BF16) packed[j] = pack_bf16(lo, hi);
-                            else {
-                                const __half2 h = __floats2half2_rn(lo, hi);
-                                packed[j] = *reinterpret_cast<const uint32_t *>(&h);
-                            }
-                        }
-                        if (full && (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                reinterpret_cast<uint4 *>(y)[j] =
-                                    make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (nbase + j < a.n)
-                                    y[j] = static_cast<uint16_t>((packed[j >> 1] >> (16 * (j & 1))) & 0xffffu);
-                        }
+                    for (int j = 0; j < 32; ++j) {
+                        const int t = tile_t0 + 32 * c + j;
+                        if (32 * c + j < ntok && t < a.m) store_out(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + row, r[j]);
                     }
                 }
             }
         }
-    } else if (tid == 0) {
-        // gave up: let what is in flight land (bounded) before the tensor memory is released
-        for (int i = max(0, issued - UG_STAGES); i < issued; ++i)
-            mbar_wait_bounded(&full_a[i % UG_STAGES], (i / UG_STAGES) & 1, a.status, STATUS_UMMA_WAIT_TMA);
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem_d, TMEM_COLS);
+    if (warp == 0) tmem_dealloc(tmem_d, tmem_cols);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -417,19 +557,13 @@ static EncodeTiledFn encode_tiled_fn() {
 
 using GemmFn = void (*)(const CUtensorMap, const UmmaGemmArgs);
 
-template <int FMT>
-static GemmFn pick_tile(int nt, int mt) {
-    if (nt == 128) return mt == 2 ? umma_gemm_kernel<FMT, 128, 2> : umma_gemm_kernel<FMT, 128, 1>;
-    return mt == 2 ? umma_gemm_kernel<FMT, 64, 2> : umma_gemm_kernel<FMT, 64, 1>;
-}
-
 }  // namespace b200q
 
 using namespace b200q;
 
 extern "C" int b200q_gemm_supported(int fmt, int n, int k, int x_dtype, int m) {
     if (fmt != B200Q_Q8_0 && fmt != B200Q_Q4_K && fmt != B200Q_Q5_K && fmt != B200Q_Q6_K) return 0;
-    if (x_dtype != B200Q_BF16 || n < 1 || m < 1 || k < UG_BK || k % UG_BK != 0 || k % fmt_elems(fmt) != 0) return 0;
+    if (x_dtype != B200Q_BF16 || n < 1 || m < 1 || k < 256 || k % 256 != 0) return 0;
     return 1;
 }
 
@@ -441,7 +575,7 @@ extern "C" int b200q_gemm(const void *w, int fmt, int n, int k, const void *x, i
     if (n <= 0 || m <= 0 || k <= 0 || k % fmt_elems(fmt) != 0)
         return fail(B200Q_EINVAL, "gemm: bad shape n=%d k=%d m=%d", n, k, m);
     if (!b200q_gemm_supported(fmt, n, k, x_dtype, m))
-        return fail(B200Q_EUNSUPPORTED, "gemm: needs BF16 activations and K a multiple of %d (use b200q_gemv)", UG_BK);
+        return fail(B200Q_EUNSUPPORTED, "gemm: needs BF16 activations and K a multiple of 256 (use b200q_gemv)");
     if (reinterpret_cast<uintptr_t>(x) & 15) return fail(B200Q_EUNSUPPORTED, "gemm: activations must be 16-byte aligned");
     if (reinterpret_cast<uintptr_t>(w) & 1) return fail(B200Q_EUNSUPPORTED, "gemm: weights must be 2-byte aligned");
     int *status = device_status_word();
@@ -449,38 +583,54 @@ extern "C" int b200q_gemm(const void *w, int fmt, int n, int k, const void *x, i
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return fail(B200Q_ECUDA, "gemm: the driver does not provide cuTensorMapEncodeTiled");
 
+    // Token tile: the whole batch rounded up to 16 when it fits one accumulator, else 256. Two tiles per
+    // CTA (every decoded weight slab then feeds 512 tokens) only when that still leaves a CTA for every SM.
+    const int ntok = m >= 256 ? 256 : (m + 15) / 16 * 16;
+    const int token_tiles = (m + ntok - 1) / ntok;
+    const int n_tiles = (n + UG_BM - 1) / UG_BM;
+    const int mt = (token_tiles >= 2 && static_cast<long long>(n_tiles) * ((token_tiles + 1) / 2) >= sm_count()) ? 2 : 1;
+    const int m_tiles = (token_tiles + mt - 1) / mt;
+    const int stage_bytes = UG_W_BYTES + mt * ntok * UG_BK * 2;
+    int stages = (224 * 1024) / stage_bytes;
+    if (stages > UG_MAX_STAGES) stages = UG_MAX_STAGES;
+
     CUtensorMap xmap;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(m)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
-    const cuuint32_t box[2] = {UG_BK, UG_BM};
+    const cuuint32_t box[2] = {UG_BK, static_cast<cuuint32_t>(ntok)};
     const cuuint32_t elem_strides[2] = {1, 1};
     const CUresult res = encode(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(x), dims, strides, box,
                                 elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (res != CUDA_SUCCESS) return fail(B200Q_ECUDA, "gemm: cuTensorMapEncodeTiled failed (%d)", static_cast<int>(res));
 
-    // Tile choice: two token tiles per CTA once there are more than 128 tokens (every decoded weight slab
-    // then feeds 256 tokens); 64 weight rows per CTA while 128 would leave most SMs without a tile.
-    const int mt = m > UG_BM ? 2 : 1;
-    const int m_tiles = (m + mt * UG_BM - 1) / (mt * UG_BM);
-    const int nt = (static_cast<long long>((n + 127) / 128) * m_tiles >= sm_count()) ? 128 : 64;
-    const int n_tiles = (n + nt - 1) / nt;
-
     UmmaGemmArgs a{};
     a.w = static_cast<const uint8_t *>(w);
     a.n = n; a.k = k; a.m = m;
     a.row_bytes = static_cast<long long>(k / fmt_elems(fmt)) * fmt_bytes(fmt);
-    a.y = y; a.y_dtype = y_dtype; a.status = status;
-    GemmFn fn = fmt == B200Q_Q8_0 ? pick_tile<B200Q_Q8_0>(nt, mt)
-              : fmt == B200Q_Q4_K ? pick_tile<B200Q_Q4_K>(nt, mt)
-              : fmt == B200Q_Q5_K ? pick_tile<B200Q_Q5_K>(nt, mt)
-                                  : pick_tile<B200Q_Q6_K>(nt, mt);
-    const size_t smem = static_cast<size_t>(UG_STAGES) * (mt * UG_A_BYTES + nt * UG_BK * 2) + 1024;
-    cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void *>(fn),
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (err != cudaSuccess) {
-        cudaGetLastError();
-        return fail(B200Q_ECUDA, "gemm: shared memory opt-in failed: %s", cudaGetErrorString(err));
+    a.y = y; a.y_dtype = y_dtype; a.ntok = ntok; a.mt = mt; a.stages = stages; a.status = status;
+    GemmFn fn = fmt == B200Q_Q8_0 ? umma_gemm_kernel<B200Q_Q8_0>
+              : fmt == B200Q_Q4_K ? umma_gemm_kernel<B200Q_Q4_K>
+              : fmt == B200Q_Q5_K ? umma_gemm_kernel<B200Q_Q5_K>
+                                  : umma_gemm_kernel<B200Q_Q6_K>;
+    const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024;
+    // the opt-in to large dynamic shared memory is per function and device: done once each
+    {
+        static std::mutex mu;
+        static std::vector<std::pair<const void *, int>> opted;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        std::lock_guard<std::mutex> lock(mu);
+        const std::pair<const void *, int> key(reinterpret_cast<const void *>(fn), dev);
+        if (std::find(opted.begin(), opted.end(), key) == opted.end()) {
+            cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void *>(fn),
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+            if (err != cudaSuccess) {
+                cudaGetLastError();
+                return fail(B200Q_ECUDA, "gemm: shared memory opt-in failed: %s", cudaGetErrorString(err));
+            }
+            opted.push_back(key);
+        }
     }
     launch_chained(fn, dim3(n_tiles, m_tiles), dim3(UG_THREADS), smem, static_cast<cudaStream_t>(stream), xmap, a);
     return check_launch("gemm");

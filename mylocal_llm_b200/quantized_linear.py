@@ -233,16 +233,20 @@ def quantized_linear(x, weight, *, block_k=512, cpu_packed_backend="reference", 
     return out.reshape(tuple(x.shape[:-1]) + (n,))
 
 
-GEMM_MIN_TOKENS = 17        # up to 16 tokens one GEMV pass reads the weights once; beyond, the tensor-core GEMM does
+# Tokens from which the tensor-core GEMM beats repeated GEMV passes (one pass serves 16 tokens): measured on
+# the [8192 x 2048] / [2048 x 8192] shapes, 17 for the 16-byte aligned formats, 48 for Q6_K / Q8_0, whose
+# 2-byte aligned blocks decode more slowly in the GEMM.
+GEMM_MIN_TOKENS = {"Q4_K": 17, "Q5_K": 17, "Q6_K": 48, "Q8_0": 48}
 
 
 def _use_gemm(weight, x, m, n, k, dt):
-    """More than 16 tokens of BF16 activations on a GGUF-layout weight go to the tcgen05 GEMM
-    (``b200q_gemm``: weights read once, BF16-weight precision); everything else stays on the GEMV
-    kernels (exact products, FP32 / FP16 activations, device tile layouts). ``B200Q_GEMM=0`` keeps
-    every call on the GEMV path."""
+    """Enough tokens of BF16 activations on a GGUF-layout weight go to the tcgen05 GEMM (``b200q_gemm``:
+    weights read once, BF16-weight precision); everything else stays on the GEMV kernels (exact
+    products, FP32 / FP16 activations, device tile layouts). ``B200Q_GEMM=0`` keeps every call on the
+    GEMV path."""
     import os
-    if m < GEMM_MIN_TOKENS or weight.quant_type in DEVICE_LAYOUTS or os.environ.get("B200Q_GEMM", "1") == "0":
+    if (weight.quant_type in DEVICE_LAYOUTS or m < GEMM_MIN_TOKENS.get(weight.quant_type, 1 << 30)
+            or os.environ.get("B200Q_GEMM", "1") == "0"):
         return False
     if x.data_ptr() % 16 or weight.data.data_ptr() % 2:
         return False
