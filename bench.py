@@ -64,6 +64,13 @@ WORKLOADS = {
     "gemv_q8_0_131072x4096_m16": ("Q8_0", 131072, 4096, 16, "bfloat16"),
     "gemv_q4k_65536x4096_m8": ("Q4_K", 65536, 4096, 8, "bfloat16"),
     "gemv_q4k_65536x4096_m16": ("Q4_K", 65536, 4096, 16, "bfloat16"),
+    # prefill / batched sizes of the second configuration: the tcgen05 GEMM (weights in GGUF layout, read once)
+    "gemm_q4k_8192x2048_m512": ("Q4_K", 8192, 2048, 512, "bfloat16"),
+    "gemm_q4k_2048x8192_m512": ("Q4_K", 2048, 8192, 512, "bfloat16"),
+    "gemm_q5k_8192x2048_m512": ("Q5_K", 8192, 2048, 512, "bfloat16"),
+    "gemm_q6k_8192x2048_m512": ("Q6_K", 8192, 2048, 512, "bfloat16"),
+    "gemm_q4k_8192x2048_m32": ("Q4_K", 8192, 2048, 32, "bfloat16"),
+    "gemm_q4k_8192x2048_m2048": ("Q4_K", 8192, 2048, 2048, "bfloat16"),
 }
 # name: (layers, tokens per step, chained)  - the packed MoE layer of the baseline's fourth configuration
 # (hidden 2048, 512 experts of width 512, top-10, shared expert, Q4_K gate/up + Q6_K down); "stack" = the
@@ -95,6 +102,17 @@ def measured_peaks():
         except Exception:
             pass
     return 6650.0, "fallback"
+
+
+def measured_tensor_peak():
+    """Sustained dense BF16 TFLOP/s (the bench times the kernel inside a long loop), else the stated fallback."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["bf16_tflops_sustained"]), "measured"
+        except Exception:
+            pass
+    return 1400.0, "fallback"
 
 
 class ClockSampler:
@@ -233,7 +251,7 @@ def cpu_gemv_throughput(fmt, n, k, m, act_bytes, seconds):
     per_pass = algorithmic_bytes(fmt, rows, k, m, act_bytes)
     gbs = per_pass * passes / elapsed / 1e9
     sample = f"{passes} passes over {rows} of {n} rows ({fmt}, K={k}, M={m}) in {elapsed:.1f} s"
-    return gbs, kind, threads, sample, elapsed / passes
+    return gbs, kind, threads, sample, elapsed / passes, 2.0 * m * rows * k * passes / elapsed / 1e12
 
 
 def run_reference_arm(args, name):
@@ -258,6 +276,12 @@ def run_reference_arm(args, name):
         "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    if m > 16:
+        tfl = statistics.mean(r[5] for r in timed)
+        line.update({"metric": "quantized GEMM TFLOP/s (2*M*N*K per launch / time)", "value": round(tfl, 6),
+                     "unit": "TFLOP/s", "dtype": "bf16"})
+        line["cpu_baseline"].update({"value": round(tfl, 6), "unit": "TFLOP/s"})
+        line["e2e"].update({"value": round(tfl, 6), "unit": "TFLOP/s"})
     print(json.dumps(line))
 
 
@@ -286,7 +310,8 @@ def run_gpu_arm(args, name):
     base = random_packed(fmt, (n, k), seed=1234 + rank, d=0.01, dmin=0.005)
     weights = []
     for c in range(copies):
-        weights.append(upload(base, act))   # a distinct HBM allocation per copy
+        # a distinct HBM allocation per copy; the GEMM workloads read the GGUF layout
+        weights.append(packed_to_device(base) if m > 16 else upload(base, act))
     rng = np.random.default_rng(7 + rank)
     host_x = torch.from_numpy(rng.normal(0, 1, (copies, m, k)).astype(np.float32)).to(act_dtype).pin_memory()
     dev_x = host_x.cuda()
@@ -362,8 +387,8 @@ def run_gpu_arm(args, name):
         peak, peak_kind = measured_peaks()
         per_gpu = per_launch * launches / (dev_ms * 1e-3) / 1e9
         want_cpu = world == 1 and not args.skip_cpu_baseline
-        cpu_gbs, cpu_kind, cpu_cores, cpu_sample, _ = (cpu_gemv_throughput(fmt, n, k, m, act_bytes, 12.0)
-                                                       if want_cpu else (None, None, None, None, None))
+        cpu_gbs, cpu_kind, cpu_cores, cpu_sample, _, cpu_tfl = (cpu_gemv_throughput(fmt, n, k, m, act_bytes, 12.0)
+                                                                if want_cpu else (None,) * 6)
         line = {
             "metric": "quant-GEMV HBM GB/s (algorithmic bytes per launch / time)",
             "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -387,9 +412,24 @@ def run_gpu_arm(args, name):
             "gpu_launches": launches,
             "clocks": clocks,
         }
+        if m > 16:
+            # a contraction: report FLOP/s against the measured tensor peak instead of bytes against HBM
+            tpeak, tkind = measured_tensor_peak()
+            flops = 2.0 * m * n * k
+            tfl = flops * launches / (dev_ms * 1e-3) / 1e12
+            line.update({"metric": "quantized GEMM TFLOP/s (2*M*N*K per launch / time)", "value": round(tfl * world, 2),
+                         "unit": "TFLOP/s", "dtype": "bf16"})
+            line["e2e"].update({"value": round(flops * launches * world / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s"})
+            line["roofline"] = {"bound": "tensor", "achieved": round(tfl, 2), "peak": tpeak, "unit": "TFLOP/s",
+                                "frac": round(tfl / tpeak, 4), "peak_source": f"of {tkind} (sustained BF16)",
+                                "traffic": None, "kernel": "umma_gemm_kernel (tcgen05.mma, TMEM accumulator, TMA activations)",
+                                "us_per_launch": round(dev_ms * 1e3 / launches, 3), "flops_per_launch": flops,
+                                "packed_weight_bytes": wbytes}
         if cpu_gbs is not None:
             line["cpu_baseline"] = {"value": round(cpu_gbs, 3), "unit": "GB/s", "cores": cpu_cores,
                                     "kind": cpu_kind, "sample": cpu_sample}
+            if m > 16:
+                line["cpu_baseline"].update({"value": round(cpu_tfl, 6), "unit": "TFLOP/s"})
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
