@@ -184,6 +184,8 @@ class ResidentExpertExecutor:
         self.model_id = model_id
         self.d_model, self.d_ff = first.d_model, first.d_ff
         self.compute_dtype = compute_dtype
+        self._dispatch_depth = 0
+        self.counters = {"gpu_experts": 0, "grouped_gpu_dispatches": 0}
 
     def bank(self, layer_id):
         return self.banks[int(layer_id)]
@@ -192,14 +194,46 @@ class ResidentExpertExecutor:
         """One expert's FFN on a batch of rows ``[M, D]``."""
         return self.bank(layer_id).expert(expert_id).forward(x)
 
+    @contextlib.contextmanager
     def dispatch_scope(self, layer_id, expert_ids):
-        return contextlib.nullcontext()
+        """Scope of one layer's dispatch (the reference pins the selected experts against eviction here,
+        ``expert_residency.py:539-560``; nothing can be evicted from a resident bank, so only the depth is
+        kept: ``try_forward_grouped`` is valid inside a scope only, as in the reference)."""
+        self._dispatch_depth += 1
+        try:
+            yield self
+        finally:
+            self._dispatch_depth -= 1
+
+    def try_forward_grouped(self, layer_id, expert_ids, x, routing_weights, slots):
+        """One-row grouped dispatch over resident experts, or ``None`` when the call is not eligible
+        (``expert_residency.py:1166-1193``): needs an open ``dispatch_scope``, a single FP32 row, expert
+        ids of this layer's bank and a layout the grouped kernels support. A decline changes no counter."""
+        from .grouped_quantized_experts import grouped_quantized_experts_forward, supports_grouped_quantized_experts
+        if not self._dispatch_depth or x.shape[0] != 1 or int(layer_id) not in self.banks:
+            return None
+        bank = self.banks[int(layer_id)]
+        ids = [int(e) for e in expert_ids]
+        if not ids or any(not 0 <= e < bank.n_experts for e in ids):
+            return None
+        experts = [bank.expert(e) for e in ids]
+        if not supports_grouped_quantized_experts(x, experts, routing_weights, routing_slots=None if slots is None
+                                                  else tuple(slots)):
+            return None
+        out = grouped_quantized_experts_forward(x, experts, routing_weights,
+                                                routing_slots=None if slots is None else tuple(slots))
+        self.counters["gpu_experts"] += len(experts)
+        self.counters["grouped_gpu_dispatches"] += 1
+        return out
 
     def forward_routed(self, layer_id, x2d, weights2d, ids2d, **kwargs):
+        """Device-side dispatch of any number of rows (plan, grouped kernels, ordered combine) with no
+        host round trip - the fast path ``ExpertsInference`` prefers when an executor offers it."""
         return routed_experts_forward(x2d, weights2d, ids2d, self.bank(layer_id), **kwargs)
 
     def statistics(self):
-        return {"resident_layers": len(self.banks), "resident_bytes": sum(b.nbytes for b in self.banks.values())}
+        return {"resident_layers": len(self.banks), "resident_bytes": sum(b.nbytes for b in self.banks.values()),
+                **self.counters}
 
 
 class ExpertsInference:
@@ -214,7 +248,14 @@ class ExpertsInference:
         self.layer_id = int(layer_id)
 
     def forward(self, x, weights, expert_indices, *, on_cpu_submitted=None):
-        """x [B,T,D]; weights [B,T,k]; expert_indices [B,T,k] -> [B,T,D] in x's dtype."""
+        """x [B,T,D]; weights [B,T,k]; expert_indices [B,T,k] -> [B,T,D] in x's dtype.
+
+        An executor that offers ``forward_routed`` (``ResidentExpertExecutor``) gets the whole dispatch
+        as device work. Any other executor is driven through the reference's own seam
+        (``mini_llm/ops/experts_inference.py:188-312``): inside ``dispatch_scope``, one row with
+        unique ids first tries ``try_forward_grouped(layer_id, ascending ids, x, weights, slots)``;
+        otherwise each active expert, in ascending id, runs ``forward(layer_id, id, rows)`` and its
+        route-weighted output is added to the rows' accumulators (FP32, rounded once at the end)."""
         batch, seq, d_model = x.shape
         k = weights.shape[-1]
         n = batch * seq
@@ -224,10 +265,48 @@ class ExpertsInference:
         ids = expert_indices.reshape(n, k)
         if not ids.is_contiguous():
             ids = ids.contiguous()
-        out = self.expert_executor.forward_routed(self.layer_id, x2d, weights.reshape(n, k), ids)
-        if on_cpu_submitted is not None:
+        executor = self.expert_executor
+        if hasattr(executor, "forward_routed"):
+            out = executor.forward_routed(self.layer_id, x2d, weights.reshape(n, k), ids)
+            if on_cpu_submitted is not None:
+                on_cpu_submitted()
+            return out.reshape(batch, seq, d_model)
+        return self._forward_reference_seam(x2d, weights.reshape(n, k), ids, on_cpu_submitted).reshape(batch, seq, d_model)
+
+    def _forward_reference_seam(self, x2d, weights2d, ids2d, on_cpu_submitted):
+        torch = _torch()
+        executor = self.expert_executor
+        n, k = ids2d.shape
+        host_ids = ids2d.detach().cpu().numpy().astype(np.int64)         # the reference plans on the host as well
+        if host_ids.min(initial=0) < 0 or host_ids.max(initial=0) >= self.n_experts:
+            raise ValueError("expert index outside [0, n_experts)")
+        active = [int(e) for e in np.unique(host_ids)]
+        singleton = n == 1 and len(active) == k                          # one row, no repeated id
+        acc = torch.zeros(x2d.shape, dtype=torch.float32, device=x2d.device)
+        called = False
+        with executor.dispatch_scope(self.layer_id, active):
+            grouped = getattr(executor, "try_forward_grouped", None)
+            if singleton and grouped is not None:
+                slot_of = {int(e): s for s, e in enumerate(host_ids[0])}
+                out = grouped(self.layer_id, active, x2d, weights2d.reshape(-1), tuple(slot_of[e] for e in active))
+                if out is not None:
+                    if on_cpu_submitted is not None:
+                        on_cpu_submitted()
+                    return out.to(x2d.dtype)
+            if on_cpu_submitted is not None:
+                on_cpu_submitted()
+                called = True
+            for e in active:
+                rows, slots = np.nonzero(host_ids == e)
+                order = np.argsort(rows, kind="stable")
+                rows_t = torch.as_tensor(rows[order], device=x2d.device)
+                slots_t = torch.as_tensor(slots[order], device=x2d.device)
+                out = executor.forward(self.layer_id, e, x2d.index_select(0, rows_t))
+                term = out.float() * weights2d[rows_t, slots_t].float()[:, None]
+                acc.index_add_(0, rows_t, term)                          # a row names an expert once per slot
+        if on_cpu_submitted is not None and not called:
             on_cpu_submitted()
-        return out.reshape(batch, seq, d_model)
+        return acc.to(x2d.dtype)
 
 
 def synthetic_bank(n_experts, d_model, d_ff, types=("Q4_K", "Q4_K", "Q6_K"), seed=0, device="cuda"):

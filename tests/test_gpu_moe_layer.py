@@ -245,3 +245,47 @@ def test_moe_layer_with_shared_expert_of_a_different_width(cuda):
     ref = po.moe_layer_fp64(hidden[0], w_router, k, 2.0 ** -14, experts,
                             tuple((w.data, w.shape, w.quant_type) for w in (sg, su, sd)), gate_vec)
     np.testing.assert_allclose(out, ref, rtol=4e-4, atol=8e-6)
+
+
+class SeamOnly:
+    """A resident executor seen only through the reference's three methods (no forward_routed)."""
+
+    def __init__(self, inner):
+        self.inner = inner
+
+    def forward(self, layer_id, expert_id, x):
+        return self.inner.forward(layer_id, expert_id, x)
+
+    def try_forward_grouped(self, *args):
+        return self.inner.try_forward_grouped(*args)
+
+    def dispatch_scope(self, layer_id, expert_ids):
+        return self.inner.dispatch_scope(layer_id, expert_ids)
+
+
+@pytest.mark.parametrize("tokens", [1, 6])
+def test_reference_executor_seam_agrees_with_the_device_dispatch(cuda, golden, tokens, kernel_family):
+    if kernel_family != "tensor":
+        pytest.skip("one kernel family is enough for the host-side seam")
+    bank, d, f, e, k = golden_bank(golden)
+    inner = ResidentExpertExecutor({0: bank})
+    rng = np.random.default_rng(tokens)
+    x = to_cuda(cuda, rng.normal(0, 1, (1, tokens, d)).astype(np.float32))
+    ids = to_cuda(cuda, np.stack([rng.permutation(e)[:k] for _ in range(tokens)])[None])
+    w = to_cuda(cuda, rng.random((1, tokens, k)).astype(np.float32))
+    fast = ExpertsInference(d, f, e, expert_executor=inner, layer_id=0).forward(x, w, ids)
+    seam = ExpertsInference(d, f, e, expert_executor=SeamOnly(inner), layer_id=0).forward(x, w, ids)
+    np.testing.assert_allclose(seam.cpu().numpy(), fast.cpu().numpy(), rtol=4e-4, atol=8e-6)
+    stats = inner.statistics()
+    assert stats["grouped_gpu_dispatches"] == (1 if tokens == 1 else 0)      # one row: the grouped hook ran
+    # outside a dispatch scope the hook declines, as the reference's does
+    assert inner.try_forward_grouped(0, [0, 1], x[0, :1], w[0, 0, :2].contiguous(), (0, 1)) is None
+    with inner.dispatch_scope(0, [0, 1]):
+        assert inner.try_forward_grouped(0, [0, e + 3], x[0, :1], w[0, 0, :2].contiguous(), (0, 1)) is None
+        got = inner.try_forward_grouped(0, [0, 1], x[0, :1], w[0, 0, :2].contiguous(), (1, 0))
+    trip = lambda i: tuple((golden[key][i], shape, fmt) for key, shape, fmt in (
+        ("moe_gate_bytes", (f, d), "Q4_K"), ("moe_up_bytes", (f, d), "Q4_K"), ("moe_down_bytes", (d, f), "Q6_K")))
+    x0 = x[0, :1].cpu().numpy()
+    wh = w[0, 0, :2].cpu().numpy()
+    ref = wh[1] * po.expert_ffn_fp64(x0, *trip(0)) + wh[0] * po.expert_ffn_fp64(x0, *trip(1))
+    np.testing.assert_allclose(got.cpu().numpy(), ref, rtol=4e-4, atol=8e-6)
