@@ -25,7 +25,9 @@ extern "C" {
 
 /* packed formats */
 #define B200Q_Q8_0 0
+#define B200Q_Q4_0 1
 #define B200Q_Q4_K 2
+#define B200Q_Q3_K 3
 #define B200Q_Q5_K 4
 #define B200Q_Q6_K 5
 /* Q6_K re-ordered on the device into 16-row x 1-super-block tiles (b200q_q6k_retile): same size, same

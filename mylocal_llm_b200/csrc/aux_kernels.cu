@@ -12,6 +12,22 @@ __device__ __forceinline__ float decode_one(const uint8_t *blk, int fmt, int e) 
         const float d = half_bits_to_float(blk[0] | (blk[1] << 8));
         return __fmul_rn(d, static_cast<float>(static_cast<int>(static_cast<int8_t>(blk[2 + e]))));
     }
+    if (fmt == B200Q_Q4_0) {        // 16 code bytes: low nibbles = values 0..15, high nibbles = 16..31; q - 8
+        const float d = half_bits_to_float(blk[0] | (blk[1] << 8));
+        const int q = ((blk[2 + (e & 15)] >> (4 * (e >> 4))) & 15) - 8;
+        return __fmul_rn(d, static_cast<float>(q));
+    }
+    if (fmt == B200Q_Q3_K) {
+        // hmask[32] | qs[64] | 12 scale bytes | d: two low bits from qs, minus 4 unless the mask bit is set,
+        // sixteen 6-bit scales minus 32 (mini_llm/ops/quantized_weight.py:251-265)
+        const float d = half_bits_to_float(blk[108] | (blk[109] << 8));
+        const int j = e & 31, low = (blk[32 + 32 * (e >> 7) + j] >> (2 * ((e >> 5) & 3))) & 3;
+        const int high = (blk[j] >> (e >> 5)) & 1;
+        const int s = e >> 4;
+        const int sc = (((blk[96 + (s & 7)] >> (4 * (s >> 3))) & 15) | (((blk[104 + (s & 3)] >> (2 * (s >> 2))) & 3) << 4)) - 32;
+        const float scale = __fmul_rn(d, static_cast<float>(sc));
+        return __fmul_rn(scale, static_cast<float>(low - ((high ^ 1) << 2)));
+    }
     if (fmt == B200Q_Q4_K || fmt == B200Q_Q5_K) {
         const float d = half_bits_to_float(blk[0] | (blk[1] << 8));
         const float dmin = half_bits_to_float(blk[2] | (blk[3] << 8));

@@ -13,14 +13,17 @@ namespace b200q {
 // ---------------------------------------------------------------------------------------------
 // Formats (block layouts: mini_llm/ops/quantized_weight.py:24-37 of the reference)
 // ---------------------------------------------------------------------------------------------
-__host__ __device__ constexpr int fmt_elems(int fmt) { return fmt == B200Q_Q8_0 ? 32 : 256; }
+__host__ __device__ constexpr int fmt_elems(int fmt) { return (fmt == B200Q_Q8_0 || fmt == B200Q_Q4_0) ? 32 : 256; }
 __host__ __device__ constexpr int fmt_bytes(int fmt) {
-    return fmt == B200Q_Q8_0 ? 34 : fmt == B200Q_Q4_K ? 144 : fmt == B200Q_Q5_K ? 176
-         : fmt == B200Q_Q6_K ? 210 : 0;
+    return fmt == B200Q_Q8_0 ? 34 : fmt == B200Q_Q4_0 ? 18 : fmt == B200Q_Q3_K ? 110 : fmt == B200Q_Q4_K ? 144
+         : fmt == B200Q_Q5_K ? 176 : fmt == B200Q_Q6_K ? 210 : 0;
 }
 inline bool fmt_valid(int fmt) {
-    return fmt == B200Q_Q8_0 || fmt == B200Q_Q4_K || fmt == B200Q_Q5_K || fmt == B200Q_Q6_K;
+    return fmt == B200Q_Q8_0 || fmt == B200Q_Q4_0 || fmt == B200Q_Q3_K || fmt == B200Q_Q4_K || fmt == B200Q_Q5_K ||
+           fmt == B200Q_Q6_K;
 }
+// The two legacy formats run on the FP32-lane kernels only (no tensor-core fragment builder, no tile layout).
+inline bool fmt_lanes_only(int fmt) { return fmt == B200Q_Q4_0 || fmt == B200Q_Q3_K; }
 inline bool dtype_valid(int dt) { return dt == B200Q_F32 || dt == B200Q_F16 || dt == B200Q_BF16; }
 inline size_t dtype_size(int dt) { return dt == B200Q_F32 ? 4 : 2; }
 

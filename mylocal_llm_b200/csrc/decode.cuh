@@ -289,4 +289,92 @@ struct LaneDecoder<B200Q_Q8_0> {
     }
 };
 
+// ------------------------------------------------------------------------------------------ Q4_0
+// 18-byte blocks of 32 values: fp16 d, 16 code bytes (low nibbles = values 0..15, high nibbles =
+// values 16..31), weight = d * (code - 8) (mini_llm/ops/quantized_weight.py:212-216).
+template <>
+struct LaneDecoder<B200Q_Q4_0> {
+    __device__ static __forceinline__ void load_x(const float *x, int k, int slice, int lane, float (&xr)[XREGS],
+                                                  float (&xs)[4 * 2]) {
+        LaneDecoder<B200Q_Q8_0>::load_x(x, k, slice, lane, xr, xs);       // 32 consecutive activations per block
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) s += xr[32 * t + i];
+            xs[4 * t] = s;
+        }
+    }
+    __device__ static __forceinline__ float dot(const uint8_t *row, int k, int slice, int lane,
+                                                const float (&xr)[XREGS], const float (&xs)[4 * 2]) {
+        float total = 0.f;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const int b = slice * 64 + t * 32 + lane;
+            if (b * 32 >= k) continue;
+            const uint8_t *blk = row + b * 18;  // 2-byte aligned
+            const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(blk));
+            float2 a0 = make_float2(0.f, 0.f), a1 = a0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t q = lds_u32_align2(blk + 2 + 4 * i);
+                fma_u8x4(q & 0x0f0f0f0fu, &xr[32 * t + 4 * i], a0, a1);
+                fma_u8x4((q >> 4) & 0x0f0f0f0fu, &xr[32 * t + 16 + 4 * i], a0, a1);
+            }
+            total += d * (((a0.x + a0.y) + (a1.x + a1.y)) - 8.0f * xs[4 * t]);
+        }
+        return total;
+    }
+};
+
+// ------------------------------------------------------------------------------------------ Q3_K
+// 110-byte super-blocks of 256 values: hmask[32] | qs[64] | 12 scale bytes | fp16 d. Value p takes its two
+// low bits from qs[32*(p/128) + p%32] >> 2*((p/32)%4) and is lowered by 4 unless bit p/32 of hmask[p%32]
+// is set; sixteen 6-bit scales (minus 32) apply per 16 values (mini_llm/ops/quantized_weight.py:251-265).
+// A lane covers 64 consecutive positions: one 32-byte half of qs at two shifts, two mask bits, four scales.
+template <>
+struct LaneDecoder<B200Q_Q3_K> {
+    __device__ static __forceinline__ void load_x(const float *x, int k, int slice, int lane, float (&xr)[XREGS],
+                                                  float (&xs)[4 * 2]) {
+        LaneDecoder<B200Q_Q4_K>::load_x(x, k, slice, lane, xr, xs);       // 64 consecutive activations
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) s += xr[16 * g + i];
+            xs[g] = s;
+        }
+    }
+    __device__ static __forceinline__ float dot(const uint8_t *row, int k, int slice, int lane,
+                                                const float (&xr)[XREGS], const float (&xs)[4 * 2]) {
+        const int sb = slice * 8 + (lane >> 2);
+        if (sb * 256 >= k) return 0.f;
+        const int j = lane & 3;                                  // positions 64j .. 64j+63 of the super-block
+        const uint8_t *blk = row + sb * 110;                     // 2-byte aligned
+        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(blk + 108));
+        const uint8_t *qs = blk + 32 + 32 * (j >> 1);
+        const int sh = 4 * (j & 1);                              // shifts 2*(2*(j&1)) and +2
+        float total = 0.f;
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {                   // 32 positions each: mask bit 2j + part
+            float2 a0 = make_float2(0.f, 0.f), a1 = a0, b0 = a0, b1 = a0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t q = lds_u32_align2(qs + 4 * i), h = lds_u32_align2(blk + 4 * i);
+                const uint32_t code = ((q >> (sh + 2 * part)) & 0x03030303u) | (((h >> (2 * j + part)) & 0x01010101u) << 2);
+                if (i < 4) fma_u8x4(code, &xr[32 * part + 4 * i], a0, a1);
+                else fma_u8x4(code, &xr[32 * part + 4 * i], b0, b1);
+            }
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int s = 4 * j + 2 * part + half;           // scale index = position / 16
+                const int sc = (((blk[96 + (s & 7)] >> (4 * (s >> 3))) & 15) | (((blk[104 + (s & 3)] >> (2 * (s >> 2))) & 3) << 4)) - 32;
+                const float sum = half ? (b0.x + b0.y) + (b1.x + b1.y) : (a0.x + a0.y) + (a1.x + a1.y);
+                total += (d * static_cast<float>(sc)) * (sum - 4.0f * xs[2 * part + half]);
+            }
+        }
+        return total;
+    }
+};
+
 }  // namespace b200q

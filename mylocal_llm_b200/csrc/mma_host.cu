@@ -83,6 +83,7 @@ int mma_tokens_per_pass(int fmt, int mode, int k, int x_dtype, bool tiled) {
 
 int mma_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) {
     *launched = false;
+    if (fmt_lanes_only(q.fmt_a) || fmt_lanes_only(q.fmt_b)) return B200Q_OK;    // FP32-lane kernels only
     if (direct_allowed() || q.tiled) {
         int rc = direct_try_launch(q, stream, launched);
         if (rc || *launched) return rc;

@@ -23,6 +23,9 @@ static KernelFn pick_b(int fb) {
 
 template <int MODE>
 static KernelFn pick_dual(int fa, int fb) {
+    // the two legacy formats pair only with themselves (keeps the number of kernel variants down)
+    if (fa == B200Q_Q4_0 && fb == B200Q_Q4_0) return stream_gemv_kernel<B200Q_Q4_0, B200Q_Q4_0, MODE>;
+    if (fa == B200Q_Q3_K && fb == B200Q_Q3_K) return stream_gemv_kernel<B200Q_Q3_K, B200Q_Q3_K, MODE>;
     switch (fa) {
         case B200Q_Q8_0: return pick_b<MODE, B200Q_Q8_0>(fb);
         case B200Q_Q4_K: return pick_b<MODE, B200Q_Q4_K>(fb);
@@ -39,6 +42,8 @@ static KernelFn pick_single(int fa) {
         case B200Q_Q4_K: return stream_gemv_kernel<B200Q_Q4_K, B200Q_Q4_K, MODE>;
         case B200Q_Q5_K: return stream_gemv_kernel<B200Q_Q5_K, B200Q_Q5_K, MODE>;
         case B200Q_Q6_K: return stream_gemv_kernel<B200Q_Q6_K, B200Q_Q6_K, MODE>;
+        case B200Q_Q4_0: return stream_gemv_kernel<B200Q_Q4_0, B200Q_Q4_0, MODE>;
+        case B200Q_Q3_K: return stream_gemv_kernel<B200Q_Q3_K, B200Q_Q3_K, MODE>;
     }
     return nullptr;
 }
@@ -234,6 +239,7 @@ int b200q_swiglu(const void *gate, int gate_fmt, const void *up, int up_fmt, int
     int rc = plan_tiles(a, true, mt);
     if (rc) return rc;
     KernelFn fn = pick_dual<1>(gate_fmt, up_fmt);
+    if (!fn) return fail(B200Q_EUNSUPPORTED, "swiglu: Q4_0 / Q3_K pair only with the same format");
     int grid = sm_count();
     const int min_rows = a.rows_per_tile < 4 ? a.rows_per_tile : 4;
     if (static_cast<long long>(grid) * min_rows > f) grid = (f + min_rows - 1) / min_rows;
@@ -306,6 +312,7 @@ int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, 
         return fail(B200Q_EUNSUPPORTED, "moe_gate_up: d=%d too large for %d tokens per segment", d, MAX_TOKENS);
     int rc = plan_tiles(a, true, MAX_TOKENS);
     if (rc) return rc;
+    if (!pick_dual<2>(gate_fmt, up_fmt)) return fail(B200Q_EUNSUPPORTED, "moe_gate_up: Q4_0 / Q3_K pair only with the same format");
     return launch(pick_dual<2>(gate_fmt, up_fmt), a, true, sm_count(), static_cast<cudaStream_t>(stream),
                   "moe_gate_up");
 }

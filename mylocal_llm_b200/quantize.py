@@ -119,7 +119,50 @@ def quantize_q6_k(w):
     return PackedGGUFWeight(raw.reshape(-1), w.shape, "Q6_K")
 
 
-QUANTIZERS = {"Q8_0": quantize_q8_0, "Q4_K": quantize_q4_k, "Q5_K": quantize_q5_k, "Q6_K": quantize_q6_k}
+def quantize_q4_0(w):
+    """32-value blocks: d = -(value of largest magnitude) / 8, codes round(w / d) + 8 clipped to 0..15."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    blocks = w.reshape(-1, 32)
+    pick = np.argmax(np.abs(blocks), axis=1)
+    extreme = blocks[np.arange(blocks.shape[0]), pick]
+    d = (extreme / -8.0).astype("<f2")
+    d32 = d.astype(np.float32)
+    q = np.clip(np.round(blocks / np.where(d32 != 0, d32, 1.0)[:, None]) + 8, 0, 15).astype(np.uint8)
+    raw = np.concatenate([d.view(np.uint8).reshape(-1, 2), q[:, :16] | (q[:, 16:] << 4)], axis=1)
+    return PackedGGUFWeight(raw.reshape(-1), w.shape, "Q4_0")
+
+
+def quantize_q3_k(w):
+    """256-value super-blocks, sixteen groups of 16 with signed 6-bit scales and 3-bit codes in -4..3."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    sub = w.reshape(-1, 16, 16)
+    pick = np.argmax(np.abs(sub), axis=2)
+    extreme = np.take_along_axis(sub, pick[:, :, None], axis=2)[:, :, 0]
+    scale = extreme / -4.0                                     # the extreme value maps to code -4
+    d = (np.abs(scale).max(axis=1) / 31.0).astype("<f2").astype(np.float32)
+    d_safe = np.where(d > 0, d, 1.0)
+    sc = np.clip(np.round(scale / d_safe[:, None]), -32, 31).astype(np.int32)
+    eff = d[:, None] * sc.astype(np.float32)
+    q = np.clip(np.round(sub / np.where(eff != 0, eff, 1.0)[:, :, None]), -4, 3).astype(np.int32).reshape(-1, 256)
+    nb = q.shape[0]
+    raw = np.zeros((nb, 110), np.uint8)
+    code = (q + 4).astype(np.uint8)                            # 0..7: bit 2 = "not lowered by 4" flag, bits 0-1 = low
+    pos = np.arange(256)
+    for p0 in range(0, 256, 32):
+        blk = code[:, p0:p0 + 32]
+        raw[:, 0:32] |= ((blk >> 2) & 1) << (p0 // 32)
+        at = 32 + 32 * (p0 // 128)
+        raw[:, at:at + 32] |= (blk & 3) << (2 * ((p0 // 32) % 4))
+    stored = (sc + 32).astype(np.uint8)                        # 6-bit field
+    for s_i in range(16):
+        raw[:, 96 + (s_i & 7)] |= (stored[:, s_i] & 15) << (4 * (s_i >> 3))
+        raw[:, 104 + (s_i & 3)] |= ((stored[:, s_i] >> 4) & 3) << (2 * (s_i >> 2))
+    raw[:, 108:110] = _f16_bytes(d)
+    return PackedGGUFWeight(raw.reshape(-1), w.shape, "Q3_K")
+
+
+QUANTIZERS = {"Q8_0": quantize_q8_0, "Q4_0": quantize_q4_0, "Q3_K": quantize_q3_k, "Q4_K": quantize_q4_k,
+              "Q5_K": quantize_q5_k, "Q6_K": quantize_q6_k}
 
 
 def quantize(w, quant_type):
@@ -135,6 +178,8 @@ def set_sane_scales(raw, quant_type, d=None, dmin=None):
     """Overwrite the FP16 scale fields of random blocks ``raw`` [nb, block_bytes] with finite values."""
     if quant_type == "Q6_K":
         raw[:, 208:210] = _f16_bytes(np.asarray([1 / 1024 if d is None else d], np.float32))
+    elif quant_type == "Q3_K":
+        raw[:, 108:110] = _f16_bytes(np.asarray([1 / 256 if d is None else d], np.float32))
     elif quant_type in ("Q4_K", "Q5_K"):
         raw[:, 0:2] = _f16_bytes(np.asarray([0.03125 if d is None else d], np.float32))
         raw[:, 2:4] = _f16_bytes(np.asarray([0.015625 if dmin is None else dmin], np.float32))

@@ -16,6 +16,8 @@ import numpy as np
 # elements per block, bytes per block (GGUF packs along the innermost dimension)
 BLOCK_FORMATS = {
     "Q8_0": (32, 34),
+    "Q4_0": (32, 18),
+    "Q3_K": (256, 110),
     "Q4_K": (256, 144),
     "Q5_K": (256, 176),
     "Q6_K": (256, 210),

@@ -27,7 +27,7 @@ REF_SO = HERE / "_ref" / "libref_packed_cpu.so"
 REFERENCE_ROOT = Path(os.environ.get("MYLOCAL_REFERENCE_ROOT") or HERE.parent.parent / "reference")
 REFERENCE_CPP = REFERENCE_ROOT / "mini_llm" / "ops" / "native_packed_cpu.cpp"
 
-FORMAT_ID = {"Q8_0": 0, "Q4_K": 2, "Q5_K": 4, "Q6_K": 5}
+FORMAT_ID = {"Q8_0": 0, "Q4_0": 1, "Q4_K": 2, "Q3_K": 3, "Q5_K": 4, "Q6_K": 5}
 _LOCK = threading.Lock()
 _LIBS = {}
 

@@ -18,8 +18,11 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def golden():
     """Golden vectors produced by the reference (tests/golden/make_golden.py)."""
-    with np.load(ROOT / "tests" / "golden" / "packed_golden.npz") as data:
-        return {key: data[key] for key in data.files}
+    merged = {}
+    for name in ("packed_golden.npz", "legacy_formats_golden.npz"):
+        with np.load(ROOT / "tests" / "golden" / name) as data:
+            merged.update({key: data[key] for key in data.files})
+    return merged
 
 
 @pytest.fixture(scope="session")

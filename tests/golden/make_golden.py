@@ -170,5 +170,39 @@ def main():
     print("wrote", path, path.stat().st_size, "bytes,", len(out), "arrays")
 
 
+def legacy_formats():
+    """Q4_0 and Q3_K (the two remaining FP32-lane formats of the reference's packed GPU path): decoder and
+    linear fixtures, written to a file of their own so the first file's arrays keep their values."""
+    out = {}
+    rng = np.random.default_rng(4103)
+    for fmt in ("Q4_0", "Q3_K"):
+        k = 64 if fmt == "Q4_0" else 512
+        rnd = random_packed(fmt, (5, k), seed=2000 + ord(fmt[1]))
+        out[f"deq_{fmt}_random_bytes"] = rnd.data.copy()
+        out[f"deq_{fmt}_random_shape"] = np.asarray(rnd.shape)
+        out[f"deq_{fmt}_random_out"] = ref_weight(rnd).dequantize_reference()
+        w = rng.normal(0, 0.02, (3, k)).astype(np.float32)
+        qz = quantize(w, fmt)
+        out[f"deq_{fmt}_quant_bytes"] = qz.data.copy()
+        out[f"deq_{fmt}_quant_shape"] = np.asarray(qz.shape)
+        out[f"deq_{fmt}_quant_src"] = w
+        out[f"deq_{fmt}_quant_out"] = ref_weight(qz).dequantize_reference()
+        n, k, m = 13, 768 if fmt != "Q4_0" else 96, 3
+        wq = random_packed(fmt, (n, k), seed=88 + ord(fmt[1]))
+        x = rng.normal(0, 1, (m, k)).astype(np.float32)
+        out[f"lin_{fmt}_bytes"] = wq.data.copy()
+        out[f"lin_{fmt}_shape"] = np.asarray(wq.shape)
+        out[f"lin_{fmt}_x"] = x
+        out[f"lin_{fmt}_y_numpy"] = ref_linear(x, ref_weight(wq), cpu_packed_backend="reference")
+        out[f"lin_{fmt}_y_native"] = ref_linear(x, ref_weight(wq), cpu_packed_backend="native")
+    path = HERE / "legacy_formats_golden.npz"
+    np.savez_compressed(path, **out)
+    print("wrote", path, path.stat().st_size, "bytes,", len(out), "arrays")
+
+
 if __name__ == "__main__":
-    main()
+    which = sys.argv[1:] or ["packed", "legacy"]
+    if "packed" in which:
+        main()
+    if "legacy" in which:
+        legacy_formats()

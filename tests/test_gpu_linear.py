@@ -27,7 +27,7 @@ def kernel_family(request, monkeypatch):
     "lanes" the FP32-lane kernel."""
     monkeypatch.setenv("B200Q_KERNEL", {"tensor": "auto", "staged": "staged", "lanes": "lanes"}[request.param])
     return request.param
-FORMATS = ("Q8_0", "Q4_K", "Q5_K", "Q6_K")
+FORMATS = ("Q8_0", "Q4_0", "Q3_K", "Q4_K", "Q5_K", "Q6_K")
 
 
 def to_cuda(torch, a, dtype=None):
@@ -121,13 +121,15 @@ def test_linear_config0_shape_q8_0(cuda):
 
 @pytest.mark.parametrize("fmt", ["Q4_K", "Q5_K", "Q6_K"])
 @pytest.mark.parametrize("shape", [(8192, 2048), (2048, 8192)])
-def test_linear_config1_shapes_bf16(cuda, fmt, shape, kernel_family):
+def test_linear_config1_shapes_bf16(cuda, fmt, shape, kernel_family, monkeypatch):
     """Second benchmark configuration: both matrix shapes, the three K-quant formats, BF16 activations
     at every batch size it names (1, 8, 32, 512), BF16 and FP32 outputs. Random-byte weights keep the
     host side fast. Band: the reference's FP16 band (rtol 2e-2 / atol 6e-3, tests/test_0106c:99-100),
     its absolute part scaled by the RMS of the outputs (these weights give outputs of O(100), the
     reference's fixtures O(1)); FP32 outputs of the same BF16 inputs must be 100x closer. Batches the
     GEMM serves get the BF16-weight bound stated below instead."""
+    if kernel_family != "tensor":
+        monkeypatch.setenv("B200Q_GEMM", "0")          # these families cover the GEMV passes at 32 tokens as well
     w = random_packed(fmt, shape, seed=shape[0], d=0.01, dmin=0.005)
     dw = packed_to_device(w)
     dense = bo.port_dequantize(w.data, w.shape, fmt).astype(np.float64)
@@ -222,6 +224,7 @@ def test_swiglu_and_expert_ffn_match_reference_golden(cuda, golden):
 
 
 @pytest.mark.parametrize("gf,uf", [("Q4_K", "Q4_K"), ("Q5_K", "Q5_K"), ("Q6_K", "Q6_K"), ("Q8_0", "Q8_0"),
+                                   ("Q4_0", "Q4_0"), ("Q3_K", "Q3_K"),
                                    ("Q4_K", "Q6_K"), ("Q8_0", "Q4_K"), ("Q6_K", "Q5_K")])
 @pytest.mark.parametrize("m", [1, 5])
 def test_swiglu_mixed_formats(cuda, gf, uf, m):

@@ -17,6 +17,12 @@ from mylocal_llm_b200.quantized_linear import retile_weight
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def gemv_passes_only(monkeypatch):
+    """This file is about the GEMV kernels' token tiles; more than 16 BF16 tokens would otherwise go to the GEMM."""
+    monkeypatch.setenv("B200Q_GEMM", "0")
+
+
 def weights(fmt, n, k, seed, tile):
     rng = np.random.default_rng(seed)
     w = quantize(rng.normal(0, 0.02, (n, k)).astype(np.float32), fmt)

@@ -52,8 +52,10 @@ def test_entry_points_validate_before_launching():
 
 
 def test_block_formats_and_support_table():
-    assert BLOCK_FORMATS == {"Q8_0": (32, 34), "Q4_K": (256, 144), "Q5_K": (256, 176), "Q6_K": (256, 210)}
-    assert all(supports_packed_gpu_type(f) for f in FORMATS)
+    # the six FP32-lane formats of the reference's packed GPU path (mini_llm/ops/quantized_linear.py:34)
+    assert BLOCK_FORMATS == {"Q8_0": (32, 34), "Q4_0": (32, 18), "Q3_K": (256, 110), "Q4_K": (256, 144),
+                             "Q5_K": (256, 176), "Q6_K": (256, 210)}
+    assert all(supports_packed_gpu_type(f) for f in BLOCK_FORMATS)
     assert not supports_packed_gpu_type("IQ2_S")
 
 

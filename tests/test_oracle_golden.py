@@ -13,7 +13,7 @@ import pytest
 from oracle import packed_oracle as po
 from oracle import build_oracle as bo
 
-FORMATS = ("Q8_0", "Q4_K", "Q5_K", "Q6_K")
+FORMATS = ("Q8_0", "Q4_0", "Q3_K", "Q4_K", "Q5_K", "Q6_K")
 
 
 def f16(value):
@@ -109,7 +109,7 @@ def test_dequantize_matches_reference_bit_for_bit(golden, fmt, kind):
 @pytest.mark.parametrize("fmt", FORMATS)
 def test_quantiser_fixture_is_close_to_its_source(golden, fmt):
     src, out = golden[f"deq_{fmt}_quant_src"], golden[f"deq_{fmt}_quant_out"]
-    bound = {"Q8_0": 0.005, "Q4_K": 0.08, "Q5_K": 0.04, "Q6_K": 0.03}[fmt]
+    bound = {"Q8_0": 0.005, "Q4_0": 0.14, "Q3_K": 0.3, "Q4_K": 0.08, "Q5_K": 0.04, "Q6_K": 0.03}[fmt]
     assert np.abs(out - src).max() <= bound * np.abs(src).max()
 
 
@@ -219,7 +219,7 @@ def test_port_matches_reference_cpu_library(fmt):
         pytest.skip("oracle/_ref was not built (no reference tree on this machine)")
     from mylocal_llm_b200.quantize import random_packed
     qk, _ = po.BLOCKS[fmt]
-    n, k = 19, 3 * qk if fmt != "Q8_0" else 160
+    n, k = 19, 3 * qk if qk == 256 else 160
     w = random_packed(fmt, (n, k), seed=5)
     x = np.random.default_rng(6).normal(0, 1, (3, k)).astype(np.float32)
     y_ref = bo.cpu_gemv(ref, w.data, fmt, n, k, x)
