@@ -19,13 +19,14 @@ adapter; here they stay packed and resident in HBM, which is the point of the ex
 """
 
 import ctypes
+import os
 from dataclasses import dataclass
 
 import numpy as np
 
 from . import _lib
 from .moe_layer import RMSNormInference
-from .quantized_linear import (DevicePackedGGUFWeight, dequantize_device, packed_to_device, quantized_linear,
+from .quantized_linear import (GEMM_MIN_TOKENS, DevicePackedGGUFWeight, dequantize_device, packed_to_device, quantized_linear,
                                quantized_swiglu, retile_enabled, retile_gate_up, retile_weight)
 from .quantized_weight import PackedGGUFWeight, block_format
 
@@ -142,8 +143,21 @@ class ExternalLlamaModel:
                 return None
             data = torch.cat([w.data for w in parts])
             rows = sum(w.shape[0] for w in parts)
-            return self._matrix(DevicePackedGGUFWeight(data, (rows, parts[0].shape[1]), parts[0].quant_type))
+            return with_prefill_copy(DevicePackedGGUFWeight(data, (rows, parts[0].shape[1]), parts[0].quant_type))
 
+        def with_prefill_copy(native):
+            """The matrix in the layout the decode kernels read (a tile layout where there is one) and,
+            kept beside it under ``native_of``, the GGUF-layout bytes when they differ: the tensor-core
+            GEMM that serves many-token calls (prefill) reads the GGUF layout. Costs one more copy of
+            the packed bytes in HBM (1.8 GB for a 1.7B Q8_0 model); ``B200Q_PREFILL_GEMM=0`` skips it."""
+            native = self._matrix(native, tile=False)
+            decode = self._matrix(native)
+            if (decode is not native and self.dtype == torch.bfloat16
+                    and os.environ.get("B200Q_PREFILL_GEMM", "1") != "0"):
+                self.native_of[id(decode)] = native
+            return decode
+
+        self.native_of = {}
         self.embed = self._matrix(weights["model.embed_tokens.weight"], tile=False)     # rows are gathered
         self.lm_head = self.embed if cfg.tie_word_embeddings else self._matrix(weights["lm_head.weight"])
         if cfg.tie_word_embeddings and retile_enabled():
@@ -156,15 +170,15 @@ class ExternalLlamaModel:
                 "norm1": norm(p + "input_layernorm.weight"), "norm2": norm(p + "post_attention_layernorm.weight"),
                 "qkv": stacked([p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight",
                                 p + "self_attn.v_proj.weight"]),
-                "o": self._matrix(weights[p + "self_attn.o_proj.weight"]),
+                "o": with_prefill_copy(weights[p + "self_attn.o_proj.weight"]),
                 "gate": self._matrix(weights[p + "mlp.gate_proj.weight"], tile=False),
                 "up": self._matrix(weights[p + "mlp.up_proj.weight"], tile=False),
-                "down": self._matrix(weights[p + "mlp.down_proj.weight"]),
+                "down": with_prefill_copy(weights[p + "mlp.down_proj.weight"]),
             })
             layer = self.layers[-1]
             if layer["qkv"] is None:
                 for key, name in (("q", "q_proj"), ("k", "k_proj"), ("v", "v_proj")):
-                    layer[key] = self._matrix(weights[p + f"self_attn.{name}.weight"])
+                    layer[key] = with_prefill_copy(weights[p + f"self_attn.{name}.weight"])
             layer["gate_up"] = None
             if layer["gate"].quant_type == layer["up"].quant_type == "Q8_0" and retile_enabled():
                 # no fused SwiGLU kernel reads Q8_0 tiles: one tiled GEMV for both, then the product
@@ -188,7 +202,7 @@ class ExternalLlamaModel:
         for layer in self.layers:
             total += sum(layer[n].nbytes for n in ("qkv", "q", "k", "v", "o", "gate_up", "gate", "up", "down")
                          if layer.get(n) is not None)
-        return total
+        return total + sum(w.nbytes for w in self.native_of.values())
 
     # ------------------------------------------------------------------------------ running
     def _require_weights(self):
@@ -218,6 +232,14 @@ class ExternalLlamaModel:
         x0, x1 = x[..., :half], x[..., half:]
         return torch.cat([x0 * cos - x1 * sin, x0 * sin + x1 * cos], dim=-1)
 
+    def _linear(self, x, weight, out_dtype=None):
+        """Packed projection: calls of many BF16 rows (prefill) read the GGUF-layout copy, which the
+        tensor-core GEMM serves with one pass over the weights; everything else reads the decode layout."""
+        native = self.native_of.get(id(weight))
+        if native is not None and x.dtype == _torch().bfloat16 and x.shape[0] >= GEMM_MIN_TOKENS.get(native.quant_type, 1 << 30):
+            return quantized_linear(x, native, out_dtype=out_dtype)
+        return quantized_linear(x, weight, out_dtype=out_dtype)
+
     def _forward(self, token_ids, state, positions, mask):
         """token_ids [B, T]; positions [T] device int64; mask [T, horizon] additive FP32. Returns the
         final normalised hidden states [B*T, d] in the model dtype."""
@@ -230,12 +252,12 @@ class ExternalLlamaModel:
         for i, layer in enumerate(self.layers):
             qd, kd = heads * dh, kv_heads * dh
             if layer["qkv"] is not None:                     # one launch for the three projections
-                qkv = quantized_linear(hidden, layer["qkv"], out_dtype=torch.float32)
+                qkv = self._linear(hidden, layer["qkv"], torch.float32)
                 q2, k2, v2 = qkv[:, :qd], qkv[:, qd:qd + kd], qkv[:, qd + kd:]
             else:
-                q2 = quantized_linear(hidden, layer["q"], out_dtype=torch.float32)
-                k2 = quantized_linear(hidden, layer["k"], out_dtype=torch.float32)
-                v2 = quantized_linear(hidden, layer["v"], out_dtype=torch.float32)
+                q2 = self._linear(hidden, layer["q"], torch.float32)
+                k2 = self._linear(hidden, layer["k"], torch.float32)
+                v2 = self._linear(hidden, layer["v"], torch.float32)
             if t == 1 and dh in (64, 128) and self.fused_decode:
                 # one-token step: RoPE + cache store, then single-query attention, one kernel each
                 ptr = lambda x: ctypes.c_void_p(x.data_ptr())
@@ -263,7 +285,7 @@ class ExternalLlamaModel:
             scores = torch.matmul(q.permute(0, 2, 1, 3), keys.transpose(-1, -2)) * (dh ** -0.5) + mask
             ctx = torch.matmul(torch.softmax(scores, dim=-1), values)            # [B, heads, T, dh]
             ctx = ctx.permute(0, 2, 1, 3).reshape(b * t, heads * dh).to(self.dtype).contiguous()
-            attn = quantized_linear(ctx, layer["o"])
+            attn = self._linear(ctx, layer["o"])
             residual, hidden = layer["norm2"].forward_residual_add(residual, attn)
             hidden, residual = self._ffn(i, layer, hidden, residual)
         return hidden
@@ -273,14 +295,14 @@ class ExternalLlamaModel:
         updated FP32 residual stream."""
         torch = _torch()
         if layer["gate_up"] is not None:
-            gu = quantized_linear(hidden, layer["gate_up"], out_dtype=torch.float32)
+            gu = self._linear(hidden, layer["gate_up"], torch.float32)
             f = gu.shape[1] // 2
             act = torch.empty((gu.shape[0], f), dtype=self.dtype, device=gu.device)
             _lib.call("b200q_silu_mul", ctypes.c_void_p(gu.data_ptr()), gu.shape[0], f, ctypes.c_void_p(act.data_ptr()),
                       _lib.DTYPE_ID[str(self.dtype).replace("torch.", "")], _lib.current_stream())
         else:
             act = quantized_swiglu(hidden, layer["gate"], layer["up"])
-        ffn = quantized_linear(act, layer["down"])
+        ffn = self._linear(act, layer["down"])
         nxt = self.layers[i + 1]["norm1"] if i + 1 < len(self.layers) else self.final_norm
         residual, hidden = nxt.forward_residual_add(residual, ffn)
         return hidden, residual

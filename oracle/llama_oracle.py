@@ -9,9 +9,13 @@ the native block it drives (pre-norm residual block: ``x += attn(norm1(x)); x +=
 ``theta_i = pos / base**(2i/d_head)`` (``mini_llm/ops/attention_inference.py:255-277``), causal
 attention scaled by ``1/sqrt(d_head)`` with grouped KV heads, and the SwiGLU FFN
 ``down(silu(gate x) * (up x))``. Packed matrices enter through the bit-exact dequantiser of
-``packed_oracle``; parity of the GPU model is therefore "unpinned" against reference outputs (the
-reference's Llama adapter expands weights to dense and needs its whole native engine) and pinned
-only through the operators it is made of.
+``packed_oracle``.
+
+Parity is PINNED: ``tests/test_llama_golden.py`` checks ``llama_logits`` against logits the reference's
+own ``ExternalLlamaModel`` produced in this repository's build container (NumPy backend, FP32, Q8_0
+weights handed over dequantised as its GGUF reader does; ``tests/golden/make_golden.py llama`` ->
+``tests/golden/llama_golden.npz``): the prompt's last position and three greedy decode steps agree
+within FP32 rounding (rtol 2e-4).
 """
 
 import numpy as np

@@ -200,9 +200,55 @@ def legacy_formats():
     print("wrote", path, path.stat().st_size, "bytes,", len(out), "arrays")
 
 
+LLAMA_CONFIG = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2,
+                    num_key_value_heads=1, head_dim=64, vocab_size=256, max_position_embeddings=64,
+                    rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False)
+
+
+def llama():
+    """The reference's ExternalLlamaModel (mini_llm/external/llama_model.py, NumPy backend, FP32) on Q8_0
+    weights: every matrix is quantised to Q8_0, and the reference is fed what its GGUF reader hands it for
+    such a tensor - the dequantised dense FP32 matrix (mini_llm/external/gguf_loader.py). Stored: the packed
+    bytes, the norm vectors, a prompt, the logits of the prompt's last position and of three greedy
+    decode steps."""
+    from mini_llm.external import ExternalLlamaModel as RefLlama
+    from mini_llm.external.config import ExternalLlamaConfig as RefConfig
+    cfg = RefConfig(**LLAMA_CONFIG)
+    model = RefLlama(cfg, dtype="float32")
+    rng = np.random.default_rng(85)
+    out, dense = {}, {}
+    for name, shape in model.expected_shapes().items():
+        if name.endswith("norm.weight") or "layernorm.weight" in name:
+            dense[name] = (np.ones(shape, dtype=np.float32) + 0.025 * rng.normal(size=shape)).astype(np.float32)
+            out["norm:" + name] = dense[name]
+        else:
+            packed = quantize((rng.normal(size=shape) * 0.07).astype(np.float32), "Q8_0")
+            out["q8:" + name] = packed.data.copy()
+            dense[name] = ref_weight(packed).dequantize_reference()
+    model.set_weights(dense)
+    prompt = rng.integers(0, cfg.vocab_size, (1, 12))
+    state = model.create_generation_state(1, 32)
+    logits = np.asarray(model.prefill(prompt, state), dtype=np.float32)
+    logits = logits.reshape(-1, cfg.vocab_size)[-1]
+    steps, tokens = [logits], []
+    for _ in range(3):
+        token = int(np.argmax(steps[-1]))
+        tokens.append(token)
+        step = np.asarray(model.decode_one(np.asarray([[token]]), state), dtype=np.float32)
+        steps.append(step.reshape(-1, cfg.vocab_size)[-1])
+    out["prompt"] = prompt.astype(np.int64)
+    out["greedy_tokens"] = np.asarray(tokens, np.int64)
+    out["logits"] = np.stack(steps)                      # [4, vocab]: prompt's last position, then three decode steps
+    path = HERE / "llama_golden.npz"
+    np.savez_compressed(path, **out)
+    print("wrote", path, path.stat().st_size, "bytes,", len(out), "arrays; logits rms", float(np.sqrt((out["logits"] ** 2).mean())))
+
+
 if __name__ == "__main__":
-    which = sys.argv[1:] or ["packed", "legacy"]
+    which = sys.argv[1:] or ["packed", "legacy", "llama"]
     if "packed" in which:
         main()
     if "legacy" in which:
         legacy_formats()
+    if "llama" in which:
+        llama()

@@ -131,3 +131,45 @@ def test_set_weights_rejects_incomplete_or_misshaped_imports(cuda):
         model.create_generation_state()
     with pytest.raises(ValueError):
         ExternalLlamaConfig(**{**CFG, "num_key_value_heads": 3}).validate()
+
+
+def test_one_layer_of_the_third_configuration_prefill_gemm_and_decode(cuda, monkeypatch):
+    """The layer shape of the third benchmark configuration (hidden 2048, 32 heads of 64, FFN 8192, Q8_0
+    everywhere, BF16 activations) with one layer and a small vocabulary: a 48-token prefill - long enough
+    for the projections to run on the tensor-core GEMM from their GGUF-layout copies - and two decode steps
+    against the FP64 oracle, and the prefill again with the GEMM switched off (GEMV passes on the tile
+    layouts): both must meet the BF16 band, and agree with each other within it."""
+    torch = cuda
+    cfg = dict(vocab_size=512, hidden_size=2048, intermediate_size=8192, num_hidden_layers=1, num_attention_heads=32,
+               num_key_value_heads=32, head_dim=64, max_position_embeddings=128, rope_theta=10000.0, rms_norm_eps=1e-5)
+    model = ExternalLlamaModel(ExternalLlamaConfig(**cfg), dtype="bfloat16")
+    rng = np.random.default_rng(3)
+    packed, oracle = {}, {}
+    for name, shape in model.expected_shapes().items():
+        if len(shape) == 1:
+            packed[name] = oracle[name] = np.ones(shape, np.float32)
+            continue
+        w = quantize(rng.normal(0, 0.5 if "embed" in name else 0.02, shape).astype(np.float32), "Q8_0")
+        packed[name], oracle[name] = w, (w.data, w.shape, "Q8_0")
+    model.set_weights(packed)
+    assert model.native_of, "no GGUF-layout copies were kept for the prefill GEMM"
+    tokens = rng.integers(0, cfg["vocab_size"], 50)
+    ref = lo.llama_logits(oracle, cfg, tokens)
+    scale = np.abs(ref).max()
+    calls = []
+    from mylocal_llm_b200 import _lib
+    real = _lib.call
+    monkeypatch.setattr(_lib, "call", lambda name, *a: (calls.append(name), real(name, *a))[1])
+    state = model.create_generation_state(1, 64)
+    logits = model.prefill(torch.from_numpy(tokens[:48][None]).cuda(), state)
+    assert calls.count("b200q_gemm") == 4, calls          # qkv, o, gate|up, down of the one layer
+    np.testing.assert_allclose(logits[0].cpu().numpy(), ref[47], rtol=6e-2, atol=6e-2 * scale)
+    for step in (48, 49):
+        logits = model.decode_one(torch.from_numpy(tokens[step:step + 1]).cuda(), state)
+        np.testing.assert_allclose(logits[0].cpu().numpy(), ref[step], rtol=6e-2, atol=6e-2 * scale)
+    monkeypatch.setenv("B200Q_GEMM", "0")
+    calls.clear()
+    state2 = model.create_generation_state(1, 64)
+    logits2 = model.prefill(torch.from_numpy(tokens[:48][None]).cuda(), state2)
+    assert "b200q_gemm" not in calls
+    np.testing.assert_allclose(logits2[0].cpu().numpy(), ref[47], rtol=6e-2, atol=6e-2 * scale)
