@@ -64,6 +64,9 @@ WORKLOADS = {
     "gemv_q8_0_131072x4096_m16": ("Q8_0", 131072, 4096, 16, "bfloat16"),
     "gemv_q4k_65536x4096_m8": ("Q4_K", 65536, 4096, 8, "bfloat16"),
     "gemv_q4k_65536x4096_m16": ("Q4_K", 65536, 4096, 16, "bfloat16"),
+    # integer-dot mode (Q8_1 activations, opt-in): the activation dtype field names the mode
+    "gemv_q4k_65536x8192_m1_q8_1": ("Q4_K", 65536, 8192, 1, "q8_1"),
+    "gemv_q4k_8192x2048_m1_q8_1": ("Q4_K", 8192, 2048, 1, "q8_1"),
     # prefill / batched sizes of the second configuration: the tcgen05 GEMM (weights in GGUF layout, read once)
     "gemm_q4k_8192x2048_m512": ("Q4_K", 8192, 2048, 512, "bfloat16"),
     "gemm_q4k_2048x8192_m512": ("Q4_K", 2048, 8192, 512, "bfloat16"),
@@ -293,6 +296,9 @@ def run_gpu_arm(args, name):
     from mylocal_llm_b200.quantize import random_packed
 
     fmt, n, k, m, act = WORKLOADS[name]
+    q8_mode = act == "q8_1"                  # FP32 activations, quantised to Q8_1 by a kernel inside the timed step
+    if q8_mode:
+        act = "float32"
     act_dtype = getattr(torch, act)
     act_bytes = 4 if act == "float32" else 2
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -319,11 +325,16 @@ def run_gpu_arm(args, name):
 
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
-        outs = [quantized_linear(dev_x[c], weights[c]) for c in range(copies)]   # warm-up, lazy init
+        if q8_mode:
+            from mylocal_llm_b200.q8_1 import q8_1_linear, quantize_q8_1
+            run = lambda c: q8_1_linear(quantize_q8_1(dev_x[c]), weights[c])     # quantiser + GEMV: two launches
+        else:
+            run = lambda c: quantized_linear(dev_x[c], weights[c])
+        outs = [run(c) for c in range(copies)]   # warm-up, lazy init
         stream.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            outs = [quantized_linear(dev_x[c], weights[c]) for c in range(copies)]
+            outs = [run(c) for c in range(copies)]
         out_stack = outs
 
         def barrier():

@@ -85,6 +85,18 @@ int b200q_gemm(const void *w, int fmt, int n, int k, const void *x, int x_dtype,
                int y_dtype, void *stream);
 int b200q_gemm_supported(int fmt, int n, int k, int x_dtype, int m);
 
+/* ---- Integer-dot mode (opt-in; changes numerics): Q8_1 activations. ------------------------------
+ * b200q_quantize_q8_1: x[rows, k] (fp32 / fp16 / bf16) -> rows * k/32 blocks of 36 bytes {fp16 d, fp16 sum,
+ * 32 x int8}: d = max|x| / 127 of the block, codes = round-half-away(x / d) clamped to +-127 (0 for an
+ * all-zero block), sum = sum of the block's inputs; IEEE arithmetic. Replaces the quantiser of
+ * mini_llm/ops/q8_1_gpu.py:30-58 (its non-fast-math "ieee" variant).
+ * b200q_gemv_q8_1: y[m, n] = dequant(xq)[m, k] @ W[n, k]^T with integer dots (dp4a) per sub-block and the
+ * per-sub-block scaling of mini_llm/ops/mixed_q8_gpu.py:86-139 (q8_linear / k_part for Q4_K). W: Q4_K in
+ * GGUF or tile layout (other formats: 3 = unsupported), K a multiple of 256; 1..4 tokens per pass over W. */
+int b200q_quantize_q8_1(const void *x, int x_dtype, int rows, int k, void *out_blocks, void *stream);
+int b200q_gemv_q8_1(const void *w, int fmt, int n, int k, const void *xq_blocks, int m, void *y, int y_dtype,
+                    void *stream);
+
 /* h[m,f] = silu(x @ G^T) * (x @ U^T); gate and up may use different formats.
  * Replaces quantized_swiglu and _packed_gate_up_swiglu_kernel
  * (mini_llm/ops/quantized_linear.py:194-221,338-400). */

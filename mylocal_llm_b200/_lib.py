@@ -26,6 +26,8 @@ SIGNATURES = {
     "b200q_device_status_clear": [],
     "b200q_dequantize": [_ptr, _c_int, _c_i64, _c_int, _ptr, _ptr],
     "b200q_gemv": [_ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr, _c_int, _ptr],
+    "b200q_quantize_q8_1": [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr],
+    "b200q_gemv_q8_1": [_ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr, _c_int, _ptr],
     "b200q_gemm": [_ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr, _c_int, _ptr],
     "b200q_gemm_supported": [_c_int, _c_int, _c_int, _c_int, _c_int],
     "b200q_swiglu": [_ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr, _c_int, _ptr],
