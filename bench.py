@@ -84,7 +84,8 @@ MOE_WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "moe_stack_b64"
 # dense decode GEMVs timed briefly next to every MoE run (rank 0): second configuration + one large matrix
-SIDE_GEMVS = ("gemv_q4k_8192x2048_m1", "gemv_q8_0_4096x4096_m1", "gemv_q4k_65536x8192_m1")
+SIDE_GEMVS = ("gemv_q4k_8192x2048_m1", "gemv_q8_0_4096x4096_m1", "gemv_q4k_65536x8192_m1",
+              "gemm_q4k_8192x2048_m512", "gemm_q4k_2048x8192_m512")
 
 
 def packed_bytes(fmt, n, k):
@@ -471,7 +472,7 @@ def gemv_side_numbers(names, replays=20):
         wbytes = packed_bytes(fmt, n, k)
         copies = min(max(2, -(-2 * L2_BYTES // wbytes)), 64)
         base = random_packed(fmt, (n, k), seed=99, d=0.01, dmin=0.005)
-        weights = [upload(base, act) for _ in range(copies)]
+        weights = [packed_to_device(base) if m > 16 else upload(base, act) for _ in range(copies)]
         x = torch.randn((copies, m, k), device="cuda").to(act_dtype)
         with torch.cuda.stream(stream):
             for c in range(copies):
@@ -495,6 +496,11 @@ def gemv_side_numbers(names, replays=20):
         gbs = per_launch / (us * 1e-6) / 1e9
         out[name] = {"GB/s": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4), "us_per_launch": round(us, 3),
                      "layout": weights[0].quant_type}
+        if m > 16:          # a contraction: FLOP/s against the measured sustained BF16 peak
+            tpeak, _ = measured_tensor_peak()
+            tfl = 2.0 * m * n * k / (us * 1e-6) / 1e12
+            out[name] = {"TFLOP/s": round(tfl, 1), "frac_of_tensor_peak": round(tfl / tpeak, 4),
+                         "us_per_launch": round(us, 3), "layout": weights[0].quant_type}
         del weights, graph
     torch.cuda.empty_cache()
     return out
