@@ -192,6 +192,24 @@ int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, 
                       const int32_t *seg_count, const int32_t *num_segments, int max_segments,
                       float *hbuf, void *stream);
 
+/* The same launch fed with per-token activation images. A token routed to k experts is otherwise converted
+ * (scaled, split into FP16 fragments, summed per sub-block) once per expert segment it appears in;
+ * b200q_moe_token_images does that conversion once per row of x [rows, d] and stores it, and
+ * b200q_moe_gate_up_images lets every segment gather its tokens' images instead. The conversion code is
+ * the same, so the results are the same bits as b200q_moe_gate_up's. `images` holds rows *
+ * b200q_moe_token_image_bytes(d, x_dtype) bytes, 16-byte aligned; that function returns 0 when d has no
+ * images (not a multiple of 256, or too large), and kernels that do not use images ignore the buffer.
+ * No counterpart in the reference: its grouped op indexes the activations per expert
+ * (mini_llm/ops/grouped_quantized_experts.py:31-43). */
+int b200q_moe_token_image_bytes(int d, int x_dtype);
+int b200q_moe_token_images(const void *x, int x_dtype, int rows, int d, void *images, void *stream);
+int b200q_moe_gate_up_images(const void *gate_base, int64_t gate_stride, int gate_fmt, const void *up_base,
+                             int64_t up_stride, int up_fmt, const uint64_t *gate_table, const uint64_t *up_table,
+                             int tables_aligned16, int f, int d, const void *x, int x_dtype, const void *images,
+                             int k, const int32_t *order, const int32_t *seg_expert, const int32_t *seg_begin,
+                             const int32_t *seg_count, const int32_t *num_segments, int max_segments,
+                             float *hbuf, void *stream);
+
 /* Grouped down projection with the route weight applied and stored per assignment:
  *   terms[pos, d] (fp32) = (hbuf[pos] . D_e) * route[order[pos]]
  * With flat_rows != 0 the row index is order[pos] (the flat assignment index row*k+slot) instead of

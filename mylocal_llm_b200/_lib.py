@@ -47,6 +47,10 @@ SIGNATURES = {
                        _ptr, _c_int, _ptr, _ptr],
     "b200q_moe_gate_up": [_ptr, _c_i64, _c_int, _ptr, _c_i64, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr,
                           _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr],
+    "b200q_moe_token_image_bytes": [_c_int, _c_int],
+    "b200q_moe_token_images": [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr],
+    "b200q_moe_gate_up_images": [_ptr, _c_i64, _c_int, _ptr, _c_i64, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr,
+                                 _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr],
     "b200q_moe_plan_ex": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
                           _ptr, _ptr, _c_int, _ptr, _ptr],
     "b200q_moe_combine_ids": [_ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr],

@@ -77,6 +77,9 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) 
     a.topk = q.topk; a.order = q.order; a.seg_expert = q.seg_expert; a.seg_begin = q.seg_begin;
     a.seg_count = q.seg_count; a.num_segments = q.num_segments; a.max_segments = q.max_segments;
     a.route = q.route; a.flat_rows = q.flat_rows; a.y_table = q.y_table; a.rows_per_rank = q.rows_per_rank;
+    a.images = q.mode == 2 ? static_cast<const uint8_t *>(q.images) : nullptr;
+    a.image_stride = direct_token_image_bytes(q.k, q.x_dtype);
+    if (a.images && (a.image_stride == 0 || (reinterpret_cast<uintptr_t>(a.images) & 15))) a.images = nullptr;
 
     const bool q5 = q.fmt_a == B200Q_Q5_K;
     DirectFn fn = q5 ? (a.nterms == 2 ? pick_mode<true, 2>(q.mode, token_tiles) : pick_mode<true, 1>(q.mode, token_tiles))
@@ -97,6 +100,34 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) 
     launch_chained(fn, dim3(grid), dim3(MD_THREADS), static_cast<size_t>(smem), stream, a);
     *launched = true;
     return check_launch("direct gemv");
+}
+
+static long long token_image_smem(int k, int x_dtype) {
+    const long long nterms = (x_dtype == B200Q_F32) ? 2 : 1;
+    const long long nsb = k / 256;
+    return MD_CTRL_BYTES + nterms * nsb * 16 * 256 + nsb * 2 * 128;
+}
+
+int direct_token_image_bytes(int k, int x_dtype) {
+    if (k <= 0 || k % 256 != 0 || token_image_smem(k, x_dtype) > MM_SMEM_LIMIT) return 0;
+    return token_image_units(x_dtype == B200Q_F32 ? 2 : 1, k / 256) * 16;
+}
+
+int direct_token_images(const void *x, int x_dtype, int rows, int k, void *images, cudaStream_t stream) {
+    if (direct_token_image_bytes(k, x_dtype) == 0)
+        return fail(B200Q_EUNSUPPORTED, "token images: K=%d is not a multiple of 256 or too large", k);
+    if (reinterpret_cast<uintptr_t>(images) & 15) return fail(B200Q_EINVAL, "token images: the buffer must be 16-byte aligned");
+    using ImageFn = void (*)(const void *, int, int, uint8_t *);
+    ImageFn fn = x_dtype == B200Q_F32 ? token_image_kernel<2> : token_image_kernel<1>;
+    cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void *>(fn),
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM_LIMIT);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail(B200Q_ECUDA, "token images: shared memory opt-in failed: %s", cudaGetErrorString(err));
+    }
+    launch_chained(fn, dim3(rows), dim3(MD_THREADS), static_cast<size_t>(token_image_smem(k, x_dtype)), stream, x,
+                   x_dtype, k, static_cast<uint8_t *>(images));
+    return check_launch("token images");
 }
 
 }  // namespace b200q

@@ -58,6 +58,8 @@ struct DirectArgs {
     int flat_rows;       // mode 3: term rows stored at the flat assignment index
     const uint64_t *y_table;   // mode 3, optional: per-rank base addresses of the term buffers (peer memory)
     int rows_per_rank;   // flat rows owned by each rank when y_table is set
+    const uint8_t *images;   // mode 2, optional: token images (token_image_kernel), image_stride bytes per row of x
+    int image_stride;
 };
 
 __device__ __forceinline__ uint4 ldg128(const uint8_t *p) {
@@ -304,6 +306,66 @@ __device__ __forceinline__ void prepare_direct(RowFn row_of, int m_tokens, int k
     named_barrier_sync(1, MD_THREADS);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Token images. In the grouped gate/up launch every expert segment needs the fragments of its tokens, and
+// a token routed to k experts would be converted k times (at 64 tokens: 704 conversions of 64 distinct
+// rows, each a chain of dependent loads, a reduction and three barriers). token_image_kernel runs
+// prepare_direct once per token - same code, so the same bits - and stores what it wrote for token slot 0:
+//   [NTERMS * nfrag * 32 bytes]  the slot's four fragment lanes (tig 0..3, 8 bytes each) of every fragment
+//   [nsb * 2 * 16 bytes]         the slot's four words of every activation-sum row
+//   [16 bytes]                   scale, inverse scale
+// gather_token_images copies the images of a segment's tokens into the slots of the CTA's buffers with
+// independent 16-byte loads.
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ constexpr int token_image_units(int nterms, int nsb) {      // 16-byte units per token
+    return nterms * nsb * 16 * 2 + nsb * 2 + 1;
+}
+
+template <int NTERMS>
+__global__ void __launch_bounds__(MD_THREADS, 1) token_image_kernel(const void *x, int x_dtype, int k, uint8_t *images) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    chain_trigger();
+    chain_wait();                 // x comes from the preceding kernel
+    const int nsb = k >> 8, nfrag = nsb * 16;
+    float *tok_scale = reinterpret_cast<float *>(smem);
+    uint2 *bfrag = reinterpret_cast<uint2 *>(smem + MD_CTRL_BYTES);
+    uint32_t *xsfrag = reinterpret_cast<uint32_t *>(smem + MD_CTRL_BYTES + NTERMS * nfrag * 256);
+    const int row = blockIdx.x, tid = threadIdx.x;
+    prepare_direct<NTERMS, 4>([row](int) { return row; }, 1, k, x, x_dtype, bfrag, xsfrag, tok_scale, tid);
+    const int nb = NTERMS * nfrag * 2, units = token_image_units(NTERMS, nsb);
+    uint4 *dst = reinterpret_cast<uint4 *>(images + static_cast<size_t>(row) * units * 16);
+    for (int u = tid; u < units; u += MD_THREADS) {
+        uint4 v;
+        if (u < nb) v = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint8_t *>(bfrag) + (u >> 1) * 256 + (u & 1) * 16);
+        else if (u < units - 1) v = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint8_t *>(xsfrag) + (u - nb) * 128);
+        else v = make_uint4(__float_as_uint(tok_scale[0]), __float_as_uint(tok_scale[8]), 0u, 0u);
+        dst[u] = v;
+    }
+}
+
+// Slots 0..m_tokens-1 of the CTA's buffers <- the images of rows order[seg_begin + t] / topk. The caller
+// brackets the call with CTA barriers.
+__device__ __forceinline__ void gather_token_images(const uint8_t *images, int image_stride, const int32_t *order,
+                                                    int seg_begin, int topk, int m_tokens, int nterms, int nsb,
+                                                    uint2 *bfrag, uint32_t *xsfrag, float *tok_scale, int tid) {
+    const int nb = nterms * nsb * 32, units = token_image_units(nterms, nsb);
+    const int t = (tid >> 5) & 7;                 // two warps per token slot, all their loads independent
+    if (t < m_tokens) {
+        const int row = order[seg_begin + t] / topk;
+        const uint4 *src = reinterpret_cast<const uint4 *>(images + static_cast<size_t>(row) * image_stride);
+#pragma unroll 5
+        for (int u = (tid >> 8) * 32 + (tid & 31); u < units; u += 64) {
+            const uint4 v = src[u];
+            if (u < nb) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(bfrag) + (u >> 1) * 256 + t * 32 + (u & 1) * 16) = v;
+            else if (u < units - 1) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(xsfrag) + (u - nb) * 128 + t * 16) = v;
+            else {
+                tok_scale[t] = __uint_as_float(v.x);
+                tok_scale[8 + t] = __uint_as_float(v.y);
+            }
+        }
+    }
+}
+
 // 16 mma steps of one super-block for rows (g, g+8): acc += sum(sc*q*x); accm += sum(mn * sum_x/64).
 // With NT token tiles (8 tokens each; their fragments `btile` / `xtile` entries apart) every decoded
 // A operand is multiplied into each tile, so the decode cost is paid once per 8*NT tokens; the
@@ -511,7 +573,12 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
             if (MODE == 2 && m_tokens == 1) single = a.order[seg_begin] / a.topk;
             const bool reuse = (single >= 0 && single == last_single);
             last_single = single;
-            if (!reuse) {
+            if (!reuse && MODE == 2 && a.images) {
+                named_barrier_sync(1, MD_THREADS);       // every warp is done with the previous segment's fragments
+                gather_token_images(a.images, a.image_stride, a.order, seg_begin, a.topk, m_tokens, NTERMS, nsb, bfrag,
+                                    xsfrag, tok_scale, tid);
+                named_barrier_sync(1, MD_THREADS);
+            } else if (!reuse) {
                 named_barrier_sync(1, MD_THREADS);
                 if (tid < m_tokens) {
                     const int flat = a.order[seg_begin + tid];

@@ -31,6 +31,7 @@ struct MmaRequest {
     const uint64_t *y_table;
     int rows_per_rank;
     int *status;
+    const void *images;   // mode 2, optional: per-token activation images (direct_token_images) of the rows of x
 };
 
 // Launches the tensor-core kernel when the request fits it (alignment, K multiple of 256, shared
@@ -45,6 +46,13 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched);
 // Tokens per launch the direct kernel takes for this format / mode / K (8, or 16 in the dense modes
 // when two token tiles fit in shared memory).
 int direct_tokens_per_pass(int fmt, int mode, int k, int x_dtype);
+
+// Activation images for the grouped gate/up launch of the direct kernel: what that kernel would prepare for
+// a token (scaled FP16 fragments, sub-block sums, the scale), written once per token so that an expert
+// segment only gathers its tokens' images. Bytes per token (0 = this K / dtype has no images), and the
+// launch that fills `images` [rows x bytes] from x [rows x k].
+int direct_token_image_bytes(int k, int x_dtype);
+int direct_token_images(const void *x, int x_dtype, int rows, int k, void *images, cudaStream_t stream);
 
 // Weights in the Q6_K / Q8_0 tile layouts (mode 0 or 3, at most tiled_tokens_per_pass() tokens):
 // there is no other kernel for these layouts, so a request that does not fit returns an error

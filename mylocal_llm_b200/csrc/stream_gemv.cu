@@ -253,12 +253,12 @@ int b200q_swiglu(const void *gate, int gate_fmt, const void *up, int up_fmt, int
     return B200Q_OK;
 }
 
-int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, const void *up_base,
-                      int64_t up_stride, int up_fmt, const uint64_t *gate_table, const uint64_t *up_table,
-                      int tables_aligned16, int f, int d, const void *x, int x_dtype, int k,
-                      const int32_t *order, const int32_t *seg_expert, const int32_t *seg_begin,
-                      const int32_t *seg_count, const int32_t *num_segments, int max_segments, float *hbuf,
-                      void *stream) {
+static int moe_gate_up_impl(const void *gate_base, int64_t gate_stride, int gate_fmt, const void *up_base,
+                            int64_t up_stride, int up_fmt, const uint64_t *gate_table, const uint64_t *up_table,
+                            int tables_aligned16, int f, int d, const void *x, int x_dtype, int k,
+                            const int32_t *order, const int32_t *seg_expert, const int32_t *seg_begin,
+                            const int32_t *seg_count, const int32_t *num_segments, int max_segments, float *hbuf,
+                            const void *images, void *stream) {
     if ((!gate_table != !up_table) || (!gate_table && (!gate_base || !up_base)) || !x || !order || !seg_expert || !seg_begin || !seg_count || !num_segments || !hbuf)
         return fail(B200Q_EINVAL, "moe_gate_up: NULL pointer");
     const bool tiled = gate_fmt == B200Q_Q4_K_TILED;
@@ -303,6 +303,7 @@ int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, 
         q.n = f; q.k = d; q.m = MAX_TOKENS; q.x = x; q.x_dtype = x_dtype; q.y = hbuf;
         q.y_dtype = B200Q_F32; q.topk = k; q.order = order; q.seg_expert = seg_expert; q.seg_begin = seg_begin;
         q.seg_count = seg_count; q.num_segments = num_segments; q.max_segments = max_segments; q.status = status;
+        q.images = images;
         bool launched = false;
         int rc = mma_try_launch(q, static_cast<cudaStream_t>(stream), &launched);
         if (rc || launched) return rc;
@@ -315,6 +316,39 @@ int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, 
     if (!pick_dual<2>(gate_fmt, up_fmt)) return fail(B200Q_EUNSUPPORTED, "moe_gate_up: Q4_0 / Q3_K pair only with the same format");
     return launch(pick_dual<2>(gate_fmt, up_fmt), a, true, sm_count(), static_cast<cudaStream_t>(stream),
                   "moe_gate_up");
+}
+
+int b200q_moe_gate_up(const void *gate_base, int64_t gate_stride, int gate_fmt, const void *up_base,
+                      int64_t up_stride, int up_fmt, const uint64_t *gate_table, const uint64_t *up_table,
+                      int tables_aligned16, int f, int d, const void *x, int x_dtype, int k,
+                      const int32_t *order, const int32_t *seg_expert, const int32_t *seg_begin,
+                      const int32_t *seg_count, const int32_t *num_segments, int max_segments, float *hbuf,
+                      void *stream) {
+    return moe_gate_up_impl(gate_base, gate_stride, gate_fmt, up_base, up_stride, up_fmt, gate_table, up_table,
+                            tables_aligned16, f, d, x, x_dtype, k, order, seg_expert, seg_begin, seg_count, num_segments,
+                            max_segments, hbuf, nullptr, stream);
+}
+
+int b200q_moe_token_image_bytes(int d, int x_dtype) {
+    return dtype_valid(x_dtype) ? direct_token_image_bytes(d, x_dtype) : 0;
+}
+
+int b200q_moe_token_images(const void *x, int x_dtype, int rows, int d, void *images, void *stream) {
+    if (!x || !images) return fail(B200Q_EINVAL, "moe_token_images: NULL pointer");
+    if (!dtype_valid(x_dtype) || rows <= 0 || d <= 0) return fail(B200Q_EINVAL, "moe_token_images: bad shape rows=%d d=%d", rows, d);
+    return direct_token_images(x, x_dtype, rows, d, images, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_moe_gate_up_images(const void *gate_base, int64_t gate_stride, int gate_fmt, const void *up_base,
+                             int64_t up_stride, int up_fmt, const uint64_t *gate_table, const uint64_t *up_table,
+                             int tables_aligned16, int f, int d, const void *x, int x_dtype, const void *images, int k,
+                             const int32_t *order, const int32_t *seg_expert, const int32_t *seg_begin,
+                             const int32_t *seg_count, const int32_t *num_segments, int max_segments, float *hbuf,
+                             void *stream) {
+    if (!images) return fail(B200Q_EINVAL, "moe_gate_up_images: NULL image buffer");
+    return moe_gate_up_impl(gate_base, gate_stride, gate_fmt, up_base, up_stride, up_fmt, gate_table, up_table,
+                            tables_aligned16, f, d, x, x_dtype, k, order, seg_expert, seg_begin, seg_count, num_segments,
+                            max_segments, hbuf, images, stream);
 }
 
 static int moe_down_impl(const void *down_base, int64_t down_stride, int down_fmt, const uint64_t *down_table,

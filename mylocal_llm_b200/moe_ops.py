@@ -5,6 +5,7 @@ returns torch tensors; all work is enqueued on torch's current stream and nothin
 synchronises or reads device memory back.
 """
 
+import os
 import ctypes
 from dataclasses import dataclass
 
@@ -154,14 +155,46 @@ def router_topk_plan_row(logits2d, k, n_experts, *, renormalize=True, floor=2.0 
     return weights, ids, plan
 
 
+# Rows of activations from which the grouped gate/up launch is fed with per-token images (one extra small
+# launch that converts every row once; below this the segments convert their few tokens themselves).
+TOKEN_IMAGE_MIN_ROWS = 32
+
+
+def token_images(x2d):
+    """Per-token activation images of ``x2d [rows, d]`` for ``moe_gate_up(..., images=...)``, or ``None``
+    when this width has none. One image serves every expert segment (and every layer input equal to
+    ``x2d``) the token appears in."""
+    torch = _torch()
+    rows, d = x2d.shape
+    per_row = _lib.load().b200q_moe_token_image_bytes(int(d), _dtype_id(x2d))
+    if per_row <= 0:
+        return None
+    images = torch.empty((rows, per_row), dtype=torch.uint8, device=x2d.device)
+    _lib.call("b200q_moe_token_images", _ptr(x2d), _dtype_id(x2d), int(rows), int(d), _ptr(images),
+              _lib.current_stream())
+    return images
+
+
 def moe_gate_up(x2d, plan, gate_bank, up_bank, gate_fmt, up_fmt, f, d, gate_stride, up_stride, *,
-                gate_table=None, up_table=None, tables_aligned16=False):
+                gate_table=None, up_table=None, tables_aligned16=False, images=None):
     """FP32 hidden activations ``[T*k, F]`` in sorted-assignment order.
 
     Experts live either in contiguous banks (``*_bank`` + byte stride) or behind device pointer
-    tables (int64 tensors with one address per expert)."""
+    tables (int64 tensors with one address per expert). ``images`` = ``token_images(x2d)``; by default they
+    are made here when ``x2d`` has at least ``TOKEN_IMAGE_MIN_ROWS`` rows (``B200Q_TOKEN_IMAGES=0`` turns
+    that off). The results are the same bits either way."""
     torch = _torch()
     hbuf = torch.empty((plan.rows * plan.k, f), dtype=torch.float32, device=x2d.device)
+    if images is None and x2d.shape[0] >= TOKEN_IMAGE_MIN_ROWS and os.environ.get("B200Q_TOKEN_IMAGES", "1") != "0" \
+            and gate_fmt in ("Q4_K", "Q5_K", "Q4_K_TILED") and gate_fmt == up_fmt:
+        images = token_images(x2d)
+    if images is not None:
+        _lib.call("b200q_moe_gate_up_images", _ptr(gate_bank), int(gate_stride), _lib.FORMAT_ID[gate_fmt],
+                  _ptr(up_bank), int(up_stride), _lib.FORMAT_ID[up_fmt], _ptr(gate_table), _ptr(up_table),
+                  1 if tables_aligned16 else 0, f, d, _ptr(x2d), _dtype_id(x2d), _ptr(images), plan.k,
+                  _ptr(plan.order), _ptr(plan.seg_expert), _ptr(plan.seg_begin), _ptr(plan.seg_count),
+                  _ptr(plan.num_segments), plan.max_segments, _ptr(hbuf), _lib.current_stream())
+        return hbuf
     _lib.call("b200q_moe_gate_up", _ptr(gate_bank), int(gate_stride), _lib.FORMAT_ID[gate_fmt], _ptr(up_bank),
               int(up_stride), _lib.FORMAT_ID[up_fmt], _ptr(gate_table), _ptr(up_table), 1 if tables_aligned16 else 0,
               f, d, _ptr(x2d), _dtype_id(x2d), plan.k, _ptr(plan.order),

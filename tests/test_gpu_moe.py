@@ -176,3 +176,36 @@ def test_grouped_experts_against_fp64_oracle_with_crowded_experts(cuda, tokens):
     ref = po.experts_forward_fp32sum(hidden, w.astype(np.float32), ids,
                                      lambda ex, rows: po.expert_ffn_fp64(rows, *experts[ex]), e)
     np.testing.assert_allclose(out.cpu().numpy(), ref, rtol=4e-4, atol=8e-6)
+
+
+@pytest.mark.parametrize("fmt,x_dtype", [("Q4_K", "bfloat16"), ("Q4_K", "float32"), ("Q5_K", "float16"),
+                                         ("Q4_K_TILED", "bfloat16"), ("Q4_K_TILED", "float32")])
+@pytest.mark.parametrize("tokens,e,k", [(40, 5, 2), (64, 96, 6), (9, 33, 4)])
+def test_gate_up_with_token_images_is_bit_identical(cuda, kernel_family, fmt, x_dtype, tokens, e, k):
+    # the images are what the kernel would have prepared per token: same bits with them, without them, and
+    # when the caller makes them once and passes them in; crowded experts give segments of 8 and re-used tokens
+    from mylocal_llm_b200.quantized_linear import retile_bytes
+    if kernel_family != "tensor":
+        pytest.skip("only the direct-load kernel gathers images; the other families ignore the buffer")
+    d, f = 768, 64
+    base = "Q4_K" if fmt == "Q4_K_TILED" else fmt
+    rng = np.random.default_rng(tokens + e)
+    packs = [[quantize(rng.normal(0, 0.05, (f, d)).astype(np.float32), base) for _ in range(e)] for _ in range(2)]
+    banks = [to_cuda(cuda, np.stack([p.data for p in group]).reshape(-1)) for group in packs]
+    stride = packs[0][0].data.size
+    if fmt == "Q4_K_TILED":
+        banks = [retile_bytes(b, e * f, d, "Q4_K") for b in banks]
+    x = to_cuda(cuda, rng.normal(0, 1, (tokens, d)).astype(np.float32), getattr(cuda, x_dtype))
+    _, ids = po.router_topk(rng.normal(0, 1, (tokens, e)), k, 2.0 ** -14)
+    plan = moe_ops.moe_plan(to_cuda(cuda, ids), e)
+    run = lambda **kw: moe_ops.moe_gate_up(x, plan, banks[0], banks[1], fmt, fmt, f, d, stride, stride, **kw)
+    import os
+    os.environ["B200Q_TOKEN_IMAGES"] = "0"
+    try:
+        plain = run()
+    finally:
+        del os.environ["B200Q_TOKEN_IMAGES"]
+    images = moe_ops.token_images(x)
+    assert images is not None and images.shape[0] == tokens
+    assert cuda.equal(run(), plain)
+    assert cuda.equal(run(images=images), plain)
