@@ -672,7 +672,14 @@ def batch1_side_numbers(torch, stream, stack):
     graph.reset()
     step_bytes = len(stack.layers) * ((MOE_SHAPE["top_k"] + 1) * EXPERT_BYTES + 4 * 2048 * 512)
     out["moe_stack_b1"] = {"tokens/s": round(1e3 / ms, 1), "ms_per_step": round(ms, 4), "layers": len(stack.layers),
-                           "step_bytes": step_bytes, "frac_of_peak": round(step_bytes / (ms * 1e-3) / 1e9 / peak, 4)}
+                           "step_bytes": step_bytes, "frac_of_peak": round(step_bytes / (ms * 1e-3) / 1e9 / peak, 4),
+                           "step": "one persistent kernel" if getattr(stack, "persistent_step", False) else "chain of launches"}
+    if getattr(stack, "persistent_step", False):
+        stack.persistent_step = False
+        ms_chain, graph, _ = graph_time(torch, stream, lambda: stack.forward(x1)[0], replays=30)
+        graph.reset()
+        stack.persistent_step = True
+        out["moe_stack_b1"]["chain_of_launches_tokens/s"] = round(1e3 / ms_chain, 1)
     model = ExternalLlamaModel.synthetic(ExternalLlamaConfig(**LLAMA_SHAPE), seed=0)
     state = model.create_generation_state(1, LLAMA_PROMPT + 256)
     gen = torch.Generator(device="cuda")
@@ -856,11 +863,18 @@ def run_moe_gpu_arm(args, name):
             return res
 
         moe_ops.moe_gate_up = timed_gate_up
+        # (a one-token step runs as one persistent kernel; its gate/up stage is the same device function as the
+        # separate launch timed here)
+        persistent = getattr(stack, "persistent_step", False)
+        if persistent:
+            stack.persistent_step = False
         for _ in range(2):
             records.clear()
             step_fn()
             stream.synchronize()
         moe_ops.moe_gate_up = real_gate_up
+        if persistent:
+            stack.persistent_step = True
         gate_up_ms = [a0.elapsed_time(a1) for a0, a1, _ in records]
         # expert-parallel plans end with one entry counting the assignments other ranks execute
         executed = [c[:-1] if world > 1 else c for _, _, c in records]

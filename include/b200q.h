@@ -344,6 +344,30 @@ int b200q_peer_push3(const void *src0, size_t bytes0, size_t dst_offset0, const 
                      size_t dst_offset1, const void *src2, size_t bytes2, size_t dst_offset2,
                      const uint64_t *dst_bases, int world, void *stream);
 
+/* One-token decode step of a whole stack of MoE layers (norm -> router -> top-k -> routed + shared experts ->
+ * ordered combine -> residual add, per layer) as ONE persistent cooperative kernel: the stages the entry points
+ * b200q_rmsnorm, b200q_router_logits_t, b200q_router_topk_plan_row, b200q_moe_gate_up, b200q_moe_down and
+ * b200q_moe_combine_norm run as separate launches are walked by one grid with a bounded device-wide barrier
+ * between them, and the result is bit-identical to that chain of launches. Replaces the per-layer launch
+ * sequence the reference captures for one decode step (mini_llm/external/cuda_graph_decode.py:379-449).
+ *   layers        device array of n_layers records of five 8-byte pointers: router weight [e, d] FP32
+ *                 (expert-major, 16-byte aligned), gate / up / down pointer tables (e + 1 addresses each: the
+ *                 routed experts, then the always-selected shared expert; 16-byte aligned matrices), and the
+ *                 weight of the norm that FOLLOWS the layer (the last record: the final norm)
+ *   gamma0        weight of the norm in front of the first layer; all norm weights have type act_dtype
+ *   residual_in   FP32 [d]; residual_out FP32 [d] and hidden_out [d] (act_dtype) receive the residual stream
+ *                 and the normalised activations after the last layer
+ *   workspace     b200q_moe_decode_stack_workspace(d, f, e, k) bytes, 256-byte aligned, used by one step
+ *                 at a time
+ * Supported: gate/up Q4_K (native or tile layout), down in the Q6_K tile layout, BF16/FP16 activations,
+ * e <= 1024, k <= 15, d and f multiples of 256; anything else returns 3 and the caller runs the separate
+ * launches. A wait at the device-wide barrier that runs out (1 s) sets device status 401 and ends the step. */
+long long b200q_moe_decode_stack_workspace(int d, int f, int e, int k);
+int b200q_moe_decode_stack(const void *layers, int n_layers, int d, int f, int e, int k, int renormalize,
+                           float floor_value, int gate_up_fmt, int down_fmt, const void *gamma0, int act_dtype,
+                           float eps, const float *residual_in, float *residual_out, void *hidden_out,
+                           void *workspace, long long workspace_bytes, void *stream);
+
 /* One SwiGLU expert, y[m,d_model] = down( silu(x gate^T) * (x up^T) ), for callers that cannot
  * allocate device memory. (No counterpart in the reference: its expert FFN allocates the hidden
  * activations with CuPy.) The FP32 hidden activations [m, d_ff] between the two kernels live in a

@@ -47,6 +47,9 @@ SIGNATURES = {
                        _ptr, _c_int, _ptr, _ptr],
     "b200q_moe_gate_up": [_ptr, _c_i64, _c_int, _ptr, _c_i64, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr,
                           _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr],
+    "b200q_moe_decode_stack_workspace": [_c_int, _c_int, _c_int, _c_int],
+    "b200q_moe_decode_stack": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f32, _c_int, _c_int, _ptr, _c_int,
+                               _c_f32, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr],
     "b200q_moe_token_image_bytes": [_c_int, _c_int],
     "b200q_moe_token_images": [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr],
     "b200q_moe_gate_up_images": [_ptr, _c_i64, _c_int, _ptr, _c_i64, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr,
@@ -105,7 +108,7 @@ def load():
         for name, argtypes in SIGNATURES.items():
             fn = getattr(lib, name)
             fn.argtypes = argtypes
-            fn.restype = _c_int
+            fn.restype = _c_i64 if name == "b200q_moe_decode_stack_workspace" else _c_int
         lib.b200q_last_error.argtypes = []
         lib.b200q_last_error.restype = ctypes.c_char_p
         _LIB = lib

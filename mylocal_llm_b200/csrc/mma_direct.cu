@@ -30,19 +30,18 @@ int direct_tokens_per_pass(int fmt, int mode, int k, int x_dtype) {
     return direct_smem_bytes(k, x_dtype, 2) <= MM_SMEM_LIMIT ? 16 : 8;
 }
 
-int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) {
-    *launched = false;
+bool direct_plan_args(const MmaRequest &q, DirectArgs *out, long long *smem_out) {
     const bool dual = (q.mode == 1 || q.mode == 2);
     const bool grouped = q.mode >= 2;
-    if (q.fmt_a != B200Q_Q4_K && q.fmt_a != B200Q_Q5_K) return B200Q_OK;
-    if (dual && q.fmt_a != q.fmt_b) return B200Q_OK;
-    if (q.k % 256 != 0 || q.m > direct_tokens_per_pass(q.fmt_a, q.mode, q.k, q.x_dtype)) return B200Q_OK;
+    if (q.fmt_a != B200Q_Q4_K && q.fmt_a != B200Q_Q5_K) return false;
+    if (dual && q.fmt_a != q.fmt_b) return false;
+    if (q.k % 256 != 0 || q.m > direct_tokens_per_pass(q.fmt_a, q.mode, q.k, q.x_dtype)) return false;
     const int token_tiles = q.m > 8 ? 2 : 1;
-    if (q.tiled && (q.fmt_a != B200Q_Q4_K || q.n % 16 != 0)) return B200Q_OK;
-    if (reinterpret_cast<uintptr_t>(q.wa) & 15) return B200Q_OK;
-    if (dual && (reinterpret_cast<uintptr_t>(q.wb) & 15)) return B200Q_OK;
-    if (grouped && !q.table_a && ((q.stride_a & 15) || (dual && (q.stride_b & 15)))) return B200Q_OK;
-    if (grouped && q.table_a && !q.tables_aligned16) return B200Q_OK;
+    if (q.tiled && (q.fmt_a != B200Q_Q4_K || q.n % 16 != 0)) return false;
+    if (reinterpret_cast<uintptr_t>(q.wa) & 15) return false;
+    if (dual && (reinterpret_cast<uintptr_t>(q.wb) & 15)) return false;
+    if (grouped && !q.table_a && ((q.stride_a & 15) || (dual && (q.stride_b & 15)))) return false;
+    if (grouped && q.table_a && !q.tables_aligned16) return false;
 
     DirectArgs a{};
     a.wa = q.wa; a.wb = q.wb; a.stride_a = q.stride_a; a.stride_b = q.stride_b;
@@ -66,12 +65,23 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) 
         return per_unit * (grouped ? (q.max_segments > 1 ? q.max_segments / 2 : 1) : 1);
     };
     while (kp * 2 <= MD_WARPS && kp * 2 <= nsb && blocks_for(kp) < 6LL * sm_count()) kp *= 2;
+    // A plan of a few segments (one decoded token) cannot fill the SMs six times over whatever the split; what
+    // counts then is that no CTA runs two blocks - each block is one chain of dependent loads - while most run one:
+    // with between one and two blocks per SM at most, widen the blocks until every CTA has at most one.
+    if (grouped) {
+        auto most = [&](int parts) {
+            const int rows = 16 * (MD_WARPS / parts);
+            return static_cast<long long>((q.n + rows - 1) / rows) * q.max_segments;
+        };
+        if (most(kp) > sm_count() && most(kp) <= 2LL * sm_count())
+            while (kp > 1 && most(kp) > sm_count()) kp /= 2;
+    }
     a.kp = kp;
     a.rg = MD_WARPS / kp;
     a.off_bfrag = MD_CTRL_BYTES + token_tiles * MD_PART_BYTES;
     const long long bfrag_bytes = static_cast<long long>(token_tiles) * a.nterms * nsb * 16 * 256;
     const long long smem = direct_smem_bytes(q.k, q.x_dtype, token_tiles);
-    if (smem > MM_SMEM_LIMIT) return B200Q_OK;
+    if (smem > MM_SMEM_LIMIT) return false;
     a.off_xsfrag = static_cast<int>(a.off_bfrag + bfrag_bytes);
     a.x = q.x; a.x_dtype = q.x_dtype; a.y = q.y; a.y_dtype = q.y_dtype;
     a.topk = q.topk; a.order = q.order; a.seg_expert = q.seg_expert; a.seg_begin = q.seg_begin;
@@ -80,7 +90,18 @@ int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) 
     a.images = q.mode == 2 ? static_cast<const uint8_t *>(q.images) : nullptr;
     a.image_stride = direct_token_image_bytes(q.k, q.x_dtype);
     if (a.images && (a.image_stride == 0 || (reinterpret_cast<uintptr_t>(a.images) & 15))) a.images = nullptr;
+    *out = a;
+    *smem_out = smem;
+    return true;
+}
 
+int direct_try_launch(const MmaRequest &q, cudaStream_t stream, bool *launched) {
+    *launched = false;
+    const bool grouped = q.mode >= 2;
+    const int token_tiles = q.m > 8 ? 2 : 1;
+    DirectArgs a{};
+    long long smem = 0;
+    if (!direct_plan_args(q, &a, &smem)) return B200Q_OK;
     const bool q5 = q.fmt_a == B200Q_Q5_K;
     DirectFn fn = q5 ? (a.nterms == 2 ? pick_mode<true, 2>(q.mode, token_tiles) : pick_mode<true, 1>(q.mode, token_tiles))
                      : (a.nterms == 2 ? pick_mode<false, 2>(q.mode, token_tiles)

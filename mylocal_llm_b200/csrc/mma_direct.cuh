@@ -62,6 +62,16 @@ struct DirectArgs {
     int image_stride;
 };
 
+// The pointers of a launch that a persistent multi-stage kernel changes between calls of a stage body (the
+// kernels fill it from their arguments; the shapes and the split of the work stay in the argument block).
+struct StagePointers {
+    const void *x;
+    void *y;
+    const unsigned long long *table_a, *table_b;
+    const int32_t *order, *seg_expert, *seg_begin, *seg_count, *num_segments;
+    const float *route;
+};
+
 __device__ __forceinline__ uint4 ldg128(const uint8_t *p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -439,16 +449,16 @@ __device__ __forceinline__ void superblock_mma(const SuperBlockRegs<Q5> &ra, con
 // nt holds tokens 8nt..8nt+7 with its own scales (MD_TOK_STRIDE floats further on), fragments and
 // activation sums.
 constexpr int MD_TOK_STRIDE = 128;     // floats between the token tiles' scale blocks (inside the control bytes)
+// The work of CTA `block` of `nblocks` (MD_THREADS threads, all of them call): the kernel below is this body
+// for (blockIdx.x, gridDim.x); a persistent kernel that walks several stages calls it with its own.
+// `smem`: 128-byte aligned, direct-kernel layout (control bytes, partial sums, fragments at a.off_bfrag).
 template <bool Q5, int MODE, int NTERMS, int NT = 1>
-__global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectArgs a) {
+__device__ __forceinline__ void mma_direct_body(const DirectArgs &a, const StagePointers &gp, uint8_t *smem, const int block,
+                                                const int nblocks) {
     constexpr bool DUAL = (MODE == 1 || MODE == 2);
     constexpr bool GROUPED = (MODE >= 2);
     constexpr int QB = Q5 ? 176 : 144;
     static_assert(NT == 1 || !GROUPED, "several token tiles only in the dense modes");
-    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
-    if (GROUPED) chain_wait();      // the segment list comes from the plan kernel
-
-    extern __shared__ __align__(128) uint8_t smem[];
     float *tok_scale = reinterpret_cast<float *>(smem);           // [8] scale, [8] inverse
     float *route_w = reinterpret_cast<float *>(smem + 128);       // [8]
     int *seg_tokens = reinterpret_cast<int *>(smem + 192);        // [8]
@@ -468,13 +478,13 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
     const int blocks_per_unit = (a.n + rows_per_block - 1) / rows_per_block;
     long long units = 1;
     if (GROUPED) {
-        int nseg = *a.num_segments;
+        int nseg = *gp.num_segments;
         if (nseg > a.max_segments) nseg = a.max_segments;
         units = nseg;
     }
     const long long total_blocks = units * blocks_per_unit;
-    const long long blk_begin = total_blocks * blockIdx.x / gridDim.x;
-    const long long blk_end = total_blocks * (blockIdx.x + 1) / gridDim.x;
+    const long long blk_begin = total_blocks * block / nblocks;
+    const long long blk_end = total_blocks * (block + 1) / nblocks;
     if (!GROUPED) {
         // the CTA's row blocks are one contiguous byte range of the matrix (rows, or 16-row tiles)
         if (blk_begin < blk_end) {
@@ -505,7 +515,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
     };
     auto block_ptrs = [&](int unit, int row0) {
         BlockPtrs p;
-        const int expert = GROUPED ? a.seg_expert[unit] : 0;
+        const int expert = GROUPED ? gp.seg_expert[unit] : 0;
         size_t off_lo, off_hi;
         if (!Q5 && a.tiled) {   // tile of (row group, super-block kpi); n is a multiple of 16 here
             const int group = min((row0 >> 4) + rgi, (a.n >> 4) - 1);
@@ -514,12 +524,12 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
             off_lo = static_cast<size_t>(min(row0 + 16 * rgi + g, a.n - 1)) * a.rb + static_cast<size_t>(kpi) * QB;
             off_hi = static_cast<size_t>(min(row0 + 16 * rgi + g + 8, a.n - 1)) * a.rb + static_cast<size_t>(kpi) * QB;
         }
-        const uint8_t *base_a = expert_matrix(a.wa, a.stride_a, a.table_a, expert);
+        const uint8_t *base_a = expert_matrix(a.wa, a.stride_a, gp.table_a, expert);
         p.a_lo = base_a + off_lo;
         p.a_hi = base_a + off_hi;
         p.b_lo = p.b_hi = nullptr;
         if (DUAL) {
-            const uint8_t *base_b = expert_matrix(a.wb, a.stride_b, a.table_b, expert);
+            const uint8_t *base_b = expert_matrix(a.wb, a.stride_b, gp.table_b, expert);
             p.b_lo = base_b + off_lo;
             p.b_hi = base_b + off_hi;
         }
@@ -553,7 +563,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
             prepare_direct<NTERMS, (NT == 1 ? 4 : 2)>([nt](int t) { return 8 * nt + t; }, max(min(a.m - 8 * nt, 8), 0),
-                                                      a.k, a.x, a.x_dtype, bfrag + nt * btile, xsfrag + nt * xtile,
+                                                      a.k, gp.x, a.x_dtype, bfrag + nt * btile, xsfrag + nt * xtile,
                                                       tok_scale + nt * MD_TOK_STRIDE, tid);
     }
 
@@ -567,29 +577,29 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
         if (has_next) nxt_p = block_ptrs(unit_i, bi * rows_per_block);
         if (GROUPED && unit != cur_unit) {
             cur_unit = unit;
-            seg_begin = a.seg_begin[unit];
-            m_tokens = min(a.seg_count[unit], 8);
+            seg_begin = gp.seg_begin[unit];
+            m_tokens = min(gp.seg_count[unit], 8);
             int single = -1;
-            if (MODE == 2 && m_tokens == 1) single = a.order[seg_begin] / a.topk;
+            if (MODE == 2 && m_tokens == 1) single = gp.order[seg_begin] / a.topk;
             const bool reuse = (single >= 0 && single == last_single);
             last_single = single;
             if (!reuse && MODE == 2 && a.images) {
                 named_barrier_sync(1, MD_THREADS);       // every warp is done with the previous segment's fragments
-                gather_token_images(a.images, a.image_stride, a.order, seg_begin, a.topk, m_tokens, NTERMS, nsb, bfrag,
+                gather_token_images(a.images, a.image_stride, gp.order, seg_begin, a.topk, m_tokens, NTERMS, nsb, bfrag,
                                     xsfrag, tok_scale, tid);
                 named_barrier_sync(1, MD_THREADS);
             } else if (!reuse) {
                 named_barrier_sync(1, MD_THREADS);
                 if (tid < m_tokens) {
-                    const int flat = a.order[seg_begin + tid];
+                    const int flat = gp.order[seg_begin + tid];
                     seg_tokens[tid] = (MODE == 2) ? flat / a.topk : seg_begin + tid;
                     if (MODE == 3) {
-                        route_w[tid] = a.route[flat];
-                        out_ptr[tid] = term_row_pointer(static_cast<float *>(a.y), a.y_table, a.rows_per_rank, a.n, a.flat_rows ? flat : seg_begin + tid);
+                        route_w[tid] = gp.route[flat];
+                        out_ptr[tid] = term_row_pointer(static_cast<float *>(gp.y), a.y_table, a.rows_per_rank, a.n, a.flat_rows ? flat : seg_begin + tid);
                     }
                 }
                 named_barrier_sync(1, MD_THREADS);
-                prepare_direct<NTERMS, 2>([&](int t) { return seg_tokens[t]; }, m_tokens, a.k, a.x, a.x_dtype, bfrag,
+                prepare_direct<NTERMS, 2>([&](int t) { return seg_tokens[t]; }, m_tokens, a.k, gp.x, a.x_dtype, bfrag,
                                        xsfrag, tok_scale, tid);
             }
         }
@@ -647,17 +657,26 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
             const float inv = tok_scale[nt * MD_TOK_STRIDE + 8 + tl];
             pa *= inv;
             pbv *= inv;
-            if (MODE == 0) store_from_float(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, pa);
+            if (MODE == 0) store_from_float(gp.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, pa);
             else if (MODE == 1)
-                store_from_float(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, swiglu_f32(pa, pbv));
+                store_from_float(gp.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, swiglu_f32(pa, pbv));
             else if (MODE == 2)
-                static_cast<float *>(a.y)[static_cast<size_t>(seg_begin + t) * a.n + orow] = swiglu_f32(pa, pbv);
+                static_cast<float *>(gp.y)[static_cast<size_t>(seg_begin + t) * a.n + orow] = swiglu_f32(pa, pbv);
             else
                 out_ptr[t][orow] = pa * route_w[t];
         }
         pbuf ^= 1;
         cur_p = nxt_p;
     }
+}
+
+template <bool Q5, int MODE, int NTERMS, int NT = 1>
+__global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectArgs a) {
+    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
+    if (MODE >= 2) chain_wait();      // the segment list comes from the plan kernel
+    extern __shared__ __align__(128) uint8_t smem[];
+    const StagePointers gp{a.x, a.y, a.table_a, a.table_b, a.order, a.seg_expert, a.seg_begin, a.seg_count, a.num_segments, a.route};
+    mma_direct_body<Q5, MODE, NTERMS, NT>(a, gp, smem, blockIdx.x, gridDim.x);
 }
 
 }  // namespace b200q

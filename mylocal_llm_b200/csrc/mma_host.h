@@ -58,6 +58,13 @@ int direct_token_images(const void *x, int x_dtype, int rows, int k, void *image
 // there is no other kernel for these layouts, so a request that does not fit returns an error
 // instead of declining.
 int q6k_tiled_launch(const MmaRequest &q, cudaStream_t stream);
+
+// The kernel arguments and dynamic shared memory the two grouped launches above would use for a request,
+// without launching (the persistent one-token MoE step runs the same bodies with the same split of the work).
+struct DirectArgs;
+struct Q6TiledArgs;
+bool direct_plan_args(const MmaRequest &q, DirectArgs *out, long long *smem_out);
+int tiled_plan_args(const MmaRequest &q, Q6TiledArgs *out, long long *smem_out);
 int tiled_tokens_per_pass(int mode, int k, int x_dtype);
 
 }  // namespace b200q

@@ -145,7 +145,7 @@ int tiled_tokens_per_pass(int mode, int k, int x_dtype) {
 
 // Runs the tiled kernel for a mode 0 or mode 3 request whose weights are in a tile layout
 // (q.fmt_a: B200Q_Q6_K_TILED or B200Q_Q8_0_TILED).
-int q6k_tiled_launch(const MmaRequest &q, cudaStream_t stream) {
+int tiled_plan_args(const MmaRequest &q, Q6TiledArgs *out, long long *smem_out) {
     const bool grouped = q.mode == 3;
     if (q.mode != 0 && q.mode != 3) return fail(B200Q_EUNSUPPORTED, "tiled Q6_K: only linear and grouped down");
     const int nt = q.m > 8 ? 2 : 1;                    // 8-token tiles served by one pass over the weights
@@ -171,6 +171,16 @@ int q6k_tiled_launch(const MmaRequest &q, cudaStream_t stream) {
         return per_unit * (grouped ? (q.max_segments > 1 ? q.max_segments / 2 : 1) : 1);
     };
     while (kp * 2 <= Q6T_WARPS && kp * 2 <= nsb && blocks_for(kp) < 6LL * sm_count()) kp *= 2;
+    // a plan of a few segments: at most one block per CTA rather than one for most and two for some (each block
+    // is one chain of dependent loads; see the direct kernel's launcher)
+    if (grouped) {
+        auto most = [&](int parts) {
+            const int groups = Q6T_WARPS / parts;
+            return static_cast<long long>((q.n / 16 + groups - 1) / groups) * q.max_segments;
+        };
+        if (most(kp) > sm_count() && most(kp) <= 2LL * sm_count())
+            while (kp > 1 && most(kp) > sm_count()) kp /= 2;
+    }
     a.kp = kp;
     a.rg = Q6T_WARPS / kp;
     a.off_bfrag = Q6T_CTRL_BYTES + nt * Q6T_PART_BYTES;
@@ -180,6 +190,18 @@ int q6k_tiled_launch(const MmaRequest &q, cudaStream_t stream) {
     a.order = q.order; a.seg_expert = q.seg_expert; a.seg_begin = q.seg_begin; a.seg_count = q.seg_count;
     a.num_segments = q.num_segments; a.max_segments = q.max_segments; a.route = q.route;
     a.flat_rows = q.flat_rows; a.y_table = q.y_table; a.rows_per_rank = q.rows_per_rank;
+    *out = a;
+    *smem_out = smem;
+    return B200Q_OK;
+}
+
+int q6k_tiled_launch(const MmaRequest &q, cudaStream_t stream) {
+    const bool grouped = q.mode == 3;
+    const int nt = q.m > 8 ? 2 : 1;
+    Q6TiledArgs a{};
+    long long smem = 0;
+    const int rc = tiled_plan_args(q, &a, &smem);
+    if (rc) return rc;
     Q6Fn fn;
     if (q.fmt_a == B200Q_Q8_0_TILED) {
         if (grouped) fn = a.nterms == 2 ? tiled_kernel<Q8Tile, 3, 2, 1> : tiled_kernel<Q8Tile, 3, 1, 1>;

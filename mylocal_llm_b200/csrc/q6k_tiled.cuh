@@ -359,13 +359,13 @@ __device__ __forceinline__ void prepare_fragments(RowFn row_of, int m_tokens, in
 // NT (mode 0 only) is the number of 8-token tiles served by one pass over the weights: tile nt
 // holds tokens 8nt..8nt+7, with its own scales (Q6T_TOK_STRIDE floats further on) and fragments.
 constexpr int Q6T_TOK_STRIDE = 128;     // floats between the token tiles' scale blocks (inside the control bytes)
+// tiled_body is the work of CTA `block` of `nblocks` (Q6T_THREADS threads, all of them call; `smem` 128-byte
+// aligned): the kernel runs it for its own index in the grid, a persistent multi-stage kernel likewise.
 template <typename TILE, int MODE, int NTERMS, int NT>
-__global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs a) {
+__device__ __forceinline__ void tiled_body(const Q6TiledArgs &a, const StagePointers &gp, uint8_t *smem, const int block,
+                                           const int nblocks) {
     constexpr bool GROUPED = (MODE == 3);
     static_assert(NT == 1 || MODE == 0, "several token tiles only in the linear mode");
-    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
-    if (GROUPED) chain_wait();      // the segment list comes from the plan kernel
-    extern __shared__ __align__(128) uint8_t smem[];
     float *tok_scale = reinterpret_cast<float *>(smem);           // per token tile: [8] scale, [8] inverse, [8] amax bits
     float *route_w = reinterpret_cast<float *>(smem + 128);       // [8]
     int *seg_tokens = reinterpret_cast<int *>(smem + 192);        // [8]
@@ -384,13 +384,13 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs
     const int blocks_per_unit = (groups_total + a.rg - 1) / a.rg;
     long long units = 1;
     if (GROUPED) {
-        int nseg = *a.num_segments;
+        int nseg = *gp.num_segments;
         if (nseg > a.max_segments) nseg = a.max_segments;
         units = nseg;
     }
     const long long total_blocks = units * blocks_per_unit;
-    const long long blk_begin = total_blocks * blockIdx.x / gridDim.x;
-    const long long blk_end = total_blocks * (blockIdx.x + 1) / gridDim.x;
+    const long long blk_begin = total_blocks * block / nblocks;
+    const long long blk_end = total_blocks * (block + 1) / nblocks;
     if (!GROUPED) {
         // the CTA's row blocks are one contiguous run of tiles
         if (blk_begin < blk_end) {
@@ -404,9 +404,9 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs
 
     const int items_per_block = kpi < nsb ? (nsb - kpi + a.kp - 1) / a.kp : 0;
     auto block_base = [&](int unit, int bi) -> const uint8_t * {
-        const int expert = GROUPED ? a.seg_expert[unit] : 0;
+        const int expert = GROUPED ? gp.seg_expert[unit] : 0;
         const int group = min(bi * a.rg + rgi, groups_total - 1);      // clamped groups are loaded, never stored
-        return expert_matrix(a.w, a.stride, a.table, expert) +
+        return expert_matrix(a.w, a.stride, gp.table_a, expert) +
                (static_cast<size_t>(group) * nsb + kpi) * TILE::BYTES;
     };
     const size_t item_step = static_cast<size_t>(a.kp) * TILE::BYTES;
@@ -423,7 +423,7 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
             prepare_fragments<NTERMS, (NT == 1 ? 4 : 2)>([nt](int t) { return 8 * nt + t; }, max(min(a.m - 8 * nt, 8), 0),
-                                                         a.k, a.x, a.x_dtype, bfrag + nt * tile_stride,
+                                                         a.k, gp.x, a.x_dtype, bfrag + nt * tile_stride,
                                                          tok_scale + nt * Q6T_TOK_STRIDE, tid);
     }
 
@@ -436,18 +436,18 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs
         if (has_next) nxt_p = block_base(unit_i, bi);
         if (GROUPED && unit != cur_unit) {
             cur_unit = unit;
-            seg_begin = a.seg_begin[unit];
-            m_tokens = min(a.seg_count[unit], 8);
+            seg_begin = gp.seg_begin[unit];
+            m_tokens = min(gp.seg_count[unit], 8);
             named_barrier_sync(1, Q6T_THREADS);
             if (tid < m_tokens) {
-                const int flat = a.order[seg_begin + tid];
+                const int flat = gp.order[seg_begin + tid];
                 seg_tokens[tid] = seg_begin + tid;
-                route_w[tid] = a.route[flat];
-                out_ptr[tid] = term_row_pointer(static_cast<float *>(a.y), a.y_table, a.rows_per_rank, a.n,
+                route_w[tid] = gp.route[flat];
+                out_ptr[tid] = term_row_pointer(static_cast<float *>(gp.y), a.y_table, a.rows_per_rank, a.n,
                                                 a.flat_rows ? flat : seg_begin + tid);
             }
             named_barrier_sync(1, Q6T_THREADS);
-            prepare_fragments<NTERMS, 2>([&](int t) { return seg_tokens[t]; }, m_tokens, a.k, a.x, a.x_dtype, bfrag,
+            prepare_fragments<NTERMS, 2>([&](int t) { return seg_tokens[t]; }, m_tokens, a.k, gp.x, a.x_dtype, bfrag,
                                       tok_scale, tid);
         }
 
@@ -474,7 +474,7 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs
                         const int orow = group * 16 + g + 8 * (i >> 1), tl = 2 * tig + (i & 1), t = 8 * nt + tl;
                         if (t < m_tokens) {
                             const float v = tot[nt][i] * tok_scale[nt * Q6T_TOK_STRIDE + 8 + tl];
-                            if (MODE == 0) store_from_float(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, v);
+                            if (MODE == 0) store_from_float(gp.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, v);
                             else out_ptr[t][orow] = v * route_w[t];
                         }
                     }
@@ -499,13 +499,22 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs
                 for (int kq = 0; kq < a.kp; ++kq) v += src[kq * (NT * 128)];
                 v *= tok_scale[nt * Q6T_TOK_STRIDE + 8 + tl];
                 const int orow = group * 16 + r;
-                if (MODE == 0) store_from_float(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, v);
+                if (MODE == 0) store_from_float(gp.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, v);
                 else out_ptr[t][orow] = v * route_w[t];
             }
             pbuf ^= 1;
         }
         cur_p = nxt_p;
     }
+}
+
+template <typename TILE, int MODE, int NTERMS, int NT>
+__global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs a) {
+    chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
+    if (MODE == 3) chain_wait();      // the segment list comes from the plan kernel
+    extern __shared__ __align__(128) uint8_t smem[];
+    const StagePointers gp{a.x, a.y, a.table, nullptr, a.order, a.seg_expert, a.seg_begin, a.seg_count, a.num_segments, a.route};
+    tiled_body<TILE, MODE, NTERMS, NT>(a, gp, smem, blockIdx.x, gridDim.x);
 }
 
 }  // namespace b200q

@@ -3,6 +3,7 @@
 // (mini_llm/ops/router_decode.py:16-96): descending logit, ties -> lower id, NaN last,
 // p = exp(v - max) / sum, optional division by max(selected mass, floor).
 #include "common.cuh"
+#include "router_device.cuh"
 
 namespace b200q {
 
@@ -173,136 +174,14 @@ int launch_combine_cols(const float *terms, const int32_t *inv, int rows, int k,
     return check_launch("moe_combine");
 }
 
-// One CTA of four warps per row, n <= 1024 (eight values per thread, value idx = i*128 + tid).
-// Every value becomes a 64-bit key that orders like the selection rule: high word = the float's
-// bits made monotonic (NaN -> 0, below -inf; -0 counted as +0), low word = ~index, so the largest
-// key is the largest logit and, among equals, the lowest index. A round is then two warp-wide
-// integer maximum reductions plus one exchange between the four warps.
-__device__ __forceinline__ uint32_t orderable_bits(float v) {
-    if (isnan(v)) return 0u;
-    const uint32_t b = __float_as_uint(v + 0.0f);
-    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-}
-__device__ __forceinline__ float from_orderable_bits(uint32_t h) {
-    if (h == 0u) return __int_as_float(0x7fc00000);
-    return __uint_as_float((h & 0x80000000u) ? (h & 0x7fffffffu) : ~h);
-}
-
+// One CTA of four warps per row, n <= 1024; the arithmetic is topk_row (router_device.cuh).
 __global__ void __launch_bounds__(128) router_topk_block_kernel(const float *logits, int n, int k, int renorm,
                                                                 float floor_value, int extra_id,
                                                                 const float *extra_weight, float *weights,
                                                                 int64_t *ids, const RowPlanOut plan) {
     chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
     chain_wait();         // inputs come from preceding kernels
-    __shared__ unsigned long long warp_best[2][4];
-    __shared__ float red[4];
-    __shared__ float sel_p[32];
-    __shared__ int sel_i[32];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int row = blockIdx.x;
-    const float neg_inf = __int_as_float(0xff800000), qnan = __int_as_float(0x7fc00000);
-    const float *src = logits + static_cast<size_t>(row) * n;
-    float v[8];
-    uint32_t hi[8];
-    float mx = neg_inf;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int idx = i * 128 + tid;
-        v[i] = idx < n ? src[idx] : neg_inf;
-        hi[i] = idx < n ? orderable_bits(v[i]) : 0u;
-        if (idx < n) mx = (isnan(v[i]) || isnan(mx)) ? qnan : fmaxf(mx, v[i]);
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) {
-        const float other = __shfl_xor_sync(0xffffffffu, mx, o);
-        mx = (isnan(mx) || isnan(other)) ? qnan : fmaxf(mx, other);
-    }
-    if (lane == 0) red[warp] = mx;
-    __syncthreads();
-    mx = red[0];
-#pragma unroll
-    for (int w = 1; w < 4; ++w) mx = (isnan(mx) || isnan(red[w])) ? qnan : fmaxf(mx, red[w]);
-    __syncthreads();
-    float den = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-        if (i * 128 + tid < n) den += expf(v[i] - mx);
-    den = warp_sum(den);
-    if (lane == 0) red[warp] = den;
-    __syncthreads();
-    den = ((red[0] + red[1]) + red[2]) + red[3];
-
-    for (int slot = 0; slot < k; ++slot) {
-        // best key of this thread among its values that are inside the row and not yet taken
-        uint32_t bh = 0u, bl = 0u;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t lo = ~static_cast<uint32_t>(i * 128 + tid);
-            const bool take = (i * 128 + tid < n) && (hi[i] > bh || (hi[i] == bh && lo > bl)) && hi[i] != 0xffffffffu;
-            if (take) { bh = hi[i]; bl = lo; }
-        }
-        const uint32_t wh = __reduce_max_sync(0xffffffffu, bh);
-        const uint32_t wl = __reduce_max_sync(0xffffffffu, bh == wh ? bl : 0u);
-        if (lane == 0) warp_best[slot & 1][warp] = (static_cast<unsigned long long>(wh) << 32) | wl;
-        __syncthreads();
-        unsigned long long best = warp_best[slot & 1][0];
-#pragma unroll
-        for (int w = 1; w < 4; ++w) best = max(best, warp_best[slot & 1][w]);
-        const int bi = static_cast<int>(~static_cast<uint32_t>(best));
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-            if (i * 128 + tid == bi) hi[i] = 0xffffffffu;          // marks "taken" (never a real key)
-        if (tid == 0) {
-            sel_p[slot] = __fdiv_rn(expf(from_orderable_bits(static_cast<uint32_t>(best >> 32)) - mx), den);
-            sel_i[slot] = bi;
-        }
-    }
-    __syncthreads();
-    const int k_out = k + (extra_id >= 0 ? 1 : 0);
-    float norm = 1.0f;
-    if (renorm) {
-        float mass = 0.f;
-        for (int s = 0; s < k; ++s) mass = __fadd_rn(mass, sel_p[s]);      // slot order, same on every thread
-        norm = isnan(mass) ? mass : fmaxf(mass, floor_value);
-    }
-    if (tid < k) {
-        weights[static_cast<size_t>(row) * k_out + tid] = renorm ? __fdiv_rn(sel_p[tid], norm) : sel_p[tid];
-        ids[static_cast<size_t>(row) * k_out + tid] = sel_i[tid];
-    }
-    if (extra_id >= 0 && tid == 0) {
-        ids[static_cast<size_t>(row) * k_out + k] = extra_id;
-        weights[static_cast<size_t>(row) * k_out + k] = extra_weight ? extra_weight[row] : 1.0f;
-    }
-    if (plan.order != nullptr) {
-        // Single row (grid of one CTA): the routing plan of its k_out distinct ids. Position of an
-        // assignment = number of smaller ids; one segment of one row per selected expert, ascending.
-        auto id_of = [&](int j) { return j < k ? sel_i[j] : extra_id; };
-        if (tid < k_out) {
-            const int mine = id_of(tid);
-            int pos = 0;
-            for (int j = 0; j < k_out; ++j) pos += id_of(j) < mine;
-            plan.order[pos] = tid;
-            plan.inv[tid] = pos;
-            if (pos < plan.max_segments) {
-                plan.seg_expert[pos] = mine;
-                plan.seg_begin[pos] = pos;
-                plan.seg_count[pos] = 1;
-            }
-        }
-        for (int ex = tid; ex <= plan.e; ex += 128) {
-            int below = 0, hit = 0;
-            for (int j = 0; j < k_out; ++j) {
-                below += id_of(j) < ex;
-                hit += id_of(j) == ex;
-            }
-            plan.offsets[ex] = below;
-            if (ex < plan.e) plan.counts[ex] = hit;
-        }
-        if (tid == 0) {
-            plan.num_segments[0] = min(k_out, plan.max_segments);
-            plan.status[0] = k_out > plan.max_segments ? 2 : 0;
-        }
-    }
+    topk_row(blockIdx.x, threadIdx.x, logits, n, k, renorm, floor_value, extra_id, extra_weight, weights, ids, plan);
 }
 
 int launch_topk_warp(const float *logits, int rows, int n, int k, int renorm, float floor_value, int extra_id,

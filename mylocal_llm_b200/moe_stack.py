@@ -8,9 +8,11 @@ of layer i+1 (``residual_add_rmsnorm``), as the reference's low-precision engine
 quantized path exactly as the 48-layer benchmark configuration prescribes.
 """
 
+import ctypes
 import os
 
-from .experts_inference import synthetic_bank
+from . import _lib
+from .experts_inference import ResidentExpertExecutor, synthetic_bank
 from .moe_layer import PackedMoELayer, RMSNormInference
 from .quantize import random_packed
 from .quantized_linear import packed_to_device
@@ -30,6 +32,10 @@ class PackedMoEStack:
         # default: one CTA per row has less parallelism than the two kernels it replaces and measured slower
         # (1 token: 384 vs 425 tokens/s on the 48-layer stack; 64 tokens: 5019 vs 5069); the results are the same.
         self.fuse_residual_norm = os.environ.get("B200Q_FUSE_NORM", "0") == "1"
+        # One-token steps run as one persistent kernel over all layers when the stack qualifies
+        # (``B200Q_PERSISTENT=0``: always the chain of launches; the results are the same bits).
+        self.persistent_step = os.environ.get("B200Q_PERSISTENT", "1") != "0"
+        self._persistent = None           # (layer table, workspace, call arguments) or False once found unfit
 
     @property
     def packed_bytes(self):
@@ -40,10 +46,73 @@ class PackedMoEStack:
                 total += sum(w.nbytes for w in layer.shared)
         return total
 
+    def _persistent_setup(self):
+        """Layer table and workspace of ``b200q_moe_decode_stack`` if every layer fits it: resident executor,
+        routed and shared experts behind 16-byte aligned pointer tables, no router bias, no shared gate, one
+        shape / format / top-k / floor for all layers, norm weights of one 16-bit type."""
+        torch = _torch()
+        first = self.layers[0]
+        bank = first.bank
+        norms = list(self.norms) + [self.final_norm]
+        dtypes = {n.gamma.dtype for n in norms}
+        key = lambda l: (l.bank.d_model, l.bank.d_ff, l.bank.n_experts, l.router.k, l.router.normalization_floor,
+                         l.bank.gate_type, l.bank.up_type, l.bank.down_type)
+        fits = (len(dtypes) == 1 and next(iter(dtypes)) in (torch.bfloat16, torch.float16)
+                and len({n.eps for n in norms}) == 1
+                and all(isinstance(l.executor, ResidentExpertExecutor) and l._tables is not None and l._tables[1]
+                        and l.shared_gate is None and l.router.b_router is None and l.fuse_row_plan
+                        and l.router._w_expert_major is not None and l.router._w_expert_major.data_ptr() % 16 == 0
+                        and key(l) == key(first) for l in self.layers)
+                and bank.gate_type == bank.up_type and bank.gate_type in ("Q4_K", "Q4_K_TILED")
+                and bank.down_type == "Q6_K_TILED" and bank.n_experts <= 1024 and first.router.k <= 15
+                and bank.d_model % 256 == 0 and bank.d_ff % 256 == 0)
+        if not fits:
+            return False
+        rows = []
+        for i, layer in enumerate(self.layers):
+            tables = layer._tables[0]
+            rows.append([layer.router._w_expert_major.data_ptr(), tables[0].data_ptr(), tables[1].data_ptr(),
+                         tables[2].data_ptr(), norms[i + 1].gamma.data_ptr()])
+        device = first.router._w_expert_major.device
+        table = torch.tensor(rows, dtype=torch.int64, device=device)
+        d, f, e, k = bank.d_model, bank.d_ff, bank.n_experts, first.router.k
+        nbytes = int(_lib.load().b200q_moe_decode_stack_workspace(d, f, e, k))
+        workspace = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        return table, workspace, (d, f, e, k)
+
+    def forward_one_token(self, residual):
+        """The step for a single row as one persistent kernel, or ``None`` when the stack does not fit it."""
+        torch = _torch()
+        if self._persistent is None:
+            self._persistent = self._persistent_setup()
+        if not self._persistent:
+            return None
+        table, workspace, (d, f, e, k) = self._persistent
+        if not residual.is_contiguous() or residual.dtype != torch.float32 or residual.device != table.device:
+            return None
+        first, gamma0 = self.layers[0], self.norms[0].gamma
+        res = torch.empty_like(residual)
+        hidden = torch.empty(residual.shape, dtype=gamma0.dtype, device=residual.device)
+        ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+        try:
+            _lib.call("b200q_moe_decode_stack", ptr(table), len(self.layers), d, f, e, k, 1,
+                      float(first.router.normalization_floor), _lib.FORMAT_ID[first.bank.gate_type],
+                      _lib.FORMAT_ID[first.bank.down_type], ptr(gamma0),
+                      _lib.DTYPE_ID[str(gamma0.dtype).replace("torch.", "")], float(self.norms[0].eps), ptr(residual),
+                      ptr(res), ptr(hidden), ptr(workspace), int(workspace.numel()), _lib.current_stream())
+        except NotImplementedError:
+            self._persistent = False
+            return None
+        return res, hidden
+
     def forward(self, residual, trace=None):
         """residual FP32 [B, T, D] -> (new residual FP32, final normalised activations). ``trace``: a list
         that receives, per layer, ``(layer input, layer output)`` - the tensors a layer-by-layer check
         against a reference needs; it forces the two-kernel combine + norm."""
+        if trace is None and self.persistent_step and residual.ndim == 3 and residual.shape[0] * residual.shape[1] == 1:
+            out = self.forward_one_token(residual)
+            if out is not None:
+                return out
         res = residual
         hidden = self.norms[0].forward_residual(res)
         for i, layer in enumerate(self.layers):
