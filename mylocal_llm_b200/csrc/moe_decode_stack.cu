@@ -93,7 +93,6 @@ __device__ __forceinline__ bool grid_barrier(unsigned int *words, unsigned int &
                 }
             }
         }
-        __threadfence();
         if (!ok) *abort_smem = 1;
     }
     ++generation;
@@ -257,6 +256,11 @@ __global__ void __launch_bounds__(DS_THREADS, 1) moe_decode_stack_kernel(const D
     int32_t *seg_count = seg_begin + DS_PLAN_SLOTS;
     int32_t *num_segments = seg_count + DS_PLAN_SLOTS;                  // [1] (+ the plan's status word)
     float *logit_s = reinterpret_cast<float *>(num_segments + 2);       // [e] the row's logits
+    // The selected experts' matrix addresses, per segment: fetched once per layer right after the top-k, so the
+    // stage bodies (given the identity as their segment -> expert map and these as their pointer tables) do not
+    // start with a dependent look-up in global memory.
+    __shared__ unsigned long long gate_ptrs[DS_PLAN_SLOTS], up_ptrs[DS_PLAN_SLOTS], down_ptrs[DS_PLAN_SLOTS];
+    __shared__ int32_t seg_ident[DS_PLAN_SLOTS];
 
     if (tid == 0) abort_flag = 0;
     unsigned int generation = 0;                                         // the host zeroes the words before the launch
@@ -267,9 +271,10 @@ __global__ void __launch_bounds__(DS_THREADS, 1) moe_decode_stack_kernel(const D
     __syncthreads();
 
     if (tid == 0) {
-        gu_ptrs = StagePointers{x_act, p.hbuf, nullptr, nullptr, order, seg_expert, seg_begin, seg_count, num_segments, nullptr};
-        dn_ptrs = StagePointers{p.hbuf, p.terms, nullptr, nullptr, order, seg_expert, seg_begin, seg_count, num_segments, weights};
+        gu_ptrs = StagePointers{x_act, p.hbuf, gate_ptrs, up_ptrs, order, seg_ident, seg_begin, seg_count, num_segments, nullptr};
+        dn_ptrs = StagePointers{p.hbuf, p.terms, down_ptrs, nullptr, order, seg_ident, seg_begin, seg_count, num_segments, weights};
     }
+    if (tid < DS_PLAN_SLOTS) seg_ident[tid] = tid;
     __syncthreads();
     const RowPlanOut plan{nullptr, nullptr, order, inv, seg_expert, seg_begin, seg_count, num_segments, num_segments + 1,
                           e + 1, p.max_segments};
@@ -286,16 +291,40 @@ __global__ void __launch_bounds__(DS_THREADS, 1) moe_decode_stack_kernel(const D
         // (every thread fetches a logit or two into shared memory: one round trip instead of the lane's sixteen)
         for (int i = tid; i < e; i += DS_THREADS) logit_s[i] = __ldcg(p.logits + i);
         __syncthreads();
-        if (warp == 0) stage_topk(lane, logit_s, e, p.k, p.renorm, p.floor_value, weights, ids, &plan);
-        if (tid == DS_THREADS - 1) {
-            gu_ptrs.table_a = lay.gate_table;
-            gu_ptrs.table_b = lay.up_table;
-            dn_ptrs.table_a = lay.down_table;
+        if (warp == 0) {
+            stage_topk(lane, logit_s, e, p.k, p.renorm, p.floor_value, weights, ids, &plan);
+            __syncwarp();
+            const int nseg = min(num_segments[0], p.max_segments);
+            for (int u = lane; u < nseg; u += 32) {
+                const int ex = seg_expert[u];
+                gate_ptrs[u] = lay.gate_table[ex];
+                up_ptrs[u] = lay.up_table[ex];
+                down_ptrs[u] = lay.down_table[ex];
+            }
+        } else if (layer + 1 < p.n_layers) {
+            // meanwhile: ask L2 for the router rows this CTA's warps take in the next layer
+            const float *next_wt = p.layers[layer + 1].router_wt;
+            for (int row = block * (DS_THREADS / 32) + warp; row < e; row += nblocks * (DS_THREADS / 32))
+                for (int off = lane * 32; off < d; off += 32 * 32)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(next_wt + static_cast<size_t>(row) * d + off));
         }
         __syncthreads();
+        {
+            // ask L2 for the down-projection tiles of this CTA's blocks of stage D (the split tiled_body makes)
+            const int nseg = min(num_segments[0], p.max_segments);
+            const int groups_total = d >> 4, nsb_d = p.f >> 8;
+            const int bpu = (groups_total + p.dn.rg - 1) / p.dn.rg;
+            const long long total = static_cast<long long>(nseg) * bpu;
+            for (long long blk = total * block / nblocks; blk < total * (block + 1) / nblocks; ++blk) {
+                const int unit = static_cast<int>(blk / bpu), group0 = static_cast<int>(blk - static_cast<long long>(unit) * bpu) * p.dn.rg;
+                const int groups = min(p.dn.rg, groups_total - group0);
+                const uint8_t *base = reinterpret_cast<const uint8_t *>(static_cast<uintptr_t>(down_ptrs[unit])) +
+                                      static_cast<size_t>(group0) * nsb_d * Q6T_TILE_BYTES;
+                prefetch_l2_range(base, static_cast<size_t>(groups) * nsb_d * Q6T_TILE_BYTES, 1u << 20, tid, DS_THREADS);
+            }
+        }
 
-        // C: grouped gate/up + SwiGLU -> hbuf (the stages' pointer blocks live in shared memory: thread 0 fills
-        // in what changes with the layer while the first four warps run the top-k)
+        // C: grouped gate/up + SwiGLU -> hbuf
         mma_direct_body<false, 2, 1, 1>(p.gu, gu_ptrs, smem, block, nblocks);
         if (!(ok = grid_barrier(p.sync, generation, nblocks, p.status, &abort_flag))) break;
 
