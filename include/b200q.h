@@ -40,6 +40,9 @@ extern "C" {
 /* Q8_0 in 16-row x 256-value tiles (b200q_q8_0_retile): codes stored +128, eight block scales per row
  * kept as fp16. Accepted by b200q_gemv and b200q_moe_down(_peer); K must be a multiple of 256. */
 #define B200Q_Q8_0_TILED 23
+/* Q5_K in the tile layout of Q4_K plus the rows' fifth bits (b200q_q5k_retile): same size, a permutation of
+ * 16-byte pieces. Accepted where B200Q_Q4_K_TILED is. */
+#define B200Q_Q5_K_TILED 24
 
 /* activation / output element types */
 #define B200Q_F32 0
@@ -265,6 +268,8 @@ int b200q_moe_combine_ids(const float *terms, const void *ids, int ids_is_i64, i
 int b200q_q4k_retile(const void *native, void *tiled, int64_t rows, int k, void *stream);
 int b200q_q4k_untile(const void *tiled, void *native, int64_t rows, int k, void *stream);
 int b200q_q6k_retile(const void *native, void *tiled, int64_t rows, int k, void *stream);
+int b200q_q5k_retile(const void *native, void *tiled, int64_t rows, int k, void *stream);
+int b200q_q5k_untile(const void *tiled, void *native, int64_t rows, int k, void *stream);
 int b200q_q8_0_retile(const void *native, void *tiled, int64_t rows, int k, void *stream);
 int b200q_q8_0_untile(const void *tiled, void *native, int64_t rows, int k, void *stream);
 int b200q_q6k_untile(const void *tiled, void *native, int64_t rows, int k, void *stream);

@@ -14,7 +14,7 @@ _PKG = Path(__file__).resolve().parent
 # B200Q_LIBRARY points the loader at another build of the same ABI (A/B measurements).
 LIB_PATH = Path(os.environ.get("B200Q_LIBRARY") or _PKG / "libb200q.so")
 
-FORMAT_ID = {"Q8_0": 0, "Q4_0": 1, "Q4_K": 2, "Q3_K": 3, "Q5_K": 4, "Q6_K": 5, "Q6_K_TILED": 21, "Q4_K_TILED": 22, "Q8_0_TILED": 23}
+FORMAT_ID = {"Q8_0": 0, "Q4_0": 1, "Q4_K": 2, "Q3_K": 3, "Q5_K": 4, "Q6_K": 5, "Q6_K_TILED": 21, "Q4_K_TILED": 22, "Q8_0_TILED": 23, "Q5_K_TILED": 24}
 DTYPE_ID = {"float32": 0, "float16": 1, "bfloat16": 2}
 
 _c_int, _c_i64, _c_f32, _ptr = ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p
@@ -50,6 +50,8 @@ SIGNATURES = {
     "b200q_moe_decode_stack_workspace": [_c_int, _c_int, _c_int, _c_int],
     "b200q_moe_decode_stack": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f32, _c_int, _c_int, _ptr, _c_int,
                                _c_f32, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr],
+    "b200q_q5k_retile": [_ptr, _ptr, _c_i64, _c_int, _ptr],
+    "b200q_q5k_untile": [_ptr, _ptr, _c_i64, _c_int, _ptr],
     "b200q_moe_token_image_bytes": [_c_int, _c_int],
     "b200q_moe_token_images": [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr],
     "b200q_moe_gate_up_images": [_ptr, _c_i64, _c_int, _ptr, _c_i64, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr,

@@ -93,6 +93,11 @@ inline cudaError_t launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, d
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Q4_K / Q5_K in their tile layouts: the GGUF format a tile-layout id stands for, or -1 for any other id.
+inline int direct_tiled_base(int fmt) {
+    return fmt == B200Q_Q4_K_TILED ? B200Q_Q4_K : fmt == B200Q_Q5_K_TILED ? B200Q_Q5_K : -1;
+}
+
 // Routing-plan outputs the top-k kernel fills itself when it routes a single row (order == nullptr:
 // none). For one row the plan is a sort of k distinct ids, so the separate plan launch of a
 // one-token decode step is saved; the arrays are those of b200q_moe_plan.

@@ -37,7 +37,7 @@ bool direct_plan_args(const MmaRequest &q, DirectArgs *out, long long *smem_out)
     if (dual && q.fmt_a != q.fmt_b) return false;
     if (q.k % 256 != 0 || q.m > direct_tokens_per_pass(q.fmt_a, q.mode, q.k, q.x_dtype)) return false;
     const int token_tiles = q.m > 8 ? 2 : 1;
-    if (q.tiled && (q.fmt_a != B200Q_Q4_K || q.n % 16 != 0)) return false;
+    if (q.tiled && q.n % 16 != 0) return false;
     if (reinterpret_cast<uintptr_t>(q.wa) & 15) return false;
     if (dual && (reinterpret_cast<uintptr_t>(q.wb) & 15)) return false;
     if (grouped && !q.table_a && ((q.stride_a & 15) || (dual && (q.stride_b & 15)))) return false;

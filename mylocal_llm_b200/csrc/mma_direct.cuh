@@ -38,7 +38,7 @@ struct DirectArgs {
     long long stride_a, stride_b;
     const unsigned long long *table_a, *table_b;   // optional per-expert pointer tables
     int rb;              // packed bytes per weight row (both streams share the format)
-    int tiled;           // Q4_K only: weights in the 16-row tile layout (see load_superblock_tiled)
+    int tiled;           // weights in the 16-row tile layout of their format (see load_superblock_tiled)
     int n, k, m;
     int kp, rg;          // warps along K and row groups per CTA pass (kp * rg == 16)
     int nterms;
@@ -122,16 +122,34 @@ __device__ __forceinline__ void load_superblock(SuperBlockRegs<Q5> &r, const uin
 //                row g+8 - exactly the pieces load_superblock() fetches, so the arithmetic is shared.
 // Tiles are ordered (row group, super-block): a warp instruction reads 512 contiguous bytes.
 constexpr int Q4T_TILE_BYTES = 2304;
-__device__ __forceinline__ void load_superblock_tiled(SuperBlockRegs<false> &ra, SuperBlockRegs<false> &rb,
+// Q5_K the same way (2816 bytes, the size of 16 native blocks): the 16 headers, then the rows' 32 bytes of
+// fifth bits (row r at 256 + 32 r; a lane reads the half its elements need, lanes tig and tig + 2 the same
+// one), then the four quant planes:
+//   [0, 256) headers | [256, 768) fifth bits | [768, 2816) planes 0/1 (row g), 2/3 (row g + 8), lane * 16 each
+constexpr int Q5T_TILE_BYTES = 2816;
+template <bool Q5>
+__host__ __device__ constexpr int direct_tile_bytes() { return Q5 ? Q5T_TILE_BYTES : Q4T_TILE_BYTES; }
+
+template <bool Q5>
+__device__ __forceinline__ void load_superblock_tiled(SuperBlockRegs<Q5> &ra, SuperBlockRegs<Q5> &rb,
                                                       const uint8_t *tile, int lane) {
-    const int g = lane >> 2;
+    const int g = lane >> 2, tig = lane & 3;
     ra.hd = ldg128(tile + 16 * g);
     rb.hd = ldg128(tile + 16 * (g + 8));
-    ra.qa = ldg128(tile + 256 + lane * 16);
-    ra.qb = ldg128(tile + 768 + lane * 16);
-    rb.qa = ldg128(tile + 1280 + lane * 16);
-    rb.qb = ldg128(tile + 1792 + lane * 16);
-    ra.qh = rb.qh = make_uint4(0u, 0u, 0u, 0u);
+    if (Q5) {
+        ra.qh = ldg128(tile + 256 + 32 * g + 16 * (tig & 1));
+        rb.qh = ldg128(tile + 256 + 32 * (g + 8) + 16 * (tig & 1));
+        ra.qa = ldg128(tile + 768 + lane * 16);
+        ra.qb = ldg128(tile + 1280 + lane * 16);
+        rb.qa = ldg128(tile + 1792 + lane * 16);
+        rb.qb = ldg128(tile + 2304 + lane * 16);
+    } else {
+        ra.qa = ldg128(tile + 256 + lane * 16);
+        ra.qb = ldg128(tile + 768 + lane * 16);
+        rb.qa = ldg128(tile + 1280 + lane * 16);
+        rb.qb = ldg128(tile + 1792 + lane * 16);
+        ra.qh = rb.qh = make_uint4(0u, 0u, 0u, 0u);
+    }
 }
 
 // Scales of one row for this lane: the four sub-blocks its quant bytes belong to, as FP16 pairs
@@ -489,9 +507,9 @@ __device__ __forceinline__ void mma_direct_body(const DirectArgs &a, const Stage
         // the CTA's row blocks are one contiguous byte range of the matrix (rows, or 16-row tiles)
         if (blk_begin < blk_end) {
             size_t first, last;
-            if (!Q5 && a.tiled) {
-                first = static_cast<size_t>(blk_begin) * a.rg * nsb * Q4T_TILE_BYTES;
-                last = static_cast<size_t>(min(static_cast<long long>(a.n >> 4), blk_end * a.rg)) * nsb * Q4T_TILE_BYTES;
+            if (a.tiled) {
+                first = static_cast<size_t>(blk_begin) * a.rg * nsb * direct_tile_bytes<Q5>();
+                last = static_cast<size_t>(min(static_cast<long long>(a.n >> 4), blk_end * a.rg)) * nsb * direct_tile_bytes<Q5>();
             } else {
                 first = static_cast<size_t>(blk_begin) * rows_per_block * a.rb;
                 last = static_cast<size_t>(min(static_cast<long long>(a.n), blk_end * rows_per_block)) * a.rb;
@@ -517,9 +535,9 @@ __device__ __forceinline__ void mma_direct_body(const DirectArgs &a, const Stage
         BlockPtrs p;
         const int expert = GROUPED ? gp.seg_expert[unit] : 0;
         size_t off_lo, off_hi;
-        if (!Q5 && a.tiled) {   // tile of (row group, super-block kpi); n is a multiple of 16 here
+        if (a.tiled) {   // tile of (row group, super-block kpi); n is a multiple of 16 here
             const int group = min((row0 >> 4) + rgi, (a.n >> 4) - 1);
-            off_lo = off_hi = (static_cast<size_t>(group) * nsb + kpi) * Q4T_TILE_BYTES;
+            off_lo = off_hi = (static_cast<size_t>(group) * nsb + kpi) * direct_tile_bytes<Q5>();
         } else {
             off_lo = static_cast<size_t>(min(row0 + 16 * rgi + g, a.n - 1)) * a.rb + static_cast<size_t>(kpi) * QB;
             off_hi = static_cast<size_t>(min(row0 + 16 * rgi + g + 8, a.n - 1)) * a.rb + static_cast<size_t>(kpi) * QB;
@@ -536,15 +554,13 @@ __device__ __forceinline__ void mma_direct_body(const DirectArgs &a, const Stage
         return p;
     };
     // item -> byte offset from the block pointers, and stream
-    const int sb_step_bytes = a.kp * ((!Q5 && a.tiled) ? Q4T_TILE_BYTES : QB);
+    const int sb_step_bytes = a.kp * (a.tiled ? direct_tile_bytes<Q5>() : QB);
     auto issue_item = [&](const BlockPtrs &p, int item, SuperBlockRegs<Q5> &ra, SuperBlockRegs<Q5> &rb) {
         const int stream = DUAL ? (item & 1) : 0;
         const size_t off = static_cast<size_t>(DUAL ? (item >> 1) : item) * sb_step_bytes;
-        if constexpr (!Q5) {
-            if (a.tiled) {
-                load_superblock_tiled(ra, rb, (stream ? p.b_lo : p.a_lo) + off, lane);
-                return;
-            }
+        if (a.tiled) {
+            load_superblock_tiled<Q5>(ra, rb, (stream ? p.b_lo : p.a_lo) + off, lane);
+            return;
         }
         load_superblock<Q5>(ra, (stream ? p.b_lo : p.a_lo) + off, tig);
         load_superblock<Q5>(rb, (stream ? p.b_hi : p.a_hi) + off, tig);

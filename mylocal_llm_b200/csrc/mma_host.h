@@ -13,7 +13,7 @@ struct MmaRequest {
     long long stride_a, stride_b;
     const unsigned long long *table_a, *table_b;   // optional per-expert pointer tables
     int tables_aligned16;                          // caller vouches: every table entry is 16-byte aligned
-    int tiled;                                     // Q4_K weights in the tile layout (direct kernel only)
+    int tiled;                                     // Q4_K / Q5_K weights in their tile layout (direct kernel only)
     int n, k, m;
     const void *x;
     int x_dtype;

@@ -95,6 +95,33 @@ __global__ void __launch_bounds__(256) q4k_retile_kernel(const uint8_t *src, uin
     if (lane < 16) move(native_at(lane, 0), tile_off + 16 * lane);
 }
 
+// Q5_K <-> tile layout: as Q4_K, plus the rows' 32 bytes of fifth bits (lanes 0-15 move a row's two halves).
+template <bool FORWARD>
+__global__ void __launch_bounds__(256) q5k_retile_kernel(const uint8_t *src, uint8_t *dst, long long tiles, int nsb) {
+    const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    const long long tile = idx >> 5;
+    if (tile >= tiles) return;
+    const int lane = static_cast<int>(idx & 31), g = lane >> 2, tig = lane & 3;
+    const long long group = tile / nsb;
+    const int sb = static_cast<int>(tile - group * nsb);
+    const size_t row_bytes = static_cast<size_t>(nsb) * 176;
+    const size_t tile_off = static_cast<size_t>(tile) * Q5T_TILE_BYTES;
+    auto native_at = [&](int row, int byte) { return (static_cast<size_t>(group) * 16 + row) * row_bytes + static_cast<size_t>(sb) * 176 + byte; };
+    auto move = [&](size_t native_off, size_t tiled_off) {
+        if (FORWARD) *reinterpret_cast<uint4 *>(dst + tiled_off) = *reinterpret_cast<const uint4 *>(src + native_off);
+        else *reinterpret_cast<uint4 *>(dst + native_off) = *reinterpret_cast<const uint4 *>(src + tiled_off);
+    };
+    move(native_at(g, 48 + 16 * tig), tile_off + 768 + lane * 16);
+    move(native_at(g, 112 + 16 * tig), tile_off + 1280 + lane * 16);
+    move(native_at(g + 8, 48 + 16 * tig), tile_off + 1792 + lane * 16);
+    move(native_at(g + 8, 112 + 16 * tig), tile_off + 2304 + lane * 16);
+    if (lane < 16) {
+        move(native_at(lane, 0), tile_off + 16 * lane);
+        move(native_at(lane, 16), tile_off + 256 + 32 * lane);
+        move(native_at(lane, 32), tile_off + 256 + 32 * lane + 16);
+    }
+}
+
 using Q6Fn = void (*)(const Q6TiledArgs);
 
 // Q8_0 <-> tile layout. One thread per (tile, lane): the 16 code words of its two rows (codes +128);
@@ -270,6 +297,25 @@ static int q4k_retile_common(const void *src, void *dst, long long rows, int k, 
     return check_launch("q4k_retile");
 }
 
+static int q5k_retile_common(const void *src, void *dst, long long rows, int k, bool forward, void *stream) {
+    if (!src || !dst) return fail(B200Q_EINVAL, "q5k_retile: NULL pointer");
+    if (rows <= 0 || rows % 16 != 0 || k <= 0 || k % 256 != 0)
+        return fail(B200Q_EINVAL, "q5k_retile: rows must be a multiple of 16 and K a multiple of 256");
+    if (src == dst) return fail(B200Q_EINVAL, "q5k_retile: in-place conversion is not supported");
+    if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15)
+        return fail(B200Q_EINVAL, "q5k_retile: both buffers must be 16-byte aligned");
+    const int nsb = k / 256;
+    const long long tiles = rows / 16 * nsb;
+    const unsigned blocks = static_cast<unsigned>((tiles * 32 + 255) / 256);
+    if (forward)
+        q5k_retile_kernel<true><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst), tiles, nsb);
+    else
+        q5k_retile_kernel<false><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst), tiles, nsb);
+    return check_launch("q5k_retile");
+}
+
 static int q8_retile_common(const void *src, void *dst, long long rows, int k, bool forward, void *stream) {
     if (!src || !dst) return fail(B200Q_EINVAL, "q8_0_retile: NULL pointer");
     if (rows <= 0 || rows % 16 != 0 || k <= 0 || k % 256 != 0)
@@ -293,6 +339,14 @@ extern "C" int b200q_q8_0_retile(const void *native, void *tiled, int64_t rows, 
 
 extern "C" int b200q_q8_0_untile(const void *tiled, void *native, int64_t rows, int k, void *stream) {
     return q8_retile_common(tiled, native, rows, k, false, stream);
+}
+
+extern "C" int b200q_q5k_retile(const void *native, void *tiled, int64_t rows, int k, void *stream) {
+    return q5k_retile_common(native, tiled, rows, k, true, stream);
+}
+
+extern "C" int b200q_q5k_untile(const void *tiled, void *native, int64_t rows, int k, void *stream) {
+    return q5k_retile_common(tiled, native, rows, k, false, stream);
 }
 
 extern "C" int b200q_q4k_retile(const void *native, void *tiled, int64_t rows, int k, void *stream) {

@@ -55,14 +55,14 @@ extern "C" int b200q_expert_ffn_static(const void *gate, int gate_fmt, const voi
     if (m < 1 || d_ff < 1 || d_model < 1) return fail(B200Q_EINVAL, "expert_ffn_static: bad shape");
     // everything the two inner calls would reject is checked here, so either both kernels launch or none
     auto base_fmt = [](int fmt, bool swiglu_side) {
-        if (fmt == B200Q_Q4_K_TILED) return B200Q_Q4_K;
+        if (direct_tiled_base(fmt) >= 0) return direct_tiled_base(fmt);
         if (!swiglu_side && fmt == B200Q_Q6_K_TILED) return B200Q_Q6_K;
         if (!swiglu_side && fmt == B200Q_Q8_0_TILED) return B200Q_Q8_0;
         return fmt;
     };
     const int gf = base_fmt(gate_fmt, true), uf = base_fmt(up_fmt, true), df = base_fmt(down_fmt, false);
     if (!fmt_valid(gf) || !fmt_valid(uf) || !fmt_valid(df)) return fail(B200Q_EINVAL, "expert_ffn_static: unknown format");
-    if ((gate_fmt == B200Q_Q4_K_TILED) != (up_fmt == B200Q_Q4_K_TILED))
+    if ((direct_tiled_base(gate_fmt) >= 0) != (direct_tiled_base(up_fmt) >= 0))
         return fail(B200Q_EINVAL, "expert_ffn_static: gate and up must share the layout");
     if (!dtype_valid(x_dtype) || !dtype_valid(y_dtype)) return fail(B200Q_EINVAL, "expert_ffn_static: bad element type");
     if (d_model % fmt_elems(gf) || d_model % fmt_elems(uf) || d_ff % fmt_elems(df))

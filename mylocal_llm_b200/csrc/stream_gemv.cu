@@ -132,8 +132,8 @@ int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype,
         }
         return B200Q_OK;
     }
-    const bool tiled = fmt == B200Q_Q4_K_TILED;
-    if (tiled) fmt = B200Q_Q4_K;
+    const bool tiled = direct_tiled_base(fmt) >= 0;
+    if (tiled) fmt = direct_tiled_base(fmt);
     if (!fmt_valid(fmt)) return fail(B200Q_EINVAL, "gemv: unknown format %d", fmt);
     if (!dtype_valid(x_dtype) || !dtype_valid(y_dtype)) return fail(B200Q_EINVAL, "gemv: bad dtype");
     if (n <= 0 || m <= 0 || !k_ok(fmt, k)) return fail(B200Q_EINVAL, "gemv: bad shape n=%d k=%d m=%d", n, k, m);
@@ -170,7 +170,7 @@ int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype,
         }
         if (all) return B200Q_OK;
     }
-    if (tiled) return fail(B200Q_EUNSUPPORTED, "gemv: no kernel reads this shape in the Q4_K tile layout");
+    if (tiled) return fail(B200Q_EUNSUPPORTED, "gemv: no kernel reads this shape in the Q4_K / Q5_K tile layout");
     const int mt = tokens_per_launch(m, k);
     if (mt < 1) return fail(B200Q_EUNSUPPORTED, "gemv: K=%d too large", k);
     int rc = plan_tiles(a, false, mt);
@@ -192,9 +192,9 @@ int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype,
 int b200q_swiglu(const void *gate, int gate_fmt, const void *up, int up_fmt, int f, int k, const void *x,
                  int x_dtype, int m, void *h, int h_dtype, void *stream) {
     if (!gate || !up || !x || !h) return fail(B200Q_EINVAL, "swiglu: NULL pointer");
-    const bool tiled = gate_fmt == B200Q_Q4_K_TILED;
-    if (tiled != (up_fmt == B200Q_Q4_K_TILED)) return fail(B200Q_EINVAL, "swiglu: gate and up must share the layout");
-    if (tiled) gate_fmt = up_fmt = B200Q_Q4_K;
+    const bool tiled = direct_tiled_base(gate_fmt) >= 0;
+    if (tiled != (direct_tiled_base(up_fmt) >= 0)) return fail(B200Q_EINVAL, "swiglu: gate and up must share the layout");
+    if (tiled) { gate_fmt = direct_tiled_base(gate_fmt); up_fmt = direct_tiled_base(up_fmt); }
     if (!fmt_valid(gate_fmt) || !fmt_valid(up_fmt)) return fail(B200Q_EINVAL, "swiglu: unknown format");
     if (!dtype_valid(x_dtype) || !dtype_valid(h_dtype)) return fail(B200Q_EINVAL, "swiglu: bad dtype");
     if (f <= 0 || m <= 0 || !k_ok(gate_fmt, k) || !k_ok(up_fmt, k))
@@ -233,7 +233,7 @@ int b200q_swiglu(const void *gate, int gate_fmt, const void *up, int up_fmt, int
         }
         if (all) return B200Q_OK;
     }
-    if (tiled) return fail(B200Q_EUNSUPPORTED, "swiglu: no kernel reads this shape in the Q4_K tile layout");
+    if (tiled) return fail(B200Q_EUNSUPPORTED, "swiglu: no kernel reads this shape in the Q4_K / Q5_K tile layout");
     const int mt = tokens_per_launch(m, k);
     if (mt < 1) return fail(B200Q_EUNSUPPORTED, "swiglu: K=%d too large", k);
     int rc = plan_tiles(a, true, mt);
@@ -261,10 +261,10 @@ static int moe_gate_up_impl(const void *gate_base, int64_t gate_stride, int gate
                             const void *images, void *stream) {
     if ((!gate_table != !up_table) || (!gate_table && (!gate_base || !up_base)) || !x || !order || !seg_expert || !seg_begin || !seg_count || !num_segments || !hbuf)
         return fail(B200Q_EINVAL, "moe_gate_up: NULL pointer");
-    const bool tiled = gate_fmt == B200Q_Q4_K_TILED;
-    if (tiled != (up_fmt == B200Q_Q4_K_TILED))
+    const bool tiled = direct_tiled_base(gate_fmt) >= 0;
+    if (tiled != (direct_tiled_base(up_fmt) >= 0))
         return fail(B200Q_EINVAL, "moe_gate_up: gate and up must share the layout");
-    if (tiled) gate_fmt = up_fmt = B200Q_Q4_K;
+    if (tiled) { gate_fmt = direct_tiled_base(gate_fmt); up_fmt = direct_tiled_base(up_fmt); }
     if (!fmt_valid(gate_fmt) || !fmt_valid(up_fmt) || !dtype_valid(x_dtype))
         return fail(B200Q_EINVAL, "moe_gate_up: bad format/dtype");
     if (f <= 0 || k <= 0 || max_segments <= 0 || !k_ok(gate_fmt, d) || !k_ok(up_fmt, d))
@@ -308,7 +308,7 @@ static int moe_gate_up_impl(const void *gate_base, int64_t gate_stride, int gate
         int rc = mma_try_launch(q, static_cast<cudaStream_t>(stream), &launched);
         if (rc || launched) return rc;
     }
-    if (tiled) return fail(B200Q_EUNSUPPORTED, "moe_gate_up: no kernel reads this shape in the Q4_K tile layout");
+    if (tiled) return fail(B200Q_EUNSUPPORTED, "moe_gate_up: no kernel reads this shape in the Q4_K / Q5_K tile layout");
     if (static_cast<long long>(MAX_TOKENS) * d * 4 > XBUF_LIMIT)
         return fail(B200Q_EUNSUPPORTED, "moe_gate_up: d=%d too large for %d tokens per segment", d, MAX_TOKENS);
     int rc = plan_tiles(a, true, MAX_TOKENS);
@@ -372,8 +372,8 @@ static int moe_down_impl(const void *down_base, int64_t down_stride, int down_fm
         q.rows_per_rank = rows_per_rank;
         return q6k_tiled_launch(q, static_cast<cudaStream_t>(stream));
     }
-    const bool tiled = down_fmt == B200Q_Q4_K_TILED;
-    if (tiled) down_fmt = B200Q_Q4_K;
+    const bool tiled = direct_tiled_base(down_fmt) >= 0;
+    if (tiled) down_fmt = direct_tiled_base(down_fmt);
     if (!fmt_valid(down_fmt)) return fail(B200Q_EINVAL, "moe_down: bad format");
     if (d <= 0 || max_segments <= 0 || !k_ok(down_fmt, f)) return fail(B200Q_EINVAL, "moe_down: bad shape d=%d f=%d", d, f);
     int *status = device_status_word();
@@ -416,7 +416,7 @@ static int moe_down_impl(const void *down_base, int64_t down_stride, int down_fm
         int rc = mma_try_launch(q, static_cast<cudaStream_t>(stream), &launched);
         if (rc || launched) return rc;
     }
-    if (tiled) return fail(B200Q_EUNSUPPORTED, "moe_down: no kernel reads this shape in the Q4_K tile layout");
+    if (tiled) return fail(B200Q_EUNSUPPORTED, "moe_down: no kernel reads this shape in the Q4_K / Q5_K tile layout");
     if (static_cast<long long>(MAX_TOKENS) * f * 4 > XBUF_LIMIT)
         return fail(B200Q_EUNSUPPORTED, "moe_down: f=%d too large for %d tokens per segment", f, MAX_TOKENS);
     int rc = plan_tiles(a, false, MAX_TOKENS);

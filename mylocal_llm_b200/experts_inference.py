@@ -86,13 +86,13 @@ class PackedExpertBank:
                    packed_bytes_to_device(down.data), gate.quant_type, up.quant_type, down.quant_type, e, d, f)
 
     def retiled(self):
-        """Bank with its Q4_K / Q6_K projections in the tile layout (new tensors for the converted
+        """Bank with its Q4_K / Q5_K / Q6_K / Q8_0 projections in the tile layout (new tensors for the converted
         banks, the others are shared). Gate and up are converted together or not at all; shapes the
         layout does not cover keep the GGUF bytes."""
         from .quantized_linear import can_retile, retile_bytes, _RETILE
         gate, up, down = self.gate, self.up, self.down
         gate_type, up_type, down_type = self.gate_type, self.up_type, self.down_type
-        if gate_type == up_type and can_retile(gate_type, self.d_ff, self.d_model) and gate_type == "Q4_K":
+        if gate_type == up_type and can_retile(gate_type, self.d_ff, self.d_model) and gate_type in ("Q4_K", "Q5_K"):
             gate = retile_bytes(gate, self.n_experts * self.d_ff, self.d_model, gate_type)
             up = retile_bytes(up, self.n_experts * self.d_ff, self.d_model, up_type)
             gate_type = up_type = _RETILE[gate_type][1]

@@ -186,7 +186,7 @@ def moe_gate_up(x2d, plan, gate_bank, up_bank, gate_fmt, up_fmt, f, d, gate_stri
     torch = _torch()
     hbuf = torch.empty((plan.rows * plan.k, f), dtype=torch.float32, device=x2d.device)
     if images is None and x2d.shape[0] >= TOKEN_IMAGE_MIN_ROWS and os.environ.get("B200Q_TOKEN_IMAGES", "1") != "0" \
-            and gate_fmt in ("Q4_K", "Q5_K", "Q4_K_TILED") and gate_fmt == up_fmt:
+            and gate_fmt in ("Q4_K", "Q5_K", "Q4_K_TILED", "Q5_K_TILED") and gate_fmt == up_fmt:
         images = token_images(x2d)
     if images is not None:
         _lib.call("b200q_moe_gate_up_images", _ptr(gate_bank), int(gate_stride), _lib.FORMAT_ID[gate_fmt],

@@ -122,8 +122,10 @@ def retile_enabled():
 
 
 _RETILE = {"Q6_K": ("b200q_q6k_retile", "Q6_K_TILED"), "Q4_K": ("b200q_q4k_retile", "Q4_K_TILED"),
+           "Q5_K": ("b200q_q5k_retile", "Q5_K_TILED"),
            "Q8_0": ("b200q_q8_0_retile", "Q8_0_TILED")}
-_UNTILE = {"Q6_K_TILED": "b200q_q6k_untile", "Q4_K_TILED": "b200q_q4k_untile", "Q8_0_TILED": "b200q_q8_0_untile"}
+_UNTILE = {"Q6_K_TILED": "b200q_q6k_untile", "Q4_K_TILED": "b200q_q4k_untile", "Q8_0_TILED": "b200q_q8_0_untile",
+           "Q5_K_TILED": "b200q_q5k_untile"}
 
 
 def retile_bytes(data, rows, k, quant_type):
@@ -156,7 +158,7 @@ def can_retile(quant_type, rows, k, force=False):
 
 
 def retile_weight(weight, force=False):
-    """``DevicePackedGGUFWeight`` in the tile layout when its type has one (Q4_K, Q6_K, Q8_0) and the
+    """``DevicePackedGGUFWeight`` in the tile layout when its type has one (Q4_K, Q5_K, Q6_K, Q8_0) and the
     shape allows it (rows a multiple of 16, K a multiple of 256 and <= TILED_MAX_K); otherwise the
     weight itself. ``force`` lifts the K limit for callers that only ever pass 16-bit activations
     (Q4_K and Q8_0 up to K = 8192)."""
@@ -170,8 +172,8 @@ def retile_weight(weight, force=False):
 
 def retile_gate_up(gate, up, force=False):
     """Gate / up pair for the fused SwiGLU launch: both in the tile layout when the fused kernel reads
-    it (Q4_K for both), otherwise both unchanged."""
-    if gate.quant_type == up.quant_type == "Q4_K":
+    it (Q4_K or Q5_K for both), otherwise both unchanged."""
+    if gate.quant_type == up.quant_type and gate.quant_type in ("Q4_K", "Q5_K"):
         gate_t, up_t = retile_weight(gate, force), retile_weight(up, force)
         if gate_t.quant_type == up_t.quant_type:
             return gate_t, up_t

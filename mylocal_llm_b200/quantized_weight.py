@@ -26,7 +26,7 @@ BLOCK_FORMATS = {
 
 # Device-only layouts: a lossless re-ordering of a GGUF type's bytes (same size) that only the GPU
 # kernels read; host-side PackedGGUFWeight never carries them.
-DEVICE_LAYOUTS = {"Q6_K_TILED": "Q6_K", "Q4_K_TILED": "Q4_K", "Q8_0_TILED": "Q8_0"}
+DEVICE_LAYOUTS = {"Q6_K_TILED": "Q6_K", "Q4_K_TILED": "Q4_K", "Q8_0_TILED": "Q8_0", "Q5_K_TILED": "Q5_K"}
 
 
 def block_format(quant_type):

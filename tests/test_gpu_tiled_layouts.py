@@ -1,4 +1,4 @@
-"""Device tile layouts of Q6_K and Q4_K: lossless re-ordering, and the kernels that read them, against
+"""Device tile layouts of Q6_K, Q4_K, Q5_K and Q8_0: lossless re-ordering, and the kernels that read them, against
 the oracle and against the kernels that read the GGUF bytes."""
 
 import numpy as np
@@ -41,8 +41,8 @@ def test_retile_rejects_bad_shapes(cuda):
         retile_q6k(buf, 24, 256)                     # rows not a multiple of 16
     small = packed_to_device(random_packed("Q6_K", (24, 256), seed=1))
     assert retile_weight(small) is small             # kept native
-    q5 = packed_to_device(random_packed("Q5_K", (32, 256), seed=1))
-    assert retile_weight(q5) is q5                   # no tile layout for this type
+    q3 = packed_to_device(random_packed("Q3_K", (32, 256), seed=1))
+    assert retile_weight(q3) is q3                   # no tile layout for this type
     wide = packed_to_device(random_packed("Q4_K", (16, 8192), seed=1))
     assert retile_weight(wide) is wide               # K above the limit stays native unless forced
 
@@ -105,45 +105,52 @@ def test_grouped_down_on_a_tiled_bank_equals_the_native_bank_closely(cuda, token
     np.testing.assert_array_equal(c, b)
 
 
-# ------------------------------------------------------------------------------------------ Q4_K
+# ----------------------------------------------------------------------------------- Q4_K, Q5_K
+BLOCK_BYTES = {"Q4_K": 144, "Q5_K": 176}
+K_FORMATS = pytest.mark.parametrize("fmt", ["Q4_K", "Q5_K"])
+
+
+@K_FORMATS
 @pytest.mark.parametrize("rows,k", [(16, 256), (48, 512), (512, 2048), (32, 8192)])
-def test_q4k_retile_then_untile_restores_the_gguf_bytes(cuda, rows, k):
-    raw = np.random.default_rng(rows + k).integers(0, 256, rows * k // 256 * 144, dtype=np.uint8)
+def test_q4k_retile_then_untile_restores_the_gguf_bytes(cuda, fmt, rows, k):
+    raw = np.random.default_rng(rows + k).integers(0, 256, rows * k // 256 * BLOCK_BYTES[fmt], dtype=np.uint8)
     native = cuda.from_numpy(raw).cuda()
-    tiled = retile_bytes(native, rows, k, "Q4_K")
+    tiled = retile_bytes(native, rows, k, fmt)
     assert tiled.shape == native.shape and not cuda.equal(tiled, native)
-    assert cuda.equal(untile_bytes(tiled, rows, k, "Q4_K_TILED"), native)
+    assert cuda.equal(untile_bytes(tiled, rows, k, fmt + "_TILED"), native)
     # every byte only moved: same multiset
     assert cuda.equal(tiled.sort().values, native.sort().values)
 
 
-def test_q4k_tiled_weight_dequantizes_to_the_same_values(cuda):
-    w = random_packed("Q4_K", (64, 512), seed=3, d=0.01, dmin=0.005)
+@K_FORMATS
+def test_q4k_tiled_weight_dequantizes_to_the_same_values(cuda, fmt):
+    w = random_packed(fmt, (64, 512), seed=3, d=0.01, dmin=0.005)
     tiled = retile_weight(packed_to_device(w))
-    assert tiled.quant_type == "Q4_K_TILED"
-    got = dequantize_device(tiled.data, 64, 512, "Q4_K_TILED").cpu().numpy()
-    np.testing.assert_array_equal(got, po.dequantize(w.data, w.shape, "Q4_K"))
+    assert tiled.quant_type == fmt + "_TILED"
+    got = dequantize_device(tiled.data, 64, 512, fmt + "_TILED").cpu().numpy()
+    np.testing.assert_array_equal(got, po.dequantize(w.data, w.shape, fmt))
 
 
 @pytest.mark.parametrize("n,k", [(8192, 2048), (512, 2048), (2048, 512), (16, 256), (2048, 8192)])
 @pytest.mark.parametrize("m", [1, 5, 8, 13])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16", "float16"])
-def test_q4k_tiled_gemv_equals_the_native_direct_kernel_and_the_oracle(cuda, n, k, m, dtype):
+@K_FORMATS
+def test_q4k_tiled_gemv_equals_the_native_direct_kernel_and_the_oracle(cuda, fmt, n, k, m, dtype):
     if n * k >= 8192 * 2048 and m not in (1, 8):
         pytest.skip("large shapes: two batch sizes are enough")
     rng = np.random.default_rng(n + k + m)
-    w = quantize(rng.normal(0, 0.02, (n, k)).astype(np.float32), "Q4_K")
+    w = quantize(rng.normal(0, 0.02, (n, k)).astype(np.float32), fmt)
     dev = packed_to_device(w)
     force = k > 4096 and dtype != "float32"
     tiled = retile_weight(dev, force=force)
     if k > 4096 and not force:
         assert tiled is dev
         return
-    assert tiled.quant_type == "Q4_K_TILED"
+    assert tiled.quant_type == fmt + "_TILED"
     x = cuda.from_numpy(rng.normal(0, 1, (m, k)).astype(np.float32)).cuda().to(getattr(cuda, dtype))
     got = quantized_linear(x, tiled)
     assert cuda.equal(got, quantized_linear(x, dev))             # same arithmetic, other addresses
-    ref = po.linear_fp64(x.float().cpu().numpy(), w.data, w.shape, "Q4_K")
+    ref = po.linear_fp64(x.float().cpu().numpy(), w.data, w.shape, fmt)
     if dtype == "float32":
         np.testing.assert_allclose(got.cpu().numpy(), ref, rtol=2e-4, atol=2e-5 * np.sqrt(k / 256))
     else:
@@ -157,12 +164,13 @@ def test_q4k_tiled_k8192_with_fp32_activations_is_refused(cuda):
         quantized_linear(x, w)
 
 
+@K_FORMATS
 @pytest.mark.parametrize("m", [1, 8, 9])
-def test_q4k_tiled_swiglu_equals_the_native_kernel(cuda, m):
+def test_q4k_tiled_swiglu_equals_the_native_kernel(cuda, fmt, m):
     f, k = 512, 2048
     rng = np.random.default_rng(m)
-    gate = packed_to_device(quantize(rng.normal(0, 0.02, (f, k)).astype(np.float32), "Q4_K"))
-    up = packed_to_device(quantize(rng.normal(0, 0.02, (f, k)).astype(np.float32), "Q4_K"))
+    gate = packed_to_device(quantize(rng.normal(0, 0.02, (f, k)).astype(np.float32), fmt))
+    up = packed_to_device(quantize(rng.normal(0, 0.02, (f, k)).astype(np.float32), fmt))
     x = cuda.from_numpy(rng.normal(0, 1, (m, k)).astype(np.float32)).cuda().to(cuda.bfloat16)
     want = quantized_swiglu(x, gate, up, out_dtype=cuda.float32)
     got = quantized_swiglu(x, retile_weight(gate), retile_weight(up), out_dtype=cuda.float32)
@@ -171,12 +179,13 @@ def test_q4k_tiled_swiglu_equals_the_native_kernel(cuda, m):
         quantized_swiglu(x, retile_weight(gate), up)             # mixed layouts
 
 
+@K_FORMATS
 @pytest.mark.parametrize("tokens", [1, 7, 33])
-def test_fully_tiled_bank_matches_the_native_bank(cuda, tokens):
+def test_fully_tiled_bank_matches_the_native_bank(cuda, fmt, tokens):
     e, d, f, k = 10, 512, 256, 3
-    bank = synthetic_bank(e, d, f, ("Q4_K", "Q4_K", "Q6_K"), seed=4)
+    bank = synthetic_bank(e, d, f, (fmt, fmt, "Q6_K"), seed=4)
     tiled = bank.retiled()
-    assert (tiled.gate_type, tiled.up_type, tiled.down_type) == ("Q4_K_TILED", "Q4_K_TILED", "Q6_K_TILED")
+    assert (tiled.gate_type, tiled.up_type, tiled.down_type) == (fmt + "_TILED", fmt + "_TILED", "Q6_K_TILED")
     rng = np.random.default_rng(tokens)
     x = cuda.from_numpy(rng.normal(0, 1, (tokens, d)).astype(np.float32)).cuda().to(cuda.bfloat16)
     ids = cuda.from_numpy(np.stack([rng.choice(e, k, replace=False) for _ in range(tokens)])).cuda()
