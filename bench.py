@@ -62,6 +62,7 @@ WORKLOADS = {
     "gemv_q8_0_131072x4096_m8": ("Q8_0", 131072, 4096, 8, "bfloat16"),
     # 16 tokens: two 8-token tiles share one pass over the weights
     "gemv_q8_0_131072x4096_m16": ("Q8_0", 131072, 4096, 16, "bfloat16"),
+    "gemv_q5k_65536x4096_m1": ("Q5_K", 65536, 4096, 1, "bfloat16"),
     "gemv_q4k_65536x4096_m8": ("Q4_K", 65536, 4096, 8, "bfloat16"),
     "gemv_q4k_65536x4096_m16": ("Q4_K", 65536, 4096, 16, "bfloat16"),
     # integer-dot mode (Q8_1 activations, opt-in): the activation dtype field names the mode
