@@ -87,6 +87,14 @@ int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype,
 int b200q_gemm(const void *w, int fmt, int n, int k, const void *x, int x_dtype, int m, void *y,
                int y_dtype, void *stream);
 int b200q_gemm_supported(int fmt, int n, int k, int x_dtype, int m);
+/* The same product with room for a split of K. Shapes with few weight-row tiles (e.g. [2048 x 8192] at 512
+ * tokens: 32 CTAs) leave most SMs idle; given b200q_gemm_workspace_bytes(...) bytes of 16-byte aligned device
+ * scratch, 2-8 CTAs share the K range of a tile, store FP32 partial results there, and a second small kernel adds
+ * them in ascending order (deterministic) and rounds once. The query returns 0 when the shape is not split;
+ * without (enough) workspace the call behaves like b200q_gemm. */
+long long b200q_gemm_workspace_bytes(int fmt, int n, int k, int x_dtype, int m);
+int b200q_gemm_ws(const void *w, int fmt, int n, int k, const void *x, int x_dtype, int m, void *y, int y_dtype,
+                  void *workspace, long long workspace_bytes, void *stream);
 
 /* ---- Integer-dot mode (opt-in; changes numerics): Q8_1 activations. ------------------------------
  * b200q_quantize_q8_1: x[rows, k] (fp32 / fp16 / bf16) -> rows * k/32 blocks of 36 bytes {fp16 d, fp16 sum,

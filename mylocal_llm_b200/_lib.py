@@ -30,6 +30,8 @@ SIGNATURES = {
     "b200q_gemv_q8_1": [_ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr, _c_int, _ptr],
     "b200q_gemm": [_ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr, _c_int, _ptr],
     "b200q_gemm_supported": [_c_int, _c_int, _c_int, _c_int, _c_int],
+    "b200q_gemm_workspace_bytes": [_c_int, _c_int, _c_int, _c_int, _c_int],
+    "b200q_gemm_ws": [_ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr, _c_int, _ptr, _c_i64, _ptr],
     "b200q_swiglu": [_ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr, _c_int, _ptr],
     "b200q_expert_ffn_static": [_ptr, _c_int, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr,
                                 _c_int, _ptr],
@@ -110,7 +112,7 @@ def load():
         for name, argtypes in SIGNATURES.items():
             fn = getattr(lib, name)
             fn.argtypes = argtypes
-            fn.restype = _c_i64 if name == "b200q_moe_decode_stack_workspace" else _c_int
+            fn.restype = _c_i64 if name in ("b200q_moe_decode_stack_workspace", "b200q_gemm_workspace_bytes") else _c_int
         lib.b200q_last_error.argtypes = []
         lib.b200q_last_error.restype = ctypes.c_char_p
         _LIB = lib

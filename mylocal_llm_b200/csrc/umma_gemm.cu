@@ -57,6 +57,8 @@ struct UmmaGemmArgs {
     int mt;                   // token tiles (accumulators) per CTA: 1 or 2
     int stages;               // shared-memory stages (2..4)
     int *status;
+    int groups_per_split;     // 256-position groups of K per CTA along grid.z (split-K); k / 256 without a split
+    float *partial;           // split-K: FP32 partial results [grid.z][m][n], summed by splitk_reduce_kernel
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -365,7 +367,10 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
     const int n0 = blockIdx.x * UG_BM;
     const int ntok = a.ntok, mt_count = a.mt;
     const int m0 = blockIdx.y * (mt_count * ntok);
-    const int nslab = a.k / UG_BK;
+    // split-K: this CTA walks the groups [group0, group0 + ngroups) of K
+    const int group0 = blockIdx.z * a.groups_per_split;
+    const int ngroups = min(a.groups_per_split, a.k / 256 - group0);
+    const int nslab = ngroups * (256 / UG_BK);
     const int S = a.stages;
     const int x_bytes = ntok * UG_BK * 2;                       // one activation slab of one token tile
     const int stage_bytes = UG_W_BYTES + mt_count * x_bytes;
@@ -403,13 +408,12 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
             prow[j] = id % UG_BM;
             pquart[j] = id / UG_BM;
             const int wrow = min(n0 + prow[j], a.n - 1);      // rows past the end decode the last row; never stored
-            row_ptr[j] = a.w + static_cast<size_t>(wrow) * a.row_bytes;
+            row_ptr[j] = a.w + static_cast<size_t>(wrow) * a.row_bytes + static_cast<size_t>(group0) * fmt_group_bytes(FMT);
         }
         // Two register sets hold the packed bytes of the current and the next 256-position group (the
         // loop is unrolled by two so the sets are named statically and nothing is copied); one group
         // further ahead the lines are only asked into L2. Weights are read-only: no dependency wait.
         constexpr int GB = fmt_group_bytes(FMT);
-        const int ngroups = a.k / 256;
         DecoderRing ring{smem, free_bar, full_bar, &abort_flag, a.status, stage_bytes, S, 0, 0};
         RawGroup set0[UG_PIECES], set1[UG_PIECES];
 #pragma unroll
@@ -439,7 +443,7 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
             }
             mbar_arrive_expect_tx(&full_bar[s], mt_count * x_bytes);
             for (int mt = 0; mt < mt_count; ++mt)
-                tma_load_2d(dst + mt * x_bytes, &xmap, i * UG_BK, m0 + mt * ntok, &full_bar[s]);
+                tma_load_2d(dst + mt * x_bytes, &xmap, (group0 * (256 / UG_BK) + i) * UG_BK, m0 + mt * ntok, &full_bar[s]);
             issued = i + 1;
             dst += stage_bytes;
             if (++s == S) {
@@ -522,7 +526,11 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int t = tile_t0 + 32 * c + j;
-                        if (32 * c + j < ntok && t < a.m) store_out(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + row, r[j]);
+                        if (32 * c + j < ntok && t < a.m) {
+                            if (a.partial)
+                                a.partial[(static_cast<size_t>(blockIdx.z) * a.m + t) * a.n + row] = __uint_as_float(r[j]);
+                            else store_out(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + row, r[j]);
+                        }
                     }
                 }
             }
@@ -557,6 +565,38 @@ static EncodeTiledFn encode_tiled_fn() {
 
 using GemmFn = void (*)(const CUtensorMap, const UmmaGemmArgs);
 
+// y[t, col] = partial[0][t, col] + partial[1][t, col] + ... in ascending split order (deterministic), rounded once.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *partial, int splits, long long count, void *y,
+                                                            int y_dtype) {
+    chain_trigger();
+    chain_wait();
+    const long long i = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) * 4;
+    if (i >= count) return;                           // count is a multiple of 4 (n is)
+    float4 acc = *reinterpret_cast<const float4 *>(partial + i);
+    for (int z = 1; z < splits; ++z) {
+        const float4 v = *reinterpret_cast<const float4 *>(partial + static_cast<size_t>(z) * count + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    store_out(y, y_dtype, i, __float_as_uint(acc.x));
+    store_out(y, y_dtype, i + 1, __float_as_uint(acc.y));
+    store_out(y, y_dtype, i + 2, __float_as_uint(acc.z));
+    store_out(y, y_dtype, i + 3, __float_as_uint(acc.w));
+}
+
+// Split of K over grid.z for shapes with too few (weight-row tile x token tile) CTAs to fill the SMs: a power
+// of two, at least 8 groups (32 slabs) of K per CTA, no more CTAs than SMs; 1 = no split.
+static int gemm_splits(int n, int k, int m) {
+    if (n % 4 != 0) return 1;
+    const int ntok = m >= 256 ? 256 : (m + 15) / 16 * 16;
+    const int token_tiles = (m + ntok - 1) / ntok;
+    const int n_tiles = (n + UG_BM - 1) / UG_BM;
+    const int mt = (token_tiles >= 2 && static_cast<long long>(n_tiles) * ((token_tiles + 1) / 2) >= sm_count()) ? 2 : 1;
+    const long long ctas = static_cast<long long>(n_tiles) * ((token_tiles + mt - 1) / mt);
+    int splits = 1;
+    while (splits < 8 && ctas * splits * 2 <= sm_count() && (k / 256) / (splits * 2) >= 8) splits *= 2;
+    return splits;
+}
+
 }  // namespace b200q
 
 using namespace b200q;
@@ -567,8 +607,14 @@ extern "C" int b200q_gemm_supported(int fmt, int n, int k, int x_dtype, int m) {
     return 1;
 }
 
-extern "C" int b200q_gemm(const void *w, int fmt, int n, int k, const void *x, int x_dtype, int m, void *y,
-                          int y_dtype, void *stream) {
+extern "C" long long b200q_gemm_workspace_bytes(int fmt, int n, int k, int x_dtype, int m) {
+    if (!b200q_gemm_supported(fmt, n, k, x_dtype, m)) return 0;
+    const int splits = gemm_splits(n, k, m);
+    return splits > 1 ? static_cast<long long>(splits) * m * n * 4 : 0;
+}
+
+static int gemm_impl(const void *w, int fmt, int n, int k, const void *x, int x_dtype, int m, void *y, int y_dtype,
+                     void *workspace, long long workspace_bytes, void *stream) {
     if (!w || !x || !y) return fail(B200Q_EINVAL, "gemm: NULL pointer");
     if (!fmt_valid(fmt)) return fail(B200Q_EINVAL, "gemm: unknown or device-only format %d", fmt);
     if (!dtype_valid(x_dtype) || !dtype_valid(y_dtype)) return fail(B200Q_EINVAL, "gemm: bad dtype");
@@ -609,6 +655,12 @@ extern "C" int b200q_gemm(const void *w, int fmt, int n, int k, const void *x, i
     a.n = n; a.k = k; a.m = m;
     a.row_bytes = static_cast<long long>(k / fmt_elems(fmt)) * fmt_bytes(fmt);
     a.y = y; a.y_dtype = y_dtype; a.ntok = ntok; a.mt = mt; a.stages = stages; a.status = status;
+    int splits = gemm_splits(n, k, m);
+    if (!workspace || workspace_bytes < static_cast<long long>(splits) * m * n * 4 ||
+        (reinterpret_cast<uintptr_t>(workspace) & 15))
+        splits = 1;                                    // no room for partial results: one CTA walks all of K
+    a.groups_per_split = (k / 256 + splits - 1) / splits;
+    a.partial = splits > 1 ? static_cast<float *>(workspace) : nullptr;
     GemmFn fn = fmt == B200Q_Q8_0 ? umma_gemm_kernel<B200Q_Q8_0>
               : fmt == B200Q_Q4_K ? umma_gemm_kernel<B200Q_Q4_K>
               : fmt == B200Q_Q5_K ? umma_gemm_kernel<B200Q_Q5_K>
@@ -632,6 +684,21 @@ extern "C" int b200q_gemm(const void *w, int fmt, int n, int k, const void *x, i
             opted.push_back(key);
         }
     }
-    launch_chained(fn, dim3(n_tiles, m_tiles), dim3(UG_THREADS), smem, static_cast<cudaStream_t>(stream), xmap, a);
-    return check_launch("gemm");
+    launch_chained(fn, dim3(n_tiles, m_tiles, splits), dim3(UG_THREADS), smem, static_cast<cudaStream_t>(stream), xmap, a);
+    int rc = check_launch("gemm");
+    if (rc || splits == 1) return rc;
+    const long long count = static_cast<long long>(m) * n;
+    launch_chained(splitk_reduce_kernel, dim3(static_cast<unsigned>((count / 4 + 255) / 256)), dim3(256), 0,
+                   static_cast<cudaStream_t>(stream), static_cast<const float *>(workspace), splits, count, y, y_dtype);
+    return check_launch("gemm (split-K sum)");
+}
+
+extern "C" int b200q_gemm(const void *w, int fmt, int n, int k, const void *x, int x_dtype, int m, void *y,
+                          int y_dtype, void *stream) {
+    return gemm_impl(w, fmt, n, k, x, x_dtype, m, y, y_dtype, nullptr, 0, stream);
+}
+
+extern "C" int b200q_gemm_ws(const void *w, int fmt, int n, int k, const void *x, int x_dtype, int m, void *y,
+                             int y_dtype, void *workspace, long long workspace_bytes, void *stream) {
+    return gemm_impl(w, fmt, n, k, x, x_dtype, m, y, y_dtype, workspace, workspace_bytes, stream);
 }

@@ -19,6 +19,8 @@ from dataclasses import dataclass
 import ctypes
 import math
 
+import os
+
 import numpy as np
 
 from . import _lib
@@ -228,9 +230,19 @@ def quantized_linear(x, weight, *, block_k=512, cpu_packed_backend="reference", 
     n, k = weight.shape
     m = int(x.numel()) // k
     out = torch.empty((m, n), dtype=out_dtype or x.dtype, device=x.device)
-    if m:
-        entry = "b200q_gemm" if _use_gemm(weight, x, m, n, k, dt) else "b200q_gemv"
-        _lib.call(entry, _ptr(weight.data), _lib.FORMAT_ID[weight.quant_type], n, k, _ptr(x), dt, m,
+    if m and _use_gemm(weight, x, m, n, k, dt):
+        fmt = _lib.FORMAT_ID[weight.quant_type]
+        # shapes with few weight-row tiles split K over several CTAs, given scratch for the partial results
+        nbytes = int(_lib.load().b200q_gemm_workspace_bytes(fmt, n, k, dt, m))
+        if nbytes and os.environ.get("B200Q_GEMM_SPLITK", "1") != "0":
+            scratch = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+            _lib.call("b200q_gemm_ws", _ptr(weight.data), fmt, n, k, _ptr(x), dt, m, _ptr(out), _dtype_id(out),
+                      _ptr(scratch), nbytes, _lib.current_stream())
+        else:
+            _lib.call("b200q_gemm", _ptr(weight.data), fmt, n, k, _ptr(x), dt, m, _ptr(out), _dtype_id(out),
+                      _lib.current_stream())
+    elif m:
+        _lib.call("b200q_gemv", _ptr(weight.data), _lib.FORMAT_ID[weight.quant_type], n, k, _ptr(x), dt, m,
                   _ptr(out), _dtype_id(out), _lib.current_stream())
     return out.reshape(tuple(x.shape[:-1]) + (n,))
 

@@ -31,25 +31,33 @@ def bf16_round(torch, a):
     return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(torch.bfloat16).double().numpy()
 
 
-def run_gemm(torch, w, x_bf16, out_dtype):
+def run_gemm(torch, w, x_bf16, out_dtype, split=False):
     n, k = w.shape
     m = x_bf16.shape[0]
     dev = packed_to_device(w)
     y = torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda")
     ptr = lambda t: ctypes.c_void_p(t.data_ptr())
-    _lib.call("b200q_gemm", ptr(dev.data), _lib.FORMAT_ID[w.quant_type], n, k, ptr(x_bf16), _lib.DTYPE_ID["bfloat16"], m,
-              ptr(y), _lib.DTYPE_ID[str(out_dtype).replace("torch.", "")], _lib.current_stream())
+    fmt, bf16 = _lib.FORMAT_ID[w.quant_type], _lib.DTYPE_ID["bfloat16"]
+    if split:
+        nbytes = int(_lib.load().b200q_gemm_workspace_bytes(fmt, n, k, bf16, m))
+        assert nbytes > 0 and nbytes % (m * n * 4) == 0, "this shape was expected to split K"
+        scratch = torch.full((nbytes // 4,), float("nan"), dtype=torch.float32, device="cuda")
+        _lib.call("b200q_gemm_ws", ptr(dev.data), fmt, n, k, ptr(x_bf16), bf16, m, ptr(y),
+                  _lib.DTYPE_ID[str(out_dtype).replace("torch.", "")], ptr(scratch), nbytes, _lib.current_stream())
+    else:
+        _lib.call("b200q_gemm", ptr(dev.data), fmt, n, k, ptr(x_bf16), bf16, m,
+                  ptr(y), _lib.DTYPE_ID[str(out_dtype).replace("torch.", "")], _lib.current_stream())
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
     return y
 
 
-def check(torch, w, m, seed, out_dtype=None):
+def check(torch, w, m, seed, out_dtype=None, split=False):
     out_dtype = out_dtype or torch.float32
     n, k = w.shape
     x = np.random.default_rng(seed).normal(0, 1, (m, k)).astype(np.float32)
     xd = torch.from_numpy(x).cuda().to(torch.bfloat16)
-    y = run_gemm(torch, w, xd, out_dtype).double().cpu().numpy()
+    y = run_gemm(torch, w, xd, out_dtype, split).double().cpu().numpy()
     assert np.isfinite(y).all(), "some outputs were never written"
     dense = bo.port_dequantize(w.data, w.shape, w.quant_type)
     x64 = xd.double().cpu().numpy()
@@ -121,3 +129,32 @@ def test_gemm_rejects_what_it_does_not_cover(cuda):
     assert _lib.load().b200q_gemm_supported(2, 64, 256, 2, 32) == 1
     assert _lib.load().b200q_gemm_supported(2, 64, 256, 0, 32) == 0
     assert _lib.load().b200q_gemm_supported(0, 64, 96, 2, 32) == 0
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("n,k,m,out", [(256, 8192, 64, "float32"), (128, 4096, 300, "bfloat16"), (2048, 8192, 512, "bfloat16"),
+                                       (200, 4352, 33, "float32")])
+def test_gemm_split_k_sums_partial_tiles_in_order(cuda, fmt, n, k, m, out):
+    # few weight-row tiles: K is split over 2-8 CTAs, FP32 partial tiles added in ascending order by a second kernel;
+    # same bars as the one-CTA-per-tile product, rows and tokens off the tile grid included
+    if fmt != "Q4_K" and n * k >= 2048 * 8192:
+        pytest.skip("the large shape once")
+    w = random_packed(fmt, (n, k), seed=n + m, d=0.01, dmin=0.005) if n * k >= 2048 * 8192 else quantize(
+        np.random.default_rng(n + k).normal(0, 0.02, (n, k)).astype(np.float32), fmt)
+    check(cuda, w, m, seed=m, out_dtype=getattr(cuda, out), split=True)
+
+
+def test_gemm_split_k_is_used_by_the_linear_and_can_be_turned_off(cuda, monkeypatch):
+    torch = cuda
+    w = packed_to_device(quantize(np.random.default_rng(1).normal(0, 0.02, (256, 8192)).astype(np.float32), "Q4_K"))
+    x = torch.randn((64, 8192), device="cuda").to(torch.bfloat16)
+    calls = []
+    real = _lib.call
+    monkeypatch.setattr(_lib, "call", lambda name, *a: (calls.append(name), real(name, *a))[1])
+    split = quantized_linear(x, w, out_dtype=torch.float32)
+    monkeypatch.setenv("B200Q_GEMM_SPLITK", "0")
+    whole = quantized_linear(x, w, out_dtype=torch.float32)
+    assert calls == ["b200q_gemm_ws", "b200q_gemm"]
+    # the same products added in another order
+    torch.testing.assert_close(split, whole, rtol=2e-5, atol=2e-5 * float(whole.abs().max()))
+    assert _lib.load().b200q_gemm_workspace_bytes(2, 8192, 2048, 2, 512) == 0          # enough tiles: no split

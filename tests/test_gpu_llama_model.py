@@ -162,7 +162,8 @@ def test_one_layer_of_the_third_configuration_prefill_gemm_and_decode(cuda, monk
     monkeypatch.setattr(_lib, "call", lambda name, *a: (calls.append(name), real(name, *a))[1])
     state = model.create_generation_state(1, 64)
     logits = model.prefill(torch.from_numpy(tokens[:48][None]).cuda(), state)
-    assert calls.count("b200q_gemm") == 4, calls          # qkv, o, gate|up, down of the one layer
+    # qkv, o, gate|up, down of the one layer (a projection with few row tiles takes the split-K entry point)
+    assert calls.count("b200q_gemm") + calls.count("b200q_gemm_ws") == 4, calls
     np.testing.assert_allclose(logits[0].cpu().numpy(), ref[47], rtol=6e-2, atol=6e-2 * scale)
     for step in (48, 49):
         logits = model.decode_one(torch.from_numpy(tokens[step:step + 1]).cuda(), state)
