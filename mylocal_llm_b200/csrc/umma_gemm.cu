@@ -353,7 +353,7 @@ constexpr int UG_DECODE_THREADS = 512;
 constexpr int UG_THREADS = UG_DECODE_THREADS + 64;
 constexpr int UG_PIECES = UG_BM * 4 / UG_DECODE_THREADS;      // 16-weight pieces per decoder thread and slab
 
-template <int FMT>
+template <int FMT, bool SPLIT>
 __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_constant__ CUtensorMap xmap,
                                                                   const UmmaGemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
@@ -368,8 +368,10 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
     const int ntok = a.ntok, mt_count = a.mt;
     const int m0 = blockIdx.y * (mt_count * ntok);
     // split-K: this CTA walks the groups [group0, group0 + ngroups) of K
-    const int group0 = blockIdx.z * a.groups_per_split;
-    const int ngroups = min(a.groups_per_split, a.k / 256 - group0);
+    // (SPLIT is a template argument: the one-CTA-per-tile kernel keeps the code it had before the split existed;
+    // the same source with a run-time test measured 9 % slower at [8192 x 2048] x 512)
+    const int group0 = SPLIT ? blockIdx.z * a.groups_per_split : 0;
+    const int ngroups = SPLIT ? min(a.groups_per_split, a.k / 256 - group0) : a.k / 256;
     const int nslab = ngroups * (256 / UG_BK);
     const int S = a.stages;
     const int x_bytes = ntok * UG_BK * 2;                       // one activation slab of one token tile
@@ -434,7 +436,7 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
         chain_wait();                 // the activations come from the preceding kernel on the stream
         // (stage index and barrier phase are kept as running counters: this lane's loop is a chain of
         // dependent instructions, and a runtime division per slab would cost more than the copies' issue)
-        int issued = 0, s = 0, wraps = 0;
+        int issued = 0, s = 0, wraps = 0, xcol = group0 * 256;
         uint8_t *dst = smem + UG_W_BYTES;
         for (int i = 0; i < nslab && !abort_flag; ++i) {
             if (wraps > 0 && !mbar_wait_bounded(&free_bar[s], (wraps - 1) & 1, a.status, STATUS_UMMA_WAIT_MMA)) {
@@ -443,8 +445,9 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
             }
             mbar_arrive_expect_tx(&full_bar[s], mt_count * x_bytes);
             for (int mt = 0; mt < mt_count; ++mt)
-                tma_load_2d(dst + mt * x_bytes, &xmap, (group0 * (256 / UG_BK) + i) * UG_BK, m0 + mt * ntok, &full_bar[s]);
+                tma_load_2d(dst + mt * x_bytes, &xmap, xcol, m0 + mt * ntok, &full_bar[s]);
             issued = i + 1;
+            xcol += UG_BK;
             dst += stage_bytes;
             if (++s == S) {
                 s = 0;
@@ -527,7 +530,7 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
                     for (int j = 0; j < 32; ++j) {
                         const int t = tile_t0 + 32 * c + j;
                         if (32 * c + j < ntok && t < a.m) {
-                            if (a.partial)
+                            if (SPLIT)
                                 a.partial[(static_cast<size_t>(blockIdx.z) * a.m + t) * a.n + row] = __uint_as_float(r[j]);
                             else store_out(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + row, r[j]);
                         }
@@ -584,7 +587,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *partial
 }
 
 // Split of K over grid.z for shapes with too few (weight-row tile x token tile) CTAs to fill the SMs: a power
-// of two, at least 8 groups (32 slabs) of K per CTA, no more CTAs than SMs; 1 = no split.
+// of two, at least 4 groups (16 slabs) of K per CTA, no more CTAs than SMs; 1 = no split.
 static int gemm_splits(int n, int k, int m) {
     if (n % 4 != 0) return 1;
     const int ntok = m >= 256 ? 256 : (m + 15) / 16 * 16;
@@ -593,7 +596,7 @@ static int gemm_splits(int n, int k, int m) {
     const int mt = (token_tiles >= 2 && static_cast<long long>(n_tiles) * ((token_tiles + 1) / 2) >= sm_count()) ? 2 : 1;
     const long long ctas = static_cast<long long>(n_tiles) * ((token_tiles + mt - 1) / mt);
     int splits = 1;
-    while (splits < 8 && ctas * splits * 2 <= sm_count() && (k / 256) / (splits * 2) >= 8) splits *= 2;
+    while (splits < 8 && ctas * splits * 2 <= sm_count() && (k / 256) / (splits * 2) >= 4) splits *= 2;
     return splits;
 }
 
@@ -661,10 +664,13 @@ static int gemm_impl(const void *w, int fmt, int n, int k, const void *x, int x_
         splits = 1;                                    // no room for partial results: one CTA walks all of K
     a.groups_per_split = (k / 256 + splits - 1) / splits;
     a.partial = splits > 1 ? static_cast<float *>(workspace) : nullptr;
-    GemmFn fn = fmt == B200Q_Q8_0 ? umma_gemm_kernel<B200Q_Q8_0>
-              : fmt == B200Q_Q4_K ? umma_gemm_kernel<B200Q_Q4_K>
-              : fmt == B200Q_Q5_K ? umma_gemm_kernel<B200Q_Q5_K>
-                                  : umma_gemm_kernel<B200Q_Q6_K>;
+    GemmFn fn;
+    if (splits > 1)
+        fn = fmt == B200Q_Q8_0 ? umma_gemm_kernel<B200Q_Q8_0, true> : fmt == B200Q_Q4_K ? umma_gemm_kernel<B200Q_Q4_K, true>
+           : fmt == B200Q_Q5_K ? umma_gemm_kernel<B200Q_Q5_K, true> : umma_gemm_kernel<B200Q_Q6_K, true>;
+    else
+        fn = fmt == B200Q_Q8_0 ? umma_gemm_kernel<B200Q_Q8_0, false> : fmt == B200Q_Q4_K ? umma_gemm_kernel<B200Q_Q4_K, false>
+           : fmt == B200Q_Q5_K ? umma_gemm_kernel<B200Q_Q5_K, false> : umma_gemm_kernel<B200Q_Q6_K, false>;
     const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024;
     // the opt-in to large dynamic shared memory is per function and device: done once each
     {
