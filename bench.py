@@ -676,6 +676,11 @@ def batch1_side_numbers(torch, stream, stack):
                            "step_bytes": step_bytes, "frac_of_peak": round(step_bytes / (ms * 1e-3) / 1e9 / peak, 4),
                            "step": "one persistent kernel" if getattr(stack, "persistent_step", False) else "chain of launches"}
     if getattr(stack, "persistent_step", False):
+        os.environ["B200Q_STAGE_TIMES"] = "1"           # one more step with the kernel's stage stamps switched on
+        stack.forward(x1)
+        stream.synchronize()
+        del os.environ["B200Q_STAGE_TIMES"]
+        out["moe_stack_b1"]["last_layer_stage_us"] = stack.stage_times()
         stack.persistent_step = False
         ms_chain, graph, _ = graph_time(torch, stream, lambda: stack.forward(x1)[0], replays=30)
         graph.reset()

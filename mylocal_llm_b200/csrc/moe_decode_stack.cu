@@ -24,6 +24,7 @@
 #include "norm_device.cuh"
 #include "mma_host.h"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace b200q {
@@ -55,6 +56,7 @@ struct DecodeStackArgs {
     void *hidden_out;
     float *logits, *hbuf, *terms;              // [e], [(k+1) f], [(k+1) d]
     unsigned int *sync;                        // [0] arrivals, [1] generation, [2] abort
+    unsigned long long *stamps;                // optional: nine %globaltimer readings of the last layer (CTA 1)
     int *status;
     int max_segments;
     int off_state;                             // byte offset of the per-CTA state in dynamic shared memory
@@ -281,11 +283,17 @@ __global__ void __launch_bounds__(DS_THREADS, 1) moe_decode_stack_kernel(const D
     bool ok = true;
     for (int layer = 0; layer < p.n_layers && ok; ++layer) {
         const DecodeStackLayer lay = p.layers[layer];
+        // diagnostic (B200Q_STAGE_TIMES=1): when the stages of the last layer ended on CTA 1 (which has a block in
+        // both grouped stages of a one-row plan), in nanoseconds
+        unsigned long long *stamp = (p.stamps && block == min(1, nblocks - 1) && tid == 0 && layer == p.n_layers - 1) ? p.stamps : nullptr;
+        if (stamp) stamp[0] = global_timer_ns();
         // A: router logits; a warp per expert row, the arithmetic of router_logits_t_kernel for one token
         for (int c = tid; c < d; c += DS_THREADS) xs[c] = load_as_float(x_act, p.act_dtype, c);
         __syncthreads();
         stage_router(block * (DS_THREADS / 32) + warp, nblocks * (DS_THREADS / 32), lane, e, d, lay.router_wt, xs, p.logits);
+        if (stamp) stamp[1] = global_timer_ns();
         if (!(ok = grid_barrier(p.sync, generation, nblocks, p.status, &abort_flag))) break;
+        if (stamp) stamp[2] = global_timer_ns();
 
         // B: top-k and the one-row plan, in every CTA
         // (every thread fetches a logit or two into shared memory: one round trip instead of the lane's sixteen)
@@ -324,17 +332,23 @@ __global__ void __launch_bounds__(DS_THREADS, 1) moe_decode_stack_kernel(const D
             }
         }
 
+        if (stamp) stamp[3] = global_timer_ns();
         // C: grouped gate/up + SwiGLU -> hbuf
         mma_direct_body<false, 2, 1, 1>(p.gu, gu_ptrs, smem, block, nblocks);
+        if (stamp) stamp[4] = global_timer_ns();
         if (!(ok = grid_barrier(p.sync, generation, nblocks, p.status, &abort_flag))) break;
+        if (stamp) stamp[5] = global_timer_ns();
 
         // D: grouped down, route-weighted -> terms
         tiled_body<Q6Tile, 3, 2, 1>(p.dn, dn_ptrs, smem, block, nblocks);
+        if (stamp) stamp[6] = global_timer_ns();
         if (!(ok = grid_barrier(p.sync, generation, nblocks, p.status, &abort_flag))) break;
+        if (stamp) stamp[7] = global_timer_ns();
 
         // E: ordered combine + residual add + norm of the next layer, in every CTA
         stage_combine_norm(tid, p.terms, inv, k_out, d, p.act_dtype, resid, lay.gamma_next, p.eps, x_act);
         __syncthreads();
+        if (stamp) stamp[8] = global_timer_ns();
     }
     if (ok && block == 0) {
         const int esize = p.act_dtype == B200Q_F32 ? 4 : 2;
@@ -415,6 +429,10 @@ extern "C" int b200q_moe_decode_stack(const void *layers, int n_layers, int d, i
     a.terms = reinterpret_cast<float *>(ws);
     ws += align_up(static_cast<size_t>(k_out) * d * 4, 256);
     a.sync = reinterpret_cast<unsigned int *>(ws);
+    {
+        const char *v = std::getenv("B200Q_STAGE_TIMES");
+        a.stamps = (v && v[0] == '1') ? reinterpret_cast<unsigned long long *>(ws + 64) : nullptr;      // behind the barrier words
+    }
     a.status = status;
     a.max_segments = max_segments;
     a.off_state = static_cast<int>(off_state);

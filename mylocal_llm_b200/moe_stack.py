@@ -105,6 +105,19 @@ class PackedMoEStack:
             return None
         return res, hidden
 
+    def stage_times(self):
+        """Microseconds the stages of the last layer took in the latest persistent step (router, barrier, top-k +
+        plan, gate/up, barrier, down, barrier, combine + norm), as seen by one CTA; needs ``B200Q_STAGE_TIMES=1``
+        in the environment of that step. ``None`` when no such step ran."""
+        if not self._persistent:
+            return None
+        workspace = self._persistent[1]
+        raw = workspace[workspace.numel() - 192: workspace.numel() - 192 + 72].cpu().numpy().view("int64")
+        if raw[0] == 0 or raw[8] < raw[0]:
+            return None
+        names = ("router", "barrier_1", "topk_plan", "gate_up", "barrier_2", "down", "barrier_3", "combine_norm")
+        return {n: round(float(raw[i + 1] - raw[i]) / 1e3, 2) for i, n in enumerate(names)}
+
     def forward(self, residual, trace=None):
         """residual FP32 [B, T, D] -> (new residual FP32, final normalised activations). ``trace``: a list
         that receives, per layer, ``(layer input, layer output)`` - the tensors a layer-by-layer check
