@@ -70,6 +70,8 @@ struct StagePointers {
     const unsigned long long *table_a, *table_b;
     const int32_t *order, *seg_expert, *seg_begin, *seg_count, *num_segments;
     const float *route;
+    int prepared_row;      // grouped gate/up: the row of x whose fragments the caller has already prepared in the
+                           // CTA's buffers (-1: none); a first segment of just that row then needs no preparation
 };
 
 __device__ __forceinline__ uint4 ldg128(const uint8_t *p) {
@@ -230,7 +232,9 @@ __device__ __forceinline__ void load4(const void *x, int x_dtype, size_t e, bool
 // loaded again). Entries of tokens >= m_tokens are left as they are: a column of B only feeds the
 // same column of the product, and those columns are never stored.
 
-template <int NTERMS, int KEEP, typename RowFn>
+// (THREADS consecutive threads tid = 0..THREADS-1 take part and meet at named barrier BARRIER; the result does
+// not depend on THREADS, which must be a multiple of 32.)
+template <int NTERMS, int KEEP, int THREADS = MD_THREADS, int BARRIER = 1, typename RowFn>
 __device__ __forceinline__ void prepare_direct(RowFn row_of, int m_tokens, int k, const void *x, int x_dtype,
                                                uint2 *bfrag, uint32_t *xsfrag, float *tok_scale, int tid) {
     const int lane = tid & 31;
@@ -240,7 +244,7 @@ __device__ __forceinline__ void prepare_direct(RowFn row_of, int m_tokens, int k
     const bool vec_ok = (reinterpret_cast<uintptr_t>(x) % (4 * esize)) == 0;   // rows are multiples of 256 elements
     unsigned int *amax_bits = reinterpret_cast<unsigned int *>(tok_scale + 16);   // [8], non-negative floats as ints
     if (tid < 8) amax_bits[tid] = 0u;
-    named_barrier_sync(1, MD_THREADS);
+    named_barrier_sync(BARRIER, THREADS);
     const int chunks_per_token = k >> 2;            // a multiple of 64: a warp's 32 chunks share one token
     const int total = m_tokens * chunks_per_token;
     float kept[KEEP][4];
@@ -258,12 +262,12 @@ __device__ __forceinline__ void prepare_direct(RowFn row_of, int m_tokens, int k
     };
 #pragma unroll
     for (int sl = 0; sl < KEEP; ++sl)
-        if (first + sl * MD_THREADS < total) load_chunk(first + sl * MD_THREADS, kept[sl]);
-    for (int c0 = first + KEEP * MD_THREADS; c0 < total; c0 += MD_THREADS) {
+        if (first + sl * THREADS < total) load_chunk(first + sl * THREADS, kept[sl]);
+    for (int c0 = first + KEEP * THREADS; c0 < total; c0 += THREADS) {
         float v[4];
         load_chunk(c0, v);
     }
-    named_barrier_sync(1, MD_THREADS);
+    named_barrier_sync(BARRIER, THREADS);
     if (tid < 8) {
         const float amax = __uint_as_float(amax_bits[tid]);
         float s = 1.0f;
@@ -275,7 +279,7 @@ __device__ __forceinline__ void prepare_direct(RowFn row_of, int m_tokens, int k
         tok_scale[tid] = s;
         tok_scale[8 + tid] = 1.0f / s;
     }
-    named_barrier_sync(1, MD_THREADS);
+    named_barrier_sync(BARRIER, THREADS);
     // 2. scale, split, store: the chunk at position p of token t is fragment entry (f, lane 4t+tig) with
     //    sb = p>>8, sub = (p>>5)&7, X = sub>>2, nib = sub&1, tig = 2*((sub>>1)&1) + ((p>>4)&1), j = (p>>2)&3
     auto store_chunk = [&](int c0, const float (&v)[4]) {
@@ -323,15 +327,15 @@ __device__ __forceinline__ void prepare_direct(RowFn row_of, int m_tokens, int k
     };
 #pragma unroll
     for (int sl = 0; sl < KEEP; ++sl)
-        if (first + sl * MD_THREADS < total) store_chunk(first + sl * MD_THREADS, kept[sl]);
-    for (int c0 = first + KEEP * MD_THREADS; c0 < total; c0 += MD_THREADS) {
+        if (first + sl * THREADS < total) store_chunk(first + sl * THREADS, kept[sl]);
+    for (int c0 = first + KEEP * THREADS; c0 < total; c0 += THREADS) {
         const int t = c0 / chunks_per_token;
         float v[4];
         load4(x, x_dtype, static_cast<size_t>(row_of(t)) * k + static_cast<size_t>(c0 + lane - t * chunks_per_token) * 4,
               vec_ok, v);
         store_chunk(c0, v);
     }
-    named_barrier_sync(1, MD_THREADS);
+    named_barrier_sync(BARRIER, THREADS);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -574,7 +578,7 @@ __device__ __forceinline__ void mma_direct_body(const DirectArgs &a, const Stage
     if (items_per_block > 0) issue_item(cur_p, 0, nxt_a, nxt_b);
 
     int m_tokens = a.m;
-    int seg_begin = 0, cur_unit = -1, last_single = -1;
+    int seg_begin = 0, cur_unit = -1, last_single = (MODE == 2) ? gp.prepared_row : -1;
     if (!GROUPED) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
@@ -691,7 +695,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mma_direct_kernel(const DirectA
     chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
     if (MODE >= 2) chain_wait();      // the segment list comes from the plan kernel
     extern __shared__ __align__(128) uint8_t smem[];
-    const StagePointers gp{a.x, a.y, a.table_a, a.table_b, a.order, a.seg_expert, a.seg_begin, a.seg_count, a.num_segments, a.route};
+    const StagePointers gp{a.x, a.y, a.table_a, a.table_b, a.order, a.seg_expert, a.seg_begin, a.seg_count, a.num_segments, a.route, -1};
     mma_direct_body<Q5, MODE, NTERMS, NT>(a, gp, smem, blockIdx.x, gridDim.x);
 }
 

@@ -273,8 +273,8 @@ __global__ void __launch_bounds__(DS_THREADS, 1) moe_decode_stack_kernel(const D
     __syncthreads();
 
     if (tid == 0) {
-        gu_ptrs = StagePointers{x_act, p.hbuf, gate_ptrs, up_ptrs, order, seg_ident, seg_begin, seg_count, num_segments, nullptr};
-        dn_ptrs = StagePointers{p.hbuf, p.terms, down_ptrs, nullptr, order, seg_ident, seg_begin, seg_count, num_segments, weights};
+        gu_ptrs = StagePointers{x_act, p.hbuf, gate_ptrs, up_ptrs, order, seg_ident, seg_begin, seg_count, num_segments, nullptr, 0};
+        dn_ptrs = StagePointers{p.hbuf, p.terms, down_ptrs, nullptr, order, seg_ident, seg_begin, seg_count, num_segments, weights, -1};
     }
     if (tid < DS_PLAN_SLOTS) seg_ident[tid] = tid;
     __syncthreads();
@@ -309,29 +309,17 @@ __global__ void __launch_bounds__(DS_THREADS, 1) moe_decode_stack_kernel(const D
                 up_ptrs[u] = lay.up_table[ex];
                 down_ptrs[u] = lay.down_table[ex];
             }
-        } else if (layer + 1 < p.n_layers) {
-            // meanwhile: ask L2 for the router rows this CTA's warps take in the next layer
-            const float *next_wt = p.layers[layer + 1].router_wt;
-            for (int row = block * (DS_THREADS / 32) + warp; row < e; row += nblocks * (DS_THREADS / 32))
-                for (int off = lane * 32; off < d; off += 32 * 32)
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(next_wt + static_cast<size_t>(row) * d + off));
+        } else {
+            // meanwhile the other fifteen warps turn the row into the gate/up stage's activation fragments (the
+            // stage's own preparation, run by 480 threads; the stage finds its single row prepared and skips it)
+            prepare_direct<1, 2, DS_THREADS - 32, 13>([](int) { return 0; }, 1, d, x_act, p.act_dtype,
+                                                      reinterpret_cast<uint2 *>(smem + p.gu.off_bfrag),
+                                                      reinterpret_cast<uint32_t *>(smem + p.gu.off_xsfrag),
+                                                      reinterpret_cast<float *>(smem), tid - 32);
         }
         __syncthreads();
-        {
-            // ask L2 for the down-projection tiles of this CTA's blocks of stage D (the split tiled_body makes)
-            const int nseg = min(num_segments[0], p.max_segments);
-            const int groups_total = d >> 4, nsb_d = p.f >> 8;
-            const int bpu = (groups_total + p.dn.rg - 1) / p.dn.rg;
-            const long long total = static_cast<long long>(nseg) * bpu;
-            for (long long blk = total * block / nblocks; blk < total * (block + 1) / nblocks; ++blk) {
-                const int unit = static_cast<int>(blk / bpu), group0 = static_cast<int>(blk - static_cast<long long>(unit) * bpu) * p.dn.rg;
-                const int groups = min(p.dn.rg, groups_total - group0);
-                const uint8_t *base = reinterpret_cast<const uint8_t *>(static_cast<uintptr_t>(down_ptrs[unit])) +
-                                      static_cast<size_t>(group0) * nsb_d * Q6T_TILE_BYTES;
-                prefetch_l2_range(base, static_cast<size_t>(groups) * nsb_d * Q6T_TILE_BYTES, 1u << 20, tid, DS_THREADS);
-            }
-        }
-
+        // (L2 prefetches issued here - the next layer's router rows, this CTA's down tiles - cost this stage more
+        // than they saved the later ones: 1.1 us against 0.4 us, measured with the stage stamps)
         if (stamp) stamp[3] = global_timer_ns();
         // C: grouped gate/up + SwiGLU -> hbuf
         mma_direct_body<false, 2, 1, 1>(p.gu, gu_ptrs, smem, block, nblocks);

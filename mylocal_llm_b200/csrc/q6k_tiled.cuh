@@ -513,7 +513,7 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs
     chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
     if (MODE == 3) chain_wait();      // the segment list comes from the plan kernel
     extern __shared__ __align__(128) uint8_t smem[];
-    const StagePointers gp{a.x, a.y, a.table, nullptr, a.order, a.seg_expert, a.seg_begin, a.seg_count, a.num_segments, a.route};
+    const StagePointers gp{a.x, a.y, a.table, nullptr, a.order, a.seg_expert, a.seg_begin, a.seg_count, a.num_segments, a.route, -1};
     tiled_body<TILE, MODE, NTERMS, NT>(a, gp, smem, blockIdx.x, gridDim.x);
 }
 
