@@ -443,6 +443,16 @@ extern "C" int b200q_moe_decode_stack(const void *layers, int n_layers, int d, i
             opted[dev] = smem;
         }
     }
+    {
+        // the whole grid has to be resident at once: one CTA per SM must fit
+        int per_sm = 0;
+        cudaError_t err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, moe_decode_stack_kernel, DS_THREADS,
+                                                                        static_cast<size_t>(smem));
+        if (err != cudaSuccess || per_sm < 1) {
+            cudaGetLastError();
+            return fail(B200Q_EUNSUPPORTED, "moe_decode_stack: a CTA of this step does not fit an SM of this device");
+        }
+    }
     cudaError_t err = cudaMemsetAsync(a.sync, 0, 16, st);
     if (err != cudaSuccess) {
         cudaGetLastError();
