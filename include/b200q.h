@@ -76,6 +76,18 @@ int b200q_dequantize(const void *w, int fmt, int64_t n, int k, float *out, void 
 int b200q_gemv(const void *w, int fmt, int n, int k, const void *x, int x_dtype, int m, void *y,
                int y_dtype, void *stream);
 
+/* b200q_residual_rmsnorm followed by b200q_gemv as ONE launch, for one-token decoder steps, where the norm of a
+ * row of a few KB is a launch of its own: every CTA of the GEMV normalises the m <= 4 rows itself (residual +
+ * alpha * branch, RMSNorm with `gamma`, rounded to act_dtype - the arithmetic of b200q_residual_rmsnorm), keeps
+ * them in shared memory and multiplies; res_out receives the new FP32 residual stream. Same bits as the two calls.
+ * Tile-layout Q6_K / Q8_0 weights, BF16 / FP16 activations (= the type of gamma); b200q_gemv_norm_supported answers
+ * without a launch. Replaces RMSNormInference.forward_residual_add + quantized_linear of the reference's decoder
+ * block (mini_llm/ops/rmsnorm_inference.py:228-252, mini_llm/ops/quantized_linear.py:174-192). */
+int b200q_gemv_norm_supported(int fmt, int n, int k, int act_dtype, int m);
+int b200q_gemv_norm(const void *w, int fmt, int n, int k, const float *residual, const void *branch,
+                    int branch_dtype, float alpha, const void *gamma, int act_dtype, float eps, int m,
+                    float *res_out, void *y, int y_dtype, void *stream);
+
 /* The same product for many tokens (prefill, batched decode) on the tensor cores: W is read once per
  * call, decoded tile by tile to BF16 in shared memory and multiplied by tcgen05.mma with an FP32
  * accumulator in tensor memory; the activations arrive by TMA. Serves the any-M contract of

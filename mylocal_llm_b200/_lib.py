@@ -30,6 +30,9 @@ SIGNATURES = {
     "b200q_gemv_q8_1": [_ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr, _c_int, _ptr],
     "b200q_gemm": [_ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr, _c_int, _ptr],
     "b200q_gemm_supported": [_c_int, _c_int, _c_int, _c_int, _c_int],
+    "b200q_gemv_norm_supported": [_c_int, _c_int, _c_int, _c_int, _c_int],
+    "b200q_gemv_norm": [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _c_f32, _ptr, _c_int, _c_f32, _c_int, _ptr, _ptr,
+                        _c_int, _ptr],
     "b200q_gemm_workspace_bytes": [_c_int, _c_int, _c_int, _c_int, _c_int],
     "b200q_gemm_ws": [_ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr, _c_int, _ptr, _c_i64, _ptr],
     "b200q_swiglu": [_ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr, _c_int, _ptr],

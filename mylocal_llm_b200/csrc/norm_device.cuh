@@ -10,6 +10,7 @@ namespace b200q {
 // One 256-thread CTA per row. FP32 math with the reference's operation order
 // (mini_llm/ops/rmsnorm_inference.py:80-119): mean = sum/d, inv = 1/sqrt(mean+eps) by correctly
 // rounded division and square root, y = (x*inv)*gamma.
+// rmsnorm_row is the work of the 256 threads that handle row `row` (res_out may be null: the sum is then not stored)
 // rmsnorm_row is the work of the 256 threads that handle row `row` (tid = 0..255; they meet at named barrier
 // ROW_BARRIER, so a CTA with more threads can run it on its first eight warps).
 constexpr int ROW_BARRIER = 12;
@@ -68,7 +69,7 @@ __device__ __forceinline__ void rmsnorm_row(const int row, const int tid, const 
         for (int i = 0; i < KEEP; ++i) {
             const int c = tid + 256 * i;
             if (c < d) {
-                if (RESIDUAL) res_out[base + c] = kept[i];
+                if (RESIDUAL && res_out) res_out[base + c] = kept[i];
                 store_from_float(y, y_dtype, base + c, (kept[i] * inv) * gam[i]);
             }
         }
@@ -78,7 +79,7 @@ __device__ __forceinline__ void rmsnorm_row(const int row, const int tid, const 
         float v = load_as_float(x, x_dtype, base + c);
         if (RESIDUAL) {
             v = residual[base + c] + alpha * v;
-            res_out[base + c] = v;
+            if (res_out) res_out[base + c] = v;
         }
         store_from_float(y, y_dtype, base + c, (v * inv) * load_as_float(gamma, gamma_dtype, c));
     }

@@ -278,6 +278,54 @@ static int retile_common(const void *src, void *dst, long long rows, int k, bool
 
 using namespace b200q;
 
+// b200q_gemv_norm: y[m, n] = rmsnorm(residual + alpha * branch) W^T with the new residual stream stored as well;
+// tile-layout Q6_K / Q8_0 weights, at most NORM_GEMV_MAX_ROWS rows (every CTA normalises the rows itself).
+constexpr int NORM_GEMV_MAX_ROWS = 4;
+
+extern "C" int b200q_gemv_norm_supported(int fmt, int n, int k, int act_dtype, int m) {
+    if (fmt != B200Q_Q6_K_TILED && fmt != B200Q_Q8_0_TILED) return 0;
+    if (act_dtype != B200Q_BF16 && act_dtype != B200Q_F16) return 0;
+    if (m < 1 || m > NORM_GEMV_MAX_ROWS || n < 16 || n % 16 != 0 || k < 256 || k % 256 != 0) return 0;
+    const long long body = Q6T_CTRL_BYTES + Q6T_PART_BYTES + static_cast<long long>(k / 16) * 256;
+    return body + 128 + static_cast<long long>(m) * k * 2 + 10LL * k <= MM_SMEM_LIMIT - 4096 ? 1 : 0;      // + one row's staging
+}
+
+extern "C" int b200q_gemv_norm(const void *w, int fmt, int n, int k, const float *residual, const void *branch,
+                               int branch_dtype, float alpha, const void *gamma, int act_dtype, float eps, int m,
+                               float *res_out, void *y, int y_dtype, void *stream) {
+    if (!w || !residual || !branch || !gamma || !res_out || !y) return fail(B200Q_EINVAL, "gemv_norm: NULL pointer");
+    if (!dtype_valid(branch_dtype) || !dtype_valid(y_dtype)) return fail(B200Q_EINVAL, "gemv_norm: bad dtype");
+    if (!b200q_gemv_norm_supported(fmt, n, k, act_dtype, m))
+        return fail(B200Q_EUNSUPPORTED, "gemv_norm: needs tile-layout Q6_K / Q8_0 weights, 16-bit activations, at most %d rows",
+                    NORM_GEMV_MAX_ROWS);
+    MmaRequest q{};
+    q.mode = 0; q.wa = static_cast<const uint8_t *>(w); q.fmt_a = q.fmt_b = fmt; q.n = n; q.k = k; q.m = m;
+    q.x = residual;            // placeholder: the kernel reads the normalised rows from its shared memory
+    q.x_dtype = act_dtype; q.y = y; q.y_dtype = y_dtype;
+    Q6TiledArgs a{};
+    long long smem = 0;
+    int rc = tiled_plan_args(q, &a, &smem);
+    if (rc) return rc;
+    NormPrologue pro{};
+    pro.residual = residual; pro.branch = branch; pro.branch_dtype = branch_dtype; pro.alpha = alpha;
+    pro.gamma = gamma; pro.gamma_dtype = act_dtype; pro.eps = eps; pro.res_out = res_out;
+    pro.x_off = static_cast<int>((smem + 127) / 128 * 128);
+    smem = pro.x_off + static_cast<long long>(m) * k * 2 + 10LL * k;
+    using NormFn = void (*)(const Q6TiledArgs, const NormPrologue);
+    NormFn fn = fmt == B200Q_Q8_0_TILED ? tiled_norm_kernel<Q8Tile, 1> : tiled_norm_kernel<Q6Tile, 1>;
+    cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void *>(fn),
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM_LIMIT - 4096);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail(B200Q_ECUDA, "gemv_norm: shared memory opt-in failed: %s", cudaGetErrorString(err));
+    }
+    int grid = sm_count();
+    const int blocks = (n / 16 + a.rg - 1) / a.rg;
+    if (blocks < grid) grid = blocks;
+    launch_chained(fn, dim3(grid), dim3(Q6T_THREADS), static_cast<size_t>(smem), static_cast<cudaStream_t>(stream), a, pro);
+    return check_launch("gemv_norm");
+}
+
 static int q4k_retile_common(const void *src, void *dst, long long rows, int k, bool forward, void *stream) {
     if (!src || !dst) return fail(B200Q_EINVAL, "q4k_retile: NULL pointer");
     if (rows <= 0 || rows % 16 != 0 || k <= 0 || k % 256 != 0)

@@ -517,4 +517,101 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_kernel(const Q6TiledArgs
     tiled_body<TILE, MODE, NTERMS, NT>(a, gp, smem, blockIdx.x, gridDim.x);
 }
 
+// Residual add + RMSNorm fused into the GEMV that consumes it (one-token decoder steps: the norm is a 4-5 us launch
+// of its own for a row of a few KB). Every CTA normalises the rows itself - the arithmetic of rmsnorm_kernel<true>,
+// run by its first 256 threads, the normalised row kept in shared memory behind the GEMV's buffers in the
+// activation type - and then runs the GEMV body on it; CTA 0 also stores the new residual stream. Same bits as
+// the two launches.
+struct NormPrologue {
+    const float *residual;     // [m, k] FP32
+    const void *branch;        // [m, k], added to the residual (alpha * branch)
+    int branch_dtype;
+    float alpha;
+    const void *gamma;         // [k]; its type is the type of the normalised activations
+    int gamma_dtype;
+    float eps;
+    float *res_out;            // [m, k] FP32: residual + alpha * branch
+    int x_off;                 // byte offset of the normalised rows in dynamic shared memory
+};
+
+}  // namespace b200q
+
+#include "norm_device.cuh"
+
+namespace b200q {
+
+// One row of residual add + RMSNorm by the whole CTA with the arithmetic of rmsnorm_row<true>: thread t < 256 owns
+// columns t, t + 256, ... (sum of squares in ascending order, the same reduction tree, the same roundings). The
+// inputs are first copied to shared memory with one vector load per thread - inside this large kernel the compiler
+// issued rmsnorm_row's 24 loads per thread one by one, 6 us per launch.
+__device__ __forceinline__ void norm_row_staged(int row, int tid, const NormPrologue &n, int k, float *res_s,
+                                                uint8_t *br_s, uint8_t *gam_s, uint8_t *x_row, bool store_residual) {
+    __shared__ float warp_sums[8];
+    __shared__ float inv_shared;
+    const int lane = tid & 31, warp = tid >> 5;
+    const size_t base = static_cast<size_t>(row) * k;
+    const int bsize = n.branch_dtype == B200Q_F32 ? 4 : 2;
+    for (int i = tid; i < k / 4; i += Q6T_THREADS)
+        reinterpret_cast<float4 *>(res_s)[i] = reinterpret_cast<const float4 *>(n.residual + base)[i];
+    for (int i = tid; i < k * bsize / 16; i += Q6T_THREADS)
+        reinterpret_cast<uint4 *>(br_s)[i] = reinterpret_cast<const uint4 *>(static_cast<const uint8_t *>(n.branch) + base * bsize)[i];
+    for (int i = tid; i < k * 2 / 16; i += Q6T_THREADS)
+        reinterpret_cast<uint4 *>(gam_s)[i] = reinterpret_cast<const uint4 *>(n.gamma)[i];
+    __syncthreads();
+    if (tid < ROW_THREADS) {
+        float ss = 0.f;
+        for (int c = tid; c < k; c += ROW_THREADS) {
+            float v = load_as_float(br_s, n.branch_dtype, c);
+            v = res_s[c] + n.alpha * v;
+            res_s[c] = v;
+            ss += v * v;
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) warp_sums[warp] = ss;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < 8 ? warp_sums[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) inv_shared = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(t, static_cast<float>(k)) + n.eps));
+    }
+    __syncthreads();
+    const float inv = inv_shared;
+    for (int c = tid; c < k; c += Q6T_THREADS)
+        store_from_float(x_row, n.gamma_dtype, c, (res_s[c] * inv) * load_as_float(gam_s, n.gamma_dtype, c));
+    if (store_residual)
+        for (int i = tid; i < k / 4; i += Q6T_THREADS)
+            reinterpret_cast<float4 *>(n.res_out + base)[i] = reinterpret_cast<const float4 *>(res_s)[i];
+    __syncthreads();
+}
+
+template <typename TILE, int NTERMS>
+__global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_norm_kernel(const Q6TiledArgs a, const NormPrologue n) {
+    chain_trigger();
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x;
+    {
+        // the CTA's slice of the weights is asked into L2 before the wait (as the GEMV body does): the norm
+        // below then runs while the bytes arrive
+        const int groups_total = a.n >> 4, nsb = a.k >> 8;
+        const long long total_blocks = (groups_total + a.rg - 1) / a.rg;
+        const long long blk_begin = total_blocks * blockIdx.x / gridDim.x, blk_end = total_blocks * (blockIdx.x + 1) / gridDim.x;
+        if (blk_begin < blk_end) {
+            const size_t first = static_cast<size_t>(blk_begin) * a.rg * nsb * TILE::BYTES;
+            const size_t last = static_cast<size_t>(min(static_cast<long long>(groups_total), blk_end * a.rg)) * nsb * TILE::BYTES;
+            prefetch_l2_range(a.w + first, last - first, CHAIN_PREFETCH_BYTES, tid, Q6T_THREADS);
+        }
+    }
+    chain_wait();              // residual and branch come from preceding kernels
+    uint8_t *x_rows = smem + n.x_off;                          // [m][k] activations, then the staging of one row
+    uint8_t *stage = x_rows + static_cast<size_t>(a.m) * a.k * 2;
+    float *res_s = reinterpret_cast<float *>(stage);
+    uint8_t *br_s = stage + static_cast<size_t>(a.k) * 4;
+    uint8_t *gam_s = br_s + static_cast<size_t>(a.k) * 4;
+    for (int row = 0; row < a.m; ++row)
+        norm_row_staged(row, tid, n, a.k, res_s, br_s, gam_s, x_rows + static_cast<size_t>(row) * a.k * 2, blockIdx.x == 0);
+    const StagePointers gp{x_rows, a.y, a.table, nullptr, a.order, a.seg_expert, a.seg_begin, a.seg_count, a.num_segments, a.route, -1};
+    tiled_body<TILE, 0, NTERMS, 1>(a, gp, smem, blockIdx.x, gridDim.x);
+}
+
 }  // namespace b200q

@@ -83,6 +83,9 @@ class ExternalLlamaModel:
             raise ValueError("dtype must be float32, float16 or bfloat16")
         self.config, self.dtype, self.device = config, getattr(torch, dtype), device
         self.fused_decode = True       # one-token steps use the RoPE+store and attention kernels
+        # ... and run each residual-add + RMSNorm inside the projection that consumes it (``B200Q_NORM_GEMV=0``: as a
+        # launch of its own; the results are the same bits)
+        self.fused_norm_linear = os.environ.get("B200Q_NORM_GEMV", "1") != "0"
         self._loaded = False
 
     def expected_shapes(self):
@@ -240,6 +243,63 @@ class ExternalLlamaModel:
             return quantized_linear(x, native, out_dtype=out_dtype)
         return quantized_linear(x, weight, out_dtype=out_dtype)
 
+    def _norm_linear(self, norm, residual, branch, weight, out_dtype):
+        """``(residual + branch, rmsnorm(residual + branch) @ weight.T)``: one launch (``b200q_gemv_norm``) where the
+        fused kernel covers the case - tile-layout Q6_K / Q8_0 weight, 16-bit model type, a few rows - else the
+        norm kernel followed by the projection."""
+        torch = _torch()
+        rows, d = residual.shape
+        n, k = weight.shape
+        fmt = _lib.FORMAT_ID.get(weight.quant_type, -1)
+        dt = _lib.DTYPE_ID[str(norm.gamma.dtype).replace("torch.", "")]
+        # (one row only: every CTA of the projection normalises the rows itself, one after the other)
+        if (self.fused_norm_linear and rows == 1 and branch.is_contiguous() and residual.is_contiguous() and k == d
+                and _lib.load().b200q_gemv_norm_supported(fmt, n, k, dt, rows)):
+            ptr = lambda x: ctypes.c_void_p(x.data_ptr())
+            res_out = torch.empty_like(residual)
+            y = torch.empty((rows, n), dtype=out_dtype or norm.gamma.dtype, device=residual.device)
+            _lib.call("b200q_gemv_norm", ptr(weight.data), fmt, n, k, ptr(residual), ptr(branch),
+                      _lib.DTYPE_ID[str(branch.dtype).replace("torch.", "")], 1.0, ptr(norm.gamma), dt, float(norm.eps),
+                      rows, ptr(res_out), ptr(y), _lib.DTYPE_ID[str(y.dtype).replace("torch.", "")],
+                      _lib.current_stream())
+            return res_out, y
+        residual, hidden = norm.forward_residual_add(residual, branch)
+        return residual, self._linear(hidden, weight, out_dtype)
+
+    def _forward_one_token(self, token_ids, state, positions):
+        """The one-token step with every residual-add + RMSNorm deferred into the projection that follows it
+        (stacked qkv, stacked gate|up, LM head). Returns FP32 logits [B, vocab]."""
+        torch = _torch()
+        cfg = self.config
+        b = token_ids.shape[0]
+        heads, kv_heads, dh = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        qd, kd = heads * dh, kv_heads * dh
+        ptr = lambda x: ctypes.c_void_p(x.data_ptr())
+        cache_id = _lib.DTYPE_ID[str(self.dtype).replace("torch.", "")]
+        residual = self._embed(token_ids)                                         # FP32 [B, d]
+        pending = None                                                            # (norm, branch) not applied yet
+        for i, layer in enumerate(self.layers):
+            if pending is None:
+                qkv = self._linear(layer["norm1"].forward_residual(residual), layer["qkv"], torch.float32)
+            else:
+                residual, qkv = self._norm_linear(layer["norm1"], residual, pending, layer["qkv"], torch.float32)
+            q2, k2, v2 = qkv[:, :qd], qkv[:, qd:qd + kd], qkv[:, qd + kd:]
+            _lib.call("b200q_rope_kv_store", ptr(q2), ptr(k2), ptr(v2), q2.stride(0), k2.stride(0), v2.stride(0),
+                      ptr(positions), ptr(self._cos), ptr(self._sin), int(self._cos.shape[0]), b, 1, heads, kv_heads, dh,
+                      state.horizon, ptr(state.k[i]), ptr(state.v[i]), cache_id, _lib.current_stream())
+            ctx = torch.empty((b, heads * dh), dtype=self.dtype, device=residual.device)
+            _lib.call("b200q_decode_attention", ptr(q2), q2.stride(0), ptr(state.k[i]), ptr(state.v[i]), cache_id,
+                      ptr(positions), b, heads, kv_heads, dh, state.horizon, float(dh ** -0.5), ptr(ctx), cache_id,
+                      _lib.current_stream())
+            attn = quantized_linear(ctx, layer["o"])
+            residual, gu = self._norm_linear(layer["norm2"], residual, attn, layer["gate_up"], torch.float32)
+            f = gu.shape[1] // 2
+            act = torch.empty((b, f), dtype=self.dtype, device=gu.device)
+            _lib.call("b200q_silu_mul", ptr(gu), b, f, ptr(act), cache_id, _lib.current_stream())
+            pending = self._linear(act, layer["down"])
+        _, logits = self._norm_linear(self.final_norm, residual, pending, self.lm_head, torch.float32)
+        return logits
+
     def _forward(self, token_ids, state, positions, mask):
         """token_ids [B, T]; positions [T] device int64; mask [T, horizon] additive FP32. Returns the
         final normalised hidden states [B*T, d] in the model dtype."""
@@ -332,6 +392,13 @@ class ExternalLlamaModel:
         if state.length >= state.horizon:
             raise ValueError("generation state is full")
         positions = state.position.clone()
+        cfg = self.config
+        if (self.fused_decode and self.fused_norm_linear and cfg.head_dim in (64, 128)
+                and all(layer["qkv"] is not None and layer["gate_up"] is not None for layer in self.layers)):
+            logits = self._forward_one_token(token_ids.reshape(-1, 1), state, positions)
+            state.position.add_(1)
+            state.length += 1
+            return logits
         cols = torch.arange(state.horizon, device=self.device)
         mask = torch.where(cols[None, :] <= positions[:, None], 0.0, float("-inf")).float()
         hidden = self._forward(token_ids.reshape(-1, 1), state, positions, mask)
