@@ -144,9 +144,9 @@ __device__ __forceinline__ void topk_row(const int row, const int tid, const flo
 // of dependent latencies (the persistent one-token MoE step). Lane L plays threads L, L + 32, L + 64, L + 96
 // of topk_row ("virtual warps" w = 0..3): every partial sum is formed over the same values in the same order
 // and reduced by the same butterfly; maxima and the selection are order-independent (keys are unique). A lane
-// keeps its NE = n / 32 (rounded up to 16 or 32) keys in registers; a selection round is a tree of 64-bit
-// maxima over them, two warp-wide maxima and one cleared bit, and the k probabilities are computed together
-// after the last round. Writes weights / ids (k + 1 entries with the appended id) and the one-row plan's order,
+// keeps its NE = n / 32 (rounded up to 16 or 32) keys in registers; a selection round is a tree of 32-bit maxima
+// over them (carrying the entry's position), a warp-wide maximum, a warp-wide minimum of the index among the equal
+// keys and one cleared bit, and the k probabilities are computed together after the last round. Writes weights / ids (k + 1 entries with the appended id) and the one-row plan's order,
 // inv, segment arrays and num_segments; counts / offsets only when given. n <= 32 NE, k <= 31, extra_id >= 0.
 template <int NE>
 __device__ __forceinline__ void topk_plan_warp(const int lane, const float *logits, int n, int k, int renorm,
@@ -180,37 +180,50 @@ __device__ __forceinline__ void topk_plan_warp(const int lane, const float *logi
         const float other = __shfl_xor_sync(0xffffffffu, mx, o);
         mx = (isnan(mx) || isnan(other)) ? qnan : fmaxf(mx, other);
     }
-    float den = 0.f;
+    // the four virtual warps' partial sums, each over its values in ascending order, reduced by four butterflies
+    // that advance together
+    float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-        float part = 0.f;
+    for (int i = 0; i < NE / 4; ++i)
 #pragma unroll
-        for (int i = 0; i < NE / 4; ++i)
-            if (i * 128 + 32 * w + lane < n) part += expf(from_orderable_bits(hi[4 * i + w]) - mx);
-        part = warp_sum(part);
-        den = w == 0 ? part : den + part;              // ((r0 + r1) + r2) + r3
-    }
+        for (int w = 0; w < 4; ++w)
+            if (i * 128 + 32 * w + lane < n) part[w] += expf(from_orderable_bits(hi[4 * i + w]) - mx);
+#pragma unroll
+    for (int o = 16; o; o >>= 1)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) part[w] += __shfl_xor_sync(0xffffffffu, part[w], o);
+    const float den = ((part[0] + part[1]) + part[2]) + part[3];
 
+    // Selection keys: monotonic float bits + 1, so that 0 can stand for "taken / outside the row" (a NaN's key is
+    // 1, the largest key is +inf's 0xFF800001: no wrap). Within a lane a lower entry is a lower index, so a
+    // strict "greater" keeps the lower index on ties; across lanes the smallest index among the equal keys wins.
+    uint32_t h1[NE];
+#pragma unroll
+    for (int t = 0; t < NE; ++t) h1[t] = hi[t] + 1u;
     uint32_t my_h = 0u;        // lane s keeps slot s
     int my_i = 0;
 #pragma unroll 1
     for (int slot = 0; slot < k; ++slot) {
-        // 64-bit keys order like the selection rule: (monotonic float bits, ~index); 0 = nothing to offer
-        unsigned long long key[NE];
+        uint32_t val[NE], pos[NE];
 #pragma unroll
-        for (int t = 0; t < NE; ++t)
-            key[t] = ((alive >> t) & 1u) ? ((static_cast<unsigned long long>(hi[t]) << 32) | ~static_cast<uint32_t>(lane + 32 * t))
-                                         : 0ull;
+        for (int t = 0; t < NE; ++t) {
+            val[t] = ((alive >> t) & 1u) ? h1[t] : 0u;
+            pos[t] = t;
+        }
 #pragma unroll
         for (int span = NE / 2; span >= 1; span >>= 1)
 #pragma unroll
-            for (int t = 0; t < span; ++t) key[t] = max(key[t], key[t + span]);
-        const uint32_t bh = static_cast<uint32_t>(key[0] >> 32), bl = static_cast<uint32_t>(key[0]);
-        const uint32_t wh = __reduce_max_sync(0xffffffffu, bh);
-        const uint32_t wl = __reduce_max_sync(0xffffffffu, bh == wh ? bl : 0u);
-        const int bi = static_cast<int>(~wl);
+            for (int t = 0; t < span; ++t) {
+                const bool take = val[t + span] > val[t];
+                pos[t] = take ? pos[t + span] : pos[t];
+                val[t] = max(val[t], val[t + span]);
+            }
+        const uint32_t wv = __reduce_max_sync(0xffffffffu, val[0]);
+        const uint32_t idx = static_cast<uint32_t>(lane) + 32u * pos[0];
+        const uint32_t bi_u = __reduce_min_sync(0xffffffffu, (val[0] == wv && wv != 0u) ? idx : 0xffffffffu);
+        const int bi = static_cast<int>(bi_u);                    // -1 when nothing is left, as in topk_row
         if (bi >= 0 && (bi & 31) == lane) alive &= ~(1u << ((bi >> 5) & 31));
-        if (lane == slot) { my_h = wh; my_i = bi; }
+        if (lane == slot) { my_h = wv - 1u; my_i = bi; }
     }
     const float my_p = __fdiv_rn(expf(from_orderable_bits(my_h) - mx), den);
     const int k_out = k + 1;
