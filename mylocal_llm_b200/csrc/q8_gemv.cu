@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(Q8G_THREADS, 1) q4k_q8_gemv_kernel(const Q8Gem
     chain_trigger();
     extern __shared__ __align__(16) uint8_t smem[];
     const int nblk = a.k >> 5, nsb = a.k >> 8;
-    // shared memory: codes [MT][k] | dx [MT][nblk] | dxs [MT][nblk][2] | partial [16 warps][16 rows][MT]
+    // shared memory: codes [MT][k] | dx [MT][nblk] | dxs [MT][nblk][2] | partial [2][16 warps][16 rows][MT]
     int8_t *qs_s = reinterpret_cast<int8_t *>(smem);
     float *dx_s = reinterpret_cast<float *>(smem + static_cast<size_t>(MT) * a.k);
     float *dxs_s = dx_s + MT * nblk;
@@ -157,6 +157,7 @@ __global__ void __launch_bounds__(Q8G_THREADS, 1) q4k_q8_gemv_kernel(const Q8Gem
     if (blk_begin >= blk_end) return;
 
     const int pair = tig >> 1, half = tig & 1;
+    int pbuf = 0;
     for (int blk = blk_begin; blk < blk_end; ++blk) {
         const int row0 = blk * rows_per_block;
         float tot_a[MT], tot_b[MT];
@@ -225,23 +226,29 @@ __global__ void __launch_bounds__(Q8G_THREADS, 1) q4k_q8_gemv_kernel(const Q8Gem
             tot_b[t] += __shfl_xor_sync(0xffffffffu, tot_b[t], 1);
             tot_b[t] += __shfl_xor_sync(0xffffffffu, tot_b[t], 2);
         }
-        __syncthreads();          // the previous row block's partial sums have been consumed
+        // The K parts of a row group are added by that group's own warps behind a barrier of just those warps, with
+        // the partial sums double-buffered: no CTA-wide stop per row block (a warp writes buffer b again only after
+        // its group's next barrier, which every reader of b has reached by then).
+        float *pb = partial + pbuf * (Q8G_WARPS * 16 * MT);
         if (tig == 0) {
 #pragma unroll
             for (int t = 0; t < MT; ++t) {
-                partial[(warp * 16 + g) * MT + t] = tot_a[t];
-                partial[(warp * 16 + g + 8) * MT + t] = tot_b[t];
+                pb[(warp * 16 + g) * MT + t] = tot_a[t];
+                pb[(warp * 16 + g + 8) * MT + t] = tot_b[t];
             }
         }
-        __syncthreads();
-        for (int o = tid; o < a.rg * 16 * MT; o += Q8G_THREADS) {
-            const int t = o % MT, r = (o / MT) & 15, grp = o / (16 * MT);
-            const int orow = row0 + 16 * grp + r;
+        const int group_threads = a.kp * 32;
+        if (a.kp == 1) __syncwarp();
+        else named_barrier_sync(2 + rgi, group_threads);          // kp >= 2: at most 8 row groups, ids 2..9
+        for (int o = kpi * 32 + lane; o < 16 * MT; o += group_threads) {
+            const int t = o % MT, r = o / MT;
+            const int orow = row0 + 16 * rgi + r;
             if (orow >= a.n || t >= a.m) continue;
             float sum = 0.f;
-            for (int kq = 0; kq < a.kp; ++kq) sum += partial[((grp * a.kp + kq) * 16 + r) * MT + t];
+            for (int kq = 0; kq < a.kp; ++kq) sum += pb[((rgi * a.kp + kq) * 16 + r) * MT + t];
             store_from_float(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + orow, sum);
         }
+        pbuf ^= 1;
     }
 }
 
@@ -283,7 +290,7 @@ extern "C" int b200q_gemv_q8_1(const void *w, int fmt, int n, int k, const void 
         auto blocks_for = [&](int parts) { return (static_cast<long long>(n) + 16 * (Q8G_WARPS / parts) - 1) / (16 * (Q8G_WARPS / parts)); };
         while (kp * 2 <= Q8G_WARPS && kp * 2 <= nsb && blocks_for(kp) < 6LL * sm_count()) kp *= 2;
         a.kp = kp; a.rg = Q8G_WARPS / kp;
-        const size_t smem = static_cast<size_t>(mt) * k + static_cast<size_t>(mt) * (k / 32) * 12 + Q8G_WARPS * 16 * mt * 4;
+        const size_t smem = static_cast<size_t>(mt) * k + static_cast<size_t>(mt) * (k / 32) * 12 + 2 * Q8G_WARPS * 16 * mt * 4;
         if (smem > 200 * 1024) return fail(B200Q_EUNSUPPORTED, "gemv_q8_1: K=%d too large for the activation tile", k);
         auto fn = mt == 4 ? q4k_q8_gemv_kernel<4> : mt == 2 ? q4k_q8_gemv_kernel<2> : q4k_q8_gemv_kernel<1>;
         cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void *>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
