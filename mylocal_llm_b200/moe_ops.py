@@ -181,11 +181,13 @@ def moe_gate_up(x2d, plan, gate_bank, up_bank, gate_fmt, up_fmt, f, d, gate_stri
 
     Experts live either in contiguous banks (``*_bank`` + byte stride) or behind device pointer
     tables (int64 tensors with one address per expert). ``images`` = ``token_images(x2d)``; by default they
-    are made here when ``x2d`` has at least ``TOKEN_IMAGE_MIN_ROWS`` rows (``B200Q_TOKEN_IMAGES=0`` turns
-    that off). The results are the same bits either way."""
+    are made here when ``x2d`` has at least ``TOKEN_IMAGE_MIN_ROWS`` rows (``B200Q_TOKEN_IMAGES=0`` or
+    ``images=False`` turns that off). The results are the same bits either way."""
     torch = _torch()
     hbuf = torch.empty((plan.rows * plan.k, f), dtype=torch.float32, device=x2d.device)
-    if images is None and x2d.shape[0] >= TOKEN_IMAGE_MIN_ROWS and os.environ.get("B200Q_TOKEN_IMAGES", "1") != "0" \
+    if images is False:          # the caller knows its plan executes too few of the rows for images to pay
+        images = None
+    elif images is None and x2d.shape[0] >= TOKEN_IMAGE_MIN_ROWS and os.environ.get("B200Q_TOKEN_IMAGES", "1") != "0" \
             and gate_fmt in ("Q4_K", "Q5_K", "Q4_K_TILED", "Q5_K_TILED") and gate_fmt == up_fmt:
         images = token_images(x2d)
     if images is not None:
