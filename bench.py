@@ -68,6 +68,7 @@ WORKLOADS = {
     # integer-dot mode (Q8_1 activations, opt-in): the activation dtype field names the mode
     "gemv_q4k_65536x8192_m1_q8_1": ("Q4_K", 65536, 8192, 1, "q8_1"),
     "gemv_q4k_8192x2048_m1_q8_1": ("Q4_K", 8192, 2048, 1, "q8_1"),
+    "gemv_q5k_65536x4096_m1_q8_1": ("Q5_K", 65536, 4096, 1, "q8_1"),
     # prefill / batched sizes of the second configuration: the tcgen05 GEMM (weights in GGUF layout, read once)
     "gemm_q4k_8192x2048_m512": ("Q4_K", 8192, 2048, 512, "bfloat16"),
     "gemm_q4k_2048x8192_m512": ("Q4_K", 2048, 8192, 512, "bfloat16"),

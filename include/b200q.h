@@ -114,8 +114,8 @@ int b200q_gemm_ws(const void *w, int fmt, int n, int k, const void *x, int x_dty
  * all-zero block), sum = sum of the block's inputs; IEEE arithmetic. Replaces the quantiser of
  * mini_llm/ops/q8_1_gpu.py:30-58 (its non-fast-math "ieee" variant).
  * b200q_gemv_q8_1: y[m, n] = dequant(xq)[m, k] @ W[n, k]^T with integer dots (dp4a) per sub-block and the
- * per-sub-block scaling of mini_llm/ops/mixed_q8_gpu.py:86-139 (q8_linear / k_part for Q4_K). W: Q4_K in
- * GGUF or tile layout (other formats: 3 = unsupported), K a multiple of 256; 1..4 tokens per pass over W. */
+ * per-sub-block scaling of mini_llm/ops/mixed_q8_gpu.py:86-139 (q8_linear / k_part for Q4_K and Q5_K). W: Q4_K
+ * or Q5_K in GGUF or tile layout (other formats: 3 = unsupported), K a multiple of 256; 1..4 tokens per pass over W. */
 int b200q_quantize_q8_1(const void *x, int x_dtype, int rows, int k, void *out_blocks, void *stream);
 int b200q_gemv_q8_1(const void *w, int fmt, int n, int k, const void *xq_blocks, int m, void *y, int y_dtype,
                     void *stream);

@@ -51,6 +51,7 @@ __device__ __forceinline__ uint4 q8g_ldg128(const uint8_t *p) {
 struct Q4Item {
     uint4 hd_a, hd_b;         // d, dmin, 12 scale bytes of rows g and g+8
     uint4 qa_a, qb_a, qa_b, qb_b;
+    uint4 qh_a, qh_b;         // Q5_K: the fifth bits of the lane's 16 elements (all eight sub-blocks), rows g and g+8
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -87,8 +88,10 @@ __global__ void q8_1_quantize_kernel(const void *x, int x_dtype, long long total
 // ---------------------------------------------------------------------------------------------
 // GEMV kernel
 // ---------------------------------------------------------------------------------------------
-template <int MT>
+template <int MT, bool Q5>
 __global__ void __launch_bounds__(Q8G_THREADS, 1) q4k_q8_gemv_kernel(const Q8GemvArgs a) {
+    constexpr int QB = Q5 ? 176 : 144;                        // bytes of a native super-block
+    constexpr int TILE = Q5 ? 2816 : Q8G_TILE_BYTES;           // bytes of a 16-row tile (b200q_q4k_retile / b200q_q5k_retile)
     chain_trigger();
     extern __shared__ __align__(16) uint8_t smem[];
     const int nblk = a.k >> 5, nsb = a.k >> 8;
@@ -109,22 +112,32 @@ __global__ void __launch_bounds__(Q8G_THREADS, 1) q4k_q8_gemv_kernel(const Q8Gem
     auto issue = [&](int row0, int sb, Q4Item &it) {
         if (a.tiled) {
             const int group = min((row0 >> 4) + rgi, (a.n >> 4) - 1);
-            const uint8_t *tile = a.w + (static_cast<size_t>(group) * nsb + sb) * Q8G_TILE_BYTES;
+            const uint8_t *tile = a.w + (static_cast<size_t>(group) * nsb + sb) * TILE;
+            constexpr int P = Q5 ? 768 : 256;                  // first quant plane (Q5_K: behind the fifth bits)
             it.hd_a = q8g_ldg128(tile + 16 * g);
             it.hd_b = q8g_ldg128(tile + 16 * (g + 8));
-            it.qa_a = q8g_ldg128(tile + 256 + lane * 16);
-            it.qb_a = q8g_ldg128(tile + 768 + lane * 16);
-            it.qa_b = q8g_ldg128(tile + 1280 + lane * 16);
-            it.qb_b = q8g_ldg128(tile + 1792 + lane * 16);
+            if (Q5) {
+                it.qh_a = q8g_ldg128(tile + 256 + 32 * g + 16 * (tig & 1));
+                it.qh_b = q8g_ldg128(tile + 256 + 32 * (g + 8) + 16 * (tig & 1));
+            }
+            it.qa_a = q8g_ldg128(tile + P + lane * 16);
+            it.qb_a = q8g_ldg128(tile + P + 512 + lane * 16);
+            it.qa_b = q8g_ldg128(tile + P + 1024 + lane * 16);
+            it.qb_b = q8g_ldg128(tile + P + 1536 + lane * 16);
         } else {
-            const uint8_t *ra = a.w + static_cast<size_t>(min(row0 + 16 * rgi + g, a.n - 1)) * a.row_bytes + sb * 144;
-            const uint8_t *rb = a.w + static_cast<size_t>(min(row0 + 16 * rgi + g + 8, a.n - 1)) * a.row_bytes + sb * 144;
+            const uint8_t *ra = a.w + static_cast<size_t>(min(row0 + 16 * rgi + g, a.n - 1)) * a.row_bytes + sb * QB;
+            const uint8_t *rb = a.w + static_cast<size_t>(min(row0 + 16 * rgi + g + 8, a.n - 1)) * a.row_bytes + sb * QB;
+            constexpr int Q = Q5 ? 48 : 16;                    // first quant byte of a native block
             it.hd_a = q8g_ldg128(ra);
             it.hd_b = q8g_ldg128(rb);
-            it.qa_a = q8g_ldg128(ra + 16 + 16 * tig);
-            it.qb_a = q8g_ldg128(ra + 80 + 16 * tig);
-            it.qa_b = q8g_ldg128(rb + 16 + 16 * tig);
-            it.qb_b = q8g_ldg128(rb + 80 + 16 * tig);
+            if (Q5) {
+                it.qh_a = q8g_ldg128(ra + 16 + 16 * (tig & 1));
+                it.qh_b = q8g_ldg128(rb + 16 + 16 * (tig & 1));
+            }
+            it.qa_a = q8g_ldg128(ra + Q + 16 * tig);
+            it.qb_a = q8g_ldg128(ra + Q + 64 + 16 * tig);
+            it.qa_b = q8g_ldg128(rb + Q + 16 * tig);
+            it.qb_b = q8g_ldg128(rb + Q + 64 + 16 * tig);
         }
     };
     const int sb_count = kpi < nsb ? (nsb - kpi + a.kp - 1) / a.kp : 0;     // this warp's super-blocks: kpi, kpi+kp, ..
@@ -188,6 +201,7 @@ __global__ void __launch_bounds__(Q8G_THREADS, 1) q4k_q8_gemv_kernel(const Q8Gem
             scales(cur.hd_b, sc_b, mn_b, d_b, dm_b);
             const uint32_t wa[2][4] = {{cur.qa_a.x, cur.qa_a.y, cur.qa_a.z, cur.qa_a.w}, {cur.qb_a.x, cur.qb_a.y, cur.qb_a.z, cur.qb_a.w}};
             const uint32_t wb[2][4] = {{cur.qa_b.x, cur.qa_b.y, cur.qa_b.z, cur.qa_b.w}, {cur.qb_b.x, cur.qb_b.y, cur.qb_b.z, cur.qb_b.w}};
+            const uint32_t ha[4] = {cur.qh_a.x, cur.qh_a.y, cur.qh_a.z, cur.qh_a.w}, hb[4] = {cur.qh_b.x, cur.qh_b.y, cur.qh_b.z, cur.qh_b.w};
 #pragma unroll
             for (int t = 0; t < MT; ++t) {
                 float sd_a = 0.f, sm_a = 0.f, sd_b = 0.f, sm_b = 0.f;
@@ -202,8 +216,13 @@ __global__ void __launch_bounds__(Q8G_THREADS, 1) q4k_q8_gemv_kernel(const Q8Gem
                         int dot_a = 0, dot_b = 0;
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            const int ca = static_cast<int>((wa[X][j] >> (4 * nib)) & 0x0f0f0f0fu);
-                            const int cb = static_cast<int>((wb[X][j] >> (4 * nib)) & 0x0f0f0f0fu);
+                            uint32_t ua = (wa[X][j] >> (4 * nib)) & 0x0f0f0f0fu, ub = (wb[X][j] >> (4 * nib)) & 0x0f0f0f0fu;
+                            if (Q5) {                          // bit (sub-block) of the fifth-bit byte -> bit 4 of the code
+                                const int sub = 4 * X + 2 * pair + nib;
+                                ua |= ((ha[j] >> sub) << 4) & 0x10101010u;
+                                ub |= ((hb[j] >> sub) << 4) & 0x10101010u;
+                            }
+                            const int ca = static_cast<int>(ua), cb = static_cast<int>(ub);
                             dot_a = __dp4a(ca, uw[j], dot_a);
                             dot_b = __dp4a(cb, uw[j], dot_b);
                         }
@@ -269,8 +288,10 @@ extern "C" int b200q_quantize_q8_1(const void *x, int x_dtype, int rows, int k, 
 extern "C" int b200q_gemv_q8_1(const void *w, int fmt, int n, int k, const void *xq, int m, void *y, int y_dtype,
                                void *stream) {
     if (!w || !xq || !y) return fail(B200Q_EINVAL, "gemv_q8_1: NULL pointer");
-    const bool tiled = fmt == B200Q_Q4_K_TILED;
-    if (fmt != B200Q_Q4_K && !tiled) return fail(B200Q_EUNSUPPORTED, "gemv_q8_1: the integer-dot mode reads Q4_K (GGUF or tile layout)");
+    const bool tiled = fmt == B200Q_Q4_K_TILED || fmt == B200Q_Q5_K_TILED;
+    const bool q5 = fmt == B200Q_Q5_K || fmt == B200Q_Q5_K_TILED;
+    if (fmt != B200Q_Q4_K && fmt != B200Q_Q5_K && !tiled)
+        return fail(B200Q_EUNSUPPORTED, "gemv_q8_1: the integer-dot mode reads Q4_K / Q5_K (GGUF or tile layout)");
     if (!dtype_valid(y_dtype) || n <= 0 || m <= 0 || k <= 0 || k % 256) return fail(B200Q_EINVAL, "gemv_q8_1: bad shape n=%d k=%d m=%d", n, k, m);
     if (tiled && n % 16) return fail(B200Q_EINVAL, "gemv_q8_1: the tile layout needs rows in multiples of 16");
     if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(xq) & 3))
@@ -281,7 +302,7 @@ extern "C" int b200q_gemv_q8_1(const void *w, int fmt, int n, int k, const void 
         Q8GemvArgs a{};
         a.w = static_cast<const uint8_t *>(w); a.tiled = tiled ? 1 : 0; a.n = n; a.k = k;
         a.m = mt;
-        a.row_bytes = static_cast<long long>(nsb) * 144;
+        a.row_bytes = static_cast<long long>(nsb) * (q5 ? 176 : 144);
         a.xq = static_cast<const uint8_t *>(xq) + static_cast<size_t>(t0) * (k / 32) * 36;
         a.y = static_cast<uint8_t *>(y) + static_cast<size_t>(t0) * n * dtype_size(y_dtype);
         a.y_dtype = y_dtype;
@@ -292,7 +313,8 @@ extern "C" int b200q_gemv_q8_1(const void *w, int fmt, int n, int k, const void 
         a.kp = kp; a.rg = Q8G_WARPS / kp;
         const size_t smem = static_cast<size_t>(mt) * k + static_cast<size_t>(mt) * (k / 32) * 12 + 2 * Q8G_WARPS * 16 * mt * 4;
         if (smem > 200 * 1024) return fail(B200Q_EUNSUPPORTED, "gemv_q8_1: K=%d too large for the activation tile", k);
-        auto fn = mt == 4 ? q4k_q8_gemv_kernel<4> : mt == 2 ? q4k_q8_gemv_kernel<2> : q4k_q8_gemv_kernel<1>;
+        auto fn = q5 ? (mt == 4 ? q4k_q8_gemv_kernel<4, true> : mt == 2 ? q4k_q8_gemv_kernel<2, true> : q4k_q8_gemv_kernel<1, true>)
+                     : (mt == 4 ? q4k_q8_gemv_kernel<4, false> : mt == 2 ? q4k_q8_gemv_kernel<2, false> : q4k_q8_gemv_kernel<1, false>);
         cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void *>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (err != cudaSuccess) {
             cudaGetLastError();

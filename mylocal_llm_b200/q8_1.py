@@ -16,7 +16,7 @@ from .quantized_linear import DevicePackedGGUFWeight
 
 Q8_1_BLOCK_BYTES = 36
 Q8_1_BLOCK_ELEMENTS = 32
-SUPPORTED_Q8_1_WEIGHT_TYPES = frozenset({"Q4_K", "Q4_K_TILED"})
+SUPPORTED_Q8_1_WEIGHT_TYPES = frozenset({"Q4_K", "Q4_K_TILED", "Q5_K", "Q5_K_TILED"})
 
 
 def _torch():

@@ -55,20 +55,27 @@ def dequantize_q8_1(blocks):
     return (d[..., None] * q).reshape(blocks.shape[0], -1)
 
 
-def q4k_q8_1_linear(blocks, data, shape):
-    """Integer-dot evaluation of dequant(blocks) @ W.T for a Q4_K matrix (data, shape): float64 [rows, N]."""
+def q4k_q8_1_linear(blocks, data, shape, fmt="Q4_K"):
+    """Integer-dot evaluation of dequant(blocks) @ W.T for a Q4_K or Q5_K matrix (data, shape): float64
+    [rows, N]. Q5_K: the same formula with 5-bit codes (the fifth bit of element l of sub-block s is bit s of
+    byte l of the block's 32 high-bit bytes, ``mini_llm/ops/quantized_weight.py:233-241``)."""
     n, k = shape
-    raw = np.asarray(data, np.uint8).reshape(n, k // 256, 144)
+    block = 176 if fmt == "Q5_K" else 144
+    raw = np.asarray(data, np.uint8).reshape(n, k // 256, block)
     d = raw[..., 0:2].copy().view("<f2").astype(np.float64)[..., 0]            # [n, nsb]
     dmin = raw[..., 2:4].copy().view("<f2").astype(np.float64)[..., 0]
     sc, mn = po._k_scales_mins(raw[..., 4:16].reshape(-1, 12))
     sc, mn = sc.reshape(n, k // 256, 8).astype(np.int64), mn.reshape(n, k // 256, 8).astype(np.int64)
-    nib = raw[..., 16:].astype(np.int64)                                       # [n, nsb, 128]
+    nib = raw[..., block - 128:].astype(np.int64)                              # [n, nsb, 128]
     codes = np.empty((n, k // 256, 8, 32), np.int64)
     for pair in range(4):
         chunk = nib[..., 32 * pair:32 * pair + 32]
         codes[..., 2 * pair, :] = chunk & 15
         codes[..., 2 * pair + 1, :] = chunk >> 4
+    if fmt == "Q5_K":
+        high = raw[..., 16:48].astype(np.int64)                                # [n, nsb, 32]
+        for sub in range(8):
+            codes[..., sub, :] |= ((high >> sub) & 1) << 4
     rows = blocks.shape[0]
     dx = blocks[..., 0:2].copy().view("<f2").astype(np.float64)[..., 0].reshape(rows, k // 256, 8)
     u = blocks[..., 4:].view(np.int8).astype(np.int64).reshape(rows, k // 256, 8, 32)

@@ -30,19 +30,20 @@ def test_quantiser_matches_the_oracle_bit_for_bit(cuda, rows, k):
     np.testing.assert_array_equal(quantize_q8_1(xb).cpu().numpy(), qo.quantize_q8_1(xb.float().cpu().numpy()))
 
 
+@pytest.mark.parametrize("fmt", ["Q4_K", "Q5_K"])
 @pytest.mark.parametrize("tiled", [False, True])
 @pytest.mark.parametrize("n,k,m", [(16, 256, 1), (48, 512, 2), (80, 2048, 3), (512, 2048, 4), (96, 4096, 5), (32, 8192, 8),
                                    (2048, 1024, 1)])
-def test_gemv_matches_the_integer_formula(cuda, tiled, n, k, m):
-    w = random_packed("Q4_K", (n, k), seed=n + k + m, d=0.01, dmin=0.005)
+def test_gemv_matches_the_integer_formula(cuda, fmt, tiled, n, k, m):
+    w = random_packed(fmt, (n, k), seed=n + k + m, d=0.01, dmin=0.005)
     dev = packed_to_device(w)
     if tiled:
         dev = retile_weight(dev, force=True)
-        assert dev.quant_type == "Q4_K_TILED"
+        assert dev.quant_type == fmt + "_TILED"
     x = np.random.default_rng(m).normal(0, 1, (m, k)).astype(np.float32)
     blocks = quantize_q8_1(cuda.from_numpy(x).cuda())
     y = q8_1_linear(blocks, dev).cpu().numpy()
-    ref = qo.q4k_q8_1_linear(blocks.cpu().numpy(), w.data, w.shape)
+    ref = qo.q4k_q8_1_linear(blocks.cpu().numpy(), w.data, w.shape, fmt)
     rms = float(np.sqrt((ref ** 2).mean()))
     np.testing.assert_allclose(y, ref, rtol=2e-5, atol=2e-5 * rms)
 

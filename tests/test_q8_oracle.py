@@ -3,6 +3,7 @@
 pinned dequantised weights with the dequantised activations (the two are the same sum regrouped)."""
 
 import numpy as np
+import pytest
 
 from oracle import packed_oracle as po
 from oracle import q8_oracle as qo
@@ -39,13 +40,14 @@ def test_codec_follows_its_definition():
     np.testing.assert_allclose(s[0], x[0].reshape(8, 32).sum(axis=1), rtol=2e-3, atol=2e-2)
 
 
-def test_integer_dot_formula_equals_the_dequantised_product():
-    w = random_packed("Q4_K", (11, 512), seed=4, d=0.01, dmin=0.005)
+@pytest.mark.parametrize("fmt", ["Q4_K", "Q5_K"])
+def test_integer_dot_formula_equals_the_dequantised_product(fmt):
+    w = random_packed(fmt, (11, 512), seed=4, d=0.01, dmin=0.005)
     x = np.random.default_rng(1).normal(0, 1, (3, 512)).astype(np.float32)
     blocks = qo.quantize_q8_1(x)
-    got = qo.q4k_q8_1_linear(blocks, w.data, w.shape)
-    ref = qo.dequantize_q8_1(blocks) @ po.dequantize(w.data, w.shape, "Q4_K").astype(np.float64).T
+    got = qo.q4k_q8_1_linear(blocks, w.data, w.shape, fmt)
+    ref = qo.dequantize_q8_1(blocks) @ po.dequantize(w.data, w.shape, fmt).astype(np.float64).T
     np.testing.assert_allclose(got, ref, rtol=1e-9, atol=1e-9)
     # and the mode's distance from FP32 activations: int8 rounding of x, well inside 2 % of the output scale
-    exact = po.linear_fp64(x, w.data, w.shape, "Q4_K")
+    exact = po.linear_fp64(x, w.data, w.shape, fmt)
     assert np.abs(got - exact).max() <= 0.02 * np.abs(exact).max()
