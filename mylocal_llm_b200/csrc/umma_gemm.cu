@@ -401,14 +401,16 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
     if (warp < UG_DECODE_THREADS / 32) {
         // ---------------------------------------------------------------- decoders
         // piece j of this thread: weight row prow[j] of the tile, 16-value quarter pquart[j] of a slab's
-        // 64 positions; the lanes of a warp hold consecutive rows (conflict-free swizzled stores)
+        // 64 positions; four consecutive lanes hold the four quarters of a row (their loads cover 64 contiguous
+        // bytes of it, a warp eight rows; the 16-byte swizzled stores of a warp still take the minimum of four
+        // wavefronts: for each quarter the eight rows land in the eight different chunks)
         const uint8_t *row_ptr[UG_PIECES];
         int prow[UG_PIECES], pquart[UG_PIECES];
 #pragma unroll
         for (int j = 0; j < UG_PIECES; ++j) {
             const int id = tid + UG_DECODE_THREADS * j;
-            prow[j] = id % UG_BM;
-            pquart[j] = id / UG_BM;
+            prow[j] = (id >> 2) % UG_BM;
+            pquart[j] = id & 3;
             const int wrow = min(n0 + prow[j], a.n - 1);      // rows past the end decode the last row; never stored
             row_ptr[j] = a.w + static_cast<size_t>(wrow) * a.row_bytes + static_cast<size_t>(group0) * fmt_group_bytes(FMT);
         }
