@@ -149,11 +149,13 @@ __device__ __forceinline__ uint4 load16(const uint8_t *p) {
         const uint32_t *w = reinterpret_cast<const uint32_t *>(p);
         v = make_uint4(w[0], w[1], w[2], w[3]);
     } else {
-        const uint16_t *h = reinterpret_cast<const uint16_t *>(p);
-        v.x = h[0] | (static_cast<uint32_t>(h[1]) << 16);
-        v.y = h[2] | (static_cast<uint32_t>(h[3]) << 16);
-        v.z = h[4] | (static_cast<uint32_t>(h[5]) << 16);
-        v.w = h[6] | (static_cast<uint32_t>(h[7]) << 16);
+        // two bytes past a word boundary: five aligned words, each output word straddles two of them
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(p - 2);
+        const uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3], w4 = w[4];
+        v.x = __funnelshift_r(w0, w1, 16);
+        v.y = __funnelshift_r(w1, w2, 16);
+        v.z = __funnelshift_r(w2, w3, 16);
+        v.w = __funnelshift_r(w3, w4, 16);
     }
     return v;
 }
@@ -629,6 +631,10 @@ static int gemm_impl(const void *w, int fmt, int n, int k, const void *x, int x_
         return fail(B200Q_EUNSUPPORTED, "gemm: needs BF16 activations and K a multiple of 256 (use b200q_gemv)");
     if (reinterpret_cast<uintptr_t>(x) & 15) return fail(B200Q_EUNSUPPORTED, "gemm: activations must be 16-byte aligned");
     if (reinterpret_cast<uintptr_t>(w) & 1) return fail(B200Q_EUNSUPPORTED, "gemm: weights must be 2-byte aligned");
+    // the Q8_0 decoder reads whole aligned words around its 16-byte pieces; a base on a word boundary keeps the
+    // last word of the tensor inside it
+    if (fmt == B200Q_Q8_0 && (reinterpret_cast<uintptr_t>(w) & 3))
+        return fail(B200Q_EUNSUPPORTED, "gemm: Q8_0 weights must be 4-byte aligned");
     int *status = device_status_word();
     if (!status) return fail(B200Q_ECUDA, "gemm: no CUDA device");
     EncodeTiledFn encode = encode_tiled_fn();
