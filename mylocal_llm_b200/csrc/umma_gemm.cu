@@ -20,9 +20,19 @@
 //   * after the last slab the decoder warps read the accumulator back with tcgen05.ld (each
 //     warp its 32-lane quarter = 32 weight rows), convert and store y (a warp stores 32 consecutive
 //     outputs of one token per instruction).
-// The MMA-issuing lane never waits for its own commits, so the tensor core always has queued work;
-// with NTOK = 256 an MMA runs about 128 cycles against ~55 cycles to issue it, i.e. the kernel is
-// tensor-bound; with a few dozen tokens it is bound by that issue latency (~400 cycles per slab).
+// The MMA-issuing lane never waits for its own commits, so the tensor core always has queued work.
+// With a few dozen tokens the kernel is bound by the decoders' instruction issue (~170 warp
+// instructions per warp and slab, sixteen warps on four schedulers: ~0.35 us per slab); with 256-token
+// tiles the tensor core's time per slab is of the same size and the two overlap.
+//
+// Paired variant (PAIR, from about a thousand tokens on): CTAs 2p and 2p + 1 are a cluster of two on
+// neighbouring SMs and one tensor-core unit (cta_group::2, D = [256 weight rows x NTOK tokens]). Each
+// decodes its own 128 rows into its own shared memory and loads half of the token rows; the first CTA's
+// `full` barrier collects the decoder arrivals of both CTAs (the second CTA's come as remote arrivals)
+// and the bytes of both TMA halves (the second CTA's loads name the first CTA's barrier); the first CTA
+// issues the MMAs for both and commits to the `free` and `done` barriers of both; each CTA reads its own
+// 128 accumulator rows back. Tensor memory is allocated and freed by warp 0 of both CTAs, with a cluster
+// barrier after the allocation and before the release.
 // Weights are rounded to BF16, so results carry BF16-weight precision (relative 2^-9 per weight,
 // like the BF16 activations this path requires); the GEMV kernels keep their exact-product
 // arithmetic for m <= 16 and for FP32 activations.
@@ -33,6 +43,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <utility>
 #include <vector>
@@ -64,33 +75,108 @@ struct UmmaGemmArgs {
 // ---------------------------------------------------------------------------------------------
 // tcgen05 / TMA wrappers (sm_100a)
 // ---------------------------------------------------------------------------------------------
+// PAIR: the two CTAs of a cluster work as one tensor-core unit (cta_group::2). Tensor memory is then allocated
+// and freed by the same warp of both CTAs, with the same shared-memory slot for the address.
+template <bool PAIR>
 __device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
-                 : "memory");
+    if (PAIR)
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+                     "r"(cols)
+                     : "memory");
+    else
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+                     "r"(cols)
+                     : "memory");
 }
+template <bool PAIR>
 __device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    else asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 }
+template <bool PAIR>
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+    if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// Cluster helpers for the paired kernel.
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Every thread of both CTAs; orders shared-memory and barrier initialisation across the pair.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The shared::cluster address of this CTA's shared-memory address `addr` as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Waits of the MMA-issuing lane of a pair: the arrivals come from both CTAs.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t *bar, uint32_t parity, int *status, int code) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+            atomicExch(status, code);
+            return false;
+        }
+    }
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // D[tmem] (+)= A[smem desc] * B[smem desc]; `accumulate` = 0 overwrites D.
+// In a pair (issued by the first CTA only) D is [256 x N]: each CTA's tensor memory holds the 128 rows of its own A
+// operand; the N rows of B come half from each CTA's shared memory, at the same offsets.
+template <bool PAIR>
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                           uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if (PAIR)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
 }
-// The mbarrier receives one arrival when every tcgen05.mma issued so far by this thread has completed.
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
+// The mbarrier (a shared::cluster address: this CTA's or, in a pair, the partner's) receives one arrival when every
+// tcgen05.mma issued so far by this thread has completed.
+template <bool PAIR>
+__device__ __forceinline__ void umma_commit(uint32_t bar_addr) {
+    if (PAIR)
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr)
+                     : "memory");
+    else
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr)
+                     : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -112,6 +198,15 @@ __device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *m
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst_smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// The same load issued by a CTA of a pair: the completion bytes go to the mbarrier at `bar_addr`, a shared::cluster
+// address that may lie in the partner CTA (the one that issues the MMAs); the data lands in this CTA.
+__device__ __forceinline__ void tma_load_2d_pair(void *dst_smem, const CUtensorMap *map, int x, int y, uint32_t bar_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst_smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_addr), "r"(x), "r"(y)
         : "memory");
 }
 
@@ -289,6 +384,7 @@ struct DecoderRing {
     int *status;
     int stage_bytes, stages;
     int stage, wraps;         // stage of the next slab, and how many times the ring has wrapped
+    uint32_t remote_full;     // second CTA of a pair: shared::cluster address of the first CTA's full_bar[0]; else 0
 };
 
 // Decode slab SL of the groups in `grp` into the ring's next stage and publish it; false = gave up.
@@ -318,7 +414,10 @@ __device__ __forceinline__ bool decode_store_slab(const RawGroup (&grp)[PIECES],
     }
     fence_proxy_async();          // the decoded pieces must be visible to the tensor core's reads
     __syncwarp();
-    if (lane == 0) mbar_arrive(&ring.full_bar[ring.stage]);
+    if (lane == 0) {
+        if (ring.remote_full) mbar_arrive_cluster(ring.remote_full + 8u * ring.stage);
+        else mbar_arrive(&ring.full_bar[ring.stage]);
+    }
     if (++ring.stage == ring.stages) {
         ring.stage = 0;
         ++ring.wraps;
@@ -350,12 +449,12 @@ __device__ __forceinline__ bool decode_group(RawGroup (&grp)[PIECES], const uint
 // 16 issues the MMAs, one lane of warp 17 the TMA loads. A stage holds one decoded weight slab (16 KB) followed by
 // `mt` activation slabs of ntok rows x 128 bytes.
 // ---------------------------------------------------------------------------------------------
-constexpr int UG_MAX_STAGES = 4;
+constexpr int UG_MAX_STAGES = 6;
 constexpr int UG_DECODE_THREADS = 512;
 constexpr int UG_THREADS = UG_DECODE_THREADS + 64;
 constexpr int UG_PIECES = UG_BM * 4 / UG_DECODE_THREADS;      // 16-weight pieces per decoder thread and slab
 
-template <int FMT, bool SPLIT>
+template <int FMT, bool SPLIT, bool PAIR>
 __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_constant__ CUtensorMap xmap,
                                                                   const UmmaGemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
@@ -369,6 +468,10 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
     const int n0 = blockIdx.x * UG_BM;
     const int ntok = a.ntok, mt_count = a.mt;
     const int m0 = blockIdx.y * (mt_count * ntok);
+    // PAIR: CTAs 2p and 2p + 1 form a cluster and one [256 weight rows x ntok tokens] tensor-core tile. Each decodes
+    // its own 128 rows and stages half of the tokens; rank 0 issues the MMAs for both and owns the `full` barriers.
+    const uint32_t rank = PAIR ? cluster_cta_rank() : 0;
+    const int ntok_cta = PAIR ? ntok >> 1 : ntok;               // token rows this CTA stages per accumulator
     // split-K: this CTA walks the groups [group0, group0 + ngroups) of K
     // (SPLIT is a template argument: the one-CTA-per-tile kernel keeps the code it had before the split existed;
     // the same source with a run-time test measured 9 % slower at [8192 x 2048] x 512)
@@ -376,7 +479,7 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
     const int ngroups = SPLIT ? min(a.groups_per_split, a.k / 256 - group0) : a.k / 256;
     const int nslab = ngroups * (256 / UG_BK);
     const int S = a.stages;
-    const int x_bytes = ntok * UG_BK * 2;                       // one activation slab of one token tile
+    const int x_bytes = ntok_cta * UG_BK * 2;                   // this CTA's activation slab of one token tile
     const int stage_bytes = UG_W_BYTES + mt_count * x_bytes;
     const int acc_stride = (ntok + 31) & ~31;                   // TMEM columns between the accumulators
     uint32_t tmem_cols = 32;
@@ -384,7 +487,8 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
 
     if (tid == 0) {
         for (int s = 0; s < UG_MAX_STAGES; ++s) {
-            mbar_init(&full_bar[s], UG_DECODE_THREADS / 32 + 1);   // one arrival per decoder warp + the TMA lane's
+            // one arrival per decoder warp (of both CTAs in a pair) + the TMA lane's
+            mbar_init(&full_bar[s], (PAIR ? 2 : 1) * (UG_DECODE_THREADS / 32) + 1);
             mbar_init(&free_bar[s], 1);
         }
         mbar_init(&acc_done, 1);
@@ -392,11 +496,12 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
         fence_barrier_init();
     }
     if (warp == 0) {
-        tmem_alloc(&tmem_base_slot, tmem_cols);
-        tmem_relinquish();
+        tmem_alloc<PAIR>(&tmem_base_slot, tmem_cols);
+        tmem_relinquish<PAIR>();
     }
     tc_fence_before();
-    __syncthreads();
+    if (PAIR) cluster_sync_all();        // the partner's barriers are initialised before anything arrives on them
+    else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_d = tmem_base_slot;
 
@@ -420,7 +525,8 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
         // loop is unrolled by two so the sets are named statically and nothing is copied); one group
         // further ahead the lines are only asked into L2. Weights are read-only: no dependency wait.
         constexpr int GB = fmt_group_bytes(FMT);
-        DecoderRing ring{smem, free_bar, full_bar, &abort_flag, a.status, stage_bytes, S, 0, 0};
+        DecoderRing ring{smem, free_bar, full_bar, &abort_flag, a.status, stage_bytes, S, 0, 0,
+                         (PAIR && rank == 1) ? cluster_map(smem_u32(&full_bar[0]), 0) : 0u};
         RawGroup set0[UG_PIECES], set1[UG_PIECES];
 #pragma unroll
         for (int j = 0; j < UG_PIECES; ++j) {
@@ -442,14 +548,23 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
         // dependent instructions, and a runtime division per slab would cost more than the copies' issue)
         int issued = 0, s = 0, wraps = 0, xcol = group0 * 256;
         uint8_t *dst = smem + UG_W_BYTES;
+        const uint32_t full0 = PAIR ? cluster_map(smem_u32(&full_bar[0]), 0) : 0u;
+        const int row0 = m0 + static_cast<int>(rank) * ntok_cta;
         for (int i = 0; i < nslab && !abort_flag; ++i) {
             if (wraps > 0 && !mbar_wait_bounded(&free_bar[s], (wraps - 1) & 1, a.status, STATUS_UMMA_WAIT_MMA)) {
                 abort_flag = 1;
                 break;
             }
-            mbar_arrive_expect_tx(&full_bar[s], mt_count * x_bytes);
-            for (int mt = 0; mt < mt_count; ++mt)
-                tma_load_2d(dst + mt * x_bytes, &xmap, xcol, m0 + mt * ntok, &full_bar[s]);
+            if (PAIR) {
+                // the first CTA announces the bytes of both halves; either half may land first
+                if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * mt_count * x_bytes);
+                for (int mt = 0; mt < mt_count; ++mt)
+                    tma_load_2d_pair(dst + mt * x_bytes, &xmap, xcol, row0 + mt * ntok, full0 + 8u * s);
+            } else {
+                mbar_arrive_expect_tx(&full_bar[s], mt_count * x_bytes);
+                for (int mt = 0; mt < mt_count; ++mt)
+                    tma_load_2d(dst + mt * x_bytes, &xmap, xcol, m0 + mt * ntok, &full_bar[s]);
+            }
             issued = i + 1;
             xcol += UG_BK;
             dst += stage_bytes;
@@ -470,8 +585,9 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
         __syncwarp();
     } else if (warp == UG_DECODE_THREADS / 32) {
         // ---------------------------------------------------------------- MMA issue (one lane, as above)
-        if (lane == 0) {
-        const uint32_t idesc = umma_idesc_bf16(UG_BM, ntok);
+        if (lane == 0 && rank == 0) {
+        const uint32_t idesc = umma_idesc_bf16(PAIR ? 2 * UG_BM : UG_BM, ntok);
+        const uint32_t free0 = smem_u32(&free_bar[0]), free0_peer = PAIR ? cluster_map(free0, 1) : 0u;
         // descriptors advance by running additions (address field = bytes >> 4); see the note in the TMA lane
         const uint64_t w_desc0 = smem_desc_sw128(smem);
         const uint32_t stage_step = static_cast<uint32_t>(stage_bytes) >> 4, x_off = UG_W_BYTES >> 4,
@@ -488,13 +604,14 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
             for (int mt = 0; mt < mt_count; ++mt) {
                 const uint64_t x_desc = w_desc + x_off + mt * x_step;
                 const uint32_t d = tmem_d + mt * acc_stride;
-                umma_bf16(d, w_desc, x_desc, idesc, accumulate);              // 16 BF16 = 32 bytes per step:
-                umma_bf16(d, w_desc + 2, x_desc + 2, idesc, 1u);              // +2 in the address field
-                umma_bf16(d, w_desc + 4, x_desc + 4, idesc, 1u);
-                umma_bf16(d, w_desc + 6, x_desc + 6, idesc, 1u);
+                umma_bf16<PAIR>(d, w_desc, x_desc, idesc, accumulate);        // 16 BF16 = 32 bytes per step:
+                umma_bf16<PAIR>(d, w_desc + 2, x_desc + 2, idesc, 1u);        // +2 in the address field
+                umma_bf16<PAIR>(d, w_desc + 4, x_desc + 4, idesc, 1u);
+                umma_bf16<PAIR>(d, w_desc + 6, x_desc + 6, idesc, 1u);
             }
             accumulate = 1u;
-            umma_commit(&free_bar[s]);
+            umma_commit<PAIR>(free0 + 8u * s);                       // the stage is free again in this CTA ...
+            if (PAIR) umma_commit<PAIR>(free0_peer + 8u * s);        // ... and in the partner
             done_slabs = i + 1;
             w_desc += stage_step;
             if (++s == S) {
@@ -503,7 +620,10 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
                 w_desc = w_desc0;
             }
         }
-        if (done_slabs == nslab) umma_commit(&acc_done);
+        if (done_slabs == nslab) {
+            umma_commit<PAIR>(smem_u32(&acc_done));
+            if (PAIR) umma_commit<PAIR>(cluster_map(smem_u32(&acc_done), 1));
+        }
         }
         __syncwarp();
     }
@@ -544,8 +664,11 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
         }
     }
     tc_fence_before();
-    __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem_d, tmem_cols);
+    // a pair frees its tensor memory together, and neither CTA leaves while the other may still signal its barriers
+    // or read its activation half
+    if (PAIR) cluster_sync_all();
+    else __syncthreads();
+    if (warp == 0) tmem_dealloc<PAIR>(tmem_d, tmem_cols);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -571,6 +694,19 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 using GemmFn = void (*)(const CUtensorMap, const UmmaGemmArgs);
+
+template <bool SPLIT, bool PAIR>
+static GemmFn gemm_kernel_for(int fmt) {
+    return fmt == B200Q_Q8_0 ? umma_gemm_kernel<B200Q_Q8_0, SPLIT, PAIR>
+         : fmt == B200Q_Q4_K ? umma_gemm_kernel<B200Q_Q4_K, SPLIT, PAIR>
+         : fmt == B200Q_Q5_K ? umma_gemm_kernel<B200Q_Q5_K, SPLIT, PAIR>
+                             : umma_gemm_kernel<B200Q_Q6_K, SPLIT, PAIR>;
+}
+
+static int gemm_pair_mode() {          // read at every call, so a test can compare the kernels in one process
+    const char *v = std::getenv("B200Q_GEMM_PAIR");
+    return (v && v[0] == '0') ? 0 : (v && v[0] == '2') ? 2 : 1;
+}
 
 // y[t, col] = partial[0][t, col] + partial[1][t, col] + ... in ascending split order (deterministic), rounded once.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *partial, int splits, long long count, void *y,
@@ -647,14 +783,20 @@ static int gemm_impl(const void *w, int fmt, int n, int k, const void *x, int x_
     const int n_tiles = (n + UG_BM - 1) / UG_BM;
     const int mt = (token_tiles >= 2 && static_cast<long long>(n_tiles) * ((token_tiles + 1) / 2) >= sm_count()) ? 2 : 1;
     const int m_tiles = (token_tiles + mt - 1) / mt;
-    const int stage_bytes = UG_W_BYTES + mt * ntok * UG_BK * 2;
+    // From about a thousand tokens on, two CTAs on neighbouring SMs share a token tile (cta_group::2): each stages
+    // half of the activation rows, so the tensor core's operand reads and the TMA writes take less of each SM's
+    // shared-memory bandwidth ([8192 x 2048] x 2048: 70.9 -> 66.1 us; below that the one-CTA kernel is 1-4 %
+    // faster, its barriers being local). B200Q_GEMM_PAIR=0 keeps the one-CTA kernel, =2 pairs at every size.
+    const int pair_mode = gemm_pair_mode();
+    const bool pair = pair_mode == 2 || (pair_mode == 1 && token_tiles >= 4);
+    const int stage_bytes = UG_W_BYTES + mt * (pair ? ntok / 2 : ntok) * UG_BK * 2;
     int stages = (224 * 1024) / stage_bytes;
     if (stages > UG_MAX_STAGES) stages = UG_MAX_STAGES;
 
     CUtensorMap xmap;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(m)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
-    const cuuint32_t box[2] = {UG_BK, static_cast<cuuint32_t>(ntok)};
+    const cuuint32_t box[2] = {UG_BK, static_cast<cuuint32_t>(pair ? ntok / 2 : ntok)};
     const cuuint32_t elem_strides[2] = {1, 1};
     const CUresult res = encode(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(x), dims, strides, box,
                                 elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -672,13 +814,8 @@ static int gemm_impl(const void *w, int fmt, int n, int k, const void *x, int x_
         splits = 1;                                    // no room for partial results: one CTA walks all of K
     a.groups_per_split = (k / 256 + splits - 1) / splits;
     a.partial = splits > 1 ? static_cast<float *>(workspace) : nullptr;
-    GemmFn fn;
-    if (splits > 1)
-        fn = fmt == B200Q_Q8_0 ? umma_gemm_kernel<B200Q_Q8_0, true> : fmt == B200Q_Q4_K ? umma_gemm_kernel<B200Q_Q4_K, true>
-           : fmt == B200Q_Q5_K ? umma_gemm_kernel<B200Q_Q5_K, true> : umma_gemm_kernel<B200Q_Q6_K, true>;
-    else
-        fn = fmt == B200Q_Q8_0 ? umma_gemm_kernel<B200Q_Q8_0, false> : fmt == B200Q_Q4_K ? umma_gemm_kernel<B200Q_Q4_K, false>
-           : fmt == B200Q_Q5_K ? umma_gemm_kernel<B200Q_Q5_K, false> : umma_gemm_kernel<B200Q_Q6_K, false>;
+    const GemmFn fn = pair ? (splits > 1 ? gemm_kernel_for<true, true>(fmt) : gemm_kernel_for<false, true>(fmt))
+                           : (splits > 1 ? gemm_kernel_for<true, false>(fmt) : gemm_kernel_for<false, false>(fmt));
     const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024;
     // the opt-in to large dynamic shared memory is per function and device: done once each
     {
@@ -698,7 +835,12 @@ static int gemm_impl(const void *w, int fmt, int n, int k, const void *x, int x_
             opted.push_back(key);
         }
     }
-    launch_chained(fn, dim3(n_tiles, m_tiles, splits), dim3(UG_THREADS), smem, static_cast<cudaStream_t>(stream), xmap, a);
+    if (pair)      // an odd last weight-row tile gets a partner that decodes clamped rows and stores nothing
+        launch_chained_cluster(fn, dim3((n_tiles + 1) & ~1, m_tiles, splits), dim3(UG_THREADS), smem,
+                               static_cast<cudaStream_t>(stream), 2, xmap, a);
+    else
+        launch_chained(fn, dim3(n_tiles, m_tiles, splits), dim3(UG_THREADS), smem, static_cast<cudaStream_t>(stream), xmap,
+                       a);
     int rc = check_launch("gemm");
     if (rc || splits == 1) return rc;
     const long long count = static_cast<long long>(m) * n;

@@ -248,9 +248,8 @@ def quantized_linear(x, weight, *, block_k=512, cpu_packed_backend="reference", 
 
 
 # Tokens from which the tensor-core GEMM beats repeated GEMV passes (one pass serves 16 tokens): measured on
-# the [8192 x 2048] / [2048 x 8192] shapes, 17 for the 16-byte aligned formats, 48 for Q6_K / Q8_0, whose
-# 2-byte aligned blocks decode more slowly in the GEMM.
-GEMM_MIN_TOKENS = {"Q4_K": 17, "Q5_K": 17, "Q6_K": 48, "Q8_0": 48}
+# the [8192 x 2048] / [2048 x 8192] shapes, a second GEMV pass already costs more than the GEMM.
+GEMM_MIN_TOKENS = {"Q4_K": 17, "Q5_K": 17, "Q6_K": 17, "Q8_0": 17}
 
 
 def _use_gemm(weight, x, m, n, k, dt):
@@ -262,7 +261,7 @@ def _use_gemm(weight, x, m, n, k, dt):
     if (weight.quant_type in DEVICE_LAYOUTS or m < GEMM_MIN_TOKENS.get(weight.quant_type, 1 << 30)
             or os.environ.get("B200Q_GEMM", "1") == "0"):
         return False
-    if x.data_ptr() % 16 or weight.data.data_ptr() % 2:
+    if x.data_ptr() % 16 or weight.data.data_ptr() % (4 if weight.quant_type == "Q8_0" else 2):
         return False
     return bool(_lib.load().b200q_gemm_supported(_lib.FORMAT_ID[weight.quant_type], n, k, dt, m))
 

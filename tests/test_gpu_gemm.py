@@ -158,3 +158,34 @@ def test_gemm_split_k_is_used_by_the_linear_and_can_be_turned_off(cuda, monkeypa
     # the same products added in another order
     torch.testing.assert_close(split, whole, rtol=2e-5, atol=2e-5 * float(whole.abs().max()))
     assert _lib.load().b200q_gemm_workspace_bytes(2, 8192, 2048, 2, 512) == 0          # enough tiles: no split
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("n,k,m", [(64, 256, 17), (320, 512, 33), (192, 1024, 129), (1024, 2048, 300), (136, 256, 600),
+                                   (256, 512, 1100)])
+def test_gemm_cta_pairs(cuda, monkeypatch, fmt, n, k, m):
+    # two CTAs of a cluster as one tensor-core unit (each decodes 128 rows and stages half of the tokens), forced at
+    # every size: an odd number of weight-row tiles, token tiles cut by m, a single 8-token half, two accumulators
+    monkeypatch.setenv("B200Q_GEMM_PAIR", "2")
+    w = quantize(np.random.default_rng(n + k).normal(0, 0.02, (n, k)).astype(np.float32), fmt)
+    check(cuda, w, m, seed=m)
+    check(cuda, w, m, seed=m + 1, out_dtype=cuda.bfloat16)
+
+
+@pytest.mark.parametrize("n,k,m", [(256, 8192, 64), (200, 4352, 33)])
+def test_gemm_cta_pairs_with_split_k(cuda, monkeypatch, n, k, m):
+    monkeypatch.setenv("B200Q_GEMM_PAIR", "2")
+    w = quantize(np.random.default_rng(n + k).normal(0, 0.02, (n, k)).astype(np.float32), "Q6_K")
+    check(cuda, w, m, seed=m, split=True)
+
+
+def test_gemm_pairs_ctas_from_a_thousand_tokens_on(cuda, monkeypatch):
+    # the default: one-CTA tiles below four token tiles, pairs from there on; both kernels give the same product
+    torch = cuda
+    w = random_packed("Q4_K", (2048, 2048), seed=11, d=0.01, dmin=0.005)
+    check(torch, w, 1100, seed=3)
+    x = torch.randn((1100, 2048), device="cuda").to(torch.bfloat16)
+    paired = run_gemm(torch, w, x, torch.float32)
+    monkeypatch.setenv("B200Q_GEMM_PAIR", "0")
+    single = run_gemm(torch, w, x, torch.float32)
+    torch.testing.assert_close(paired, single, rtol=2e-5, atol=2e-5 * float(single.abs().max()))
