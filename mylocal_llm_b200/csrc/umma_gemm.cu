@@ -425,23 +425,26 @@ __device__ __forceinline__ bool decode_store_slab(const RawGroup (&grp)[PIECES],
     return true;
 }
 
-// The four slabs of group g from `grp`, then refill `grp` with group g + 2 and ask L2 for group g + 3.
+// The four slabs of group g from `cur`; after the first of them (when cur's bytes have arrived and no other
+// load of this thread is in flight) the packed bytes of group g + 1 are requested into `nxt`, and L2 is asked
+// for group g + 3. The request sits after a slab and not at the end of the previous group on purpose: the
+// hardware waits for "all loads issued so far under this dependency counter", and with the loads of both
+// register sets in flight at the first use of one of them a decoder waited out the full memory latency of
+// the set it had just requested (2.6 stalled warps per issue at [8192 x 2048] x 512).
 template <int FMT, int PIECES>
-__device__ __forceinline__ bool decode_group(RawGroup (&grp)[PIECES], const uint8_t *const (&row_ptr)[PIECES],
-                                             const int (&prow)[PIECES], const int (&pquart)[PIECES], int g, int ngroups,
-                                             DecoderRing &ring, int lane) {
+__device__ __forceinline__ bool decode_group(const RawGroup (&cur)[PIECES], RawGroup (&nxt)[PIECES],
+                                             const uint8_t *const (&row_ptr)[PIECES], const int (&prow)[PIECES],
+                                             const int (&pquart)[PIECES], int g, int ngroups, DecoderRing &ring, int lane) {
     constexpr int GB = fmt_group_bytes(FMT);
-    const bool ok = decode_store_slab<FMT, 0, PIECES>(grp, prow, pquart, ring, lane) &&
-                    decode_store_slab<FMT, 1, PIECES>(grp, prow, pquart, ring, lane) &&
-                    decode_store_slab<FMT, 2, PIECES>(grp, prow, pquart, ring, lane) &&
-                    decode_store_slab<FMT, 3, PIECES>(grp, prow, pquart, ring, lane);
-    if (!ok) return false;
+    if (!decode_store_slab<FMT, 0, PIECES>(cur, prow, pquart, ring, lane)) return false;
 #pragma unroll
     for (int j = 0; j < PIECES; ++j) {
-        fetch_group<FMT>(row_ptr[j] + static_cast<size_t>(min(g + 2, ngroups - 1)) * GB, pquart[j], grp[j]);
+        fetch_group<FMT>(row_ptr[j] + static_cast<size_t>(min(g + 1, ngroups - 1)) * GB, pquart[j], nxt[j]);
         if (g + 3 < ngroups) asm volatile("prefetch.global.L2 [%0];" ::"l"(row_ptr[j] + static_cast<size_t>(g + 3) * GB));
     }
-    return true;
+    return decode_store_slab<FMT, 1, PIECES>(cur, prow, pquart, ring, lane) &&
+           decode_store_slab<FMT, 2, PIECES>(cur, prow, pquart, ring, lane) &&
+           decode_store_slab<FMT, 3, PIECES>(cur, prow, pquart, ring, lane);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -521,9 +524,10 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
             const int wrow = min(n0 + prow[j], a.n - 1);      // rows past the end decode the last row; never stored
             row_ptr[j] = a.w + static_cast<size_t>(wrow) * a.row_bytes + static_cast<size_t>(group0) * fmt_group_bytes(FMT);
         }
-        // Two register sets hold the packed bytes of the current and the next 256-position group (the
-        // loop is unrolled by two so the sets are named statically and nothing is copied); one group
-        // further ahead the lines are only asked into L2. Weights are read-only: no dependency wait.
+        // Two register sets take turns: one holds the group being decoded, the other receives the next group's
+        // packed bytes (requested three slabs before their first use; two groups further ahead the lines are
+        // only asked into L2). Weights are read-only: no dependency wait. The loop is unrolled by two so the
+        // sets are named statically and nothing is copied.
         constexpr int GB = fmt_group_bytes(FMT);
         DecoderRing ring{smem, free_bar, full_bar, &abort_flag, a.status, stage_bytes, S, 0, 0,
                          (PAIR && rank == 1) ? cluster_map(smem_u32(&full_bar[0]), 0) : 0u};
@@ -531,11 +535,12 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
 #pragma unroll
         for (int j = 0; j < UG_PIECES; ++j) {
             fetch_group<FMT>(row_ptr[j], pquart[j], set0[j]);
-            fetch_group<FMT>(row_ptr[j] + static_cast<size_t>(min(1, ngroups - 1)) * GB, pquart[j], set1[j]);
+            for (int ahead = 1; ahead <= 2; ++ahead)
+                if (ahead < ngroups) asm volatile("prefetch.global.L2 [%0];" ::"l"(row_ptr[j] + static_cast<size_t>(ahead) * GB));
         }
         for (int g = 0; g < ngroups; g += 2) {
-            if (!decode_group<FMT, UG_PIECES>(set0, row_ptr, prow, pquart, g, ngroups, ring, lane)) break;
-            if (g + 1 < ngroups && !decode_group<FMT, UG_PIECES>(set1, row_ptr, prow, pquart, g + 1, ngroups, ring, lane))
+            if (!decode_group<FMT, UG_PIECES>(set0, set1, row_ptr, prow, pquart, g, ngroups, ring, lane)) break;
+            if (g + 1 < ngroups && !decode_group<FMT, UG_PIECES>(set1, set0, row_ptr, prow, pquart, g + 1, ngroups, ring, lane))
                 break;
         }
     } else if (warp == UG_DECODE_THREADS / 32 + 1) {
