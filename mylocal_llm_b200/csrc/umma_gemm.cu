@@ -99,6 +99,21 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
     else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 
+// True in exactly one lane of a converged warp. The warps that issue MMAs and TMA loads run their loops with all 32
+// lanes and elect the issuer per instruction group: a loop kept inside an `if (lane == 0)` branch is divergent code
+// to the compiler, which then feeds every tensor-core / TMA instruction (they take their operands from the warp-wide
+// uniform registers) through per-thread registers - the issuing lane spent ~0.55 us per slab that way, whatever
+// the tile size.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // Cluster helpers for the paired kernel.
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
     uint32_t r;
@@ -545,9 +560,8 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
         }
     } else if (warp == UG_DECODE_THREADS / 32 + 1) {
         // ---------------------------------------------------------------- TMA loads of the activation slabs
-        // (one lane works; the others park at the __syncwarp below - were they to run on to the spin-wait of
-        // the epilogue, their polling would take the issue slots of the working lane of their own warp)
-        if (lane == 0) {
+        // (the whole warp walks the loop, one elected lane issues)
+        {
         chain_wait();                 // the activations come from the preceding kernel on the stream
         // (stage index and barrier phase are kept as running counters: this lane's loop is a chain of
         // dependent instructions, and a runtime division per slab would cost more than the copies' issue)
@@ -555,21 +569,27 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
         uint8_t *dst = smem + UG_W_BYTES;
         const uint32_t full0 = PAIR ? cluster_map(smem_u32(&full_bar[0]), 0) : 0u;
         const int row0 = m0 + static_cast<int>(rank) * ntok_cta;
-        for (int i = 0; i < nslab && !abort_flag; ++i) {
-            if (wraps > 0 && !mbar_wait_bounded(&free_bar[s], (wraps - 1) & 1, a.status, STATUS_UMMA_WAIT_MMA)) {
+        for (int i = 0; i < nslab; ++i) {
+            // (votes keep the 32 lanes on one path: the elections below name all of them)
+            if (__any_sync(0xffffffffu, abort_flag != 0)) break;
+            if (wraps > 0 && !__all_sync(0xffffffffu, mbar_wait_bounded(&free_bar[s], (wraps - 1) & 1, a.status,
+                                                                        STATUS_UMMA_WAIT_MMA))) {
                 abort_flag = 1;
                 break;
             }
-            if (PAIR) {
-                // the first CTA announces the bytes of both halves; either half may land first
-                if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * mt_count * x_bytes);
-                for (int mt = 0; mt < mt_count; ++mt)
-                    tma_load_2d_pair(dst + mt * x_bytes, &xmap, xcol, row0 + mt * ntok, full0 + 8u * s);
-            } else {
-                mbar_arrive_expect_tx(&full_bar[s], mt_count * x_bytes);
-                for (int mt = 0; mt < mt_count; ++mt)
-                    tma_load_2d(dst + mt * x_bytes, &xmap, xcol, m0 + mt * ntok, &full_bar[s]);
+            if (elect_one()) {
+                if (PAIR) {
+                    // the first CTA announces the bytes of both halves; either half may land first
+                    if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * mt_count * x_bytes);
+                    for (int mt = 0; mt < mt_count; ++mt)
+                        tma_load_2d_pair(dst + mt * x_bytes, &xmap, xcol, row0 + mt * ntok, full0 + 8u * s);
+                } else {
+                    mbar_arrive_expect_tx(&full_bar[s], mt_count * x_bytes);
+                    for (int mt = 0; mt < mt_count; ++mt)
+                        tma_load_2d(dst + mt * x_bytes, &xmap, xcol, m0 + mt * ntok, &full_bar[s]);
+                }
             }
+            __syncwarp();
             issued = i + 1;
             xcol += UG_BK;
             dst += stage_bytes;
@@ -589,8 +609,8 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
         }
         __syncwarp();
     } else if (warp == UG_DECODE_THREADS / 32) {
-        // ---------------------------------------------------------------- MMA issue (one lane, as above)
-        if (lane == 0 && rank == 0) {
+        // ---------------------------------------------------------------- MMA issue (whole warp, elected lane)
+        if (rank == 0) {
         const uint32_t idesc = umma_idesc_bf16(PAIR ? 2 * UG_BM : UG_BM, ntok);
         const uint32_t free0 = smem_u32(&free_bar[0]), free0_peer = PAIR ? cluster_map(free0, 1) : 0u;
         // descriptors advance by running additions (address field = bytes >> 4); see the note in the TMA lane
@@ -600,23 +620,27 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
         uint64_t w_desc = w_desc0;
         uint32_t accumulate = 0;
         int done_slabs = 0, s = 0, phase = 0;
-        for (int i = 0; i < nslab && !abort_flag; ++i) {
-            if (!mbar_wait_bounded(&full_bar[s], phase, a.status, STATUS_UMMA_WAIT_TMA)) {
+        for (int i = 0; i < nslab; ++i) {
+            if (__any_sync(0xffffffffu, abort_flag != 0)) break;
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(&full_bar[s], phase, a.status, STATUS_UMMA_WAIT_TMA))) {
                 abort_flag = 1;
                 break;
             }
             tc_fence_after();
-            for (int mt = 0; mt < mt_count; ++mt) {
-                const uint64_t x_desc = w_desc + x_off + mt * x_step;
-                const uint32_t d = tmem_d + mt * acc_stride;
-                umma_bf16<PAIR>(d, w_desc, x_desc, idesc, accumulate);        // 16 BF16 = 32 bytes per step:
-                umma_bf16<PAIR>(d, w_desc + 2, x_desc + 2, idesc, 1u);        // +2 in the address field
-                umma_bf16<PAIR>(d, w_desc + 4, x_desc + 4, idesc, 1u);
-                umma_bf16<PAIR>(d, w_desc + 6, x_desc + 6, idesc, 1u);
+            if (elect_one()) {
+                for (int mt = 0; mt < mt_count; ++mt) {
+                    const uint64_t x_desc = w_desc + x_off + mt * x_step;
+                    const uint32_t d = tmem_d + mt * acc_stride;
+                    umma_bf16<PAIR>(d, w_desc, x_desc, idesc, accumulate);        // 16 BF16 = 32 bytes per step:
+                    umma_bf16<PAIR>(d, w_desc + 2, x_desc + 2, idesc, 1u);        // +2 in the address field
+                    umma_bf16<PAIR>(d, w_desc + 4, x_desc + 4, idesc, 1u);
+                    umma_bf16<PAIR>(d, w_desc + 6, x_desc + 6, idesc, 1u);
+                }
+                umma_commit<PAIR>(free0 + 8u * s);                       // the stage is free again in this CTA ...
+                if (PAIR) umma_commit<PAIR>(free0_peer + 8u * s);        // ... and in the partner
             }
+            __syncwarp();
             accumulate = 1u;
-            umma_commit<PAIR>(free0 + 8u * s);                       // the stage is free again in this CTA ...
-            if (PAIR) umma_commit<PAIR>(free0_peer + 8u * s);        // ... and in the partner
             done_slabs = i + 1;
             w_desc += stage_step;
             if (++s == S) {
@@ -625,7 +649,7 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
                 w_desc = w_desc0;
             }
         }
-        if (done_slabs == nslab) {
+        if (done_slabs == nslab && elect_one()) {
             umma_commit<PAIR>(smem_u32(&acc_done));
             if (PAIR) umma_commit<PAIR>(cluster_map(smem_u32(&acc_done), 1));
         }
@@ -797,6 +821,7 @@ static int gemm_impl(const void *w, int fmt, int n, int k, const void *x, int x_
     const int stage_bytes = UG_W_BYTES + mt * (pair ? ntok / 2 : ntok) * UG_BK * 2;
     int stages = (224 * 1024) / stage_bytes;
     if (stages > UG_MAX_STAGES) stages = UG_MAX_STAGES;
+    if (const char *v = std::getenv("B200Q_TMP_STAGES")) stages = std::min(stages, std::atoi(v));
 
     CUtensorMap xmap;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(m)};
