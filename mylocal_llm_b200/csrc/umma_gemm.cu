@@ -402,15 +402,20 @@ struct DecoderRing {
     uint32_t remote_full;     // second CTA of a pair: shared::cluster address of the first CTA's full_bar[0]; else 0
 };
 
-// Decode slab SL of the groups in `grp` into the ring's next stage and publish it; false = gave up.
-template <int FMT, int SL, int PIECES>
-__device__ __forceinline__ bool decode_store_slab(const RawGroup (&grp)[PIECES], const int (&prow)[PIECES],
-                                                  const int (&pquart)[PIECES], DecoderRing &ring, int lane) {
-    if (ring.wraps > 0 &&
-        !mbar_wait_bounded(&ring.free_bar[ring.stage], (ring.wraps - 1) & 1, ring.status, STATUS_UMMA_WAIT_MMA))
-        *ring.abort_flag = 1;
+// Waits until the tensor core has released stage `stage` for its `wraps`-th reuse. The CTA's abort flag is read
+// only when the stage is not free at once; false = this thread or another one gave up.
+__device__ __forceinline__ bool ring_wait_free(const DecoderRing &ring, int stage, int wraps) {
+    if (wraps == 0 || mbar_try_wait(&ring.free_bar[stage], (wraps - 1) & 1)) return true;
     if (*ring.abort_flag) return false;
-    uint8_t *stage = ring.base + static_cast<size_t>(ring.stage) * ring.stage_bytes;
+    if (mbar_wait_bounded(&ring.free_bar[stage], (wraps - 1) & 1, ring.status, STATUS_UMMA_WAIT_MMA)) return true;
+    *ring.abort_flag = 1;
+    return false;
+}
+
+// The pieces of slab SL of the groups in `grp`, decoded and stored into `stage` (a 16 KB weight slab of the ring).
+template <int FMT, int SL, int PIECES>
+__device__ __forceinline__ void decode_into(const RawGroup (&grp)[PIECES], const int (&prow)[PIECES],
+                                            const int (&pquart)[PIECES], uint8_t *stage) {
 #pragma unroll
     for (int j = 0; j < PIECES; ++j) {
         float wv[16];
@@ -427,20 +432,44 @@ __device__ __forceinline__ bool decode_store_slab(const RawGroup (&grp)[PIECES],
             *reinterpret_cast<uint4 *>(dst_row + chunk * 16) = v;
         }
     }
+}
+
+// Decode slabs SL and SL + 1 of the groups in `grp` into the ring's next two stages and publish both; false =
+// gave up. Two slabs per round: the per-round chain of a warp (wait, scale decode, proxy fence, warp barrier,
+// arrival) is paid once for 32 weights per thread, and the two slabs' arithmetic interleaves.
+template <int FMT, int SL, int PIECES>
+__device__ __forceinline__ bool decode_store_two(const RawGroup (&grp)[PIECES], const int (&prow)[PIECES],
+                                                 const int (&pquart)[PIECES], DecoderRing &ring, int lane) {
+    const int s0 = ring.stage, w0 = ring.wraps;
+    int s1 = s0 + 1, w1 = w0;
+    if (s1 == ring.stages) {
+        s1 = 0;
+        ++w1;
+    }
+    if (!ring_wait_free(ring, s0, w0) || !ring_wait_free(ring, s1, w1)) return false;
+    decode_into<FMT, SL, PIECES>(grp, prow, pquart, ring.base + static_cast<size_t>(s0) * ring.stage_bytes);
+    decode_into<FMT, SL + 1, PIECES>(grp, prow, pquart, ring.base + static_cast<size_t>(s1) * ring.stage_bytes);
     fence_proxy_async();          // the decoded pieces must be visible to the tensor core's reads
     __syncwarp();
     if (lane == 0) {
-        if (ring.remote_full) mbar_arrive_cluster(ring.remote_full + 8u * ring.stage);
-        else mbar_arrive(&ring.full_bar[ring.stage]);
+        if (ring.remote_full) {
+            mbar_arrive_cluster(ring.remote_full + 8u * s0);
+            mbar_arrive_cluster(ring.remote_full + 8u * s1);
+        } else {
+            mbar_arrive(&ring.full_bar[s0]);
+            mbar_arrive(&ring.full_bar[s1]);
+        }
     }
-    if (++ring.stage == ring.stages) {
+    ring.stage = s1 + 1;
+    ring.wraps = w1;
+    if (ring.stage == ring.stages) {
         ring.stage = 0;
         ++ring.wraps;
     }
     return true;
 }
 
-// The four slabs of group g from `cur`; after the first of them (when cur's bytes have arrived and no other
+// The four slabs of group g from `cur`; after the first two of them (when cur's bytes have arrived and no other
 // load of this thread is in flight) the packed bytes of group g + 1 are requested into `nxt`, and L2 is asked
 // for group g + 3. The request sits after a slab and not at the end of the previous group on purpose: the
 // hardware waits for "all loads issued so far under this dependency counter", and with the loads of both
@@ -451,15 +480,13 @@ __device__ __forceinline__ bool decode_group(const RawGroup (&cur)[PIECES], RawG
                                              const uint8_t *const (&row_ptr)[PIECES], const int (&prow)[PIECES],
                                              const int (&pquart)[PIECES], int g, int ngroups, DecoderRing &ring, int lane) {
     constexpr int GB = fmt_group_bytes(FMT);
-    if (!decode_store_slab<FMT, 0, PIECES>(cur, prow, pquart, ring, lane)) return false;
+    if (!decode_store_two<FMT, 0, PIECES>(cur, prow, pquart, ring, lane)) return false;
 #pragma unroll
     for (int j = 0; j < PIECES; ++j) {
         fetch_group<FMT>(row_ptr[j] + static_cast<size_t>(min(g + 1, ngroups - 1)) * GB, pquart[j], nxt[j]);
         if (g + 3 < ngroups) asm volatile("prefetch.global.L2 [%0];" ::"l"(row_ptr[j] + static_cast<size_t>(g + 3) * GB));
     }
-    return decode_store_slab<FMT, 1, PIECES>(cur, prow, pquart, ring, lane) &&
-           decode_store_slab<FMT, 2, PIECES>(cur, prow, pquart, ring, lane) &&
-           decode_store_slab<FMT, 3, PIECES>(cur, prow, pquart, ring, lane);
+    return decode_store_two<FMT, 2, PIECES>(cur, prow, pquart, ring, lane);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -540,7 +567,7 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
             row_ptr[j] = a.w + static_cast<size_t>(wrow) * a.row_bytes + static_cast<size_t>(group0) * fmt_group_bytes(FMT);
         }
         // Two register sets take turns: one holds the group being decoded, the other receives the next group's
-        // packed bytes (requested three slabs before their first use; two groups further ahead the lines are
+        // packed bytes (requested two slabs before their first use; two groups further ahead the lines are
         // only asked into L2). Weights are read-only: no dependency wait. The loop is unrolled by two so the
         // sets are named statically and nothing is copied.
         constexpr int GB = fmt_group_bytes(FMT);
