@@ -286,12 +286,21 @@ template <int FMT>
 __device__ __forceinline__ void fetch_group(const uint8_t *blk, int quart, RawGroup &r) {
     if constexpr (FMT == B200Q_Q8_0) {
         // slab SL, quarter quart -> block 2*SL + (quart >> 1), half quart & 1 of its 32 codes
+        // The codes start 2 bytes (even blocks) or 0 bytes (odd blocks) past a word boundary: every lane reads five
+        // aligned words from the boundary at or below its piece and shifts by its own amount, so the lanes of a
+        // warp (which hold blocks of both kinds) stay on one path. The fifth word is needed only by the shifted
+        // lanes; the others do not read it (it may lie past the end of the tensor).
         const uint8_t *b = blk + (quart >> 1) * 34;
         uint32_t d[4];
 #pragma unroll
         for (int sl = 0; sl < 4; ++sl) {
             d[sl] = *reinterpret_cast<const uint16_t *>(b + 68 * sl);
-            r.q[sl] = load16(b + 68 * sl + 2 + 16 * (quart & 1));
+            const uint8_t *p = b + 68 * sl + 2 + 16 * (quart & 1);
+            const uint32_t shift = (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p)) & 2u) * 8u;   // 0 or 16 bits
+            const uint32_t *w = reinterpret_cast<const uint32_t *>(p - (shift >> 3));
+            const uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3], w4 = shift ? w[4] : 0u;
+            r.q[sl] = make_uint4(__funnelshift_r(w0, w1, shift), __funnelshift_r(w1, w2, shift),
+                                 __funnelshift_r(w2, w3, shift), __funnelshift_r(w3, w4, shift));
         }
         r.hdr.x = d[0] | (d[1] << 16);
         r.hdr.y = d[2] | (d[3] << 16);
@@ -690,30 +699,66 @@ __global__ void __launch_bounds__(UG_THREADS, 1) umma_gemm_kernel(const __grid_c
         abort_flag = 1;
         ok = false;
     }
+    ok = __syncthreads_and(ok) != 0;      // one answer for the CTA: the groups below meet at named barriers
     if (ok && warp < UG_DECODE_THREADS / 32) {
         tc_fence_after();
         chain_wait();        // y may still be read by what precedes this kernel on the stream
         // warp w reads TMEM lanes 32*(w%4)..+31 = 32 weight rows; the 32-token chunks of every accumulator
-        // are dealt round-robin to the four groups of four warps
-        const int quarter = warp & 3;
-        const int row = n0 + 32 * quarter + lane;
+        // are dealt round-robin to the four groups of four warps. A group turns its chunk [128 rows x 32 tokens]
+        // into the output's layout in shared memory (the ring is idle by now: every MMA has completed) and stores
+        // it in 16-byte pieces, a warp instruction covering whole 128-byte lines of two (BF16) tokens; outputs
+        // whose rows are not 16-byte aligned take the direct path, 32 two- or four-byte stores per thread.
+        const int quarter = warp & 3, group = warp >> 2;
+        const int row_local = 32 * quarter + lane;
+        const int row = n0 + row_local;
         const int nchunks = (ntok + 31) >> 5;
+        uint8_t *out = SPLIT ? reinterpret_cast<uint8_t *>(a.partial + static_cast<size_t>(blockIdx.z) * a.m * a.n)
+                             : static_cast<uint8_t *>(a.y);
+        const int out_dtype = SPLIT ? B200Q_F32 : a.y_dtype;
+        const int esize = out_dtype == B200Q_F32 ? 4 : 2;
+        const bool staged = a.n % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+        uint8_t *tile = smem + group * (32 * UG_BM * 4);          // 16 KB per group
         for (int mt = 0; mt < mt_count; ++mt) {
             const int tile_t0 = m0 + mt * ntok;
             if (tile_t0 >= a.m) break;                           // whole token tile beyond m (uniform in the CTA)
-            for (int c = warp >> 2; c < nchunks; c += UG_DECODE_THREADS / 128) {
+            for (int c = group; c < nchunks; c += UG_DECODE_THREADS / 128) {
                 uint32_t r[32];
                 tmem_ld32(tmem_d + (static_cast<uint32_t>(32 * quarter) << 16) + mt * acc_stride + 32 * c, r);
                 tmem_ld_wait();
-                if (row < a.n) {
+                if (staged) {
+                    if (esize == 4) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) reinterpret_cast<uint32_t *>(tile)[j * UG_BM + row_local] = r[j];
+                    } else if (out_dtype == B200Q_BF16) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            reinterpret_cast<uint16_t *>(tile)[j * UG_BM + row_local] =
+                                __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[j])));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            reinterpret_cast<uint16_t *>(tile)[j * UG_BM + row_local] =
+                                __half_as_ushort(__float2half_rn(__uint_as_float(r[j])));
+                    }
+                    named_barrier_sync(1 + group, 128);
+                    const int pieces_per_token = 8 * esize;                  // 16-byte pieces of a 128-row line
+                    const int piece_shift = esize == 4 ? 5 : 4;
+                    for (int p = row_local; p < 32 * pieces_per_token; p += 128) {
+                        const int j = p >> piece_shift, piece = p & (pieces_per_token - 1);
+                        const int t = tile_t0 + 32 * c + j;
+                        const int col = n0 + piece * (16 / esize);
+                        if (32 * c + j < ntok && t < a.m && col < a.n) {
+                            const uint4 v = *reinterpret_cast<const uint4 *>(tile + static_cast<size_t>(j) * UG_BM * esize +
+                                                                             piece * 16);
+                            *reinterpret_cast<uint4 *>(out + (static_cast<size_t>(t) * a.n + col) * esize) = v;
+                        }
+                    }
+                    named_barrier_sync(1 + group, 128);                      // the tile is rewritten by the next chunk
+                } else if (row < a.n) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int t = tile_t0 + 32 * c + j;
-                        if (32 * c + j < ntok && t < a.m) {
-                            if (SPLIT)
-                                a.partial[(static_cast<size_t>(blockIdx.z) * a.m + t) * a.n + row] = __uint_as_float(r[j]);
-                            else store_out(a.y, a.y_dtype, static_cast<size_t>(t) * a.n + row, r[j]);
-                        }
+                        if (32 * c + j < ntok && t < a.m) store_out(out, out_dtype, static_cast<size_t>(t) * a.n + row, r[j]);
                     }
                 }
             }

@@ -74,10 +74,13 @@ def check(torch, w, m, seed, out_dtype=None, split=False):
 
 @pytest.mark.parametrize("fmt", FORMATS)
 @pytest.mark.parametrize("n,k,m", [(64, 256, 17), (128, 256, 128), (64, 512, 33), (192, 1024, 129), (80, 256, 40),
-                                   (1024, 2048, 300), (192, 512, 600), (136, 256, 257)])
+                                   (1024, 2048, 300), (192, 512, 600), (136, 256, 257), (100, 256, 40)])
 def test_gemm_small_shapes_all_formats(cuda, fmt, n, k, m):
+    # (100 rows: output rows that are not 16-byte aligned leave the staged epilogue for the direct stores)
     w = quantize(np.random.default_rng(n + k).normal(0, 0.02, (n, k)).astype(np.float32), fmt)
     check(cuda, w, m, seed=m)
+    if n == 100:
+        check(cuda, w, m, seed=m, out_dtype=cuda.bfloat16)
 
 
 @pytest.mark.parametrize("fmt", FORMATS)
