@@ -76,6 +76,8 @@ WORKLOADS = {
     "gemm_q6k_8192x2048_m512": ("Q6_K", 8192, 2048, 512, "bfloat16"),
     "gemm_q4k_8192x2048_m32": ("Q4_K", 8192, 2048, 32, "bfloat16"),
     "gemm_q4k_8192x2048_m2048": ("Q4_K", 8192, 2048, 2048, "bfloat16"),
+    "gemm_q8_0_8192x2048_m512": ("Q8_0", 8192, 2048, 512, "bfloat16"),
+    "gemm_q8_0_8192x2048_m2048": ("Q8_0", 8192, 2048, 2048, "bfloat16"),
 }
 # name: (layers, tokens per step, chained)  - the packed MoE layer of the baseline's fourth configuration
 # (hidden 2048, 512 experts of width 512, top-10, shared expert, Q4_K gate/up + Q6_K down); "stack" = the

@@ -893,7 +893,6 @@ static int gemm_impl(const void *w, int fmt, int n, int k, const void *x, int x_
     const int stage_bytes = UG_W_BYTES + mt * (pair ? ntok / 2 : ntok) * UG_BK * 2;
     int stages = (224 * 1024) / stage_bytes;
     if (stages > UG_MAX_STAGES) stages = UG_MAX_STAGES;
-    if (const char *v = std::getenv("B200Q_TMP_STAGES")) stages = std::min(stages, std::atoi(v));
 
     CUtensorMap xmap;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(m)};
