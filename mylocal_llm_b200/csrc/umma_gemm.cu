@@ -329,21 +329,51 @@ __device__ __forceinline__ void fetch_group(const uint8_t *blk, int quart, RawGr
     }
 }
 
-// Byte j of `codes` as a float, exactly: the byte becomes the low mantissa byte of 2^23.
-__device__ __forceinline__ float byte_to_float(uint32_t codes, int j, float bias) {
-    return __uint_as_float(__byte_perm(codes, 0x4B000000u, 0x7650u | static_cast<uint32_t>(j))) - bias;
+// Packed FP32 pairs (sm_100: one instruction for two IEEE operations, each rounded as the scalar one): the
+// decoders are bound by the number of instructions they issue, and these halve their floating-point part.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
 }
 
+// Bytes j and j + 1 of `codes` as floats minus `bias` (each byte becomes the low mantissa byte of 2^23: exact).
+__device__ __forceinline__ uint64_t bytes_to_float2(uint32_t codes, int j, uint64_t neg_bias2) {
+    const float lo = __uint_as_float(__byte_perm(codes, 0x4B000000u, 0x7650u | static_cast<uint32_t>(j)));
+    const float hi = __uint_as_float(__byte_perm(codes, 0x4B000000u, 0x7650u | static_cast<uint32_t>(j + 1)));
+    return add2(pack2(lo, hi), neg_bias2);
+}
+
+// out[p] = weights 2p, 2p + 1 of the piece as a packed FP32 pair.
 template <int FMT, int SL>
-__device__ __forceinline__ void decode_slab(const RawGroup &r, int quart, float (&out)[16]) {
+__device__ __forceinline__ void decode_slab(const RawGroup &r, int quart, uint64_t (&out)[8]) {
     const uint32_t qw[4] = {r.q[SL].x, r.q[SL].y, r.q[SL].z, r.q[SL].w};
     if constexpr (FMT == B200Q_Q8_0) {
         const float d = half_bits_to_float(((SL < 2 ? r.hdr.x : r.hdr.y) >> (16 * (SL & 1))) & 0xffffu);
+        const uint64_t d2 = pack2(d, d), nb = pack2(-8388736.0f, -8388736.0f);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint32_t u = qw[i] ^ 0x80808080u;              // code + 128 in every byte
-#pragma unroll
-            for (int j = 0; j < 4; ++j) out[4 * i + j] = d * byte_to_float(u, j, 8388736.0f);
+            out[2 * i] = mul2(d2, bytes_to_float2(u, 0, nb));
+            out[2 * i + 1] = mul2(d2, bytes_to_float2(u, 2, nb));
         }
         return;
     }
@@ -364,12 +394,13 @@ __device__ __forceinline__ void decode_slab(const RawGroup &r, int quart, float 
         const float scale = d * static_cast<float>(sc), neg_min = -(dmin * static_cast<float>(mn));
         const uint32_t hw[4] = {r.h[0].x, r.h[0].y, r.h[0].z, r.h[0].w};
         const int shift = 4 * hi_sub, g = 2 * SL + hi_sub;
+        const uint64_t scale2 = pack2(scale, scale), min2 = pack2(neg_min, neg_min), nb = pack2(-8388608.0f, -8388608.0f);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             uint32_t code = (qw[i] >> shift) & 0x0f0f0f0fu;
             if (FMT == B200Q_Q5_K) code |= ((hw[i] >> g) & 0x01010101u) << 4;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) out[4 * i + j] = __fmaf_rn(scale, byte_to_float(code, j, 8388608.0f), neg_min);
+            out[2 * i] = fma2(scale2, bytes_to_float2(code, 0, nb), min2);
+            out[2 * i + 1] = fma2(scale2, bytes_to_float2(code, 2, nb), min2);
         }
         return;
     }
@@ -379,15 +410,18 @@ __device__ __forceinline__ void decode_slab(const RawGroup &r, int quart, float 
     const uint4 hv = r.h[SL >> 1];
     const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
     const int lo_shift = 4 * (SL & 1), hi_shift = 2 * (2 * (SL & 1) + (quart >> 1));
+    const uint64_t scale2 = pack2(scale, scale), nb = pack2(-8388640.0f, -8388640.0f);          // code - 32
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint32_t code = ((qw[i] >> lo_shift) & 0x0f0f0f0fu) | (((hw[i] >> hi_shift) & 0x03030303u) << 4);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) out[4 * i + j] = scale * byte_to_float(code, j, 8388640.0f);   // code - 32
+        out[2 * i] = mul2(scale2, bytes_to_float2(code, 0, nb));
+        out[2 * i + 1] = mul2(scale2, bytes_to_float2(code, 2, nb));
     }
 }
 
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+__device__ __forceinline__ uint32_t pack_bf16(uint64_t pair) {
+    float lo, hi;
+    unpack2(pair, lo, hi);
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t *>(&v);
 }
@@ -427,16 +461,16 @@ __device__ __forceinline__ void decode_into(const RawGroup (&grp)[PIECES], const
                                             const int (&pquart)[PIECES], uint8_t *stage) {
 #pragma unroll
     for (int j = 0; j < PIECES; ++j) {
-        float wv[16];
+        uint64_t wv[8];
         decode_slab<FMT, SL>(grp[j], pquart[j], wv);
         uint8_t *dst_row = stage + (prow[j] >> 3) * 1024 + (prow[j] & 7) * 128;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
             uint4 v;
-            v.x = pack_bf16(wv[8 * c + 0], wv[8 * c + 1]);
-            v.y = pack_bf16(wv[8 * c + 2], wv[8 * c + 3]);
-            v.z = pack_bf16(wv[8 * c + 4], wv[8 * c + 5]);
-            v.w = pack_bf16(wv[8 * c + 6], wv[8 * c + 7]);
+            v.x = pack_bf16(wv[4 * c + 0]);
+            v.y = pack_bf16(wv[4 * c + 1]);
+            v.z = pack_bf16(wv[4 * c + 2]);
+            v.w = pack_bf16(wv[4 * c + 3]);
             const int chunk = (pquart[j] * 2 + c) ^ (prow[j] & 7);         // 128-byte swizzle
             *reinterpret_cast<uint4 *>(dst_row + chunk * 16) = v;
         }
