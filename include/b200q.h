@@ -322,6 +322,17 @@ int b200q_decode_attention(const float *q, int64_t q_row_stride, const void *k_c
                            int cache_dtype, const int64_t *position, int batch, int heads, int kv_heads, int head_dim,
                            int horizon, float scale, void *out, int out_dtype, void *stream);
 
+/* The two calls above as one launch for a one-token step (t = 1): q, k, v are the raw FP32 projection outputs
+ * ([B,H,Dh] / [B,Hkv,Dh] with their row strides); every CTA rotates its query head and the new key of its KV head,
+ * the new key / value enter the softmax from registers (rounded through cache_dtype, as a load from the cache would
+ * return them) and are written to the caches at position[0]; q is not modified. Results are bit-identical to
+ * b200q_rope_kv_store followed by b200q_decode_attention (mini_llm/ops/cuda_graph_decode.py:379-449 runs those two
+ * steps per layer); an out-of-range position behaves as in b200q_rope_kv_store (status 301). */
+int b200q_rope_attention(const float *q, const float *k, const float *v, int64_t q_row_stride, int64_t k_row_stride,
+                         int64_t v_row_stride, const int64_t *position, const float *cos_table, const float *sin_table,
+                         int table_rows, int batch, int heads, int kv_heads, int head_dim, int horizon, void *k_cache,
+                         void *v_cache, int cache_dtype, float scale, void *out, int out_dtype, void *stream);
+
 /* ---- Expert-parallel execution over the GPUs of one node (no counterpart in the reference, which is
  * single-process; semantics = the single-GPU layer, bit for bit). ------------------------------- */
 

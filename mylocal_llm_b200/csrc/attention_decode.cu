@@ -7,8 +7,19 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "norm_device.cuh"
 
 namespace b200q {
+
+// Rotate-half pair (x0 = dimension i, x1 = dimension i + Dh/2) by the angle with cosine c and sine s. One
+// definition with explicit roundings for the stand-alone kernel and for the attention kernel that rotates by
+// itself: both give the same bits.
+__device__ __forceinline__ float rope_lo(float x0, float x1, float c, float s) {
+    return __fmaf_rn(x0, c, -__fmul_rn(x1, s));
+}
+__device__ __forceinline__ float rope_hi(float x0, float x1, float c, float s) {
+    return __fmaf_rn(x0, s, __fmul_rn(x1, c));
+}
 
 // q [B, T, H, Dh], k / v [B, T, Hkv, Dh] FP32, each with its own element stride between (b, t)
 // rows (so they may be column slices of one fused projection output); positions [T] (device);
@@ -43,16 +54,16 @@ __global__ void __launch_bounds__(256) rope_kv_store_kernel(float *q, const floa
             float *p = q + (static_cast<size_t>(bb) * t + tt) * q_row + static_cast<size_t>(head) * dh;
             const float c = cos_t[pos * half + i], s = sin_t[pos * half + i];
             const float x0 = p[i], x1 = p[half + i];
-            p[i] = x0 * c - x1 * s;
-            p[half + i] = x0 * s + x1 * c;
+            p[i] = rope_lo(x0, x1, c, s);
+            p[half + i] = rope_hi(x0, x1, c, s);
         } else if (head < h + hkv) {
             const int kh = head - h;
             const float *p = k + (static_cast<size_t>(bb) * t + tt) * k_row + static_cast<size_t>(kh) * dh;
             const float c = cos_t[pos * half + i], s = sin_t[pos * half + i];
             const float x0 = p[i], x1 = p[half + i];
             const size_t dst = ((static_cast<size_t>(bb) * hkv + kh) * horizon + pos) * dh;
-            store_from_float(k_cache, cache_dtype, dst + i, x0 * c - x1 * s);
-            store_from_float(k_cache, cache_dtype, dst + half + i, x0 * s + x1 * c);
+            store_from_float(k_cache, cache_dtype, dst + i, rope_lo(x0, x1, c, s));
+            store_from_float(k_cache, cache_dtype, dst + half + i, rope_hi(x0, x1, c, s));
         } else {
             const int vh = head - h - hkv;
             const float *p = v + (static_cast<size_t>(bb) * t + tt) * v_row + static_cast<size_t>(vh) * dh;
@@ -106,27 +117,88 @@ __device__ __forceinline__ void load_row_piece(const void *cache, int dtype, siz
 // takes every SPLIT-th group of positions, the partial (max, sum, weighted values) of the CTAs are
 // merged by CTA 0 through distributed shared memory between two cluster barriers (hardware
 // barriers; nothing spins). The kernel must then be launched with cluster dimension SPLIT.
-template <int EPL, int ATT_U, int ATT_WARPS, int SPLIT>
+// FUSE: the kernel also does the work of rope_kv_store_kernel for a one-token step (same results, one launch
+// less per layer): q, k, v are the raw projection outputs; every CTA rotates its own query head and the new key
+// of its KV head, keeps the new key / value (rounded through the cache type) in shared memory for the position
+// it stands for, and the first CTA of each KV head writes them to the caches. A position outside
+// [0, min(horizon, table_rows)) leaves q unrotated and the caches untouched and records STATUS_POSITION_RANGE,
+// as the stand-alone kernel does.
+struct RopeFuse {
+    const float *k, *v;
+    long long k_row, v_row;
+    const float *cos_t, *sin_t;
+    int table_rows;
+    void *k_cache, *v_cache;       // writable views of the caches
+    int *status;
+};
+
+template <int EPL, int ATT_U, int ATT_WARPS, int SPLIT, bool FUSE>
 __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const float *q, const void *k_cache,
                                                                           const void *v_cache, int cache_dtype,
                                                                           const long long *position, long long q_row,
                                                                           int h, int hkv, int horizon, float scale,
-                                                                          void *out, int out_dtype) {
+                                                                          void *out, int out_dtype, const RopeFuse rf) {
     chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
     chain_wait();         // inputs come from preceding kernels
     constexpr int DH = EPL * 32;
     __shared__ float sm_m[ATT_WARPS], sm_l[ATT_WARPS], sm_acc[ATT_WARPS][DH];
     __shared__ float fin_ml[2], fin_acc[DH];            // this CTA's merged partial (SPLIT > 1)
+    __shared__ float new_k[FUSE ? DH : 1], new_v[FUSE ? DH : 1];
     const int part = SPLIT > 1 ? static_cast<int>(blockIdx.x % SPLIT) : 0;      // rank inside the cluster
     const int bh = blockIdx.x / SPLIT, bb = bh / h, head = bh - bb * h;
     const int kvh = head / (h / hkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    long long last = position[0];                       // newest valid cache position
+    const long long pos = position[0];
+    long long last = pos;                               // newest valid cache position
     if (last >= horizon) last = horizon - 1;
     const float *qp = q + static_cast<size_t>(bb) * q_row + static_cast<size_t>(head) * DH;
     float qv[EPL];
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) qv[e] = qp[lane * EPL + e] * scale;
+    for (int e = 0; e < EPL; ++e) qv[e] = qp[lane * EPL + e];
+    const bool fuse_valid = FUSE && pos >= 0 && pos < horizon && pos < rf.table_rows;
+    if constexpr (FUSE) {
+        // lane l holds dimensions l*EPL..; the partner of dimension i < Dh/2 is i + Dh/2 = the same slot of lane l ^ 16
+        constexpr int HALF = DH / 2;
+        if (!fuse_valid && blockIdx.x == 0 && threadIdx.x == 0) atomicExch(rf.status, STATUS_POSITION_RANGE);
+        const bool low = lane < 16;
+        float cs[EPL], sn[EPL];
+        if (fuse_valid) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                const int i = (lane & 15) * EPL + e;
+                cs[e] = rf.cos_t[pos * HALF + i];
+                sn[e] = rf.sin_t[pos * HALF + i];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, qv[e], 16);
+            if (fuse_valid) qv[e] = low ? rope_lo(qv[e], other, cs[e], sn[e]) : rope_hi(other, qv[e], cs[e], sn[e]);
+        }
+        if (warp == 0) {
+            const float *kp = rf.k + static_cast<size_t>(bb) * rf.k_row + static_cast<size_t>(kvh) * DH;
+            const float *vp = rf.v + static_cast<size_t>(bb) * rf.v_row + static_cast<size_t>(kvh) * DH;
+            const bool writer = fuse_valid && part == 0 && head == kvh * (h / hkv);
+            const size_t dst = ((static_cast<size_t>(bb) * hkv + kvh) * horizon + (fuse_valid ? pos : 0)) * DH + lane * EPL;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                const float kraw = kp[lane * EPL + e], vraw = vp[lane * EPL + e];
+                const float other = __shfl_xor_sync(0xffffffffu, kraw, 16);
+                if (fuse_valid) {
+                    const float kr = low ? rope_lo(kraw, other, cs[e], sn[e]) : rope_hi(other, kraw, cs[e], sn[e]);
+                    new_k[lane * EPL + e] = round_through(cache_dtype, kr);
+                    new_v[lane * EPL + e] = round_through(cache_dtype, vraw);
+                    if (writer) {
+                        store_from_float(rf.k_cache, cache_dtype, dst + e, kr);
+                        store_from_float(rf.v_cache, cache_dtype, dst + e, vraw);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) qv[e] *= scale;
     const size_t base = (static_cast<size_t>(bb) * hkv + kvh) * horizon * DH + lane * EPL;
     float m = __int_as_float(0xff800000), l = 0.f, acc[EPL];
 #pragma unroll
@@ -139,6 +211,17 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
             const long long j = (j0 + u <= last) ? j0 + u : last;        // clamped rows are masked below
             load_row_piece<EPL>(k_cache, cache_dtype, base + j * DH, kk[u]);
             load_row_piece<EPL>(v_cache, cache_dtype, base + j * DH, vv[u]);
+        }
+        if (fuse_valid && j0 + ATT_U > pos) {        // the group holds the new position: its row is not in the cache yet
+#pragma unroll
+            for (int u = 0; u < ATT_U; ++u)
+                if (j0 + u >= pos) {                     // the position itself and the masked rows clamped to it
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) {
+                        kk[u][e] = new_k[lane * EPL + e];
+                        vv[u][e] = new_v[lane * EPL + e];
+                    }
+                }
         }
 #pragma unroll
         for (int u = 0; u < ATT_U; ++u) {
@@ -252,6 +335,39 @@ static bool attention_split_enabled() {
     return !(v && v[0] == '0' && v[1] == 0);
 }
 
+// few (batch, head) pairs: 32 warps per CTA, and four CTAs (a cluster) per pair while those still fit the GPU
+template <bool FUSE>
+static void launch_attention(const float *q, int64_t q_row_stride, const void *k_cache, const void *v_cache, int cache_dtype,
+                             const int64_t *position, int batch, int heads, int kv_heads, int head_dim, int horizon,
+                             float scale, void *out, int out_dtype, const RopeFuse rf, void *stream) {
+    const long long *pos = reinterpret_cast<const long long *>(position);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const long long pairs = static_cast<long long>(batch) * heads;
+    const bool wide = pairs < 2LL * sm_count();
+    const bool split = wide && pairs * ATT_SPLIT <= 2LL * sm_count() && attention_split_enabled();
+    const long long q_row = q_row_stride;
+    if (head_dim == 64 && split)
+        launch_chained_cluster(decode_attention_kernel<2, 8, 32, ATT_SPLIT, FUSE>, dim3(pairs * ATT_SPLIT), dim3(1024), 0, s,
+                               ATT_SPLIT, q, k_cache, v_cache, cache_dtype, pos, q_row, heads, kv_heads, horizon, scale,
+                               out, out_dtype, rf);
+    else if (head_dim == 64 && wide)
+        launch_chained(decode_attention_kernel<2, 8, 32, 1, FUSE>, dim3(pairs), dim3(1024), 0, s, q, k_cache, v_cache,
+                       cache_dtype, pos, q_row, heads, kv_heads, horizon, scale, out, out_dtype, rf);
+    else if (head_dim == 64)
+        launch_chained(decode_attention_kernel<2, 8, 8, 1, FUSE>, dim3(pairs), dim3(256), 0, s, q, k_cache, v_cache,
+                       cache_dtype, pos, q_row, heads, kv_heads, horizon, scale, out, out_dtype, rf);
+    else if (split)
+        launch_chained_cluster(decode_attention_kernel<4, 4, 32, ATT_SPLIT, FUSE>, dim3(pairs * ATT_SPLIT), dim3(1024), 0, s,
+                               ATT_SPLIT, q, k_cache, v_cache, cache_dtype, pos, q_row, heads, kv_heads, horizon, scale,
+                               out, out_dtype, rf);
+    else if (wide)
+        launch_chained(decode_attention_kernel<4, 4, 32, 1, FUSE>, dim3(pairs), dim3(1024), 0, s, q, k_cache, v_cache,
+                       cache_dtype, pos, q_row, heads, kv_heads, horizon, scale, out, out_dtype, rf);
+    else
+        launch_chained(decode_attention_kernel<4, 8, 8, 1, FUSE>, dim3(pairs), dim3(256), 0, s, q, k_cache, v_cache,
+                       cache_dtype, pos, q_row, heads, kv_heads, horizon, scale, out, out_dtype, rf);
+}
+
 }  // namespace b200q
 
 using namespace b200q;
@@ -295,35 +411,29 @@ int b200q_decode_attention(const float *q, int64_t q_row_stride, const void *k_c
     if (batch <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || horizon <= 0 || !dtype_valid(cache_dtype) ||
         !dtype_valid(out_dtype) || q_row_stride < static_cast<int64_t>(heads) * head_dim)
         return fail(B200Q_EINVAL, "decode_attention: bad argument");
-    const long long *pos = reinterpret_cast<const long long *>(position);
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // few (batch, head) pairs: 32 warps per CTA, and four CTAs (a cluster) per pair while those still fit the GPU
-    const long long pairs = static_cast<long long>(batch) * heads;
-    const bool wide = pairs < 2LL * sm_count();
-    const bool split = wide && pairs * ATT_SPLIT <= 2LL * sm_count() && attention_split_enabled();
-    if (head_dim == 64 && split)
-        launch_chained_cluster(decode_attention_kernel<2, 8, 32, ATT_SPLIT>, dim3(pairs * ATT_SPLIT), dim3(1024), 0, s,
-                               ATT_SPLIT, q, k_cache, v_cache, cache_dtype, pos, q_row_stride, heads, kv_heads, horizon,
-                               scale, out, out_dtype);
-    else if (head_dim == 64 && wide)
-        launch_chained(decode_attention_kernel<2, 8, 32, 1>, dim3(pairs), dim3(1024), 0, s, q, k_cache, v_cache, cache_dtype,
-                       pos, q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
-    else if (head_dim == 64)
-        launch_chained(decode_attention_kernel<2, 8, 8, 1>, dim3(pairs), dim3(256), 0, s, q, k_cache, v_cache, cache_dtype,
-                       pos, q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
-    else if (head_dim == 128 && split)
-        launch_chained_cluster(decode_attention_kernel<4, 4, 32, ATT_SPLIT>, dim3(pairs * ATT_SPLIT), dim3(1024), 0, s,
-                               ATT_SPLIT, q, k_cache, v_cache, cache_dtype, pos, q_row_stride, heads, kv_heads, horizon,
-                               scale, out, out_dtype);
-    else if (head_dim == 128 && wide)
-        launch_chained(decode_attention_kernel<4, 4, 32, 1>, dim3(pairs), dim3(1024), 0, s, q, k_cache, v_cache, cache_dtype,
-                       pos, q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
-    else if (head_dim == 128)
-        launch_chained(decode_attention_kernel<4, 8, 8, 1>, dim3(pairs), dim3(256), 0, s, q, k_cache, v_cache, cache_dtype,
-                       pos, q_row_stride, heads, kv_heads, horizon, scale, out, out_dtype);
-    else
-        return fail(B200Q_EUNSUPPORTED, "decode_attention: head_dim must be 64 or 128");
+    if (head_dim != 64 && head_dim != 128) return fail(B200Q_EUNSUPPORTED, "decode_attention: head_dim must be 64 or 128");
+    launch_attention<false>(q, q_row_stride, k_cache, v_cache, cache_dtype, position, batch, heads, kv_heads, head_dim,
+                            horizon, scale, out, out_dtype, RopeFuse{}, stream);
     return check_launch("decode_attention");
+}
+
+int b200q_rope_attention(const float *q, const float *k, const float *v, int64_t q_row_stride, int64_t k_row_stride,
+                         int64_t v_row_stride, const int64_t *position, const float *cos_table, const float *sin_table,
+                         int table_rows, int batch, int heads, int kv_heads, int head_dim, int horizon, void *k_cache,
+                         void *v_cache, int cache_dtype, float scale, void *out, int out_dtype, void *stream) {
+    if (!q || !k || !v || !position || !cos_table || !sin_table || !k_cache || !v_cache || !out)
+        return fail(B200Q_EINVAL, "rope_attention: NULL pointer");
+    if (batch <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || horizon <= 0 || table_rows <= 0 ||
+        !dtype_valid(cache_dtype) || !dtype_valid(out_dtype) || q_row_stride < static_cast<int64_t>(heads) * head_dim ||
+        k_row_stride < static_cast<int64_t>(kv_heads) * head_dim || v_row_stride < static_cast<int64_t>(kv_heads) * head_dim)
+        return fail(B200Q_EINVAL, "rope_attention: bad argument");
+    if (head_dim != 64 && head_dim != 128) return fail(B200Q_EUNSUPPORTED, "rope_attention: head_dim must be 64 or 128");
+    int *status = device_status_word();
+    if (!status) return fail(B200Q_ECUDA, "rope_attention: no CUDA device");
+    const RopeFuse rf{k, v, k_row_stride, v_row_stride, cos_table, sin_table, table_rows, k_cache, v_cache, status};
+    launch_attention<true>(q, q_row_stride, k_cache, v_cache, cache_dtype, position, batch, heads, kv_heads, head_dim,
+                           horizon, scale, out, out_dtype, rf, stream);
+    return check_launch("rope_attention");
 }
 
 }  // extern "C"

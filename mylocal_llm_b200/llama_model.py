@@ -10,8 +10,8 @@ adapter; here they stay packed and resident in HBM, which is the point of the ex
   ``quantized_swiglu`` on ``DevicePackedGGUFWeight`` (tile layouts where they exist);
 * RMSNorm is ``b200q_rmsnorm`` / the fused residual-add variant; the residual stream is FP32;
 * embedding rows are gathered as packed bytes and decoded by ``b200q_dequantize``;
-* the one-token step runs rotate-half RoPE fused with the KV-cache store (``b200q_rope_kv_store``),
-  single-query attention over the cache (``b200q_decode_attention``), and ``b200q_silu_mul`` on
+* the one-token step runs rotate-half RoPE, the KV-cache store and single-query attention over the cache as one
+  kernel (``b200q_rope_attention``; ``b200q_rope_kv_store`` + ``b200q_decode_attention`` are the two-launch form), and ``b200q_silu_mul`` on
   the output of the stacked gate|up projection; prefill (and ``fused_decode = False``) does the
   RoPE / cache / attention bookkeeping with plain torch ops. The decode step has static shapes - the cache is written at a
   device-side position and attention stops at that position - so ``decode_one`` can be captured in
@@ -266,6 +266,28 @@ class ExternalLlamaModel:
         residual, hidden = norm.forward_residual_add(residual, branch)
         return residual, self._linear(hidden, weight, out_dtype)
 
+    def _rope_attention(self, q2, k2, v2, positions, state, layer_index, ctx):
+        """RoPE of the new query / key, the KV-cache store and single-query attention of a one-token step: one
+        launch (``b200q_rope_attention``), or the two separate ones with ``B200Q_ROPE_ATTENTION=0`` (same bits)."""
+        import os
+        cfg = self.config
+        heads, kv_heads, dh = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        b = q2.shape[0]
+        ptr = lambda x: ctypes.c_void_p(x.data_ptr())
+        cache_id = _lib.DTYPE_ID[str(self.dtype).replace("torch.", "")]
+        kc, vc = state.k[layer_index], state.v[layer_index]
+        if os.environ.get("B200Q_ROPE_ATTENTION", "1") != "0":
+            _lib.call("b200q_rope_attention", ptr(q2), ptr(k2), ptr(v2), q2.stride(0), k2.stride(0), v2.stride(0),
+                      ptr(positions), ptr(self._cos), ptr(self._sin), int(self._cos.shape[0]), b, heads, kv_heads, dh,
+                      state.horizon, ptr(kc), ptr(vc), cache_id, float(dh ** -0.5), ptr(ctx), cache_id,
+                      _lib.current_stream())
+            return
+        _lib.call("b200q_rope_kv_store", ptr(q2), ptr(k2), ptr(v2), q2.stride(0), k2.stride(0), v2.stride(0),
+                  ptr(positions), ptr(self._cos), ptr(self._sin), int(self._cos.shape[0]), b, 1, heads, kv_heads, dh,
+                  state.horizon, ptr(kc), ptr(vc), cache_id, _lib.current_stream())
+        _lib.call("b200q_decode_attention", ptr(q2), q2.stride(0), ptr(kc), ptr(vc), cache_id, ptr(positions), b, heads,
+                  kv_heads, dh, state.horizon, float(dh ** -0.5), ptr(ctx), cache_id, _lib.current_stream())
+
     def _forward_one_token(self, token_ids, state, positions):
         """The one-token step with every residual-add + RMSNorm deferred into the projection that follows it
         (stacked qkv, stacked gate|up, LM head). Returns FP32 logits [B, vocab]."""
@@ -284,13 +306,8 @@ class ExternalLlamaModel:
             else:
                 residual, qkv = self._norm_linear(layer["norm1"], residual, pending, layer["qkv"], torch.float32)
             q2, k2, v2 = qkv[:, :qd], qkv[:, qd:qd + kd], qkv[:, qd + kd:]
-            _lib.call("b200q_rope_kv_store", ptr(q2), ptr(k2), ptr(v2), q2.stride(0), k2.stride(0), v2.stride(0),
-                      ptr(positions), ptr(self._cos), ptr(self._sin), int(self._cos.shape[0]), b, 1, heads, kv_heads, dh,
-                      state.horizon, ptr(state.k[i]), ptr(state.v[i]), cache_id, _lib.current_stream())
             ctx = torch.empty((b, heads * dh), dtype=self.dtype, device=residual.device)
-            _lib.call("b200q_decode_attention", ptr(q2), q2.stride(0), ptr(state.k[i]), ptr(state.v[i]), cache_id,
-                      ptr(positions), b, heads, kv_heads, dh, state.horizon, float(dh ** -0.5), ptr(ctx), cache_id,
-                      _lib.current_stream())
+            self._rope_attention(q2, k2, v2, positions, state, i, ctx)
             attn = quantized_linear(ctx, layer["o"])
             residual, gu = self._norm_linear(layer["norm2"], residual, attn, layer["gate_up"], torch.float32)
             f = gu.shape[1] // 2
@@ -322,14 +339,8 @@ class ExternalLlamaModel:
                 # one-token step: RoPE + cache store, then single-query attention, one kernel each
                 ptr = lambda x: ctypes.c_void_p(x.data_ptr())
                 cache_id = _lib.DTYPE_ID[str(self.dtype).replace("torch.", "")]
-                _lib.call("b200q_rope_kv_store", ptr(q2), ptr(k2), ptr(v2), q2.stride(0), k2.stride(0), v2.stride(0),
-                          ptr(positions), ptr(self._cos), ptr(self._sin), int(self._cos.shape[0]), b, 1, heads, kv_heads, dh,
-                          state.horizon,
-                          ptr(state.k[i]), ptr(state.v[i]), cache_id, _lib.current_stream())
                 ctx = torch.empty((b, heads * dh), dtype=self.dtype, device=hidden.device)
-                _lib.call("b200q_decode_attention", ptr(q2), q2.stride(0), ptr(state.k[i]), ptr(state.v[i]), cache_id,
-                          ptr(positions), b, heads, kv_heads, dh, state.horizon, float(dh ** -0.5), ptr(ctx), cache_id,
-                          _lib.current_stream())
+                self._rope_attention(q2, k2, v2, positions, state, i, ctx)
                 attn = quantized_linear(ctx, layer["o"])
                 residual, hidden = layer["norm2"].forward_residual_add(residual, attn)
                 hidden, residual = self._ffn(i, layer, hidden, residual)
