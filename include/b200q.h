@@ -88,6 +88,15 @@ int b200q_gemv_norm(const void *w, int fmt, int n, int k, const float *residual,
                     int branch_dtype, float alpha, const void *gamma, int act_dtype, float eps, int m,
                     float *res_out, void *y, int y_dtype, void *stream);
 
+/* y[m, n] = (silu(gate) * up) W^T with gate|up the stacked FP32 projection output [m, 2k] of the preceding launch:
+ * b200q_silu_mul fused into the GEMV that consumes it (the down projection of the Llama MLP whose gate, up and
+ * down matrices mini_llm/external/llama_model.py:125-130 wires, in a one-token step), same bits as the two launches. Tile-layout
+ * Q6_K / Q8_0 weights, act_dtype (the type the activation is rounded to) F16 or BF16, at most 4 rows;
+ * b200q_gemv_silu_supported tells whether a shape is covered. */
+int b200q_gemv_silu_supported(int fmt, int n, int k, int act_dtype, int m);
+int b200q_gemv_silu(const void *w, int fmt, int n, int k, const float *gate_up, int act_dtype, int m, void *y,
+                    int y_dtype, void *stream);
+
 /* The same product for many tokens (prefill, batched decode) on the tensor cores: W is read once per
  * call, decoded tile by tile to BF16 in shared memory and multiplied by tcgen05.mma with an FP32
  * accumulator in tensor memory; the activations arrive by TMA. Serves the any-M contract of

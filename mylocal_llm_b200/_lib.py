@@ -75,6 +75,8 @@ SIGNATURES = {
     "b200q_silu_mul": [_ptr, _c_int, _c_int, _ptr, _c_int, _ptr],
     "b200q_decode_attention": [_ptr, _c_i64, _ptr, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f32,
                                _ptr, _c_int, _ptr],
+    "b200q_gemv_silu_supported": [_c_int, _c_int, _c_int, _c_int, _c_int],
+    "b200q_gemv_silu": [_ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _ptr, _c_int, _ptr],
     "b200q_rope_attention": [_ptr, _ptr, _ptr, _c_i64, _c_i64, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int,
                              _c_int, _c_int, _ptr, _ptr, _c_int, _c_f32, _ptr, _c_int, _ptr],
     "b200q_q8_0_retile": [_ptr, _ptr, _c_i64, _c_int, _ptr],

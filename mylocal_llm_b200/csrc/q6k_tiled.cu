@@ -326,6 +326,49 @@ extern "C" int b200q_gemv_norm(const void *w, int fmt, int n, int k, const float
     return check_launch("gemv_norm");
 }
 
+// b200q_gemv_silu: y[m, n] = (silu(gate) * up) W^T for a stacked FP32 gate|up row [m, 2k]; same shapes as b200q_gemv_norm.
+extern "C" int b200q_gemv_silu_supported(int fmt, int n, int k, int act_dtype, int m) {
+    if (fmt != B200Q_Q6_K_TILED && fmt != B200Q_Q8_0_TILED) return 0;
+    if (act_dtype != B200Q_BF16 && act_dtype != B200Q_F16) return 0;
+    if (m < 1 || m > NORM_GEMV_MAX_ROWS || n < 16 || n % 16 != 0 || k < 256 || k % 256 != 0) return 0;
+    const long long body = Q6T_CTRL_BYTES + Q6T_PART_BYTES + static_cast<long long>(k / 16) * 256;
+    return body + 128 + static_cast<long long>(m) * k * 2 <= MM_SMEM_LIMIT - 4096 ? 1 : 0;
+}
+
+extern "C" int b200q_gemv_silu(const void *w, int fmt, int n, int k, const float *gate_up, int act_dtype, int m, void *y,
+                               int y_dtype, void *stream) {
+    if (!w || !gate_up || !y) return fail(B200Q_EINVAL, "gemv_silu: NULL pointer");
+    if (!dtype_valid(y_dtype)) return fail(B200Q_EINVAL, "gemv_silu: bad dtype");
+    if (reinterpret_cast<uintptr_t>(gate_up) & 15) return fail(B200Q_EUNSUPPORTED, "gemv_silu: gate|up must be 16-byte aligned");
+    if (!b200q_gemv_silu_supported(fmt, n, k, act_dtype, m))
+        return fail(B200Q_EUNSUPPORTED, "gemv_silu: needs tile-layout Q6_K / Q8_0 weights, 16-bit activations, at most %d rows",
+                    NORM_GEMV_MAX_ROWS);
+    MmaRequest q{};
+    q.mode = 0; q.wa = static_cast<const uint8_t *>(w); q.fmt_a = q.fmt_b = fmt; q.n = n; q.k = k; q.m = m;
+    q.x = gate_up;             // placeholder: the kernel reads the activation rows from its shared memory
+    q.x_dtype = act_dtype; q.y = y; q.y_dtype = y_dtype;
+    Q6TiledArgs a{};
+    long long smem = 0;
+    int rc = tiled_plan_args(q, &a, &smem);
+    if (rc) return rc;
+    const int x_off = static_cast<int>((smem + 127) / 128 * 128);
+    smem = x_off + static_cast<long long>(m) * k * 2;
+    using SiluFn = void (*)(const Q6TiledArgs, const float *, int);
+    SiluFn fn = fmt == B200Q_Q8_0_TILED ? tiled_silu_kernel<Q8Tile, 1> : tiled_silu_kernel<Q6Tile, 1>;
+    cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void *>(fn),
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM_LIMIT - 4096);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail(B200Q_ECUDA, "gemv_silu: shared memory opt-in failed: %s", cudaGetErrorString(err));
+    }
+    int grid = sm_count();
+    const int blocks = (n / 16 + a.rg - 1) / a.rg;
+    if (blocks < grid) grid = blocks;
+    launch_chained(fn, dim3(grid), dim3(Q6T_THREADS), static_cast<size_t>(smem), static_cast<cudaStream_t>(stream), a, gate_up,
+                   x_off);
+    return check_launch("gemv_silu");
+}
+
 static int q4k_retile_common(const void *src, void *dst, long long rows, int k, bool forward, void *stream) {
     if (!src || !dst) return fail(B200Q_EINVAL, "q4k_retile: NULL pointer");
     if (rows <= 0 || rows % 16 != 0 || k <= 0 || k % 256 != 0)

@@ -614,4 +614,41 @@ __global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_norm_kernel(const Q6Tile
     tiled_body<TILE, 0, NTERMS, 1>(a, gp, smem, blockIdx.x, gridDim.x);
 }
 
+// SiLU(gate) * up fused into the GEMV that consumes it (the down projection of a one-token decoder step): every CTA
+// computes the activation rows itself from the stacked FP32 gate|up projection output [m, 2k] - the arithmetic and
+// the rounding to the activation type of the stand-alone element-wise kernel - keeps them in shared memory behind
+// the GEMV's buffers and runs the GEMV body on them. Same bits as the two launches.
+template <typename TILE, int NTERMS>
+__global__ void __launch_bounds__(Q6T_THREADS, 1) tiled_silu_kernel(const Q6TiledArgs a, const float *gate_up, int x_off) {
+    chain_trigger();
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x;
+    {
+        const int groups_total = a.n >> 4, nsb = a.k >> 8;
+        const long long total_blocks = (groups_total + a.rg - 1) / a.rg;
+        const long long blk_begin = total_blocks * blockIdx.x / gridDim.x, blk_end = total_blocks * (blockIdx.x + 1) / gridDim.x;
+        if (blk_begin < blk_end) {
+            const size_t first = static_cast<size_t>(blk_begin) * a.rg * nsb * TILE::BYTES;
+            const size_t last = static_cast<size_t>(min(static_cast<long long>(groups_total), blk_end * a.rg)) * nsb * TILE::BYTES;
+            prefetch_l2_range(a.w + first, last - first, CHAIN_PREFETCH_BYTES, tid, Q6T_THREADS);
+        }
+    }
+    chain_wait();              // the gate|up projection comes from the preceding kernel
+    uint8_t *x_rows = smem + x_off;                            // [m][k] activations (16-bit)
+    const int quads = a.k >> 2;
+    for (int i = tid; i < a.m * quads; i += Q6T_THREADS) {
+        const int row = i / quads, c4 = i - row * quads;
+        const float4 g = reinterpret_cast<const float4 *>(gate_up + static_cast<size_t>(row) * 2 * a.k)[c4];
+        const float4 u = reinterpret_cast<const float4 *>(gate_up + static_cast<size_t>(row) * 2 * a.k + a.k)[c4];
+        const size_t o = static_cast<size_t>(row) * a.k + 4 * c4;
+        store_from_float(x_rows, a.x_dtype, o, swiglu_f32(g.x, u.x));
+        store_from_float(x_rows, a.x_dtype, o + 1, swiglu_f32(g.y, u.y));
+        store_from_float(x_rows, a.x_dtype, o + 2, swiglu_f32(g.z, u.z));
+        store_from_float(x_rows, a.x_dtype, o + 3, swiglu_f32(g.w, u.w));
+    }
+    __syncthreads();
+    const StagePointers gp{x_rows, a.y, a.table, nullptr, a.order, a.seg_expert, a.seg_begin, a.seg_count, a.num_segments, a.route, -1};
+    tiled_body<TILE, 0, NTERMS, 1>(a, gp, smem, blockIdx.x, gridDim.x);
+}
+
 }  // namespace b200q

@@ -266,6 +266,29 @@ class ExternalLlamaModel:
         residual, hidden = norm.forward_residual_add(residual, branch)
         return residual, self._linear(hidden, weight, out_dtype)
 
+    def _silu_linear(self, gu, weight):
+        """``(silu(gate) * up) @ weight.T`` for the stacked FP32 gate|up output ``gu`` [B, 2F]: ``b200q_silu_mul``
+        followed by the projection. ``B200Q_SILU_GEMV=1`` makes it one launch (``b200q_gemv_silu``, same bits) for a
+        tile-layout Q6_K / Q8_0 weight and one row - measured slower at the 1.7B shape (778 against 828 tokens/s:
+        every CTA of the projection computes the 8192 activations itself before it starts on its weights, which
+        costs more than the 1.8 us of the chained element-wise launch)."""
+        import os
+        torch = _torch()
+        b, f = gu.shape[0], gu.shape[1] // 2
+        n, k = weight.shape
+        ptr = lambda x: ctypes.c_void_p(x.data_ptr())
+        dt = _lib.DTYPE_ID[str(self.dtype).replace("torch.", "")]
+        fmt = _lib.FORMAT_ID.get(weight.quant_type, -1)
+        if (b == 1 and k == f and gu.is_contiguous() and gu.data_ptr() % 16 == 0 and self.dtype != torch.float32
+                and os.environ.get("B200Q_SILU_GEMV", "0") == "1"
+                and _lib.load().b200q_gemv_silu_supported(fmt, n, k, dt, b)):
+            y = torch.empty((b, n), dtype=self.dtype, device=gu.device)
+            _lib.call("b200q_gemv_silu", ptr(weight.data), fmt, n, k, ptr(gu), dt, b, ptr(y), dt, _lib.current_stream())
+            return y
+        act = torch.empty((b, f), dtype=self.dtype, device=gu.device)
+        _lib.call("b200q_silu_mul", ptr(gu), b, f, ptr(act), dt, _lib.current_stream())
+        return self._linear(act, weight)
+
     def _rope_attention(self, q2, k2, v2, positions, state, layer_index, ctx):
         """RoPE of the new query / key, the KV-cache store and single-query attention of a one-token step: one
         launch (``b200q_rope_attention``), or the two separate ones with ``B200Q_ROPE_ATTENTION=0`` (same bits)."""
@@ -310,10 +333,7 @@ class ExternalLlamaModel:
             self._rope_attention(q2, k2, v2, positions, state, i, ctx)
             attn = quantized_linear(ctx, layer["o"])
             residual, gu = self._norm_linear(layer["norm2"], residual, attn, layer["gate_up"], torch.float32)
-            f = gu.shape[1] // 2
-            act = torch.empty((b, f), dtype=self.dtype, device=gu.device)
-            _lib.call("b200q_silu_mul", ptr(gu), b, f, ptr(act), cache_id, _lib.current_stream())
-            pending = self._linear(act, layer["down"])
+            pending = self._silu_linear(gu, layer["down"])
         _, logits = self._norm_linear(self.final_norm, residual, pending, self.lm_head, torch.float32)
         return logits
 

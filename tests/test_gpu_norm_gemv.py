@@ -123,3 +123,71 @@ def test_llama_one_token_step_with_deferred_norms(cuda, batch, graph):
     for a, b in zip(got, want):
         assert torch.equal(a, b)
     assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("fmt", ["Q8_0", "Q6_K"])
+@pytest.mark.parametrize("n,k", [(2048, 8192), (64, 256), (512, 1024)])
+@pytest.mark.parametrize("rows", [1, 3])
+@pytest.mark.parametrize("act", ["bfloat16", "float16"])
+def test_fused_silu_gemv_equals_the_two_launches(cuda, fmt, n, k, rows, act):
+    """``b200q_gemv_silu`` (SiLU(gate) * up computed by every CTA of the down projection) against ``b200q_silu_mul``
+    followed by ``b200q_gemv``: same bits."""
+    torch = cuda
+    if n * k > 512 * 1024 and (fmt != "Q8_0" or act != "bfloat16"):
+        pytest.skip("the large shape once per row count")
+    rng = np.random.default_rng(n + k + rows)
+    # (force: K = 8192 is tiled only for callers that pass 16-bit activations, as the Llama model does)
+    weight = retile_weight(packed_to_device(quantize(rng.normal(0, 0.02, (n, k)).astype(np.float32), fmt)), force=True)
+    assert weight.quant_type == fmt + "_TILED"
+    dt = getattr(torch, act)
+    gu = torch.from_numpy(rng.normal(0, 2, (rows, 2 * k)).astype(np.float32)).cuda()
+    gu[0, :4] = torch.tensor([-100.0, 100.0, 0.0, -0.0], device="cuda")          # both branches of the logistic
+    act_rows = torch.empty((rows, k), dtype=dt, device="cuda")
+    _lib.call("b200q_silu_mul", ptr(gu), rows, k, ptr(act_rows), dtype_id(act_rows), _lib.current_stream())
+    fmt_id = _lib.FORMAT_ID[weight.quant_type]
+    assert _lib.load().b200q_gemv_silu_supported(fmt_id, n, k, dtype_id(act_rows), rows) == 1
+    for out_dtype in (torch.float32, dt):
+        want = quantized_linear(act_rows, weight, out_dtype=out_dtype)
+        got = torch.full((rows, n), float("nan"), dtype=out_dtype, device="cuda")
+        _lib.call("b200q_gemv_silu", ptr(weight.data), fmt_id, n, k, ptr(gu), dtype_id(act_rows), rows, ptr(got),
+                  dtype_id(got), _lib.current_stream())
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    assert _lib.device_status() == 0
+
+
+def test_llama_one_token_step_fusions_change_no_bit(cuda, monkeypatch):
+    """RoPE + cache store inside the attention kernel and SiLU * up inside the down projection: the step's logits and
+    its caches are those of the separate launches."""
+    torch = cuda
+    model = ExternalLlamaModel.synthetic(ExternalLlamaConfig(**LLAMA), seed=4)
+    prompt = torch.randint(0, LLAMA["vocab_size"], (1, 9), device="cuda")
+
+    def run():
+        state = model.create_generation_state(1, 32)
+        token = model.prefill(prompt, state).argmax(dim=-1)
+        outs, calls = [], []
+        real = _lib.call
+        _lib.call = lambda name, *a: (calls.append(name), real(name, *a))[1]
+        try:
+            for _ in range(3):
+                logits = model.decode_one(token, state)
+                outs.append(logits.clone())
+                token = logits.argmax(dim=-1)
+        finally:
+            _lib.call = real
+        return outs, calls, [k.clone() for k in state.k], [v.clone() for v in state.v]
+
+    monkeypatch.setenv("B200Q_SILU_GEMV", "1")            # off by default (measured slower at the 1.7B shape)
+    got, calls_fused, k_got, v_got = run()
+    monkeypatch.setenv("B200Q_ROPE_ATTENTION", "0")
+    monkeypatch.setenv("B200Q_SILU_GEMV", "0")
+    want, calls_plain, k_want, v_want = run()
+    assert "b200q_rope_attention" in calls_fused and "b200q_rope_kv_store" not in calls_fused
+    assert "b200q_gemv_silu" in calls_fused and "b200q_silu_mul" not in calls_fused
+    assert "b200q_rope_kv_store" in calls_plain and "b200q_silu_mul" in calls_plain
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    for a, b in zip(k_got + v_got, k_want + v_want):
+        assert torch.equal(a, b)
+    assert _lib.device_status() == 0
