@@ -194,8 +194,11 @@ def test_fully_tiled_bank_matches_the_native_bank(cuda, fmt, tokens):
     b = routed_experts_forward(x, weights, ids, tiled, out_dtype=cuda.float32).cpu().numpy()
     np.testing.assert_allclose(b, a, rtol=2e-4, atol=1e-5)
     one = tiled.expert(3).forward(x)                              # per-expert handles see whole tiles
-    np.testing.assert_allclose(one.float().cpu().numpy(), bank.expert(3).forward(x).float().cpu().numpy(),
-                               rtol=2e-2, atol=2e-2)
+    # (from 17 BF16 tokens on the GGUF-layout handle runs its projections on the tensor-core GEMM, whose weights carry
+    # one BF16 rounding, and the BF16 outputs of magnitude ~100 have an ulp of 0.5: the band is relative to the
+    # output scale, not to each element)
+    want = bank.expert(3).forward(x).float().cpu().numpy()
+    np.testing.assert_allclose(one.float().cpu().numpy(), want, rtol=2e-2, atol=2e-2 * max(1.0, float(np.abs(want).max())))
 
 
 # ------------------------------------------------------------------------------------------ Q8_0
