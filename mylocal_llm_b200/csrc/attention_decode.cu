@@ -139,7 +139,6 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
                                                                           int h, int hkv, int horizon, float scale,
                                                                           void *out, int out_dtype, const RopeFuse rf) {
     chain_trigger();      // the next kernel of the stream may be scheduled; it waits for this grid itself
-    chain_wait();         // inputs come from preceding kernels
     constexpr int DH = EPL * 32;
     __shared__ float sm_m[ATT_WARPS], sm_l[ATT_WARPS], sm_acc[ATT_WARPS][DH];
     __shared__ float fin_ml[2], fin_acc[DH];            // this CTA's merged partial (SPLIT > 1)
@@ -148,6 +147,27 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     const int bh = blockIdx.x / SPLIT, bb = bh / h, head = bh - bb * h;
     const int kvh = head / (h / hkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    {
+        // Before the dependency wait: the cache rows of this warp's first two groups of positions are asked into L2
+        // while the projection that precedes this kernel still runs (the rows were written by earlier steps and left
+        // L2 since: a step streams the whole model through it). The position read here may be one step old - it only
+        // steers the hint; the real one is read after the wait.
+        long long hint = position[0];
+        if (hint >= horizon) hint = horizon - 1;
+        const int esize = cache_dtype == B200Q_F32 ? 4 : 2;
+        const size_t row0 = (static_cast<size_t>(bb) * hkv + kvh) * horizon;
+        for (int gi = 0; gi < 2; ++gi) {
+            const long long j0 = (static_cast<long long>(gi) * SPLIT * ATT_WARPS + part * ATT_WARPS + warp) * ATT_U;
+#pragma unroll
+            for (int u = 0; u < ATT_U; ++u) {
+                if (j0 + u > hint) break;
+                const size_t off = ((row0 + j0 + u) * DH + lane * EPL) * esize;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const uint8_t *>(k_cache) + off));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const uint8_t *>(v_cache) + off));
+            }
+        }
+    }
+    chain_wait();         // inputs come from preceding kernels
     const long long pos = position[0];
     long long last = pos;                               // newest valid cache position
     if (last >= horizon) last = horizon - 1;
