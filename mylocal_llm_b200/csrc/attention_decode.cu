@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     const int kvh = head / (h / hkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     {
-        // Before the dependency wait: the cache rows of this warp's first two groups of positions are asked into L2
+        // Before the dependency wait: the cache rows of this warp's first (up to sixteen) groups of positions are asked into L2
         // while the projection that precedes this kernel still runs (the rows were written by earlier steps and left
         // L2 since: a step streams the whole model through it). The position read here may be one step old - it only
         // steers the hint; the real one is read after the wait.
@@ -156,8 +156,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
         if (hint >= horizon) hint = horizon - 1;
         const int esize = cache_dtype == B200Q_F32 ? 4 : 2;
         const size_t row0 = (static_cast<size_t>(bb) * hkv + kvh) * horizon;
-        for (int gi = 0; gi < 2; ++gi) {
+        for (int gi = 0; gi < 16; ++gi) {
             const long long j0 = (static_cast<long long>(gi) * SPLIT * ATT_WARPS + part * ATT_WARPS + warp) * ATT_U;
+            if (j0 > hint) break;
 #pragma unroll
             for (int u = 0; u < ATT_U; ++u) {
                 if (j0 + u > hint) break;
