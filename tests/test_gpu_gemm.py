@@ -88,6 +88,7 @@ def test_gemm_random_bytes_exercise_every_code_bit(cuda, fmt):
     w = random_packed(fmt, (256, 1024), seed=5, d=0.01, dmin=0.005)
     check(cuda, w, 70, seed=1)
     check(cuda, w, 70, seed=1, out_dtype=cuda.bfloat16)
+    check(cuda, w, 70, seed=1, out_dtype=cuda.float16)
 
 
 @pytest.mark.parametrize("fmt", ["Q4_K", "Q5_K", "Q6_K"])
