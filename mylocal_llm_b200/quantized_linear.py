@@ -247,9 +247,11 @@ def quantized_linear(x, weight, *, block_k=512, cpu_packed_backend="reference", 
     return out.reshape(tuple(x.shape[:-1]) + (n,))
 
 
-# Tokens from which the tensor-core GEMM beats repeated GEMV passes (one pass serves 16 tokens): measured on
-# the [8192 x 2048] / [2048 x 8192] shapes, a second GEMV pass already costs more than the GEMM.
-GEMM_MIN_TOKENS = {"Q4_K": 17, "Q5_K": 17, "Q6_K": 17, "Q8_0": 17}
+# Tokens from which the tensor-core GEMM beats the GEMV kernels: more than one 8-token tile. A GEMV pass over two
+# tiles (9-16 tokens) reads the weights once but takes 21-29 us on the [8192 x 2048] shapes where the GEMM needs
+# 12-18 us (a 1.7B Llama step at batch 16: 4167 -> 5883 tokens/s); one tile (<= 8 tokens) stays on the GEMV kernels
+# with their exact products.
+GEMM_MIN_TOKENS = {"Q4_K": 9, "Q5_K": 9, "Q6_K": 9, "Q8_0": 9}
 
 
 def _use_gemm(weight, x, m, n, k, dt):

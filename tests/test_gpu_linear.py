@@ -142,8 +142,8 @@ def test_linear_config1_shapes_bf16(cuda, fmt, shape, kernel_family, monkeypatch
         rms = float(np.sqrt((ref ** 2).mean()))
         y = quantized_linear(xd, dw).float().cpu().numpy()
         y32 = quantized_linear(xd, dw, out_dtype=cuda.float32).cpu().numpy()
-        if m > 16 and kernel_family == "tensor":
-            # more than 16 tokens run on the tensor-core GEMM, which rounds the dequantised weights to BF16:
+        if m > 8 and kernel_family == "tensor":
+            # more than 8 tokens (one tile) run on the tensor-core GEMM, which rounds the dequantised weights to BF16:
             # element by element, twelve standard deviations of that rounding (independent-error model,
             # 2^-9 / sqrt(3) relative per weight; equal codes round alike, hence twelve and not six)
             sigma = 2.0 ** -9 / np.sqrt(3.0) * np.sqrt((x64 ** 2) @ (dense ** 2).T)

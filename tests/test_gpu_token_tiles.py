@@ -19,7 +19,7 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(autouse=True)
 def gemv_passes_only(monkeypatch):
-    """This file is about the GEMV kernels' token tiles; more than 16 BF16 tokens would otherwise go to the GEMM."""
+    """This file is about the GEMV kernels' token tiles; more than 8 BF16 tokens on a GGUF-layout weight would otherwise go to the GEMM."""
     monkeypatch.setenv("B200Q_GEMM", "0")
 
 
