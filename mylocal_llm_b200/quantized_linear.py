@@ -254,6 +254,10 @@ def quantized_linear(x, weight, *, block_k=512, cpu_packed_backend="reference", 
 GEMM_MIN_TOKENS = {"Q4_K": 9, "Q5_K": 9, "Q6_K": 9, "Q8_0": 9}
 
 
+# quantized_swiglu: from three 8-token passes on, two GEMMs and an element-wise kernel beat the fused GEMV passes.
+SWIGLU_GEMM_MIN_TOKENS = 17
+
+
 def _use_gemm(weight, x, m, n, k, dt):
     """Enough tokens of BF16 activations on a GGUF-layout weight go to the tcgen05 GEMM (``b200q_gemm``:
     weights read once, BF16-weight precision); everything else stays on the GEMV kernels (exact
@@ -294,7 +298,14 @@ def quantized_swiglu(x, gate, up, *, block_k=512, out_dtype=None):
     torch = _torch()
     m = int(x.numel()) // k
     out = torch.empty((m, f), dtype=out_dtype or x.dtype, device=x.device)
-    if m:
+    if m >= SWIGLU_GEMM_MIN_TOKENS and _use_gemm(gate, x, m, f, k, dt) and _use_gemm(up, x, m, f, k, dt):
+        # many BF16 tokens on GGUF-layout weights: the two projections on the tensor-core GEMM (weights read once
+        # instead of once per 8-token pass), then the element-wise SiLU(gate) * up of the fused kernel
+        x2d = x.reshape(m, k)
+        gu = torch.cat([quantized_linear(x2d, gate, out_dtype=torch.float32),
+                        quantized_linear(x2d, up, out_dtype=torch.float32)], dim=1)
+        _lib.call("b200q_silu_mul", _ptr(gu), m, f, _ptr(out), _dtype_id(out), _lib.current_stream())
+    elif m:
         _lib.call("b200q_swiglu", _ptr(gate.data), _lib.FORMAT_ID[gate.quant_type], _ptr(up.data),
                   _lib.FORMAT_ID[up.quant_type], f, k, _ptr(x), dt, m, _ptr(out), _dtype_id(out),
                   _lib.current_stream())

@@ -205,3 +205,31 @@ def test_gemm_pairs_ctas_from_a_thousand_tokens_on(cuda, monkeypatch):
     monkeypatch.setenv("B200Q_GEMM_PAIR", "0")
     single = run_gemm(torch, w, x, torch.float32)
     torch.testing.assert_close(paired, single, rtol=2e-5, atol=2e-5 * float(single.abs().max()))
+
+
+@pytest.mark.parametrize("fmt", ["Q4_K", "Q6_K"])
+@pytest.mark.parametrize("m", [40, 300])
+def test_swiglu_of_many_bf16_tokens_runs_its_projections_on_the_gemm(cuda, monkeypatch, fmt, m):
+    from mylocal_llm_b200 import quantized_swiglu
+    from oracle import packed_oracle as po
+    torch = cuda
+    f, k = 384, 1024
+    rng = np.random.default_rng(m)
+    gate_w = quantize(rng.normal(0, 0.03, (f, k)).astype(np.float32), fmt)
+    up_w = quantize(rng.normal(0, 0.03, (f, k)).astype(np.float32), fmt)
+    gate, up = packed_to_device(gate_w), packed_to_device(up_w)
+    x = torch.from_numpy(rng.normal(0, 1, (m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    calls = []
+    real = _lib.call
+    monkeypatch.setattr(_lib, "call", lambda name, *a: (calls.append(name), real(name, *a))[1])
+    h = quantized_swiglu(x, gate, up, out_dtype=torch.float32)
+    assert calls == ["b200q_gemm", "b200q_gemm", "b200q_silu_mul"]
+    calls.clear()
+    monkeypatch.setenv("B200Q_GEMM", "0")
+    h_gemv = quantized_swiglu(x, gate, up, out_dtype=torch.float32)
+    assert calls == ["b200q_swiglu"]
+    ref = po.swiglu_fp64(x.float().cpu().numpy(), (gate_w.data, gate_w.shape, fmt), (up_w.data, up_w.shape, fmt))
+    scale = float(np.abs(ref).max())
+    np.testing.assert_allclose(h_gemv.cpu().numpy(), ref, rtol=3e-4, atol=2e-4)             # the exact-product path
+    # the GEMM route: BF16-rounded weights in both projections (2^-9 relative each) before the product of the two
+    assert float(np.abs(h.cpu().numpy() - ref).max()) <= 1e-2 * scale
