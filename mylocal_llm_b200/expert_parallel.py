@@ -331,7 +331,8 @@ class DeviceExpertEngine:
         extra = extra_scale = None
         if self.shared is not None and not self.folded:
             gate, up, down = self.shared
-            extra = quantized_linear(quantized_swiglu(x_home, gate, up, out_dtype=torch.float32), down)
+            extra = quantized_linear(quantized_swiglu(x_home, gate, up, out_dtype=torch.float32, allow_gemm=False), down,
+                                     allow_gemm=False)
             if self.shared_gate is not None:
                 extra_scale = moe_ops.shared_gate(x_home, self.shared_gate)
         return moe_ops.moe_combine_ids(terms_home, ids_home, self.bank.d_model, extra=extra, extra_scale=extra_scale,

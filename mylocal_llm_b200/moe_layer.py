@@ -203,8 +203,10 @@ class PackedMoELayer:
         extra = extra_scale = None
         if self.shared is not None:
             gate, up, down = self.shared
-            shared_hidden = quantized_swiglu(x2d, gate, up, out_dtype=torch.float32)
-            extra = quantized_linear(shared_hidden, down)
+            # (the GEMV kernels whatever the number of rows: a layer's result must not depend on how a batch is
+            # split over calls or ranks, and the tensor-core GEMM rounds its weights to BF16)
+            shared_hidden = quantized_swiglu(x2d, gate, up, out_dtype=torch.float32, allow_gemm=False)
+            extra = quantized_linear(shared_hidden, down, allow_gemm=False)
             if self.shared_gate is not None:
                 extra_scale = moe_ops.shared_gate(x2d, self.shared_gate)
         out = self.executor.forward_routed(self.layer_id, x2d, weights, ids, extra=extra, extra_scale=extra_scale,

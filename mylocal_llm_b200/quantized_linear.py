@@ -200,11 +200,13 @@ def _check_activation(x, what="Packed linear input"):
         raise TypeError(f"{what} must be a NumPy array or a torch CUDA tensor")
 
 
-def quantized_linear(x, weight, *, block_k=512, cpu_packed_backend="reference", out_dtype=None):
+def quantized_linear(x, weight, *, block_k=512, cpu_packed_backend="reference", out_dtype=None, allow_gemm=True):
     """``x @ weight.T`` for packed GGUF ``[out_features, in_features]`` on the GPU.
 
     ``out_dtype`` (an addition to the reference signature) selects the output element type;
-    by default the output has the activation dtype, as in the reference."""
+    by default the output has the activation dtype, as in the reference. ``allow_gemm=False`` keeps the call on
+    the GEMV kernels (exact products) whatever the number of tokens: for callers whose result must not depend on
+    how a batch is split."""
     _check_activation(x)
     if x.ndim not in (2, 3):
         raise ValueError("Expected x as [M, K] or [B, T, K]")
@@ -230,7 +232,7 @@ def quantized_linear(x, weight, *, block_k=512, cpu_packed_backend="reference", 
     n, k = weight.shape
     m = int(x.numel()) // k
     out = torch.empty((m, n), dtype=out_dtype or x.dtype, device=x.device)
-    if m and _use_gemm(weight, x, m, n, k, dt):
+    if m and allow_gemm and _use_gemm(weight, x, m, n, k, dt):
         fmt = _lib.FORMAT_ID[weight.quant_type]
         # shapes with few weight-row tiles split K over several CTAs, given scratch for the partial results
         nbytes = int(_lib.load().b200q_gemm_workspace_bytes(fmt, n, k, dt, m))
@@ -265,14 +267,14 @@ def _use_gemm(weight, x, m, n, k, dt):
     GEMV path."""
     import os
     if (weight.quant_type in DEVICE_LAYOUTS or m < GEMM_MIN_TOKENS.get(weight.quant_type, 1 << 30)
-            or os.environ.get("B200Q_GEMM", "1") == "0"):
+            or os.environ.get("B200Q_GEMM", "1") == "0" or os.environ.get("B200Q_KERNEL", "auto") != "auto"):
         return False
     if x.data_ptr() % 16 or weight.data.data_ptr() % (4 if weight.quant_type == "Q8_0" else 2):
         return False
     return bool(_lib.load().b200q_gemm_supported(_lib.FORMAT_ID[weight.quant_type], n, k, dt, m))
 
 
-def quantized_swiglu(x, gate, up, *, block_k=512, out_dtype=None):
+def quantized_swiglu(x, gate, up, *, block_k=512, out_dtype=None, allow_gemm=True):
     """``SiLU(x @ gate.T) * (x @ up.T)`` in one launch; gate/up formats may differ."""
     if not isinstance(gate, (PackedGGUFWeight, DevicePackedGGUFWeight)) or not isinstance(
             up, (PackedGGUFWeight, DevicePackedGGUFWeight)):
@@ -298,7 +300,8 @@ def quantized_swiglu(x, gate, up, *, block_k=512, out_dtype=None):
     torch = _torch()
     m = int(x.numel()) // k
     out = torch.empty((m, f), dtype=out_dtype or x.dtype, device=x.device)
-    if m >= SWIGLU_GEMM_MIN_TOKENS and _use_gemm(gate, x, m, f, k, dt) and _use_gemm(up, x, m, f, k, dt):
+    if (allow_gemm and m >= SWIGLU_GEMM_MIN_TOKENS and _use_gemm(gate, x, m, f, k, dt)
+            and _use_gemm(up, x, m, f, k, dt)):
         # many BF16 tokens on GGUF-layout weights: the two projections on the tensor-core GEMM (weights read once
         # instead of once per 8-token pass), then the element-wise SiLU(gate) * up of the fused kernel
         x2d = x.reshape(m, k)
